@@ -1,0 +1,309 @@
+"""numpy front end of the CPU oracle (oracle/w8a8_oracle.c) and of the compiled reference
+tile kernel (oracle/_ref/libzendnn_ref.so).
+
+TEST INFRASTRUCTURE ONLY.  Imported by tests/, by __graft_entry__.smoke() and by the CPU
+baseline legs of bench.py; the product package never imports it.
+
+bf16 tensors are carried as numpy uint16 arrays holding the bit patterns.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+# dtype / post-op codes of the reference (common/data_types.hpp:44-58,
+# operators/common/post_op.hpp:36-57)
+DT = dict(none=0, f32=1, f16=2, bf16=3, s32=4, s64=5, s16=6, s8=7, s4=8, u32=9, u16=10, u8=11, u4=12)
+PO = dict(none=0, elu=1, relu=2, leaky_relu=3, gelu_tanh=4, gelu_erf=5, sigmoid=6, swish=7, tanh=8,
+          softmax=9, pooling=10, square=11, abs=12, sqrt=13, exp=14, log=15, clip=16, binary_add=17,
+          binary_mul=18, mish=19)
+ACT = dict(none=0, silu_and_mul=1, gelu_and_mul=2, swiglu_oai_mul=3)
+
+
+def build(force=False):
+    """Compile liboracle.so (always possible) and, if a reference checkout exists, _ref."""
+    lib = os.path.join(_HERE, "liboracle.so")
+    if force or not os.path.exists(lib) or os.path.getmtime(lib) < os.path.getmtime(
+            os.path.join(_HERE, "w8a8_oracle.c")):
+        subprocess.check_call(["make", "-C", _HERE, "-s"])
+    ref_root = os.environ.get("ZENDNN_REFERENCE_ROOT", "/root/reference")
+    ref = os.path.join(_HERE, "_ref", "libzendnn_ref.so")
+    if os.path.isdir(ref_root) and (force or not os.path.exists(ref)):
+        subprocess.check_call(["make", "-C", _HERE, "-s", "ref", "REF=" + ref_root])
+
+
+class _PostOp(C.Structure):
+    _fields_ = [("type", C.c_int32), ("dt", C.c_int32), ("buff", C.c_void_p), ("ld", C.c_int64),
+                ("alpha", C.c_float), ("beta", C.c_float)]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        _lib = C.CDLL(path)
+        _lib.orc_gemm_s32.restype = C.c_int
+        _lib.orc_epilogue.restype = C.c_int
+    return _lib
+
+
+_ref = None
+
+
+def ref_lib():
+    """The compiled reference tile kernel, or None when absent / the host lacks AVX-512 VNNI+BF16."""
+    global _ref
+    if _ref is None:
+        path = os.path.join(_HERE, "_ref", "libzendnn_ref.so")
+        if not os.path.exists(path):
+            _ref = False
+        else:
+            try:
+                l = C.CDLL(path)
+                _ref = l if l.ref_available() else False
+            except OSError:
+                _ref = False
+    return _ref or None
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def f32_to_bf16(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().orc_f32_to_bf16(_p(x), _p(out), C.c_int64(x.size))
+    return out
+
+
+def bf16_to_f32(x):
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    return (x.astype(np.uint32) << 16).view(np.float32)
+
+
+def _dt_of(a):
+    return {np.dtype(np.float32): DT["f32"], np.dtype(np.uint16): DT["bf16"], np.dtype(np.int32): DT["s32"],
+            np.dtype(np.int8): DT["s8"], np.dtype(np.uint8): DT["u8"]}[a.dtype]
+
+
+def gemm_s32(A, B, transB=False):
+    """Exact int32 accumulators.  A [M,K] u8|s8; B [K,N] s8, or [N,K] when transB."""
+    A = np.ascontiguousarray(A)
+    B = np.ascontiguousarray(B)
+    M, K = A.shape
+    N = B.shape[0] if transB else B.shape[1]
+    out = np.empty((M, N), dtype=np.int32)
+    rc = lib().orc_gemm_s32(_p(A), int(A.dtype == np.uint8), C.c_int64(K), _p(B), C.c_int64(B.shape[1]),
+                            int(transB), M, N, K, _p(out), C.c_int64(N))
+    assert rc == 0
+    return out
+
+
+def colsum(B, transB=False):
+    B = np.ascontiguousarray(B)
+    K, N = (B.shape[1], B.shape[0]) if transB else B.shape
+    out = np.empty(N, dtype=np.int32)
+    lib().orc_colsum(_p(B), C.c_int64(B.shape[1]), int(transB), K, N, _p(out))
+    return out
+
+
+def _postops(postops, keep):
+    arr = (_PostOp * max(1, len(postops)))()
+    for i, po in enumerate(postops):
+        if isinstance(po, str):
+            po = dict(type=po)
+        arr[i].type = PO[po["type"]]
+        arr[i].alpha = po.get("alpha", 0.0)
+        arr[i].beta = po.get("beta", 0.0)
+        b = po.get("buff")
+        if b is not None:
+            b = np.ascontiguousarray(b)
+            keep.append(b)
+            arr[i].buff = b.ctypes.data
+            arr[i].dt = _dt_of(b)
+            arr[i].ld = 0 if (b.ndim == 1 or b.shape[0] == 1) else b.shape[1]
+    return arr
+
+
+def epilogue(acc, dst_dt="bf16", src_scale=None, wei_scale=None, src_zp=0, col_sum=None, bias=None,
+             postops=(), order=0):
+    """Dequantising epilogue over s32 accumulators; returns f32 / bf16-bits(uint16) / s32 array."""
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    M, N = acc.shape
+    keep = []
+    ss = None if src_scale is None else np.ascontiguousarray(np.asarray(src_scale, dtype=np.float32).reshape(-1))
+    ws = None if wei_scale is None else np.ascontiguousarray(np.asarray(wei_scale, dtype=np.float32).reshape(-1))
+    cs = None if col_sum is None else np.ascontiguousarray(col_sum, dtype=np.int32)
+    b = None if bias is None else np.ascontiguousarray(bias)
+    po = _postops(list(postops), keep)
+    out = np.empty((M, N), dtype={"bf16": np.uint16, "f32": np.float32, "s32": np.int32}[dst_dt])
+    rc = lib().orc_epilogue(_p(acc), C.c_int64(N), M, N, order, _p(ss), 0 if ss is None else ss.size,
+                            _p(ws), 0 if ws is None else ws.size, C.c_int32(int(src_zp)), _p(cs),
+                            _p(b), 0 if b is None else _dt_of(b), po, len(postops),
+                            _p(out), DT[dst_dt], C.c_int64(N))
+    assert rc == 0
+    return out
+
+
+def matmul_w8a8(A, B, dst_dt="bf16", transB=False, src_scale=None, wei_scale=None, src_zp=0, bias=None,
+                postops=(), order=0):
+    """matmul_direct INT8 semantics: exact GEMM then epilogue."""
+    acc = gemm_s32(A, B, transB)
+    cs = colsum(B, transB) if src_zp != 0 else None
+    return epilogue(acc, dst_dt, src_scale, wei_scale, src_zp, cs, bias, postops, order)
+
+
+def quant_per_token(x, scales_only=False):
+    """x [M,K] f32 or bf16-bits.  Returns (s8 [M,K] or None, f32 scales [M])."""
+    x = np.ascontiguousarray(x)
+    M, K = x.shape
+    q = None if scales_only else np.empty((M, K), dtype=np.int8)
+    s = np.empty(M, dtype=np.float32)
+    lib().orc_quant_per_token(_p(x), _dt_of(x), C.c_int64(M), C.c_int64(K), C.c_int64(K), _p(q),
+                              C.c_int64(K), _p(s))
+    return q, s
+
+
+def dyn_scales(x, per_channel=True):
+    x = np.ascontiguousarray(x)
+    M, N = x.shape
+    s = np.empty(N if per_channel else 1, dtype=np.float32)
+    lib().orc_dyn_scales(_p(x), _dt_of(x), C.c_int64(M), C.c_int64(N), C.c_int64(N), int(per_channel), _p(s))
+    return s
+
+
+def quant_static(x, scale, zp=None, dst_dt="s8"):
+    x = np.ascontiguousarray(x)
+    M, N = x.shape
+    scale = np.ascontiguousarray(np.asarray(scale, dtype=np.float32).reshape(-1))
+    z = None if zp is None else np.ascontiguousarray(np.asarray(zp, dtype=np.int32).reshape(-1))
+    out = np.empty((M, N), dtype=np.uint8 if dst_dt == "u8" else np.int8)
+    lib().orc_quant_static(_p(x), _dt_of(x), C.c_int64(M), C.c_int64(N), C.c_int64(N), _p(scale),
+                           C.c_int64(scale.size), _p(z), C.c_int64(0 if z is None else z.size), _p(out),
+                           DT[dst_dt], C.c_int64(N))
+    return out
+
+
+def dequant_static(q, scale, zp=None, dst_dt="f32"):
+    q = np.ascontiguousarray(q)
+    M, N = q.shape
+    scale = np.ascontiguousarray(np.asarray(scale, dtype=np.float32).reshape(-1))
+    z = None if zp is None else np.ascontiguousarray(np.asarray(zp, dtype=np.int32).reshape(-1))
+    out = np.empty((M, N), dtype=np.uint16 if dst_dt == "bf16" else np.float32)
+    lib().orc_dequant_static(_p(q), _dt_of(q), C.c_int64(M), C.c_int64(N), C.c_int64(N), _p(scale),
+                             C.c_int64(scale.size), _p(z), C.c_int64(0 if z is None else z.size), _p(out),
+                             DT[dst_dt], C.c_int64(N))
+    return out
+
+
+def quant_weights_per_channel(w):
+    """The reference tests' weight quantisation (gtests/gtest_utils.cpp:4269-4369): dynamic
+    per-column scale, then static quantise.  w [K,N] f32 or bf16-bits -> (s8 [K,N], f32 [N])."""
+    s = dyn_scales(w, per_channel=True)
+    return quant_static(w, s), s
+
+
+def gated_act(y, act="silu_and_mul"):
+    """In-place semantics on a copy: y [M, 2I] f32 or bf16-bits -> [M, I]."""
+    y = np.array(y, copy=True, order="C")
+    M, N = y.shape
+    lib().orc_gated_act(_p(y), _dt_of(y), C.c_int64(M), C.c_int64(N), C.c_int64(N), ACT[act])
+    return np.ascontiguousarray(y[:, : N // 2])
+
+
+def gated_act_f32_pairs(g, u, act="silu_and_mul", dst_dt="bf16"):
+    g = np.ascontiguousarray(g, dtype=np.float32)
+    u = np.ascontiguousarray(u, dtype=np.float32)
+    out = np.empty(g.shape, dtype=np.uint16 if dst_dt == "bf16" else np.float32)
+    lib().orc_gated_act_f32_pairs(_p(g), _p(u), C.c_int64(g.size), ACT[act], DT[dst_dt], _p(out))
+    return out
+
+
+def moe_weighted_reduce(rows, weights, topk, skip_weighted=False, fused=False):
+    """rows [T*topk, D] (slot order t*topk+k) f32 or bf16-bits; weights [T,topk] f32."""
+    rows = np.ascontiguousarray(rows)
+    T = rows.shape[0] // topk
+    D = rows.shape[1]
+    ptrs = (C.c_void_p * (T * topk))(*[rows.ctypes.data + i * rows.strides[0] for i in range(T * topk)])
+    w = np.ascontiguousarray(weights, dtype=np.float32)
+    out = np.empty((T, D), dtype=rows.dtype)
+    lib().orc_moe_weighted_reduce(ptrs, _p(w), T, topk, D, int(skip_weighted), _dt_of(rows), _p(out),
+                                  C.c_int64(D), int(fused))
+    return out
+
+
+def router_topk(logits, k, renorm=True):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    T, E = logits.shape
+    ids = np.empty((T, k), dtype=np.int32)
+    w = np.empty((T, k), dtype=np.float32)
+    lib().orc_router_topk(_p(logits), T, E, k, int(renorm), _p(ids), _p(w))
+    return ids, w
+
+
+def fused_moe(x_bf16, ids, weights, w13, s13, w2, s2, act="silu_and_mul", round_before_act=False):
+    """Dynamic-INT8 fused MoE data flow of group_matmul_direct
+    (group_matmul/group_matmul_fused_moe.cpp:906-1078; test convention
+    gtests/group_matmul/test_fused_moe.cpp:2565-2676).
+
+    x_bf16 [T,H] bf16-bits; ids/weights [T,k]; w13[e] s8 [H,2I] ([gate|up]) with scales s13[e] [2I];
+    w2[e] s8 [I,H] with s2[e] [H].  Rows are gathered per expert in token order (stable), each
+    expert runs quant -> GEMM -> act -> bf16 -> quant -> GEMM -> bf16, then the top-k weighted
+    reduce.  round_before_act selects the separate-pass form (Op1 output rounded to bf16 before
+    the activation, group_matmul_moe_act.cpp:110-117); default is the fused-epilogue form
+    (group_matmul_act_avx512.hpp:62-70).  Returns (out [T,H] bf16-bits, expert row outputs
+    [T*k, H] in slot order)."""
+    T, H = x_bf16.shape
+    k = ids.shape[1]
+    E = len(w13)
+    slot_out = np.zeros((T * k, H), dtype=np.uint16)
+    flat = ids.reshape(-1)
+    for e in range(E):
+        slots = np.nonzero(flat == e)[0]
+        if slots.size == 0:
+            continue
+        xe = np.ascontiguousarray(x_bf16[slots // k])
+        q1, sc1 = quant_per_token(xe)
+        acc1 = gemm_s32(q1, w13[e])
+        I = acc1.shape[1] // 2
+        if round_before_act:
+            y = epilogue(acc1, "bf16", sc1, s13[e])
+            z = gated_act(y, act)
+        else:
+            y = epilogue(acc1, "f32", sc1, s13[e])
+            if act == "swiglu_oai_mul":
+                z = gated_act_f32_pairs(y[:, 0::2], y[:, 1::2], act)
+            else:
+                z = gated_act_f32_pairs(y[:, :I], y[:, I:], act)
+        q2, sc2 = quant_per_token(z)
+        o = matmul_w8a8(q2, w2[e], "bf16", src_scale=sc2, wei_scale=s2[e])
+        slot_out[slots] = o
+    out = moe_weighted_reduce(slot_out, weights, k)
+    return out, slot_out
+
+
+def ref_int8_matmul(A_u8, B_s8, src_zp, src_scale, wei_scale, bias=None, fused_op=0, dst_dt="bf16"):
+    """Runs the compiled reference tile kernel (per-tensor src scale/zp).  None if unavailable."""
+    r = ref_lib()
+    if r is None:
+        return None
+    A = np.ascontiguousarray(A_u8, dtype=np.uint8)
+    B = np.ascontiguousarray(B_s8, dtype=np.int8)
+    M, K = A.shape
+    N = B.shape[1]
+    ws = np.ascontiguousarray(np.asarray(wei_scale, dtype=np.float32).reshape(-1))
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    out = np.empty((M, N), dtype=np.uint16 if dst_dt == "bf16" else np.float32)
+    rc = r.ref_int8_matmul(_p(A), K, _p(B), N, M, N, K, C.c_int32(int(src_zp)), C.c_float(float(src_scale)),
+                           _p(ws), int(ws.size), _p(b), int(fused_op),
+                           _p(out) if dst_dt == "bf16" else None, _p(out) if dst_dt == "f32" else None, N)
+    return out if rc == 0 else None

@@ -1,0 +1,448 @@
+/*
+ * CPU oracle for the LowOHA W8A8 hot path.  TEST INFRASTRUCTURE ONLY: this file is the
+ * checker the CUDA kernels are compared against and the CPU baseline that the benchmark
+ * times.  Nothing in the product library links or calls it.
+ *
+ * It restates, in plain C, the arithmetic of the reference (amd/ZenDNN, "ZenDNNL" 6.0.1).
+ * The reference's default INT8 GEMM lives in a third-party library that is not part of the
+ * reference tree (amd/aocl-dlp, pinned by cmake/ZenDnnlDependenciesInfo.cmake:34-35 to tag
+ * AOCL-202606W01, commit b3db7f5800aca3ba3ce5bdfab10f557c5b896e5a); what is restated here is
+ * the formula the reference requests from it and the in-tree statements of the same math.
+ * Each function cites the reference file:line it follows (paths relative to the reference
+ * root).
+ *
+ * Parity pin: the "order B" epilogue below is checked bit-for-bit against the reference's
+ * own AVX-512 VNNI tile kernel (int8_brgemm_ukernel.cpp) compiled from the reference
+ * sources, and the outputs of that kernel are committed as golden fixtures.  The quantise,
+ * gated-activation and weighted-reduce functions follow scalar reference code that has no
+ * golden vectors in the reference tests (its tests are differential); for those parity is
+ * pinned by formula only.  The router (softmax/top-k/renormalise) has no counterpart in the
+ * reference at all: parity unpinned.
+ *
+ * Build: see oracle/Makefile (gcc -O2 -fopenmp -ffp-contract=off; the VNNI loop is selected
+ * at run time so the same .so runs on hosts without AVX-512).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <immintrin.h>
+
+#define ORC_API __attribute__((visibility("default")))
+
+/* data_type_t values of the reference (common/data_types.hpp:44-58) */
+enum { DT_NONE = 0, DT_F32 = 1, DT_F16 = 2, DT_BF16 = 3, DT_S32 = 4, DT_S8 = 7, DT_U8 = 11 };
+/* post_op_type_t values of the reference (operators/common/post_op.hpp:36-57) */
+enum { PO_NONE = 0, PO_ELU = 1, PO_RELU = 2, PO_LEAKY_RELU = 3, PO_GELU_TANH = 4, PO_GELU_ERF = 5,
+       PO_SIGMOID = 6, PO_SWISH = 7, PO_TANH = 8, PO_CLIP = 16, PO_BINARY_ADD = 17,
+       PO_BINARY_MUL = 18, PO_MISH = 19 };
+
+/* ---- bf16 <-> f32: common/bfloat16.cpp:68-82 (RNE on the bit pattern, no NaN case) ---- */
+static inline float bf16_to_f32(uint16_t h) {
+  uint32_t u = (uint32_t)h << 16; float f; memcpy(&f, &u, 4); return f;
+}
+static inline uint16_t f32_to_bf16(float f) {
+  uint32_t u; memcpy(&u, &f, 4);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+ORC_API void orc_f32_to_bf16(const float *src, uint16_t *dst, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) dst[i] = f32_to_bf16(src[i]);
+}
+ORC_API void orc_bf16_to_f32(const uint16_t *src, float *dst, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) dst[i] = bf16_to_f32(src[i]);
+}
+static inline float load_as_f32(const void *p, int dt, int64_t i) {
+  switch (dt) {
+  case DT_F32: return ((const float *)p)[i];
+  case DT_BF16: return bf16_to_f32(((const uint16_t *)p)[i]);
+  case DT_S32: return (float)((const int32_t *)p)[i];
+  case DT_S8: return (float)((const int8_t *)p)[i];
+  case DT_U8: return (float)((const uint8_t *)p)[i];
+  default: return 0.f;
+  }
+}
+
+/* ======================================================================================
+ * Exact int32 GEMM.  acc[m,n] = sum_k (int32)A[m,k] * (int32)B[k,n], no saturation, no
+ * float anywhere: the arithmetic vpdpbusd performs in the reference's VNNI kernels
+ * (matmul_native/brgemm/kernel/int8/int8_brgemm_ukernel.cpp:60-88) and the formula of the
+ * scalar kernel (operators/matmul/matmul_ref_kernel.cpp:1005-1029) *without* its float
+ * store, which rounds above 2^24.
+ * ====================================================================================== */
+
+/* column sums of B over K (lru_cache/lowoha_cache.hpp:99-133 computes -zp * this) */
+ORC_API void orc_colsum(const int8_t *B, int64_t ldb, int transB, int K, int N, int32_t *colsum) {
+  #pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    int32_t s = 0;
+    if (transB) for (int k = 0; k < K; ++k) s += B[(int64_t)n * ldb + k];
+    else        for (int k = 0; k < K; ++k) s += B[(int64_t)k * ldb + n];
+    colsum[n] = s;
+  }
+}
+
+static void gemm_rows_scalar(const uint8_t *Au, const int8_t *Bt, int K4, int m0, int m1, int N,
+                             int32_t *C, int64_t ldc) {
+  for (int m = m0; m < m1; ++m)
+    for (int n = 0; n < N; ++n) {
+      const uint8_t *a = Au + (int64_t)m * K4; const int8_t *b = Bt + (int64_t)n * K4;
+      int32_t s = 0;
+      for (int k = 0; k < K4; ++k) s += (int32_t)a[k] * (int32_t)b[k];
+      C[(int64_t)m * ldc + n] = s;
+    }
+}
+
+__attribute__((target("avx512f,avx512bw,avx512vl,avx512vnni")))
+static void gemm_rows_vnni(const uint8_t *Au, const int8_t *Bt, int K4, int m0, int m1, int N,
+                           int32_t *C, int64_t ldc) {
+  /* 4 rows x 4 columns of dot products per step; both operands K-contiguous */
+  for (int m = m0; m < m1; m += 4) {
+    int mr = m1 - m < 4 ? m1 - m : 4;
+    for (int n = 0; n < N; n += 4) {
+      int nr = N - n < 4 ? N - n : 4;
+      __m512i acc[4][4];
+      for (int i = 0; i < 4; ++i) for (int j = 0; j < 4; ++j) acc[i][j] = _mm512_setzero_si512();
+      for (int k = 0; k < K4; k += 64) {
+        int rem = K4 - k;
+        __mmask64 msk = rem >= 64 ? ~(__mmask64)0 : (((__mmask64)1 << rem) - 1);
+        __m512i bv[4], av[4];
+        for (int j = 0; j < 4; ++j)
+          bv[j] = j < nr ? _mm512_maskz_loadu_epi8(msk, Bt + (int64_t)(n + j) * K4 + k) : _mm512_setzero_si512();
+        for (int i = 0; i < 4; ++i)
+          av[i] = i < mr ? _mm512_maskz_loadu_epi8(msk, Au + (int64_t)(m + i) * K4 + k) : _mm512_setzero_si512();
+        for (int i = 0; i < 4; ++i) for (int j = 0; j < 4; ++j)
+          acc[i][j] = _mm512_dpbusd_epi32(acc[i][j], av[i], bv[j]);
+      }
+      for (int i = 0; i < mr; ++i) for (int j = 0; j < nr; ++j)
+        C[(int64_t)(m + i) * ldc + n + j] = _mm512_reduce_add_epi32(acc[i][j]);
+    }
+  }
+}
+
+static int have_vnni(void) {
+  static int v = -1;
+  if (v < 0) {
+    __builtin_cpu_init();
+    v = __builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512bw") &&
+        __builtin_cpu_supports("avx512vl") && !getenv("ORC_NO_VNNI");
+  }
+  return v;
+}
+
+/* A: [M,lda] u8 (a_unsigned=1) or s8; B: [K,ldb] row-major, or [N,ldb] when transB. */
+ORC_API int orc_gemm_s32(const void *A, int a_unsigned, int64_t lda, const int8_t *B, int64_t ldb,
+                         int transB, int M, int N, int K, int32_t *C, int64_t ldc) {
+  if (M <= 0 || N <= 0) return 0;
+  int K4 = (K + 3) & ~3;
+  if (K4 == 0) { for (int m = 0; m < M; ++m) memset(C + (int64_t)m * ldc, 0, 4 * (size_t)N); return 0; }
+  /* operands repacked K-contiguous; s8 A is biased to u8 (+128) and corrected below */
+  uint8_t *Au = (uint8_t *)calloc((size_t)M * K4, 1);
+  int8_t *Bt = (int8_t *)calloc((size_t)N * K4, 1);
+  int32_t *cs = (int32_t *)malloc(4 * (size_t)N);
+  if (!Au || !Bt || !cs) { free(Au); free(Bt); free(cs); return -1; }
+  #pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    const uint8_t *a = (const uint8_t *)A + (int64_t)m * lda;
+    for (int k = 0; k < K; ++k) Au[(int64_t)m * K4 + k] = a_unsigned ? a[k] : (uint8_t)(a[k] ^ 0x80);
+    if (!a_unsigned) for (int k = K; k < K4; ++k) Au[(int64_t)m * K4 + k] = 0x80;
+  }
+  if (transB) {
+    #pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n) memcpy(Bt + (int64_t)n * K4, B + (int64_t)n * ldb, (size_t)K);
+  } else {
+    #pragma omp parallel for schedule(static)
+    for (int n0 = 0; n0 < N; n0 += 64)
+      for (int k = 0; k < K; ++k)
+        for (int n = n0; n < N && n < n0 + 64; ++n) Bt[(int64_t)n * K4 + k] = B[(int64_t)k * ldb + n];
+  }
+  #pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    int32_t s = 0; for (int k = 0; k < K4; ++k) s += Bt[(int64_t)n * K4 + k]; cs[n] = s;
+  }
+  int vn = have_vnni();
+  #pragma omp parallel for schedule(dynamic, 1)
+  for (int m0 = 0; m0 < M; m0 += 8) {
+    int m1 = m0 + 8 < M ? m0 + 8 : M;
+    if (vn) gemm_rows_vnni(Au, Bt, K4, m0, m1, N, C, ldc);
+    else    gemm_rows_scalar(Au, Bt, K4, m0, m1, N, C, ldc);
+    if (!a_unsigned)
+      for (int m = m0; m < m1; ++m)
+        for (int n = 0; n < N; ++n) C[(int64_t)m * ldc + n] -= 128 * cs[n];
+  }
+  free(Au); free(Bt); free(cs);
+  return 0;
+}
+
+/* ======================================================================================
+ * Element-wise post-ops: operators/matmul/matmul_ref_kernel.cpp:694-761 with the constants
+ * of matmul_ref_kernel.hpp:31-33.  Double-typed literals of the reference are kept double.
+ * The LowOHA mapping (backends/aocl/aocl_postop.cpp:404-441) fixes swish's scale to 1, the
+ * leaky-relu slope to 0.01 (aocl_postop.hpp:33), clip to (alpha=lower, beta=upper), and
+ * gives binary add/mul no scale.
+ * ====================================================================================== */
+#define SQRT_2_OVER_PI 0.79788458347320556640625f
+#define SQRT_2_OVER_2 0.707106769084930419921875f
+#define FITTING_CONST 0.044715f
+
+static inline float po_gelu_tanh(float x) {
+  float v = tanhf(SQRT_2_OVER_PI * x * (1 + FITTING_CONST * x * x));
+  return (float)(0.5 * x * (1.0f + v));
+}
+static inline float po_gelu_erf(float x) { float v = x * SQRT_2_OVER_2; return 0.5f * x * (1.0f + erff(v)); }
+static inline float po_sigmoid(float x) { return (float)(1.0 / (1.0 + expf(-x))); }
+static inline float po_swish(float x, float s) { float sx = x * s; return (float)(x * (1.0 / (1.0 + expf(-sx)))); }
+
+typedef struct {
+  int32_t type;       /* post_op_type_t */
+  int32_t dt;         /* dtype of buff for binary ops */
+  const void *buff;   /* binary operand */
+  int64_t ld;         /* 0: {1,N} row broadcast; >0: dense [M,ld] */
+  float alpha, beta;
+} orc_postop;
+
+static inline float apply_postop(const orc_postop *p, float x, int m, int n) {
+  switch (p->type) {
+  case PO_RELU: return x > 0 ? x : 0;
+  case PO_LEAKY_RELU: return x > 0 ? x : 0.01f * x;
+  case PO_ELU: return x > 0 ? x : (float)(p->alpha * (expf(x) - 1.0));
+  case PO_GELU_TANH: return po_gelu_tanh(x);
+  case PO_GELU_ERF: return po_gelu_erf(x);
+  case PO_SIGMOID: return po_sigmoid(x);
+  case PO_SWISH: return po_swish(x, 1.0f);
+  case PO_TANH: return tanhf(x);
+  case PO_CLIP: { float lo = p->alpha, hi = p->beta; x = x > lo ? x : lo; return x > hi ? hi : x; }
+  case PO_BINARY_ADD: return x + load_as_f32(p->buff, p->dt, p->ld ? (int64_t)m * p->ld + n : n);
+  case PO_BINARY_MUL: return x * load_as_f32(p->buff, p->dt, p->ld ? (int64_t)m * p->ld + n : n);
+  default: return x;
+  }
+}
+
+/* ======================================================================================
+ * Dequantising epilogue over exact s32 accumulators.
+ *   order 0 ("A"/"A'"/"C"): what matmul_direct requests from the GEMM backend
+ *     (backends/aocl/aocl_postop.cpp:1339-1453): zero-point compensation added in s32
+ *     (comp[n] = -src_zp * colsum[n], lru_cache/lowoha_cache.hpp:99-133), then x*src_scale,
+ *     then *wei_scale[n] (two separate f32 multiplies), +bias[n], post-ops in list order,
+ *     RNE to dst.  With a per-token src scale this is the "sym_quant" group post-op
+ *     (aocl_postop.cpp:1279-1304) and the group custom micro-kernel
+ *     (group_matmul/custom_kernel/ukernel/int8_microkernel.cpp:161-177).
+ *   order 1 ("B"): the in-tree native VNNI kernel (int8_brgemm_ukernel.cpp:91-129):
+ *     x = fma(-(float)zp, (float)colsum[n], (float)acc); x *= (src_scale * wei_scale[n]);
+ *     +bias; one activation; bf16/f32 store.  Used to validate against the compiled
+ *     reference kernel; per-tensor src scale only.
+ * dst_dt: f32, bf16, or s32 (s32: compensated accumulators, scales/bias/post-ops rejected
+ * by the caller).  n_src_scale is 1 or M; n_wei_scale 0, 1 or N.
+ * ====================================================================================== */
+ORC_API int orc_epilogue(const int32_t *acc, int64_t ldacc, int M, int N, int order,
+                         const float *src_scale, int n_src_scale, const float *wei_scale, int n_wei_scale,
+                         int32_t src_zp, const int32_t *colsum,
+                         const void *bias, int bias_dt, const orc_postop *po, int npo,
+                         void *dst, int dst_dt, int64_t ldc) {
+  if (src_zp != 0 && !colsum) return -1;
+  #pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    for (int n = 0; n < N; ++n) {
+      int32_t a = acc[(int64_t)m * ldacc + n];
+      float x;
+      if (order == 1) {
+        float ws = n_wei_scale > 1 ? wei_scale[n] : (n_wei_scale == 1 ? wei_scale[0] : 1.0f);
+        float cs = colsum ? (float)colsum[n] : 0.0f;
+        x = fmaf(-(float)src_zp, cs, (float)a);
+        x = x * (src_scale[0] * ws);
+      } else {
+        if (src_zp != 0) a = (int32_t)((uint32_t)a + (uint32_t)(-src_zp * colsum[n]));
+        if (dst_dt == DT_S32) { ((int32_t *)dst)[(int64_t)m * ldc + n] = a; continue; }
+        x = (float)a;
+        if (n_src_scale > 0) x = x * src_scale[n_src_scale > 1 ? m : 0];
+        if (n_wei_scale > 0) x = x * wei_scale[n_wei_scale > 1 ? n : 0];
+      }
+      if (bias) x = x + load_as_f32(bias, bias_dt, n);
+      for (int i = 0; i < npo; ++i) x = apply_postop(&po[i], x, m, n);
+      if (dst_dt == DT_BF16) ((uint16_t *)dst)[(int64_t)m * ldc + n] = f32_to_bf16(x);
+      else ((float *)dst)[(int64_t)m * ldc + n] = x;
+    }
+  }
+  return 0;
+}
+
+/* ======================================================================================
+ * Quantisation.
+ * ====================================================================================== */
+
+/* Per-token symmetric dynamic quant: reorder/reorder_data_type/scalar_impl/
+ * dynamic_per_token_ref_kernel.cpp:31-36 (scale) and :70-124 (rows): absmax over finite
+ * values, clamp 1e-10, scale = absmax/127, clamp 1e-10, q = (int8) nearbyint(v / scale) with
+ * true division; non-finite -> 0.  dst==NULL computes scales only (lowoha_reorder.cpp:198-201). */
+ORC_API void orc_quant_per_token(const void *src, int src_dt, int64_t M, int64_t K, int64_t src_stride,
+                                 int8_t *dst, int64_t dst_stride, float *scales) {
+  #pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    float absmax = 0.0f;
+    for (int64_t j = 0; j < K; ++j) {
+      float v = load_as_f32(src, src_dt, m * src_stride + j);
+      if (isfinite(v)) absmax = fmaxf(absmax, fabsf(v));
+    }
+    if (absmax < 1e-10f) absmax = 1e-10f;
+    float scale = absmax / 127.0f;
+    if (scale < 1e-10f) scale = 1e-10f;
+    scales[m] = scale;
+    if (!dst) continue;
+    for (int64_t j = 0; j < K; ++j) {
+      float v = load_as_f32(src, src_dt, m * src_stride + j);
+      int8_t q = 0;
+      if (isfinite(v)) q = (int8_t)(int32_t)nearbyintf(v / scale);
+      dst[m * dst_stride + j] = q;
+    }
+  }
+}
+
+/* Dynamic symmetric scales at per-channel (one per column, dims {1,N}) or per-tensor
+ * granularity: reorder/lowoha_reorder_utils.cpp:708-766 (scale from min/max), :908-935
+ * (per-column scan over finite values). */
+ORC_API void orc_dyn_scales(const void *src, int src_dt, int64_t M, int64_t N, int64_t ld,
+                            int per_channel, float *scales) {
+  int64_t cnt = per_channel ? N : 1;
+  for (int64_t c = 0; c < cnt; ++c) {
+    float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+    int64_t n0 = per_channel ? c : 0, n1 = per_channel ? c + 1 : N;
+    for (int64_t m = 0; m < M; ++m)
+      for (int64_t n = n0; n < n1; ++n) {
+        float v = load_as_f32(src, src_dt, m * ld + n);
+        if (isfinite(v)) { mn = fminf(mn, v); mx = fmaxf(mx, v); }
+      }
+    if (mn == 3.402823466e+38f && mx == -3.402823466e+38f) { mn = 0.f; mx = 0.f; }
+    float am = fmaxf(fabsf(mn), fabsf(mx));
+    if (am < 1e-10f) am = 1e-10f;
+    float s = am / 127.0f;
+    if (s < 1e-10f) s = 1e-10f;
+    scales[c] = s;
+  }
+}
+
+/* Static quantise to s8 / u8: q = clamp(nearbyint(x / s) + zp): reorder/lowoha_reorder_utils.hpp:
+ * 148-153 and reorder_data_type/scalar_impl/scalar_ref_kernels.cpp:28-56.  n_scale 1 or N. */
+ORC_API void orc_quant_static(const void *src, int src_dt, int64_t M, int64_t N, int64_t ld,
+                              const float *scale, int64_t n_scale, const int32_t *zp, int64_t n_zp,
+                              void *dst, int dst_dt, int64_t dst_ld) {
+  int lo = dst_dt == DT_U8 ? 0 : -128, hi = dst_dt == DT_U8 ? 255 : 127;
+  #pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m)
+    for (int64_t n = 0; n < N; ++n) {
+      float v = load_as_f32(src, src_dt, m * ld + n);
+      float s = scale[n_scale > 1 ? n : 0];
+      int32_t z = zp ? zp[n_zp > 1 ? n : 0] : 0;
+      int32_t q = (int32_t)nearbyintf(v / s) + z;
+      q = q < lo ? lo : (q > hi ? hi : q);
+      if (dst_dt == DT_U8) ((uint8_t *)dst)[m * dst_ld + n] = (uint8_t)q;
+      else ((int8_t *)dst)[m * dst_ld + n] = (int8_t)q;
+    }
+}
+
+/* Static dequantise: x = (q - zp) * s (scalar_ref_kernels.cpp:28-56), f32 or bf16 dst. */
+ORC_API void orc_dequant_static(const void *src, int src_dt, int64_t M, int64_t N, int64_t ld,
+                                const float *scale, int64_t n_scale, const int32_t *zp, int64_t n_zp,
+                                void *dst, int dst_dt, int64_t dst_ld) {
+  #pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m)
+    for (int64_t n = 0; n < N; ++n) {
+      int32_t q = src_dt == DT_U8 ? (int32_t)((const uint8_t *)src)[m * ld + n]
+                                  : (int32_t)((const int8_t *)src)[m * ld + n];
+      int32_t z = zp ? zp[n_zp > 1 ? n : 0] : 0;
+      float x = (float)(q - z) * scale[n_scale > 1 ? n : 0];
+      if (dst_dt == DT_BF16) ((uint16_t *)dst)[m * dst_ld + n] = f32_to_bf16(x);
+      else ((float *)dst)[m * dst_ld + n] = x;
+    }
+}
+
+/* ======================================================================================
+ * Gated activations over a [M, N] row (N = 2*I): group_matmul/group_matmul_moe_act.cpp:88-196.
+ * In place; result occupies the first I columns.  act: 1 silu_and_mul, 2 gelu_and_mul (erf),
+ * 3 swiglu_oai_mul (interleaved pairs, clamp +-7, alpha 1.702)
+ * (group_matmul/group_matmul_direct.hpp:153-158).
+ * ====================================================================================== */
+static inline float act_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+static inline float gated(int act, float g, float u) {
+  if (act == 1) return (g * act_sigmoid(g)) * u;
+  if (act == 2) return (g * 0.5f * (1.0f + erff(g * 0.70710678118654752440f))) * u;
+  g = fmaxf(-7.0f, fminf(g, 7.0f)); u = fmaxf(-7.0f, fminf(u, 7.0f));
+  return (1.0f + u) * g * act_sigmoid(g * 1.702f);
+}
+ORC_API void orc_gated_act(void *buf, int dt, int64_t M, int64_t N, int64_t ldc, int act) {
+  int64_t I = N / 2;
+  #pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m)
+    for (int64_t n = 0; n < I; ++n) {
+      int64_t gi = act == 3 ? 2 * n : n, ui = act == 3 ? 2 * n + 1 : I + n;
+      if (dt == DT_BF16) {
+        uint16_t *row = (uint16_t *)buf + m * ldc;
+        row[n] = f32_to_bf16(gated(act, bf16_to_f32(row[gi]), bf16_to_f32(row[ui])));
+      } else {
+        float *row = (float *)buf + m * ldc;
+        row[n] = gated(act, row[gi], row[ui]);
+      }
+    }
+}
+/* Same activation on f32 (g,u) pairs held separately, rounding once to dt: the arithmetic of
+ * the fused in-register epilogue (group_matmul/group_matmul_act_avx512.hpp:62-70). */
+ORC_API void orc_gated_act_f32_pairs(const float *g, const float *u, int64_t n, int act, int dt, void *out) {
+  for (int64_t i = 0; i < n; ++i) {
+    float r = gated(act, g[i], u[i]);
+    if (dt == DT_BF16) ((uint16_t *)out)[i] = f32_to_bf16(r); else ((float *)out)[i] = r;
+  }
+}
+
+/* ======================================================================================
+ * MoE weighted reduce: group_matmul/group_matmul_moe_postop.cpp:103-129.
+ * out[t,d] = sum_k w[t,k] * row_ptrs[t*topk+k][d]; f32 accumulation in k order starting from
+ * 0 (acc += w*x, no contraction); RNE store.  The AVX-512 form (:216-283) multiplies for k=0
+ * and then uses fused multiply-adds; `fused` selects that association.
+ * ====================================================================================== */
+ORC_API void orc_moe_weighted_reduce(const void *const *row_ptrs, const float *w, int T, int topk, int D,
+                                     int skip_weighted, int dt, void *out, int64_t ld_out, int fused) {
+  #pragma omp parallel for schedule(static)
+  for (int t = 0; t < T; ++t)
+    for (int d = 0; d < D; ++d) {
+      float acc = 0.f;
+      for (int k = 0; k < topk; ++k) {
+        float wk = skip_weighted ? 1.f : w[(int64_t)t * topk + k];
+        float x = load_as_f32(row_ptrs[(int64_t)t * topk + k], dt, d);
+        if (fused) acc = k == 0 ? wk * x : fmaf(wk, x, acc);
+        else acc = acc + wk * x;
+      }
+      if (dt == DT_BF16) ((uint16_t *)out)[(int64_t)t * ld_out + d] = f32_to_bf16(acc);
+      else ((float *)out)[(int64_t)t * ld_out + d] = acc;
+    }
+}
+
+/* ======================================================================================
+ * Router front end.  NOT in the reference (its callers do this before group_matmul_direct,
+ * examples/lowoha_group_matmul_example.cpp:273-300): parity unpinned.  Specification:
+ * softmax over E in f32 (subtract row max, expf, sequential sum in index order, divide),
+ * top-k by probability with ties to the lower expert index, renormalise the k weights by
+ * their sequential sum in descending order.  Outputs ids [T,k] and weights [T,k].
+ * ====================================================================================== */
+ORC_API void orc_router_topk(const float *logits, int T, int E, int k, int renorm, int32_t *ids, float *w) {
+  #pragma omp parallel for schedule(static)
+  for (int t = 0; t < T; ++t) {
+    const float *l = logits + (int64_t)t * E;
+    float *p = (float *)malloc(4 * (size_t)E);
+    float mx = l[0];
+    for (int e = 1; e < E; ++e) mx = fmaxf(mx, l[e]);
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) { p[e] = expf(l[e] - mx); sum = sum + p[e]; }
+    for (int e = 0; e < E; ++e) p[e] = p[e] / sum;
+    float tot = 0.f;
+    for (int j = 0; j < k; ++j) {
+      int best = -1;
+      for (int e = 0; e < E; ++e) {
+        int taken = 0;
+        for (int q = 0; q < j; ++q) taken |= ids[(int64_t)t * k + q] == e;
+        if (!taken && (best < 0 || p[e] > p[best])) best = e;
+      }
+      ids[(int64_t)t * k + j] = best; w[(int64_t)t * k + j] = p[best]; tot = tot + p[best];
+    }
+    if (renorm) for (int j = 0; j < k; ++j) w[(int64_t)t * k + j] = w[(int64_t)t * k + j] / tot;
+    free(p);
+  }
+}
