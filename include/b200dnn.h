@@ -1,0 +1,205 @@
+/*
+ * b200dnn.h -- C ABI of the B200-native LowOHA W8A8 hot path (libb200dnn.so).
+ *
+ * Plain C, plain pointers and sizes.  Every entry point names the reference (amd/ZenDNN)
+ * interface it stands in for; paths are relative to the reference root,
+ * zendnnl/src/lowoha_operators/ unless stated.  The C++ shims that keep the reference's
+ * own signatures (include/zendnnl_b200/lowoha.hpp) are thin callers of these functions.
+ *
+ * Conventions
+ *  - Return value: the reference's status_t as int32 (common/error_status.hpp:34-58):
+ *    1 success, 0 failure (contract violation or CUDA error), -1 unimplemented.
+ *    b200dnn_last_error() gives the text for the calling thread.
+ *  - Data pointers may be host or device pointers, independently; each is classified with
+ *    cudaPointerGetAttributes.  Host buffers are staged through library-owned device
+ *    workspace (inputs copied in, outputs copied back before the call returns).  With device
+ *    pointers the call only enqueues work on `stream` and returns.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *  - dtype codes are the reference's data_type_t (common/data_types.hpp:44-58):
+ *    1 f32, 3 bf16, 4 s32, 7 s8, 11 u8.  Post-op codes are post_op_type_t
+ *    (../operators/common/post_op.hpp:36-57).
+ *  - There is no CPU fallback anywhere: without a usable CUDA device every compute entry
+ *    point returns failure.
+ */
+#ifndef B200DNN_H
+#define B200DNN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200DNN_API __attribute__((visibility("default")))
+#else
+#define B200DNN_API
+#endif
+
+#define B200DNN_SUCCESS 1
+#define B200DNN_FAILURE 0
+#define B200DNN_UNIMPLEMENTED (-1)
+
+enum { B200DNN_F32 = 1, B200DNN_BF16 = 3, B200DNN_S32 = 4, B200DNN_S8 = 7, B200DNN_U8 = 11 };
+enum { B200DNN_MAX_POSTOPS = 8 };
+
+/* One scale / zero-point tensor: matmul_quantization_params_t::matmul_quant_t
+ * (matmul/lowoha_common.hpp:67-86).  count = number of elements: 1 per-tensor,
+ * M per-token ({M,1}), N per-channel ({1,N}); 0 = absent. */
+typedef struct b200dnn_quant_t {
+  const void *buff;
+  int32_t dt;
+  int32_t reserved;
+  int64_t count;
+} b200dnn_quant_t;
+
+/* One post-op: matmul_post_op (matmul/lowoha_common.hpp:53-65).  For binary_add/mul,
+ * ld == 0 means a {1,N} row broadcast, ld > 0 a dense [M,ld] operand.  clip: alpha = lower,
+ * beta = upper (matmul/backends/aocl/aocl_postop.cpp:424-433). */
+typedef struct b200dnn_postop_t {
+  int32_t type;
+  int32_t dt;
+  const void *buff;
+  int64_t ld;
+  float alpha;
+  float beta;
+} b200dnn_postop_t;
+
+/* Flat form of the arguments of matmul_direct (matmul/lowoha_matmul.hpp:104-108) plus the
+ * fields of matmul_params it reads on the INT8 path (matmul/lowoha_common.hpp:142-227). */
+typedef struct b200dnn_matmul_t {
+  int32_t M, N, K;
+  int32_t transB;        /* 0: weight is [K,ldb]; 1: weight is [N,ldb] */
+  int32_t src_dt;        /* u8 | s8, or bf16 | f32 together with dynamic_quant */
+  int32_t wei_dt;        /* s8 */
+  int32_t dst_dt;        /* bf16 | f32 | s32 */
+  int32_t bias_dt;       /* f32 | bf16; ignored when bias == NULL */
+  int64_t lda, ldb, ldc; /* in elements */
+  const void *src;
+  const void *weight;    /* raw s8 weights, or a buffer written by b200dnn_prepack when wei_format=='r' */
+  const void *bias;
+  void *dst;
+  int32_t wei_format;    /* 'n' raw | 'r' prepacked: matmul_params::mem_format_b */
+  int32_t weights_const; /* is_weights_const: raw weights are packed once and cached by address */
+  int32_t dynamic_quant; /* matmul_params::dynamic_quant: per-token s8 quantisation of a bf16/f32 src */
+  int32_t n_postops;
+  b200dnn_quant_t src_scale; /* with dynamic_quant: buff may be NULL; if not, the M scales are written there */
+  b200dnn_quant_t wei_scale;
+  b200dnn_quant_t src_zp;    /* per-tensor; dt s32 | s8 | u8 */
+  b200dnn_postop_t postops[B200DNN_MAX_POSTOPS];
+  int32_t force_kernel;  /* 0 auto, 1 streaming (mma.sync) kernel, 2 tcgen05 kernel; for tests */
+  int32_t reserved;
+} b200dnn_matmul_t;
+
+B200DNN_API const char *b200dnn_last_error(void);
+B200DNN_API int32_t b200dnn_version(void);
+/* Number of CUDA devices the library can use; 0 when there is none (no compute possible). */
+B200DNN_API int32_t b200dnn_device_count(void);
+/* Kernels launched by this library in the calling process so far (for benchmark accounting). */
+B200DNN_API int64_t b200dnn_launch_count(void);
+
+/* matmul_direct, INT8 path (matmul/lowoha_matmul.cpp:278): C = postops(dequant(A*B) + bias). */
+B200DNN_API int32_t b200dnn_matmul(const b200dnn_matmul_t *desc, void *stream);
+
+/* weight_prepack_size (reorder/prepack/lowoha_prepack.cpp:285): bytes of the packed form of a
+ * K x N s8 weight (multiple of 64).  gated != 0 selects the gate/up interleaved form used by
+ * the fused MoE first GEMM (N = 2*I, I a multiple of 32). */
+B200DNN_API size_t b200dnn_prepack_size(int64_t K, int64_t N, int32_t gated);
+/* reorder_direct with is_prepack (reorder/lowoha_reorder.cpp:43 -> prepack/lowoha_prepack.cpp:315):
+ * writes the packed weight (K-major rows padded for TMA, column sums appended) into dst. */
+B200DNN_API int32_t b200dnn_prepack(const void *weight, int64_t K, int64_t N, int64_t ldb, int32_t transB,
+                        int32_t gated, void *dst, void *stream);
+
+/* reorder_direct, dynamic per-token symmetric quantisation (reorder/lowoha_reorder.cpp:119-136):
+ * src [M,K] f32|bf16 with row stride src_ld -> dst s8 [M,K] (row stride dst_ld; dst may be NULL:
+ * scales only) and M scales (scale_dt f32|bf16). */
+B200DNN_API int32_t b200dnn_quant_per_token(const void *src, int32_t src_dt, int64_t M, int64_t K, int64_t src_ld,
+                                void *dst, int64_t dst_ld, void *scale, int32_t scale_dt, void *stream);
+/* group_dynamic_quant (reorder/lowoha_reorder.cpp:279): the same over num_groups tensors;
+ * groups with M[i]==0 are skipped. */
+B200DNN_API int32_t b200dnn_group_quant_per_token(int32_t num_groups, const void *const *src, int32_t src_dt,
+                                      const int32_t *M, const int32_t *K, const int64_t *src_ld,
+                                      void *const *dst, const int64_t *dst_ld, void *const *scale,
+                                      int32_t scale_dt, void *stream);
+/* reorder_direct, dynamic symmetric scales at per-channel ({1,N}, per_channel=1) or per-tensor
+ * granularity followed by the static quantise (reorder/lowoha_reorder_utils.cpp:591, 708-766,
+ * 908-935): src [M,N] f32|bf16 -> dst s8 [M,N] (may be NULL) + f32 scales. */
+B200DNN_API int32_t b200dnn_quant_dynamic(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t src_ld,
+                              int32_t per_channel, void *dst, int64_t dst_ld, float *scale, void *stream);
+/* reorder_direct, static quantise / dequantise (reorder/lowoha_reorder.cpp:211-267):
+ * q = clamp(rne(x/s)+zp), x = (q-zp)*s; n_scale and n_zp are 1 or N; zp may be NULL. */
+B200DNN_API int32_t b200dnn_quant_static(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t src_ld,
+                             const float *scale, int64_t n_scale, const int32_t *zp, int64_t n_zp,
+                             void *dst, int32_t dst_dt, int64_t dst_ld, void *stream);
+B200DNN_API int32_t b200dnn_dequant_static(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t src_ld,
+                               const float *scale, int64_t n_scale, const int32_t *zp, int64_t n_zp,
+                               void *dst, int32_t dst_dt, int64_t dst_ld, void *stream);
+
+/* group_matmul_moe_act_execute (matmul/group_matmul/group_matmul_moe_act.cpp:728): in place on
+ * buf [M, N=2I] (row stride ldc), result in the first I columns.  act: 1 silu_and_mul,
+ * 2 gelu_and_mul, 3 swiglu_oai_mul (matmul/group_matmul/group_matmul_direct.hpp:153-158). */
+B200DNN_API int32_t b200dnn_gated_act(void *buf, int32_t dt, int64_t M, int64_t N, int64_t ldc, int32_t act, void *stream);
+
+/* group_matmul_moe_postop_execute (matmul/group_matmul/group_matmul_moe_postop.cpp:506):
+ * out[t,0:D] = sum_k w[t,k] * row_ptrs[t*topk+k][0:D].  row_ptrs is an array of T*topk
+ * pointers (host array; the rows themselves may be host or device memory, all alike). */
+B200DNN_API int32_t b200dnn_moe_weighted_reduce(const void *const *row_ptrs, const float *topk_weights,
+                                    int32_t num_tokens, int32_t topk, int32_t D, int32_t skip_weighted,
+                                    int32_t dt, void *out, int64_t ld_out, void *stream);
+
+/* Flat form of one expert of group_matmul_direct in fused-MoE mode
+ * (matmul/lowoha_matmul.hpp:204-223, matmul/group_matmul/group_matmul_direct.hpp:406-577). */
+typedef struct b200dnn_moe_expert_t {
+  int32_t M;             /* rows routed to this expert (0 allowed: skipped) */
+  int32_t reserved;
+  const void *src;       /* [M,K] bf16 rows gathered by the caller, row stride lda */
+  int64_t lda;
+  const void *w13;       /* s8 [K, 2I] = [gate | up] (transB: [2I, K]) */
+  int64_t ldb13;
+  const float *w13_scale; /* [2I] */
+  const void *w2;        /* s8 [I, H] (transB: [H, I]) */
+  int64_t ldb2;
+  const float *w2_scale; /* [H] */
+  void *dst_down;        /* [M,H] bf16, row stride ldc_down */
+  int64_t ldc_down;
+} b200dnn_moe_expert_t;
+
+/* group_matmul_direct with fused_moe + gated_act (+ optional moe_postop), dynamic per-token INT8
+ * on both GEMMs (matmul/group_matmul/group_matmul_fused_moe.cpp:1131, data flow :906-1078):
+ * per expert  quant(src) -> GEMM(w13) -> gated act -> bf16 -> quant -> GEMM(w2) -> dst_down,
+ * then, if row_ptrs != NULL, the weighted top-k reduce into `out`.
+ * K = hidden size, I = expert FFN width (N of the first GEMM is 2*I), H = output width. */
+B200DNN_API int32_t b200dnn_fused_moe(int32_t num_experts, const b200dnn_moe_expert_t *experts, int32_t K, int32_t I,
+                          int32_t H, int32_t transB, int32_t act, int32_t weights_const,
+                          const void *const *row_ptrs, const float *topk_weights, int32_t num_tokens,
+                          int32_t topk, void *out, int64_t ld_out, void *stream);
+
+/* Router + permutation front end.  Has NO counterpart in the reference: the reference's callers do
+ * this themselves before group_matmul_direct (examples/lowoha_group_matmul_example.cpp:273-300).
+ * logits [T,E] f32 -> softmax -> top-k (ties to the lower expert id) -> renormalised weights;
+ * also returns the per-expert row counts and, per (token,k) slot, the row index inside the
+ * stable expert-sorted order.  All outputs may be NULL except ids. */
+B200DNN_API int32_t b200dnn_moe_route(const float *logits, int32_t T, int32_t E, int32_t topk, int32_t renorm,
+                          int32_t *ids, float *weights, int32_t *expert_counts, int32_t *slot_to_row,
+                          void *stream);
+
+/* End-to-end MoE layer on one GPU built from the pieces above, with the token gather fused into
+ * the first quantisation and the un-permute fused into the weighted reduce:
+ * x [T,K] bf16, logits [T,E] f32, per-expert weights as in b200dnn_moe_expert_t (M/src/dst_down
+ * ignored), optional shared experts appended after the E routed ones (applied to every token with
+ * weight 1).  out [T,H] bf16. */
+B200DNN_API int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *logits, int32_t T, int32_t E,
+                          int32_t num_shared, int32_t topk, const b200dnn_moe_expert_t *experts,
+                          int32_t K, int32_t I, int32_t H, int32_t transB, int32_t act, void *out,
+                          int64_t ld_out, void *stream);
+
+/* Drops every cached packed weight / staged buffer: the counterpart of the reference's cache
+ * clearing between tests (gtests/gtest_utils.cpp:77-118) and clear_fused_moe_scratch()
+ * (matmul/group_matmul/group_matmul_direct.hpp:683). */
+B200DNN_API int32_t b200dnn_clear_caches(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200DNN_H */

@@ -108,6 +108,32 @@ def gemm_s32(A, B, transB=False):
     return out
 
 
+class PackedB:
+    """Weight packed once for repeated oracle GEMMs (CPU-baseline timing)."""
+
+    def __init__(self, B, transB=False):
+        B = np.ascontiguousarray(B)
+        self.K, self.N = (B.shape[1], B.shape[0]) if transB else B.shape
+        lib().orc_pack_b.restype = C.c_void_p
+        self.h = C.c_void_p(lib().orc_pack_b(_p(B), C.c_int64(B.shape[1]), int(transB), self.K, self.N))
+
+    def gemm_s32(self, A, out=None):
+        A = np.ascontiguousarray(A)
+        M = A.shape[0]
+        if out is None:
+            out = np.empty((M, self.N), dtype=np.int32)
+        rc = lib().orc_gemm_s32_packed(_p(A), int(A.dtype == np.uint8), C.c_int64(A.shape[1]), self.h, M, _p(out),
+                                       C.c_int64(self.N))
+        assert rc == 0
+        return out
+
+    def __del__(self):
+        try:
+            lib().orc_free_b(self.h)
+        except Exception:
+            pass
+
+
 def colsum(B, transB=False):
     B = np.ascontiguousarray(B)
     K, N = (B.shape[1], B.shape[0]) if transB else B.shape

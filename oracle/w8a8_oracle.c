@@ -174,6 +174,52 @@ ORC_API int orc_gemm_s32(const void *A, int a_unsigned, int64_t lda, const int8_
   return 0;
 }
 
+/* Pre-packed form for repeated GEMMs against one weight (what the reference's weight cache gives
+ * its backend, matmul/backends/aocl/aocl_kernel.cpp:310-494): B^T rows padded to a multiple of 4
+ * plus the column sums.  Used by the CPU-baseline timing so that packing is outside the timed
+ * region, as it is for the reference after its first call. */
+typedef struct { int8_t *Bt; int32_t *cs; int K, N, K4; } orc_packed_b;
+ORC_API void *orc_pack_b(const int8_t *B, int64_t ldb, int transB, int K, int N) {
+  orc_packed_b *p = (orc_packed_b *)malloc(sizeof *p);
+  p->K = K; p->N = N; p->K4 = (K + 3) & ~3;
+  p->Bt = (int8_t *)calloc((size_t)N * p->K4, 1);
+  p->cs = (int32_t *)malloc(4 * (size_t)N);
+  #pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    int32_t s = 0;
+    for (int k = 0; k < K; ++k) {
+      int8_t v = transB ? B[(int64_t)n * ldb + k] : B[(int64_t)k * ldb + n];
+      p->Bt[(int64_t)n * p->K4 + k] = v; s += v;
+    }
+    p->cs[n] = s;
+  }
+  return p;
+}
+ORC_API void orc_free_b(void *h) { orc_packed_b *p = (orc_packed_b *)h; if (p) { free(p->Bt); free(p->cs); free(p); } }
+ORC_API int orc_gemm_s32_packed(const void *A, int a_unsigned, int64_t lda, const void *h, int M, int32_t *C, int64_t ldc) {
+  const orc_packed_b *p = (const orc_packed_b *)h;
+  const int K = p->K, N = p->N, K4 = p->K4;
+  uint8_t *Au = (uint8_t *)malloc((size_t)M * K4);
+  if (!Au) return -1;
+  for (int m = 0; m < M; ++m) {
+    const uint8_t *a = (const uint8_t *)A + (int64_t)m * lda;
+    for (int k = 0; k < K; ++k) Au[(int64_t)m * K4 + k] = a_unsigned ? a[k] : (uint8_t)(a[k] ^ 0x80);
+    for (int k = K; k < K4; ++k) Au[(int64_t)m * K4 + k] = a_unsigned ? 0 : 0x80;
+  }
+  int vn = have_vnni();
+  /* columns are split across threads so that small M still uses every core */
+  #pragma omp parallel for schedule(static)
+  for (int n0 = 0; n0 < N; n0 += 64) {
+    int nn = N - n0 < 64 ? N - n0 : 64;
+    if (vn) gemm_rows_vnni(Au, p->Bt + (int64_t)n0 * K4, K4, 0, M, nn, C + n0, ldc);
+    else    gemm_rows_scalar(Au, p->Bt + (int64_t)n0 * K4, K4, 0, M, nn, C + n0, ldc);
+    if (!a_unsigned)
+      for (int m = 0; m < M; ++m) for (int n = 0; n < nn; ++n) C[(int64_t)m * ldc + n0 + n] -= 128 * p->cs[n0 + n];
+  }
+  free(Au);
+  return 0;
+}
+
 /* ======================================================================================
  * Element-wise post-ops: operators/matmul/matmul_ref_kernel.cpp:694-761 with the constants
  * of matmul_ref_kernel.hpp:31-33.  Double-typed literals of the reference are kept double.

@@ -1,0 +1,208 @@
+"""GPU parity tests of b200dnn_matmul (the matmul_direct INT8 path) against the CPU oracle and the
+golden outputs of the reference's own kernel.  Mirrors the reference's TestMatmul.INT8,
+INT8_SYM_QUANT_PER_TOKEN_* and INT8_DYNAMIC_GEMM_* cases (zendnnl/gtests/test_matmul.cpp:975-1650).
+s32 results must be bit-exact; bf16 results within 1 bf16 ulp (rel <= 8e-3)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from helpers import assert_bf16_close, config1, decode_case
+
+pytestmark = pytest.mark.gpu
+
+STREAM, TC = 1, 2
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from zendnn_b200 import capi as c
+    assert c.lib.b200dnn_device_count() > 0, "no CUDA device"
+    return c
+
+
+def run(capi, M, N, K, A, W, dst_dt, **kw):
+    out = np.zeros((M, N), dtype={"bf16": np.uint16, "f32": np.float32, "s32": np.int32}[dst_dt])
+    d = capi.make_matmul(M, N, K, A, W, out, src_dt=capi.dt_of(A) if "src_dt" not in kw else kw.pop("src_dt"),
+                         dst_dt=capi.DT[dst_dt], **kw)
+    st = capi.matmul(d)
+    assert st == capi.SUCCESS, capi.last_error()
+    return out
+
+
+@pytest.mark.parametrize("kernel", [STREAM, TC])
+@pytest.mark.parametrize("shape", [(1, 64, 16), (5, 100, 24), (16, 256, 64), (33, 260, 80), (128, 512, 128),
+                                   (130, 384, 200), (257, 1024, 264)])
+def test_s32_bit_exact_small(capi, oracle, kernel, shape):
+    M, K, N = shape
+    rng = np.random.default_rng(M * 131 + K)
+    for src in ("u8", "s8"):
+        A = rng.integers(0, 256, (M, K), dtype=np.uint8) if src == "u8" else rng.integers(-128, 128, (M, K), dtype=np.int8)
+        W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+        if kernel == TC and K % 16 != 0:
+            continue    # tcgen05 path needs 16-byte aligned rows; the dispatcher sends these to the streaming kernel
+        got = run(capi, M, N, K, A, W, "s32", weights_const=False, force_kernel=kernel)
+        assert (got == oracle.gemm_s32(A, W)).all(), (src, shape)
+        # zero-point compensation stays exact in s32
+        zp = np.array([37], dtype=np.int32)
+        got = run(capi, M, N, K, A, W, "s32", weights_const=False, force_kernel=kernel, src_zp=zp)
+        ref = oracle.epilogue(oracle.gemm_s32(A, W), "s32", src_zp=37, col_sum=oracle.colsum(W))
+        assert (got == ref).all(), (src, shape, "zp")
+        # transposed weight layout [N,K]
+        Wt = np.ascontiguousarray(W.T)
+        got = run(capi, M, N, K, A, Wt, "s32", weights_const=False, force_kernel=kernel, transB=True)
+        assert (got == oracle.gemm_s32(A, W)).all(), (src, shape, "transB")
+
+
+@pytest.mark.parametrize("kernel", [STREAM, TC])
+def test_golden_reference_cases(capi, oracle, golden, kernel):
+    """Outputs of the reference's own INT8 tile kernel (tests/golden): <= 1 bf16 ulp."""
+    fused = {0: [], 1: ["relu"], 2: ["gelu_tanh"], 5: ["swish"]}
+    i = 0
+    while "c%d_meta" % i in golden:
+        p = "c%d_" % i
+        M, K, N, zp, fo, is_bf16, has_bias = [int(v) for v in golden[p + "meta"]]
+        A, W, ws = golden[p + "A"], golden[p + "B"], golden[p + "ws"]
+        i += 1
+        if kernel == TC and K % 16 != 0:
+            continue
+        bias = golden[p + "bias"] if has_bias else None
+        got = run(capi, M, N, K, A, W, "bf16" if is_bf16 else "f32", weights_const=False, force_kernel=kernel,
+                  src_scale=golden[p + "ss"], wei_scale=ws, src_zp=np.array([zp], dtype=np.int32), bias=bias,
+                  postops=fused[fo])
+        ref = golden[p + "out"]
+        if is_bf16:
+            assert_bf16_close(got, ref, 1 if fo in (0, 1) else 2, "golden case %d" % (i - 1))
+        else:
+            assert np.allclose(got, ref, rtol=2e-4, atol=1e-4)
+
+
+def test_config1_full_size(capi, oracle):
+    """M128 K4096 N4096, u8 zp 128 scale .02, per-channel weight scales, f32 bias, ReLU, bf16 out, seed 0."""
+    c = config1(oracle)
+    M, K, N = 128, 4096, 4096
+    acc = oracle.gemm_s32(c["A"], c["W"])
+    for kernel in (STREAM, TC):
+        got = run(capi, M, N, K, c["A"], c["W"], "s32", force_kernel=kernel)
+        assert (got == acc).all()
+        got = run(capi, M, N, K, c["A"], c["W"], "bf16", force_kernel=kernel, src_scale=c["ss"], wei_scale=c["ws"],
+                  src_zp=c["zp"], bias=c["bias"], postops=["relu"])
+        ref = oracle.epilogue(acc, "bf16", c["ss"], c["ws"], 128, oracle.colsum(c["W"]), c["bias"], ["relu"])
+        assert (got == ref).all(), "bf16 output differs from the oracle (same operation order): %d" % int((got != ref).sum())
+        assert np.abs(oracle.bf16_to_f32(got)).sum() > 1e-3
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+@pytest.mark.parametrize("KN", [(4096, 4096), (4096, 11008), (11008, 4096)])
+def test_decode_shapes_prepacked(capi, oracle, M, KN):
+    """Config 2: per-token s8 activations x per-channel s8 weights, prepacked, bf16 out."""
+    K, N = KN
+    c = decode_case(oracle, M, K, N, seed=M)
+    size = capi.lib.b200dnn_prepack_size(K, N, 0)
+    packed = np.zeros(size, dtype=np.uint8)
+    assert capi.lib.b200dnn_prepack(capi.ptr(c["W"]), K, N, N, 0, 0, capi.ptr(packed), None) == capi.SUCCESS, capi.last_error()
+    got = run(capi, M, N, K, c["A"], packed, "bf16", wei_format="r", src_scale=c["sa"], wei_scale=c["sw"])
+    ref = oracle.matmul_w8a8(c["A"], c["W"], "bf16", src_scale=c["sa"], wei_scale=c["sw"])
+    assert (got == ref).all(), int((got != ref).sum())
+    # raw weights give the same bytes
+    got2 = run(capi, M, N, K, c["A"], c["W"], "bf16", weights_const=False, src_scale=c["sa"], wei_scale=c["sw"])
+    assert (got2 == ref).all()
+
+
+def test_scales_in_bf16_storage(capi, oracle):
+    c = decode_case(oracle, 8, 512, 128, seed=3)
+    sa16, sw16 = oracle.f32_to_bf16(c["sa"]), oracle.f32_to_bf16(c["sw"])
+    got = run(capi, 8, 128, 512, c["A"], c["W"], "bf16", weights_const=False, src_scale=sa16, wei_scale=sw16)
+    ref = oracle.matmul_w8a8(c["A"], c["W"], "bf16", src_scale=oracle.bf16_to_f32(sa16), wei_scale=oracle.bf16_to_f32(sw16))
+    assert (got == ref).all()
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 512, 256), (300, 1024, 384)])
+def test_dynamic_quant_gelu(capi, oracle, M, K, N):
+    """Config 3 family: bf16 activations quantised per token inside the call, bias, GELU(tanh), bf16 out."""
+    rng = np.random.default_rng(M)
+    x = oracle.f32_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    qw, sw = oracle.quant_weights_per_channel(oracle.f32_to_bf16((rng.normal(size=(K, N)) * 0.02).astype(np.float32)))
+    bias = rng.normal(size=N).astype(np.float32)
+    qa, sa = oracle.quant_per_token(x)
+    ref = oracle.matmul_w8a8(qa, qw, "bf16", src_scale=sa, wei_scale=sw, bias=bias, postops=["gelu_tanh"])
+    for with_buf in (False, True):
+        scales = np.zeros(M, dtype=np.float32)
+        ss = capi.quant(scales if with_buf else None, count=M, dt=capi.DT["f32"])
+        got = run(capi, M, N, K, x, qw, "bf16", src_dt=capi.DT["bf16"], dynamic_quant=True, weights_const=False,
+                  src_scale=ss, wei_scale=sw, bias=bias, postops=["gelu_tanh"])
+        assert_bf16_close(got, ref, 1, "dynamic quant + gelu")
+        if with_buf:
+            assert (scales == sa).all()          # the library writes the scales it used
+
+
+def test_postop_chain_and_strides(capi, oracle):
+    rng = np.random.default_rng(9)
+    M, K, N, lda, ldc = 40, 192, 72, 208, 96
+    Afull = rng.integers(-128, 128, (M, lda), dtype=np.int8)
+    A = Afull[:, :K]
+    W = rng.integers(-64, 64, (K, N), dtype=np.int8)
+    sw = rng.uniform(0.001, 0.01, N).astype(np.float32)
+    add = rng.normal(size=(1, N)).astype(np.float32)
+    mul = rng.normal(size=(M, N)).astype(np.float32)
+    po = [dict(type="binary_add", buff=add), "swish", dict(type="binary_mul", buff=mul),
+          dict(type="clip", alpha=-0.5, beta=0.75)]
+    ref = oracle.matmul_w8a8(np.ascontiguousarray(A), W, "f32", src_scale=[0.05], wei_scale=sw, postops=po)
+    out = np.full((M, ldc), 7.0, dtype=np.float32)
+    for kernel in (STREAM, TC):
+        out[:] = 7.0
+        d = capi.make_matmul(M, N, K, Afull, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["f32"], lda=lda, ldc=ldc,
+                             weights_const=False, src_scale=np.array([0.05], dtype=np.float32), wei_scale=sw, postops=po,
+                             force_kernel=kernel)
+        assert capi.matmul(d) == capi.SUCCESS, capi.last_error()
+        assert np.allclose(out[:, :N], ref, rtol=2e-6, atol=1e-6)
+        assert (out[:, N:] == 7.0).all()      # padding columns untouched
+
+
+def test_device_pointers_and_weight_cache(capi, oracle):
+    import torch
+    c = decode_case(oracle, 4, 1024, 512, seed=11)
+    dev = torch.device("cuda:0")
+    A = torch.from_numpy(c["A"]).to(dev)
+    W = torch.from_numpy(c["W"]).to(dev)
+    sa, sw = torch.from_numpy(c["sa"]).to(dev), torch.from_numpy(c["sw"]).to(dev)
+    out = torch.zeros(4, 512, dtype=torch.bfloat16, device=dev)
+    d = capi.make_matmul(4, 512, 1024, A, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["bf16"], src_scale=sa, wei_scale=sw)
+    n0 = capi.lib.b200dnn_launch_count()
+    assert capi.matmul(d, torch.cuda.current_stream().cuda_stream) == capi.SUCCESS, capi.last_error()
+    n1 = capi.lib.b200dnn_launch_count()
+    assert capi.matmul(d, torch.cuda.current_stream().cuda_stream) == capi.SUCCESS
+    n2 = capi.lib.b200dnn_launch_count()
+    torch.cuda.synchronize()
+    assert n1 - n0 > n2 - n1 == 1          # second call hits the packed-weight cache: one GEMM launch
+    ref = oracle.matmul_w8a8(c["A"], c["W"], "bf16", src_scale=c["sa"], wei_scale=c["sw"])
+    got = out.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert (got == ref).all()
+    assert capi.lib.b200dnn_clear_caches() == capi.SUCCESS
+
+
+def test_contract_violations(capi):
+    """Boundary contract: failures and unimplemented features are reported, nothing is computed."""
+    A = np.zeros((4, 64), dtype=np.int8); W = np.zeros((64, 16), dtype=np.int8); out = np.zeros((4, 16), dtype=np.float32)
+    mk = lambda **kw: capi.make_matmul(4, 16, 64, A, W, out, **{**dict(src_dt=capi.DT["s8"], dst_dt=capi.DT["f32"]), **kw})
+    d = mk(); d.src = None
+    assert capi.matmul(d) == capi.FAILURE
+    d = mk(); d.M = 0
+    assert capi.matmul(d) == capi.FAILURE
+    d = mk(); d.lda = 8
+    assert capi.matmul(d) == capi.FAILURE
+    d = mk(); d.wei_dt = capi.DT["s4"]
+    assert capi.matmul(d) == capi.UNIMPLEMENTED
+    d = mk(src_dt=capi.DT["f32"])
+    assert capi.matmul(d) == capi.UNIMPLEMENTED          # float source without dynamic_quant
+    d = mk(postops=["mish"])
+    assert capi.matmul(d) == capi.FAILURE                # rejected on INT8, as the reference does
+    d = mk(postops=["softmax"])
+    assert capi.matmul(d) == capi.UNIMPLEMENTED
+    # per-token source scale needs a per-channel weight scale of N elements
+    d = mk(src_scale=np.ones(4, dtype=np.float32), wei_scale=np.ones(1, dtype=np.float32))
+    assert capi.matmul(d) == capi.FAILURE
+    # per-token source scale forbids a zero-point
+    d = mk(src_scale=np.ones(4, dtype=np.float32), wei_scale=np.ones(16, dtype=np.float32), src_zp=np.array([3], dtype=np.int32))
+    assert capi.matmul(d) == capi.FAILURE
+    assert "zero-point" in capi.last_error()

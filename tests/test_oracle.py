@@ -1,0 +1,171 @@
+"""CPU tests of the oracle: exact GEMM against numpy int64, the native-order epilogue against the
+golden outputs of the reference's own INT8 tile kernel (bit-for-bit), and the other restated
+formulas against independent numpy statements."""
+import numpy as np
+import pytest
+
+
+def _cases(golden):
+    i = 0
+    while "c%d_meta" % i in golden:
+        p = "c%d_" % i
+        M, K, N, zp, fo, is_bf16, has_bias = [int(v) for v in golden[p + "meta"]]
+        yield dict(A=golden[p + "A"], B=golden[p + "B"], ws=golden[p + "ws"], ss=float(golden[p + "ss"][0]),
+                   bias=golden[p + "bias"] if has_bias else None, zp=zp, fo=fo,
+                   dst="bf16" if is_bf16 else "f32", out=golden[p + "out"], M=M, K=K, N=N)
+        i += 1
+
+
+FUSED = {0: [], 1: ["relu"], 2: ["gelu_tanh"], 3: ["gelu_erf"], 4: ["sigmoid"], 5: ["swish"], 6: ["tanh"]}
+
+
+def test_gemm_s32_exact(oracle):
+    rng = np.random.default_rng(0)
+    for M, K, N in [(1, 1, 1), (3, 5, 7), (17, 67, 33), (64, 1000, 48)]:
+        A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+        B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+        ref = A.astype(np.int64) @ B.astype(np.int64)
+        assert (oracle.gemm_s32(A, B) == ref).all()
+        As = rng.integers(-128, 128, (M, K), dtype=np.int8)
+        ref = As.astype(np.int64) @ B.astype(np.int64)
+        assert (oracle.gemm_s32(As, B) == ref).all()
+        assert (oracle.gemm_s32(As, np.ascontiguousarray(B.T), transB=True) == ref).all()
+
+
+def test_gemm_s32_extremes(oracle):
+    # largest magnitudes the configs reach stay exact (no float, no saturation)
+    K = 11008
+    A = np.full((2, K), -128, dtype=np.int8)
+    B = np.full((K, 3), -128, dtype=np.int8)
+    assert (oracle.gemm_s32(A, B) == 128 * 128 * K).all()
+    Au = np.full((2, K), 255, dtype=np.uint8)
+    assert (oracle.gemm_s32(Au, B) == -255 * 128 * K).all()
+
+
+def test_native_order_matches_reference_golden(oracle, golden):
+    """order=1 restates int8_brgemm_ukernel.cpp:91-129; fixtures are that kernel's outputs."""
+    n = 0
+    for c in _cases(golden):
+        got = oracle.matmul_w8a8(c["A"], c["B"], c["dst"], src_scale=[c["ss"]], wei_scale=c["ws"], src_zp=c["zp"],
+                                 bias=c["bias"], postops=FUSED[c["fo"]], order=1)
+        if c["fo"] in (0, 1):
+            assert (got == c["out"]).all(), "case M%d K%d N%d" % (c["M"], c["K"], c["N"])
+        else:
+            # the reference kernel uses polynomial tanh/sigmoid (~5e-5 relative)
+            a = oracle.bf16_to_f32(got) if c["dst"] == "bf16" else got
+            b = oracle.bf16_to_f32(c["out"]) if c["dst"] == "bf16" else c["out"]
+            assert np.allclose(a, b, rtol=8e-3, atol=1e-4)
+        n += 1
+    assert n >= 8
+
+
+def test_requested_order_within_one_ulp_of_reference(oracle, golden):
+    """order=0 (exact s32 compensation, two multiplies) vs the reference kernel: <= 1 bf16 ulp."""
+    for c in _cases(golden):
+        if c["fo"] not in (0, 1):
+            continue
+        got = oracle.matmul_w8a8(c["A"], c["B"], c["dst"], src_scale=[c["ss"]], wei_scale=c["ws"], src_zp=c["zp"],
+                                 bias=c["bias"], postops=FUSED[c["fo"]], order=0)
+        if c["dst"] == "bf16":
+            assert np.abs(got.astype(np.int32) - c["out"].astype(np.int32)).max() <= 1
+        else:
+            assert np.allclose(got, c["out"], rtol=1e-5, atol=1e-5)
+
+
+def test_live_reference_kernel_if_present(oracle):
+    if oracle.ref_lib() is None:
+        pytest.skip("compiled reference kernel not available on this host")
+    rng = np.random.default_rng(5)
+    A = rng.integers(0, 256, (37, 200), dtype=np.uint8)
+    B = rng.integers(-127, 128, (200, 64), dtype=np.int8)
+    ws = rng.uniform(0.001, 0.01, 64).astype(np.float32)
+    bias = rng.normal(size=64).astype(np.float32)
+    ref = oracle.ref_int8_matmul(A, B, 128, 0.02, ws, bias, 1, "bf16")
+    got = oracle.matmul_w8a8(A, B, "bf16", src_scale=[0.02], wei_scale=ws, src_zp=128, bias=bias, postops=["relu"], order=1)
+    assert (ref == got).all()
+
+
+def test_bf16_rne(oracle):
+    x = np.array([1.0, 1.00390625, 1.005859375, -2.5, 3.1415927, 1e-30, 65504.0], dtype=np.float32)
+    bits = oracle.f32_to_bf16(x)
+    u = x.view(np.uint32).astype(np.uint64)
+    exp = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    assert (bits == exp).all()
+    assert (oracle.bf16_to_f32(bits).view(np.uint32) == (bits.astype(np.uint32) << 16)).all()
+
+
+def test_quant_per_token(oracle):
+    rng = np.random.default_rng(1)
+    x = rng.normal(size=(9, 257)).astype(np.float32)
+    x[3] = 0.0                      # all-zero row: scale clamps to 1e-10
+    x[4, 5] = np.inf                # non-finite -> 0, ignored by absmax
+    q, s = oracle.quant_per_token(x)
+    fin = np.where(np.isfinite(x), np.abs(x), 0).max(axis=1)
+    exp_s = np.maximum(np.maximum(fin, np.float32(1e-10)) / np.float32(127.0), np.float32(1e-10)).astype(np.float32)
+    assert (s == exp_s).all()
+    with np.errstate(invalid="ignore", over="ignore"):
+        exp_q = np.where(np.isfinite(x), np.rint(x / exp_s[:, None]), 0).astype(np.int8)
+    assert (q == exp_q).all()
+    assert np.abs(q[np.isfinite(x)]).max() <= 127
+    # bf16 input goes through f32
+    xb = oracle.f32_to_bf16(x)
+    qb, sb = oracle.quant_per_token(xb)
+    q2, s2 = oracle.quant_per_token(oracle.bf16_to_f32(xb))
+    assert (qb == q2).all() and (sb == s2).all()
+
+
+def test_quant_weights_per_channel_roundtrip(oracle):
+    rng = np.random.default_rng(2)
+    w = (rng.normal(size=(300, 40)) * 0.02).astype(np.float32)
+    q, s = oracle.quant_weights_per_channel(w)
+    assert q.dtype == np.int8 and s.shape == (40,)
+    assert (np.abs(q).max(axis=0) == 127).all()
+    back = oracle.dequant_static(q, s)
+    assert np.abs(back - w).max() <= s.max() * 0.5 + 1e-9
+
+
+def test_gated_act_and_reduce(oracle):
+    rng = np.random.default_rng(3)
+    y = rng.normal(size=(5, 64)).astype(np.float32)
+    z = oracle.gated_act(y, "silu_and_mul")
+    g, u = y[:, :32], y[:, 32:]
+    ref = (g * (1.0 / (1.0 + np.exp(-g.astype(np.float64))))).astype(np.float32) * u
+    assert np.allclose(z, ref, rtol=1e-5, atol=1e-6)
+    z3 = oracle.gated_act(y, "swiglu_oai_mul")
+    g3, u3 = np.clip(y[:, 0::2], -7, 7), np.clip(y[:, 1::2], -7, 7)
+    ref3 = (1 + u3) * g3 / (1 + np.exp(-1.702 * g3))
+    assert np.allclose(z3, ref3, rtol=1e-5, atol=1e-6)
+    rows = rng.normal(size=(12, 16)).astype(np.float32)
+    w = rng.uniform(size=(4, 3)).astype(np.float32)
+    out = oracle.moe_weighted_reduce(rows, w, 3)
+    ref = (rows.reshape(4, 3, 16) * w[:, :, None]).sum(axis=1)
+    assert np.allclose(out, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_router(oracle):
+    rng = np.random.default_rng(4)
+    l = rng.normal(size=(50, 8)).astype(np.float32)
+    ids, w = oracle.router_topk(l, 2)
+    p = np.exp(l - l.max(axis=1, keepdims=True))
+    p /= p.sum(axis=1, keepdims=True)
+    top = np.argsort(-p, axis=1, kind="stable")[:, :2]
+    assert (ids == top).all()
+    assert np.allclose(w.sum(axis=1), 1.0, atol=1e-6)
+
+
+def test_fused_moe_flow_small(oracle):
+    rng = np.random.default_rng(6)
+    T, H, I, E, k = 24, 64, 32, 4, 2
+    x = oracle.f32_to_bf16(rng.normal(size=(T, H)).astype(np.float32))
+    ids, w = oracle.router_topk(rng.normal(size=(T, E)).astype(np.float32), k)
+    w13, s13, w2, s2 = [], [], [], []
+    for _ in range(E):
+        q, s = oracle.quant_weights_per_channel((rng.normal(size=(H, 2 * I)) * 0.02).astype(np.float32))
+        w13.append(q); s13.append(s)
+        q, s = oracle.quant_weights_per_channel((rng.normal(size=(I, H)) * 0.02).astype(np.float32))
+        w2.append(q); s2.append(s)
+    out, _ = oracle.fused_moe(x, ids, w, w13, s13, w2, s2)
+    out2, _ = oracle.fused_moe(x, ids, w, w13, s13, w2, s2, round_before_act=True)
+    a, b = oracle.bf16_to_f32(out), oracle.bf16_to_f32(out2)
+    assert np.abs(a).sum() > 1e-3            # anti-vacuity, as the reference's fused-MoE tests do
+    assert np.allclose(a, b, rtol=0.05, atol=2e-3)

@@ -1,0 +1,148 @@
+"""GPU parity tests of the reorder_direct family (quantise / prepack) against the oracle.  The
+reference checks these with quantise->dequantise round trips (zendnnl/gtests/reorder/
+test_dynamic_quant.cpp:32,100, test_static_quant_dequant.cpp); here the s8 bytes and the scales
+must equal the oracle's exactly, and the round-trip property is checked at full size."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from zendnn_b200 import capi as c
+    assert c.lib.b200dnn_device_count() > 0
+    return c
+
+
+@pytest.mark.parametrize("M,K", [(1, 16), (3, 100), (16, 4096), (33, 4097), (8, 14336), (5, 20000)])
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_per_token_quant(capi, oracle, M, K, dt):
+    rng = np.random.default_rng(M + K)
+    x = rng.normal(size=(M, K)).astype(np.float32)
+    if M > 2:
+        x[1] = 0.0                     # all-zero row -> scale clamp 1e-10
+        x[2, K // 2] = np.nan          # non-finite -> 0
+        x[0, 0] = 1e30 if dt == "f32" else 3e38
+    if dt == "bf16":
+        x = oracle.f32_to_bf16(x)
+    q_ref, s_ref = oracle.quant_per_token(x)
+    q = np.zeros((M, K), dtype=np.int8); s = np.zeros(M, dtype=np.float32)
+    st = capi.lib.b200dnn_quant_per_token(capi.ptr(x), capi.DT[dt], M, K, K, capi.ptr(q), K, capi.ptr(s), capi.DT["f32"], None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert (s == s_ref).all()
+    assert (q == q_ref).all()
+    # scales only (dst == NULL) and bf16 scale storage
+    s16 = np.zeros(M, dtype=np.uint16)
+    st = capi.lib.b200dnn_quant_per_token(capi.ptr(x), capi.DT[dt], M, K, K, None, 0, capi.ptr(s16), capi.DT["bf16"], None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert (s16 == oracle.f32_to_bf16(s_ref)).all()
+
+
+def test_per_token_quant_strided(capi, oracle):
+    rng = np.random.default_rng(0)
+    M, K, ld, dld = 7, 120, 136, 128
+    full = rng.normal(size=(M, ld)).astype(np.float32)
+    q = np.full((M, dld), 99, dtype=np.int8); s = np.zeros(M, dtype=np.float32)
+    st = capi.lib.b200dnn_quant_per_token(capi.ptr(full), capi.DT["f32"], M, K, ld, capi.ptr(q), dld, capi.ptr(s), capi.DT["f32"], None)
+    assert st == capi.SUCCESS, capi.last_error()
+    q_ref, s_ref = oracle.quant_per_token(np.ascontiguousarray(full[:, :K]))
+    assert (q[:, :K] == q_ref).all() and (s == s_ref).all() and (q[:, K:] == 99).all()
+
+
+def test_group_dynamic_quant(capi, oracle):
+    """group_dynamic_quant: several tensors in one call, M == 0 groups skipped
+    (zendnnl/gtests/group_matmul/test_quant.cpp:1284-1413)."""
+    rng = np.random.default_rng(1)
+    Ms = [0, 5, 1, 0, 17]
+    K = 256
+    xs = [oracle.f32_to_bf16(rng.normal(size=(max(m, 1), K)).astype(np.float32)) for m in Ms]
+    qs = [np.zeros((max(m, 1), K), dtype=np.int8) for m in Ms]
+    ss = [np.zeros(max(m, 1), dtype=np.float32) for m in Ms]
+    G = len(Ms)
+    arr = lambda xs_: (C.c_void_p * G)(*[x.ctypes.data for x in xs_])
+    Mv = (C.c_int32 * G)(*Ms); Kv = (C.c_int32 * G)(*([K] * G)); ld = (C.c_int64 * G)(*([K] * G))
+    st = capi.lib.b200dnn_group_quant_per_token(G, arr(xs), capi.DT["bf16"], Mv, Kv, ld, arr(qs), ld, arr(ss), capi.DT["f32"], None)
+    assert st == capi.SUCCESS, capi.last_error()
+    for m, x, q, s in zip(Ms, xs, qs, ss):
+        if m == 0:
+            assert not q.any() and not s.any()
+            continue
+        q_ref, s_ref = oracle.quant_per_token(x[:m])
+        assert (q[:m] == q_ref).all() and (s[:m] == s_ref).all()
+
+
+@pytest.mark.parametrize("K,N", [(64, 16), (300, 40), (4096, 1024)])
+def test_per_channel_weight_quant(capi, oracle, K, N):
+    rng = np.random.default_rng(K)
+    w = oracle.f32_to_bf16((rng.normal(size=(K, N)) * 0.02).astype(np.float32))
+    q_ref, s_ref = oracle.quant_weights_per_channel(w)
+    q = np.zeros((K, N), dtype=np.int8); s = np.zeros(N, dtype=np.float32)
+    st = capi.lib.b200dnn_quant_dynamic(capi.ptr(w), capi.DT["bf16"], K, N, N, 1, capi.ptr(q), N, capi.ptr(s), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert (s == s_ref).all() and (q == q_ref).all()
+    # per-tensor scale
+    s1 = np.zeros(1, dtype=np.float32)
+    st = capi.lib.b200dnn_quant_dynamic(capi.ptr(w), capi.DT["bf16"], K, N, N, 0, None, 0, capi.ptr(s1), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert s1[0] == oracle.dyn_scales(w, per_channel=False)[0]
+
+
+def test_static_quant_dequant_roundtrip(capi, oracle):
+    rng = np.random.default_rng(2)
+    M, N = 64, 96
+    x = rng.uniform(-2, 2, size=(M, N)).astype(np.float32)
+    scale = rng.uniform(0.01, 0.03, N).astype(np.float32)
+    zp = rng.integers(-5, 5, N).astype(np.int32)
+    q = np.zeros((M, N), dtype=np.int8)
+    st = capi.lib.b200dnn_quant_static(capi.ptr(x), capi.DT["f32"], M, N, N, capi.ptr(scale), N, capi.ptr(zp), N, capi.ptr(q), capi.DT["s8"], N, None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert (q == oracle.quant_static(x, scale, zp)).all()
+    back = np.zeros((M, N), dtype=np.float32)
+    st = capi.lib.b200dnn_dequant_static(capi.ptr(q), capi.DT["s8"], M, N, N, capi.ptr(scale), N, capi.ptr(zp), N, capi.ptr(back), capi.DT["f32"], N, None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert (back == oracle.dequant_static(q, scale, zp)).all()
+    unclipped = np.abs(np.rint(x / scale) + zp) < 127
+    assert np.abs(back - x)[unclipped].max() <= scale.max() * 0.5 + 1e-6
+    # u8 per-tensor
+    qu = np.zeros((M, N), dtype=np.uint8)
+    s1 = np.array([0.02], dtype=np.float32); z1 = np.array([128], dtype=np.int32)
+    st = capi.lib.b200dnn_quant_static(capi.ptr(x), capi.DT["f32"], M, N, N, capi.ptr(s1), 1, capi.ptr(z1), 1, capi.ptr(qu), capi.DT["u8"], N, None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert (qu == oracle.quant_static(x, s1, z1, "u8")).all()
+
+
+@pytest.mark.parametrize("transB", [False, True])
+@pytest.mark.parametrize("K,N", [(64, 16), (130, 200), (512, 384)])
+def test_prepack_layout(capi, oracle, K, N, transB):
+    """Packed form: header, column sums, K-major zero-padded rows."""
+    rng = np.random.default_rng(K + N)
+    W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    src = np.ascontiguousarray(W.T) if transB else W
+    size = capi.lib.b200dnn_prepack_size(K, N, 0)
+    buf = np.zeros(size, dtype=np.uint8)
+    st = capi.lib.b200dnn_prepack(capi.ptr(src), K, N, K if transB else N, int(transB), 0, capi.ptr(buf), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    Kp, Np = -(-K // 128) * 128, -(-N // 128) * 128
+    hdr = buf[:48].view(np.int64)
+    assert int(buf[:4].view(np.uint32)[0]) == 0x38573242 and list(hdr[1:5]) == [K, N, Kp, Np]
+    colsum = buf[256:256 + 4 * Np].view(np.int32)
+    wt = buf[256 + 4 * Np:256 + 4 * Np + Np * Kp].view(np.int8).reshape(Np, Kp)
+    assert (wt[:N, :K] == W.T).all() and not wt[N:].any() and not wt[:, K:].any()
+    assert (colsum[:N] == W.astype(np.int32).sum(axis=0)).all() and not colsum[N:].any()
+
+
+def test_prepack_gated_interleave(capi):
+    rng = np.random.default_rng(5)
+    K, I = 128, 64
+    W = rng.integers(-128, 128, (K, 2 * I), dtype=np.int8)
+    size = capi.lib.b200dnn_prepack_size(K, 2 * I, 1)
+    buf = np.zeros(size, dtype=np.uint8)
+    assert capi.lib.b200dnn_prepack(capi.ptr(W), K, 2 * I, 2 * I, 0, 1, capi.ptr(buf), None) == capi.SUCCESS, capi.last_error()
+    Np = 128
+    wt = buf[256 + 4 * Np:].view(np.int8).reshape(Np, 128)
+    # packed rows: g[0:32] u[0:32] g[32:64] u[32:64]
+    exp = np.concatenate([W[:, 0:32], W[:, I:I + 32], W[:, 32:64], W[:, I + 32:I + 64]], axis=1).T
+    assert (wt == exp).all()

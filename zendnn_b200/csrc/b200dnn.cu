@@ -1,0 +1,676 @@
+// libb200dnn: extern "C" entry points (include/b200dnn.h) over the sm_100a kernels.
+// Validation mirrors the INT8 rules of the reference's validator
+// (matmul/lowoha_matmul_utils.cpp:180-420) for the supported subset; everything else returns
+// unimplemented, never a different computation.
+#include <cudaTypedefs.h>
+
+#include "runtime.cuh"
+#include "common.cuh"
+#include "quant_kernels.cuh"
+#include "pack_kernels.cuh"
+#include "stream_gemm.cuh"
+#include "tc_gemm.cuh"
+#include "moe_kernels.cuh"
+
+using namespace b200;
+
+namespace {
+
+cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+int env_int(const char *name, int dflt) {
+  const char *e = getenv(name);
+  return e ? atoi(e) : dflt;
+}
+
+// ------------------------------------------------------------------------------------ prepack
+int32_t pack_into(const void *w_dev, int64_t K, int64_t N, int64_t ldb, int transB, int gated, void *dst_dev,
+                  cudaStream_t st, PackedWeight *out) {
+  const int64_t Kp = round_up(K, 128), Np = round_up(N, 128);
+  const int64_t I = gated ? N / 2 : 0;
+  if (gated) B2_CHECK(N % 2 == 0 && I % kGateGranule == 0, B200DNN_UNIMPLEMENTED,
+                      "gated prepack needs N = 2*I with I a multiple of %d (N=%lld)", kGateGranule, (long long)N);
+  uint8_t *base = reinterpret_cast<uint8_t *>(dst_dev);
+  B2_CHECK((reinterpret_cast<uintptr_t>(base) & 255) == 0, B200DNN_FAILURE, "prepack destination must be 256-byte aligned");
+  int32_t *colsum = reinterpret_cast<int32_t *>(base + kPackHeaderBytes);
+  int8_t *wt = reinterpret_cast<int8_t *>(base + kPackHeaderBytes + Np * 4);
+  pack_header_kernel<<<1, 1, 0, st>>>(reinterpret_cast<PackHeader *>(base), K, N, Kp, Np, gated, I);
+  B2_LAUNCHED();
+  dim3 grid((unsigned)(Kp / 64), (unsigned)(Np / 32));
+  pack_weight_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const int8_t *>(w_dev), ldb, transB, K, N, Kp, gated, I, wt);
+  B2_LAUNCHED();
+  pack_colsum_kernel<<<(unsigned)((Np + 7) / 8), 256, 0, st>>>(wt, Np, Kp, colsum);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  if (out) { out->colsum = colsum; out->wt = wt; out->K = K; out->N = N; out->Kp = Kp; out->Np = Np; out->gated = gated; out->I = I; }
+  return B200DNN_SUCCESS;
+}
+
+PackedWeight view_of(const void *dev_base, const PackHeader &h) {
+  PackedWeight pw;
+  const uint8_t *b = reinterpret_cast<const uint8_t *>(dev_base);
+  pw.colsum = reinterpret_cast<const int32_t *>(b + kPackHeaderBytes);
+  pw.wt = reinterpret_cast<const int8_t *>(b + kPackHeaderBytes + h.Np * 4);
+  pw.K = h.K; pw.N = h.N; pw.Kp = h.Kp; pw.Np = h.Np; pw.gated = h.gated; pw.I = h.I;
+  return pw;
+}
+
+// Resolves the weight argument of a GEMM to a packed device buffer.
+int32_t resolve_weight(const void *weight, int wei_format, int64_t K, int64_t N, int64_t ldb, int transB, int gated,
+                       int weights_const, cudaStream_t st, PackedWeight *pw) {
+  Runtime &R = rt();
+  if (wei_format == 'r') {
+    if (is_device_ptr(weight)) {
+      auto it = R.packed_registry.find(weight);
+      if (it == R.packed_registry.end()) {
+        PackHeader h;
+        B2_CUDA(cudaMemcpyAsync(&h, weight, sizeof h, cudaMemcpyDeviceToHost, st));
+        B2_CUDA(cudaStreamSynchronize(st));
+        B2_CHECK(h.magic == kPackMagic, B200DNN_FAILURE, "mem_format_b='r' but the weight buffer was not written by b200dnn_prepack");
+        it = R.packed_registry.emplace(weight, view_of(weight, h)).first;
+      }
+      *pw = it->second;
+    } else {
+      auto it = R.host_packed.find(weight);
+      if (it == R.host_packed.end()) {
+        PackHeader h; memcpy(&h, weight, sizeof h);
+        B2_CHECK(h.magic == kPackMagic, B200DNN_FAILURE, "mem_format_b='r' but the weight buffer was not written by b200dnn_prepack");
+        size_t bytes = pack_bytes(h.K, h.N);
+        void *d = nullptr;
+        B2_CUDA(cudaMalloc(&d, bytes));
+        B2_CUDA(cudaMemcpyAsync(d, weight, bytes, cudaMemcpyHostToDevice, st));
+        PackedWeight v = view_of(d, h); v.owned = d;
+        it = R.host_packed.emplace(weight, v).first;
+      }
+      *pw = it->second;
+    }
+    B2_CHECK(pw->K == K && pw->N == N && pw->gated == gated, B200DNN_FAILURE,
+             "prepacked weight is K=%lld N=%lld gated=%d, call asks for K=%lld N=%lld gated=%d", (long long)pw->K,
+             (long long)pw->N, pw->gated, (long long)K, (long long)N, gated);
+    return B200DNN_SUCCESS;
+  }
+  B2_CHECK(wei_format == 'n' || wei_format == 0, B200DNN_FAILURE, "mem_format_b must be 'n' or 'r'");
+  auto key = std::make_tuple(weight, K, N, ldb, transB, gated);
+  const bool cache = weights_const && env_int("ZENDNNL_MATMUL_WEIGHT_CACHE", 1) != 0;
+  if (cache) {
+    auto it = R.wcache.find(key);
+    if (it != R.wcache.end()) { *pw = it->second; return B200DNN_SUCCESS; }
+  }
+  const int64_t wrows = transB ? N : K, wcols = transB ? K : N;
+  const void *w_dev = nullptr;
+  B2_TRY(stage_in(weight, span_bytes(wrows, wcols, ldb, B200DNN_S8), st, &w_dev));
+  void *buf = nullptr;
+  if (cache) B2_CUDA(cudaMalloc(&buf, pack_bytes(K, N)));
+  else { buf = R.ws.alloc(pack_bytes(K, N)); B2_CHECK(buf, B200DNN_FAILURE, "workspace allocation failed"); }
+  B2_TRY(pack_into(w_dev, K, N, ldb, transB, gated, buf, st, pw));
+  if (cache) { pw->owned = buf; R.wcache.emplace(key, *pw); }
+  return B200DNN_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------ quant helpers
+int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, cudaStream_t st) {
+  if (rows <= 0) return B200DNN_SUCCESS;
+  if (src_dt == B200DNN_BF16) quant_per_token_kernel<uint16_t><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
+  else if (src_dt == B200DNN_F32) quant_per_token_kernel<float><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
+  else return fail(B200DNN_UNIMPLEMENTED, "per-token quantisation takes f32 or bf16 input");
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return B200DNN_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------ GEMM launchers
+int32_t launch_stream(const uint8_t *A, int64_t lda, bool a_unsigned, int M, int N, int K, const PackedWeight &pw,
+                      const EpiParams &epi, cudaStream_t st) {
+  Runtime &R = rt();
+  StreamGemmArgs g{};
+  g.A = A; g.lda = lda; g.M = M; g.N = N; g.K = K; g.Wt = pw.wt; g.Kp = (int)pw.Kp;
+  g.chunks_total = (int)(pw.Kp / 64);
+  // shape heuristic: enough CTAs to cover the SMs about twice, K range per CTA >= 1024 bytes
+  int nb = env_int("B200DNN_STREAM_NB", 4);
+  if (nb != 1 && nb != 2 && nb != 4 && nb != 8) nb = 4;
+  g.nb = nb; g.kw = 8 / nb;
+  const int tiles_n = (N + nb * 8 - 1) / (nb * 8);
+  const int tiles_m = (M + 15) / 16;
+  int ksplit = env_int("B200DNN_STREAM_KSPLIT", 0);
+  if (ksplit <= 0) {
+    ksplit = 1;
+    while (tiles_n * tiles_m * ksplit < 2 * R.sm_count && g.chunks_total / (ksplit * 2) >= 16) ksplit *= 2;
+  }
+  if (ksplit > g.chunks_total) ksplit = g.chunks_total;
+  g.chunks_per_cta = (g.chunks_total + ksplit - 1) / ksplit;
+  ksplit = (g.chunks_total + g.chunks_per_cta - 1) / g.chunks_per_cta;
+  const int kbytes = g.chunks_per_cta * 64;
+  g.a_stride = (int)round_up(kbytes, 128) + 64;
+  size_t smem = (size_t)16 * g.a_stride;
+  if (smem < 4096) smem = 4096;
+  B2_CHECK(smem <= 200 * 1024, B200DNN_FAILURE, "streaming kernel: K range per CTA too large (%d bytes)", kbytes);
+  const size_t tiles = (size_t)tiles_n * tiles_m;
+  if (ksplit > 1) {
+    B2_CHECK(tiles <= R.n_counters, B200DNN_FAILURE, "streaming kernel: too many tiles for the split-K counters");
+    g.partial = (int32_t *)R.ws.alloc(tiles * ksplit * 16 * nb * 8 * sizeof(int32_t));
+    B2_CHECK(g.partial, B200DNN_FAILURE, "workspace allocation failed");
+    g.counters = R.counters;
+  }
+  dim3 grid(tiles_n, ksplit, tiles_m);
+  if (a_unsigned) {
+    B2_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    stream_gemm_kernel<true><<<grid, 256, smem, st>>>(g, epi);
+  } else {
+    B2_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    stream_gemm_kernel<false><<<grid, 256, smem, st>>>(g, epi);
+  }
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return B200DNN_SUCCESS;
+}
+
+int pick_bn(int m_tiles, int N, int sm_count, int gated) {
+  int forced = env_int("B200DNN_TC_BN", 0);
+  if (forced > 0) return forced;
+  const int cands[4] = {256, 128, 64, 32};
+  for (int i = 0; i < 4; ++i) {
+    int bn = cands[i];
+    if (gated && bn < 64) break;
+    if ((long long)m_tiles * ((N + bn - 1) / bn) >= sm_count || i == 3 || (gated && bn == 64)) return bn;
+  }
+  return gated ? 64 : 32;
+}
+
+// Plain or grouped tcgen05 GEMM.  A: [M_total, lda] device, 16-byte aligned rows.
+int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, int N, int K, const PackedWeight &pw0,
+                  TcGemmArgs args, const EpiParams &epi, int m_tiles_hint, cudaStream_t st) {
+  Runtime &R = rt();
+  CUtensorMap map_a, map_b;
+  B2_TRY(make_map_2d(&map_a, A, (uint64_t)K, (uint64_t)M_total, (uint64_t)lda, kTcBM));
+  args.M_total = M_total; args.N = N; args.k_blocks = (int)(pw0.Kp / 128);
+  args.a_unsigned = a_unsigned ? 1 : 0; args.gated = pw0.gated; args.status = R.status;
+  args.BN = pick_bn(m_tiles_hint, N, R.sm_count, pw0.gated);
+  B2_CHECK(args.BN % 32 == 0 && args.BN >= 32 && args.BN <= 256 && (!pw0.gated || args.BN % 64 == 0), B200DNN_FAILURE,
+           "bad tile width %d", args.BN);
+  args.n_tiles = (N + args.BN - 1) / args.BN;
+  const int stage_bytes = kTcBM * kTcBK + args.BN * kTcBK;
+  int stages = kTcSmemBudget / stage_bytes;
+  if (stages > 8) stages = 8;
+  int forced_stages = env_int("B200DNN_TC_STAGES", 0);
+  if (forced_stages > 0 && forced_stages <= stages) stages = forced_stages;
+  args.stages = stages;
+  B2_TRY(make_map_2d(&map_b, pw0.wt, (uint64_t)pw0.Kp, (uint64_t)pw0.Np, (uint64_t)pw0.Kp, (uint32_t)args.BN));
+  const size_t smem = (size_t)stages * stage_bytes + 1024;
+  B2_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  long long tiles = (long long)m_tiles_hint * args.n_tiles;
+  int grid = (int)(tiles < R.sm_count ? (tiles > 0 ? tiles : 1) : R.sm_count);
+  tc_gemm_kernel<<<grid, kTcThreads, smem, st>>>(map_a, map_b, args, epi);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return B200DNN_SUCCESS;
+}
+
+// reads back the tcgen05 status word (only on paths that synchronise anyway)
+int32_t check_tc_status(cudaStream_t st) {
+  Runtime &R = rt();
+  B2_CUDA(cudaMemcpyAsync(R.status_host, R.status, 4, cudaMemcpyDeviceToHost, st));
+  B2_CUDA(cudaStreamSynchronize(st));
+  if (*R.status_host != 0) {
+    int code = *R.status_host;
+    cudaMemsetAsync(R.status, 0, 4, st);
+    return fail(B200DNN_FAILURE, "tcgen05 GEMM gave up waiting (code %d)", code);
+  }
+  return B200DNN_SUCCESS;
+}
+
+int32_t fill_epi(const b200dnn_matmul_t *d, EpiParams *e) {
+  memset(e, 0, sizeof *e);
+  e->dst_dt = d->dst_dt; e->ldc = d->ldc;
+  e->bias_dt = d->bias_dt;
+  e->n_po = d->n_postops;
+  return B200DNN_SUCCESS;
+}
+
+}  // namespace
+
+// =========================================================================================== C ABI
+extern "C" {
+
+const char *b200dnn_last_error(void) { return err_text().c_str(); }
+int32_t b200dnn_version(void) { return 100; }
+int32_t b200dnn_device_count(void) { return device_count(); }
+int64_t b200dnn_launch_count(void) { return launch_counter().load(); }
+
+size_t b200dnn_prepack_size(int64_t K, int64_t N, int32_t gated) {
+  (void)gated;
+  if (K <= 0 || N <= 0) return 0;
+  return (pack_bytes(K, N) + 63) & ~size_t(63);
+}
+
+int32_t b200dnn_prepack(const void *weight, int64_t K, int64_t N, int64_t ldb, int32_t transB, int32_t gated, void *dst,
+                        void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(weight && dst && K > 0 && N > 0, B200DNN_FAILURE, "prepack: null pointer or non-positive dimension");
+  B2_CHECK(ldb >= (transB ? K : N), B200DNN_FAILURE, "prepack: ldb=%lld too small", (long long)ldb);
+  const void *w_dev = nullptr;
+  B2_TRY(stage_in(weight, span_bytes(transB ? N : K, transB ? K : N, ldb, B200DNN_S8), st, &w_dev));
+  Staged out;
+  B2_TRY(stage_out(dst, pack_bytes(K, N), st, &out));
+  PackedWeight pw;
+  B2_TRY(pack_into(w_dev, K, N, ldb, transB, gated, out.dev, st, &pw));
+  if (!out.copy_back) rt().packed_registry[dst] = pw;
+  else rt().host_packed.erase(dst);
+  return finish_out({&out}, st);
+}
+
+int32_t b200dnn_quant_per_token(const void *src, int32_t src_dt, int64_t M, int64_t K, int64_t src_ld, void *dst,
+                                int64_t dst_ld, void *scale, int32_t scale_dt, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(src && scale, B200DNN_FAILURE, "dynamic quantisation needs src and a scale buffer");
+  B2_CHECK(M > 0 && K > 0 && src_ld >= K && (!dst || dst_ld >= K), B200DNN_FAILURE, "bad shape or stride");
+  B2_CHECK(scale_dt == B200DNN_F32 || scale_dt == B200DNN_BF16, B200DNN_UNIMPLEMENTED, "scale dtype must be f32 or bf16");
+  const void *s_dev = nullptr;
+  B2_TRY(stage_in(src, span_bytes(M, K, src_ld, src_dt), st, &s_dev));
+  Staged o_q, o_s;
+  B2_TRY(stage_out(dst, span_bytes(M, K, dst_ld, B200DNN_S8), st, &o_q, dst && dst_ld != K));
+  B2_TRY(stage_out(scale, (size_t)M * dt_size(scale_dt), st, &o_s));
+  RowQuantArgs a{};
+  a.src = s_dev; a.src_ld = src_ld; a.dst = (int8_t *)o_q.dev; a.dst_ld = dst_ld; a.scale = o_s.dev; a.scale_dt = scale_dt;
+  a.K = (int32_t)K; a.gather_div = 1;
+  B2_TRY(launch_quant_rows(a, src_dt, M, st));
+  return finish_out({&o_q, &o_s}, st);
+}
+
+int32_t b200dnn_group_quant_per_token(int32_t num_groups, const void *const *src, int32_t src_dt, const int32_t *M,
+                                      const int32_t *K, const int64_t *src_ld, void *const *dst, const int64_t *dst_ld,
+                                      void *const *scale, int32_t scale_dt, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(num_groups > 0 && src && M && K && src_ld && dst && dst_ld && scale, B200DNN_FAILURE, "null argument");
+  // groups with the same K share one launch; the reference allows K to differ per group, handled per K value
+  std::vector<Staged> outs;
+  outs.reserve(2 * num_groups);
+  std::vector<const void *> s_dev(num_groups); std::vector<void *> d_dev(num_groups), sc_dev(num_groups);
+  std::vector<int32_t> row_off(num_groups + 1, 0);
+  for (int g = 0; g < num_groups; ++g) {
+    row_off[g + 1] = row_off[g] + (M[g] > 0 ? M[g] : 0);
+    if (M[g] <= 0) { s_dev[g] = nullptr; d_dev[g] = nullptr; sc_dev[g] = nullptr; continue; }
+    B2_CHECK(K[g] == K[0] || M[0] <= 0, B200DNN_UNIMPLEMENTED, "group_dynamic_quant: differing K per group");
+    B2_CHECK(src[g] && scale[g] && src_ld[g] >= K[g], B200DNN_FAILURE, "group %d: null pointer or bad stride", g);
+    B2_TRY(stage_in(src[g], span_bytes(M[g], K[g], src_ld[g], src_dt), st, &s_dev[g]));
+    Staged a, b;
+    B2_TRY(stage_out(dst[g], span_bytes(M[g], K[g], dst_ld[g], B200DNN_S8), st, &a, dst[g] && dst_ld[g] != K[g]));
+    B2_TRY(stage_out(scale[g], (size_t)M[g] * dt_size(scale_dt), st, &b));
+    d_dev[g] = a.dev; sc_dev[g] = b.dev; outs.push_back(a); outs.push_back(b);
+  }
+  int Kc = 0; for (int g = 0; g < num_groups; ++g) if (M[g] > 0) { Kc = K[g]; break; }
+  if (row_off[num_groups] == 0) return B200DNN_SUCCESS;
+  // device tables
+  const size_t tb = sizeof(void *) * num_groups;
+  uint8_t *tab = (uint8_t *)rt().ws.alloc(3 * tb + 2 * sizeof(int64_t) * num_groups + sizeof(int32_t) * (num_groups + 1));
+  B2_CHECK(tab, B200DNN_FAILURE, "workspace allocation failed");
+  std::vector<uint8_t> host(3 * tb + 2 * sizeof(int64_t) * num_groups + sizeof(int32_t) * (num_groups + 1));
+  uint8_t *h = host.data();
+  memcpy(h, s_dev.data(), tb); memcpy(h + tb, d_dev.data(), tb); memcpy(h + 2 * tb, sc_dev.data(), tb);
+  memcpy(h + 3 * tb, src_ld, sizeof(int64_t) * num_groups);
+  memcpy(h + 3 * tb + sizeof(int64_t) * num_groups, dst_ld, sizeof(int64_t) * num_groups);
+  memcpy(h + 3 * tb + 2 * sizeof(int64_t) * num_groups, row_off.data(), sizeof(int32_t) * (num_groups + 1));
+  B2_CUDA(cudaMemcpyAsync(tab, h, host.size(), cudaMemcpyHostToDevice, st));
+  B2_CUDA(cudaStreamSynchronize(st));   // host table goes out of scope
+  RowQuantArgs a{};
+  a.n_groups = num_groups; a.K = Kc; a.scale_dt = scale_dt; a.gather_div = 1;
+  a.g_src = (const void *const *)tab; a.g_dst = (void *const *)(tab + tb); a.g_scale = (void *const *)(tab + 2 * tb);
+  a.g_src_ld = (const int64_t *)(tab + 3 * tb); a.g_dst_ld = (const int64_t *)(tab + 3 * tb + sizeof(int64_t) * num_groups);
+  a.row_off = (const int32_t *)(tab + 3 * tb + 2 * sizeof(int64_t) * num_groups);
+  B2_TRY(launch_quant_rows(a, src_dt, row_off[num_groups], st));
+  bool any = false;
+  for (auto &s : outs) if (s.copy_back) { B2_CUDA(cudaMemcpyAsync(s.host, s.dev, s.bytes, cudaMemcpyDeviceToHost, st)); any = true; }
+  if (any) B2_CUDA(cudaStreamSynchronize(st));
+  return B200DNN_SUCCESS;
+}
+
+int32_t b200dnn_quant_dynamic(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t src_ld, int32_t per_channel,
+                              void *dst, int64_t dst_ld, float *scale, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(src && scale && M > 0 && N > 0 && src_ld >= N && (!dst || dst_ld >= N), B200DNN_FAILURE, "bad argument");
+  B2_CHECK(src_dt == B200DNN_BF16 || src_dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "source must be f32 or bf16");
+  const void *s_dev = nullptr;
+  B2_TRY(stage_in(src, span_bytes(M, N, src_ld, src_dt), st, &s_dev));
+  const int64_t ns = per_channel ? N : 1;
+  Staged o_q, o_s;
+  B2_TRY(stage_out(dst, span_bytes(M, N, dst_ld, B200DNN_S8), st, &o_q, dst && dst_ld != N));
+  B2_TRY(stage_out(scale, (size_t)ns * 4, st, &o_s));
+  uint32_t *amax = (uint32_t *)rt().ws.alloc((size_t)ns * 4);
+  B2_CHECK(amax, B200DNN_FAILURE, "workspace allocation failed");
+  B2_CUDA(cudaMemsetAsync(amax, 0, (size_t)ns * 4, st));
+  dim3 grid((unsigned)((N + 255) / 256), (unsigned)(M < 64 ? 1 : (M / 64 > 256 ? 256 : M / 64)));
+  if (src_dt == B200DNN_BF16) absmax_cols_kernel<uint16_t><<<grid, 256, 0, st>>>((const uint16_t *)s_dev, M, N, src_ld, per_channel, amax);
+  else absmax_cols_kernel<float><<<grid, 256, 0, st>>>((const float *)s_dev, M, N, src_ld, per_channel, amax);
+  B2_LAUNCHED();
+  scales_from_absmax_kernel<<<(unsigned)((ns + 255) / 256), 256, 0, st>>>(amax, ns, (float *)o_s.dev);
+  B2_LAUNCHED();
+  if (dst) {
+    dim3 g2((unsigned)((N + 255) / 256), (unsigned)(M > 1024 ? 1024 : M));
+    if (src_dt == B200DNN_BF16)
+      quant_static_kernel<uint16_t><<<g2, 256, 0, st>>>((const uint16_t *)s_dev, M, N, src_ld, (const float *)o_s.dev, ns, nullptr, 0, o_q.dev, B200DNN_S8, dst_ld);
+    else
+      quant_static_kernel<float><<<g2, 256, 0, st>>>((const float *)s_dev, M, N, src_ld, (const float *)o_s.dev, ns, nullptr, 0, o_q.dev, B200DNN_S8, dst_ld);
+    B2_LAUNCHED();
+  }
+  B2_CUDA(cudaGetLastError());
+  return finish_out({&o_q, &o_s}, st);
+}
+
+int32_t b200dnn_quant_static(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t src_ld, const float *scale,
+                             int64_t n_scale, const int32_t *zp, int64_t n_zp, void *dst, int32_t dst_dt, int64_t dst_ld,
+                             void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(src && dst && scale && M > 0 && N > 0 && src_ld >= N && dst_ld >= N, B200DNN_FAILURE, "bad argument");
+  B2_CHECK((n_scale == 1 || n_scale == N) && (!zp || n_zp == 1 || n_zp == N), B200DNN_UNIMPLEMENTED, "scale / zero-point granularity");
+  B2_CHECK((src_dt == B200DNN_BF16 || src_dt == B200DNN_F32) && (dst_dt == B200DNN_S8 || dst_dt == B200DNN_U8), B200DNN_UNIMPLEMENTED, "dtype combination");
+  const void *s_dev, *sc_dev, *zp_dev = nullptr;
+  B2_TRY(stage_in(src, span_bytes(M, N, src_ld, src_dt), st, &s_dev));
+  B2_TRY(stage_in(scale, (size_t)n_scale * 4, st, &sc_dev));
+  if (zp) B2_TRY(stage_in(zp, (size_t)n_zp * 4, st, &zp_dev));
+  Staged o;
+  B2_TRY(stage_out(dst, span_bytes(M, N, dst_ld, dst_dt), st, &o, dst_ld != N));
+  dim3 g2((unsigned)((N + 255) / 256), (unsigned)(M > 1024 ? 1024 : M));
+  if (src_dt == B200DNN_BF16)
+    quant_static_kernel<uint16_t><<<g2, 256, 0, st>>>((const uint16_t *)s_dev, M, N, src_ld, (const float *)sc_dev, n_scale, (const int32_t *)zp_dev, n_zp, o.dev, dst_dt, dst_ld);
+  else
+    quant_static_kernel<float><<<g2, 256, 0, st>>>((const float *)s_dev, M, N, src_ld, (const float *)sc_dev, n_scale, (const int32_t *)zp_dev, n_zp, o.dev, dst_dt, dst_ld);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return finish_out({&o}, st);
+}
+
+int32_t b200dnn_dequant_static(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t src_ld, const float *scale,
+                               int64_t n_scale, const int32_t *zp, int64_t n_zp, void *dst, int32_t dst_dt, int64_t dst_ld,
+                               void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(src && dst && scale && M > 0 && N > 0 && src_ld >= N && dst_ld >= N, B200DNN_FAILURE, "bad argument");
+  B2_CHECK((n_scale == 1 || n_scale == N) && (!zp || n_zp == 1 || n_zp == N), B200DNN_UNIMPLEMENTED, "scale / zero-point granularity");
+  B2_CHECK((src_dt == B200DNN_S8 || src_dt == B200DNN_U8) && (dst_dt == B200DNN_F32 || dst_dt == B200DNN_BF16), B200DNN_UNIMPLEMENTED, "dtype combination");
+  const void *s_dev, *sc_dev, *zp_dev = nullptr;
+  B2_TRY(stage_in(src, span_bytes(M, N, src_ld, src_dt), st, &s_dev));
+  B2_TRY(stage_in(scale, (size_t)n_scale * 4, st, &sc_dev));
+  if (zp) B2_TRY(stage_in(zp, (size_t)n_zp * 4, st, &zp_dev));
+  Staged o;
+  B2_TRY(stage_out(dst, span_bytes(M, N, dst_ld, dst_dt), st, &o, dst_ld != N));
+  dim3 g2((unsigned)((N + 255) / 256), (unsigned)(M > 1024 ? 1024 : M));
+  dequant_static_kernel<<<g2, 256, 0, st>>>(s_dev, src_dt, M, N, src_ld, (const float *)sc_dev, n_scale, (const int32_t *)zp_dev, n_zp, o.dev, dst_dt, dst_ld);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return finish_out({&o}, st);
+}
+
+int32_t b200dnn_gated_act(void *buf, int32_t dt, int64_t M, int64_t N, int64_t ldc, int32_t act, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(buf && M > 0 && N > 0 && N % 2 == 0 && ldc >= N, B200DNN_FAILURE, "bad argument");
+  B2_CHECK(act >= 1 && act <= 3, B200DNN_FAILURE, "unknown gated activation %d", act);
+  B2_CHECK(dt == B200DNN_BF16 || dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "gated activation on f32 or bf16 only");
+  Staged o;
+  B2_TRY(stage_out(buf, span_bytes(M, N, ldc, dt), st, &o, true));
+  if (dt == B200DNN_BF16) gated_act_kernel<uint16_t><<<(unsigned)M, 256, 0, st>>>((uint16_t *)o.dev, N, ldc, act);
+  else gated_act_kernel<float><<<(unsigned)M, 256, 0, st>>>((float *)o.dev, N, ldc, act);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return finish_out({&o}, st);
+}
+
+int32_t b200dnn_moe_weighted_reduce(const void *const *row_ptrs, const float *topk_weights, int32_t T, int32_t topk,
+                                    int32_t D, int32_t skip_weighted, int32_t dt, void *out, int64_t ld_out, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(row_ptrs && out && T > 0 && topk > 0 && D > 0 && ld_out >= D, B200DNN_FAILURE, "bad argument");
+  B2_CHECK(skip_weighted || topk_weights, B200DNN_FAILURE, "topk_weights is null");
+  B2_CHECK(dt == B200DNN_BF16 || dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "weighted reduce on f32 or bf16 only");
+  const size_t nslot = (size_t)T * topk;
+  // row_ptrs is a host array (the reference's contract); rows on the host are staged row by row
+  std::vector<const void *> dev_rows(nslot);
+  const bool rows_on_device = is_device_ptr(row_ptrs[0]);
+  if (rows_on_device) {
+    for (size_t i = 0; i < nslot; ++i) { B2_CHECK(row_ptrs[i], B200DNN_FAILURE, "row_ptrs[%zu] is null", i); dev_rows[i] = row_ptrs[i]; }
+  } else {
+    const size_t rb = (size_t)D * dt_size(dt);
+    uint8_t *slab = (uint8_t *)rt().ws.alloc(nslot * ((rb + 15) & ~size_t(15)));
+    B2_CHECK(slab, B200DNN_FAILURE, "workspace allocation failed");
+    const size_t pitch = (rb + 15) & ~size_t(15);
+    for (size_t i = 0; i < nslot; ++i) {
+      B2_CHECK(row_ptrs[i], B200DNN_FAILURE, "row_ptrs[%zu] is null", i);
+      B2_CUDA(cudaMemcpyAsync(slab + i * pitch, row_ptrs[i], rb, cudaMemcpyHostToDevice, st));
+      dev_rows[i] = slab + i * pitch;
+    }
+  }
+  void *tab = rt().ws.alloc(nslot * sizeof(void *));
+  B2_CHECK(tab, B200DNN_FAILURE, "workspace allocation failed");
+  B2_CUDA(cudaMemcpyAsync(tab, dev_rows.data(), nslot * sizeof(void *), cudaMemcpyHostToDevice, st));
+  B2_CUDA(cudaStreamSynchronize(st));
+  const void *w_dev = nullptr;
+  if (!skip_weighted) B2_TRY(stage_in(topk_weights, nslot * 4, st, &w_dev));
+  Staged o;
+  B2_TRY(stage_out(out, span_bytes(T, D, ld_out, dt), st, &o, ld_out != D));
+  ReduceArgs a{};
+  a.row_ptrs = (const void *const *)tab; a.w = (const float *)w_dev; a.skip_weighted = skip_weighted;
+  a.nslots = topk; a.D = D; a.dt = dt; a.out = o.dev; a.ld_out = ld_out;
+  moe_reduce_kernel<<<(unsigned)T, 256, (sizeof(void *) + 4) * topk, st>>>(a);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return finish_out({&o}, st);
+}
+
+int32_t b200dnn_moe_route(const float *logits, int32_t T, int32_t E, int32_t topk, int32_t renorm, int32_t *ids,
+                          float *weights, int32_t *expert_counts, int32_t *slot_to_row, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(logits && ids && T > 0 && E > 0 && topk > 0 && topk <= E && topk <= kMaxTopk, B200DNN_FAILURE, "bad argument");
+  const void *l_dev;
+  B2_TRY(stage_in(logits, (size_t)T * E * 4, st, &l_dev));
+  const size_t ns = (size_t)T * topk;
+  Staged o_ids, o_w, o_cnt, o_s2r;
+  B2_TRY(stage_out(ids, ns * 4, st, &o_ids));
+  B2_TRY(stage_out(weights, ns * 4, st, &o_w));
+  B2_TRY(stage_out(expert_counts, (size_t)E * 4, st, &o_cnt));
+  B2_TRY(stage_out(slot_to_row, ns * 4, st, &o_s2r));
+  float *w_dev = (float *)o_w.dev;
+  if (!w_dev) { w_dev = (float *)rt().ws.alloc(ns * 4); B2_CHECK(w_dev, B200DNN_FAILURE, "workspace allocation failed"); }
+  route_topk_kernel<<<(unsigned)((T + 127) / 128), 128, 0, st>>>((const float *)l_dev, T, E, topk, renorm, (int32_t *)o_ids.dev, w_dev);
+  B2_LAUNCHED();
+  if (expert_counts || slot_to_row) {
+    int32_t *cnt = (int32_t *)o_cnt.dev;
+    if (!cnt) { cnt = (int32_t *)rt().ws.alloc((size_t)E * 4); B2_CHECK(cnt, B200DNN_FAILURE, "workspace allocation failed"); }
+    int32_t *rank = (int32_t *)rt().ws.alloc(ns * 4);
+    int32_t *off = (int32_t *)rt().ws.alloc((size_t)(E + 1) * 4);
+    B2_CHECK(rank && off, B200DNN_FAILURE, "workspace allocation failed");
+    expert_rank_kernel<<<(unsigned)E, 1024, 0, st>>>((const int32_t *)o_ids.dev, (int)ns, rank, cnt);
+    B2_LAUNCHED();
+    if (slot_to_row) {
+      expert_offsets_kernel<<<1, 32, 0, st>>>(cnt, E, 0, T, off);
+      B2_LAUNCHED();
+      int32_t *row_tok = (int32_t *)rt().ws.alloc(ns * 4);
+      float *sw = (float *)rt().ws.alloc(ns * 4);
+      B2_CHECK(row_tok && sw, B200DNN_FAILURE, "workspace allocation failed");
+      build_maps_kernel<<<(unsigned)((ns + 255) / 256), 256, 0, st>>>((const int32_t *)o_ids.dev, rank, w_dev, off, T, topk, E, 0,
+                                                                     (int32_t *)o_s2r.dev, sw, row_tok);
+      B2_LAUNCHED();
+    }
+  }
+  B2_CUDA(cudaGetLastError());
+  return finish_out({&o_ids, &o_w, &o_cnt, &o_s2r}, st);
+}
+
+// -------------------------------------------------------------------------------------------- matmul
+int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
+  B2_CHECK(d, B200DNN_FAILURE, "null descriptor");
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  Runtime &R = rt();
+  R.ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  const int M = d->M, N = d->N, K = d->K;
+  // ---- contract checks (matmul/lowoha_matmul_utils.cpp:180-420, INT8 subset)
+  B2_CHECK(d->src && d->weight && d->dst, B200DNN_FAILURE, "null src, weight or dst");
+  B2_CHECK(M > 0 && N > 0 && K > 0, B200DNN_FAILURE, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
+  B2_CHECK(d->lda >= K && d->ldc >= N, B200DNN_FAILURE, "lda/ldc smaller than the row length");
+  B2_CHECK(d->wei_format == 'r' || d->ldb >= (d->transB ? K : N), B200DNN_FAILURE, "ldb smaller than the row length");
+  B2_CHECK(d->wei_dt == B200DNN_S8, B200DNN_UNIMPLEMENTED, "only s8 weights are implemented (wei dtype %d)", d->wei_dt);
+  B2_CHECK(d->dst_dt == B200DNN_BF16 || d->dst_dt == B200DNN_F32 || d->dst_dt == B200DNN_S32, B200DNN_UNIMPLEMENTED,
+           "dst dtype %d is not implemented for the INT8 path", d->dst_dt);
+  B2_CHECK(d->n_postops >= 0 && d->n_postops <= B200DNN_MAX_POSTOPS, B200DNN_FAILURE, "too many post-ops");
+  const bool dyn = d->dynamic_quant != 0;
+  if (dyn) {
+    B2_CHECK(d->src_dt == B200DNN_BF16 || d->src_dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "dynamic quantisation takes a bf16 or f32 source");
+    B2_CHECK(d->src_scale.count == M || (M == 1 && d->src_scale.count == 1) || d->src_scale.count == 0, B200DNN_UNIMPLEMENTED,
+             "dynamic quantisation is per-token only (src scale count %lld, M %d)", (long long)d->src_scale.count, M);
+    B2_CHECK(d->src_zp.buff == nullptr, B200DNN_UNIMPLEMENTED, "asymmetric dynamic quantisation is not implemented");
+  } else {
+    B2_CHECK(d->src_dt == B200DNN_S8 || d->src_dt == B200DNN_U8, B200DNN_UNIMPLEMENTED, "src dtype %d without dynamic_quant", d->src_dt);
+    B2_CHECK(d->src_scale.count == 0 || d->src_scale.buff, B200DNN_FAILURE, "src scale buffer is null");
+    B2_CHECK(d->src_scale.count == 0 || d->src_scale.count == 1 || d->src_scale.count == M, B200DNN_UNIMPLEMENTED,
+             "src scale must be per-tensor or per-token");
+  }
+  const bool per_token = d->src_scale.count > 1 || (dyn && M > 1);
+  if (per_token) {
+    // per-token rules: symmetric source, float destination, per-channel weight scale of N elements
+    // (matmul/lowoha_matmul_utils.cpp:252-292)
+    B2_CHECK(d->src_zp.buff == nullptr, B200DNN_FAILURE, "per-token source scale does not allow a zero-point");
+    B2_CHECK(dyn || d->src_dt == B200DNN_S8, B200DNN_FAILURE, "per-token source scale needs a symmetric s8 source");
+    B2_CHECK(d->dst_dt != B200DNN_S32, B200DNN_FAILURE, "per-token source scale needs an f32 or bf16 destination");
+    B2_CHECK(d->wei_scale.count == N, B200DNN_FAILURE, "per-token source scale needs a per-channel weight scale of N elements");
+  }
+  B2_CHECK(d->wei_scale.count == 0 || d->wei_scale.count == 1 || d->wei_scale.count == N, B200DNN_UNIMPLEMENTED,
+           "weight scale must be per-tensor or per-channel");
+  B2_CHECK(d->wei_scale.count == 0 || d->wei_scale.buff, B200DNN_FAILURE, "weight scale buffer is null");
+  B2_CHECK(d->src_zp.buff == nullptr || d->src_zp.count <= 1, B200DNN_UNIMPLEMENTED, "src zero-point must be per-tensor");
+  auto scale_dt_ok = [](int32_t dt) { return dt == B200DNN_F32 || dt == B200DNN_BF16; };
+  B2_CHECK(d->src_scale.count == 0 || !d->src_scale.buff || scale_dt_ok(d->src_scale.dt), B200DNN_UNIMPLEMENTED, "src scale dtype");
+  B2_CHECK(d->wei_scale.count == 0 || scale_dt_ok(d->wei_scale.dt), B200DNN_UNIMPLEMENTED, "weight scale dtype");
+  B2_CHECK(!d->bias || scale_dt_ok(d->bias_dt), B200DNN_UNIMPLEMENTED, "bias dtype %d", d->bias_dt);
+  if (d->dst_dt == B200DNN_S32)
+    B2_CHECK(d->src_scale.count == 0 && d->wei_scale.count == 0 && !d->bias && d->n_postops == 0, B200DNN_UNIMPLEMENTED,
+             "s32 destination returns raw compensated accumulators: no scales, bias or post-ops");
+  for (int i = 0; i < d->n_postops; ++i) {
+    const b200dnn_postop_t &p = d->postops[i];
+    switch (p.type) {
+    case PO_RELU: case PO_LEAKY_RELU: case PO_GELU_TANH: case PO_GELU_ERF: case PO_SIGMOID: case PO_SWISH: case PO_TANH: case PO_ELU: break;
+    case PO_CLIP: B2_CHECK(isfinite(p.alpha) && isfinite(p.beta), B200DNN_FAILURE, "clip bounds must be finite"); break;
+    case PO_BINARY_ADD: case PO_BINARY_MUL:
+      B2_CHECK(p.buff && (p.dt == B200DNN_F32 || p.dt == B200DNN_BF16), B200DNN_FAILURE, "binary post-op needs an f32 or bf16 operand");
+      B2_CHECK(p.ld == 0 || p.ld >= N, B200DNN_FAILURE, "binary post-op leading dimension");
+      break;
+    case PO_MISH: return fail(B200DNN_FAILURE, "mish is rejected on the INT8 path");
+    default: return fail(B200DNN_UNIMPLEMENTED, "post-op %d is not implemented", p.type);
+    }
+  }
+
+  // ---- operands on the device
+  PackedWeight pw;
+  B2_TRY(resolve_weight(d->weight, d->wei_format, K, N, d->ldb, d->transB, 0, d->weights_const, st, &pw));
+  EpiParams epi;
+  fill_epi(d, &epi);
+  const void *src_dev = nullptr;
+  B2_TRY(stage_in(d->src, span_bytes(M, K, d->lda, d->src_dt), st, &src_dev));
+  const uint8_t *A = (const uint8_t *)src_dev; int64_t lda = d->lda; bool a_unsigned = d->src_dt == B200DNN_U8;
+  Staged o_scale; o_scale.copy_back = false;
+  if (dyn) {
+    const int64_t Kq = round_up(K, 16);
+    int8_t *q = (int8_t *)R.ws.alloc((size_t)M * Kq);
+    B2_CHECK(q, B200DNN_FAILURE, "workspace allocation failed");
+    const int32_t sdt = d->src_scale.buff ? d->src_scale.dt : B200DNN_F32;
+    B2_TRY(stage_out(const_cast<void *>(d->src_scale.buff), (size_t)M * dt_size(sdt), st, &o_scale));
+    void *sc = o_scale.dev;
+    if (!sc) { sc = R.ws.alloc((size_t)M * 4); B2_CHECK(sc, B200DNN_FAILURE, "workspace allocation failed"); }
+    RowQuantArgs qa{};
+    qa.src = src_dev; qa.src_ld = d->lda; qa.dst = q; qa.dst_ld = Kq; qa.scale = sc; qa.scale_dt = sdt; qa.K = K; qa.gather_div = 1;
+    B2_TRY(launch_quant_rows(qa, d->src_dt, M, st));
+    A = (const uint8_t *)q; lda = Kq; a_unsigned = false;
+    epi.src_scale = sc; epi.src_scale_dt = sdt; epi.src_scale_n = M > 1 ? M : 1;
+  } else if (d->src_scale.count > 0) {
+    const void *p;
+    B2_TRY(stage_in(d->src_scale.buff, (size_t)d->src_scale.count * dt_size(d->src_scale.dt), st, &p));
+    epi.src_scale = p; epi.src_scale_dt = d->src_scale.dt; epi.src_scale_n = (int32_t)d->src_scale.count;
+  }
+  if (d->wei_scale.count > 0) {
+    const void *p;
+    B2_TRY(stage_in(d->wei_scale.buff, (size_t)d->wei_scale.count * dt_size(d->wei_scale.dt), st, &p));
+    epi.wei_scale = p; epi.wei_scale_dt = d->wei_scale.dt; epi.wei_scale_n = (int32_t)d->wei_scale.count;
+  }
+  if (d->src_zp.buff) {
+    B2_CHECK(d->src_zp.dt == B200DNN_S32 || d->src_zp.dt == B200DNN_S8 || d->src_zp.dt == B200DNN_U8, B200DNN_UNIMPLEMENTED, "src zero-point dtype");
+    const void *p;
+    B2_TRY(stage_in(d->src_zp.buff, dt_size(d->src_zp.dt), st, &p));
+    epi.src_zp = p; epi.src_zp_dt = d->src_zp.dt; epi.has_zp = 1;
+  }
+  epi.colsum = pw.colsum;
+  if (d->bias) {
+    const void *p;
+    B2_TRY(stage_in(d->bias, (size_t)N * dt_size(d->bias_dt), st, &p));
+    epi.bias = p;
+  }
+  for (int i = 0; i < d->n_postops; ++i) {
+    const b200dnn_postop_t &p = d->postops[i];
+    epi.po[i].type = p.type; epi.po[i].dt = p.dt; epi.po[i].ld = p.ld; epi.po[i].alpha = p.alpha; epi.po[i].beta = p.beta;
+    epi.po[i].buff = nullptr;
+    if (p.type == PO_BINARY_ADD || p.type == PO_BINARY_MUL) {
+      const void *b;
+      B2_TRY(stage_in(p.buff, p.ld ? span_bytes(M, N, p.ld, p.dt) : (size_t)N * dt_size(p.dt), st, &b));
+      epi.po[i].buff = b;
+    }
+  }
+  Staged o_dst;
+  B2_TRY(stage_out(d->dst, span_bytes(M, N, d->ldc, d->dst_dt), st, &o_dst, d->ldc != N));
+  epi.dst = o_dst.dev;
+
+  // ---- kernel choice: weight-streaming kernel for decode-sized M, tcgen05 otherwise
+  const bool tc_ok = (lda % 16 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+  int which = d->force_kernel;
+  if (which == 0) which = (M <= 16 || !tc_ok) ? 1 : 2;
+  B2_CHECK(which == 1 || tc_ok, B200DNN_FAILURE, "tcgen05 kernel needs a 16-byte aligned source with lda %% 16 == 0");
+  if (which == 1) {
+    B2_TRY(launch_stream(A, lda, a_unsigned, M, N, K, pw, epi, st));
+  } else {
+    TcGemmArgs ta{};
+    ta.n_groups = 1; ta.m_tiles_plain = (M + kTcBM - 1) / kTcBM;
+    B2_TRY(launch_tc(A, lda, a_unsigned, M, N, K, pw, ta, epi, ta.m_tiles_plain, st));
+  }
+  const bool sync_path = o_dst.copy_back || o_scale.copy_back;
+  B2_TRY(finish_out({&o_dst, &o_scale}, st));
+  if (which == 2 && sync_path) B2_TRY(check_tc_status(st));
+  return B200DNN_SUCCESS;
+}
+
+int32_t b200dnn_clear_caches(void) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  Runtime &R = rt();
+  if (device_count() > 0) cudaDeviceSynchronize();
+  for (auto &kv : R.wcache) if (kv.second.owned) cudaFree(kv.second.owned);
+  R.wcache.clear();
+  for (auto &kv : R.host_packed) if (kv.second.owned) cudaFree(kv.second.owned);
+  R.host_packed.clear();
+  R.packed_registry.clear();
+  R.ws.release();
+  return B200DNN_SUCCESS;
+}
+
+}  // extern "C"
+
+#include "moe_api.cuh"

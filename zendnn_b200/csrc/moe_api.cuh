@@ -1,0 +1,298 @@
+// Fused MoE entry points: b200dnn_fused_moe (the reference's group_matmul_direct contract, rows
+// gathered by the caller) and b200dnn_moe_layer (router + permutation in front, un-permute
+// behind).  Included at the end of b200dnn.cu.
+//
+// Data flow per expert, as in the reference's dynamic-INT8 two-pass semantics
+// (matmul/group_matmul/group_matmul_fused_moe.cpp:906-1078):
+//   A1 = quant_per_token(src)                          one kernel over all experts' rows
+//   Z  = bf16( act( dequant(A1 x W13) ) )              grouped tcgen05 GEMM, gated epilogue,
+//                                                      per-row max |Z| collected with atomicMax
+//   A2 = quant_per_token(Z) using that max             one kernel, Z read once
+//   O  = bf16( dequant(A2 x W2) )                      grouped tcgen05 GEMM
+//   out[t] = sum_k w[t,k] * O[row(t,k)]                weighted reduce
+#pragma once
+
+namespace {
+
+__global__ void tile_prefix_kernel(const int32_t *row_off, int n_groups, int32_t *tile_prefix) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int acc = 0;
+    for (int g = 0; g < n_groups; ++g) { tile_prefix[g] = acc; acc += (row_off[g + 1] - row_off[g] + kTcBM - 1) / kTcBM; }
+    tile_prefix[n_groups] = acc;
+  }
+}
+
+struct MoeWeights {
+  std::vector<PackedWeight> w13, w2;
+  const CUtensorMap *maps13 = nullptr, *maps2 = nullptr;   // device arrays
+  TcGroupDesc *g13 = nullptr, *g2 = nullptr;               // device arrays
+  int BN13 = 0, BN2 = 0;
+};
+
+// Uploads a host blob into workspace memory and waits for the copy (the blob is a local).
+int32_t upload_blob(const void *host, size_t bytes, cudaStream_t st, void **dev) {
+  void *d = rt().ws.alloc(bytes);
+  B2_CHECK(d, B200DNN_FAILURE, "workspace allocation failed");
+  B2_CUDA(cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, st));
+  B2_CUDA(cudaStreamSynchronize(st));
+  *dev = d;
+  return B200DNN_SUCCESS;
+}
+
+int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const std::vector<PackedWeight> &pws,
+                     const int32_t *row_off_dev, const int32_t *tile_prefix_dev, const TcGroupDesc *groups_dev,
+                     int m_tiles_bound, EpiParams epi, cudaStream_t st) {
+  Runtime &Rt = rt();
+  const int G = (int)pws.size();
+  TcGemmArgs ta{};
+  ta.n_groups = G; ta.row_off = row_off_dev; ta.tile_prefix = tile_prefix_dev; ta.groups = groups_dev;
+  // one tensor map per expert, in device memory
+  const PackedWeight &p0 = pws[0];
+  const int BN = pick_bn(m_tiles_bound, N, Rt.sm_count, p0.gated);
+  std::vector<CUtensorMap> maps(G);
+  for (int g = 0; g < G; ++g) {
+    B2_CHECK(pws[g].Kp == p0.Kp && pws[g].Np == p0.Np && pws[g].gated == p0.gated, B200DNN_UNIMPLEMENTED,
+             "experts of one grouped GEMM must share K and N");
+    B2_TRY(make_map_2d(&maps[g], pws[g].wt, (uint64_t)p0.Kp, (uint64_t)p0.Np, (uint64_t)p0.Kp, (uint32_t)BN));
+  }
+  void *maps_dev = nullptr;
+  B2_TRY(upload_blob(maps.data(), sizeof(CUtensorMap) * G, st, &maps_dev));
+  ta.maps_b = (const CUtensorMap *)maps_dev;
+  // launch_tc picks the same BN from the same inputs
+  return launch_tc(A, lda, false, R, N, K, p0, ta, epi, m_tiles_bound, st);
+}
+
+struct ExpertWeightsIn {
+  const void *w13; int64_t ldb13; const float *s13; const void *w2; int64_t ldb2; const float *s2;
+};
+
+// Shared core: rows already laid out expert by expert in device memory as the gather described by qa.
+int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, int H, int transB, int act, int weights_const,
+                 RowQuantArgs qa, int32_t src_dt, int R, const int32_t *row_off_dev, const int32_t *tile_prefix_dev,
+                 int m_tiles_bound, const std::vector<void *> *dst_down_dev, const std::vector<int64_t> *ldc_down,
+                 void **O_out, int64_t *ldO_out, cudaStream_t st) {
+  Runtime &Rt = rt();
+  B2_CHECK(act >= 1 && act <= 3, B200DNN_UNIMPLEMENTED, "fused MoE needs a gated activation (got %d)", act);
+  B2_CHECK(I % kGateGranule == 0, B200DNN_UNIMPLEMENTED, "expert FFN width must be a multiple of %d", kGateGranule);
+  const int gated = act == ACT_SWIGLU_OAI ? 2 : 1;
+  std::vector<PackedWeight> p13(G), p2(G);
+  std::vector<TcGroupDesc> g13(G), g2(G);
+  for (int g = 0; g < G; ++g) {
+    B2_CHECK(ew[g].w13 && ew[g].w2 && ew[g].s13 && ew[g].s2, B200DNN_FAILURE, "expert %d: null weight or scale", g);
+    B2_TRY(resolve_weight(ew[g].w13, 'n', K, 2 * (int64_t)I, ew[g].ldb13, transB, gated, weights_const, st, &p13[g]));
+    B2_TRY(resolve_weight(ew[g].w2, 'n', I, H, ew[g].ldb2, transB, 0, weights_const, st, &p2[g]));
+    const void *s13, *s2;
+    B2_TRY(stage_in(ew[g].s13, (size_t)2 * I * 4, st, &s13));
+    B2_TRY(stage_in(ew[g].s2, (size_t)H * 4, st, &s2));
+    g13[g] = TcGroupDesc{s13, p13[g].colsum, nullptr, nullptr, 0};
+    g2[g] = TcGroupDesc{s2, p2[g].colsum, nullptr, dst_down_dev ? (*dst_down_dev)[g] : nullptr, ldc_down ? (*ldc_down)[g] : 0};
+  }
+  void *g13_dev, *g2_dev;
+  B2_TRY(upload_blob(g13.data(), sizeof(TcGroupDesc) * G, st, &g13_dev));
+  B2_TRY(upload_blob(g2.data(), sizeof(TcGroupDesc) * G, st, &g2_dev));
+
+  const int64_t Kq = round_up(K, 16), Iq = round_up(I, 16);
+  int8_t *A1 = (int8_t *)Rt.ws.alloc((size_t)R * Kq);
+  float *s1 = (float *)Rt.ws.alloc((size_t)R * 4);
+  uint16_t *Z = (uint16_t *)Rt.ws.alloc((size_t)R * I * 2);
+  uint32_t *zmax = (uint32_t *)Rt.ws.alloc((size_t)R * 4);
+  int8_t *A2 = (int8_t *)Rt.ws.alloc((size_t)R * Iq);
+  float *s2v = (float *)Rt.ws.alloc((size_t)R * 4);
+  B2_CHECK(A1 && s1 && Z && zmax && A2 && s2v, B200DNN_FAILURE, "workspace allocation failed");
+  B2_CUDA(cudaMemsetAsync(zmax, 0, (size_t)R * 4, st));
+
+  // 1. quantise the gathered rows
+  qa.dst = A1; qa.dst_ld = Kq; qa.scale = s1; qa.scale_dt = B200DNN_F32; qa.K = K;
+  B2_TRY(launch_quant_rows(qa, src_dt, R, st));
+
+  // 2. first GEMM with the gated epilogue -> Z (bf16, [R, I]) and per-row max |Z|
+  EpiParams e1{};
+  e1.src_scale = s1; e1.src_scale_dt = B200DNN_F32; e1.src_scale_n = R > 1 ? R : 2;  // always per-row
+  e1.wei_scale_dt = B200DNN_F32; e1.wei_scale_n = 2 * I;
+  e1.dst = Z; e1.ldc = I; e1.dst_dt = B200DNN_BF16; e1.gated_act = act; e1.gated_I = I; e1.row_absmax = zmax;
+  B2_TRY(grouped_gemm((const uint8_t *)A1, Kq, R, 2 * I, K, p13, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g13_dev,
+                      m_tiles_bound, e1, st));
+
+  // 3. re-quantise the activated rows (from their bf16 values, as the reference does)
+  RowQuantArgs q2{};
+  q2.src = Z; q2.src_ld = I; q2.dst = A2; q2.dst_ld = Iq; q2.scale = s2v; q2.scale_dt = B200DNN_F32; q2.K = I;
+  q2.absmax_bits = zmax; q2.gather_div = 1;
+  B2_TRY(launch_quant_rows(q2, B200DNN_BF16, R, st));
+
+  // 4. second GEMM -> O
+  uint16_t *O = nullptr;
+  if (!dst_down_dev) { O = (uint16_t *)Rt.ws.alloc((size_t)R * H * 2); B2_CHECK(O, B200DNN_FAILURE, "workspace allocation failed"); }
+  EpiParams e2{};
+  e2.src_scale = s2v; e2.src_scale_dt = B200DNN_F32; e2.src_scale_n = R > 1 ? R : 2;
+  e2.wei_scale_dt = B200DNN_F32; e2.wei_scale_n = H;
+  e2.dst = O; e2.ldc = H; e2.dst_dt = B200DNN_BF16;
+  B2_TRY(grouped_gemm((const uint8_t *)A2, Iq, R, H, I, p2, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g2_dev,
+                      m_tiles_bound, e2, st));
+  if (O_out) { *O_out = O; *ldO_out = H; }
+  return B200DNN_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, int32_t K, int32_t I, int32_t H,
+                                     int32_t transB, int32_t act, int32_t weights_const, const void *const *row_ptrs,
+                                     const float *topk_weights, int32_t T, int32_t topk, void *out, int64_t ld_out,
+                                     void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  Runtime &Rt = rt();
+  Rt.ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(G > 0 && ex && K > 0 && I > 0 && H > 0, B200DNN_FAILURE, "bad argument");
+  std::vector<int32_t> row_off(G + 1, 0), tile_prefix(G + 1, 0);
+  for (int g = 0; g < G; ++g) {
+    B2_CHECK(ex[g].M >= 0, B200DNN_FAILURE, "expert %d: negative M", g);
+    row_off[g + 1] = row_off[g] + ex[g].M;
+    tile_prefix[g + 1] = tile_prefix[g] + (ex[g].M + kTcBM - 1) / kTcBM;
+    if (ex[g].M > 0) {
+      B2_CHECK(ex[g].src && ex[g].dst_down, B200DNN_FAILURE, "expert %d: null src or dst_down", g);
+      B2_CHECK(ex[g].lda >= K && ex[g].ldc_down >= H, B200DNN_FAILURE, "expert %d: leading dimension too small", g);
+    }
+  }
+  const int R = row_off[G];
+  if (R == 0) return B200DNN_SUCCESS;
+  // stage per-expert sources / destinations and build the device tables
+  std::vector<const void *> src_dev(G, nullptr);
+  std::vector<void *> dst_dev(G, nullptr);
+  std::vector<int64_t> src_ld(G), ldc_down(G);
+  std::vector<Staged> outs(G);
+  for (int g = 0; g < G; ++g) {
+    src_ld[g] = ex[g].lda; ldc_down[g] = ex[g].ldc_down;
+    outs[g].copy_back = false;
+    if (ex[g].M == 0) continue;
+    B2_TRY(stage_in(ex[g].src, span_bytes(ex[g].M, K, ex[g].lda, B200DNN_BF16), st, &src_dev[g]));
+    B2_TRY(stage_out(ex[g].dst_down, span_bytes(ex[g].M, H, ex[g].ldc_down, B200DNN_BF16), st, &outs[g], ex[g].ldc_down != H));
+    dst_dev[g] = outs[g].dev;
+  }
+  // blob: src ptrs | src ld | row_off | tile_prefix
+  const size_t o_ptr = 0, o_ld = o_ptr + sizeof(void *) * G, o_ro = o_ld + sizeof(int64_t) * G,
+               o_tp = o_ro + sizeof(int32_t) * (G + 1), total = o_tp + sizeof(int32_t) * (G + 1);
+  std::vector<uint8_t> blob((total + 15) & ~size_t(15));
+  memcpy(blob.data() + o_ptr, src_dev.data(), sizeof(void *) * G);
+  memcpy(blob.data() + o_ld, src_ld.data(), sizeof(int64_t) * G);
+  memcpy(blob.data() + o_ro, row_off.data(), sizeof(int32_t) * (G + 1));
+  memcpy(blob.data() + o_tp, tile_prefix.data(), sizeof(int32_t) * (G + 1));
+  void *bd;
+  B2_TRY(upload_blob(blob.data(), blob.size(), st, &bd));
+  uint8_t *b = (uint8_t *)bd;
+  const int32_t *row_off_dev = (const int32_t *)(b + o_ro), *tile_prefix_dev = (const int32_t *)(b + o_tp);
+
+  std::vector<ExpertWeightsIn> ew(G);
+  for (int g = 0; g < G; ++g) ew[g] = ExpertWeightsIn{ex[g].w13, ex[g].ldb13, ex[g].w13_scale, ex[g].w2, ex[g].ldb2, ex[g].w2_scale};
+
+  // the experts' rows are first laid back to back in one bf16 slab, then quantised in one launch
+  RowQuantArgs qa{};
+  qa.gather_div = 1;
+  uint16_t *X = (uint16_t *)Rt.ws.alloc((size_t)R * K * 2);
+  B2_CHECK(X, B200DNN_FAILURE, "workspace allocation failed");
+  for (int g = 0; g < G; ++g) {
+    if (ex[g].M == 0) continue;
+    B2_CUDA(cudaMemcpy2DAsync(X + (size_t)row_off[g] * K, (size_t)K * 2, src_dev[g], (size_t)ex[g].lda * 2, (size_t)K * 2,
+                              (size_t)ex[g].M, cudaMemcpyDeviceToDevice, st));
+  }
+  qa.src = X; qa.src_ld = K;
+
+  B2_TRY(moe_core(G, ew, K, I, H, transB, act, weights_const, qa, B200DNN_BF16, R, row_off_dev, tile_prefix_dev,
+                  tile_prefix[G], &dst_dev, &ldc_down, nullptr, nullptr, st));
+
+  Staged o_out; o_out.copy_back = false;
+  if (row_ptrs) {
+    B2_CHECK(out && T > 0 && topk > 0 && ld_out >= H, B200DNN_FAILURE, "weighted reduce: bad argument");
+    B2_CHECK(topk_weights, B200DNN_FAILURE, "weighted reduce: topk_weights is null");
+    const size_t ns = (size_t)T * topk;
+    // translate the caller's row pointers (into dst_down buffers) to device addresses
+    std::vector<const void *> dev_rows(ns);
+    for (size_t i = 0; i < ns; ++i) {
+      const uint8_t *p = (const uint8_t *)row_ptrs[i];
+      B2_CHECK(p, B200DNN_FAILURE, "row_ptrs[%zu] is null", i);
+      const void *dp = nullptr;
+      for (int g = 0; g < G && !dp; ++g) {
+        if (ex[g].M == 0) continue;
+        const uint8_t *lo = (const uint8_t *)ex[g].dst_down;
+        const uint8_t *hi = lo + span_bytes(ex[g].M, H, ex[g].ldc_down, B200DNN_BF16);
+        if (p >= lo && p < hi) dp = (const uint8_t *)dst_dev[g] + (p - lo);
+      }
+      B2_CHECK(dp, B200DNN_FAILURE, "row_ptrs[%zu] does not point into any dst_down buffer", i);
+      dev_rows[i] = dp;
+    }
+    void *tab, *w_dev;
+    B2_TRY(upload_blob(dev_rows.data(), ns * sizeof(void *), st, &tab));
+    const void *wd;
+    B2_TRY(stage_in(topk_weights, ns * 4, st, &wd));
+    w_dev = const_cast<void *>(wd);
+    B2_TRY(stage_out(out, span_bytes(T, H, ld_out, B200DNN_BF16), st, &o_out, ld_out != H));
+    ReduceArgs ra{};
+    ra.row_ptrs = (const void *const *)tab; ra.w = (const float *)w_dev; ra.nslots = topk; ra.D = H; ra.dt = B200DNN_BF16;
+    ra.out = o_out.dev; ra.ld_out = ld_out;
+    moe_reduce_kernel<<<(unsigned)T, 256, (sizeof(void *) + 4) * topk, st>>>(ra);
+    B2_LAUNCHED();
+    B2_CUDA(cudaGetLastError());
+  }
+  bool any = o_out.copy_back;
+  for (auto &s : outs) if (s.copy_back) { B2_CUDA(cudaMemcpyAsync(s.host, s.dev, s.bytes, cudaMemcpyDeviceToHost, st)); any = true; }
+  if (o_out.copy_back) B2_CUDA(cudaMemcpyAsync(o_out.host, o_out.dev, o_out.bytes, cudaMemcpyDeviceToHost, st));
+  if (any) { B2_CUDA(cudaStreamSynchronize(st)); B2_TRY(check_tc_status(st)); }
+  return B200DNN_SUCCESS;
+}
+
+extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *logits, int32_t T, int32_t E, int32_t S,
+                                     int32_t topk, const b200dnn_moe_expert_t *ex, int32_t K, int32_t I, int32_t H,
+                                     int32_t transB, int32_t act, void *out, int64_t ld_out, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  Runtime &Rt = rt();
+  Rt.ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(x && logits && ex && out && T > 0 && E > 0 && S >= 0 && topk > 0 && topk <= E && topk <= kMaxTopk, B200DNN_FAILURE, "bad argument");
+  B2_CHECK(ldx >= K && ld_out >= H, B200DNN_FAILURE, "leading dimension too small");
+  const int G = E + S, ns = topk + S, R = T * ns;
+  const void *x_dev, *l_dev;
+  B2_TRY(stage_in(x, span_bytes(T, K, ldx, B200DNN_BF16), st, &x_dev));
+  B2_TRY(stage_in(logits, (size_t)T * E * 4, st, &l_dev));
+  int32_t *ids = (int32_t *)Rt.ws.alloc((size_t)T * topk * 4);
+  float *w = (float *)Rt.ws.alloc((size_t)T * topk * 4);
+  int32_t *rank = (int32_t *)Rt.ws.alloc((size_t)T * topk * 4);
+  int32_t *cnt = (int32_t *)Rt.ws.alloc((size_t)E * 4);
+  int32_t *row_off = (int32_t *)Rt.ws.alloc((size_t)(G + 1) * 4);
+  int32_t *tile_prefix = (int32_t *)Rt.ws.alloc((size_t)(G + 1) * 4);
+  int32_t *slot_rows = (int32_t *)Rt.ws.alloc((size_t)R * 4);
+  float *slot_w = (float *)Rt.ws.alloc((size_t)R * 4);
+  int32_t *row_token = (int32_t *)Rt.ws.alloc((size_t)R * 4);
+  B2_CHECK(ids && w && rank && cnt && row_off && tile_prefix && slot_rows && slot_w && row_token, B200DNN_FAILURE, "workspace allocation failed");
+  route_topk_kernel<<<(unsigned)((T + 127) / 128), 128, 0, st>>>((const float *)l_dev, T, E, topk, 1, ids, w);
+  B2_LAUNCHED();
+  expert_rank_kernel<<<(unsigned)E, 1024, 0, st>>>(ids, T * topk, rank, cnt);
+  B2_LAUNCHED();
+  expert_offsets_kernel<<<1, 32, 0, st>>>(cnt, E, S, T, row_off);
+  B2_LAUNCHED();
+  tile_prefix_kernel<<<1, 32, 0, st>>>(row_off, G, tile_prefix);
+  B2_LAUNCHED();
+  build_maps_kernel<<<(unsigned)((R + 255) / 256), 256, 0, st>>>(ids, rank, w, row_off, T, topk, E, S, slot_rows, slot_w, row_token);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+
+  std::vector<ExpertWeightsIn> ew(G);
+  for (int g = 0; g < G; ++g) ew[g] = ExpertWeightsIn{ex[g].w13, ex[g].ldb13, ex[g].w13_scale, ex[g].w2, ex[g].ldb2, ex[g].w2_scale};
+  RowQuantArgs qa{};
+  qa.src = x_dev; qa.src_ld = ldx; qa.gather = row_token; qa.gather_div = 1;
+  void *O = nullptr; int64_t ldO = 0;
+  const int m_tiles_bound = (R + kTcBM - 1) / kTcBM + G;
+  B2_TRY(moe_core(G, ew, K, I, H, transB, act, 1, qa, B200DNN_BF16, R, row_off, tile_prefix, m_tiles_bound, nullptr, nullptr, &O, &ldO, st));
+
+  Staged o_out;
+  B2_TRY(stage_out(out, span_bytes(T, H, ld_out, B200DNN_BF16), st, &o_out, ld_out != H));
+  ReduceArgs ra{};
+  ra.base = O; ra.ld = ldO; ra.slot_rows = slot_rows; ra.w = slot_w; ra.nslots = ns; ra.D = H; ra.dt = B200DNN_BF16;
+  ra.out = o_out.dev; ra.ld_out = ld_out;
+  moe_reduce_kernel<<<(unsigned)T, 256, (sizeof(void *) + 4) * ns, st>>>(ra);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  B2_TRY(finish_out({&o_out}, st));
+  if (o_out.copy_back) B2_TRY(check_tc_status(st));
+  return B200DNN_SUCCESS;
+}

@@ -1,0 +1,189 @@
+// Memory-bound pieces of the fused MoE path around the grouped GEMMs:
+//  - gated activation as a separate pass  (matmul/group_matmul/group_matmul_moe_act.cpp:88-196, 728)
+//  - weighted top-k reduce over gathered rows (matmul/group_matmul/group_matmul_moe_postop.cpp:103-129, 216-283)
+//  - router softmax / top-k / renormalise and the stable expert-sorted permutation.  The reference has no
+//    such code (its callers prepare src[e] and row_ptrs themselves,
+//    examples/lowoha_group_matmul_example.cpp:273-300); the specification is stated at route_topk_kernel.
+#pragma once
+#include "common.cuh"
+#include "quant_kernels.cuh"
+
+namespace b200 {
+
+// ---- gated activation, in place on [M, N=2I] rows; one CTA per row --------------------------------
+// Chunked so that the in-place element-interleaved form never overwrites a value before it is read:
+// chunk c reads columns [2cB, 2(c+1)B) (or the two halves) and writes [cB, (c+1)B).
+template <typename T>
+__global__ void __launch_bounds__(256) gated_act_kernel(T *buf, int64_t N, int64_t ldc, int act) {
+  T *row = buf + (int64_t)blockIdx.x * ldc;
+  const int64_t I = N / 2;
+  for (int64_t base = 0; base < I; base += blockDim.x) {
+    const int64_t n = base + threadIdx.x;
+    float g = 0.f, u = 0.f;
+    if (n < I) {
+      if (act == ACT_SWIGLU_OAI) { g = elem_to_f32<T>(row[2 * n]); u = elem_to_f32<T>(row[2 * n + 1]); }
+      else { g = elem_to_f32<T>(row[n]); u = elem_to_f32<T>(row[I + n]); }
+    }
+    __syncthreads();
+    if (n < I) {
+      float r = gated_f32(act, g, u);
+      if (sizeof(T) == 2) reinterpret_cast<uint16_t *>(row)[n] = f32_to_bf16_bits(r);
+      else reinterpret_cast<float *>(row)[n] = r;
+    }
+    __syncthreads();
+  }
+}
+
+// ---- weighted reduce ---------------------------------------------------------------------------------
+// out[t,d] = sum_k w[t,k] * row(t,k)[d]; f32 accumulate in k order: multiply for k = 0, fused
+// multiply-add afterwards (the association of the reference's vector form), RNE store.
+// Rows come either from a device array of pointers (the reference's row_ptrs) or from
+// base + slot_rows[t*nslots+k] * ld (the in-library un-permute).
+struct ReduceArgs {
+  const void *const *row_ptrs;
+  const void *base; int64_t ld; const int32_t *slot_rows;
+  const float *w; int skip_weighted;
+  int nslots, D, dt;
+  void *out; int64_t ld_out;
+};
+__global__ void __launch_bounds__(256) moe_reduce_kernel(ReduceArgs a) {
+  const int t = blockIdx.x;
+  extern __shared__ uint8_t rsm[];
+  const void **rows = reinterpret_cast<const void **>(rsm);
+  float *ws = reinterpret_cast<float *>(rsm + sizeof(void *) * a.nslots);
+  for (int k = threadIdx.x; k < a.nslots; k += blockDim.x) {
+    const int64_t slot = (int64_t)t * a.nslots + k;
+    const void *p;
+    if (a.row_ptrs) p = a.row_ptrs[slot];
+    else p = reinterpret_cast<const uint8_t *>(a.base) + (int64_t)a.slot_rows[slot] * a.ld * (a.dt == DT_BF16 ? 2 : 4);
+    rows[k] = p;
+    ws[k] = a.skip_weighted ? 1.f : a.w[slot];
+  }
+  __syncthreads();
+  if (a.dt == DT_BF16) {
+    uint16_t *o = reinterpret_cast<uint16_t *>(a.out) + (int64_t)t * a.ld_out;
+    bool vec = (a.D % 8 == 0) && ((reinterpret_cast<uintptr_t>(o) & 15) == 0);
+    for (int k = 0; k < a.nslots; ++k) vec = vec && ((reinterpret_cast<uintptr_t>(rows[k]) & 15) == 0);
+    if (vec) {
+      for (int v = threadIdx.x; v < a.D / 8; v += blockDim.x) {
+        float acc[8];
+        for (int k = 0; k < a.nslots; ++k) {
+          uint4 q = reinterpret_cast<const uint4 *>(rows[k])[v];
+          const uint16_t *e = reinterpret_cast<const uint16_t *>(&q);
+          const float wk = ws[k];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float x = bf16_bits_to_f32(e[i]);
+            acc[i] = k == 0 ? __fmul_rn(wk, x) : __fmaf_rn(wk, x, acc[i]);
+          }
+        }
+        uint16_t r[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r[i] = f32_to_bf16_bits(a.nslots ? acc[i] : 0.f);
+        reinterpret_cast<uint4 *>(o)[v] = *reinterpret_cast<uint4 *>(r);
+      }
+    } else {
+      for (int d = threadIdx.x; d < a.D; d += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < a.nslots; ++k) {
+          float x = bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(rows[k])[d]);
+          acc = k == 0 ? __fmul_rn(ws[k], x) : __fmaf_rn(ws[k], x, acc);
+        }
+        o[d] = f32_to_bf16_bits(acc);
+      }
+    }
+  } else {
+    float *o = reinterpret_cast<float *>(a.out) + (int64_t)t * a.ld_out;
+    for (int d = threadIdx.x; d < a.D; d += blockDim.x) {
+      float acc = 0.f;
+      for (int k = 0; k < a.nslots; ++k) {
+        float x = reinterpret_cast<const float *>(rows[k])[d];
+        acc = k == 0 ? __fmul_rn(ws[k], x) : __fmaf_rn(ws[k], x, acc);
+      }
+      o[d] = acc;
+    }
+  }
+}
+
+// ---- router ------------------------------------------------------------------------------------------
+// Specification (no reference counterpart): p = softmax(logits[t,:]) in f32 (subtract the row max,
+// expf, sum sequentially in expert order, divide); the k experts with the largest p, ties to the
+// lower expert id, in descending order; weights renormalised by their sequential sum when renorm.
+constexpr int kMaxTopk = 16;
+__global__ void route_topk_kernel(const float *logits, int T, int E, int k, int renorm, int32_t *ids, float *w) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const float *l = logits + (int64_t)t * E;
+  float mx = l[0];
+  for (int e = 1; e < E; ++e) mx = fmaxf(mx, l[e]);
+  float sum = 0.f;
+  for (int e = 0; e < E; ++e) sum = __fadd_rn(sum, expf(__fadd_rn(l[e], -mx)));
+  int chosen[kMaxTopk]; float pw[kMaxTopk];
+  float tot = 0.f;
+  for (int j = 0; j < k; ++j) {
+    int best = -1; float bp = 0.f;
+    for (int e = 0; e < E; ++e) {
+      bool taken = false;
+      for (int q = 0; q < j; ++q) taken |= chosen[q] == e;
+      if (taken) continue;
+      float p = __fdiv_rn(expf(__fadd_rn(l[e], -mx)), sum);
+      if (best < 0 || p > bp) { best = e; bp = p; }
+    }
+    chosen[j] = best; pw[j] = bp; tot = __fadd_rn(tot, bp);
+  }
+  for (int j = 0; j < k; ++j) {
+    ids[(int64_t)t * k + j] = chosen[j];
+    if (w) w[(int64_t)t * k + j] = renorm ? __fdiv_rn(pw[j], tot) : pw[j];
+  }
+}
+
+// Stable rank of every (token,k) slot inside its expert: one CTA per expert walks all slots in order.
+__global__ void __launch_bounds__(1024) expert_rank_kernel(const int32_t *ids, int nslots, int32_t *rank, int32_t *counts) {
+  __shared__ int warp_sums[32];
+  __shared__ int running;
+  const int e = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (threadIdx.x == 0) running = 0;
+  __syncthreads();
+  for (int base = 0; base < nslots; base += blockDim.x) {
+    const int s = base + threadIdx.x;
+    const bool mine = s < nslots && ids[s] == e;
+    const unsigned bal = __ballot_sync(0xffffffffu, mine);
+    if (lane == 0) warp_sums[warp] = __popc(bal);
+    __syncthreads();
+    int before = running;
+    for (int i = 0; i < warp; ++i) before += warp_sums[i];
+    if (mine) rank[s] = before + __popc(bal & ((1u << lane) - 1u));
+    __syncthreads();
+    if (threadIdx.x == 0) { int tot = 0; for (int i = 0; i < nwarps; ++i) tot += warp_sums[i]; running += tot; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) counts[e] = running;
+}
+
+// Device-side expert offsets.  counts[0..E) are the routed experts' rows; shared experts (if any) get T
+// rows each.  Writes row_off[E+S+1].
+__global__ void expert_offsets_kernel(const int32_t *counts, int E, int S, int T, int32_t *row_off) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) { row_off[e] = acc; acc += counts[e]; }
+    for (int s = 0; s < S; ++s) { row_off[E + s] = acc; acc += T; }
+    row_off[E + S] = acc;
+  }
+}
+
+// slot -> row (expert-sorted order) and row -> source token; shared-expert rows follow the routed ones.
+// slot_rows is [T][k+S]; slot_w is [T][k+S] (shared slots get weight 1).
+__global__ void build_maps_kernel(const int32_t *ids, const int32_t *rank, const float *w, const int32_t *row_off,
+                                  int T, int k, int E, int S, int32_t *slot_rows, float *slot_w, int32_t *row_token) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int ns = k + S;
+  if (i >= T * ns) return;
+  const int t = i / ns, j = i - t * ns;
+  int row; float wt;
+  if (j < k) { const int s = t * k + j; row = row_off[ids[s]] + rank[s]; wt = w[s]; }
+  else { row = row_off[E + (j - k)] + t; wt = 1.0f; }
+  slot_rows[i] = row; slot_w[i] = wt; row_token[row] = t;
+}
+
+}  // namespace b200

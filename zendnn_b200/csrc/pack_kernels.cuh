@@ -1,0 +1,107 @@
+// Weight prepack: the B200 counterpart of the reference's weight reorder
+// (reorder/prepack/lowoha_prepack.cpp:173-252, matmul/backends/aocl/aocl_kernel.cpp:310-494) and
+// of its zero-point compensation pass (matmul/lru_cache/lowoha_cache.hpp:65-133).
+//
+// Packed form, all in one caller- or cache-owned buffer:
+//   [0,256)                 PackHeader
+//   [256, 256+4*Np)         int32 colsum[Np]: sum over K of each packed weight row
+//   [256+4*Np, ...)         int8  Wt[Np][Kp]: the weight transposed, K contiguous ("K-major"),
+//                           K zero-padded to Kp = roundup(K,128), rows zero-padded to Np = roundup(N,128)
+// Kp a multiple of 128 makes every row a whole number of 128-byte TMA swizzle spans; the tcgen05
+// kernel loads [rows x 128 B] boxes of Wt with SWIZZLE_128B and the streaming kernel reads the
+// same rows with 16-byte loads.
+//
+// Gated form (first GEMM of the fused MoE, N = 2*I with caller columns [gate(0:I) | up(I:2I)]):
+// packed row order is [g(0:32) u(0:32) g(32:64) u(32:64) ...] so that one accumulator tile holds
+// the (gate, up) pair of every output column it produces.  The reference interleaves for the same
+// reason (matmul/group_matmul/custom_kernel/pack.hpp:217-258).  For swiglu_oai_mul the caller
+// layout is already interleaved by element ([g0,u0,g1,u1,...]); it is mapped to the same packed
+// order (gated == 2).
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr uint32_t kPackMagic = 0x38573242u;  // "B2W8"
+constexpr int kPackHeaderBytes = 256;
+constexpr int kGateGranule = 32;
+
+struct PackHeader {
+  uint32_t magic, version;
+  int64_t K, N, Kp, Np;
+  int32_t gated;  // 0 plain, 1 split halves [gate|up], 2 element-interleaved pairs
+  int32_t I;
+};
+
+__host__ __device__ inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+inline size_t pack_bytes(int64_t K, int64_t N) {
+  int64_t Kp = round_up(K, 128), Np = round_up(N, 128);
+  return (size_t)kPackHeaderBytes + (size_t)Np * 4 + (size_t)Np * Kp;
+}
+
+// caller column of packed row pn
+__host__ __device__ __forceinline__ int64_t packed_to_logical(int64_t pn, int gated, int64_t I) {
+  if (!gated) return pn;
+  int64_t blk = pn / (2 * kGateGranule), r = pn % (2 * kGateGranule);
+  int64_t j = blk * kGateGranule + (r % kGateGranule);   // output column
+  bool up = r >= kGateGranule;
+  if (gated == 1) return up ? I + j : j;
+  return 2 * j + (up ? 1 : 0);
+}
+
+// grid: (Kp/64, Np/32); block 256.  Each CTA moves a [64 k][32 n] tile through shared memory.
+__global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t *W, int64_t ldb, int transB, int64_t K, int64_t N,
+                                                          int64_t Kp, int gated, int64_t I, int8_t *Wt) {
+  __shared__ int8_t tile[32][64 + 4];
+  const int64_t k0 = (int64_t)blockIdx.x * 64, pn0 = (int64_t)blockIdx.y * 32;
+  // 32 consecutive packed rows map to 32 consecutive caller columns (stride 1, or 2 when gated == 2)
+  const int64_t n0 = packed_to_logical(pn0, gated, I);
+  const int64_t nstep = gated == 2 ? 2 : 1;
+  const int tid = threadIdx.x;
+  if (!transB) {
+    // W[k][n]: read 32 n per k (coalesced along n)
+    for (int i = tid; i < 64 * 32; i += 256) {
+      int kk = i >> 5, nn = i & 31;
+      int64_t k = k0 + kk, n = n0 + nn * nstep;
+      tile[nn][kk] = (k < K && pn0 + nn < N) ? W[k * ldb + n] : (int8_t)0;
+    }
+  } else {
+    // W[n][k]: read 64 k per n (coalesced along k)
+    for (int i = tid; i < 64 * 32; i += 256) {
+      int nn = i >> 6, kk = i & 63;
+      int64_t k = k0 + kk, n = n0 + nn * nstep;
+      tile[nn][kk] = (k < K && pn0 + nn < N) ? W[n * ldb + k] : (int8_t)0;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < 32 * 16; i += 256) {
+    int nn = i >> 4, k4 = i & 15;
+    const int8_t *t = &tile[nn][k4 * 4];
+    uint32_t v = (uint32_t)(uint8_t)t[0] | ((uint32_t)(uint8_t)t[1] << 8) | ((uint32_t)(uint8_t)t[2] << 16) |
+                 ((uint32_t)(uint8_t)t[3] << 24);
+    *reinterpret_cast<uint32_t *>(Wt + (pn0 + nn) * Kp + k0 + k4 * 4) = v;
+  }
+}
+
+// one warp per packed row
+__global__ void __launch_bounds__(256) pack_colsum_kernel(const int8_t *Wt, int64_t Np, int64_t Kp, int32_t *colsum) {
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= Np) return;
+  const int lane = threadIdx.x & 31;
+  const uint4 *p = reinterpret_cast<const uint4 *>(Wt + row * Kp);
+  int s = 0;
+  for (int64_t i = lane; i < Kp / 16; i += 32) {
+    uint4 v = p[i];
+    s = __dp4a((int)v.x, 0x01010101, s); s = __dp4a((int)v.y, 0x01010101, s);
+    s = __dp4a((int)v.z, 0x01010101, s); s = __dp4a((int)v.w, 0x01010101, s);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) colsum[row] = s;
+}
+
+__global__ void pack_header_kernel(PackHeader *h, int64_t K, int64_t N, int64_t Kp, int64_t Np, int gated, int64_t I) {
+  h->magic = kPackMagic; h->version = 1; h->K = K; h->N = N; h->Kp = Kp; h->Np = Np; h->gated = gated; h->I = (int32_t)I;
+}
+
+}  // namespace b200

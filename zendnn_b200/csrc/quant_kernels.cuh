@@ -1,0 +1,208 @@
+// Memory-bound quantisation kernels behind reorder_direct / group_dynamic_quant.
+//
+//  - per-token symmetric dynamic quantisation (one pass over the row: the row is held in
+//    registers between the abs-max reduction and the quantise step);
+//    reference: reorder/reorder_data_type/scalar_impl/dynamic_per_token_ref_kernel.cpp:31-36,70-124
+//    and the AVX-512 form dynamic_quant_impl/per_token_avx512_f32_fma_kernel.cpp:207-300.
+//  - per-channel / per-tensor dynamic scales: reorder/lowoha_reorder_utils.cpp:708-766,908-935.
+//  - static quantise / dequantise: reorder/lowoha_reorder_utils.hpp:148-153,
+//    reorder_data_type/scalar_impl/scalar_ref_kernels.cpp:28-56.
+//
+// Arithmetic contract: abs-max over finite values, clamp to 1e-10, scale = absmax / 127 (IEEE
+// division), clamp to 1e-10, q = rne(v / scale) with IEEE division; non-finite inputs give 0.
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ float scale_from_absmax(float absmax) {
+  if (absmax < 1e-10f) absmax = 1e-10f;
+  float s = __fdiv_rn(absmax, 127.0f);
+  if (s < 1e-10f) s = 1e-10f;
+  return s;
+}
+__device__ __forceinline__ int8_t quant_sym(float v, float scale) {
+  if (!finite_f32(v)) return 0;
+  return (int8_t)__float2int_rn(__fdiv_rn(v, scale));
+}
+
+// Where the rows of one per-token quantisation come from and go to.  Rows can be a plain
+// strided matrix, a gather of rows of a matrix (MoE dispatch), or the concatenation of several
+// matrices (group_dynamic_quant / the per-expert src[] of group_matmul_direct).
+struct RowQuantArgs {
+  const void *src; int64_t src_ld;      // plain / gather source
+  const int32_t *gather;                // optional: source row of output row r (entries < 0: row skipped)
+  int32_t gather_div;                   // source row = gather_src[r] / gather_div (slot -> token)
+  int8_t *dst; int64_t dst_ld;          // may be null (scales only)
+  void *scale; int32_t scale_dt;        // f32 or bf16, one per row
+  const uint32_t *absmax_bits;          // optional: per-row abs-max already known (float bits)
+  int32_t K;
+  // grouped form (used when n_groups > 0): row r belongs to the group with row_off[g] <= r < row_off[g+1]
+  int32_t n_groups;
+  const void *const *g_src; const int64_t *g_src_ld;
+  void *const *g_dst; const int64_t *g_dst_ld;
+  void *const *g_scale;
+  const int32_t *row_off;
+};
+
+constexpr int kQuantThreads = 256;
+constexpr int kQuantRegVec = 8;   // 16-byte vectors cached per thread
+
+template <typename T> struct VecTraits;
+template <> struct VecTraits<uint16_t> { static constexpr int kPer16B = 8; };
+template <> struct VecTraits<float> { static constexpr int kPer16B = 4; };
+
+template <typename T> __device__ __forceinline__ float elem_to_f32(T v);
+template <> __device__ __forceinline__ float elem_to_f32<uint16_t>(uint16_t v) { return bf16_bits_to_f32(v); }
+template <> __device__ __forceinline__ float elem_to_f32<float>(float v) { return v; }
+
+__device__ __forceinline__ float block_max(float v, float *sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = sh[0];
+  for (int i = 1; i < (int)(blockDim.x >> 5); ++i) r = fmaxf(r, sh[i]);
+  __syncthreads();
+  return r;
+}
+
+// One CTA per row.  T = uint16_t (bf16 bits) or float.
+template <typename T>
+__global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuantArgs a) {
+  __shared__ float sh[kQuantThreads / 32];
+  constexpr int E = VecTraits<T>::kPer16B;
+  const int r = blockIdx.x;
+  const T *src; int8_t *dst; void *scale_out; int64_t scale_idx;
+  if (a.n_groups > 0) {
+    int g = 0;
+    while (g + 1 < a.n_groups && r >= a.row_off[g + 1]) ++g;
+    const int lr = r - a.row_off[g];
+    src = reinterpret_cast<const T *>(a.g_src[g]) + (int64_t)lr * a.g_src_ld[g];
+    dst = a.g_dst[g] ? reinterpret_cast<int8_t *>(a.g_dst[g]) + (int64_t)lr * a.g_dst_ld[g] : nullptr;
+    scale_out = a.g_scale[g]; scale_idx = lr;
+  } else {
+    int64_t sr = r;
+    if (a.gather) { int32_t s = a.gather[r]; if (s < 0) return; sr = s / a.gather_div; }
+    src = reinterpret_cast<const T *>(a.src) + sr * a.src_ld;
+    dst = a.dst ? a.dst + (int64_t)r * a.dst_ld : nullptr;
+    scale_out = a.scale; scale_idx = r;
+  }
+  const int K = a.K;
+  const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (K % E == 0) &&
+                   (!dst || (reinterpret_cast<uintptr_t>(dst) % E) == 0);
+  const int nvec = vec ? K / E : 0;
+  uint4 cache[kQuantRegVec];
+  float amax = 0.f;
+  if (vec) {
+#pragma unroll
+    for (int j = 0; j < kQuantRegVec; ++j) {
+      int v = threadIdx.x + j * kQuantThreads;
+      if (v < nvec) {
+        cache[j] = reinterpret_cast<const uint4 *>(src)[v];
+        const T *e = reinterpret_cast<const T *>(&cache[j]);
+#pragma unroll
+        for (int i = 0; i < E; ++i) { float f = elem_to_f32<T>(e[i]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f)); }
+      }
+    }
+    for (int v = threadIdx.x + kQuantRegVec * kQuantThreads; v < nvec; v += kQuantThreads) {
+      uint4 q = reinterpret_cast<const uint4 *>(src)[v];
+      const T *e = reinterpret_cast<const T *>(&q);
+#pragma unroll
+      for (int i = 0; i < E; ++i) { float f = elem_to_f32<T>(e[i]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f)); }
+    }
+  } else {
+    for (int k = threadIdx.x; k < K; k += kQuantThreads) {
+      float f = elem_to_f32<T>(src[k]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f));
+    }
+  }
+  float scale;
+  if (a.absmax_bits) scale = scale_from_absmax(__uint_as_float(a.absmax_bits[r]));
+  else scale = scale_from_absmax(block_max(amax, sh));
+  if (threadIdx.x == 0 && scale_out) {
+    if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(scale_out)[scale_idx] = f32_to_bf16_bits(scale);
+    else reinterpret_cast<float *>(scale_out)[scale_idx] = scale;
+  }
+  if (!dst) return;
+  if (vec) {
+    auto emit = [&](const uint4 &q, int v) {
+      const T *e = reinterpret_cast<const T *>(&q);
+      int8_t o[E];
+#pragma unroll
+      for (int i = 0; i < E; ++i) o[i] = quant_sym(elem_to_f32<T>(e[i]), scale);
+      if (E == 8) reinterpret_cast<uint2 *>(dst)[v] = *reinterpret_cast<uint2 *>(o);
+      else reinterpret_cast<uint32_t *>(dst)[v] = *reinterpret_cast<uint32_t *>(o);
+    };
+#pragma unroll
+    for (int j = 0; j < kQuantRegVec; ++j) {
+      int v = threadIdx.x + j * kQuantThreads;
+      if (v < nvec) emit(cache[j], v);
+    }
+    for (int v = threadIdx.x + kQuantRegVec * kQuantThreads; v < nvec; v += kQuantThreads)
+      emit(reinterpret_cast<const uint4 *>(src)[v], v);
+  } else {
+    for (int k = threadIdx.x; k < K; k += kQuantThreads) dst[k] = quant_sym(elem_to_f32<T>(src[k]), scale);
+  }
+}
+
+// ---- per-channel / per-tensor dynamic scales over a [M,N] matrix -----------------------------
+// pass 1: abs-max per column (or one for the tensor) with atomicMax on the float bit pattern
+// (non-negative floats order like unsigned integers); out must be zeroed first.
+template <typename T>
+__global__ void absmax_cols_kernel(const T *src, int64_t M, int64_t N, int64_t ld, int per_channel, uint32_t *out) {
+  const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t rows_per = (M + gridDim.y - 1) / gridDim.y;
+  const int64_t m0 = (int64_t)blockIdx.y * rows_per, m1 = min(M, m0 + rows_per);
+  float amax = 0.f;
+  if (n < N)
+    for (int64_t m = m0; m < m1; ++m) {
+      float f = elem_to_f32<T>(src[m * ld + n]);
+      if (finite_f32(f)) amax = fmaxf(amax, fabsf(f));
+    }
+  if (per_channel) {
+    if (n < N) atomicMax(out + n, __float_as_uint(amax));
+  } else {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(out, __float_as_uint(amax));
+  }
+}
+__global__ void scales_from_absmax_kernel(const uint32_t *amax, int64_t n, float *scale) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) scale[i] = scale_from_absmax(__uint_as_float(amax[i]));
+}
+
+// ---- static quantise / dequantise, element-wise over [M,N] --------------------------------------
+template <typename T>
+__global__ void quant_static_kernel(const T *src, int64_t M, int64_t N, int64_t ld, const float *scale, int64_t n_scale,
+                                    const int32_t *zp, int64_t n_zp, void *dst, int32_t dst_dt, int64_t dst_ld) {
+  const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const float s = scale[n_scale > 1 ? n : 0];
+  const int32_t z = zp ? zp[n_zp > 1 ? n : 0] : 0;
+  const int lo = dst_dt == DT_U8 ? 0 : -128, hi = dst_dt == DT_U8 ? 255 : 127;
+  for (int64_t m = blockIdx.y; m < M; m += gridDim.y) {
+    float v = elem_to_f32<T>(src[m * ld + n]);
+    int q = __float2int_rn(__fdiv_rn(v, s)) + z;
+    q = max(lo, min(hi, q));
+    if (dst_dt == DT_U8) reinterpret_cast<uint8_t *>(dst)[m * dst_ld + n] = (uint8_t)q;
+    else reinterpret_cast<int8_t *>(dst)[m * dst_ld + n] = (int8_t)q;
+  }
+}
+__global__ void dequant_static_kernel(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t ld,
+                                      const float *scale, int64_t n_scale, const int32_t *zp, int64_t n_zp,
+                                      void *dst, int32_t dst_dt, int64_t dst_ld) {
+  const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const float s = scale[n_scale > 1 ? n : 0];
+  const int32_t z = zp ? zp[n_zp > 1 ? n : 0] : 0;
+  for (int64_t m = blockIdx.y; m < M; m += gridDim.y) {
+    int q = src_dt == DT_U8 ? (int)reinterpret_cast<const uint8_t *>(src)[m * ld + n]
+                            : (int)reinterpret_cast<const int8_t *>(src)[m * ld + n];
+    float x = __fmul_rn((float)(q - z), s);
+    if (dst_dt == DT_BF16) reinterpret_cast<uint16_t *>(dst)[m * dst_ld + n] = f32_to_bf16_bits(x);
+    else reinterpret_cast<float *>(dst)[m * dst_ld + n] = x;
+  }
+}
+
+}  // namespace b200

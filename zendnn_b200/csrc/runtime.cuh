@@ -1,0 +1,171 @@
+// Host-side runtime of libb200dnn: error text, pointer classification, device workspace,
+// the packed-weight cache (the counterpart of the reference's weight-reorder LRU keyed by the
+// weight address, matmul/backends/aocl/aocl_kernel.cpp:237-307 and matmul/lru_cache/zendnnl_key.hpp:28-75)
+// and the TMA descriptor encoder.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "../../include/b200dnn.h"
+#include "pack_kernels.cuh"
+
+namespace b200 {
+
+inline std::string &err_text() { static thread_local std::string s; return s; }
+inline int32_t fail(int32_t code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap; va_start(ap, fmt); vsnprintf(buf, sizeof buf, fmt, ap); va_end(ap);
+  err_text() = buf;
+  if (const char *e = getenv("ZENDNNL_API_LOG_LEVEL")) if (atoi(e) > 0) fprintf(stderr, "[b200dnn] %s\n", buf);
+  return code;
+}
+#define B2_CUDA(expr)                                                                              \
+  do { cudaError_t e__ = (expr);                                                                   \
+    if (e__ != cudaSuccess) return fail(B200DNN_FAILURE, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
+  } while (0)
+#define B2_CHECK(cond, code, ...) do { if (!(cond)) return fail(code, __VA_ARGS__); } while (0)
+#define B2_TRY(expr) do { int32_t rc__ = (expr); if (rc__ != B200DNN_SUCCESS) return rc__; } while (0)
+
+inline std::atomic<int64_t> &launch_counter() { static std::atomic<int64_t> c{0}; return c; }
+#define B2_LAUNCHED() (++b200::launch_counter())
+
+inline int device_count() {
+  static int n = [] { int c = 0; if (cudaGetDeviceCount(&c) != cudaSuccess) { cudaGetLastError(); c = 0; } return c; }();
+  return n;
+}
+
+inline bool is_device_ptr(const void *p) {
+  if (!p) return false;
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+// ---- workspace: bump allocator over device blocks, rewound at the start of every API call -------
+struct Workspace {
+  struct Block { uint8_t *p; size_t cap, used; };
+  std::vector<Block> blocks;
+  void rewind() { for (auto &b : blocks) b.used = 0; }
+  void *alloc(size_t bytes) {
+    bytes = (bytes + 255) & ~size_t(255);
+    if (bytes == 0) bytes = 256;
+    for (auto &b : blocks)
+      if (b.cap - b.used >= bytes) { void *r = b.p + b.used; b.used += bytes; return r; }
+    size_t cap = bytes > (size_t(64) << 20) ? bytes : (size_t(64) << 20);
+    void *p = nullptr;
+    if (cudaMalloc(&p, cap) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    blocks.push_back({(uint8_t *)p, cap, bytes});
+    return p;
+  }
+  void release() { for (auto &b : blocks) cudaFree(b.p); blocks.clear(); }
+};
+
+struct PackedWeight {
+  const int32_t *colsum = nullptr;
+  const int8_t *wt = nullptr;
+  int64_t K = 0, N = 0, Kp = 0, Np = 0;
+  int gated = 0; int64_t I = 0;
+  void *owned = nullptr;   // cache-owned device buffer
+};
+
+struct Runtime {
+  std::mutex mu;
+  Workspace ws;
+  uint32_t *counters = nullptr; size_t n_counters = 0;   // split-K tile counters, kept zero between launches
+  int32_t *status = nullptr;                              // device status word of the tcgen05 kernel
+  int32_t *status_host = nullptr;                         // pinned mirror
+  std::map<std::tuple<const void *, int64_t, int64_t, int64_t, int, int>, PackedWeight> wcache;
+  std::map<const void *, PackedWeight> packed_registry;   // buffers written by b200dnn_prepack (device address)
+  std::map<const void *, PackedWeight> host_packed;       // host-resident prepacked buffers uploaded once
+  PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  int sm_count = 0;
+
+  int32_t init() {
+    if (counters) return B200DNN_SUCCESS;
+    B2_CHECK(device_count() > 0, B200DNN_FAILURE, "no CUDA device: libb200dnn has no CPU fallback");
+    cudaDeviceProp prop; int dev = 0;
+    B2_CUDA(cudaGetDevice(&dev));
+    B2_CUDA(cudaGetDeviceProperties(&prop, dev));
+    B2_CHECK(prop.major == 10, B200DNN_FAILURE, "device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
+    sm_count = prop.multiProcessorCount;
+    n_counters = 1 << 16;
+    B2_CUDA(cudaMalloc(&counters, n_counters * sizeof(uint32_t)));
+    B2_CUDA(cudaMemset(counters, 0, n_counters * sizeof(uint32_t)));
+    B2_CUDA(cudaMalloc(&status, 256));
+    B2_CUDA(cudaMemset(status, 0, 256));
+    B2_CUDA(cudaMallocHost(&status_host, 256));
+    void *fn = nullptr; cudaDriverEntryPointQueryResult qres;
+    B2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    B2_CHECK(fn && qres == cudaDriverEntryPointSuccess, B200DNN_FAILURE, "cuTensorMapEncodeTiled not available from the driver");
+    encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+    return B200DNN_SUCCESS;
+  }
+};
+inline Runtime &rt() { static Runtime r; return r; }
+
+// 2-D uint8 tensor map [rows][row_bytes used of pitch] with a [box_rows x 128 B] box, SWIZZLE_128B.
+inline int32_t make_map_2d(CUtensorMap *m, const void *base, uint64_t inner_bytes, uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows) {
+  B2_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0 && pitch_bytes % 16 == 0, B200DNN_FAILURE,
+           "TMA operand must be 16-byte aligned with a 16-byte multiple pitch");
+  cuuint64_t dims[2] = {inner_bytes, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = rt().encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B2_CHECK(r == CUDA_SUCCESS, B200DNN_FAILURE, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return B200DNN_SUCCESS;
+}
+
+// One host-or-device buffer made visible on the device for the duration of a call.
+struct Staged {
+  void *dev = nullptr; void *host = nullptr; size_t bytes = 0; bool copy_back = false;
+};
+inline int32_t stage_in(const void *p, size_t bytes, cudaStream_t st, const void **out) {
+  if (!p || bytes == 0) { *out = p; return B200DNN_SUCCESS; }
+  if (is_device_ptr(p)) { *out = p; return B200DNN_SUCCESS; }
+  void *d = rt().ws.alloc(bytes);
+  B2_CHECK(d, B200DNN_FAILURE, "workspace allocation of %zu bytes failed", bytes);
+  B2_CUDA(cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, st));
+  *out = d;
+  return B200DNN_SUCCESS;
+}
+// Output buffer: device pointer is used as is; a host pointer gets a workspace twin that finish() copies back.
+// preload: the kernel updates the buffer (in-place ops) so its current contents are needed too.
+inline int32_t stage_out(void *p, size_t bytes, cudaStream_t st, Staged *s, bool preload = false) {
+  s->host = nullptr; s->dev = p; s->bytes = bytes; s->copy_back = false;
+  if (!p || bytes == 0 || is_device_ptr(p)) return B200DNN_SUCCESS;
+  void *d = rt().ws.alloc(bytes);
+  B2_CHECK(d, B200DNN_FAILURE, "workspace allocation of %zu bytes failed", bytes);
+  if (preload) B2_CUDA(cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, st));
+  s->host = p; s->dev = d; s->copy_back = true;
+  return B200DNN_SUCCESS;
+}
+inline int32_t finish_out(std::initializer_list<Staged *> outs, cudaStream_t st) {
+  bool any = false;
+  for (Staged *s : outs)
+    if (s->copy_back) { B2_CUDA(cudaMemcpyAsync(s->host, s->dev, s->bytes, cudaMemcpyDeviceToHost, st)); any = true; }
+  if (any) B2_CUDA(cudaStreamSynchronize(st));
+  return B200DNN_SUCCESS;
+}
+
+inline size_t dt_size(int32_t dt) {
+  switch (dt) { case B200DNN_F32: case B200DNN_S32: return 4; case B200DNN_BF16: return 2; case B200DNN_S8: case B200DNN_U8: return 1; default: return 0; }
+}
+inline size_t span_bytes(int64_t rows, int64_t cols, int64_t ld, int32_t dt) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return (size_t)((rows - 1) * ld + cols) * dt_size(dt);
+}
+
+}  // namespace b200

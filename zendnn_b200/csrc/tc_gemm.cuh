@@ -1,0 +1,343 @@
+// tcgen05 W8A8 GEMM for sm_100a: the prefill-sized and grouped (MoE) form of the INT8 GEMM that
+// the reference delegates to its backend (matmul/backends/aocl/aocl_kernel.cpp:1190-1301) and, for
+// group_matmul_direct, to its tile micro-kernel (matmul/group_matmul/custom_kernel/ukernel/
+// int8_microkernel.hpp:39-56) under a CPU scheduler (matmul/group_matmul/group_matmul_dispatch.cpp).
+//
+// One persistent CTA per SM, 192 threads, three roles:
+//   warp 0     TMA producer: per K block of 128 bytes, one [128 x 128 B] box of A and one
+//              [BN x 128 B] box of the packed weight into a ring of shared-memory stages
+//              (SWIZZLE_128B, no multicast), completion on an mbarrier.
+//   warp 1     MMA issuer: one lane issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=BN, K=32),
+//              four per stage, accumulating s32 in tensor memory; tcgen05.commit releases the
+//              stage and, after the last K block, publishes the accumulator.
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per thread),
+//              dequantise / bias / post-ops (or gated activation) and store.  Two accumulator
+//              buffers (2 x BN <= 512 TMEM columns) let the epilogue of tile i overlap the MMAs
+//              of tile i+1.
+// Tiles are walked n-tile-major so that CTAs running at the same time share weight tiles through L2.
+// Grouped form: A is one [rows x K] matrix holding every expert's rows back to back; row offsets
+// and the cumulative tile counts live in device memory, so no host round trip is needed after routing.
+// Every wait is bounded: on expiry the kernel records a code in *status and leaves.
+#pragma once
+#include <cuda.h>
+#include "common.cuh"
+#include "pack_kernels.cuh"
+
+namespace b200 {
+
+constexpr int kTcBM = 128;
+constexpr int kTcBK = 128;               // bytes of K per stage row (one 128-byte swizzle span)
+constexpr int kTcThreads = 192;
+constexpr int kTcSmemBudget = 200 * 1024; // stage ring
+constexpr long long kTcWaitCycles = 2000000000LL;  // ~1 s
+
+struct TcGroupDesc {   // per expert, device memory (grouped form with caller-owned outputs)
+  const void *wei_scale;
+  const int32_t *colsum;
+  const void *bias;
+  void *dst;
+  int64_t ldc;
+};
+
+struct TcGemmArgs {
+  int n_groups;               // 1: plain GEMM
+  int M_total;                // rows of A
+  int N;                      // packed columns to produce (N, or 2*I in gated form)
+  int k_blocks;               // Kp / 128
+  int BN, stages;
+  int n_tiles;                // ceil(N / BN)
+  int m_tiles_plain;          // plain form: ceil(M / 128)
+  const int32_t *row_off;     // grouped: [n_groups+1] first row of each group (device)
+  const int32_t *tile_prefix; // grouped: [n_groups+1] cumulative 128-row tiles (device)
+  const CUtensorMap *maps_b;  // grouped: one map per group (device memory); plain: null
+  const TcGroupDesc *groups;  // grouped, optional: per-group epilogue pointers (local row index)
+  int a_unsigned;
+  int gated;                  // packed gate/up interleave: 0, 1 or 2 (see pack_kernels.cuh)
+  int32_t *status;            // device word: 0 ok
+};
+
+// ---------------------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// bounded wait; false on expiry
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > kTcWaitCycles) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
+               ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, SWIZZLE_128B shared-memory operand descriptor: 8-row groups 1024 B apart
+// (stride byte offset), leading byte offset unused for swizzled K-major, descriptor version 1.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// instruction descriptor, kind::i8: D = s32, A = u8|s8, B = s8, both K-major, M = 128, N = BN
+__host__ __device__ inline uint32_t make_idesc_i8(int a_unsigned, int BN) {
+  return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
+}
+
+struct TileCoord { int g, row0, rows, m_local0, nt; };
+
+__device__ __forceinline__ TileCoord tc_tile(const TcGemmArgs &a, int tile, int m_tiles) {
+  TileCoord t;
+  t.nt = tile / m_tiles;
+  const int mt = tile - t.nt * m_tiles;
+  if (!a.tile_prefix) {
+    t.g = 0; t.m_local0 = mt * kTcBM; t.row0 = t.m_local0; t.rows = min(kTcBM, a.M_total - t.row0);
+  } else {
+    int g = 0;
+    while (g + 1 < a.n_groups && mt >= a.tile_prefix[g + 1]) ++g;
+    t.g = g;
+    t.m_local0 = (mt - a.tile_prefix[g]) * kTcBM;
+    t.row0 = a.row_off[g] + t.m_local0;
+    t.rows = min(kTcBM, a.row_off[g + 1] - t.row0);
+  }
+  return t;
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+               const TcGemmArgs a, const EpiParams epi) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * 8 + 4];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile int s_err;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_bytes = kTcBM * kTcBK, b_bytes = (uint32_t)a.BN * kTcBK, stage_bytes = a_bytes + b_bytes;
+  const int S = a.stages;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (8 + s); };
+  auto tfull_bar = [&](int i) { return bar0 + 8u * (16 + i); };
+  auto tempty_bar = [&](int i) { return bar0 + 8u * (18 + i); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), 4); }
+    s_err = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const int m_tiles = a.tile_prefix ? a.tile_prefix[a.n_groups] : a.m_tiles_plain;
+  const int total_tiles = m_tiles * a.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !s_err; tile += gridDim.x) {
+        const TileCoord t = tc_tile(a, tile, m_tiles);
+        const CUtensorMap *mb = a.maps_b ? a.maps_b + t.g : &map_b0;
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { s_err = 1; atomicExch(a.status, 1); break; }
+          const uint32_t sa = smem0 + (uint32_t)stage * stage_bytes;
+          mbar_expect_tx(full_bar(stage), stage_bytes);
+          tma_load_2d(sa, &map_a, kb * kTcBK, t.row0, full_bar(stage));
+          tma_load_2d(sa + a_bytes, mb, kb * kTcBK, t.nt * a.BN, full_bar(stage));
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_i8(a.a_unsigned, a.BN);
+      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !s_err; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { s_err = 2; atomicExch(a.status, 2); break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * a.BN);
+        bool ok = true;
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem0 + (uint32_t)stage * stage_bytes;
+          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + a_bytes);
+#pragma unroll
+          for (int k = 0; k < kTcBK / 32; ++k)
+            tc_mma_i8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+          tc_commit(empty_bar(stage));
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) { s_err = 3; atomicExch(a.status, 3); break; }
+        tc_commit(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may access
+    const int row_in_tile = q * 32 + lane;
+    const int32_t zp = load_zp(epi);
+    int acc = 0; uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const TileCoord t = tc_tile(a, tile, m_tiles);
+      bool ok = mbar_wait(tfull_bar(acc), acc_phase);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok || s_err) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
+      tc_fence_after();
+      // per-tile epilogue operands
+      const int m_local = t.m_local0 + row_in_tile;
+      const int m_global = t.row0 + row_in_tile;
+      const bool row_ok = row_in_tile < t.rows;
+      EpiCtx cx = epi_ctx(epi, row_ok ? m_global : 0);
+      int m_dst = m_global;
+      if (a.groups) {
+        const TcGroupDesc gd = a.groups[t.g];
+        cx.wei_scale = gd.wei_scale; cx.colsum = gd.colsum; cx.bias = gd.bias;
+        if (gd.dst) { cx.dst = gd.dst; cx.ldc = gd.ldc; m_dst = m_local; }   // else: shared dst, global row index
+      }
+      const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * a.BN);
+      const int pc_tile = t.nt * a.BN;
+      if (!a.gated) {
+        for (int c = 0; c < a.BN / 32; ++c) {
+          const int pc0 = pc_tile + c * 32;
+          if (pc0 >= a.N) break;           // warp-uniform
+          uint32_t r[32];
+          tc_ld32(taddr0 + (uint32_t)(c * 32), r);
+          tc_wait_ld();
+          if (!row_ok) continue;
+          if (epi.dst_dt == DT_S32) {
+            int32_t *o = reinterpret_cast<int32_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (pc0 + i < a.N) o[i] = (int32_t)r[i] - (zp ? zp * cx.colsum[pc0 + i] : 0);
+          } else if (epi.dst_dt == DT_BF16) {
+            uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float x0 = 0.f, x1 = 0.f;
+              if (pc0 + i < a.N) x0 = epi_finish(epi, cx, epi_dequant(epi, cx, (int32_t)r[i], zp, pc0 + i, pc0 + i), m_dst, pc0 + i);
+              if (pc0 + i + 1 < a.N) x1 = epi_finish(epi, cx, epi_dequant(epi, cx, (int32_t)r[i + 1], zp, pc0 + i + 1, pc0 + i + 1), m_dst, pc0 + i + 1);
+              pk[i >> 1] = (uint32_t)f32_to_bf16_bits(x0) | ((uint32_t)f32_to_bf16_bits(x1) << 16);
+            }
+            if (pc0 + 32 <= a.N && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                reinterpret_cast<uint4 *>(o)[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (pc0 + i < a.N) o[i] = (uint16_t)(pk[i >> 1] >> ((i & 1) * 16));
+            }
+          } else {
+            float *o = reinterpret_cast<float *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (pc0 + i < a.N) o[i] = epi_finish(epi, cx, epi_dequant(epi, cx, (int32_t)r[i], zp, pc0 + i, pc0 + i), m_dst, pc0 + i);
+          }
+        }
+      } else {
+        // gated: packed columns [g(32) u(32)] -> 32 outputs; dst is [rows, I] bf16
+        float amax = 0.f;
+        for (int c = 0; c < a.BN / 64; ++c) {
+          const int pc0 = pc_tile + c * 64;
+          if (pc0 >= a.N) break;
+          uint32_t rg[32], ru[32];
+          tc_ld32(taddr0 + (uint32_t)(c * 64), rg);
+          tc_ld32(taddr0 + (uint32_t)(c * 64 + 32), ru);
+          tc_wait_ld();
+          if (!row_ok) continue;
+          const int j0 = pc0 / 2;   // first output column of this pair of chunks
+          uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + j0;
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int j = j0 + i;
+            const int ng = a.gated == 1 ? j : 2 * j, nu = a.gated == 1 ? epi.gated_I + j : 2 * j + 1;
+            float gv = epi_dequant(epi, cx, (int32_t)rg[i], 0, ng, pc0 + i);
+            float uv = epi_dequant(epi, cx, (int32_t)ru[i], 0, nu, pc0 + 32 + i);
+            if (cx.bias) { gv = __fadd_rn(gv, load_as_f32(cx.bias, epi.bias_dt, ng)); uv = __fadd_rn(uv, load_as_f32(cx.bias, epi.bias_dt, nu)); }
+            const uint16_t zb = f32_to_bf16_bits(gated_f32(epi.gated_act, gv, uv));
+            const float az = fabsf(bf16_bits_to_f32(zb));
+            if (finite_f32(az)) amax = fmaxf(amax, az);
+            if (i & 1) pk[i >> 1] |= (uint32_t)zb << 16; else pk[i >> 1] = zb;
+          }
+          if ((reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              reinterpret_cast<uint4 *>(o)[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = (uint16_t)(pk[i >> 1] >> ((i & 1) * 16));
+          }
+        }
+        if (row_ok && epi.row_absmax) atomicMax(epi.row_absmax + m_global, __float_as_uint(amax));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (s_err) {
+    // give copies that may still be in flight time to land before shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+}  // namespace b200
