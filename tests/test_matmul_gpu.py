@@ -12,6 +12,7 @@ from helpers import assert_bf16_close, config1, decode_case
 pytestmark = pytest.mark.gpu
 
 STREAM, TC = 1, 2
+KERNELS = [pytest.param(STREAM, id="stream"), pytest.param(TC, id="tc")]
 
 
 @pytest.fixture(scope="module")
@@ -30,7 +31,7 @@ def run(capi, M, N, K, A, W, dst_dt, **kw):
     return out
 
 
-@pytest.mark.parametrize("kernel", [STREAM, TC])
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("shape", [(1, 64, 16), (5, 100, 24), (16, 256, 64), (33, 260, 80), (128, 512, 128),
                                    (130, 384, 200), (257, 1024, 264)])
 def test_s32_bit_exact_small(capi, oracle, kernel, shape):
@@ -54,7 +55,7 @@ def test_s32_bit_exact_small(capi, oracle, kernel, shape):
         assert (got == oracle.gemm_s32(A, W)).all(), (src, shape, "transB")
 
 
-@pytest.mark.parametrize("kernel", [STREAM, TC])
+@pytest.mark.parametrize("kernel", KERNELS)
 def test_golden_reference_cases(capi, oracle, golden, kernel):
     """Outputs of the reference's own INT8 tile kernel (tests/golden): <= 1 bf16 ulp."""
     fused = {0: [], 1: ["relu"], 2: ["gelu_tanh"], 5: ["swish"]}
@@ -72,17 +73,20 @@ def test_golden_reference_cases(capi, oracle, golden, kernel):
                   postops=fused[fo])
         ref = golden[p + "out"]
         if is_bf16:
-            assert_bf16_close(got, ref, 1 if fo in (0, 1) else 2, "golden case %d" % (i - 1))
+            # the reference kernel evaluates tanh / sigmoid with ~5e-5-relative polynomials: its activation
+            # cases are compared with an absolute floor, the linear ones to 1 ulp
+            assert_bf16_close(got, ref, 1 if fo in (0, 1) else 2, "golden case %d" % (i - 1), atol=0.0 if fo in (0, 1) else 1e-4)
         else:
             assert np.allclose(got, ref, rtol=2e-4, atol=1e-4)
 
 
-def test_config1_full_size(capi, oracle):
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_config1_full_size(capi, oracle, kernel):
     """M128 K4096 N4096, u8 zp 128 scale .02, per-channel weight scales, f32 bias, ReLU, bf16 out, seed 0."""
     c = config1(oracle)
     M, K, N = 128, 4096, 4096
     acc = oracle.gemm_s32(c["A"], c["W"])
-    for kernel in (STREAM, TC):
+    if True:
         got = run(capi, M, N, K, c["A"], c["W"], "s32", force_kernel=kernel)
         assert (got == acc).all()
         got = run(capi, M, N, K, c["A"], c["W"], "bf16", force_kernel=kernel, src_scale=c["ss"], wei_scale=c["ws"],
@@ -118,7 +122,7 @@ def test_scales_in_bf16_storage(capi, oracle):
 
 
 @pytest.mark.parametrize("M,K,N", [(64, 512, 256), (300, 1024, 384)])
-def test_dynamic_quant_gelu(capi, oracle, M, K, N):
+def test_dynamic_quant_gelu_tc(capi, oracle, M, K, N):
     """Config 3 family: bf16 activations quantised per token inside the call, bias, GELU(tanh), bf16 out."""
     rng = np.random.default_rng(M)
     x = oracle.f32_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
@@ -136,7 +140,8 @@ def test_dynamic_quant_gelu(capi, oracle, M, K, N):
             assert (scales == sa).all()          # the library writes the scales it used
 
 
-def test_postop_chain_and_strides(capi, oracle):
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_postop_chain_and_strides(capi, oracle, kernel):
     rng = np.random.default_rng(9)
     M, K, N, lda, ldc = 40, 192, 72, 208, 96
     Afull = rng.integers(-128, 128, (M, lda), dtype=np.int8)
@@ -149,7 +154,7 @@ def test_postop_chain_and_strides(capi, oracle):
           dict(type="clip", alpha=-0.5, beta=0.75)]
     ref = oracle.matmul_w8a8(np.ascontiguousarray(A), W, "f32", src_scale=[0.05], wei_scale=sw, postops=po)
     out = np.full((M, ldc), 7.0, dtype=np.float32)
-    for kernel in (STREAM, TC):
+    if True:
         out[:] = 7.0
         d = capi.make_matmul(M, N, K, Afull, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["f32"], lda=lda, ldc=ldc,
                              weights_const=False, src_scale=np.array([0.05], dtype=np.float32), wei_scale=sw, postops=po,
