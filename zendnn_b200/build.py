@@ -50,8 +50,8 @@ def build(force=False, verbose=False):
         cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
                "-ccbin", host_cxx(), "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared",
                "-Xptxas", "-v" if verbose else "-O3",
-               "-I", os.path.join(ROOT, "include"), "-o", LIB_CUDA, os.path.join(CSRC, "b200dnn.cu"),
-               "-lcudart"]
+               "-I", os.path.join(ROOT, "include"), "-o", LIB_CUDA] + \
+              [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cu")] + ["-lcudart"]
         subprocess.check_call(cmd)
     host_src = os.path.join(CSRC, "lowoha_host.cpp")
     if os.path.exists(host_src) and (force or _newer(LIB_HOST, deps)):

@@ -50,7 +50,7 @@ __host__ __device__ __forceinline__ int64_t packed_to_logical(int64_t pn, int ga
 }
 
 // grid: (Kp/64, Np/32); block 256.  Each CTA moves a [64 k][32 n] tile through shared memory.
-__global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t *W, int64_t ldb, int transB, int64_t K, int64_t N,
+static __global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t *W, int64_t ldb, int transB, int64_t K, int64_t N,
                                                           int64_t Kp, int gated, int64_t I, int8_t *Wt) {
   __shared__ int8_t tile[32][64 + 4];
   const int64_t k0 = (int64_t)blockIdx.x * 64, pn0 = (int64_t)blockIdx.y * 32;
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t *W, int64
 }
 
 // one warp per packed row
-__global__ void __launch_bounds__(256) pack_colsum_kernel(const int8_t *Wt, int64_t Np, int64_t Kp, int32_t *colsum) {
+static __global__ void __launch_bounds__(256) pack_colsum_kernel(const int8_t *Wt, int64_t Np, int64_t Kp, int32_t *colsum) {
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= Np) return;
   const int lane = threadIdx.x & 31;
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(256) pack_colsum_kernel(const int8_t *Wt, int6
   if (lane == 0) colsum[row] = s;
 }
 
-__global__ void pack_header_kernel(PackHeader *h, int64_t K, int64_t N, int64_t Kp, int64_t Np, int gated, int64_t I) {
+static __global__ void pack_header_kernel(PackHeader *h, int64_t K, int64_t N, int64_t Kp, int64_t Np, int gated, int64_t I) {
   h->magic = kPackMagic; h->version = 1; h->K = K; h->N = N; h->Kp = Kp; h->Np = Np; h->gated = gated; h->I = (int32_t)I;
 }
 

@@ -4,6 +4,7 @@
 // and the TMA descriptor encoder.
 #pragma once
 #include <cuda.h>
+#include <cudaTypedefs.h>
 #include <cuda_runtime.h>
 #include <atomic>
 #include <cstdarg>
