@@ -102,6 +102,17 @@ B200DNN_API int64_t b200dnn_launch_count(void);
 /* matmul_direct, INT8 path (matmul/lowoha_matmul.cpp:278): C = postops(dequant(A*B) + bias). */
 B200DNN_API int32_t b200dnn_matmul(const b200dnn_matmul_t *desc, void *stream);
 
+/* No counterpart in the reference.  The same W8A8 matmul for callers that cannot allocate device
+ * memory at call time (a server whose own pool already holds all free memory, a latency-bound loop
+ * that cannot risk a blocking cudaMalloc): it never allocates.  The split-K scratch is a fixed
+ * 8 MiB + 16 KiB device array inside the library, held by every GPU that loads it; shapes that need
+ * more are rejected with failure.  Restrictions: every pointer is a device pointer, the weight is a
+ * buffer written by b200dnn_prepack for this K and N (wei_format 'r'), no dynamic_quant.  The first
+ * call on a device resolves the array's address (make that call before any stream capture).  All
+ * calls share the array: calls that overlap on the GPU race, so keep them on one stream or
+ * otherwise serialised. */
+B200DNN_API int32_t b200dnn_matmul_static_scratch(const b200dnn_matmul_t *desc, void *stream);
+
 /* weight_prepack_size (reorder/prepack/lowoha_prepack.cpp:285): bytes of the packed form of a
  * K x N s8 weight (multiple of 64).  gated != 0 selects the gate/up interleaved form used by
  * the fused MoE first GEMM (N = 2*I, I a multiple of 32). */

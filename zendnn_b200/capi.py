@@ -50,7 +50,7 @@ class MoeExpert(C.Structure):
 
 
 EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b200dnn_launch_count",
-           "b200dnn_matmul", "b200dnn_prepack_size", "b200dnn_prepack", "b200dnn_quant_per_token",
+           "b200dnn_matmul", "b200dnn_matmul_static_scratch", "b200dnn_prepack_size", "b200dnn_prepack", "b200dnn_quant_per_token",
            "b200dnn_group_quant_per_token", "b200dnn_quant_dynamic", "b200dnn_quant_static",
            "b200dnn_dequant_static", "b200dnn_gated_act", "b200dnn_moe_weighted_reduce", "b200dnn_fused_moe",
            "b200dnn_moe_route", "b200dnn_moe_layer", "b200dnn_clear_caches"]
@@ -67,6 +67,7 @@ lib.b200dnn_prepack_size.argtypes = [C.c_int64, C.c_int64, C.c_int32]
 lib.b200dnn_launch_count.restype = C.c_int64
 i32, i64, vp = C.c_int32, C.c_int64, C.c_void_p
 lib.b200dnn_matmul.argtypes = [C.POINTER(MatmulDesc), vp]
+lib.b200dnn_matmul_static_scratch.argtypes = [C.POINTER(MatmulDesc), vp]
 lib.b200dnn_prepack.argtypes = [vp, i64, i64, i64, i32, i32, vp, vp]
 lib.b200dnn_quant_per_token.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i32, vp]
 lib.b200dnn_group_quant_per_token.argtypes = [i32, vp, i32, vp, vp, vp, vp, vp, vp, i32, vp]
