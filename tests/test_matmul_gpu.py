@@ -135,7 +135,8 @@ def test_dynamic_quant_gelu_tc(capi, oracle, M, K, N):
         ss = capi.quant(scales if with_buf else None, count=M, dt=capi.DT["f32"])
         got = run(capi, M, N, K, x, qw, "bf16", src_dt=capi.DT["bf16"], dynamic_quant=True, weights_const=False,
                   src_scale=ss, wei_scale=sw, bias=bias, postops=["gelu_tanh"])
-        assert_bf16_close(got, ref, 1, "dynamic quant + gelu")
+        # the libm form 0.5*x*(1+tanh(u)) cancels for very negative u (outputs of order 1e-6): absolute floor there
+        assert_bf16_close(got, ref, 1, "dynamic quant + gelu", atol=1e-5)
         if with_buf:
             assert (scales == sa).all()          # the library writes the scales it used
 

@@ -184,6 +184,19 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
   B2_TRY(make_map_2d(&map_a, A, (uint64_t)K, (uint64_t)M_total, (uint64_t)lda, kTcBM));
   args.M_total = M_total; args.N = N; args.k_blocks = (int)(pw0.Kp / 128);
   args.a_unsigned = a_unsigned ? 1 : 0; args.gated = pw0.gated; args.status = R.status;
+  args.fast_act = FA_GENERIC;
+  if (epi.n_po == 0) args.fast_act = FA_NONE;
+  else if (epi.n_po == 1) {
+    switch (epi.po[0].type) {
+    case PO_RELU: args.fast_act = FA_RELU; break;
+    case PO_GELU_TANH: args.fast_act = FA_GELU_TANH; break;
+    case PO_GELU_ERF: args.fast_act = FA_GELU_ERF; break;
+    case PO_SIGMOID: args.fast_act = FA_SIGMOID; break;
+    case PO_SWISH: args.fast_act = FA_SWISH; break;
+    case PO_TANH: args.fast_act = FA_TANH; break;
+    default: break;
+    }
+  }
   args.BN = pick_bn(m_tiles_hint, N, R.sm_count, pw0.gated);
   B2_CHECK(args.BN % 32 == 0 && args.BN >= 32 && args.BN <= 256 && (!pw0.gated || args.BN % 64 == 0), B200DNN_FAILURE,
            "bad tile width %d", args.BN);

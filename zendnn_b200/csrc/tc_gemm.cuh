@@ -3,17 +3,19 @@
 // group_matmul_direct, to its tile micro-kernel (matmul/group_matmul/custom_kernel/ukernel/
 // int8_microkernel.hpp:39-56) under a CPU scheduler (matmul/group_matmul/group_matmul_dispatch.cpp).
 //
-// One persistent CTA per SM, 192 threads, three roles:
+// One persistent CTA per SM, 320 threads, three roles:
 //   warp 0     TMA producer: per K block of 128 bytes, one [128 x 128 B] box of A and one
 //              [BN x 128 B] box of the packed weight into a ring of shared-memory stages
 //              (SWIZZLE_128B, no multicast), completion on an mbarrier.
 //   warp 1     MMA issuer: one lane issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=BN, K=32),
 //              four per stage, accumulating s32 in tensor memory; tcgen05.commit releases the
 //              stage and, after the last K block, publishes the accumulator.
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per thread),
-//              dequantise / bias / post-ops (or gated activation) and store.  Two accumulator
-//              buffers (2 x BN <= 512 TMEM columns) let the epilogue of tile i overlap the MMAs
-//              of tile i+1.
+//   warps 2-9  epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per thread, two
+//              warps per lane quadrant taking alternate 32-column chunks), dequantise / bias /
+//              post-ops (or gated activation) and store.  Per-column operands (weight scale, bias,
+//              zero-point compensation) are staged once per tile in shared memory as f32/s32.
+//              Two accumulator buffers (2 x BN <= 512 TMEM columns) let the epilogue of tile i
+//              overlap the MMAs of tile i+1.
 // Tiles are walked n-tile-major so that CTAs running at the same time share weight tiles through L2.
 // Grouped form: A is one [rows x K] matrix holding every expert's rows back to back; row offsets
 // and the cumulative tile counts live in device memory, so no host round trip is needed after routing.
@@ -27,7 +29,8 @@ namespace b200 {
 
 constexpr int kTcBM = 128;
 constexpr int kTcBK = 128;               // bytes of K per stage row (one 128-byte swizzle span)
-constexpr int kTcThreads = 192;
+constexpr int kTcEpiWarps = 8;
+constexpr int kTcThreads = 64 + 32 * kTcEpiWarps;   // producer warp + MMA warp + epilogue warps
 constexpr int kTcSmemBudget = 200 * 1024; // stage ring
 constexpr long long kTcWaitCycles = 2000000000LL;  // ~1 s
 
@@ -53,6 +56,7 @@ struct TcGemmArgs {
   const TcGroupDesc *groups;  // grouped, optional: per-group epilogue pointers (local row index)
   int a_unsigned;
   int gated;                  // packed gate/up interleave: 0, 1 or 2 (see pack_kernels.cuh)
+  int fast_act;               // FA_* code: which specialised epilogue loop to run
   int32_t *status;            // device word: 0 ok
 };
 
@@ -138,11 +142,101 @@ __device__ __forceinline__ TileCoord tc_tile(const TcGemmArgs &a, int tile, int 
   return t;
 }
 
+// ---- epilogue arithmetic ---------------------------------------------------------------------------
+// Post-op structure resolved on the host so that the per-element loop carries no dispatch.
+enum : int { FA_GENERIC = -1, FA_NONE = 0, FA_RELU, FA_GELU_TANH, FA_GELU_ERF, FA_SIGMOID, FA_SWISH, FA_TANH };
+
+// sigmoid-family activations through one exp and one reciprocal.  gelu_tanh uses the identity
+// 0.5*x*(1+tanh(u)) = x / (1 + exp(-2u)), which has no cancellation for very negative u.
+__device__ __forceinline__ float fast_sigmoid_mul(float x, float arg) { return __fdividef(x, 1.0f + __expf(-arg)); }
+
+template <int ACT>
+__device__ __forceinline__ float tc_act(const EpiParams &epi, float x, int m, int n) {
+  if (ACT == FA_NONE) return x;
+  if (ACT == FA_RELU) return fmaxf(x, 0.0f);
+  if (ACT == FA_GELU_TANH) {
+    const float c = 0.79788458347320556640625f, f = 0.044715f;
+    const float inner = (c * x) * (1.0f + (f * x) * x);
+    return fast_sigmoid_mul(x, 2.0f * inner);
+  }
+  if (ACT == FA_GELU_ERF) return po_gelu_erf(x);
+  if (ACT == FA_SIGMOID) return fast_sigmoid_mul(1.0f, x);
+  if (ACT == FA_SWISH) return fast_sigmoid_mul(x, x);
+  if (ACT == FA_TANH) return tanhf(x);
+  for (int i = 0; i < epi.n_po; ++i) x = apply_postop(epi.po[i], x, m, n);
+  return x;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  // one instruction; same round-to-nearest-even as the reference's bit trick for every finite value
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+struct TileCols {          // per-tile column operands staged in shared memory
+  float ws[256];
+  float bias[256];
+  int32_t comp[256];
+};
+
+// One 32-column chunk of one output row.
+template <int ACT>
+__device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx &cx, const uint32_t (&r)[32], const TileCols &tc,
+                                             int c0, int pc0, int N, int m_dst, bool has_bias) {
+  if (epi.dst_dt == DT_S32) {
+    int32_t *o = reinterpret_cast<int32_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (pc0 + i < N) o[i] = (int32_t)r[i] - tc.comp[c0 + i];
+    return;
+  }
+  float x[32];
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float4 w4 = *reinterpret_cast<const float4 *>(&tc.ws[c0 + i]);
+    const float4 b4 = *reinterpret_cast<const float4 *>(&tc.bias[c0 + i]);
+    const int4 k4 = *reinterpret_cast<const int4 *>(&tc.comp[c0 + i]);
+    const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+    const int kv[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float v = __fmul_rn(__fmul_rn((float)((int32_t)r[i + j] - kv[j]), cx.s_src), wv[j]);
+      if (has_bias) v = __fadd_rn(v, bv[j]);
+      x[i + j] = tc_act<ACT>(epi, v, m_dst, pc0 + i + j);
+    }
+  }
+  if (epi.dst_dt == DT_BF16) {
+    uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+    if (pc0 + 32 <= N && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        reinterpret_cast<uint4 *>(o)[v] = make_uint4(pack_bf16x2(x[8 * v], x[8 * v + 1]), pack_bf16x2(x[8 * v + 2], x[8 * v + 3]),
+                                                     pack_bf16x2(x[8 * v + 4], x[8 * v + 5]), pack_bf16x2(x[8 * v + 6], x[8 * v + 7]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (pc0 + i < N) o[i] = f32_to_bf16_bits(x[i]);
+    }
+  } else {
+    float *o = reinterpret_cast<float *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+    if (pc0 + 32 <= N && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+      for (int v = 0; v < 8; ++v) reinterpret_cast<float4 *>(o)[v] = make_float4(x[4 * v], x[4 * v + 1], x[4 * v + 2], x[4 * v + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (pc0 + i < N) o[i] = x[i];
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                const TcGemmArgs a, const EpiParams epi) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * 8 + 4];
+  __shared__ __align__(16) TileCols cols;
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int s_err;
 
@@ -158,7 +252,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), kTcEpiWarps); }
     s_err = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -219,18 +313,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int ew = warp - 2;                // 0..7
     const int q = warp & 3;                 // TMEM lane quadrant this warp may access
+    const int half = ew >> 2;               // which alternate chunks this warp takes
+    const int etid = ew * 32 + lane;        // 0..255
     const int row_in_tile = q * 32 + lane;
     const int32_t zp = load_zp(epi);
     int acc = 0; uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const TileCoord t = tc_tile(a, tile, m_tiles);
+      // the decision to go on must be the same in all epilogue warps (they meet at a named barrier):
+      // it depends only on this wait, which either completes for all of them or expires for all
       bool ok = mbar_wait(tfull_bar(acc), acc_phase);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok || s_err) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
+      if (!ok) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
       tc_fence_after();
-      // per-tile epilogue operands
       const int m_local = t.m_local0 + row_in_tile;
       const int m_global = t.row0 + row_in_tile;
       const bool row_ok = row_in_tile < t.rows;
@@ -241,51 +339,45 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         cx.wei_scale = gd.wei_scale; cx.colsum = gd.colsum; cx.bias = gd.bias;
         if (gd.dst) { cx.dst = gd.dst; cx.ldc = gd.ldc; m_dst = m_local; }   // else: shared dst, global row index
       }
-      const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * a.BN);
       const int pc_tile = t.nt * a.BN;
+      // stage this tile's column operands (f32 / s32) once
+      if (etid < a.BN) {
+        const int pc = pc_tile + etid;
+        float w = 1.0f, b = 0.0f; int32_t k = 0;
+        if (pc < a.N) {
+          const int n = (int)packed_to_logical(pc, a.gated, epi.gated_I);
+          if (epi.wei_scale_n) w = load_as_f32(cx.wei_scale, epi.wei_scale_dt, epi.wei_scale_n > 1 ? n : 0);
+          if (cx.bias) b = load_as_f32(cx.bias, epi.bias_dt, n);
+          if (zp) k = zp * cx.colsum[pc];
+        }
+        cols.ws[etid] = w; cols.bias[etid] = b; cols.comp[etid] = k;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kTcEpiWarps) : "memory");
+      const bool has_bias = cx.bias != nullptr;
+      const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * a.BN);
       if (!a.gated) {
-        for (int c = 0; c < a.BN / 32; ++c) {
+        for (int c = half; c < a.BN / 32; c += 2) {
           const int pc0 = pc_tile + c * 32;
           if (pc0 >= a.N) break;           // warp-uniform
           uint32_t r[32];
           tc_ld32(taddr0 + (uint32_t)(c * 32), r);
           tc_wait_ld();
           if (!row_ok) continue;
-          if (epi.dst_dt == DT_S32) {
-            int32_t *o = reinterpret_cast<int32_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (pc0 + i < a.N) o[i] = (int32_t)r[i] - (zp ? zp * cx.colsum[pc0 + i] : 0);
-          } else if (epi.dst_dt == DT_BF16) {
-            uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
-            uint32_t pk[16];
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float x0 = 0.f, x1 = 0.f;
-              if (pc0 + i < a.N) x0 = epi_finish(epi, cx, epi_dequant(epi, cx, (int32_t)r[i], zp, pc0 + i, pc0 + i), m_dst, pc0 + i);
-              if (pc0 + i + 1 < a.N) x1 = epi_finish(epi, cx, epi_dequant(epi, cx, (int32_t)r[i + 1], zp, pc0 + i + 1, pc0 + i + 1), m_dst, pc0 + i + 1);
-              pk[i >> 1] = (uint32_t)f32_to_bf16_bits(x0) | ((uint32_t)f32_to_bf16_bits(x1) << 16);
-            }
-            if (pc0 + 32 <= a.N && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-              for (int v = 0; v < 4; ++v)
-                reinterpret_cast<uint4 *>(o)[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (pc0 + i < a.N) o[i] = (uint16_t)(pk[i >> 1] >> ((i & 1) * 16));
-            }
-          } else {
-            float *o = reinterpret_cast<float *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (pc0 + i < a.N) o[i] = epi_finish(epi, cx, epi_dequant(epi, cx, (int32_t)r[i], zp, pc0 + i, pc0 + i), m_dst, pc0 + i);
+          switch (a.fast_act) {
+          case FA_NONE: tc_epi_chunk<FA_NONE>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_RELU: tc_epi_chunk<FA_RELU>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_GELU_TANH: tc_epi_chunk<FA_GELU_TANH>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_GELU_ERF: tc_epi_chunk<FA_GELU_ERF>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_SIGMOID: tc_epi_chunk<FA_SIGMOID>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_SWISH: tc_epi_chunk<FA_SWISH>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_TANH: tc_epi_chunk<FA_TANH>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          default: tc_epi_chunk<FA_GENERIC>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
           }
         }
       } else {
         // gated: packed columns [g(32) u(32)] -> 32 outputs; dst is [rows, I] bf16
         float amax = 0.f;
-        for (int c = 0; c < a.BN / 64; ++c) {
+        for (int c = half; c < a.BN / 64; c += 2) {
           const int pc0 = pc_tile + c * 64;
           if (pc0 >= a.N) break;
           uint32_t rg[32], ru[32];
@@ -294,16 +386,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_wait_ld();
           if (!row_ok) continue;
           const int j0 = pc0 / 2;   // first output column of this pair of chunks
+          const int cg = c * 64, cu = c * 64 + 32;
           uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + j0;
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int j = j0 + i;
-            const int ng = a.gated == 1 ? j : 2 * j, nu = a.gated == 1 ? epi.gated_I + j : 2 * j + 1;
-            float gv = epi_dequant(epi, cx, (int32_t)rg[i], 0, ng, pc0 + i);
-            float uv = epi_dequant(epi, cx, (int32_t)ru[i], 0, nu, pc0 + 32 + i);
-            if (cx.bias) { gv = __fadd_rn(gv, load_as_f32(cx.bias, epi.bias_dt, ng)); uv = __fadd_rn(uv, load_as_f32(cx.bias, epi.bias_dt, nu)); }
-            const uint16_t zb = f32_to_bf16_bits(gated_f32(epi.gated_act, gv, uv));
+            float gv = __fmul_rn(__fmul_rn((float)(int32_t)rg[i], cx.s_src), cols.ws[cg + i]);
+            float uv = __fmul_rn(__fmul_rn((float)(int32_t)ru[i], cx.s_src), cols.ws[cu + i]);
+            if (has_bias) { gv = __fadd_rn(gv, cols.bias[cg + i]); uv = __fadd_rn(uv, cols.bias[cu + i]); }
+            float z;
+            if (epi.gated_act == ACT_SILU_MUL) z = __fmul_rn(fast_sigmoid_mul(gv, gv), uv);
+            else z = gated_f32(epi.gated_act, gv, uv);
+            const uint16_t zb = f32_to_bf16_bits(z);
             const float az = fabsf(bf16_bits_to_f32(zb));
             if (finite_f32(az)) amax = fmaxf(amax, az);
             if (i & 1) pk[i >> 1] |= (uint32_t)zb << 16; else pk[i >> 1] = zb;
@@ -320,7 +414,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (row_ok && epi.row_absmax) atomicMax(epi.row_absmax + m_global, __float_as_uint(amax));
       }
       tc_fence_before();
-      __syncwarp();
+      // all epilogue warps are done with this accumulator and with the staged column operands
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kTcEpiWarps) : "memory");
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
