@@ -88,7 +88,7 @@ typedef struct b200dnn_matmul_t {
   b200dnn_quant_t wei_scale;
   b200dnn_quant_t src_zp;    /* per-tensor; dt s32 | s8 | u8 */
   b200dnn_postop_t postops[B200DNN_MAX_POSTOPS];
-  int32_t force_kernel;  /* 0 auto, 1 streaming (mma.sync) kernel, 2 tcgen05 kernel; for tests */
+  int32_t force_kernel;  /* for tests: 0 auto, 1 weight-streaming kernels, 2 tcgen05 kernel, 3 tiled streaming kernel only */
   int32_t reserved;
 } b200dnn_matmul_t;
 

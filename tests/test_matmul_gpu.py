@@ -12,7 +12,8 @@ from helpers import assert_bf16_close, config1, decode_case
 pytestmark = pytest.mark.gpu
 
 STREAM, TC = 1, 2
-KERNELS = [pytest.param(STREAM, id="stream"), pytest.param(TC, id="tc")]
+TILED = 3   # the tiled split-K streaming kernel only (STREAM picks the persistent decode kernel when M <= 16)
+KERNELS = [pytest.param(STREAM, id="stream"), pytest.param(TC, id="tc"), pytest.param(TILED, id="tiled")]
 
 
 @pytest.fixture(scope="module")

@@ -9,6 +9,7 @@
 #include "quant_kernels.cuh"
 #include "pack_kernels.cuh"
 #include "stream_gemm.cuh"
+#include "decode_gemm.cuh"
 #include "tc_gemm.cuh"
 #include "moe_kernels.cuh"
 
@@ -158,6 +159,39 @@ int32_t launch_stream(const uint8_t *A, int64_t lda, bool a_unsigned, int M, int
   } else {
     B2_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     stream_gemm_kernel<false><<<grid, 256, smem, st>>>(g, epi);
+  }
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return B200DNN_SUCCESS;
+}
+
+// Decode-shape kernel (M <= 16): persistent, evenly split over all warps of the device.
+// Returns unimplemented when the shape does not fit it (the caller then uses the tiled streaming kernel).
+int32_t launch_decode(const uint8_t *A, int64_t lda, bool a_unsigned, int M, int N, int K, const PackedWeight &pw,
+                      const EpiParams &epi, cudaStream_t st) {
+  Runtime &R = rt();
+  DecodeGemmArgs g{};
+  g.A = A; g.lda = lda; g.M = M; g.N = N; g.K = K; g.Wt = pw.wt; g.Kp = (int)pw.Kp;
+  g.groups = (N + 7) / 8; g.chunks = (int)(pw.Kp / 64);
+  g.a_stride = (int)pw.Kp + 64;
+  g.rows_staged = M > 8 ? 16 : 8;
+  const size_t smem = (size_t)g.rows_staged * g.a_stride;
+  if (M > 16 || smem > 200 * 1024 || (size_t)g.groups > R.n_counters) return B200DNN_UNIMPLEMENTED;
+  if ((size_t)g.groups > R.decode_groups) {
+    if (R.decode_sums) { B2_CUDA(cudaStreamSynchronize(st)); B2_CUDA(cudaFree(R.decode_sums)); R.decode_sums = nullptr; }
+    const size_t ng = (size_t)g.groups > 4096 ? (size_t)g.groups : 4096;
+    B2_CUDA(cudaMalloc(&R.decode_sums, ng * 128 * sizeof(int32_t)));
+    B2_CUDA(cudaMemset(R.decode_sums, 0, ng * 128 * sizeof(int32_t)));
+    R.decode_groups = ng;
+  }
+  g.sums = R.decode_sums; g.counters = R.counters;
+  const int grid = R.sm_count;
+  if (a_unsigned) {
+    B2_CUDA(cudaFuncSetAttribute(decode_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    decode_gemm_kernel<true><<<grid, kDecodeWarps * 32, smem, st>>>(g, epi);
+  } else {
+    B2_CUDA(cudaFuncSetAttribute(decode_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    decode_gemm_kernel<false><<<grid, kDecodeWarps * 32, smem, st>>>(g, epi);
   }
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
@@ -657,9 +691,12 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   const bool tc_ok = (lda % 16 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
   int which = d->force_kernel;
   if (which == 0) which = (M <= 16 || !tc_ok) ? 1 : 2;
-  B2_CHECK(which == 1 || tc_ok, B200DNN_FAILURE, "tcgen05 kernel needs a 16-byte aligned source with lda %% 16 == 0");
-  if (which == 1) {
-    B2_TRY(launch_stream(A, lda, a_unsigned, M, N, K, pw, epi, st));
+  B2_CHECK(which == 1 || which == 3 || tc_ok, B200DNN_FAILURE, "tcgen05 kernel needs a 16-byte aligned source with lda %% 16 == 0");
+  if (which == 1 || which == 3) {
+    int32_t rc = B200DNN_UNIMPLEMENTED;
+    if (which == 1 && M <= 16 && env_int("B200DNN_DECODE_KERNEL", 1) != 0) rc = launch_decode(A, lda, a_unsigned, M, N, K, pw, epi, st);
+    if (rc == B200DNN_UNIMPLEMENTED) rc = launch_stream(A, lda, a_unsigned, M, N, K, pw, epi, st);
+    B2_TRY(rc);
   } else {
     TcGemmArgs ta{};
     ta.n_groups = 1; ta.m_tiles_plain = (M + kTcBM - 1) / kTcBM;

@@ -83,6 +83,7 @@ struct Runtime {
   std::mutex mu;
   Workspace ws;
   uint32_t *counters = nullptr; size_t n_counters = 0;   // split-K tile counters, kept zero between launches
+  int32_t *decode_sums = nullptr; size_t decode_groups = 0;   // decode kernel partial sums [groups][16][8], kept zero between launches
   int32_t *status = nullptr;                              // device status word of the tcgen05 kernel
   int32_t *status_host = nullptr;                         // pinned mirror
   std::map<std::tuple<const void *, int64_t, int64_t, int64_t, int, int>, PackedWeight> wcache;
