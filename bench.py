@@ -152,7 +152,7 @@ def run_ours(args, rank, world, local_rank):
             keep.append((A, SA, out))
             for buf, sw in packed:
                 d = capi.make_matmul(M, N, K, A, buf, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["bf16"], wei_format="r",
-                                     src_scale=SA, wei_scale=sw)
+                                     src_scale=SA, wei_scale=sw, flags=capi.FLAG_STABLE_WEIGHTS)
                 calls.append((d, decode_bytes(M, K, N)))
     step_bytes = sum(b for _, b in calls)
 
@@ -235,7 +235,7 @@ def run_ours(args, rank, world, local_rank):
             keep.append((A, SA, out))
             for buf, sw in keep[DECODE_KN.index((K, N)) * 4]:
                 d = capi.make_matmul(M, N, K, A, buf, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["bf16"], wei_format="r",
-                                     src_scale=SA, wei_scale=sw)
+                                     src_scale=SA, wei_scale=sw, flags=capi.FLAG_STABLE_WEIGHTS)
                 e2e_calls.append(d)
                 h2d += M * K + 4 * M
                 d2h += 2 * M * N

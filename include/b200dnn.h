@@ -43,6 +43,12 @@ extern "C" {
 
 enum { B200DNN_F32 = 1, B200DNN_BF16 = 3, B200DNN_S32 = 4, B200DNN_S8 = 7, B200DNN_U8 = 11 };
 enum { B200DNN_MAX_POSTOPS = 8 };
+/* b200dnn_matmul_t::flags.  STABLE_WEIGHTS: the (prepacked or cached) weight was written before
+ * any work still pending on the stream, so the decode kernel may start streaming it while the
+ * previous kernel of the stream is still finishing (programmatic dependent launch).  Activations,
+ * scales and outputs are never touched early.  Do not set it when the weight buffer is produced
+ * by work enqueued just before the call. */
+enum { B200DNN_FLAG_STABLE_WEIGHTS = 1 };
 
 /* One scale / zero-point tensor: matmul_quantization_params_t::matmul_quant_t
  * (matmul/lowoha_common.hpp:67-86).  count = number of elements: 1 per-tensor,
@@ -89,7 +95,7 @@ typedef struct b200dnn_matmul_t {
   b200dnn_quant_t src_zp;    /* per-tensor; dt s32 | s8 | u8 */
   b200dnn_postop_t postops[B200DNN_MAX_POSTOPS];
   int32_t force_kernel;  /* for tests: 0 auto, 1 weight-streaming kernels, 2 tcgen05 kernel, 3 tiled streaming kernel only */
-  int32_t reserved;
+  int32_t flags;         /* B200DNN_FLAG_* */
 } b200dnn_matmul_t;
 
 B200DNN_API const char *b200dnn_last_error(void);

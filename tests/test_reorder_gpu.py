@@ -114,6 +114,12 @@ def test_static_quant_dequant_roundtrip(capi, oracle):
     assert (qu == oracle.quant_static(x, s1, z1, "u8")).all()
 
 
+def _unblock(flat, Np, Kp):
+    """Packed weight bytes Wt[Np/8][Kp/128][8][128] (rows interleaved eight at a time in 128-byte
+    pieces) back to a plain [Np, Kp] row-major matrix."""
+    return flat.reshape(Np // 8, Kp // 128, 8, 128).transpose(0, 2, 1, 3).reshape(Np, Kp)
+
+
 @pytest.mark.parametrize("transB", [False, True])
 @pytest.mark.parametrize("K,N", [(64, 16), (130, 200), (512, 384)])
 def test_prepack_layout(capi, oracle, K, N, transB):
@@ -129,7 +135,7 @@ def test_prepack_layout(capi, oracle, K, N, transB):
     hdr = buf[:48].view(np.int64)
     assert int(buf[:4].view(np.uint32)[0]) == 0x38573242 and list(hdr[1:5]) == [K, N, Kp, Np]
     colsum = buf[256:256 + 4 * Np].view(np.int32)
-    wt = buf[256 + 4 * Np:256 + 4 * Np + Np * Kp].view(np.int8).reshape(Np, Kp)
+    wt = _unblock(buf[256 + 4 * Np:256 + 4 * Np + Np * Kp].view(np.int8), Np, Kp)
     assert (wt[:N, :K] == W.T).all() and not wt[N:].any() and not wt[:, K:].any()
     assert (colsum[:N] == W.astype(np.int32).sum(axis=0)).all() and not colsum[N:].any()
 
@@ -142,7 +148,7 @@ def test_prepack_gated_interleave(capi):
     buf = np.zeros(size, dtype=np.uint8)
     assert capi.lib.b200dnn_prepack(capi.ptr(W), K, 2 * I, 2 * I, 0, 1, capi.ptr(buf), None) == capi.SUCCESS, capi.last_error()
     Np = 128
-    wt = buf[256 + 4 * Np:].view(np.int8).reshape(Np, 128)
+    wt = _unblock(buf[256 + 4 * Np:256 + 4 * Np + Np * 128].view(np.int8), Np, 128)
     # packed rows: g[0:32] u[0:32] g[32:64] u[32:64]
     exp = np.concatenate([W[:, 0:32], W[:, I:I + 32], W[:, 32:64], W[:, I + 32:I + 64]], axis=1).T
     assert (wt == exp).all()

@@ -39,7 +39,9 @@ class MatmulDesc(C.Structure):
                 ("n_postops", C.c_int32),
                 ("src_scale", Quant), ("wei_scale", Quant), ("src_zp", Quant),
                 ("postops", PostOp * MAX_POSTOPS),
-                ("force_kernel", C.c_int32), ("reserved", C.c_int32)]
+                ("force_kernel", C.c_int32), ("flags", C.c_int32)]
+
+FLAG_STABLE_WEIGHTS = 1
 
 
 class MoeExpert(C.Structure):
@@ -130,7 +132,7 @@ def quant(buf, count=None, dt=None):
 
 def make_matmul(M, N, K, src, weight, dst, *, src_dt, dst_dt, lda=None, ldb=None, ldc=None, transB=False,
                 bias=None, bias_dt=None, wei_format="n", weights_const=True, dynamic_quant=False,
-                src_scale=None, wei_scale=None, src_zp=None, postops=(), force_kernel=0):
+                src_scale=None, wei_scale=None, src_zp=None, postops=(), force_kernel=0, flags=0):
     d = MatmulDesc()
     d.M, d.N, d.K, d.transB = M, N, K, int(transB)
     d.src_dt, d.wei_dt, d.dst_dt = src_dt, DT["s8"], dst_dt
@@ -168,6 +170,7 @@ def make_matmul(M, N, K, src, weight, dst, *, src_dt, dst_dt, lda=None, ldb=None
             shape = tuple(b.shape)
             d.postops[i].ld = po.get("ld", 0 if (len(shape) == 1 or shape[0] == 1) else shape[-1])
     d.force_kernel = force_kernel
+    d.flags = flags
     return d
 
 

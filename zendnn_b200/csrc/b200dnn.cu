@@ -168,33 +168,27 @@ int32_t launch_stream(const uint8_t *A, int64_t lda, bool a_unsigned, int M, int
 // Decode-shape kernel (M <= 16): persistent, evenly split over all warps of the device.
 // Returns unimplemented when the shape does not fit it (the caller then uses the tiled streaming kernel).
 int32_t launch_decode(const uint8_t *A, int64_t lda, bool a_unsigned, int M, int N, int K, const PackedWeight &pw,
-                      const EpiParams &epi, cudaStream_t st) {
+                      const EpiParams &epi, bool early_weights, cudaStream_t st) {
   Runtime &R = rt();
   DecodeGemmArgs g{};
   g.A = A; g.lda = lda; g.M = M; g.N = N; g.K = K; g.Wt = pw.wt; g.Kp = (int)pw.Kp;
-  g.groups = (N + 7) / 8; g.chunks = (int)(pw.Kp / 64);
+  g.groups = (N + 7) / 8; g.blocks = (int)(pw.Kp / 128);
   g.a_stride = (int)pw.Kp + 64;
   g.rows_staged = M > 8 ? 16 : 8;
-  const size_t smem = (size_t)g.rows_staged * g.a_stride;
-  if (M > 16 || smem > 200 * 1024 || (size_t)g.groups > R.n_counters) return B200DNN_UNIMPLEMENTED;
-  if ((size_t)g.groups > R.decode_groups) {
-    if (R.decode_sums) { B2_CUDA(cudaStreamSynchronize(st)); B2_CUDA(cudaFree(R.decode_sums)); R.decode_sums = nullptr; }
-    const size_t ng = (size_t)g.groups > 4096 ? (size_t)g.groups : 4096;
-    B2_CUDA(cudaMalloc(&R.decode_sums, ng * 128 * sizeof(int32_t)));
-    B2_CUDA(cudaMemset(R.decode_sums, 0, ng * 128 * sizeof(int32_t)));
-    R.decode_groups = ng;
-  }
-  g.sums = R.decode_sums; g.counters = R.counters;
-  const int grid = R.sm_count;
-  if (a_unsigned) {
-    B2_CUDA(cudaFuncSetAttribute(decode_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    decode_gemm_kernel<true><<<grid, kDecodeWarps * 32, smem, st>>>(g, epi);
-  } else {
-    B2_CUDA(cudaFuncSetAttribute(decode_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    decode_gemm_kernel<false><<<grid, kDecodeWarps * 32, smem, st>>>(g, epi);
-  }
+  const int grid = g.groups < R.sm_count ? g.groups : R.sm_count;
+  g.max_local_groups = (g.groups + grid - 1) / grid;
+  const size_t smem = (size_t)g.rows_staged * g.a_stride + (size_t)g.max_local_groups * 512;
+  if (M > 16 || smem > 220 * 1024) return B200DNN_UNIMPLEMENTED;
+  void (*kern)(DecodeGemmArgs, EpiParams) = a_unsigned ? decode_gemm_kernel<true> : decode_gemm_kernel<false>;
+  B2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kDecodeWarps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = early_weights ? 1 : 0;
+  B2_CUDA(cudaLaunchKernelEx(&cfg, kern, g, epi));
   B2_LAUNCHED();
-  B2_CUDA(cudaGetLastError());
   return B200DNN_SUCCESS;
 }
 
@@ -241,7 +235,7 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
   int forced_stages = env_int("B200DNN_TC_STAGES", 0);
   if (forced_stages > 0 && forced_stages <= stages) stages = forced_stages;
   args.stages = stages;
-  B2_TRY(make_map_2d(&map_b, pw0.wt, (uint64_t)pw0.Kp, (uint64_t)pw0.Np, (uint64_t)pw0.Kp, (uint32_t)args.BN));
+  B2_TRY(make_map_wt(&map_b, pw0.wt, (uint64_t)pw0.Kp, (uint64_t)pw0.Np, (uint32_t)args.BN));
   const size_t smem = (size_t)stages * stage_bytes + 1024;
   B2_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   long long tiles = (long long)m_tiles_hint * args.n_tiles;
@@ -694,7 +688,7 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   B2_CHECK(which == 1 || which == 3 || tc_ok, B200DNN_FAILURE, "tcgen05 kernel needs a 16-byte aligned source with lda %% 16 == 0");
   if (which == 1 || which == 3) {
     int32_t rc = B200DNN_UNIMPLEMENTED;
-    if (which == 1 && M <= 16 && env_int("B200DNN_DECODE_KERNEL", 1) != 0) rc = launch_decode(A, lda, a_unsigned, M, N, K, pw, epi, st);
+    if (which == 1 && M <= 16 && env_int("B200DNN_DECODE_KERNEL", 1) != 0) rc = launch_decode(A, lda, a_unsigned, M, N, K, pw, epi, (d->flags & B200DNN_FLAG_STABLE_WEIGHTS) != 0 && env_int("B200DNN_PDL", 1) != 0, st);
     if (rc == B200DNN_UNIMPLEMENTED) rc = launch_stream(A, lda, a_unsigned, M, N, K, pw, epi, st);
     B2_TRY(rc);
   } else {

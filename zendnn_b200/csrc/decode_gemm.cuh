@@ -1,20 +1,25 @@
-// Decode-shape W8A8 GEMM (M <= 16): one persistent CTA per SM, work split evenly over every warp
-// of the grid ("stream-K").  Stands in for the reference's small-M INT8 paths (AOCL-DLP call sites
+// Decode-shape W8A8 GEMM (M <= 16): one persistent CTA of 32 warps per SM, HBM-bound weight stream.
+// Stands in for the reference's small-M INT8 paths (AOCL-DLP call sites
 // matmul/backends/aocl/aocl_kernel.cpp:1190-1301; native GEMV
 // matmul/matmul_native/brgemm/kernel/int8/int8_gemv_bkc.cpp), which split N over CPU threads.
 //
-// The packed weight is W^T [Np][Kp], K contiguous.  The unit of work is a "chunk item": 8 weight
-// rows (output columns) x 64 bytes of K.  All G*C items (G = ceil(N/8) row groups, C = Kp/64) are
-// laid out group-major and cut into gridDim.x * warps equal contiguous ranges, so every SM streams
-// the same number of bytes whatever N and K are.  A lane loads 16 bytes (row g, segment t of the
-// chunk); mma.sync.m16n8k32 multiplies them with the 16 activation rows staged once per CTA in
-// shared memory (same K permutation on both operands, see stream_gemm.cuh).
-//
-// A range may start or end in the middle of a row group.  Partial sums of such groups are added
-// into a zero-initialised s32 scratch [G][16][8] with red.global.add (integer: order-free and
-// exact); a per-group counter of finished chunks tells the warp that completes a group to run the
-// epilogue.  That warp also puts the scratch words and the counter back to zero, so the scratch
-// is all-zero again when the kernel ends.  Groups covered by a single warp never touch the scratch.
+// The packed weight is block-interleaved (pack_kernels.cuh): a group of eight weight rows (output
+// columns) is one contiguous span of 8*Kp bytes made of 1 KiB blocks [8 rows][128 B of K].
+//   - CTA b owns the contiguous groups [b*G/grid, (b+1)*G/grid): its share of the weight is one
+//     contiguous range of memory and no other CTA contributes to its outputs, so there is no
+//     cross-CTA reduction and no global scratch.
+//   - Inside the CTA the blocks of those groups are cut into 32 equal contiguous ranges, one per
+//     warp.  Per block a lane issues two 16-byte loads (row g, segments t and 4+t of the 128 bytes);
+//     blocks beyond the first register batch are prefetched into L2 up front, so the latency of
+//     HBM is paid once.  mma.sync.m16n8k32 multiplies the fragments with the 16 activation rows
+//     staged once per CTA in shared memory (same K permutation on both operands, see
+//     stream_gemm.cuh).
+//   - A warp's range may cover parts of several groups; partial sums go to a shared-memory s32
+//     accumulator [groups of this CTA][16][8] with red.shared.add (integer: exact, order-free).
+//     After one barrier all threads run the epilogue for the CTA's outputs.
+// Programmatic dependent launch: the weight loads are issued before griddepcontrol.wait, so when
+// the launch carries the programmatic-serialisation attribute they overlap the tail of the
+// previous kernel on the stream; activations are read and outputs written only after the wait.
 #pragma once
 #include "common.cuh"
 #include "stream_gemm.cuh"
@@ -26,40 +31,47 @@ struct DecodeGemmArgs {
   int M, N, K;
   const int8_t *Wt; int Kp;
   int groups;                      // ceil(N / 8)
-  int chunks;                      // Kp / 64
+  int blocks;                      // Kp / 128: 1 KiB blocks per group
   int a_stride;                    // smem row stride of A: Kp + 64
   int rows_staged;                 // 8 or 16
-  int32_t *sums;                   // [groups][16][8] zero on entry, zero on exit
-  uint32_t *counters;              // [groups]        zero on entry, zero on exit
+  int max_local_groups;            // ceil(groups / gridDim.x)
 };
 
-constexpr int kDecodeWarps = 16;
-constexpr int kDecodeBatch = 8;    // 16-byte loads in flight per lane
+constexpr int kDecodeWarps = 32;
+constexpr int kDecodeBatch = 4;    // blocks per register batch: 8 x 16-byte loads per lane
+
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 template <bool A_UNSIGNED>
 __global__ void __launch_bounds__(kDecodeWarps * 32, 1) decode_gemm_kernel(DecodeGemmArgs g, EpiParams epi) {
   extern __shared__ __align__(16) uint8_t smem[];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int lg = lane >> 2, lt = lane & 3;
-  const long long total = (long long)g.groups * g.chunks;
-  const long long nwarps = (long long)gridDim.x * kDecodeWarps;
-  const long long wid = (long long)blockIdx.x * kDecodeWarps + warp;
-  long long item = wid * total / nwarps;
-  const long long item_end = (wid + 1) * total / nwarps;
+  const int g0 = (int)((long long)blockIdx.x * g.groups / gridDim.x);
+  const int g1 = (int)((long long)(blockIdx.x + 1) * g.groups / gridDim.x);
+  const int total = (g1 - g0) * g.blocks;               // blocks owned by this CTA
+  int item = (int)((long long)warp * total / kDecodeWarps);
+  const int item_end = (int)((long long)(warp + 1) * total / kDecodeWarps);
+  int32_t *red = reinterpret_cast<int32_t *>(smem + (size_t)g.rows_staged * g.a_stride);   // [local groups][16][8]
 
-  // the first batch of weight loads is issued before the activations are staged
-  int grp = (int)(item / g.chunks);
-  int c = (int)(item - (long long)grp * g.chunks);
-  int run = (int)min((long long)(g.chunks - c), item_end - item);   // chunks of this group in this warp's range
-  const int8_t *wbase = g.Wt + lt * 16;
-  uint4 w[kDecodeBatch];
-  {
-    const int8_t *wrow = wbase + (size_t)(grp * 8 + lg) * g.Kp + (size_t)c * 64;
+  // ---- weights first: register batch + L2 prefetch of the rest of this warp's range
+  const int8_t *wlane = g.Wt + (size_t)g0 * g.Kp * 8 + lg * 128 + lt * 16;   // CTA's span is contiguous: item i at i*1024
+  uint4 w[2 * kDecodeBatch];
 #pragma unroll
-    for (int u = 0; u < kDecodeBatch; ++u) w[u] = (item < item_end && u < run) ? ldg_stream(wrow + u * 64) : make_uint4(0, 0, 0, 0);
+  for (int u = 0; u < kDecodeBatch; ++u) {
+    const bool on = item + u < item_end;
+    w[2 * u] = on ? ldg_stream(wlane + (size_t)(item + u) * 1024) : make_uint4(0, 0, 0, 0);
+    w[2 * u + 1] = on ? ldg_stream(wlane + (size_t)(item + u) * 1024 + 64) : make_uint4(0, 0, 0, 0);
   }
+  for (int i = item + kDecodeBatch; i < item_end; ++i) {
+    // one 128-byte line per (row, block): lanes with lt == 0 cover the eight rows
+    if (lt == 0) prefetch_l2(wlane + (size_t)i * 1024);
+  }
+  for (int i = tid; i < (g1 - g0) * 128; i += kDecodeWarps * 32) red[i] = 0;
 
-  // stage A[0..rows_staged) x [0, Kp) (zero beyond M and K)
+  // ---- everything below may depend on the previous kernel of the stream
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   {
     const bool vec = ((reinterpret_cast<uintptr_t>(g.A) | (uintptr_t)g.lda) & 15) == 0;
     const int segs = g.Kp >> 4;
@@ -83,88 +95,65 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 1) decode_gemm_kernel(Decod
 
   const bool hi_rows = g.rows_staged > 8;
   const uint8_t *a_lo_base = smem + (size_t)lg * g.a_stride + lt * 16;
-  const int32_t zp = load_zp(epi);
+  const size_t a_hi_off = (size_t)8 * g.a_stride;
 
-  while (item < item_end) {
-    int acc[4] = {0, 0, 0, 0};
-    const int8_t *wrow = wbase + (size_t)(grp * 8 + lg) * g.Kp;
-    int done = 0;
-    while (done < run) {
-      const int nb = min(kDecodeBatch, run - done);
-      if (done > 0) {
-        const int8_t *p = wrow + (size_t)(c + done) * 64;
-#pragma unroll
-        for (int u = 0; u < kDecodeBatch; ++u) w[u] = u < nb ? ldg_stream(p + u * 64) : make_uint4(0, 0, 0, 0);
-      }
-      const uint8_t *ap = a_lo_base + (size_t)(c + done) * 64;
+  int lgrp = item / g.blocks;                 // local group of the current block
+  int c = item - lgrp * g.blocks;             // K block inside the group
+  int acc[4] = {0, 0, 0, 0};
+  auto flush = [&](int grp_local) {
+    int32_t *s = red + grp_local * 128;
+    const int col = lt * 2;
+    atomicAdd(s + lg * 8 + col, acc[0]);
+    atomicAdd(s + lg * 8 + col + 1, acc[1]);
+    if (hi_rows) {
+      atomicAdd(s + (lg + 8) * 8 + col, acc[2]);
+      atomicAdd(s + (lg + 8) * 8 + col + 1, acc[3]);
+    }
+    acc[0] = acc[1] = acc[2] = acc[3] = 0;
+  };
+  for (int base = item; base < item_end; base += kDecodeBatch) {
+    if (base != item) {
 #pragma unroll
       for (int u = 0; u < kDecodeBatch; ++u) {
-        if (u < nb) {
-          const uint4 lo = *reinterpret_cast<const uint4 *>(ap + u * 64);
-          const uint4 hi = hi_rows ? *reinterpret_cast<const uint4 *>(ap + u * 64 + (size_t)8 * g.a_stride) : make_uint4(0, 0, 0, 0);
-          mma_m16n8k32<A_UNSIGNED>(acc, lo.x, hi.x, lo.y, hi.y, w[u].x, w[u].y);
-          mma_m16n8k32<A_UNSIGNED>(acc, lo.z, hi.z, lo.w, hi.w, w[u].z, w[u].w);
-        }
-      }
-      done += nb;
-    }
-
-    // ---- this warp's share of group `grp` is in acc: combine and, if it completes the group, finish it
-    bool finish = true;
-    if (run != g.chunks) {
-      int32_t *s = g.sums + (size_t)grp * 128;
-      const int col = lt * 2;
-      atomicAdd(s + lg * 8 + col, acc[0]);
-      atomicAdd(s + lg * 8 + col + 1, acc[1]);
-      if (hi_rows) {
-        atomicAdd(s + (lg + 8) * 8 + col, acc[2]);
-        atomicAdd(s + (lg + 8) * 8 + col + 1, acc[3]);
-      }
-      __threadfence();
-      __syncwarp();
-      unsigned prev = 0;
-      if (lane == 0) prev = atomicAdd(g.counters + grp, (unsigned)run);
-      prev = __shfl_sync(0xffffffffu, prev, 0);
-      finish = (prev + (unsigned)run == (unsigned)g.chunks);
-      if (finish) {
-        __threadfence();
-        acc[0] = __ldcg(s + lg * 8 + col); acc[1] = __ldcg(s + lg * 8 + col + 1);
-        __stcg(s + lg * 8 + col, 0); __stcg(s + lg * 8 + col + 1, 0);
-        if (hi_rows) {
-          acc[2] = __ldcg(s + (lg + 8) * 8 + col); acc[3] = __ldcg(s + (lg + 8) * 8 + col + 1);
-          __stcg(s + (lg + 8) * 8 + col, 0); __stcg(s + (lg + 8) * 8 + col + 1, 0);
-        }
-        if (lane == 0) g.counters[grp] = 0;
+        const bool on = base + u < item_end;
+        w[2 * u] = on ? ldg_stream(wlane + (size_t)(base + u) * 1024) : make_uint4(0, 0, 0, 0);
+        w[2 * u + 1] = on ? ldg_stream(wlane + (size_t)(base + u) * 1024 + 64) : make_uint4(0, 0, 0, 0);
       }
     }
-    if (finish) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int m = lg + (j >> 1) * 8, n = grp * 8 + lt * 2 + (j & 1);
-        if (m >= g.M || n >= g.N) continue;
-        int32_t v = acc[j];
-        if (epi.dst_dt == DT_S32) {
-          if (zp != 0) v -= zp * epi.colsum[n];
-          reinterpret_cast<int32_t *>(epi.dst)[(size_t)m * epi.ldc + n] = v;
-          continue;
+    for (int u = 0; u < kDecodeBatch; ++u) {
+      if (base + u < item_end) {
+        const uint8_t *ap = a_lo_base + (size_t)c * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint4 lo = *reinterpret_cast<const uint4 *>(ap + h * 64);
+          const uint4 hi = hi_rows ? *reinterpret_cast<const uint4 *>(ap + h * 64 + a_hi_off) : make_uint4(0, 0, 0, 0);
+          const uint4 wv = w[2 * u + h];
+          mma_m16n8k32<A_UNSIGNED>(acc, lo.x, hi.x, lo.y, hi.y, wv.x, wv.y);
+          mma_m16n8k32<A_UNSIGNED>(acc, lo.z, hi.z, lo.w, hi.w, wv.z, wv.w);
         }
-        const EpiCtx cx = epi_ctx(epi, m);
-        const float x = epi_finish(epi, cx, epi_dequant(epi, cx, v, zp, n, n), m, n);
-        if (epi.dst_dt == DT_BF16) reinterpret_cast<uint16_t *>(epi.dst)[(size_t)m * epi.ldc + n] = f32_to_bf16_bits(x);
-        else reinterpret_cast<float *>(epi.dst)[(size_t)m * epi.ldc + n] = x;
+        if (++c == g.blocks) { flush(lgrp); c = 0; ++lgrp; }
       }
     }
+  }
+  if (c != 0 && item < item_end) flush(lgrp);
+  __syncthreads();
 
-    // ---- next run
-    item += run;
-    if (item >= item_end) break;
-    grp += 1; c = 0;
-    run = (int)min((long long)g.chunks, item_end - item);
-    {
-      const int8_t *p = wbase + (size_t)(grp * 8 + lg) * g.Kp;
-#pragma unroll
-      for (int u = 0; u < kDecodeBatch; ++u) w[u] = u < run ? ldg_stream(p + u * 64) : make_uint4(0, 0, 0, 0);
+  // ---- epilogue for the CTA's outputs: red[local group][row][column of the group]
+  const int32_t zp = load_zp(epi);
+  for (int i = tid; i < (g1 - g0) * 128; i += kDecodeWarps * 32) {
+    const int gl = i >> 7, m = (i >> 3) & 15, n = (g0 + gl) * 8 + (i & 7);
+    if (m >= g.M || n >= g.N) continue;
+    int32_t v = red[i];
+    if (epi.dst_dt == DT_S32) {
+      if (zp != 0) v -= zp * epi.colsum[n];
+      reinterpret_cast<int32_t *>(epi.dst)[(size_t)m * epi.ldc + n] = v;
+      continue;
     }
+    const EpiCtx cx = epi_ctx(epi, m);
+    const float x = epi_finish(epi, cx, epi_dequant(epi, cx, v, zp, n, n), m, n);
+    if (epi.dst_dt == DT_BF16) reinterpret_cast<uint16_t *>(epi.dst)[(size_t)m * epi.ldc + n] = f32_to_bf16_bits(x);
+    else reinterpret_cast<float *>(epi.dst)[(size_t)m * epi.ldc + n] = x;
   }
 }
 

@@ -53,7 +53,7 @@ int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const s
   for (int g = 0; g < G; ++g) {
     B2_CHECK(pws[g].Kp == p0.Kp && pws[g].Np == p0.Np && pws[g].gated == p0.gated, B200DNN_UNIMPLEMENTED,
              "experts of one grouped GEMM must share K and N");
-    B2_TRY(make_map_2d(&maps[g], pws[g].wt, (uint64_t)p0.Kp, (uint64_t)p0.Np, (uint64_t)p0.Kp, (uint32_t)BN));
+    B2_TRY(make_map_wt(&maps[g], pws[g].wt, (uint64_t)p0.Kp, (uint64_t)p0.Np, (uint32_t)BN));
   }
   void *maps_dev = nullptr;
   B2_TRY(upload_blob(maps.data(), sizeof(CUtensorMap) * G, st, &maps_dev));

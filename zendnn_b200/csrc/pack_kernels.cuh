@@ -5,11 +5,13 @@
 // Packed form, all in one caller- or cache-owned buffer:
 //   [0,256)                 PackHeader
 //   [256, 256+4*Np)         int32 colsum[Np]: sum over K of each packed weight row
-//   [256+4*Np, ...)         int8  Wt[Np][Kp]: the weight transposed, K contiguous ("K-major"),
-//                           K zero-padded to Kp = roundup(K,128), rows zero-padded to Np = roundup(N,128)
-// Kp a multiple of 128 makes every row a whole number of 128-byte TMA swizzle spans; the tcgen05
-// kernel loads [rows x 128 B] boxes of Wt with SWIZZLE_128B and the streaming kernel reads the
-// same rows with 16-byte loads.
+//   [256+4*Np, ...)         int8  Wt: the weight transposed (K contiguous inside a row), K zero-padded
+//                           to Kp = roundup(K,128), rows zero-padded to Np = roundup(N,128), rows
+//                           interleaved eight at a time in 128-byte pieces: Wt[Np/8][Kp/128][8][128]
+//                           (see wt_offset).
+// The tcgen05 kernel loads [BN rows x 128 B] boxes with a 4-D tensor map and SWIZZLE_128B (in
+// shared memory they are ordinary K-major rows); the streaming kernels read the 1 KiB blocks with
+// 16-byte loads, eight rows per warp instruction, contiguously.
 //
 // Gated form (first GEMM of the fused MoE, N = 2*I with caller columns [gate(0:I) | up(I:2I)]):
 // packed row order is [g(0:32) u(0:32) g(32:64) u(32:64) ...] so that one accumulator tile holds
@@ -49,6 +51,16 @@ __host__ __device__ __forceinline__ int64_t packed_to_logical(int64_t pn, int ga
   return 2 * j + (up ? 1 : 0);
 }
 
+// Byte offset of element (packed row pn, k) inside Wt.  Rows are interleaved in groups of eight
+// at 128-byte granularity: Wt[pn/8][k/128][pn%8][k%128].  One group of eight rows is then one
+// contiguous span of 8*Kp bytes, made of 1 KiB blocks that hold 128 bytes of K for each of the
+// eight rows.  A warp of the streaming kernels (which needs eight rows at a time for its MMA
+// fragments) walks memory contiguously, and a TMA box of BN rows x 128 B is BN/8 contiguous
+// 1 KiB blocks that land in shared memory as plain [BN rows][128 B].
+__host__ __device__ __forceinline__ size_t wt_offset(int64_t pn, int64_t k, int64_t Kp) {
+  return (size_t)(pn >> 3) * (size_t)Kp * 8 + (size_t)(k >> 7) * 1024 + (size_t)(pn & 7) * 128 + (size_t)(k & 127);
+}
+
 // grid: (Kp/64, Np/32); block 256.  Each CTA moves a [64 k][32 n] tile through shared memory.
 static __global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t *W, int64_t ldb, int transB, int64_t K, int64_t N,
                                                           int64_t Kp, int gated, int64_t I, int8_t *Wt) {
@@ -79,7 +91,7 @@ static __global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t *W
     const int8_t *t = &tile[nn][k4 * 4];
     uint32_t v = (uint32_t)(uint8_t)t[0] | ((uint32_t)(uint8_t)t[1] << 8) | ((uint32_t)(uint8_t)t[2] << 16) |
                  ((uint32_t)(uint8_t)t[3] << 24);
-    *reinterpret_cast<uint32_t *>(Wt + (pn0 + nn) * Kp + k0 + k4 * 4) = v;
+    *reinterpret_cast<uint32_t *>(Wt + wt_offset(pn0 + nn, k0 + k4 * 4, Kp)) = v;
   }
 }
 
@@ -88,10 +100,9 @@ static __global__ void __launch_bounds__(256) pack_colsum_kernel(const int8_t *W
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= Np) return;
   const int lane = threadIdx.x & 31;
-  const uint4 *p = reinterpret_cast<const uint4 *>(Wt + row * Kp);
   int s = 0;
   for (int64_t i = lane; i < Kp / 16; i += 32) {
-    uint4 v = p[i];
+    const uint4 v = *reinterpret_cast<const uint4 *>(Wt + wt_offset(row, i * 16, Kp));
     s = __dp4a((int)v.x, 0x01010101, s); s = __dp4a((int)v.y, 0x01010101, s);
     s = __dp4a((int)v.z, 0x01010101, s); s = __dp4a((int)v.w, 0x01010101, s);
   }

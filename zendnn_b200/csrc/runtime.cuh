@@ -83,7 +83,6 @@ struct Runtime {
   std::mutex mu;
   Workspace ws;
   uint32_t *counters = nullptr; size_t n_counters = 0;   // split-K tile counters, kept zero between launches
-  int32_t *decode_sums = nullptr; size_t decode_groups = 0;   // decode kernel partial sums [groups][16][8], kept zero between launches
   int32_t *status = nullptr;                              // device status word of the tcgen05 kernel
   int32_t *status_host = nullptr;                         // pinned mirror
   std::map<std::tuple<const void *, int64_t, int64_t, int64_t, int, int>, PackedWeight> wcache;
@@ -127,6 +126,23 @@ inline int32_t make_map_2d(CUtensorMap *m, const void *base, uint64_t inner_byte
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   B2_CHECK(r == CUDA_SUCCESS, B200DNN_FAILURE, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return B200DNN_SUCCESS;
+}
+
+// 4-D uint8 tensor map over a block-interleaved packed weight Wt[Np/8][Kp/128][8][128] (pack_kernels.cuh).
+// Dimensions, innermost first: 128 bytes of K, 8 rows of a group, Kp/128 K-blocks, Np/8 groups.  The box
+// {128, 8, 1, box_rows/8} lands in shared memory as box_rows consecutive 128-byte rows (SWIZZLE_128B).
+inline int32_t make_map_wt(CUtensorMap *m, const void *wt, uint64_t Kp, uint64_t Np, uint32_t box_rows) {
+  B2_CHECK((reinterpret_cast<uintptr_t>(wt) & 15) == 0 && Kp % 128 == 0 && Np % 8 == 0 && box_rows % 8 == 0, B200DNN_FAILURE,
+           "packed weight is not laid out for TMA");
+  cuuint64_t dims[4] = {128, 8, Kp / 128, Np / 8};
+  cuuint64_t strides[3] = {128, 1024, Kp * 8};
+  cuuint32_t box[4] = {128, 8, 1, box_rows / 8};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = rt().encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(wt), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B2_CHECK(r == CUDA_SUCCESS, B200DNN_FAILURE, "cuTensorMapEncodeTiled (weight) failed with %d", (int)r);
   return B200DNN_SUCCESS;
 }
 

@@ -70,13 +70,15 @@ __global__ void __launch_bounds__(256) stream_gemm_kernel(StreamGemmArgs g, EpiP
   const int rows = min(16, g.M - m0);
 
   // first batch of weight loads goes out before the activation block is staged
-  const int8_t *wrow = g.Wt + (size_t)(n_base + nbw * 8 + lg) * g.Kp + lt * 16;
+  // block-interleaved weight (pack_kernels.cuh: wt_offset): 64-byte chunk cc of the eight rows of a group
+  // sits at (cc/2)*1024 + row*128 + (cc%2)*64 inside the group's contiguous 8*Kp bytes
+  const int8_t *wrow = g.Wt + (size_t)(n_base / 8 + nbw) * g.Kp * 8 + lg * 128 + lt * 16;
   uint4 w[kStreamUnroll];
   int c = cbeg + ks;
 #pragma unroll
   for (int u = 0; u < kStreamUnroll; ++u) {
     int cc = c + u * g.kw;
-    w[u] = cc < cend ? ldg_stream(wrow + (size_t)cc * 64) : make_uint4(0, 0, 0, 0);
+    w[u] = cc < cend ? ldg_stream(wrow + (size_t)(cc >> 1) * 1024 + (cc & 1) * 64) : make_uint4(0, 0, 0, 0);
   }
 
   // stage A[m0 .. m0+rows) x [cbeg*64, cend*64) into shared memory, zero beyond M and K
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(256) stream_gemm_kernel(StreamGemmArgs g, EpiP
 #pragma unroll
     for (int u = 0; u < kStreamUnroll; ++u) {   // prefetch the next batch
       int cc = cnext + u * g.kw;
-      wn[u] = cc < cend ? ldg_stream(wrow + (size_t)cc * 64) : make_uint4(0, 0, 0, 0);
+      wn[u] = cc < cend ? ldg_stream(wrow + (size_t)(cc >> 1) * 1024 + (cc & 1) * 64) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < kStreamUnroll; ++u) {

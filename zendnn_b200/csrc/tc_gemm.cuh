@@ -91,6 +91,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// weight box from the block-interleaved layout: coordinates {byte 0, row-in-group 0, K block, row group}
+__device__ __forceinline__ void tma_load_wt(uint32_t dst, const CUtensorMap *map, int kblock, int group, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+               ::"r"(dst), "l"(map), "r"(0), "r"(0), "r"(kblock), "r"(group), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -281,7 +286,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t sa = smem0 + (uint32_t)stage * stage_bytes;
           mbar_expect_tx(full_bar(stage), stage_bytes);
           tma_load_2d(sa, &map_a, kb * kTcBK, t.row0, full_bar(stage));
-          tma_load_2d(sa + a_bytes, mb, kb * kTcBK, t.nt * a.BN, full_bar(stage));
+          tma_load_wt(sa + a_bytes, mb, kb, (t.nt * a.BN) >> 3, full_bar(stage));
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
       }
