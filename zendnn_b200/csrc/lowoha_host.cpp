@@ -1,0 +1,322 @@
+// C++ shims with the reference's LowOHA signatures (include/zendnnl_b200/lowoha.hpp) over the C ABI
+// of libb200dnn.  Each function flattens the reference's parameter structs into the plain
+// descriptors of b200dnn.h; all arithmetic happens in the CUDA library.  What the reference does
+// at this level and is kept: argument checks that need the C++ containers, the active/total
+// expert contract, the choice between fused-MoE and plain grouped execution.
+//
+// Reference entry points: lowoha_operators/matmul/lowoha_matmul.cpp:278 (matmul_direct),
+// lowoha_operators/matmul/group_matmul_direct.cpp:747 (group_matmul_direct),
+// lowoha_operators/reorder/lowoha_reorder.cpp:43,279 (reorder_direct, group_dynamic_quant),
+// lowoha_operators/reorder/prepack/lowoha_prepack.cpp:285,315 (weight_prepack_size / _into).
+#include "zendnnl_b200/lowoha.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
+#include "b200dnn.h"
+
+namespace zendnnl {
+namespace lowoha {
+
+namespace {
+using zendnnl::common::data_type_t;
+using zendnnl::error_handling::status_t;
+
+thread_local std::string g_shim_error;
+
+status_t shim_fail(status_t s, const char *msg) { g_shim_error = msg; return s; }
+status_t from_c(int32_t rc) {
+  if (rc != B200DNN_SUCCESS) g_shim_error = b200dnn_last_error();
+  return static_cast<status_t>(rc);
+}
+int64_t nelem(const std::vector<int64_t> &d) {
+  if (d.empty()) return 0;
+  int64_t n = 1;
+  for (auto v : d) n *= v;
+  return n;
+}
+template <class Q> b200dnn_quant_t flat_quant(const Q &q) {
+  b200dnn_quant_t o{};
+  o.buff = q.buff; o.dt = static_cast<int32_t>(q.dt);
+  const int64_t n = nelem(q.dims);
+  o.count = n > 0 ? n : (q.buff ? 1 : 0);
+  return o;
+}
+}  // namespace
+
+// =========================================================================================== matmul
+namespace matmul {
+
+const char *last_error() { return g_shim_error.c_str(); }
+
+namespace {
+// Flattens one matmul_direct call.  Returns success when `d` is filled, otherwise the status to return.
+status_t flatten(const char layout, const bool transA, const bool transB, const int M, const int N, const int K,
+                 const float alpha, const void *src, const int lda, const void *weight, const int ldb, const void *bias,
+                 const float beta, void *dst, const int ldc, const bool is_weights_const,
+                 const matmul_batch_params_t &bp, const matmul_params &p, b200dnn_matmul_t *d) {
+  if (layout != 'r' && layout != 'R') return shim_fail(status_t::unimplemented, "only row-major layout is implemented");
+  if (transA) return shim_fail(status_t::unimplemented, "transA is not implemented");
+  if (bp.Batch_A != 1 || bp.Batch_B != 1) return shim_fail(status_t::unimplemented, "batched matmul is not implemented");
+  if (alpha != 1.0f || beta != 0.0f) return shim_fail(status_t::unimplemented, "only alpha = 1, beta = 0 is implemented");
+  if (p.packing.pack_format_b != 0) return shim_fail(status_t::unimplemented, "GGML-packed weights are not implemented");
+  if (p.quant_params.dst_scale.buff || p.quant_params.dst_zp.buff)
+    return shim_fail(status_t::unimplemented, "requantised (s8/u8) destinations are not implemented");
+  if (p.quant_params.wei_zp.buff) return shim_fail(status_t::unimplemented, "weight zero-points are not implemented");
+  if (p.postop_.size() > B200DNN_MAX_POSTOPS) return shim_fail(status_t::failure, "too many post-ops");
+  std::memset(d, 0, sizeof *d);
+  d->M = M; d->N = N; d->K = K; d->transB = transB ? 1 : 0;
+  d->src_dt = static_cast<int32_t>(p.dtypes.src); d->wei_dt = static_cast<int32_t>(p.dtypes.wei);
+  d->dst_dt = static_cast<int32_t>(p.dtypes.dst); d->bias_dt = static_cast<int32_t>(p.dtypes.bias);
+  d->lda = lda; d->ldb = ldb; d->ldc = ldc;
+  d->src = src; d->weight = weight; d->bias = bias; d->dst = dst;
+  d->wei_format = p.mem_format_b;
+  d->weights_const = (is_weights_const && p.weight_cache_type != 0) ? 1 : 0;
+  d->dynamic_quant = p.dynamic_quant ? 1 : 0;
+  d->src_scale = flat_quant(p.quant_params.src_scale);
+  d->wei_scale = flat_quant(p.quant_params.wei_scale);
+  d->src_zp = flat_quant(p.quant_params.src_zp);
+  if (!p.quant_params.src_zp.buff) d->src_zp.count = 0;
+  d->n_postops = static_cast<int32_t>(p.postop_.size());
+  for (int i = 0; i < d->n_postops; ++i) {
+    const matmul_post_op &po = p.postop_[i];
+    b200dnn_postop_t &o = d->postops[i];
+    o.type = static_cast<int32_t>(po.po_type); o.dt = static_cast<int32_t>(po.dtype); o.buff = po.buff;
+    o.alpha = po.alpha; o.beta = po.beta;
+    const bool row_broadcast = po.dims.size() == 2 && po.dims[0] == 1;
+    const bool vec_broadcast = po.dims.size() == 1;
+    o.ld = (row_broadcast || vec_broadcast) ? 0 : (po.leading_dim > 0 ? po.leading_dim : N);   // default leading dim N
+    if (po.po_type == zendnnl::ops::post_op_type_t::clip && o.alpha > o.beta) std::swap(o.alpha, o.beta);
+  }
+  return status_t::success;
+}
+}  // namespace
+
+status_t matmul_direct(const char layout, const bool transA, const bool transB, const int M, const int N, const int K,
+                       const float alpha, const void *src, const int lda, const void *weight, const int ldb,
+                       const void *bias, const float beta, void *dst, const int ldc, const bool is_weights_const,
+                       const matmul_batch_params_t &batch_params, const matmul_params &params) {
+  b200dnn_matmul_t d;
+  status_t st = flatten(layout, transA, transB, M, N, K, alpha, src, lda, weight, ldb, bias, beta, dst, ldc, is_weights_const,
+                        batch_params, params, &d);
+  if (st != status_t::success) return st;
+  return from_c(b200dnn_matmul(&d, nullptr));
+}
+
+status_t group_matmul_moe_act_execute(const grp_matmul_gated_act_params *act_params, const std::vector<void *> &dst,
+                                      const std::vector<int> &M, const std::vector<int> &N, const std::vector<int> &ldc,
+                                      data_type_t dst_dtype, int /*num_threads*/) {
+  if (!act_params || act_params->act == grp_matmul_gated_act_t::none) return status_t::success;
+  if (dst.size() != M.size() || N.size() != M.size() || ldc.size() != M.size())
+    return shim_fail(status_t::failure, "gated activation: vector sizes differ");
+  for (size_t i = 0; i < M.size(); ++i) {
+    if (M[i] <= 0) continue;
+    if (!dst[i]) return shim_fail(status_t::failure, "gated activation: null dst");
+    status_t st = from_c(b200dnn_gated_act(dst[i], static_cast<int32_t>(dst_dtype), M[i], N[i], ldc[i],
+                                           static_cast<int32_t>(act_params->act), nullptr));
+    if (st != status_t::success) return st;
+  }
+  return status_t::success;
+}
+
+status_t group_matmul_moe_postop_execute(const group_matmul_moe_postop_params *p, int D, int /*num_threads*/,
+                                         data_type_t dst_elem) {
+  if (!p) return status_t::success;
+  if (p->num_tokens <= 0 || p->topk <= 0 || !p->output || !p->row_ptrs || D <= 0 || p->ldc_output < D)
+    return shim_fail(status_t::failure, "moe post-op: bad argument");
+  if (!p->skip_weighted && !p->topk_weights) return shim_fail(status_t::failure, "moe post-op: topk_weights is null");
+  return from_c(b200dnn_moe_weighted_reduce(p->row_ptrs, p->topk_weights, p->num_tokens, p->topk, D, p->skip_weighted ? 1 : 0,
+                                            static_cast<int32_t>(dst_elem), p->output, p->ldc_output, nullptr));
+}
+
+void clear_fused_moe_scratch() { b200dnn_clear_caches(); }
+
+status_t group_matmul_direct(const std::vector<char> &layout, const std::vector<bool> &transA, const std::vector<bool> &transB,
+                             const std::vector<int> &M, const std::vector<int> &N, const std::vector<int> &K,
+                             const std::vector<float> &alpha, const std::vector<const void *> &src, const std::vector<int> &lda,
+                             const std::vector<const void *> &weight, const std::vector<int> &ldb,
+                             const std::vector<const void *> &bias, const std::vector<float> &beta,
+                             const std::vector<void *> &dst, const std::vector<int> &ldc,
+                             const std::vector<bool> &is_weights_const, const std::vector<matmul_params> &params,
+                             const group_matmul_moe_postop_params *moe_postop, const grp_matmul_gated_act_params *gated_act,
+                             const grp_matmul_fused_moe_params *fused) {
+  // always-on guards (group_matmul_direct.cpp:812-1063): non-empty, consistent vector lengths
+  if (M.empty() || params.empty()) return shim_fail(status_t::failure, "group_matmul_direct: empty M or params");
+  // active/total contract: only params[0] is read; compute the leading `active` experts (lowoha_common.hpp:169-214)
+  size_t num_ops = M.size();
+  if (params[0].active_matmul > 0) {
+    if (params[0].total_matmul > 0 && params[0].active_matmul > params[0].total_matmul)
+      return shim_fail(status_t::failure, "group_matmul_direct: active_matmul > total_matmul");
+    num_ops = std::min<size_t>(params[0].active_matmul, M.size());
+  }
+  auto at_least = [&](size_t n) { return n >= num_ops; };
+  if (!at_least(layout.size()) || !at_least(transA.size()) || !at_least(transB.size()) || !at_least(N.size()) ||
+      !at_least(K.size()) || !at_least(alpha.size()) || !at_least(lda.size()) || !at_least(weight.size()) ||
+      !at_least(ldb.size()) || !at_least(bias.size()) || !at_least(beta.size()) || !at_least(ldc.size()) ||
+      !at_least(is_weights_const.size()) || !at_least(params.size()))
+    return shim_fail(status_t::failure, "group_matmul_direct: a per-expert vector is shorter than the number of operations");
+  if (src.size() == 1 && num_ops > 1) return shim_fail(status_t::unimplemented, "sequential (chained) group mode is not implemented");
+  if (!at_least(src.size())) return shim_fail(status_t::failure, "group_matmul_direct: src vector too short");
+  const grp_matmul_gated_act_t act = gated_act ? gated_act->act : grp_matmul_gated_act_t::none;
+
+  if (fused) {
+    // ---- fused MoE: Op1 (gate|up) -> gated activation -> per-token requantisation -> Op2 (down) [-> weighted reduce]
+    if (act == grp_matmul_gated_act_t::none) return shim_fail(status_t::failure, "fused MoE needs a gated activation");
+    if (fused->down_weight.size() < num_ops || fused->N_down.size() < num_ops || fused->ldb_down.size() < num_ops ||
+        fused->down_scale.size() < num_ops)
+      return shim_fail(status_t::failure, "fused MoE: down-projection vectors are shorter than the number of experts");
+    if (fused->dst_down.size() < num_ops || fused->ldc_down.size() < num_ops)
+      return shim_fail(status_t::unimplemented, "fused MoE: writing the result back into src[] (empty dst_down) is not implemented");
+    const matmul_params &p0 = params[0];
+    if (!(p0.dynamic_quant && p0.dtypes.src == data_type_t::bf16 && p0.dtypes.wei == data_type_t::s8 &&
+          p0.dtypes.dst == data_type_t::bf16))
+      return shim_fail(status_t::unimplemented, "fused MoE is implemented for dynamic per-token INT8 (bf16 src, s8 weights, bf16 dst)");
+    std::vector<b200dnn_moe_expert_t> ex(num_ops);
+    for (size_t i = 0; i < num_ops; ++i) {
+      if (N[i] != N[0] || K[i] != K[0] || fused->N_down[i] != fused->N_down[0] || transB[i] != transB[0])
+        return shim_fail(status_t::unimplemented, "fused MoE: experts must share K, N, N_down and transB");
+      if (layout[i] != 'r' && layout[i] != 'R') return shim_fail(status_t::failure, "fused MoE requires row-major layout");
+      if (transA[i] || alpha[i] != 1.0f || beta[i] != 0.0f) return shim_fail(status_t::unimplemented, "fused MoE: transA / alpha / beta");
+      if (bias[i] || (i < fused->bias_down.size() && fused->bias_down[i]))
+        return shim_fail(status_t::unimplemented, "fused MoE: bias is not implemented");
+      const auto &ws = params[i].quant_params.wei_scale;
+      if (!ws.buff || ws.dt != data_type_t::f32 || nelem(ws.dims) != N[i])
+        return shim_fail(status_t::failure, "fused MoE: per-channel f32 weight scale of N elements required");
+      const auto &ds = fused->down_scale[i];
+      if (!ds.buff || ds.dt != data_type_t::f32 || nelem(ds.dims) != fused->N_down[i])
+        return shim_fail(status_t::failure, "fused MoE: per-channel f32 down_scale of N_down elements required");
+      b200dnn_moe_expert_t &e = ex[i];
+      std::memset(&e, 0, sizeof e);
+      e.M = M[i]; e.src = src[i]; e.lda = lda[i];
+      e.w13 = weight[i]; e.ldb13 = ldb[i]; e.w13_scale = static_cast<const float *>(ws.buff);
+      e.w2 = fused->down_weight[i]; e.ldb2 = fused->ldb_down[i]; e.w2_scale = static_cast<const float *>(ds.buff);
+      e.dst_down = fused->dst_down[i]; e.ldc_down = fused->ldc_down[i];
+    }
+    const bool wconst = is_weights_const[0] && p0.weight_cache_type != 0;
+    return from_c(b200dnn_fused_moe(static_cast<int32_t>(num_ops), ex.data(), K[0], N[0] / 2, fused->N_down[0], transB[0] ? 1 : 0,
+                                    static_cast<int32_t>(act), wconst ? 1 : 0,
+                                    moe_postop ? reinterpret_cast<const void *const *>(moe_postop->row_ptrs) : nullptr,
+                                    moe_postop ? moe_postop->topk_weights : nullptr, moe_postop ? moe_postop->num_tokens : 0,
+                                    moe_postop ? moe_postop->topk : 0, moe_postop ? moe_postop->output : nullptr,
+                                    moe_postop ? moe_postop->ldc_output : 0, nullptr));
+  }
+
+  // ---- plain grouped mode: every expert's GEMM, experts with M == 0 skipped (group_matmul_parallel_common.hpp:1240-1248)
+  if (!at_least(dst.size())) return shim_fail(status_t::failure, "group_matmul_direct: dst vector too short");
+  const matmul_batch_params_t bp;
+  for (size_t i = 0; i < num_ops; ++i) {
+    if (M[i] == 0) continue;
+    status_t st = matmul_direct(layout[i], transA[i], transB[i], M[i], N[i], K[i], alpha[i], src[i], lda[i], weight[i], ldb[i],
+                                bias[i], beta[i], dst[i], ldc[i], is_weights_const[i], bp, params[i]);
+    if (st != status_t::success) return st;
+  }
+  if (act != grp_matmul_gated_act_t::none) {
+    std::vector<void *> d(dst.begin(), dst.begin() + num_ops);
+    std::vector<int> m(M.begin(), M.begin() + num_ops), n(N.begin(), N.begin() + num_ops), l(ldc.begin(), ldc.begin() + num_ops);
+    status_t st = group_matmul_moe_act_execute(gated_act, d, m, n, l, params[0].dtypes.dst, 0);
+    if (st != status_t::success) return st;
+  }
+  if (moe_postop) {
+    const int D = act != grp_matmul_gated_act_t::none ? N[0] / 2 : N[0];
+    return group_matmul_moe_postop_execute(moe_postop, D, 0, params[0].dtypes.dst);
+  }
+  return status_t::success;
+}
+}  // namespace matmul
+
+// =========================================================================================== reorder
+namespace reorder {
+
+size_t weight_prepack_size(const reorder_params_t &params) {
+  const prepack_params_t &pp = params.prepack;
+  if (pp.K <= 0 || pp.N <= 0 || pp.wei_dtype != data_type_t::s8) return 0;
+  if (pp.cached_size == 0) pp.cached_size = b200dnn_prepack_size(pp.K, pp.N, 0);
+  return pp.cached_size;
+}
+
+status_t weight_prepack_into(const void *weights, const reorder_params_t &params, void *dst) {
+  const prepack_params_t &pp = params.prepack;
+  if (!weights || !dst) return shim_fail(status_t::failure, "prepack: null pointer");
+  if (pp.wei_dtype != data_type_t::s8) return shim_fail(status_t::unimplemented, "prepack: only s8 weights are implemented");
+  if (pp.sym_group_size != 0 && pp.sym_group_size != pp.K)
+    return shim_fail(status_t::unimplemented, "prepack: per-group symmetric quantisation is not implemented");
+  return from_c(b200dnn_prepack(weights, pp.K, pp.N, pp.ldb > 0 ? pp.ldb : (pp.transposed ? pp.K : pp.N), pp.transposed ? 1 : 0, 0,
+                                dst, nullptr));
+}
+
+status_t reorder_direct(const void *src, void *dst, reorder_params_t &params) {
+  if (params.is_prepack) return weight_prepack_into(src, params, dst);
+  if (!src) return shim_fail(status_t::failure, "reorder: null src");
+  if (!params.is_2d()) return shim_fail(status_t::unimplemented, "reorder: only 2-D shapes are implemented");
+  const int64_t M = params.M(), N = params.N();
+  if (M <= 0 || N <= 0) return shim_fail(status_t::failure, "reorder: non-positive shape");
+  if (!params.dst_shape.empty() && params.dst_shape != params.src_shape) return shim_fail(status_t::failure, "reorder: shapes differ");
+  int64_t src_ld = N;
+  if (params.has_src_strides()) {
+    if (params.src_strides.size() != 2 || params.src_strides[1] != 1) return shim_fail(status_t::unimplemented, "reorder: source must be row-strided");
+    src_ld = params.src_strides[0];
+  }
+  const auto &sc = params.quant_params.scale;
+  const auto &zp = params.quant_params.zero_point;
+  const int32_t sdt = static_cast<int32_t>(params.src_dtype), ddt = static_cast<int32_t>(params.dst_dtype);
+  const bool src_float = params.src_dtype == data_type_t::f32 || params.src_dtype == data_type_t::bf16;
+  const int64_t ns = nelem(sc.dims) > 0 ? nelem(sc.dims) : 1;
+  const bool per_token = sc.dims.size() == 2 && sc.dims[0] == M && sc.dims[1] == 1 && M > 1;
+  const bool per_channel = sc.dims.size() == 2 && sc.dims[0] == 1 && sc.dims[1] == N && N > 1;
+  if (params.dynamic_quant) {
+    // the caller owns the scale buffer (lowoha_reorder_utils.cpp:524-528); dst == null computes scales only
+    if (!sc.buff) return shim_fail(status_t::failure, "reorder: dynamic quantisation needs a scale buffer");
+    if (zp.buff) return shim_fail(status_t::unimplemented, "reorder: asymmetric dynamic quantisation is not implemented");
+    if (!src_float || (dst && params.dst_dtype != data_type_t::s8)) return shim_fail(status_t::unimplemented, "reorder: dynamic quantisation is f32|bf16 -> s8");
+    if (per_token || (ns == M && M == 1 && N > 1 && sc.dims.size() == 2 && sc.dims[1] == 1))
+      return from_c(b200dnn_quant_per_token(src, sdt, M, N, src_ld, dst, N, sc.buff, static_cast<int32_t>(sc.dt), nullptr));
+    if (sc.dt != data_type_t::f32) return shim_fail(status_t::unimplemented, "reorder: per-channel / per-tensor scales are f32");
+    if (per_channel) return from_c(b200dnn_quant_dynamic(src, sdt, M, N, src_ld, 1, dst, N, static_cast<float *>(sc.buff), nullptr));
+    if (ns == 1) return from_c(b200dnn_quant_dynamic(src, sdt, M, N, src_ld, 0, dst, N, static_cast<float *>(sc.buff), nullptr));
+    return shim_fail(status_t::unimplemented, "reorder: per-group dynamic quantisation is not implemented");
+  }
+  if (!dst) return shim_fail(status_t::failure, "reorder: null dst");
+  if (!sc.buff || sc.dt != data_type_t::f32) return shim_fail(status_t::unimplemented, "reorder: static (de)quantisation needs an f32 scale");
+  if (!(ns == 1 || per_channel)) return shim_fail(status_t::unimplemented, "reorder: scale must be per-tensor or per-channel");
+  int64_t nz = 0;
+  if (zp.buff) {
+    if (zp.dt != data_type_t::s32) return shim_fail(status_t::unimplemented, "reorder: zero-point must be s32");
+    nz = nelem(zp.dims) > 0 ? nelem(zp.dims) : 1;
+    if (!(nz == 1 || nz == N)) return shim_fail(status_t::unimplemented, "reorder: zero-point granularity");
+  }
+  const bool dst_int = params.dst_dtype == data_type_t::s8 || params.dst_dtype == data_type_t::u8;
+  const bool src_int = params.src_dtype == data_type_t::s8 || params.src_dtype == data_type_t::u8;
+  if (src_float && dst_int)
+    return from_c(b200dnn_quant_static(src, sdt, M, N, src_ld, static_cast<const float *>(sc.buff), ns,
+                                       static_cast<const int32_t *>(zp.buff), nz, dst, ddt, N, nullptr));
+  if (src_int && (params.dst_dtype == data_type_t::f32 || params.dst_dtype == data_type_t::bf16))
+    return from_c(b200dnn_dequant_static(src, sdt, M, N, src_ld, static_cast<const float *>(sc.buff), ns,
+                                         static_cast<const int32_t *>(zp.buff), nz, dst, ddt, N, nullptr));
+  return shim_fail(status_t::unimplemented, "reorder: dtype combination is not implemented");
+}
+
+status_t group_dynamic_quant(const std::vector<const void *> &src, const std::vector<int> &M, const std::vector<int> &K,
+                             const std::vector<std::vector<int64_t>> &src_strides, const std::vector<void *> &dst,
+                             const std::vector<std::vector<int64_t>> &dst_strides, const std::vector<void *> &scale,
+                             const group_dynamic_quant_params_t &params) {
+  const size_t G = params.num_groups > 0 ? static_cast<size_t>(params.num_groups) : src.size();
+  if (G == 0 || src.size() < G || M.size() < G || K.size() < G || dst.size() < G || scale.size() < G)
+    return shim_fail(status_t::failure, "group_dynamic_quant: vectors shorter than num_groups");
+  if (params.dst_dtype != data_type_t::s8) return shim_fail(status_t::unimplemented, "group_dynamic_quant: s8 destination only");
+  std::vector<int32_t> m(G), k(G);
+  std::vector<int64_t> sld(G), dld(G);
+  for (size_t i = 0; i < G; ++i) {
+    m[i] = M[i]; k[i] = K[i];
+    sld[i] = (i < src_strides.size() && !src_strides[i].empty()) ? src_strides[i][0] : K[i];
+    dld[i] = (i < dst_strides.size() && !dst_strides[i].empty()) ? dst_strides[i][0] : K[i];
+  }
+  return from_c(b200dnn_group_quant_per_token(static_cast<int32_t>(G), src.data(), static_cast<int32_t>(params.src_dtype), m.data(),
+                                              k.data(), sld.data(), dst.data(), dld.data(), scale.data(),
+                                              static_cast<int32_t>(params.scale_dtype), nullptr));
+}
+
+}  // namespace reorder
+}  // namespace lowoha
+}  // namespace zendnnl
