@@ -278,9 +278,15 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm"], 4), "traffic": None, "peak_source": peaks["src"],
-                     "kernel": "stream_gemm_kernel", "frac_of_8TBs": round(achieved / 8000.0, 4)},
+                     "kernel": "decode_gemm_kernel", "frac_of_8TBs": round(achieved / 8000.0, 4)},
         "per_shape": per,
     }
+    # free the decode operands before the other workloads of the metric are measured
+    del calls, e2e_calls, keep, graph
+    capi.lib.b200dnn_clear_caches()
+    torch.cuda.empty_cache()
+    if not args.no_extras:
+        line["also"] = run_extras(torch, capi, dev, rank, world, peaks)
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline_decode(shapes, budget_s=12.0)
     if world > 1:
@@ -289,6 +295,89 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------- other workloads
+def _time_events(torch, fn, iters, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def run_extras(torch, capi, dev, rank, world, peaks):
+    """The other two parts of the metric: prefill W8A8 TOPS (configurations 1 and 3) on one GPU and fused-MoE
+    tokens/s (configuration 4), expert-parallel over all ranks when there are several (weak scaling: 4096
+    tokens per rank, the 8 experts sharded e % world).  Device-resident operands, CUDA-event timing."""
+    st = torch.cuda.current_stream().cuda_stream
+    out = {}
+    int8_peak = 2.0 * peaks["bf16"]          # no measured int8 figure: twice the measured dense bf16 rate
+    g = torch.Generator(device="cpu").manual_seed(7 + rank)
+
+    def gemm(M, K, N, dyn, act):
+        W = torch.randint(-127, 128, (K, N), dtype=torch.int8, generator=g).to(dev)
+        packed = torch.empty(capi.lib.b200dnn_prepack_size(K, N, 0), dtype=torch.uint8, device=dev)
+        capi.check(capi.lib.b200dnn_prepack(W.data_ptr(), K, N, N, 0, 0, packed.data_ptr(), st))
+        torch.cuda.synchronize()
+        del W
+        sw = (torch.rand(N, generator=g) * 0.009 + 0.001).to(dev)
+        bias = torch.randn(N, generator=g).to(dev)
+        o = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        if dyn:
+            A = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+            d = capi.make_matmul(M, N, K, A, packed, o, src_dt=capi.DT["bf16"], dst_dt=capi.DT["bf16"], wei_format="r",
+                                 dynamic_quant=True, src_scale=capi.quant(None, count=M, dt=capi.DT["f32"]), wei_scale=sw,
+                                 bias=bias, postops=[act])
+        else:
+            A = torch.randint(0, 256, (M, K), dtype=torch.uint8, generator=g).to(dev)
+            ss = torch.tensor([0.02], device=dev)
+            zp = torch.tensor([128], dtype=torch.int32, device=dev)
+            d = capi.make_matmul(M, N, K, A, packed, o, src_dt=capi.DT["u8"], dst_dt=capi.DT["bf16"], wei_format="r",
+                                 src_scale=ss, wei_scale=sw, src_zp=zp, bias=bias, postops=[act])
+        ms = _time_events(torch, lambda: capi.check(capi.matmul(d, st)), 20)
+        tops = 2.0 * M * N * K / ms / 1e9
+        return {"us": round(ms * 1e3, 1), "tops": round(tops, 1), "frac_of_2x_measured_bf16": round(tops / int8_peak, 3)}
+
+    if rank == 0:
+        out["prefill_M2048_K4096_N14336_dynquant_bias_gelu_bf16"] = gemm(2048, 4096, 14336, True, "gelu_tanh")
+        out["config1_M128_K4096_N4096_u8zp_bias_relu_bf16"] = gemm(128, 4096, 4096, False, "relu")
+    torch.cuda.synchronize()
+    capi.lib.b200dnn_clear_caches()
+
+    # fused MoE, configuration 4 (Mixtral-like): 4096 tokens per rank, hidden 4096, FFN 14336, 8 experts, top-2
+    from zendnn_b200 import moe_ep
+    T, H, I, E, topk = 4096, 4096, 14336, 8, 2
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
+    logits = torch.randn(T, E, generator=g).to(dev)
+    mine = []
+    for e in moe_ep.experts_on_rank(rank, world, E):
+        ge = torch.Generator(device="cpu").manual_seed(100 + e)
+        mine.append(dict(w13=torch.randint(-127, 128, (H, 2 * I), dtype=torch.int8, generator=ge).to(dev),
+                         s13=(torch.rand(2 * I, generator=ge) * 1e-3 + 1e-4).to(dev),
+                         w2=torch.randint(-127, 128, (I, H), dtype=torch.int8, generator=ge).to(dev),
+                         s2=(torch.rand(H, generator=ge) * 1e-3 + 1e-4).to(dev)))
+    ops = moe_ep.CapiOps(mine, [], H, I, H)
+    ms = _time_events(torch, lambda: moe_ep.ep_moe_forward(x, logits, topk, E, 0, ops), 5)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    rows = T * topk
+    ops_per_layer = 2.0 * rows * H * 2 * I + 2.0 * rows * I * H
+    out["moe_mixtral_like"] = {"tokens_per_s": round(world * T / ms * 1e3), "ms_per_layer": round(ms, 3), "n_gpus": world,
+                               "tokens_per_rank": T, "experts": E, "topk": topk, "scaling": "weak",
+                               "tops_per_gpu": round(ops_per_layer / ms / 1e9, 1),
+                               "path": "expert-parallel, NCCL all-to-all dispatch/combine" if world > 1 else "single GPU"}
+    del ops, mine
+    capi.lib.b200dnn_clear_caches()
+    return out
 
 
 # ---------------------------------------------------------------------------------------------- CPU arm
@@ -345,6 +434,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode"])
     ap.add_argument("--inner", type=int, default=100, help="passes over the decode grid per step")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill and MoE measurements reported under 'also'")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

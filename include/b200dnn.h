@@ -211,6 +211,32 @@ B200DNN_API int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *l
                           int32_t K, int32_t I, int32_t H, int32_t transB, int32_t act, void *out,
                           int64_t ld_out, void *stream);
 
+/* ---- Building blocks of the expert-parallel MoE (experts sharded over GPUs).  No counterpart in the
+ * reference, which is a single-process CPU library; the exchange of tokens between GPUs (NCCL
+ * all-to-all) happens in the caller between these calls.  Device pointers only. ---- */
+
+/* Stable counting sort of (token,k) slots by an integer key in [0,nkeys): counts per key and, for
+ * every slot, its row in key-sorted order.  With key = (destination rank, local expert) this gives
+ * the send order of the dispatch. */
+B200DNN_API int32_t b200dnn_moe_sort_slots(const int32_t *keys, int32_t nslots, int32_t nkeys, int32_t *counts,
+                                           int32_t *slot_to_row, void *stream);
+/* Per-token quantisation (as b200dnn_quant_per_token) of gathered rows: output row r is source row
+ * row_src[r] / row_div of src [*, K] (row stride src_ld). */
+B200DNN_API int32_t b200dnn_quant_per_token_gather(const void *src, int32_t src_dt, int64_t K, int64_t src_ld,
+                                                   const int32_t *row_src, int32_t row_div, int64_t R, void *dst,
+                                                   int64_t dst_ld, float *scale, void *stream);
+/* Expert computation of the fused MoE on rows that arrive already quantised (s8 [R,lda] + f32 scale
+ * per row): first GEMM + gated activation + requantisation + second GEMM, out bf16 [R,H].  Rows are
+ * grouped: group g has group_rows[g] consecutive rows and uses experts[group_expert[g]] (host arrays). */
+B200DNN_API int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, const float *row_scale, int32_t n_groups,
+                                           const int32_t *group_rows, const int32_t *group_expert,
+                                           const b200dnn_moe_expert_t *experts, int32_t K, int32_t I, int32_t H,
+                                           int32_t transB, int32_t act, void *out, int64_t ld_out, void *stream);
+/* Weighted reduce with row indices instead of pointers: out[t] = sum_j slot_weights[t,j] * rows[slot_rows[t,j]]. */
+B200DNN_API int32_t b200dnn_moe_weighted_reduce_rows(const void *rows, int64_t ld_rows, const int32_t *slot_rows,
+                                                     const float *slot_weights, int32_t num_tokens, int32_t nslots,
+                                                     int32_t D, int32_t dt, void *out, int64_t ld_out, void *stream);
+
 /* Drops every cached packed weight / staged buffer: the counterpart of the reference's cache
  * clearing between tests (gtests/gtest_utils.cpp:77-118) and clear_fused_moe_scratch()
  * (matmul/group_matmul/group_matmul_direct.hpp:683). */

@@ -111,6 +111,22 @@ int32_t resolve_weight(const void *weight, int wei_format, int64_t K, int64_t N,
 // ------------------------------------------------------------------------------------ quant helpers
 int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, cudaStream_t st) {
   if (rows <= 0) return B200DNN_SUCCESS;
+  // short, aligned, non-grouped rows: one warp per row
+  const int E = src_dt == B200DNN_BF16 ? 8 : 4;
+  const bool aligned = a.n_groups == 0 && a.K % E == 0 && (reinterpret_cast<uintptr_t>(a.src) & 15) == 0 &&
+                       (a.src_ld * (src_dt == B200DNN_BF16 ? 2 : 4)) % 16 == 0 &&
+                       (!a.dst || ((reinterpret_cast<uintptr_t>(a.dst) % E) == 0 && a.dst_ld % E == 0));
+  if (aligned && rows >= 64 && a.K / E <= 32 * 8 && (src_dt == B200DNN_BF16 || src_dt == B200DNN_F32)) {
+    const int nv = (a.K / E + 31) / 32;
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+#define B2_QW(T, NV) quant_per_token_warp_kernel<T, NV><<<grid, 256, 0, st>>>(a, (int)rows)
+    if (src_dt == B200DNN_BF16) { if (nv <= 2) B2_QW(uint16_t, 2); else if (nv <= 4) B2_QW(uint16_t, 4); else if (nv <= 8) B2_QW(uint16_t, 8); else B2_QW(uint16_t, 16); }
+    else { if (nv <= 2) B2_QW(float, 2); else if (nv <= 4) B2_QW(float, 4); else if (nv <= 8) B2_QW(float, 8); else B2_QW(float, 16); }
+#undef B2_QW
+    B2_LAUNCHED();
+    B2_CUDA(cudaGetLastError());
+    return B200DNN_SUCCESS;
+  }
   if (src_dt == B200DNN_BF16) quant_per_token_kernel<uint16_t><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
   else if (src_dt == B200DNN_F32) quant_per_token_kernel<float><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
   else return fail(B200DNN_UNIMPLEMENTED, "per-token quantisation takes f32 or bf16 input");
@@ -173,10 +189,11 @@ int32_t launch_decode(const uint8_t *A, int64_t lda, bool a_unsigned, int M, int
   DecodeGemmArgs g{};
   g.A = A; g.lda = lda; g.M = M; g.N = N; g.K = K; g.Wt = pw.wt; g.Kp = (int)pw.Kp;
   g.groups = (N + 7) / 8; g.blocks = (int)(pw.Kp / 128);
-  g.a_stride = (int)pw.Kp + 64;
+  g.a_stride = (int)pw.Kp + 16;
   g.rows_staged = M > 8 ? 16 : 8;
   const int grid = g.groups < R.sm_count ? g.groups : R.sm_count;
   g.max_local_groups = (g.groups + grid - 1) / grid;
+  g.tune = env_int("B200DNN_DECODE_TUNE", 0);
   const size_t smem = (size_t)g.rows_staged * g.a_stride + (size_t)g.max_local_groups * 512;
   if (M > 16 || smem > 220 * 1024) return B200DNN_UNIMPLEMENTED;
   void (*kern)(DecodeGemmArgs, EpiParams) = a_unsigned ? decode_gemm_kernel<true> : decode_gemm_kernel<false>;

@@ -9,9 +9,9 @@
 //     contiguous range of memory and no other CTA contributes to its outputs, so there is no
 //     cross-CTA reduction and no global scratch.
 //   - Inside the CTA the blocks of those groups are cut into 32 equal contiguous ranges, one per
-//     warp.  Per block a lane issues two 16-byte loads (row g, segments t and 4+t of the 128 bytes);
-//     blocks beyond the first register batch are prefetched into L2 up front, so the latency of
-//     HBM is paid once.  mma.sync.m16n8k32 multiplies the fragments with the 16 activation rows
+//     warp.  Per block a lane issues one 32-byte load (row g, bytes t*32..), so one warp instruction
+//     reads the whole block as eight full 128-byte lines; four blocks are loaded back to back and
+//     then consumed.  mma.sync.m16n8k32 multiplies the fragments with the 16 activation rows
 //     staged once per CTA in shared memory (same K permutation on both operands, see
 //     stream_gemm.cuh).
 //   - A warp's range may cover parts of several groups; partial sums go to a shared-memory s32
@@ -32,15 +32,27 @@ struct DecodeGemmArgs {
   const int8_t *Wt; int Kp;
   int groups;                      // ceil(N / 8)
   int blocks;                      // Kp / 128: 1 KiB blocks per group
-  int a_stride;                    // smem row stride of A: Kp + 64
+  int a_stride;                    // smem row stride of A: Kp + 16 (conflict-free 16-byte reads at row*stride + t*32)
   int rows_staged;                 // 8 or 16
   int max_local_groups;            // ceil(groups / gridDim.x)
+  int tune;                        // 1 = also prefetch the rest of the warp's range into L2 up front (measured slower; off)
 };
 
 constexpr int kDecodeWarps = 32;
 constexpr int kDecodeBatch = 4;    // blocks per register batch: 8 x 16-byte loads per lane
 
 __device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// 32 bytes per lane in one instruction: with lanes (g,t) at row g, bytes t*32.., a warp reads one whole
+// 1 KiB block (eight full 128-byte lines) per load instruction.
+struct W32 { uint4 a, b; };
+__device__ __forceinline__ W32 ldg_stream32(const void *p) {
+  W32 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.a.x), "=r"(v.a.y), "=r"(v.a.z), "=r"(v.a.w), "=r"(v.b.x), "=r"(v.b.y), "=r"(v.b.z), "=r"(v.b.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ W32 w32_zero() { W32 v; v.a = make_uint4(0, 0, 0, 0); v.b = v.a; return v; }
 
 template <bool A_UNSIGNED>
 __global__ void __launch_bounds__(kDecodeWarps * 32, 1) decode_gemm_kernel(DecodeGemmArgs g, EpiParams epi) {
@@ -55,18 +67,14 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 1) decode_gemm_kernel(Decod
   const int item_end = (int)((long long)(warp + 1) * total / kDecodeWarps);
   int32_t *red = reinterpret_cast<int32_t *>(smem + (size_t)g.rows_staged * g.a_stride);   // [local groups][16][8]
 
-  // ---- weights first: register batch + L2 prefetch of the rest of this warp's range
-  const int8_t *wlane = g.Wt + (size_t)g0 * g.Kp * 8 + lg * 128 + lt * 16;   // CTA's span is contiguous: item i at i*1024
-  uint4 w[2 * kDecodeBatch];
+  // ---- weights first: the first register batch is in flight while the activations are staged
+  const int8_t *wlane = g.Wt + (size_t)g0 * g.Kp * 8 + lg * 128 + lt * 32;   // CTA's span is contiguous: item i at i*1024
+  W32 w[kDecodeBatch];
 #pragma unroll
-  for (int u = 0; u < kDecodeBatch; ++u) {
-    const bool on = item + u < item_end;
-    w[2 * u] = on ? ldg_stream(wlane + (size_t)(item + u) * 1024) : make_uint4(0, 0, 0, 0);
-    w[2 * u + 1] = on ? ldg_stream(wlane + (size_t)(item + u) * 1024 + 64) : make_uint4(0, 0, 0, 0);
-  }
+  for (int u = 0; u < kDecodeBatch; ++u) w[u] = (item + u < item_end) ? ldg_stream32(wlane + (size_t)(item + u) * 1024) : w32_zero();
   for (int i = item + kDecodeBatch; i < item_end; ++i) {
     // one 128-byte line per (row, block): lanes with lt == 0 cover the eight rows
-    if (lt == 0) prefetch_l2(wlane + (size_t)i * 1024);
+    if (lt == 0 && (g.tune & 1)) prefetch_l2(wlane + (size_t)i * 1024);
   }
   for (int i = tid; i < (g1 - g0) * 128; i += kDecodeWarps * 32) red[i] = 0;
 
@@ -94,7 +102,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 1) decode_gemm_kernel(Decod
   __syncthreads();
 
   const bool hi_rows = g.rows_staged > 8;
-  const uint8_t *a_lo_base = smem + (size_t)lg * g.a_stride + lt * 16;
+  const uint8_t *a_lo_base = smem + (size_t)lg * g.a_stride + lt * 32;
   const size_t a_hi_off = (size_t)8 * g.a_stride;
 
   int lgrp = item / g.blocks;                 // local group of the current block
@@ -111,26 +119,30 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 1) decode_gemm_kernel(Decod
     }
     acc[0] = acc[1] = acc[2] = acc[3] = 0;
   };
+  // Batches: all loads of a batch are issued back to back and then consumed together.  (A rolling
+  // refill of single registers measured half the bandwidth: the loads of one warp then complete
+  // one after the other instead of overlapping.)
   for (int base = item; base < item_end; base += kDecodeBatch) {
     if (base != item) {
 #pragma unroll
-      for (int u = 0; u < kDecodeBatch; ++u) {
-        const bool on = base + u < item_end;
-        w[2 * u] = on ? ldg_stream(wlane + (size_t)(base + u) * 1024) : make_uint4(0, 0, 0, 0);
-        w[2 * u + 1] = on ? ldg_stream(wlane + (size_t)(base + u) * 1024 + 64) : make_uint4(0, 0, 0, 0);
-      }
+      for (int u = 0; u < kDecodeBatch; ++u) w[u] = (base + u < item_end) ? ldg_stream32(wlane + (size_t)(base + u) * 1024) : w32_zero();
     }
 #pragma unroll
     for (int u = 0; u < kDecodeBatch; ++u) {
       if (base + u < item_end) {
+        const uint4 w0 = w[u].a, w1 = w[u].b;
         const uint8_t *ap = a_lo_base + (size_t)c * 128;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint4 lo = *reinterpret_cast<const uint4 *>(ap + h * 64);
-          const uint4 hi = hi_rows ? *reinterpret_cast<const uint4 *>(ap + h * 64 + a_hi_off) : make_uint4(0, 0, 0, 0);
-          const uint4 wv = w[2 * u + h];
-          mma_m16n8k32<A_UNSIGNED>(acc, lo.x, hi.x, lo.y, hi.y, wv.x, wv.y);
-          mma_m16n8k32<A_UNSIGNED>(acc, lo.z, hi.z, lo.w, hi.w, wv.z, wv.w);
+        {
+          const uint4 lo = *reinterpret_cast<const uint4 *>(ap);
+          const uint4 hi = hi_rows ? *reinterpret_cast<const uint4 *>(ap + a_hi_off) : make_uint4(0, 0, 0, 0);
+          mma_m16n8k32<A_UNSIGNED>(acc, lo.x, hi.x, lo.y, hi.y, w0.x, w0.y);
+          mma_m16n8k32<A_UNSIGNED>(acc, lo.z, hi.z, lo.w, hi.w, w0.z, w0.w);
+        }
+        {
+          const uint4 lo = *reinterpret_cast<const uint4 *>(ap + 16);
+          const uint4 hi = hi_rows ? *reinterpret_cast<const uint4 *>(ap + 16 + a_hi_off) : make_uint4(0, 0, 0, 0);
+          mma_m16n8k32<A_UNSIGNED>(acc, lo.x, hi.x, lo.y, hi.y, w1.x, w1.y);
+          mma_m16n8k32<A_UNSIGNED>(acc, lo.z, hi.z, lo.w, hi.w, w1.z, w1.w);
         }
         if (++c == g.blocks) { flush(lgrp); c = 0; ++lgrp; }
       }

@@ -101,16 +101,24 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
   B2_CHECK(A1 && s1 && Z && zmax && A2 && s2v, B200DNN_FAILURE, "workspace allocation failed");
   B2_CUDA(cudaMemsetAsync(zmax, 0, (size_t)R * 4, st));
 
-  // 1. quantise the gathered rows
-  qa.dst = A1; qa.dst_ld = Kq; qa.scale = s1; qa.scale_dt = B200DNN_F32; qa.K = K;
-  B2_TRY(launch_quant_rows(qa, src_dt, R, st));
+  // 1. quantise the gathered rows (src_dt == s8: the caller hands over rows that are already quantised,
+  //    qa.src = s8 [R, qa.src_ld], qa.scale = their f32 scales -- the expert-parallel path after dispatch)
+  const uint8_t *A1_in = (const uint8_t *)A1; int64_t lda1 = Kq; const float *s1_in = s1;
+  if (src_dt == B200DNN_S8) {
+    B2_CHECK(qa.src && qa.scale && qa.src_ld % 16 == 0 && (reinterpret_cast<uintptr_t>(qa.src) & 15) == 0, B200DNN_FAILURE,
+             "pre-quantised rows must be 16-byte aligned with a row stride that is a multiple of 16");
+    A1_in = (const uint8_t *)qa.src; lda1 = qa.src_ld; s1_in = (const float *)qa.scale;
+  } else {
+    qa.dst = A1; qa.dst_ld = Kq; qa.scale = s1; qa.scale_dt = B200DNN_F32; qa.K = K;
+    B2_TRY(launch_quant_rows(qa, src_dt, R, st));
+  }
 
   // 2. first GEMM with the gated epilogue -> Z (bf16, [R, I]) and per-row max |Z|
   EpiParams e1{};
-  e1.src_scale = s1; e1.src_scale_dt = B200DNN_F32; e1.src_scale_n = R > 1 ? R : 2;  // always per-row
+  e1.src_scale = s1_in; e1.src_scale_dt = B200DNN_F32; e1.src_scale_n = R > 1 ? R : 2;  // always per-row
   e1.wei_scale_dt = B200DNN_F32; e1.wei_scale_n = 2 * I;
   e1.dst = Z; e1.ldc = I; e1.dst_dt = B200DNN_BF16; e1.gated_act = act; e1.gated_I = I; e1.row_absmax = zmax;
-  B2_TRY(grouped_gemm((const uint8_t *)A1, Kq, R, 2 * I, K, p13, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g13_dev,
+  B2_TRY(grouped_gemm(A1_in, lda1, R, 2 * I, K, p13, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g13_dev,
                       m_tiles_bound, e1, st));
 
   // 3. re-quantise the activated rows (from their bf16 values, as the reference does)
@@ -294,5 +302,119 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   B2_CUDA(cudaGetLastError());
   B2_TRY(finish_out({&o_out}, st));
   if (o_out.copy_back) B2_TRY(check_tc_status(st));
+  return B200DNN_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Building blocks of the expert-parallel MoE (token dispatch between GPUs happens outside, over
+// NCCL): stable sort positions of (token,k) slots by an integer key, gather + per-token
+// quantisation into send order, and the expert computation on rows that arrive already quantised.
+namespace {
+__global__ void slot_rows_kernel(const int32_t *keys, const int32_t *rank, const int32_t *off, int n, int32_t *slot_to_row) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) slot_to_row[i] = off[keys[i]] + rank[i];
+}
+}  // namespace
+
+extern "C" int32_t b200dnn_moe_sort_slots(const int32_t *keys, int32_t nslots, int32_t nkeys, int32_t *counts,
+                                          int32_t *slot_to_row, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  Runtime &Rt = rt();
+  Rt.ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(keys && counts && slot_to_row && nslots > 0 && nkeys > 0, B200DNN_FAILURE, "bad argument");
+  const void *k_dev;
+  B2_TRY(stage_in(keys, (size_t)nslots * 4, st, &k_dev));
+  Staged o_cnt, o_s2r;
+  B2_TRY(stage_out(counts, (size_t)nkeys * 4, st, &o_cnt));
+  B2_TRY(stage_out(slot_to_row, (size_t)nslots * 4, st, &o_s2r));
+  int32_t *rank = (int32_t *)Rt.ws.alloc((size_t)nslots * 4);
+  int32_t *off = (int32_t *)Rt.ws.alloc((size_t)(nkeys + 1) * 4);
+  B2_CHECK(rank && off, B200DNN_FAILURE, "workspace allocation failed");
+  expert_rank_kernel<<<(unsigned)nkeys, 1024, 0, st>>>((const int32_t *)k_dev, nslots, rank, (int32_t *)o_cnt.dev);
+  B2_LAUNCHED();
+  expert_offsets_kernel<<<1, 32, 0, st>>>((const int32_t *)o_cnt.dev, nkeys, 0, 0, off);
+  B2_LAUNCHED();
+  slot_rows_kernel<<<(unsigned)((nslots + 255) / 256), 256, 0, st>>>((const int32_t *)k_dev, rank, off, nslots, (int32_t *)o_s2r.dev);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return finish_out({&o_cnt, &o_s2r}, st);
+}
+
+extern "C" int32_t b200dnn_quant_per_token_gather(const void *src, int32_t src_dt, int64_t K, int64_t src_ld,
+                                                  const int32_t *row_src, int32_t row_div, int64_t R, void *dst,
+                                                  int64_t dst_ld, float *scale, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(src && row_src && dst && scale && K > 0 && R > 0 && src_ld >= K && dst_ld >= K && row_div > 0, B200DNN_FAILURE, "bad argument");
+  B2_CHECK(is_device_ptr(src) && is_device_ptr(row_src) && is_device_ptr(dst) && is_device_ptr(scale), B200DNN_UNIMPLEMENTED,
+           "gathered quantisation takes device pointers only");
+  RowQuantArgs a{};
+  a.src = src; a.src_ld = src_ld; a.gather = row_src; a.gather_div = row_div; a.dst = (int8_t *)dst; a.dst_ld = dst_ld;
+  a.scale = scale; a.scale_dt = B200DNN_F32; a.K = (int32_t)K;
+  return launch_quant_rows(a, src_dt, R, st);
+}
+
+extern "C" int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, const float *row_scale, int32_t n_groups,
+                                          const int32_t *group_rows, const int32_t *group_expert,
+                                          const b200dnn_moe_expert_t *experts, int32_t K, int32_t I, int32_t H,
+                                          int32_t transB, int32_t act, void *out, int64_t ld_out, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  Runtime &Rt = rt();
+  Rt.ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(rows_s8 && row_scale && group_rows && group_expert && experts && out && n_groups > 0, B200DNN_FAILURE, "bad argument");
+  B2_CHECK(is_device_ptr(rows_s8) && is_device_ptr(row_scale) && is_device_ptr(out), B200DNN_UNIMPLEMENTED,
+           "the expert-parallel building block takes device buffers only");
+  B2_CHECK(ld_out == H, B200DNN_UNIMPLEMENTED, "output rows must be dense (ld_out == H)");
+  std::vector<int32_t> row_off(n_groups + 1, 0), tile_prefix(n_groups + 1, 0);
+  std::vector<ExpertWeightsIn> ew(n_groups);
+  for (int g = 0; g < n_groups; ++g) {
+    B2_CHECK(group_rows[g] >= 0 && group_expert[g] >= 0, B200DNN_FAILURE, "group %d: negative row count or expert id", g);
+    row_off[g + 1] = row_off[g] + group_rows[g];
+    tile_prefix[g + 1] = tile_prefix[g] + (group_rows[g] + kTcBM - 1) / kTcBM;
+    const b200dnn_moe_expert_t &e = experts[group_expert[g]];
+    ew[g] = ExpertWeightsIn{e.w13, e.ldb13, e.w13_scale, e.w2, e.ldb2, e.w2_scale};
+  }
+  const int R = row_off[n_groups];
+  if (R == 0) return B200DNN_SUCCESS;
+  std::vector<int32_t> blob(2 * (n_groups + 1));
+  memcpy(blob.data(), row_off.data(), sizeof(int32_t) * (n_groups + 1));
+  memcpy(blob.data() + n_groups + 1, tile_prefix.data(), sizeof(int32_t) * (n_groups + 1));
+  void *bd;
+  B2_TRY(upload_blob(blob.data(), blob.size() * 4, st, &bd));
+  const int32_t *row_off_dev = (const int32_t *)bd, *tile_prefix_dev = row_off_dev + n_groups + 1;
+  RowQuantArgs qa{};
+  qa.src = rows_s8; qa.src_ld = lda; qa.scale = const_cast<float *>(row_scale);
+  void *O = nullptr; int64_t ldO = 0;
+  // O is produced in workspace and copied out: moe_core owns the layout of its result
+  B2_TRY(moe_core(n_groups, ew, K, I, H, transB, act, 1, qa, B200DNN_S8, R, row_off_dev, tile_prefix_dev, tile_prefix[n_groups],
+                  nullptr, nullptr, &O, &ldO, st));
+  B2_CUDA(cudaMemcpyAsync(out, O, (size_t)R * H * 2, cudaMemcpyDeviceToDevice, st));
+  return B200DNN_SUCCESS;
+}
+
+extern "C" int32_t b200dnn_moe_weighted_reduce_rows(const void *rows, int64_t ld_rows, const int32_t *slot_rows,
+                                                    const float *slot_weights, int32_t num_tokens, int32_t nslots, int32_t D,
+                                                    int32_t dt, void *out, int64_t ld_out, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(rows && slot_rows && slot_weights && out && num_tokens > 0 && nslots > 0 && D > 0 && ld_rows >= D && ld_out >= D,
+           B200DNN_FAILURE, "bad argument");
+  B2_CHECK(dt == B200DNN_BF16 || dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "weighted reduce on f32 or bf16 only");
+  B2_CHECK(is_device_ptr(rows) && is_device_ptr(slot_rows) && is_device_ptr(slot_weights) && is_device_ptr(out), B200DNN_UNIMPLEMENTED,
+           "device pointers only");
+  ReduceArgs ra{};
+  ra.base = rows; ra.ld = ld_rows; ra.slot_rows = slot_rows; ra.w = slot_weights; ra.nslots = nslots; ra.D = D; ra.dt = dt;
+  ra.out = out; ra.ld_out = ld_out;
+  moe_reduce_kernel<<<(unsigned)num_tokens, 256, (sizeof(void *) + 4) * nslots, st>>>(ra);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
   return B200DNN_SUCCESS;
 }

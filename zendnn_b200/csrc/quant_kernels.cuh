@@ -145,6 +145,58 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
   }
 }
 
+// One warp per row, for short rows (K <= 32 * NV * elements-per-16-bytes): the row lives in the
+// lanes' registers, the abs-max is a shuffle reduction, no shared memory and no CTA barrier.
+// Requires 16-byte aligned rows and K a multiple of the vector width (the launcher checks).
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs a, int rows) {
+  constexpr int E = VecTraits<T>::kPer16B;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  int64_t sr = r;
+  if (a.gather) { int32_t s = a.gather[r]; if (s < 0) return; sr = s / a.gather_div; }
+  const T *src = reinterpret_cast<const T *>(a.src) + sr * a.src_ld;
+  int8_t *dst = a.dst ? a.dst + (int64_t)r * a.dst_ld : nullptr;
+  const int nvec = a.K / E;
+  uint4 cache[NV];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int v = lane + j * 32;
+    if (v < nvec) {
+      cache[j] = reinterpret_cast<const uint4 *>(src)[v];
+      const T *e = reinterpret_cast<const T *>(&cache[j]);
+#pragma unroll
+      for (int i = 0; i < E; ++i) { float f = elem_to_f32<T>(e[i]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f)); }
+    }
+  }
+  float scale;
+  if (a.absmax_bits) scale = scale_from_absmax(__uint_as_float(a.absmax_bits[r]));
+  else {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    scale = scale_from_absmax(amax);
+  }
+  if (lane == 0 && a.scale) {
+    if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(a.scale)[r] = f32_to_bf16_bits(scale);
+    else reinterpret_cast<float *>(a.scale)[r] = scale;
+  }
+  if (!dst) return;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int v = lane + j * 32;
+    if (v < nvec) {
+      const T *e = reinterpret_cast<const T *>(&cache[j]);
+      int8_t o[E];
+#pragma unroll
+      for (int i = 0; i < E; ++i) o[i] = quant_sym(elem_to_f32<T>(e[i]), scale);
+      if (E == 8) reinterpret_cast<uint2 *>(dst)[v] = *reinterpret_cast<uint2 *>(o);
+      else reinterpret_cast<uint32_t *>(dst)[v] = *reinterpret_cast<uint32_t *>(o);
+    }
+  }
+}
+
 // ---- per-channel / per-tensor dynamic scales over a [M,N] matrix -----------------------------
 // pass 1: abs-max per column (or one for the tensor) with atomicMax on the float bit pattern
 // (non-negative floats order like unsigned integers); out must be zeroed first.

@@ -330,10 +330,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const TileCoord t = tc_tile(a, tile, m_tiles);
       // the decision to go on must be the same in all epilogue warps (they meet at a named barrier):
       // it depends only on this wait, which either completes for all of them or expires for all
-      bool ok = mbar_wait(tfull_bar(acc), acc_phase);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
-      tc_fence_after();
+      // Operands that do not depend on the accumulator are fetched first, so that their latency
+      // overlaps the wait for the MMAs of this tile.
       const int m_local = t.m_local0 + row_in_tile;
       const int m_global = t.row0 + row_in_tile;
       const bool row_ok = row_in_tile < t.rows;
@@ -345,29 +343,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (gd.dst) { cx.dst = gd.dst; cx.ldc = gd.ldc; m_dst = m_local; }   // else: shared dst, global row index
       }
       const int pc_tile = t.nt * a.BN;
-      // stage this tile's column operands (f32 / s32) once
+      float col_w = 1.0f, col_b = 0.0f; int32_t col_k = 0;
       if (etid < a.BN) {
         const int pc = pc_tile + etid;
-        float w = 1.0f, b = 0.0f; int32_t k = 0;
         if (pc < a.N) {
           const int n = (int)packed_to_logical(pc, a.gated, epi.gated_I);
-          if (epi.wei_scale_n) w = load_as_f32(cx.wei_scale, epi.wei_scale_dt, epi.wei_scale_n > 1 ? n : 0);
-          if (cx.bias) b = load_as_f32(cx.bias, epi.bias_dt, n);
-          if (zp) k = zp * cx.colsum[pc];
+          if (epi.wei_scale_n) col_w = load_as_f32(cx.wei_scale, epi.wei_scale_dt, epi.wei_scale_n > 1 ? n : 0);
+          if (cx.bias) col_b = load_as_f32(cx.bias, epi.bias_dt, n);
+          if (zp) col_k = zp * cx.colsum[pc];
         }
-        cols.ws[etid] = w; cols.bias[etid] = b; cols.comp[etid] = k;
       }
+      bool ok = mbar_wait(tfull_bar(acc), acc_phase);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
+      tc_fence_after();
+      // stage this tile's column operands (f32 / s32) once (the previous tile's readers left at its closing barrier)
+      if (etid < a.BN) { cols.ws[etid] = col_w; cols.bias[etid] = col_b; cols.comp[etid] = col_k; }
       asm volatile("bar.sync 1, %0;" ::"n"(32 * kTcEpiWarps) : "memory");
       const bool has_bias = cx.bias != nullptr;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * a.BN);
       if (!a.gated) {
-        for (int c = half; c < a.BN / 32; c += 2) {
+        // this warp's chunks: a contiguous half of the tile's 32-column chunks that lie inside N;
+        // the accumulator of chunk c+1 is read from tensor memory while chunk c is being processed
+        const int nc = min(a.BN / 32, (a.N - pc_tile + 31) / 32);
+        const int per = (a.BN / 32 + 1) / 2;
+        const int cb = half * per, ce = min(nc, cb + per);
+        auto process = [&](const uint32_t (&r)[32], int c) {
+          if (!row_ok) return;
           const int pc0 = pc_tile + c * 32;
-          if (pc0 >= a.N) break;           // warp-uniform
-          uint32_t r[32];
-          tc_ld32(taddr0 + (uint32_t)(c * 32), r);
-          tc_wait_ld();
-          if (!row_ok) continue;
           switch (a.fast_act) {
           case FA_NONE: tc_epi_chunk<FA_NONE>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
           case FA_RELU: tc_epi_chunk<FA_RELU>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
@@ -378,6 +381,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           case FA_TANH: tc_epi_chunk<FA_TANH>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
           default: tc_epi_chunk<FA_GENERIC>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
           }
+        };
+        uint32_t ra[32], rb[32];
+        if (cb < ce) tc_ld32(taddr0 + (uint32_t)(cb * 32), ra);
+        for (int c = cb; c < ce; c += 2) {
+          tc_wait_ld();
+          if (c + 1 < ce) tc_ld32(taddr0 + (uint32_t)((c + 1) * 32), rb);
+          process(ra, c);
+          if (c + 1 >= ce) break;
+          tc_wait_ld();
+          if (c + 2 < ce) tc_ld32(taddr0 + (uint32_t)((c + 2) * 32), ra);
+          process(rb, c + 1);
         }
       } else {
         // gated: packed columns [g(32) u(32)] -> 32 outputs; dst is [rows, I] bf16
