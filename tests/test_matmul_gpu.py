@@ -213,3 +213,25 @@ def test_contract_violations(capi):
     d = mk(src_scale=np.ones(4, dtype=np.float32), wei_scale=np.ones(16, dtype=np.float32), src_zp=np.array([3], dtype=np.int32))
     assert capi.matmul(d) == capi.FAILURE
     assert "zero-point" in capi.last_error()
+
+
+def test_pinned_host_buffers(capi, oracle):
+    """Pinned host operands: inputs are copied in, a small result is written straight into the pinned buffer."""
+    import torch
+    c = decode_case(oracle, 4, 1024, 512, seed=21)
+    A = torch.from_numpy(c["A"]).pin_memory()
+    sa, sw = torch.from_numpy(c["sa"]).pin_memory(), torch.from_numpy(c["sw"]).pin_memory()
+    out = torch.zeros(4, 512, dtype=torch.bfloat16).pin_memory()
+    d = capi.make_matmul(4, 512, 1024, A, c["W"], out, src_dt=capi.DT["s8"], dst_dt=capi.DT["bf16"], src_scale=sa, wei_scale=sw)
+    assert capi.matmul(d) == capi.SUCCESS, capi.last_error()      # synchronous for host buffers: result is there on return
+    ref = oracle.matmul_w8a8(c["A"], c["W"], "bf16", src_scale=c["sa"], wei_scale=c["sw"])
+    assert (out.view(torch.int16).numpy().view(np.uint16) == ref).all()
+    # a large pinned result takes the device-twin path
+    M, K, N = 640, 256, 1024
+    rng = np.random.default_rng(3)
+    A2 = rng.integers(-128, 128, (M, K), dtype=np.int8); W2 = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    out2 = torch.zeros(M, N, dtype=torch.int32).pin_memory()
+    d = capi.make_matmul(M, N, K, A2, W2, out2, src_dt=capi.DT["s8"], dst_dt=capi.DT["s32"], weights_const=False)
+    assert capi.matmul(d) == capi.SUCCESS, capi.last_error()
+    assert (out2.numpy() == oracle.gemm_s32(A2, W2)).all()
+    capi.lib.b200dnn_clear_caches()

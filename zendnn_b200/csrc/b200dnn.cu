@@ -314,7 +314,7 @@ int32_t b200dnn_prepack(const void *weight, int64_t K, int64_t N, int64_t ldb, i
   B2_TRY(stage_out(dst, pack_bytes(K, N), st, &out));
   PackedWeight pw;
   B2_TRY(pack_into(w_dev, K, N, ldb, transB, gated, out.dev, st, &pw));
-  if (!out.copy_back) rt().packed_registry[dst] = pw;
+  if (!out.copy_back && !out.sync) rt().packed_registry[dst] = pw;
   else rt().host_packed.erase(dst);
   return finish_out({&out}, st);
 }
@@ -385,7 +385,7 @@ int32_t b200dnn_group_quant_per_token(int32_t num_groups, const void *const *src
   a.row_off = (const int32_t *)(tab + 3 * tb + 2 * sizeof(int64_t) * num_groups);
   B2_TRY(launch_quant_rows(a, src_dt, row_off[num_groups], st));
   bool any = false;
-  for (auto &s : outs) if (s.copy_back) { B2_CUDA(cudaMemcpyAsync(s.host, s.dev, s.bytes, cudaMemcpyDeviceToHost, st)); any = true; }
+  for (auto &s : outs) { if (s.copy_back) { B2_CUDA(cudaMemcpyAsync(s.host, s.dev, s.bytes, cudaMemcpyDeviceToHost, st)); any = true; } else if (s.sync) any = true; }
   if (any) B2_CUDA(cudaStreamSynchronize(st));
   return B200DNN_SUCCESS;
 }
@@ -648,7 +648,7 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   const void *src_dev = nullptr;
   B2_TRY(stage_in(d->src, span_bytes(M, K, d->lda, d->src_dt), st, &src_dev));
   const uint8_t *A = (const uint8_t *)src_dev; int64_t lda = d->lda; bool a_unsigned = d->src_dt == B200DNN_U8;
-  Staged o_scale; o_scale.copy_back = false;
+  Staged o_scale;
   if (dyn) {
     const int64_t Kq = round_up(K, 16);
     int8_t *q = (int8_t *)R.ws.alloc((size_t)M * Kq);
@@ -713,7 +713,7 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
     ta.n_groups = 1; ta.m_tiles_plain = (M + kTcBM - 1) / kTcBM;
     B2_TRY(launch_tc(A, lda, a_unsigned, M, N, K, pw, ta, epi, ta.m_tiles_plain, st));
   }
-  const bool sync_path = o_dst.copy_back || o_scale.copy_back;
+  const bool sync_path = o_dst.copy_back || o_scale.copy_back || o_dst.sync || o_scale.sync;
   B2_TRY(finish_out({&o_dst, &o_scale}, st));
   if (which == 2 && sync_path) B2_TRY(check_tc_status(st));
   return B200DNN_SUCCESS;

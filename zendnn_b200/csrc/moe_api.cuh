@@ -241,7 +241,8 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
     B2_LAUNCHED();
     B2_CUDA(cudaGetLastError());
   }
-  bool any = o_out.copy_back;
+  bool any = o_out.copy_back || o_out.sync;
+  for (auto &s : outs) if (s.sync) any = true;
   for (auto &s : outs) if (s.copy_back) { B2_CUDA(cudaMemcpyAsync(s.host, s.dev, s.bytes, cudaMemcpyDeviceToHost, st)); any = true; }
   if (o_out.copy_back) B2_CUDA(cudaMemcpyAsync(o_out.host, o_out.dev, o_out.bytes, cudaMemcpyDeviceToHost, st));
   if (any) { B2_CUDA(cudaStreamSynchronize(st)); B2_TRY(check_tc_status(st)); }
@@ -301,7 +302,7 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
   B2_TRY(finish_out({&o_out}, st));
-  if (o_out.copy_back) B2_TRY(check_tc_status(st));
+  if (o_out.copy_back || o_out.sync) B2_TRY(check_tc_status(st));
   return B200DNN_SUCCESS;
 }
 

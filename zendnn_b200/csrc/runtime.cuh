@@ -149,6 +149,7 @@ inline int32_t make_map_wt(CUtensorMap *m, const void *wt, uint64_t Kp, uint64_t
 // One host-or-device buffer made visible on the device for the duration of a call.
 struct Staged {
   void *dev = nullptr; void *host = nullptr; size_t bytes = 0; bool copy_back = false;
+  bool sync = false;   // written in place in pinned host memory: the stream must be drained before returning
 };
 inline int32_t stage_in(const void *p, size_t bytes, cudaStream_t st, const void **out) {
   if (!p || bytes == 0) { *out = p; return B200DNN_SUCCESS; }
@@ -162,8 +163,17 @@ inline int32_t stage_in(const void *p, size_t bytes, cudaStream_t st, const void
 // Output buffer: device pointer is used as is; a host pointer gets a workspace twin that finish() copies back.
 // preload: the kernel updates the buffer (in-place ops) so its current contents are needed too.
 inline int32_t stage_out(void *p, size_t bytes, cudaStream_t st, Staged *s, bool preload = false) {
-  s->host = nullptr; s->dev = p; s->bytes = bytes; s->copy_back = false;
-  if (!p || bytes == 0 || is_device_ptr(p)) return B200DNN_SUCCESS;
+  s->host = nullptr; s->dev = p; s->bytes = bytes; s->copy_back = false; s->sync = false;
+  if (!p || bytes == 0) return B200DNN_SUCCESS;
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); at.type = cudaMemoryTypeUnregistered; }
+  if (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) return B200DNN_SUCCESS;
+  // Small results go straight into pinned host memory from the kernel's own stores (each element crosses the
+  // bus once, no separate copy is enqueued); larger ones, and pageable memory, use a device twin and one copy.
+  if (at.type == cudaMemoryTypeHost && at.devicePointer && bytes <= (size_t(1) << 20) && !preload) {
+    s->host = p; s->dev = at.devicePointer; s->sync = true;
+    return B200DNN_SUCCESS;
+  }
   void *d = rt().ws.alloc(bytes);
   B2_CHECK(d, B200DNN_FAILURE, "workspace allocation of %zu bytes failed", bytes);
   if (preload) B2_CUDA(cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, st));
@@ -174,6 +184,7 @@ inline int32_t finish_out(std::initializer_list<Staged *> outs, cudaStream_t st)
   bool any = false;
   for (Staged *s : outs)
     if (s->copy_back) { B2_CUDA(cudaMemcpyAsync(s->host, s->dev, s->bytes, cudaMemcpyDeviceToHost, st)); any = true; }
+    else if (s->sync) any = true;
   if (any) B2_CUDA(cudaStreamSynchronize(st));
   return B200DNN_SUCCESS;
 }
