@@ -10,6 +10,13 @@ from helpers import assert_bf16_close
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(scope="module")
+def capi():
+    from zendnn_b200 import capi as c
+    assert c.lib.b200dnn_device_count() > 0
+    return c
+
+
 def _torch():
     import torch
     return torch

@@ -235,3 +235,25 @@ def test_pinned_host_buffers(capi, oracle):
     assert capi.matmul(d) == capi.SUCCESS, capi.last_error()
     assert (out2.numpy() == oracle.gemm_s32(A2, W2)).all()
     capi.lib.b200dnn_clear_caches()
+
+
+@pytest.mark.parametrize("form", ["1", "2", "3", "5"])
+@pytest.mark.parametrize("shape", [(1, 64, 16), (2, 1000, 72), (3, 4096, 1184), (8, 300, 2368), (9, 2048, 4744), (16, 4224, 1000)])
+def test_decode_kernel_forms(capi, oracle, monkeypatch, form, shape):
+    """Both decode kernels (register-batch form, bulk-copy ring with 2..5 groups per stage) over all M <= 16,
+    ragged K and N, u8 + zero point and s8 + per-token scale."""
+    monkeypatch.setenv("B200DNN_DECODE_KERNEL", form)
+    M, K, N = shape
+    rng = np.random.default_rng(M * 7 + N)
+    W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    got = run(capi, M, N, K, A, W, "s32", weights_const=False, force_kernel=STREAM, src_zp=np.array([128], dtype=np.int32))
+    assert (got == oracle.epilogue(oracle.gemm_s32(A, W), "s32", src_zp=128, col_sum=oracle.colsum(W))).all()
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    sw = rng.uniform(1e-4, 5e-4, N).astype(np.float32)
+    bias = rng.normal(size=N).astype(np.float32)
+    got = run(capi, M, N, K, A, W, "bf16", weights_const=False, force_kernel=STREAM, src_scale=sa, wei_scale=sw, bias=bias,
+              postops=["relu"])
+    ref = oracle.matmul_w8a8(A, W, "bf16", src_scale=sa, wei_scale=sw, bias=bias, postops=["relu"])
+    assert (got == ref).all()

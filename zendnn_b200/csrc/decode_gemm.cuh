@@ -22,6 +22,7 @@
 // previous kernel on the stream; activations are read and outputs written only after the wait.
 #pragma once
 #include "common.cuh"
+#include "decode_epi.cuh"
 #include "stream_gemm.cuh"
 
 namespace b200 {
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 1) decode_gemm_kernel(Decod
   int item = (int)((long long)warp * total / kDecodeWarps);
   const int item_end = (int)((long long)(warp + 1) * total / kDecodeWarps);
   int32_t *red = reinterpret_cast<int32_t *>(smem + (size_t)g.rows_staged * g.a_stride);   // [local groups][16][8]
+  const DecodeEpiSmem es = decode_epi_carve(smem + (size_t)g.rows_staged * g.a_stride + (size_t)g.max_local_groups * 512, g.max_local_groups);
 
   // ---- weights first: the first register batch is in flight while the activations are staged
   const int8_t *wlane = g.Wt + (size_t)g0 * g.Kp * 8 + lg * 128 + lt * 32;   // CTA's span is contiguous: item i at i*1024
@@ -98,6 +100,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 1) decode_gemm_kernel(Decod
       }
       *reinterpret_cast<uint4 *>(smem + (size_t)r * g.a_stride + k) = v;
     }
+    decode_epi_stage(epi, es, g0 * 8, (g1 - g0) * 8, g.N, g.M, tid, kDecodeWarps * 32);
   }
   __syncthreads();
 
@@ -151,22 +154,7 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 1) decode_gemm_kernel(Decod
   if (c != 0 && item < item_end) flush(lgrp);
   __syncthreads();
 
-  // ---- epilogue for the CTA's outputs: red[local group][row][column of the group]
-  const int32_t zp = load_zp(epi);
-  for (int i = tid; i < (g1 - g0) * 128; i += kDecodeWarps * 32) {
-    const int gl = i >> 7, m = (i >> 3) & 15, n = (g0 + gl) * 8 + (i & 7);
-    if (m >= g.M || n >= g.N) continue;
-    int32_t v = red[i];
-    if (epi.dst_dt == DT_S32) {
-      if (zp != 0) v -= zp * epi.colsum[n];
-      reinterpret_cast<int32_t *>(epi.dst)[(size_t)m * epi.ldc + n] = v;
-      continue;
-    }
-    const EpiCtx cx = epi_ctx(epi, m);
-    const float x = epi_finish(epi, cx, epi_dequant(epi, cx, v, zp, n, n), m, n);
-    if (epi.dst_dt == DT_BF16) reinterpret_cast<uint16_t *>(epi.dst)[(size_t)m * epi.ldc + n] = f32_to_bf16_bits(x);
-    else reinterpret_cast<float *>(epi.dst)[(size_t)m * epi.ldc + n] = x;
-  }
+  decode_epilogue(epi, es, red, g0, g1 - g0, g.M, g.N, tid, kDecodeWarps * 32);
 }
 
 }  // namespace b200

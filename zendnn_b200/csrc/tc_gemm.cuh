@@ -23,6 +23,7 @@
 #pragma once
 #include <cuda.h>
 #include "common.cuh"
+#include "mbar.cuh"
 #include "pack_kernels.cuh"
 
 namespace b200 {
@@ -32,7 +33,6 @@ constexpr int kTcBK = 128;               // bytes of K per stage row (one 128-by
 constexpr int kTcEpiWarps = 8;
 constexpr int kTcThreads = 64 + 32 * kTcEpiWarps;   // producer warp + MMA warp + epilogue warps
 constexpr int kTcSmemBudget = 200 * 1024; // stage ring
-constexpr long long kTcWaitCycles = 2000000000LL;  // ~1 s
 
 struct TcGroupDesc {   // per expert, device memory (grouped form with caller-owned outputs)
   const void *wei_scale;
@@ -61,32 +61,6 @@ struct TcGemmArgs {
 };
 
 // ---------------------------------------------------------------------------------------- PTX
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok;
-}
-// bounded wait; false on expiry
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i) if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > kTcWaitCycles) return false;
-  }
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
