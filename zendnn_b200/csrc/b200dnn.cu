@@ -287,6 +287,11 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
   B2_CHECK(args.BN % 32 == 0 && args.BN >= 32 && args.BN <= 256 && (!pw0.gated || args.BN % 64 == 0), B200DNN_FAILURE,
            "bad tile width %d", args.BN);
   args.n_tiles = (N + args.BN - 1) / args.BN;
+  // Tile order.  Sweeping the row tiles under one column tile keeps that weight slice hot and re-reads the
+  // activations once per column tile: right while the activations fit in L2.  Past that (many rows, as in a
+  // fine-grained MoE) the column tiles of one row tile run together instead: activations are read once and
+  // the (small) weight of the group is re-read from L2.
+  args.n_fastest = env_int("B200DNN_TC_ORDER", (long long)M_total * K > (48ll << 20) ? 1 : 0);
   const int stage_bytes = kTcBM * kTcBK + args.BN * kTcBK;
   int stages = kTcSmemBudget / stage_bytes;
   if (stages > 8) stages = 8;
@@ -575,6 +580,39 @@ int32_t b200dnn_moe_weighted_reduce(const void *const *row_ptrs, const float *to
   return finish_out({&o}, st);
 }
 
+}  // extern "C"
+
+// Router and stable-rank launches: the fast forms when the sizes allow, the general kernels otherwise.
+int32_t launch_route_topk(const float *logits, int T, int E, int topk, int renorm, int32_t *ids, float *w, cudaStream_t st) {
+  const unsigned blocks = (unsigned)(((size_t)T * 32 + 255) / 256);
+  if (E <= 32) route_topk_warp_kernel<1><<<blocks, 256, 0, st>>>(logits, T, E, topk, renorm, ids, w);
+  else if (E <= 64) route_topk_warp_kernel<2><<<blocks, 256, 0, st>>>(logits, T, E, topk, renorm, ids, w);
+  else if (E <= 128) route_topk_warp_kernel<4><<<blocks, 256, 0, st>>>(logits, T, E, topk, renorm, ids, w);
+  else if (E <= 256) route_topk_warp_kernel<8><<<blocks, 256, 0, st>>>(logits, T, E, topk, renorm, ids, w);
+  else route_topk_kernel<<<(unsigned)((T + 127) / 128), 128, 0, st>>>(logits, T, E, topk, renorm, ids, w);
+  B2_LAUNCHED();
+  return B200DNN_SUCCESS;
+}
+int32_t launch_expert_rank(const int32_t *ids, int nslots, int nkeys, int32_t *rank, int32_t *counts, cudaStream_t st) {
+  const int nchunks = (nslots + kRankChunk - 1) / kRankChunk;
+  if (nkeys > kRankMaxKeys || nchunks < 4) {
+    expert_rank_kernel<<<(unsigned)nkeys, 1024, 0, st>>>(ids, nslots, rank, counts);
+    B2_LAUNCHED();
+    return B200DNN_SUCCESS;
+  }
+  int32_t *cc = (int32_t *)rt().ws.alloc((size_t)nchunks * nkeys * 4);
+  B2_CHECK(cc, B200DNN_FAILURE, "workspace allocation failed");
+  rank_count_kernel<<<(unsigned)nchunks, kRankChunk, 0, st>>>(ids, nslots, nkeys, cc);
+  B2_LAUNCHED();
+  rank_scan_kernel<<<(unsigned)((nkeys * 32 + 255) / 256), 256, 0, st>>>(cc, nchunks, nkeys, counts);
+  B2_LAUNCHED();
+  rank_assign_kernel<<<(unsigned)nchunks, kRankChunk, (size_t)32 * nkeys * 4, st>>>(ids, nslots, nkeys, cc, rank);
+  B2_LAUNCHED();
+  return B200DNN_SUCCESS;
+}
+
+extern "C" {
+
 int32_t b200dnn_moe_route(const float *logits, int32_t T, int32_t E, int32_t topk, int32_t renorm, int32_t *ids,
                           float *weights, int32_t *expert_counts, int32_t *slot_to_row, void *stream) {
   std::lock_guard<std::mutex> lk(rt().mu);
@@ -592,16 +630,14 @@ int32_t b200dnn_moe_route(const float *logits, int32_t T, int32_t E, int32_t top
   B2_TRY(stage_out(slot_to_row, ns * 4, st, &o_s2r));
   float *w_dev = (float *)o_w.dev;
   if (!w_dev) { w_dev = (float *)rt().ws.alloc(ns * 4); B2_CHECK(w_dev, B200DNN_FAILURE, "workspace allocation failed"); }
-  route_topk_kernel<<<(unsigned)((T + 127) / 128), 128, 0, st>>>((const float *)l_dev, T, E, topk, renorm, (int32_t *)o_ids.dev, w_dev);
-  B2_LAUNCHED();
+  B2_TRY(launch_route_topk((const float *)l_dev, T, E, topk, renorm, (int32_t *)o_ids.dev, w_dev, st));
   if (expert_counts || slot_to_row) {
     int32_t *cnt = (int32_t *)o_cnt.dev;
     if (!cnt) { cnt = (int32_t *)rt().ws.alloc((size_t)E * 4); B2_CHECK(cnt, B200DNN_FAILURE, "workspace allocation failed"); }
     int32_t *rank = (int32_t *)rt().ws.alloc(ns * 4);
     int32_t *off = (int32_t *)rt().ws.alloc((size_t)(E + 1) * 4);
     B2_CHECK(rank && off, B200DNN_FAILURE, "workspace allocation failed");
-    expert_rank_kernel<<<(unsigned)E, 1024, 0, st>>>((const int32_t *)o_ids.dev, (int)ns, rank, cnt);
-    B2_LAUNCHED();
+    B2_TRY(launch_expert_rank((const int32_t *)o_ids.dev, (int)ns, E, rank, cnt, st));
     if (slot_to_row) {
       expert_offsets_kernel<<<1, 32, 0, st>>>(cnt, E, 0, T, off);
       B2_LAUNCHED();

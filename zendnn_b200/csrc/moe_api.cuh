@@ -273,10 +273,8 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   float *slot_w = (float *)Rt.ws.alloc((size_t)R * 4);
   int32_t *row_token = (int32_t *)Rt.ws.alloc((size_t)R * 4);
   B2_CHECK(ids && w && rank && cnt && row_off && tile_prefix && slot_rows && slot_w && row_token, B200DNN_FAILURE, "workspace allocation failed");
-  route_topk_kernel<<<(unsigned)((T + 127) / 128), 128, 0, st>>>((const float *)l_dev, T, E, topk, 1, ids, w);
-  B2_LAUNCHED();
-  expert_rank_kernel<<<(unsigned)E, 1024, 0, st>>>(ids, T * topk, rank, cnt);
-  B2_LAUNCHED();
+  B2_TRY(launch_route_topk((const float *)l_dev, T, E, topk, 1, ids, w, st));
+  B2_TRY(launch_expert_rank(ids, T * topk, E, rank, cnt, st));
   expert_offsets_kernel<<<1, 32, 0, st>>>(cnt, E, S, T, row_off);
   B2_LAUNCHED();
   tile_prefix_kernel<<<1, 32, 0, st>>>(row_off, G, tile_prefix);
@@ -333,8 +331,7 @@ extern "C" int32_t b200dnn_moe_sort_slots(const int32_t *keys, int32_t nslots, i
   int32_t *rank = (int32_t *)Rt.ws.alloc((size_t)nslots * 4);
   int32_t *off = (int32_t *)Rt.ws.alloc((size_t)(nkeys + 1) * 4);
   B2_CHECK(rank && off, B200DNN_FAILURE, "workspace allocation failed");
-  expert_rank_kernel<<<(unsigned)nkeys, 1024, 0, st>>>((const int32_t *)k_dev, nslots, rank, (int32_t *)o_cnt.dev);
-  B2_LAUNCHED();
+  B2_TRY(launch_expert_rank((const int32_t *)k_dev, nslots, nkeys, rank, (int32_t *)o_cnt.dev, st));
   expert_offsets_kernel<<<1, 32, 0, st>>>((const int32_t *)o_cnt.dev, nkeys, 0, 0, off);
   B2_LAUNCHED();
   slot_rows_kernel<<<(unsigned)((nslots + 255) / 256), 256, 0, st>>>((const int32_t *)k_dev, rank, off, nslots, (int32_t *)o_s2r.dev);

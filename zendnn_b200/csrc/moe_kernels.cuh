@@ -161,6 +161,103 @@ __global__ void __launch_bounds__(1024) expert_rank_kernel(const int32_t *ids, i
   if (threadIdx.x == 0) counts[e] = running;
 }
 
+// Warp-per-token form of route_topk_kernel for E <= 32*PER: every probability is computed once, the sum runs
+// in expert order (lane e%32 holds expert e), the k selections are warp arg-max reductions with ties to the
+// lower expert id.  Same results as route_topk_kernel bit for bit.
+template <int PER>
+__global__ void __launch_bounds__(256) route_topk_warp_kernel(const float *logits, int T, int E, int k, int renorm, int32_t *ids, float *w) {
+  const int t = (int)((blockIdx.x * (unsigned)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const float *l = logits + (int64_t)t * E;
+  const float ninf = __int_as_float(0xff800000);
+  float v[PER], mx = ninf;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) { const int e = j * 32 + lane; v[j] = e < E ? l[e] : ninf; mx = fmaxf(mx, v[j]); }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+#pragma unroll
+  for (int j = 0; j < PER; ++j) v[j] = (j * 32 + lane < E) ? expf(__fadd_rn(v[j], -mx)) : 0.f;
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    if (j * 32 < E) {
+      const int n = min(32, E - j * 32);
+      for (int src = 0; src < n; ++src) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, v[j], src));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) v[j] = (j * 32 + lane < E) ? __fdiv_rn(v[j], sum) : -2.f;
+  float my_p = 0.f, tot = 0.f; int my_id = 0;
+  for (int jj = 0; jj < k; ++jj) {
+    float bp = -3.f; int be = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) if (v[j] > bp) { bp = v[j]; be = j * 32 + lane; }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float op = __shfl_xor_sync(0xffffffffu, bp, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (op > bp || (op == bp && oe < be)) { bp = op; be = oe; }
+    }
+#pragma unroll
+    for (int j = 0; j < PER; ++j) if (be == j * 32 + lane) v[j] = -1.f;     // taken
+    if (lane == jj) { my_p = bp; my_id = be; }
+    tot = __fadd_rn(tot, bp);
+  }
+  if (lane < k) {
+    ids[(int64_t)t * k + lane] = my_id;
+    if (w) w[(int64_t)t * k + lane] = renorm ? __fdiv_rn(my_p, tot) : my_p;
+  }
+}
+
+// Stable rank of every slot inside its key, in three passes over chunks of 1024 slots (keys <= kRankMaxKeys):
+// per-chunk histograms, a scan over chunks per key, and the in-chunk stable rank.  Same output as expert_rank_kernel.
+constexpr int kRankChunk = 1024;
+constexpr int kRankMaxKeys = 256;
+__global__ void __launch_bounds__(kRankChunk) rank_count_kernel(const int32_t *ids, int nslots, int nkeys, int32_t *chunk_counts) {
+  __shared__ int hist[kRankMaxKeys];
+  for (int i = threadIdx.x; i < nkeys; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  const int s = blockIdx.x * kRankChunk + threadIdx.x;
+  if (s < nslots) { const int key = ids[s]; if ((unsigned)key < (unsigned)nkeys) atomicAdd(&hist[key], 1); }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nkeys; i += blockDim.x) chunk_counts[(size_t)blockIdx.x * nkeys + i] = hist[i];
+}
+// one warp per key: exclusive scan of that key's counts over the chunks (in place), total to counts[key]
+__global__ void __launch_bounds__(256) rank_scan_kernel(int32_t *chunk_counts, int nchunks, int nkeys, int32_t *counts) {
+  const int key = (int)((blockIdx.x * (unsigned)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (key >= nkeys) return;
+  int running = 0;
+  for (int base = 0; base < nchunks; base += 32) {
+    const int c = base + lane;
+    const int v = c < nchunks ? chunk_counts[(size_t)c * nkeys + key] : 0;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int n = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += n; }
+    if (c < nchunks) chunk_counts[(size_t)c * nkeys + key] = running + incl - v;
+    running += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) counts[key] = running;
+}
+__global__ void __launch_bounds__(kRankChunk) rank_assign_kernel(const int32_t *ids, int nslots, int nkeys, const int32_t *chunk_base,
+                                                                 int32_t *rank) {
+  extern __shared__ int wcnt[];     // [32 warps][nkeys]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * nkeys; i += blockDim.x) wcnt[i] = 0;
+  __syncthreads();
+  const int s = blockIdx.x * kRankChunk + threadIdx.x;
+  int key = s < nslots ? ids[s] : -1;
+  if ((unsigned)key >= (unsigned)nkeys) key = -1;
+  const unsigned same = __match_any_sync(0xffffffffu, key);
+  const int in_warp = __popc(same & ((1u << lane) - 1u));
+  if (key >= 0 && in_warp == 0) wcnt[warp * nkeys + key] = __popc(same);
+  __syncthreads();
+  if (key >= 0) {
+    int before = chunk_base[(size_t)blockIdx.x * nkeys + key];
+    for (int i = 0; i < warp; ++i) before += wcnt[i * nkeys + key];
+    rank[s] = before + in_warp;
+  }
+}
+
 // Device-side expert offsets.  counts[0..E) are the routed experts' rows; shared experts (if any) get T
 // rows each.  Writes row_off[E+S+1].
 __global__ void expert_offsets_kernel(const int32_t *counts, int E, int S, int T, int32_t *row_off) {

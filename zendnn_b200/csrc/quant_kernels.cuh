@@ -25,6 +25,15 @@ __device__ __forceinline__ int8_t quant_sym(float v, float scale) {
   if (!finite_f32(v)) return 0;
   return (int8_t)__float2int_rn(__fdiv_rn(v, scale));
 }
+// Same result as quant_sym with one multiply in the common case.  rinv = __frcp_rn(scale).  v*rinv is
+// within 1e-4 of the rounded quotient for |q| < 512, so whenever it is at least 1e-3 away from a half
+// integer both round to the same integer; the rare near-tie (and anything large or non-finite) takes the
+// exact division.
+__device__ __forceinline__ int8_t quant_sym_r(float v, float scale, float rinv) {
+  const float qa = v * rinv, t = rintf(qa);
+  if (fabsf(qa) < 512.0f && fabsf(qa - t) < 0.499f) return (int8_t)(int)t;
+  return quant_sym(v, scale);
+}
 
 // Where the rows of one per-token quantisation come from and go to.  Rows can be a plain
 // strided matrix, a gather of rows of a matrix (MoE dispatch), or the concatenation of several
@@ -124,12 +133,13 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
     else reinterpret_cast<float *>(scale_out)[scale_idx] = scale;
   }
   if (!dst) return;
+  const float rinv = __frcp_rn(scale);
   if (vec) {
     auto emit = [&](const uint4 &q, int v) {
       const T *e = reinterpret_cast<const T *>(&q);
       int8_t o[E];
 #pragma unroll
-      for (int i = 0; i < E; ++i) o[i] = quant_sym(elem_to_f32<T>(e[i]), scale);
+      for (int i = 0; i < E; ++i) o[i] = quant_sym_r(elem_to_f32<T>(e[i]), scale, rinv);
       if (E == 8) reinterpret_cast<uint2 *>(dst)[v] = *reinterpret_cast<uint2 *>(o);
       else reinterpret_cast<uint32_t *>(dst)[v] = *reinterpret_cast<uint32_t *>(o);
     };
@@ -141,7 +151,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
     for (int v = threadIdx.x + kQuantRegVec * kQuantThreads; v < nvec; v += kQuantThreads)
       emit(reinterpret_cast<const uint4 *>(src)[v], v);
   } else {
-    for (int k = threadIdx.x; k < K; k += kQuantThreads) dst[k] = quant_sym(elem_to_f32<T>(src[k]), scale);
+    for (int k = threadIdx.x; k < K; k += kQuantThreads) dst[k] = quant_sym_r(elem_to_f32<T>(src[k]), scale, rinv);
   }
 }
 
@@ -160,20 +170,21 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
   int8_t *dst = a.dst ? a.dst + (int64_t)r * a.dst_ld : nullptr;
   const int nvec = a.K / E;
   uint4 cache[NV];
-  float amax = 0.f;
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int v = lane + j * 32;
-    if (v < nvec) {
-      cache[j] = reinterpret_cast<const uint4 *>(src)[v];
-      const T *e = reinterpret_cast<const T *>(&cache[j]);
-#pragma unroll
-      for (int i = 0; i < E; ++i) { float f = elem_to_f32<T>(e[i]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f)); }
-    }
+    cache[j] = v < nvec ? reinterpret_cast<const uint4 *>(src)[v] : make_uint4(0, 0, 0, 0);
   }
   float scale;
   if (a.absmax_bits) scale = scale_from_absmax(__uint_as_float(a.absmax_bits[r]));
   else {
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const T *e = reinterpret_cast<const T *>(&cache[j]);
+#pragma unroll
+      for (int i = 0; i < E; ++i) { float f = elem_to_f32<T>(e[i]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f)); }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     scale = scale_from_absmax(amax);
@@ -183,6 +194,7 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
     else reinterpret_cast<float *>(a.scale)[r] = scale;
   }
   if (!dst) return;
+  const float rinv = __frcp_rn(scale);
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int v = lane + j * 32;
@@ -190,7 +202,7 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
       const T *e = reinterpret_cast<const T *>(&cache[j]);
       int8_t o[E];
 #pragma unroll
-      for (int i = 0; i < E; ++i) o[i] = quant_sym(elem_to_f32<T>(e[i]), scale);
+      for (int i = 0; i < E; ++i) o[i] = quant_sym_r(elem_to_f32<T>(e[i]), scale, rinv);
       if (E == 8) reinterpret_cast<uint2 *>(dst)[v] = *reinterpret_cast<uint2 *>(o);
       else reinterpret_cast<uint32_t *>(dst)[v] = *reinterpret_cast<uint32_t *>(o);
     }

@@ -153,7 +153,13 @@ struct Staged {
 };
 inline int32_t stage_in(const void *p, size_t bytes, cudaStream_t st, const void **out) {
   if (!p || bytes == 0) { *out = p; return B200DNN_SUCCESS; }
-  if (is_device_ptr(p)) { *out = p; return B200DNN_SUCCESS; }
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); at.type = cudaMemoryTypeUnregistered; }
+  if (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) { *out = p; return B200DNN_SUCCESS; }
+  // A few scalars in pinned host memory (scales, a zero point) are read in place over the bus: cheaper than
+  // enqueuing a copy.  As with any asynchronous copy from pinned memory the caller keeps them unchanged until
+  // the stream has passed the call.
+  if (at.type == cudaMemoryTypeHost && at.devicePointer && bytes <= 256) { *out = at.devicePointer; return B200DNN_SUCCESS; }
   void *d = rt().ws.alloc(bytes);
   B2_CHECK(d, B200DNN_FAILURE, "workspace allocation of %zu bytes failed", bytes);
   B2_CUDA(cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, st));

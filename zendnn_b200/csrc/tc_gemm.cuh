@@ -3,7 +3,7 @@
 // group_matmul_direct, to its tile micro-kernel (matmul/group_matmul/custom_kernel/ukernel/
 // int8_microkernel.hpp:39-56) under a CPU scheduler (matmul/group_matmul/group_matmul_dispatch.cpp).
 //
-// One persistent CTA per SM, 320 threads, three roles:
+// One persistent CTA per SM, 352 threads, four roles:
 //   warp 0     TMA producer: per K block of 128 bytes, one [128 x 128 B] box of A and one
 //              [BN x 128 B] box of the packed weight into a ring of shared-memory stages
 //              (SWIZZLE_128B, no multicast), completion on an mbarrier.
@@ -16,6 +16,10 @@
 //              zero-point compensation) are staged once per tile in shared memory as f32/s32.
 //              Two accumulator buffers (2 x BN <= 512 TMEM columns) let the epilogue of tile i
 //              overlap the MMAs of tile i+1.
+//   warp 10    operand warp: runs one tile ahead of the epilogue and puts everything the epilogue needs
+//              from global memory into double-buffered shared memory: the tile's coordinates and output
+//              pointer, the per-column operands of its BN columns and the source scales of its 128 rows.
+//              The epilogue warps then read only tensor memory and shared memory.
 // Tiles are walked n-tile-major so that CTAs running at the same time share weight tiles through L2.
 // Grouped form: A is one [rows x K] matrix holding every expert's rows back to back; row offsets
 // and the cumulative tile counts live in device memory, so no host round trip is needed after routing.
@@ -31,7 +35,7 @@ namespace b200 {
 constexpr int kTcBM = 128;
 constexpr int kTcBK = 128;               // bytes of K per stage row (one 128-byte swizzle span)
 constexpr int kTcEpiWarps = 8;
-constexpr int kTcThreads = 64 + 32 * kTcEpiWarps;   // producer warp + MMA warp + epilogue warps
+constexpr int kTcThreads = 96 + 32 * kTcEpiWarps;   // producer warp + MMA warp + epilogue warps + operand warp
 constexpr int kTcSmemBudget = 200 * 1024; // stage ring
 
 struct TcGroupDesc {   // per expert, device memory (grouped form with caller-owned outputs)
@@ -57,6 +61,7 @@ struct TcGemmArgs {
   int a_unsigned;
   int gated;                  // packed gate/up interleave: 0, 1 or 2 (see pack_kernels.cuh)
   int fast_act;               // FA_* code: which specialised epilogue loop to run
+  int n_fastest;              // tile order: 0 = all row tiles of a column tile first, 1 = all column tiles of a row tile first
   int32_t *status;            // device word: 0 ok
 };
 
@@ -106,8 +111,9 @@ struct TileCoord { int g, row0, rows, m_local0, nt; };
 
 __device__ __forceinline__ TileCoord tc_tile(const TcGemmArgs &a, int tile, int m_tiles) {
   TileCoord t;
-  t.nt = tile / m_tiles;
-  const int mt = tile - t.nt * m_tiles;
+  int mt;
+  if (a.n_fastest) { mt = tile / a.n_tiles; t.nt = tile - mt * a.n_tiles; }
+  else { t.nt = tile / m_tiles; mt = tile - t.nt * m_tiles; }
   if (!a.tile_prefix) {
     t.g = 0; t.m_local0 = mt * kTcBM; t.row0 = t.m_local0; t.rows = min(kTcBM, a.M_total - t.row0);
   } else {
@@ -120,6 +126,36 @@ __device__ __forceinline__ TileCoord tc_tile(const TcGemmArgs &a, int tile, int 
   }
   return t;
 }
+
+// Same mapping computed by a whole warp: the group of a row tile is the number of prefix entries
+// tile_prefix[1..n_groups) that are <= the tile index (empty groups repeat a prefix value and are skipped).
+__device__ __forceinline__ TileCoord tc_tile_warp(const TcGemmArgs &a, int tile, int m_tiles, int lane) {
+  TileCoord t;
+  int mt;
+  if (a.n_fastest) { mt = tile / a.n_tiles; t.nt = tile - mt * a.n_tiles; }
+  else { t.nt = tile / m_tiles; mt = tile - t.nt * m_tiles; }
+  if (!a.tile_prefix) {
+    t.g = 0; t.m_local0 = mt * kTcBM; t.row0 = t.m_local0; t.rows = min(kTcBM, a.M_total - t.row0);
+    return t;
+  }
+  int g = 0;
+  for (int base = 1; base < a.n_groups; base += 32) {
+    const int i = base + lane;
+    const bool le = i < a.n_groups && a.tile_prefix[i] <= mt;
+    g += __popc(__ballot_sync(0xffffffffu, le));
+  }
+  t.g = g;
+  t.m_local0 = (mt - a.tile_prefix[g]) * kTcBM;
+  t.row0 = a.row_off[g] + t.m_local0;
+  t.rows = min(kTcBM, a.row_off[g + 1] - t.row0);
+  return t;
+}
+
+struct TileMeta {          // what the epilogue needs to know about a tile, written by the operand warp
+  int row0, rows, m_dst0, nt;
+  void *dst; int64_t ldc;
+  int has_bias;
+};
 
 // ---- epilogue arithmetic ---------------------------------------------------------------------------
 // Post-op structure resolved on the host so that the per-element loop carries no dispatch.
@@ -214,8 +250,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                const TcGemmArgs a, const EpiParams epi) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * 8 + 4];
-  __shared__ __align__(16) TileCols cols;
+  __shared__ __align__(8) uint64_t bars[2 * 8 + 8];
+  __shared__ __align__(16) TileCols cols[2];
+  __shared__ __align__(16) float row_scale[2][kTcBM];
+  __shared__ TileMeta meta[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int s_err;
 
@@ -228,10 +266,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   auto empty_bar = [&](int s) { return bar0 + 8u * (8 + s); };
   auto tfull_bar = [&](int i) { return bar0 + 8u * (16 + i); };
   auto tempty_bar = [&](int i) { return bar0 + 8u * (18 + i); };
+  auto cfull_bar = [&](int i) { return bar0 + 8u * (20 + i); };
+  auto cempty_bar = [&](int i) { return bar0 + 8u * (22 + i); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), kTcEpiWarps); }
+    for (int i = 0; i < 2; ++i) { mbar_init(cfull_bar(i), 1); mbar_init(cempty_bar(i), kTcEpiWarps); }
     s_err = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -250,13 +291,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0; uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !s_err; tile += gridDim.x) {
-        const TileCoord t = tc_tile(a, tile, m_tiles);
+    // (the whole warp walks the tiles so that the group lookup is a warp operation; lane 0 issues the copies)
+    int stage = 0; uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      // one decision for the whole warp (the lookup below uses warp-wide operations)
+      if (!__shfl_sync(0xffffffffu, (ok && !s_err) ? 1 : 0, 0)) break;
+      const TileCoord t = tc_tile_warp(a, tile, m_tiles, lane);
+      if (lane == 0) {
         const CUtensorMap *mb = a.maps_b ? a.maps_b + t.g : &map_b0;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { s_err = 1; atomicExch(a.status, 1); break; }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { s_err = 1; atomicExch(a.status, 1); ok = false; break; }
           const uint32_t sa = smem0 + (uint32_t)stage * stage_bytes;
           mbar_expect_tx(full_bar(stage), stage_bytes);
           tma_load_2d(sa, &map_a, kb * kTcBK, t.row0, full_bar(stage));
@@ -291,50 +336,77 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
+  } else if (warp == 2 + kTcEpiWarps) {
+    // ------------------------------------------------------------------ operand warp
+    const int32_t zp = load_zp(epi);
+    int cb = 0; uint32_t cphase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      if (!__shfl_sync(0xffffffffu, s_err ? 0 : 1, 0)) break;
+      const TileCoord t = tc_tile_warp(a, tile, m_tiles, lane);
+      const void *wsp = epi.wei_scale; const int32_t *csp = epi.colsum; const void *bp = epi.bias;
+      void *dst = epi.dst; int64_t ldc = epi.ldc; int m_dst0 = t.row0;
+      if (a.groups) {
+        const TcGroupDesc gd = a.groups[t.g];
+        wsp = gd.wei_scale; csp = gd.colsum; bp = gd.bias;
+        if (gd.dst) { dst = gd.dst; ldc = gd.ldc; m_dst0 = t.m_local0; }   // else: shared dst, global row index
+      }
+      const int pc_tile = t.nt * a.BN;
+      float cw[8], cbv[8]; int32_t ck[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        cw[j] = 1.0f; cbv[j] = 0.0f; ck[j] = 0;
+        const int pc = pc_tile + lane + 32 * j;
+        if (lane + 32 * j < a.BN && pc < a.N) {
+          const int n = (int)packed_to_logical(pc, a.gated, epi.gated_I);
+          if (epi.wei_scale_n) cw[j] = load_as_f32(wsp, epi.wei_scale_dt, epi.wei_scale_n > 1 ? n : 0);
+          if (bp) cbv[j] = load_as_f32(bp, epi.bias_dt, n);
+          if (zp) ck[j] = zp * csp[pc];
+        }
+      }
+      float rs[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = lane + 32 * j;
+        rs[j] = (epi.src_scale_n && r < t.rows) ? load_as_f32(epi.src_scale, epi.src_scale_dt, epi.src_scale_n > 1 ? t.row0 + r : 0) : 1.0f;
+      }
+      // the buffer is free when the epilogue warps have left the tile that used it two tiles ago
+      if (!__all_sync(0xffffffffu, mbar_wait(cempty_bar(cb), cphase ^ 1u))) { if (lane == 0) { s_err = 6; atomicExch(a.status, 6); } break; }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (lane + 32 * j < a.BN) { cols[cb].ws[lane + 32 * j] = cw[j]; cols[cb].bias[lane + 32 * j] = cbv[j]; cols[cb].comp[lane + 32 * j] = ck[j]; }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) row_scale[cb][lane + 32 * j] = rs[j];
+      if (lane == 0) {
+        TileMeta m; m.row0 = t.row0; m.rows = t.rows; m.m_dst0 = m_dst0; m.nt = t.nt; m.dst = dst; m.ldc = ldc; m.has_bias = bp != nullptr;
+        meta[cb] = m;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(cfull_bar(cb));
+      if (++cb == 2) { cb = 0; cphase ^= 1u; }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int ew = warp - 2;                // 0..7
     const int q = warp & 3;                 // TMEM lane quadrant this warp may access
     const int half = ew >> 2;               // which alternate chunks this warp takes
-    const int etid = ew * 32 + lane;        // 0..255
     const int row_in_tile = q * 32 + lane;
-    const int32_t zp = load_zp(epi);
     int acc = 0; uint32_t acc_phase = 0;
+    int ob = 0; uint32_t ophase = 0;            // operand buffer of the current tile
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const TileCoord t = tc_tile(a, tile, m_tiles);
-      // the decision to go on must be the same in all epilogue warps (they meet at a named barrier):
-      // it depends only on this wait, which either completes for all of them or expires for all
-      // Operands that do not depend on the accumulator are fetched first, so that their latency
-      // overlaps the wait for the MMAs of this tile.
-      const int m_local = t.m_local0 + row_in_tile;
-      const int m_global = t.row0 + row_in_tile;
-      const bool row_ok = row_in_tile < t.rows;
-      EpiCtx cx = epi_ctx(epi, row_ok ? m_global : 0);
-      int m_dst = m_global;
-      if (a.groups) {
-        const TcGroupDesc gd = a.groups[t.g];
-        cx.wei_scale = gd.wei_scale; cx.colsum = gd.colsum; cx.bias = gd.bias;
-        if (gd.dst) { cx.dst = gd.dst; cx.ldc = gd.ldc; m_dst = m_local; }   // else: shared dst, global row index
-      }
-      const int pc_tile = t.nt * a.BN;
-      float col_w = 1.0f, col_b = 0.0f; int32_t col_k = 0;
-      if (etid < a.BN) {
-        const int pc = pc_tile + etid;
-        if (pc < a.N) {
-          const int n = (int)packed_to_logical(pc, a.gated, epi.gated_I);
-          if (epi.wei_scale_n) col_w = load_as_f32(cx.wei_scale, epi.wei_scale_dt, epi.wei_scale_n > 1 ? n : 0);
-          if (cx.bias) col_b = load_as_f32(cx.bias, epi.bias_dt, n);
-          if (zp) col_k = zp * cx.colsum[pc];
-        }
-      }
-      bool ok = mbar_wait(tfull_bar(acc), acc_phase);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
+      // everything from global memory was put into shared memory by the operand warp
+      if (!mbar_wait(cfull_bar(ob), ophase)) { if (lane == 0) { s_err = 5; atomicExch(a.status, 5); } break; }
+      const TileMeta tm = meta[ob];
+      const TileCols &tcols = cols[ob];
+      const bool row_ok = row_in_tile < tm.rows;
+      const int m_global = tm.row0 + row_in_tile;
+      const int m_dst = tm.m_dst0 + row_in_tile;
+      EpiCtx cx;
+      cx.wei_scale = nullptr; cx.colsum = nullptr; cx.bias = nullptr; cx.dst = tm.dst; cx.ldc = tm.ldc;
+      cx.s_src = row_scale[ob][row_in_tile];
+      const int pc_tile = tm.nt * a.BN;
+      if (!mbar_wait(tfull_bar(acc), acc_phase)) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
       tc_fence_after();
-      // stage this tile's column operands (f32 / s32) once (the previous tile's readers left at its closing barrier)
-      if (etid < a.BN) { cols.ws[etid] = col_w; cols.bias[etid] = col_b; cols.comp[etid] = col_k; }
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * kTcEpiWarps) : "memory");
-      const bool has_bias = cx.bias != nullptr;
+      const bool has_bias = tm.has_bias != 0;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * a.BN);
       if (!a.gated) {
         // this warp's chunks: a contiguous half of the tile's 32-column chunks that lie inside N;
@@ -346,14 +418,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (!row_ok) return;
           const int pc0 = pc_tile + c * 32;
           switch (a.fast_act) {
-          case FA_NONE: tc_epi_chunk<FA_NONE>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_RELU: tc_epi_chunk<FA_RELU>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_GELU_TANH: tc_epi_chunk<FA_GELU_TANH>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_GELU_ERF: tc_epi_chunk<FA_GELU_ERF>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_SIGMOID: tc_epi_chunk<FA_SIGMOID>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_SWISH: tc_epi_chunk<FA_SWISH>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_TANH: tc_epi_chunk<FA_TANH>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          default: tc_epi_chunk<FA_GENERIC>(epi, cx, r, cols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_NONE: tc_epi_chunk<FA_NONE>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_RELU: tc_epi_chunk<FA_RELU>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_GELU_TANH: tc_epi_chunk<FA_GELU_TANH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_GELU_ERF: tc_epi_chunk<FA_GELU_ERF>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_SIGMOID: tc_epi_chunk<FA_SIGMOID>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_SWISH: tc_epi_chunk<FA_SWISH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_TANH: tc_epi_chunk<FA_TANH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          default: tc_epi_chunk<FA_GENERIC>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
           }
         };
         uint32_t ra[32], rb[32];
@@ -384,9 +456,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            float gv = __fmul_rn(__fmul_rn((float)(int32_t)rg[i], cx.s_src), cols.ws[cg + i]);
-            float uv = __fmul_rn(__fmul_rn((float)(int32_t)ru[i], cx.s_src), cols.ws[cu + i]);
-            if (has_bias) { gv = __fadd_rn(gv, cols.bias[cg + i]); uv = __fadd_rn(uv, cols.bias[cu + i]); }
+            float gv = __fmul_rn(__fmul_rn((float)(int32_t)rg[i], cx.s_src), tcols.ws[cg + i]);
+            float uv = __fmul_rn(__fmul_rn((float)(int32_t)ru[i], cx.s_src), tcols.ws[cu + i]);
+            if (has_bias) { gv = __fadd_rn(gv, tcols.bias[cg + i]); uv = __fadd_rn(uv, tcols.bias[cu + i]); }
             float z;
             if (epi.gated_act == ACT_SILU_MUL) z = __fmul_rn(fast_sigmoid_mul(gv, gv), uv);
             else z = gated_f32(epi.gated_act, gv, uv);
@@ -407,10 +479,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (row_ok && epi.row_absmax) atomicMax(epi.row_absmax + m_global, __float_as_uint(amax));
       }
       tc_fence_before();
-      // all epilogue warps are done with this accumulator and with the staged column operands
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * kTcEpiWarps) : "memory");
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      __syncwarp();
+      // this warp is done with the accumulator and with the tile's operand buffer
+      if (lane == 0) { mbar_arrive(tempty_bar(acc)); mbar_arrive(cempty_bar(ob)); }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      if (++ob == 2) { ob = 0; ophase ^= 1u; }
     }
   }
 
