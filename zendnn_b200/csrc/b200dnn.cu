@@ -283,15 +283,19 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
     default: break;
     }
   }
+  args.dbg = env_int("B200DNN_TC_DBG", 0);
   args.BN = pick_bn(m_tiles_hint, N, R.sm_count, pw0.gated);
   B2_CHECK(args.BN % 32 == 0 && args.BN >= 32 && args.BN <= 256 && (!pw0.gated || args.BN % 64 == 0), B200DNN_FAILURE,
            "bad tile width %d", args.BN);
   args.n_tiles = (N + args.BN - 1) / args.BN;
   // Tile order.  Sweeping the row tiles under one column tile keeps that weight slice hot and re-reads the
-  // activations once per column tile: right while the activations fit in L2.  Past that (many rows, as in a
-  // fine-grained MoE) the column tiles of one row tile run together instead: activations are read once and
-  // the (small) weight of the group is re-read from L2.
-  args.n_fastest = env_int("B200DNN_TC_ORDER", (long long)M_total * K > (48ll << 20) ? 1 : 0);
+  // activations once per column tile.  When the weight of a group is small enough to stay in L2 and the
+  // activations are the larger operand (many rows, as in a fine-grained MoE), the column tiles of one row tile
+  // run together instead: activations are read once, the weight is re-read from L2.
+  {
+    const long long w_bytes = (long long)pw0.Kp * pw0.Np, a_bytes = (long long)M_total * K;
+    args.n_fastest = env_int("B200DNN_TC_ORDER", (w_bytes <= (32ll << 20) && a_bytes > w_bytes) ? 1 : 0);
+  }
   const int stage_bytes = kTcBM * kTcBK + args.BN * kTcBK;
   int stages = kTcSmemBudget / stage_bytes;
   if (stages > 8) stages = 8;

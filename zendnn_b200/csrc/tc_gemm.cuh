@@ -3,24 +3,27 @@
 // group_matmul_direct, to its tile micro-kernel (matmul/group_matmul/custom_kernel/ukernel/
 // int8_microkernel.hpp:39-56) under a CPU scheduler (matmul/group_matmul/group_matmul_dispatch.cpp).
 //
-// One persistent CTA per SM, 352 threads, four roles:
+// One persistent CTA per SM, 608 threads, four roles:
 //   warp 0     TMA producer: per K block of 128 bytes, one [128 x 128 B] box of A and one
 //              [BN x 128 B] box of the packed weight into a ring of shared-memory stages
 //              (SWIZZLE_128B, no multicast), completion on an mbarrier.
 //   warp 1     MMA issuer: one lane issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=BN, K=32),
 //              four per stage, accumulating s32 in tensor memory; tcgen05.commit releases the
 //              stage and, after the last K block, publishes the accumulator.
-//   warps 2-9  epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per thread, two
-//              warps per lane quadrant taking alternate 32-column chunks), dequantise / bias /
-//              post-ops (or gated activation) and store.  Per-column operands (weight scale, bias,
-//              zero-point compensation) are staged once per tile in shared memory as f32/s32.
-//              Two accumulator buffers (2 x BN <= 512 TMEM columns) let the epilogue of tile i
+//   warps 2-17 epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per thread, four
+//              warps per lane quadrant, each taking a share of the tile's 32-column chunks), dequantise / bias /
+//              post-ops (or gated activation) and store; results leave through a small per-warp
+//              shared-memory block so that every store instruction writes whole 32-byte sectors of
+//              16 rows.  Two accumulator buffers (2 x BN <= 512 TMEM columns) let the epilogue of tile i
 //              overlap the MMAs of tile i+1.
-//   warp 10    operand warp: runs one tile ahead of the epilogue and puts everything the epilogue needs
+//   warp 18    operand warp: runs one tile ahead of the epilogue and puts everything the epilogue needs
 //              from global memory into double-buffered shared memory: the tile's coordinates and output
 //              pointer, the per-column operands of its BN columns and the source scales of its 128 rows.
 //              The epilogue warps then read only tensor memory and shared memory.
-// Tiles are walked n-tile-major so that CTAs running at the same time share weight tiles through L2.
+// Tile order: column-tile-major (CTAs running together share a weight tile through L2), or, when the
+// activations are the large operand and a group's weight stays in L2, row-tile-major (n_fastest).
+// Shared memory is the busiest resource (TMA writes the operands, the tensor core reads them back), so
+// the epilogue keeps its own shared-memory traffic small.
 // Grouped form: A is one [rows x K] matrix holding every expert's rows back to back; row offsets
 // and the cumulative tile counts live in device memory, so no host round trip is needed after routing.
 // Every wait is bounded: on expiry the kernel records a code in *status and leaves.
@@ -34,7 +37,11 @@ namespace b200 {
 
 constexpr int kTcBM = 128;
 constexpr int kTcBK = 128;               // bytes of K per stage row (one 128-byte swizzle span)
-constexpr int kTcEpiWarps = 8;
+#ifndef B200_TC_EPI_WARPS
+#define B200_TC_EPI_WARPS 16
+#endif
+constexpr int kTcEpiWarps = B200_TC_EPI_WARPS;      // a multiple of 4: each warp may only read its own quadrant of TMEM lanes
+constexpr int kTcEpiParts = kTcEpiWarps / 4;          // warps per lane quadrant, each taking a share of the tile's columns
 constexpr int kTcThreads = 96 + 32 * kTcEpiWarps;   // producer warp + MMA warp + epilogue warps + operand warp
 constexpr int kTcSmemBudget = 200 * 1024; // stage ring
 
@@ -61,6 +68,7 @@ struct TcGemmArgs {
   int a_unsigned;
   int gated;                  // packed gate/up interleave: 0, 1 or 2 (see pack_kernels.cuh)
   int fast_act;               // FA_* code: which specialised epilogue loop to run
+  int dbg;                    // timing experiments (results invalid): 1 no epilogue work, 2 tensor-memory loads only, 3 no stores
   int n_fastest;              // tile order: 0 = all row tiles of a column tile first, 1 = all column tiles of a row tile first
   int32_t *status;            // device word: 0 ok
 };
@@ -195,23 +203,77 @@ struct TileCols {          // per-tile column operands staged in shared memory
   int32_t comp[256];
 };
 
+// Coalesced store of a [32 rows x 32 bytes] block that a warp holds one row per lane (v[0], v[1] = the row's
+// two 16-byte pieces).  The block goes through the warp's 1 KiB of shared memory (pieces swapped on every
+// second group of four rows so that both the writes and the reads are free of bank conflicts) and leaves
+// as two instructions that each write 16 rows x 32 contiguous bytes (whole sectors), instead of 32
+// scattered 16-byte pieces per instruction.
+// g_row0: address of the block's first row; rows_valid: how many of the 32 rows exist.
+__device__ __forceinline__ void warp_store_rows32(uint8_t *sbuf, const uint4 &v0, const uint4 &v1, uint8_t *g_row0, int64_t pitch_bytes,
+                                                  int rows_valid, int lane) {
+  const int sw = (lane >> 2) & 1;
+  *reinterpret_cast<uint4 *>(sbuf + lane * 32 + ((0 ^ sw) << 4)) = v0;
+  *reinterpret_cast<uint4 *>(sbuf + lane * 32 + ((1 ^ sw) << 4)) = v1;
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int R = 16 * j + (lane >> 1), p = lane & 1;
+    const uint4 val = *reinterpret_cast<const uint4 *>(sbuf + R * 32 + ((p ^ ((R >> 2) & 1)) << 4));
+    if (R < rows_valid) *reinterpret_cast<uint4 *>(g_row0 + (int64_t)R * pitch_bytes + p * 16) = val;
+  }
+  __syncwarp();
+}
+// [32 rows x 64 bytes] as two such blocks
+__device__ __forceinline__ void warp_store_rows64(uint8_t *sbuf, const uint4 (&v)[4], uint8_t *g_row0, int64_t pitch_bytes,
+                                                  int rows_valid, int lane) {
+  warp_store_rows32(sbuf, v[0], v[1], g_row0, pitch_bytes, rows_valid, lane);
+  warp_store_rows32(sbuf, v[2], v[3], g_row0 + 32, pitch_bytes, rows_valid, lane);
+}
+
+struct EpiStore {          // where this warp's rows of the current tile go
+  uint8_t *sbuf;           // the warp's staging block
+  uint8_t *g_row0;         // address of (first row of the warp, column 0) in the destination
+  int64_t pitch_bytes;
+  int rows_valid;          // rows of the warp's 32 that exist in this tile
+  bool coalesce;           // destination 16-byte aligned: use the staged path
+  bool row_ok;             // this lane's row exists
+};
+
 // One 32-column chunk of one output row.
 template <int ACT>
 __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx &cx, const uint32_t (&r)[32], const TileCols &tc,
-                                             int c0, int pc0, int N, int m_dst, bool has_bias) {
+                                             int c0, int pc0, int N, int m_dst, bool has_bias, const EpiStore &es, int lane) {
+  const bool has_zp = epi.has_zp != 0;
   if (epi.dst_dt == DT_S32) {
-    int32_t *o = reinterpret_cast<int32_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+    int32_t y[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (pc0 + i < N) o[i] = (int32_t)r[i] - tc.comp[c0 + i];
+    for (int i = 0; i < 32; ++i) y[i] = has_zp ? (int32_t)r[i] - tc.comp[c0 + i] : (int32_t)r[i];
+    if (es.coalesce && pc0 + 32 <= N) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint4 v[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) v[p] = make_uint4(y[16 * h + 4 * p], y[16 * h + 4 * p + 1], y[16 * h + 4 * p + 2], y[16 * h + 4 * p + 3]);
+        warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)(pc0 + 16 * h) * 4, es.pitch_bytes, es.rows_valid, lane);
+      }
+    } else if (es.row_ok) {
+      int32_t *o = reinterpret_cast<int32_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (pc0 + i < N) o[i] = y[i];
+    }
     return;
   }
   float x[32];
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
+    // shared memory is the busiest resource of this kernel (the tensor core reads its operands from it):
+    // bias and compensation are fetched only when they exist
     const float4 w4 = *reinterpret_cast<const float4 *>(&tc.ws[c0 + i]);
-    const float4 b4 = *reinterpret_cast<const float4 *>(&tc.bias[c0 + i]);
-    const int4 k4 = *reinterpret_cast<const int4 *>(&tc.comp[c0 + i]);
+    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    int4 k4 = make_int4(0, 0, 0, 0);
+    if (has_bias) b4 = *reinterpret_cast<const float4 *>(&tc.bias[c0 + i]);
+    if (has_zp) k4 = *reinterpret_cast<const int4 *>(&tc.comp[c0 + i]);
     const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
     const int kv[4] = {k4.x, k4.y, k4.z, k4.w};
 #pragma unroll
@@ -222,23 +284,32 @@ __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx 
     }
   }
   if (epi.dst_dt == DT_BF16) {
-    uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
-    if (pc0 + 32 <= N && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+    if (es.coalesce && pc0 + 32 <= N) {
+      uint4 v[4];
 #pragma unroll
-      for (int v = 0; v < 4; ++v)
-        reinterpret_cast<uint4 *>(o)[v] = make_uint4(pack_bf16x2(x[8 * v], x[8 * v + 1]), pack_bf16x2(x[8 * v + 2], x[8 * v + 3]),
-                                                     pack_bf16x2(x[8 * v + 4], x[8 * v + 5]), pack_bf16x2(x[8 * v + 6], x[8 * v + 7]));
-    } else {
+      for (int p = 0; p < 4; ++p)
+        v[p] = make_uint4(pack_bf16x2(x[8 * p], x[8 * p + 1]), pack_bf16x2(x[8 * p + 2], x[8 * p + 3]),
+                          pack_bf16x2(x[8 * p + 4], x[8 * p + 5]), pack_bf16x2(x[8 * p + 6], x[8 * p + 7]));
+      warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)pc0 * 2, es.pitch_bytes, es.rows_valid, lane);
+    } else if (es.row_ok) {
+      uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
         if (pc0 + i < N) o[i] = f32_to_bf16_bits(x[i]);
     }
   } else {
-    float *o = reinterpret_cast<float *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
-    if (pc0 + 32 <= N && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+    if (es.coalesce && pc0 + 32 <= N) {
 #pragma unroll
-      for (int v = 0; v < 8; ++v) reinterpret_cast<float4 *>(o)[v] = make_float4(x[4 * v], x[4 * v + 1], x[4 * v + 2], x[4 * v + 3]);
-    } else {
+      for (int h = 0; h < 2; ++h) {
+        uint4 v[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p)
+          v[p] = make_uint4(__float_as_uint(x[16 * h + 4 * p]), __float_as_uint(x[16 * h + 4 * p + 1]),
+                            __float_as_uint(x[16 * h + 4 * p + 2]), __float_as_uint(x[16 * h + 4 * p + 3]));
+        warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)(pc0 + 16 * h) * 4, es.pitch_bytes, es.rows_valid, lane);
+      }
+    } else if (es.row_ok) {
+      float *o = reinterpret_cast<float *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
         if (pc0 + i < N) o[i] = x[i];
@@ -254,6 +325,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __shared__ __align__(16) TileCols cols[2];
   __shared__ __align__(16) float row_scale[2][kTcBM];
   __shared__ TileMeta meta[2];
+  __shared__ __align__(16) uint8_t epi_stage[kTcEpiWarps][1024];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int s_err;
 
@@ -388,7 +460,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int ew = warp - 2;                // 0..7
     const int q = warp & 3;                 // TMEM lane quadrant this warp may access
-    const int half = ew >> 2;               // which alternate chunks this warp takes
+    const int part = ew >> 2;               // which share of the tile's columns this warp takes
     const int row_in_tile = q * 32 + lane;
     int acc = 0; uint32_t acc_phase = 0;
     int ob = 0; uint32_t ophase = 0;            // operand buffer of the current tile
@@ -407,71 +479,93 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!mbar_wait(tfull_bar(acc), acc_phase)) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
       tc_fence_after();
       const bool has_bias = tm.has_bias != 0;
+      EpiStore es;
+      {
+        const int esz = epi.dst_dt == DT_BF16 ? 2 : 4;
+        es.sbuf = epi_stage[ew];
+        es.pitch_bytes = tm.ldc * esz;
+        es.g_row0 = reinterpret_cast<uint8_t *>(tm.dst) + (int64_t)(tm.m_dst0 + q * 32) * es.pitch_bytes;
+        es.rows_valid = min(32, max(0, tm.rows - q * 32));
+        es.coalesce = ((reinterpret_cast<uintptr_t>(tm.dst) | (uintptr_t)es.pitch_bytes) & 15) == 0;
+        es.row_ok = row_ok;
+      }
       const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * a.BN);
-      if (!a.gated) {
-        // this warp's chunks: a contiguous half of the tile's 32-column chunks that lie inside N;
-        // the accumulator of chunk c+1 is read from tensor memory while chunk c is being processed
+      if (a.dbg == 1) {
+        // timing experiment: no epilogue work
+      } else if (!a.gated) {
+        if (a.dbg == 3) { es.coalesce = false; es.row_ok = false; }
+        // this warp's chunks: a contiguous share of the tile's 32-column chunks that lie inside N
         const int nc = min(a.BN / 32, (a.N - pc_tile + 31) / 32);
-        const int per = (a.BN / 32 + 1) / 2;
-        const int cb = half * per, ce = min(nc, cb + per);
-        auto process = [&](const uint32_t (&r)[32], int c) {
-          if (!row_ok) return;
+        const int per = (a.BN / 32 + kTcEpiParts - 1) / kTcEpiParts;
+        const int c_begin = part * per, c_end = min(nc, c_begin + per);
+        for (int c = c_begin; c < c_end; ++c) {
+          uint32_t r[32];
+          tc_ld32(taddr0 + (uint32_t)(c * 32), r);
+          tc_wait_ld();
           const int pc0 = pc_tile + c * 32;
+          if (a.dbg == 2) { uint32_t x = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x ^= r[i];
+            if (x == 0x12345678u) atomicExch(a.status, 99); continue; }
           switch (a.fast_act) {
-          case FA_NONE: tc_epi_chunk<FA_NONE>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_RELU: tc_epi_chunk<FA_RELU>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_GELU_TANH: tc_epi_chunk<FA_GELU_TANH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_GELU_ERF: tc_epi_chunk<FA_GELU_ERF>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_SIGMOID: tc_epi_chunk<FA_SIGMOID>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_SWISH: tc_epi_chunk<FA_SWISH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          case FA_TANH: tc_epi_chunk<FA_TANH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
-          default: tc_epi_chunk<FA_GENERIC>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias); break;
+          case FA_NONE: tc_epi_chunk<FA_NONE>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
+          case FA_RELU: tc_epi_chunk<FA_RELU>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
+          case FA_GELU_TANH: tc_epi_chunk<FA_GELU_TANH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
+          case FA_GELU_ERF: tc_epi_chunk<FA_GELU_ERF>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
+          case FA_SIGMOID: tc_epi_chunk<FA_SIGMOID>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
+          case FA_SWISH: tc_epi_chunk<FA_SWISH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
+          case FA_TANH: tc_epi_chunk<FA_TANH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
+          default: tc_epi_chunk<FA_GENERIC>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
           }
-        };
-        uint32_t ra[32], rb[32];
-        if (cb < ce) tc_ld32(taddr0 + (uint32_t)(cb * 32), ra);
-        for (int c = cb; c < ce; c += 2) {
-          tc_wait_ld();
-          if (c + 1 < ce) tc_ld32(taddr0 + (uint32_t)((c + 1) * 32), rb);
-          process(ra, c);
-          if (c + 1 >= ce) break;
-          tc_wait_ld();
-          if (c + 2 < ce) tc_ld32(taddr0 + (uint32_t)((c + 2) * 32), ra);
-          process(rb, c + 1);
         }
       } else {
         // gated: packed columns [g(32) u(32)] -> 32 outputs; dst is [rows, I] bf16
         float amax = 0.f;
-        for (int c = half; c < a.BN / 64; c += 2) {
+        for (int c = part; c < a.BN / 64; c += kTcEpiParts) {
           const int pc0 = pc_tile + c * 64;
           if (pc0 >= a.N) break;
           uint32_t rg[32], ru[32];
           tc_ld32(taddr0 + (uint32_t)(c * 64), rg);
           tc_ld32(taddr0 + (uint32_t)(c * 64 + 32), ru);
           tc_wait_ld();
-          if (!row_ok) continue;
           const int j0 = pc0 / 2;   // first output column of this pair of chunks
           const int cg = c * 64, cu = c * 64 + 32;
-          uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + j0;
           uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float gv = __fmul_rn(__fmul_rn((float)(int32_t)rg[i], cx.s_src), tcols.ws[cg + i]);
-            float uv = __fmul_rn(__fmul_rn((float)(int32_t)ru[i], cx.s_src), tcols.ws[cu + i]);
-            if (has_bias) { gv = __fadd_rn(gv, tcols.bias[cg + i]); uv = __fadd_rn(uv, tcols.bias[cu + i]); }
-            float z;
-            if (epi.gated_act == ACT_SILU_MUL) z = __fmul_rn(fast_sigmoid_mul(gv, gv), uv);
-            else z = gated_f32(epi.gated_act, gv, uv);
-            const uint16_t zb = f32_to_bf16_bits(z);
-            const float az = fabsf(bf16_bits_to_f32(zb));
-            if (finite_f32(az)) amax = fmaxf(amax, az);
-            if (i & 1) pk[i >> 1] |= (uint32_t)zb << 16; else pk[i >> 1] = zb;
-          }
-          if ((reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+          for (int i = 0; i < 32; i += 4) {
+            const float4 wg4 = *reinterpret_cast<const float4 *>(&tcols.ws[cg + i]);
+            const float4 wu4 = *reinterpret_cast<const float4 *>(&tcols.ws[cu + i]);
+            const float wg[4] = {wg4.x, wg4.y, wg4.z, wg4.w}, wu[4] = {wu4.x, wu4.y, wu4.z, wu4.w};
+            float bg[4] = {0.f, 0.f, 0.f, 0.f}, bu[4] = {0.f, 0.f, 0.f, 0.f};
+            if (has_bias) {
+              const float4 bg4 = *reinterpret_cast<const float4 *>(&tcols.bias[cg + i]);
+              const float4 bu4 = *reinterpret_cast<const float4 *>(&tcols.bias[cu + i]);
+              bg[0] = bg4.x; bg[1] = bg4.y; bg[2] = bg4.z; bg[3] = bg4.w;
+              bu[0] = bu4.x; bu[1] = bu4.y; bu[2] = bu4.z; bu[3] = bu4.w;
+            }
+            uint16_t zb[4];
 #pragma unroll
-            for (int v = 0; v < 4; ++v)
-              reinterpret_cast<uint4 *>(o)[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
-          } else {
+            for (int j = 0; j < 4; ++j) {
+              float gv = __fmul_rn(__fmul_rn((float)(int32_t)rg[i + j], cx.s_src), wg[j]);
+              float uv = __fmul_rn(__fmul_rn((float)(int32_t)ru[i + j], cx.s_src), wu[j]);
+              if (has_bias) { gv = __fadd_rn(gv, bg[j]); uv = __fadd_rn(uv, bu[j]); }
+              float z;
+              if (epi.gated_act == ACT_SILU_MUL) z = __fmul_rn(fast_sigmoid_mul(gv, gv), uv);
+              else z = gated_f32(epi.gated_act, gv, uv);
+              zb[j] = f32_to_bf16_bits(z);
+              const float az = fabsf(bf16_bits_to_f32(zb[j]));
+              if (finite_f32(az)) amax = fmaxf(amax, az);
+            }
+            pk[i >> 1] = (uint32_t)zb[0] | ((uint32_t)zb[1] << 16);
+            pk[(i >> 1) + 1] = (uint32_t)zb[2] | ((uint32_t)zb[3] << 16);
+          }
+          if (es.coalesce) {
+            uint4 v[4];
+#pragma unroll
+            for (int p4 = 0; p4 < 4; ++p4) v[p4] = make_uint4(pk[4 * p4], pk[4 * p4 + 1], pk[4 * p4 + 2], pk[4 * p4 + 3]);
+            warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)j0 * 2, es.pitch_bytes, es.rows_valid, lane);
+          } else if (row_ok) {
+            uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + j0;
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = (uint16_t)(pk[i >> 1] >> ((i & 1) * 16));
           }
