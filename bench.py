@@ -320,8 +320,9 @@ def _time_events(torch, fn, iters, warm=2):
 
 def run_extras(torch, capi, dev, rank, world, peaks):
     """The other two parts of the metric: prefill W8A8 TOPS (configurations 1 and 3) on one GPU and fused-MoE
-    tokens/s (configuration 4), expert-parallel over all ranks when there are several (weak scaling: 4096
-    tokens per rank, the 8 experts sharded e % world).  Device-resident operands, CUDA-event timing."""
+    tokens/s (configurations 4 and 5), expert-parallel over all ranks when there are several (weak scaling:
+    the tokens per rank stay fixed, the routed experts are sharded e % world, shared experts are replicated).
+    Device-resident operands, CUDA-event timing."""
     st = torch.cuda.current_stream().cuda_stream
     out = {}
     int8_peak = 2.0 * peaks["bf16"]          # no measured int8 figure: twice the measured dense bf16 rate
@@ -357,33 +358,55 @@ def run_extras(torch, capi, dev, rank, world, peaks):
     torch.cuda.synchronize()
     capi.lib.b200dnn_clear_caches()
 
-    # fused MoE, configuration 4 (Mixtral-like): 4096 tokens per rank, hidden 4096, FFN 14336, 8 experts, top-2
+    # fused MoE, configurations 4 (Mixtral-like) and 5 (fine-grained, Zipf-skewed routing, 2 shared experts):
+    # tokens per rank fixed (weak scaling); one GPU runs b200dnn_moe_layer, several run the expert-parallel layer
     from zendnn_b200 import moe_ep
-    T, H, I, E, topk = 4096, 4096, 14336, 8, 2
-    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
-    logits = torch.randn(T, E, generator=g).to(dev)
-    mine = []
-    for e in moe_ep.experts_on_rank(rank, world, E):
-        ge = torch.Generator(device="cpu").manual_seed(100 + e)
-        mine.append(dict(w13=torch.randint(-127, 128, (H, 2 * I), dtype=torch.int8, generator=ge).to(dev),
-                         s13=(torch.rand(2 * I, generator=ge) * 1e-3 + 1e-4).to(dev),
-                         w2=torch.randint(-127, 128, (I, H), dtype=torch.int8, generator=ge).to(dev),
-                         s2=(torch.rand(H, generator=ge) * 1e-3 + 1e-4).to(dev)))
-    ops = moe_ep.CapiOps(mine, [], H, I, H)
-    ms = _time_events(torch, lambda: moe_ep.ep_moe_forward(x, logits, topk, E, 0, ops), 5)
-    if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    rows = T * topk
-    ops_per_layer = 2.0 * rows * H * 2 * I + 2.0 * rows * I * H
-    out["moe_mixtral_like"] = {"tokens_per_s": round(world * T / ms * 1e3), "ms_per_layer": round(ms, 3), "n_gpus": world,
-                               "tokens_per_rank": T, "experts": E, "topk": topk, "scaling": "weak",
-                               "tops_per_gpu": round(ops_per_layer / ms / 1e9, 1),
-                               "path": "expert-parallel, NCCL all-to-all dispatch/combine" if world > 1 else "single GPU"}
-    del ops, mine
-    capi.lib.b200dnn_clear_caches()
+    for name, (T, H, I, E, topk, S, zipf) in (("moe_mixtral_like", (4096, 4096, 14336, 8, 2, 0, False)),
+                                              ("moe_fine_grained", (16384, 2048, 1408, 64, 6, 2, True))):
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
+        logits = torch.randn(T, E, generator=g)
+        if zipf:
+            gz = torch.Generator(device="cpu").manual_seed(5)
+            pz = torch.arange(1, E + 1, dtype=torch.float64) ** -1.1
+            logits = logits + torch.log(pz / pz.sum())[torch.randperm(E, generator=gz)].float()
+        logits = logits.contiguous().to(dev)
+
+        def expert(e):
+            ge = torch.Generator(device="cpu").manual_seed(100 + e)
+            return dict(w13=torch.randint(-127, 128, (H, 2 * I), dtype=torch.int8, generator=ge).to(dev),
+                        s13=(torch.rand(2 * I, generator=ge) * 1e-3 + 1e-4).to(dev),
+                        w2=torch.randint(-127, 128, (I, H), dtype=torch.int8, generator=ge).to(dev),
+                        s2=(torch.rand(H, generator=ge) * 1e-3 + 1e-4).to(dev))
+        shared = [expert(E + j) for j in range(S)]
+        if world == 1:
+            every = [expert(e) for e in range(E)] + shared
+            ex = (capi.MoeExpert * len(every))()
+            for i, w in enumerate(every):
+                ex[i].w13, ex[i].ldb13, ex[i].w13_scale = w["w13"].data_ptr(), 2 * I, w["s13"].data_ptr()
+                ex[i].w2, ex[i].ldb2, ex[i].w2_scale = w["w2"].data_ptr(), H, w["s2"].data_ptr()
+            o = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+            ms = _time_events(torch, lambda: capi.check(capi.lib.b200dnn_moe_layer(
+                x.data_ptr(), H, logits.data_ptr(), T, E, S, topk, ex, H, I, H, 0, capi.ACT["silu_and_mul"], o.data_ptr(), H, st)), 5)
+            path = "single GPU, b200dnn_moe_layer"
+            del every, ex, o
+        else:
+            mine = [expert(e) for e in moe_ep.experts_on_rank(rank, world, E)]
+            ops = moe_ep.CapiOps(mine, shared, H, I, H)
+            ms = _time_events(torch, lambda: moe_ep.ep_moe_forward(x, logits, topk, E, S, ops), 5)
+            import torch.distributed as dist
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            path = "expert-parallel (expert e on rank e % N), NCCL all-to-all dispatch/combine"
+            del ops, mine
+        rows = T * (topk + S)
+        ops_per_layer = 2.0 * rows * H * 2 * I + 2.0 * rows * I * H
+        out[name] = {"tokens_per_s": round(world * T / ms * 1e3), "ms_per_layer": round(ms, 3), "n_gpus": world,
+                     "tokens_per_rank": T, "experts": E, "topk": topk, "shared_experts": S, "scaling": "weak",
+                     "tops_per_gpu": round(ops_per_layer / ms / 1e9, 1), "path": path}
+        del shared, x, logits
+        capi.lib.b200dnn_clear_caches()
+        torch.cuda.empty_cache()
     return out
 
 

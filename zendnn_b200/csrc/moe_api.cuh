@@ -110,7 +110,7 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
     A1_in = (const uint8_t *)qa.src; lda1 = qa.src_ld; s1_in = (const float *)qa.scale;
   } else {
     qa.dst = A1; qa.dst_ld = Kq; qa.scale = s1; qa.scale_dt = B200DNN_F32; qa.K = K;
-    B2_TRY(launch_quant_rows(qa, src_dt, R, st));
+    B2_TRY(launch_quant_rows(qa, src_dt, qa.scatter ? qa.scatter_rows : R, st));
   }
 
   // 2. first GEMM with the gated epilogue -> Z (bf16, [R, I]) and per-row max |Z|
@@ -286,7 +286,10 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   std::vector<ExpertWeightsIn> ew(G);
   for (int g = 0; g < G; ++g) ew[g] = ExpertWeightsIn{ex[g].w13, ex[g].ldb13, ex[g].w13_scale, ex[g].w2, ex[g].ldb2, ex[g].w2_scale};
   RowQuantArgs qa{};
-  qa.src = x_dev; qa.src_ld = ldx; qa.gather = row_token; qa.gather_div = 1;
+  // every token is quantised once and written to the rows of all its slots (routed and shared experts)
+  qa.src = x_dev; qa.src_ld = ldx; qa.gather_div = 1;
+  if (ns <= 32) { qa.scatter = slot_rows; qa.scatter_n = ns; qa.scatter_rows = T; }
+  else qa.gather = row_token;
   void *O = nullptr; int64_t ldO = 0;
   const int m_tiles_bound = (R + kTcBM - 1) / kTcBM + G;
   B2_TRY(moe_core(G, ew, K, I, H, transB, act, 1, qa, B200DNN_BF16, R, row_off, tile_prefix, m_tiles_bound, nullptr, nullptr, &O, &ldO, st));

@@ -45,6 +45,9 @@ struct RowQuantArgs {
   int8_t *dst; int64_t dst_ld;          // may be null (scales only)
   void *scale; int32_t scale_dt;        // f32 or bf16, one per row
   const uint32_t *absmax_bits;          // optional: per-row abs-max already known (float bits)
+  // scatter form: source row r is quantised once and written to the rows scatter[r*scatter_n + j] of dst / scale
+  // (entries < 0 skipped): a token routed to several experts is quantised once, not once per expert
+  const int32_t *scatter; int32_t scatter_n; int32_t scatter_rows;
   int32_t K;
   // grouped form (used when n_groups > 0): row r belongs to the group with row_off[g] <= r < row_off[g+1]
   int32_t n_groups;
@@ -97,6 +100,8 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
     dst = a.dst ? a.dst + (int64_t)r * a.dst_ld : nullptr;
     scale_out = a.scale; scale_idx = r;
   }
+  const int32_t *sc = (a.scatter && a.n_groups == 0) ? a.scatter + (int64_t)r * a.scatter_n : nullptr;
+  if (sc) dst = a.dst;     // row offsets are applied per destination
   const int K = a.K;
   const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (K % E == 0) &&
                    (!dst || (reinterpret_cast<uintptr_t>(dst) % E) == 0);
@@ -129,19 +134,31 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
   if (a.absmax_bits) scale = scale_from_absmax(__uint_as_float(a.absmax_bits[r]));
   else scale = scale_from_absmax(block_max(amax, sh));
   if (threadIdx.x == 0 && scale_out) {
-    if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(scale_out)[scale_idx] = f32_to_bf16_bits(scale);
+    if (sc) {
+      for (int j = 0; j < a.scatter_n; ++j) {
+        const int d = sc[j];
+        if (d < 0) continue;
+        if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(scale_out)[d] = f32_to_bf16_bits(scale);
+        else reinterpret_cast<float *>(scale_out)[d] = scale;
+      }
+    } else if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(scale_out)[scale_idx] = f32_to_bf16_bits(scale);
     else reinterpret_cast<float *>(scale_out)[scale_idx] = scale;
   }
   if (!dst) return;
   const float rinv = __frcp_rn(scale);
   if (vec) {
+    auto put = [&](int8_t *row, const int8_t (&o)[E], int v) {
+      if (E == 8) reinterpret_cast<uint2 *>(row)[v] = *reinterpret_cast<const uint2 *>(o);
+      else reinterpret_cast<uint32_t *>(row)[v] = *reinterpret_cast<const uint32_t *>(o);
+    };
     auto emit = [&](const uint4 &q, int v) {
       const T *e = reinterpret_cast<const T *>(&q);
-      int8_t o[E];
+      __align__(8) int8_t o[E];
 #pragma unroll
       for (int i = 0; i < E; ++i) o[i] = quant_sym_r(elem_to_f32<T>(e[i]), scale, rinv);
-      if (E == 8) reinterpret_cast<uint2 *>(dst)[v] = *reinterpret_cast<uint2 *>(o);
-      else reinterpret_cast<uint32_t *>(dst)[v] = *reinterpret_cast<uint32_t *>(o);
+      if (sc) {
+        for (int j = 0; j < a.scatter_n; ++j) { const int d = sc[j]; if (d >= 0) put(dst + (int64_t)d * a.dst_ld, o, v); }
+      } else put(dst, o, v);
     };
 #pragma unroll
     for (int j = 0; j < kQuantRegVec; ++j) {
@@ -151,7 +168,12 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
     for (int v = threadIdx.x + kQuantRegVec * kQuantThreads; v < nvec; v += kQuantThreads)
       emit(reinterpret_cast<const uint4 *>(src)[v], v);
   } else {
-    for (int k = threadIdx.x; k < K; k += kQuantThreads) dst[k] = quant_sym_r(elem_to_f32<T>(src[k]), scale, rinv);
+    for (int k = threadIdx.x; k < K; k += kQuantThreads) {
+      const int8_t qv = quant_sym_r(elem_to_f32<T>(src[k]), scale, rinv);
+      if (sc) {
+        for (int j = 0; j < a.scatter_n; ++j) { const int d = sc[j]; if (d >= 0) dst[(int64_t)d * a.dst_ld + k] = qv; }
+      } else dst[k] = qv;
+    }
   }
 }
 
@@ -167,7 +189,8 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
   int64_t sr = r;
   if (a.gather) { int32_t s = a.gather[r]; if (s < 0) return; sr = s / a.gather_div; }
   const T *src = reinterpret_cast<const T *>(a.src) + sr * a.src_ld;
-  int8_t *dst = a.dst ? a.dst + (int64_t)r * a.dst_ld : nullptr;
+  const int32_t *sc = a.scatter ? a.scatter + (int64_t)r * a.scatter_n : nullptr;
+  int8_t *dst = a.dst ? (sc ? a.dst : a.dst + (int64_t)r * a.dst_ld) : nullptr;
   const int nvec = a.K / E;
   uint4 cache[NV];
 #pragma unroll
@@ -189,9 +212,16 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     scale = scale_from_absmax(amax);
   }
-  if (lane == 0 && a.scale) {
-    if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(a.scale)[r] = f32_to_bf16_bits(scale);
-    else reinterpret_cast<float *>(a.scale)[r] = scale;
+  if (a.scale) {
+    if (sc) {
+      if (lane < a.scatter_n && sc[lane] >= 0) {
+        if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(a.scale)[sc[lane]] = f32_to_bf16_bits(scale);
+        else reinterpret_cast<float *>(a.scale)[sc[lane]] = scale;
+      }
+    } else if (lane == 0) {
+      if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(a.scale)[r] = f32_to_bf16_bits(scale);
+      else reinterpret_cast<float *>(a.scale)[r] = scale;
+    }
   }
   if (!dst) return;
   const float rinv = __frcp_rn(scale);
@@ -200,10 +230,18 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
     const int v = lane + j * 32;
     if (v < nvec) {
       const T *e = reinterpret_cast<const T *>(&cache[j]);
-      int8_t o[E];
+      __align__(8) int8_t o[E];
 #pragma unroll
       for (int i = 0; i < E; ++i) o[i] = quant_sym_r(elem_to_f32<T>(e[i]), scale, rinv);
-      if (E == 8) reinterpret_cast<uint2 *>(dst)[v] = *reinterpret_cast<uint2 *>(o);
+      if (sc) {
+        for (int jj = 0; jj < a.scatter_n; ++jj) {
+          const int d = sc[jj];
+          if (d < 0) continue;
+          int8_t *row = dst + (int64_t)d * a.dst_ld;
+          if (E == 8) reinterpret_cast<uint2 *>(row)[v] = *reinterpret_cast<uint2 *>(o);
+          else reinterpret_cast<uint32_t *>(row)[v] = *reinterpret_cast<uint32_t *>(o);
+        }
+      } else if (E == 8) reinterpret_cast<uint2 *>(dst)[v] = *reinterpret_cast<uint2 *>(o);
       else reinterpret_cast<uint32_t *>(dst)[v] = *reinterpret_cast<uint32_t *>(o);
     }
   }

@@ -1,0 +1,123 @@
+"""Run one configured case of the library a few times on cuda:0 (for profilers and quick timing).
+
+  python -m zendnn_b200.run_case matmul <auto|decode|tc> M K N [--copies C] [--reps R] [--act gelu_tanh] [--bias] [--dyn]
+  python -m zendnn_b200.run_case moe <c4|c5> [--reps R]
+
+matmul: s8 per-token activations x s8 per-channel prepacked weight -> bf16; `--copies` distinct prepacked
+weights are used in turn (pick copies * K * N above the L2 size to keep the weight stream in HBM);
+`--dyn` passes bf16 activations with dynamic_quant.  moe: b200dnn_moe_layer at the shapes of the two MoE
+configurations (c4: 4096 tokens, hidden 4096, FFN 14336, 8 experts top-2; c5: 16384 tokens, hidden 2048,
+FFN 1408, 64 experts top-6 + 2 shared, Zipf-skewed routing).  Prints the mean time per call.
+"""
+import argparse
+import time
+
+
+def _matmul(args):
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    M, K, N = args.M, args.K, args.N
+    g = torch.Generator(device=dev).manual_seed(0)
+    packed = []
+    for _ in range(args.copies):
+        W = torch.randint(-127, 128, (K, N), generator=g, dtype=torch.int8, device=dev)
+        buf = torch.empty(capi.lib.b200dnn_prepack_size(K, N, 0), dtype=torch.uint8, device=dev)
+        capi.check(capi.lib.b200dnn_prepack(W.data_ptr(), K, N, N, 0, 0, buf.data_ptr(), st))
+        torch.cuda.synchronize()
+        packed.append(buf)
+        del W
+    sw = torch.rand(N, generator=g, device=dev) * 4e-4 + 1e-4
+    bias = torch.randn(N, generator=g, device=dev) if args.bias else None
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    force = {"auto": 0, "decode": 1, "tc": 2}[args.kernel]
+    if args.dyn:
+        A = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+        kw = dict(src_dt=capi.DT["bf16"], dynamic_quant=True, src_scale=capi.quant(None, M, capi.DT["f32"]))
+    else:
+        A = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8, device=dev)
+        sa = torch.rand(M, generator=g, device=dev) * 0.04 + 0.01
+        kw = dict(src_dt=capi.DT["s8"], src_scale=sa)
+    descs = [capi.make_matmul(M, N, K, A, b, out, dst_dt=capi.DT["bf16"], wei_format="r", wei_scale=sw, bias=bias,
+                              postops=[args.act] if args.act else [], force_kernel=force,
+                              flags=capi.FLAG_STABLE_WEIGHTS, **kw) for b in packed]
+    for d in descs:
+        capi.check(capi.matmul(d, st))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.reps):
+        for d in descs:
+            capi.check(capi.matmul(d, st))
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.reps * len(descs))
+    print("matmul %s M%d K%d N%d: %.2f us per call (stream order, not graph-replayed)" % (args.kernel, M, K, N, us))
+
+
+def _moe(args):
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    T, H, I, E, k, S, zipf = dict(c4=(4096, 4096, 14336, 8, 2, 0, False), c5=(16384, 2048, 1408, 64, 6, 2, True))[args.config]
+    g = torch.Generator(device=dev).manual_seed(0)
+    G = E + S
+    keep, ex = [], (capi.MoeExpert * G)()
+    for e in range(G):
+        w13 = torch.randint(-127, 128, (H, 2 * I), generator=g, dtype=torch.int8, device=dev)
+        w2 = torch.randint(-127, 128, (I, H), generator=g, dtype=torch.int8, device=dev)
+        s13 = torch.rand(2 * I, generator=g, device=dev) * 4e-4 + 1e-4
+        s2 = torch.rand(H, generator=g, device=dev) * 4e-4 + 1e-4
+        keep.append((w13, w2, s13, s2))
+        ex[e].w13, ex[e].ldb13, ex[e].w13_scale = w13.data_ptr(), 2 * I, s13.data_ptr()
+        ex[e].w2, ex[e].ldb2, ex[e].w2_scale = w2.data_ptr(), H, s2.data_ptr()
+    x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=dev)
+    if zipf:
+        p = torch.arange(1, E + 1, device=dev, dtype=torch.float64) ** -1.1
+        logits = (logits + torch.log(p / p.sum())[torch.randperm(E, generator=g, device=dev)].float()).contiguous()
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+
+    def call():
+        capi.check(capi.lib.b200dnn_moe_layer(x.data_ptr(), H, logits.data_ptr(), T, E, S, k, ex, H, I, H, 0,
+                                              capi.ACT["silu_and_mul"], out.data_ptr(), H, st))
+    call()
+    call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.reps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.reps
+    ops = 2 * T * (k + S) * (H * 2 * I + I * H)
+    print("moe %s: %.1f us per layer, %.0f tokens/s, %.0f TOPS (wall %.1f us)" %
+          (args.config, ms * 1e3, T / ms * 1e3, ops / ms / 1e9, (time.perf_counter() - t0) / args.reps * 1e6))
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="what", required=True)
+    m = sub.add_parser("matmul")
+    m.add_argument("kernel", choices=["auto", "decode", "tc"])
+    m.add_argument("M", type=int)
+    m.add_argument("K", type=int)
+    m.add_argument("N", type=int)
+    m.add_argument("--copies", type=int, default=4)
+    m.add_argument("--reps", type=int, default=3)
+    m.add_argument("--act", default=None)
+    m.add_argument("--bias", action="store_true")
+    m.add_argument("--dyn", action="store_true")
+    e = sub.add_parser("moe")
+    e.add_argument("config", choices=["c4", "c5"])
+    e.add_argument("--reps", type=int, default=3)
+    args = ap.parse_args()
+    (_matmul if args.what == "matmul" else _moe)(args)
+
+
+if __name__ == "__main__":
+    main()
