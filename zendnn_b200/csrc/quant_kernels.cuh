@@ -25,13 +25,15 @@ __device__ __forceinline__ int8_t quant_sym(float v, float scale) {
   if (!finite_f32(v)) return 0;
   return (int8_t)__float2int_rn(__fdiv_rn(v, scale));
 }
-// Same result as quant_sym with one multiply in the common case.  rinv = __frcp_rn(scale).  v*rinv is
-// within 1e-4 of the rounded quotient for |q| < 512, so whenever it is at least 1e-3 away from a half
-// integer both round to the same integer; the rare near-tie (and anything large or non-finite) takes the
-// exact division.
+// Same result as quant_sym without a division or a conversion instruction in the common case, for a scale that
+// comes from the abs-max of the row itself (so |v/scale| <= 127 up to rounding).  rinv = __frcp_rn(scale).
+// v*rinv is within 1e-4 of the rounded quotient, so whenever it is at least 1e-3 away from a half integer
+// both round to the same integer; adding 1.5*2^23 rounds to that integer (nearest-even) and leaves its two's
+// complement in the low mantissa byte.  The rare near-tie and every non-finite input take the exact division.
 __device__ __forceinline__ int8_t quant_sym_r(float v, float scale, float rinv) {
-  const float qa = v * rinv, t = rintf(qa);
-  if (fabsf(qa) < 512.0f && fabsf(qa - t) < 0.499f) return (int8_t)(int)t;
+  const float magic = 12582912.0f;
+  const float qa = v * rinv, m = qa + magic, t = m - magic;
+  if (fabsf(qa - t) < 0.499f) return (int8_t)(__float_as_int(m) & 0xFF);
   return quant_sym(v, scale);
 }
 
@@ -108,25 +110,28 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
   const int nvec = vec ? K / E : 0;
   uint4 cache[kQuantRegVec];
   float amax = 0.f;
+  const bool need_amax = a.absmax_bits == nullptr;   // the row maximum may be given
   if (vec) {
 #pragma unroll
     for (int j = 0; j < kQuantRegVec; ++j) {
       int v = threadIdx.x + j * kQuantThreads;
       if (v < nvec) {
         cache[j] = reinterpret_cast<const uint4 *>(src)[v];
-        const T *e = reinterpret_cast<const T *>(&cache[j]);
+        if (need_amax) {
+          const T *e = reinterpret_cast<const T *>(&cache[j]);
 #pragma unroll
-        for (int i = 0; i < E; ++i) { float f = elem_to_f32<T>(e[i]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f)); }
+          for (int i = 0; i < E; ++i) { float f = elem_to_f32<T>(e[i]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f)); }
+        }
       }
     }
-    for (int v = threadIdx.x + kQuantRegVec * kQuantThreads; v < nvec; v += kQuantThreads) {
+    for (int v = threadIdx.x + kQuantRegVec * kQuantThreads; need_amax && v < nvec; v += kQuantThreads) {
       uint4 q = reinterpret_cast<const uint4 *>(src)[v];
       const T *e = reinterpret_cast<const T *>(&q);
 #pragma unroll
       for (int i = 0; i < E; ++i) { float f = elem_to_f32<T>(e[i]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f)); }
     }
   } else {
-    for (int k = threadIdx.x; k < K; k += kQuantThreads) {
+    for (int k = threadIdx.x; need_amax && k < K; k += kQuantThreads) {
       float f = elem_to_f32<T>(src[k]); if (finite_f32(f)) amax = fmaxf(amax, fabsf(f));
     }
   }
