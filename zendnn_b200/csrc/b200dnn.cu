@@ -220,7 +220,7 @@ int32_t launch_decode_ring(const uint8_t *A, int64_t lda, bool a_unsigned, int M
   g.A = A; g.lda = lda; g.M = M; g.N = N; g.K = K; g.Wt = pw.wt; g.Kp = (int)pw.Kp;
   g.groups = (N + 7) / 8; g.blocks = (int)(pw.Kp / 128);
   g.a_stride = (int)pw.Kp + 16;
-  g.rows_staged = M > 8 ? 16 : 8;
+  g.rows_staged = M > 8 ? 16 : M;
   const int grid = g.groups < R_.sm_count ? g.groups : R_.sm_count;
   g.max_local_groups = (g.groups + grid - 1) / grid;
   g.status = R_.status;
@@ -238,7 +238,7 @@ int32_t launch_decode_ring(const uint8_t *A, int64_t lda, bool a_unsigned, int M
   g.stages = stages;
   const size_t smem = fixed + (size_t)stages * stage_bytes;
   void (*kern)(DecodeRingArgs, EpiParams) = a_unsigned ? decode_ring_kernel<true, R> : decode_ring_kernel<false, R>;
-  B2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget));
+  B2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3((kRingWarps + 1) * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];

@@ -39,7 +39,7 @@ struct DecodeRingArgs {
   int groups;                      // ceil(N / 8)
   int blocks;                      // Kp / 128: 1 KiB blocks per group
   int a_stride;                    // smem row stride of A: Kp + 16
-  int rows_staged;                 // 8 or 16
+  int rows_staged;                 // M for M <= 8, else 16
   int max_local_groups;            // ceil(groups / gridDim.x)
   int stages;                      // ring depth
   int32_t *status;                 // device word: 0 ok
@@ -142,10 +142,12 @@ __global__ void __launch_bounds__((kRingWarps + 1) * 32, 1) decode_ring_kernel(D
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
     bool ok = true;
 
-    // Rows >= M of the staged activations are never written: an output row depends only on its own
+    // Rows >= M of a 16-row staging area are never written: an output row depends only on its own
     // activation row, and rows >= M are not stored.  Columns k >= K hold zero weights.
     const bool hi_rows = g.rows_staged > 8;
-    const uint8_t *a_lo_base = smem + (size_t)lg * g.a_stride + lt * 32;
+    // M <= 8: only M rows are staged; lanes of the rows that do not exist read the last real row (their outputs are not stored)
+    const int lo_row = hi_rows ? lg : (lg < g.rows_staged ? lg : g.rows_staged - 1);
+    const uint8_t *a_lo_base = smem + (size_t)lo_row * g.a_stride + lt * 32;
     const size_t a_hi_off = (size_t)8 * g.a_stride;
     const int odd = lg & 1;
     const uint32_t w_lane = (uint32_t)warp * 1024u + (uint32_t)lg * 128u + (uint32_t)lt * 32u + (odd ? 16u : 0u);
