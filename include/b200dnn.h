@@ -225,6 +225,12 @@ B200DNN_API int32_t b200dnn_moe_sort_slots(const int32_t *keys, int32_t nslots, 
 B200DNN_API int32_t b200dnn_quant_per_token_gather(const void *src, int32_t src_dt, int64_t K, int64_t src_ld,
                                                    const int32_t *row_src, int32_t row_div, int64_t R, void *dst,
                                                    int64_t dst_ld, float *scale, void *stream);
+/* Per-token quantisation of T source rows, each written to several output rows: source row t goes to the
+ * rows dst_rows[t*n_dst + j], j < n_dst, of dst and scale (entries < 0 are skipped).  A token that is routed
+ * to several experts is quantised once. */
+B200DNN_API int32_t b200dnn_quant_per_token_scatter(const void *src, int32_t src_dt, int64_t K, int64_t src_ld,
+                                                    const int32_t *dst_rows, int32_t n_dst, int64_t T, void *dst,
+                                                    int64_t dst_ld, float *scale, void *stream);
 /* Expert computation of the fused MoE on rows that arrive already quantised (s8 [R,lda] + f32 scale
  * per row): first GEMM + gated activation + requantisation + second GEMM, out bf16 [R,H].  Rows are
  * grouped: group g has group_rows[g] consecutive rows and uses experts[group_expert[g]] (host arrays). */

@@ -33,20 +33,27 @@ class CpuOps:
         s2r[order] = torch.arange(keys.numel(), dtype=keys.dtype)
         return torch.bincount(keys.long(), minlength=nkeys).to(torch.int32), s2r
 
-    def quant_gather(self, x, row_src, div, R):
-        rows = x[(row_src.long() // div)].float()
-        s = rows.abs().amax(1).clamp_min(1e-10) / 127.0
-        return torch.round(rows / s[:, None]).to(torch.int8), s
+    def quant_scatter(self, x, dst_rows, n_rows):
+        rows = x.float()
+        sc = rows.abs().amax(1).clamp_min(1e-10) / 127.0
+        qv = torch.round(rows / sc[:, None]).to(torch.int8)
+        q = torch.zeros(n_rows, x.shape[1], dtype=torch.int8)
+        s = torch.zeros(n_rows)
+        for j in range(dst_rows.shape[1]):
+            q[dst_rows[:, j].long()] = qv
+            s[dst_rows[:, j].long()] = sc
+        return q, s
 
-    def experts(self, q, s, group_rows, group_expert):
-        out = torch.zeros(q.shape[0], self.H)
+    def experts(self, q, s, group_rows, group_expert, out):
         r = 0
         for n, j in zip(group_rows, group_expert):
             if n:
                 gid = self.ids[j]
                 out[r:r + n] = (q[r:r + n].float() * s[r:r + n, None])[:, : self.H] * (gid + 1) + gid
             r += n
-        return out
+
+    def new_rows(self, n_rows, like):
+        return torch.zeros(n_rows, self.H)
 
     def reduce_rows(self, rows, slot_rows, slot_w):
         return (rows[slot_rows.long()] * slot_w[:, :, None]).sum(1)

@@ -22,13 +22,6 @@ __global__ void tile_prefix_kernel(const int32_t *row_off, int n_groups, int32_t
   }
 }
 
-struct MoeWeights {
-  std::vector<PackedWeight> w13, w2;
-  const CUtensorMap *maps13 = nullptr, *maps2 = nullptr;   // device arrays
-  TcGroupDesc *g13 = nullptr, *g2 = nullptr;               // device arrays
-  int BN13 = 0, BN2 = 0;
-};
-
 // Uploads a host blob into workspace memory and waits for the copy (the blob is a local).
 int32_t upload_blob(const void *host, size_t bytes, cudaStream_t st, void **dev) {
   void *d = rt().ws.alloc(bytes);
@@ -357,6 +350,24 @@ extern "C" int32_t b200dnn_quant_per_token_gather(const void *src, int32_t src_d
   a.src = src; a.src_ld = src_ld; a.gather = row_src; a.gather_div = row_div; a.dst = (int8_t *)dst; a.dst_ld = dst_ld;
   a.scale = scale; a.scale_dt = B200DNN_F32; a.K = (int32_t)K;
   return launch_quant_rows(a, src_dt, R, st);
+}
+
+extern "C" int32_t b200dnn_quant_per_token_scatter(const void *src, int32_t src_dt, int64_t K, int64_t src_ld,
+                                                   const int32_t *dst_rows, int32_t n_dst, int64_t T, void *dst,
+                                                   int64_t dst_ld, float *scale, void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  rt().ws.rewind();
+  cudaStream_t st = as_stream(stream);
+  B2_CHECK(src && dst_rows && dst && scale && K > 0 && T > 0 && src_ld >= K && dst_ld >= K && n_dst > 0 && n_dst <= 32,
+           B200DNN_FAILURE, "bad argument");
+  B2_CHECK(is_device_ptr(src) && is_device_ptr(dst_rows) && is_device_ptr(dst) && is_device_ptr(scale), B200DNN_UNIMPLEMENTED,
+           "scattered quantisation takes device pointers only");
+  RowQuantArgs a{};
+  a.src = src; a.src_ld = src_ld; a.gather_div = 1; a.dst = (int8_t *)dst; a.dst_ld = dst_ld;
+  a.scale = scale; a.scale_dt = B200DNN_F32; a.K = (int32_t)K;
+  a.scatter = dst_rows; a.scatter_n = n_dst; a.scatter_rows = (int32_t)T;
+  return launch_quant_rows(a, src_dt, T, st);
 }
 
 extern "C" int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, const float *row_scale, int32_t n_groups,

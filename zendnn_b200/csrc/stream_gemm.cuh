@@ -3,7 +3,7 @@
 // sites (matmul/backends/aocl/aocl_kernel.cpp:1190-1301) and the native GEMV
 // (matmul/matmul_native/brgemm/kernel/int8/int8_gemv_bkc.cpp).
 //
-// Work decomposition.  The packed weight is W^T, [Np][Kp] int8 with K contiguous.  A warp owns 8
+// Work decomposition.  The packed weight is W^T in 1 KiB blocks [Np/8][Kp/128][8 rows][128 B of K] (pack_kernels.cuh).  A warp owns 8
 // weight rows (output columns) and a strided set of 64-byte K chunks; every lane issues 16-byte
 // loads (lane = (g,t): row g, bytes t*16.. of the chunk), so the warp reads 8 rows x 64 B per
 // load instruction and `kw` warps side by side cover 8 rows x 64*kw B.  The 16 x K activation
@@ -24,7 +24,7 @@ namespace b200 {
 struct StreamGemmArgs {
   const uint8_t *A; int64_t lda;   // [M,lda] u8 or s8
   int M, N, K;
-  const int8_t *Wt; int Kp;        // packed [Np][Kp]
+  const int8_t *Wt; int Kp;        // packed, block-interleaved (pack_kernels.cuh)
   int nb, kw;                      // n-groups (of 8 columns) and K-split warps per CTA; nb*kw == 8
   int chunks_total;                // Kp / 64
   int chunks_per_cta;              // ceil(chunks_total / gridDim.y)

@@ -4,11 +4,14 @@ The reference (a single-process CPU library) has no multi-device path; this modu
 where the W8A8 hot path has a real exchange step.  Placement: expert e lives on rank e % world (its
 local index is e // world); tokens are data-parallel, every rank routes its own tokens.  Per layer:
 
-  route local tokens -> sort (token,k) slots by (destination rank, local expert) -> quantise the
-  gathered rows to s8 + one f32 scale per row (1 byte per element crosses NVLink instead of 2) ->
-  all-to-all dispatch (rows, scales; counts exchanged first) -> grouped expert GEMMs on the received
-  rows, one group per (source rank, local expert) -> all-to-all combine of the bf16 expert outputs ->
-  weighted top-k reduce on the owning rank.  Shared experts are replicated and see the rank's tokens.
+  route local tokens -> sort (token,k) slots by (destination rank, local expert) -> quantise every
+  token once to s8 + one f32 scale and write it to the send rows of all its slots (1 byte per element
+  crosses NVLink instead of 2) and, for the replicated shared experts, to their local rows ->
+  all-to-all dispatch (rows, scales; counts exchanged first) -> ONE grouped expert computation over the
+  received rows (one group per (source rank, local expert)) and the shared experts' rows -> all-to-all
+  combine of the bf16 expert outputs -> weighted reduce on the owning rank.
+  One buffer holds [received rows | shared-expert rows | send rows] (the same layout for the outputs), so
+  the exchanges and the reduce work on views of it and nothing is concatenated or copied.
 
 Per-row arithmetic does not depend on where a row is computed, so the result equals the single-GPU
 result bit for bit.
@@ -74,28 +77,30 @@ class CapiOps:
         self.capi.check(self.capi.lib.b200dnn_moe_sort_slots(keys.data_ptr(), n, nkeys, counts.data_ptr(), s2r.data_ptr(), self._st()))
         return counts, s2r
 
-    def quant_gather(self, x, row_src, div, R):
-        K = x.shape[1]
+    def quant_scatter(self, x, dst_rows, n_rows):
+        """Quantise every row of x once and write it to the rows dst_rows[t, :] of a [n_rows, Kq] buffer."""
+        T, K = x.shape
         Kq = (K + 15) // 16 * 16
-        q = torch.empty(R, Kq, dtype=torch.int8, device=x.device)
-        s = torch.empty(R, dtype=torch.float32, device=x.device)
-        if R:
-            self.capi.check(self.capi.lib.b200dnn_quant_per_token_gather(
-                x.data_ptr(), self.capi.DT["bf16"], K, x.stride(0), row_src.data_ptr(), div, R, q.data_ptr(), Kq,
-                s.data_ptr(), self._st()))
+        q = torch.empty(n_rows, Kq, dtype=torch.int8, device=x.device)
+        s = torch.empty(n_rows, dtype=torch.float32, device=x.device)
+        self.capi.check(self.capi.lib.b200dnn_quant_per_token_scatter(
+            x.data_ptr(), self.capi.DT["bf16"], K, x.stride(0), dst_rows.data_ptr(), dst_rows.shape[1], T, q.data_ptr(), Kq,
+            s.data_ptr(), self._st()))
         return q, s
 
-    def experts(self, q, s, group_rows, group_expert):
+    def experts(self, q, s, group_rows, group_expert, out):
+        """Grouped expert computation on the rows q/s (consecutive groups); results into out[:rows]."""
         R = q.shape[0]
-        out = torch.empty(R, self.H, dtype=torch.bfloat16, device=q.device)
-        if R:
+        if R and sum(int(v) for v in group_rows):
             n = len(group_rows)
             gr = (C.c_int32 * n)(*[int(v) for v in group_rows])
             ge = (C.c_int32 * n)(*[int(v) for v in group_expert])
             self.capi.check(self.capi.lib.b200dnn_moe_experts_s8(
                 q.data_ptr(), q.stride(0), s.data_ptr(), n, gr, ge, self.struct, self.K, self.I, self.H, 0, self.act,
-                out.data_ptr(), self.H, self._st()))
-        return out
+                out.data_ptr(), out.stride(0), self._st()))
+
+    def new_rows(self, n_rows, like):
+        return torch.empty(n_rows, self.H, dtype=torch.bfloat16, device=like.device)
 
     def reduce_rows(self, rows, slot_rows, slot_w):
         T, ns = slot_rows.shape
@@ -111,55 +116,49 @@ def ep_moe_forward(x, logits, topk, num_experts, num_shared, ops, group=None, ti
     `ops.all` holds this rank's routed experts (in local order) followed by the shared experts."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     T = x.shape[0]
+    S = num_shared
     e_local = (num_experts + world - 1) // world
     ids, w = ops.route(logits, topk)
     keys = dispatch_keys(ids.reshape(-1).to(torch.int64), world, num_experts)
     counts, slot_to_row = ops.sort_slots(keys, world * e_local)
     R = T * topk
-    row_to_slot = torch.empty(R, dtype=torch.int32, device=x.device)
-    row_to_slot[slot_to_row.long()] = torch.arange(R, dtype=torch.int32, device=x.device)
-    q, s = ops.quant_gather(x, row_to_slot, topk, R)
 
-    counts_h = counts.view(world, e_local)
     if world > 1:
         recv_counts = torch.empty_like(counts)
         dist.all_to_all_single(recv_counts, counts, group=group)          # [src rank][my local expert]
-        send_split = counts_h.sum(1).tolist()
-        recv_counts_h = recv_counts.view(world, e_local).cpu()
-        recv_split = recv_counts_h.sum(1).tolist()
+        both = torch.stack([counts.view(world, e_local), recv_counts.view(world, e_local)]).cpu()
+        send_split = both[0].sum(1).tolist()
+        recv_split = both[1].sum(1).tolist()
+        group_rows = both[1].reshape(-1).tolist()
         R_recv = int(sum(recv_split))
-        q_recv = torch.empty(R_recv, q.shape[1], dtype=q.dtype, device=q.device)
-        s_recv = torch.empty(R_recv, dtype=s.dtype, device=s.device)
-        dist.all_to_all_single(q_recv, q, recv_split, send_split, group=group)
-        dist.all_to_all_single(s_recv, s, recv_split, send_split, group=group)
-        group_rows = recv_counts_h.reshape(-1).tolist()
+        base_send = R_recv + S * T                                         # rows: [received | shared | send]
     else:
-        q_recv, s_recv = q, s
         group_rows = counts.cpu().tolist()
-        send_split = recv_split = None
-    group_expert = [j for _ in range(world) for j in range(e_local)]
-    # local experts that do not exist on this rank (num_experts not divisible by world) get no rows by construction
-    n_local = getattr(ops, "n_local", e_local)
-    group_expert = [min(j, max(n_local - 1, 0)) for j in group_expert]
-    o_recv = ops.experts(q_recv, s_recv, group_rows, group_expert)
+        R_recv, base_send = R, 0                                           # rows: [routed | shared]
+    base_shared = R_recv
+    n_rows = base_shared + S * T + (R if world > 1 else 0)
+
+    # where every token's quantised row goes: its topk routed slots, then one row per shared expert
+    tok = torch.arange(T, dtype=torch.int32, device=x.device)
+    cols = [slot_to_row.view(T, topk) + base_send] + [(base_shared + j * T + tok).view(T, 1) for j in range(S)]
+    slot_rows = torch.cat(cols, 1).contiguous()
+    slot_w = w if S == 0 else torch.cat([w, torch.ones(T, S, dtype=w.dtype, device=w.device)], 1).contiguous()
+    q, s = ops.quant_scatter(x, slot_rows, n_rows)
 
     if world > 1:
-        o_back = torch.empty(R, o_recv.shape[1], dtype=o_recv.dtype, device=o_recv.device)
-        dist.all_to_all_single(o_back, o_recv, send_split, recv_split, group=group)
-    else:
-        o_back = o_recv
+        dist.all_to_all_single(q[:R_recv], q[base_send:], recv_split, send_split, group=group)
+        dist.all_to_all_single(s[:R_recv], s[base_send:], recv_split, send_split, group=group)
 
-    slot_rows = slot_to_row.view(T, topk)
-    slot_w = w
-    if num_shared:
-        ident = torch.arange(T, dtype=torch.int32, device=x.device)
-        qs, ss = ops.quant_gather(x, ident, 1, T)
-        outs = [o_back]
-        extra_rows = []
-        for j in range(num_shared):
-            outs.append(ops.experts(qs, ss, [T], [n_local + j]))
-            extra_rows.append((R + j * T + ident).view(T, 1))
-        o_back = torch.cat(outs, 0)
-        slot_rows = torch.cat([slot_rows] + extra_rows, 1).contiguous()
-        slot_w = torch.cat([w, torch.ones(T, num_shared, dtype=w.dtype, device=w.device)], 1).contiguous()
-    return ops.reduce_rows(o_back, slot_rows.contiguous(), slot_w.contiguous())
+    # one grouped computation: (source rank, local expert) groups over the received rows, then the shared experts
+    n_local = getattr(ops, "n_local", e_local)
+    # local experts that do not exist on this rank (num_experts not divisible by world) get no rows by construction
+    group_expert = [min(j, max(n_local - 1, 0)) for _ in range(world) for j in range(e_local)]
+    group_rows = list(group_rows) + [T] * S
+    group_expert = group_expert + [n_local + j for j in range(S)]
+    n_in = base_shared + S * T
+    o = ops.new_rows(n_rows, x)
+    ops.experts(q[:n_in], s[:n_in], group_rows, group_expert, o)
+
+    if world > 1:
+        dist.all_to_all_single(o[base_send:], o[:R_recv], send_split, recv_split, group=group)
+    return ops.reduce_rows(o, slot_rows, slot_w)
