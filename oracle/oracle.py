@@ -31,7 +31,8 @@ def build(force=False):
         subprocess.check_call(["make", "-C", _HERE, "-s"])
     ref_root = os.environ.get("ZENDNN_REFERENCE_ROOT", "/root/reference")
     ref = os.path.join(_HERE, "_ref", "libzendnn_ref.so")
-    if os.path.isdir(ref_root) and (force or not os.path.exists(ref)):
+    ref2 = os.path.join(_HERE, "_ref", "libzendnn_ref2.so")
+    if os.path.isdir(ref_root) and (force or not os.path.exists(ref) or not os.path.exists(ref2)):
         subprocess.check_call(["make", "-C", _HERE, "-s", "ref", "REF=" + ref_root])
 
 
@@ -72,6 +73,62 @@ def ref_lib():
             except OSError:
                 _ref = False
     return _ref or None
+
+
+_ref2 = None
+
+
+def ref2_lib():
+    """The reference's per-token quantisation kernels, gated activations and MoE weighted reduce compiled from the
+    reference tree (oracle/ref_driver2.cpp), or None when absent.  The environment variable ORACLE_REF_SCALAR=1,
+    set before the first call, makes the reference take its scalar code paths."""
+    global _ref2
+    if _ref2 is None:
+        path = os.path.join(_HERE, "_ref", "libzendnn_ref2.so")
+        try:
+            _ref2 = C.CDLL(path) if os.path.exists(path) else False
+        except OSError:
+            _ref2 = False
+    return _ref2 or None
+
+
+def ref2_quant_per_token(x, native=False):
+    """Reference dynamic per-token quantisation (scalar kernel, or the AVX-512 one).  None if unavailable."""
+    r = ref2_lib()
+    x = np.ascontiguousarray(x)
+    M, K = x.shape
+    q = np.zeros((M, K), dtype=np.int8)
+    s = np.zeros(M, dtype=np.float32)
+    if r is None or (native and not r.ref2_avx512()):
+        return None
+    rc = r.ref2_quant_per_token(_p(x), int(x.dtype == np.uint16), _p(q), _p(s), C.c_int64(M), C.c_int64(K), int(native))
+    return (q, s) if rc == 0 else None
+
+
+def ref2_gated_act(y, act):
+    """Reference gated activation (in place in the reference; here on a copy).  y [M, 2I] f32 or bf16 bits."""
+    r = ref2_lib()
+    if r is None:
+        return None
+    buf = np.ascontiguousarray(y).copy()
+    M, N = buf.shape
+    r.ref2_gated_act(ACT[act], _p(buf), M, N, N, DT["bf16"] if buf.dtype == np.uint16 else DT["f32"])
+    return np.ascontiguousarray(buf[:, : N // 2])
+
+
+def ref2_moe_reduce(rows, weights, topk, skip_weighted=False, threads=1):
+    """Reference MoE weighted reduce over rows [T*topk, D] (f32 or bf16 bits), weights [T, topk]."""
+    r = ref2_lib()
+    if r is None:
+        return None
+    rows = np.ascontiguousarray(rows)
+    T, D = rows.shape[0] // topk, rows.shape[1]
+    w = np.ascontiguousarray(weights, dtype=np.float32)
+    ptrs = (C.c_void_p * (T * topk))(*[rows.ctypes.data + i * rows.strides[0] for i in range(T * topk)])
+    out = np.zeros((T, D), dtype=rows.dtype)
+    rc = r.ref2_moe_reduce(ptrs, _p(w), int(skip_weighted), T, topk, D, DT["bf16"] if rows.dtype == np.uint16 else DT["f32"],
+                           _p(out), D, threads)
+    return out if rc == 1 else None
 
 
 def _p(a):

@@ -11,13 +11,21 @@
  * Each function cites the reference file:line it follows (paths relative to the reference
  * root).
  *
- * Parity pin: the "order B" epilogue below is checked bit-for-bit against the reference's
- * own AVX-512 VNNI tile kernel (int8_brgemm_ukernel.cpp) compiled from the reference
- * sources, and the outputs of that kernel are committed as golden fixtures.  The quantise,
- * gated-activation and weighted-reduce functions follow scalar reference code that has no
- * golden vectors in the reference tests (its tests are differential); for those parity is
- * pinned by formula only.  The router (softmax/top-k/renormalise) has no counterpart in the
- * reference at all: parity unpinned.
+ * Parity pins, all against code compiled from the reference tree where it lies (oracle/Makefile,
+ * oracle/ref_driver.cpp, oracle/ref_driver2.cpp) with the outputs committed as fixtures under
+ * tests/golden/:
+ *   - the "order B" epilogue equals the reference's AVX-512 VNNI tile kernel
+ *     (int8_brgemm_ukernel.cpp) bit for bit;
+ *   - per-token quantisation equals the reference's scalar kernel
+ *     (dynamic_per_token_ref_kernel.cpp) and its AVX-512 kernel
+ *     (per_token_avx512_f32_fma_kernel.cpp) bit for bit, non-finite and all-zero rows included;
+ *   - the gated activations equal the reference's scalar path (group_matmul_moe_act.cpp) bit for
+ *     bit; its AVX-512 path (polynomial exponentials) is within 2 bf16 ulp;
+ *   - the weighted reduce equals the reference's AVX-512 path in its fused form and the
+ *     reference's scalar path in its unfused form (group_matmul_moe_postop.cpp), bit for bit.
+ * Per-channel weight quantisation and the static quantise / dequantise follow scalar reference
+ * code without a compiled cross-check: pinned by formula.  The router (softmax / top-k /
+ * renormalise) has no counterpart in the reference at all: parity unpinned.
  *
  * Build: see oracle/Makefile (gcc -O2 -fopenmp -ffp-contract=off; the VNNI loop is selected
  * at run time so the same .so runs on hosts without AVX-512).

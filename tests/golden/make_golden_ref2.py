@@ -1,0 +1,73 @@
+"""Generates tests/golden/ref2_cases.npz from more of the REFERENCE's own code: the dynamic per-token
+quantisation kernels, the gated activations (AVX-512 and scalar paths) and the MoE weighted reduce.
+
+Run in a container that has the reference checkout (default /root/reference) and AVX-512:
+    python tests/golden/make_golden_ref2.py
+It builds oracle/_ref/libzendnn_ref2.so from the reference sources (oracle/Makefile, oracle/ref_driver2.cpp),
+runs the reference functions on seeded inputs and stores inputs and outputs.  The scalar paths are produced by
+a child process started with ORACLE_REF_SCALAR=1.  The fixtures travel with the repository; the reference
+does not.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from oracle import oracle as O  # noqa: E402
+
+ACTS = ["silu_and_mul", "gelu_and_mul", "swiglu_oai_mul"]
+
+
+def inputs():
+    rng = np.random.default_rng(77)
+    x32 = (rng.normal(size=(12, 520)) * rng.uniform(0.01, 30, size=(12, 1))).astype(np.float32)
+    x32[0, :3] = [np.inf, -np.inf, np.nan]
+    x32[2, :] = 0
+    y32 = (rng.normal(size=(16, 256)) * 3).astype(np.float32)
+    rows32 = rng.normal(size=(16 * 3, 136)).astype(np.float32)
+    w = rng.uniform(0, 1, size=(16, 3)).astype(np.float32)
+    return x32, y32, rows32, w
+
+
+def run(tag):
+    x32, y32, rows32, w = inputs()
+    out = {}
+    for dt in ("bf16", "f32"):
+        x = O.f32_to_bf16(x32) if dt == "bf16" else x32
+        y = O.f32_to_bf16(y32) if dt == "bf16" else y32
+        rows = O.f32_to_bf16(rows32) if dt == "bf16" else rows32
+        native = tag == "vec"
+        q, s = O.ref2_quant_per_token(x, native=native)
+        out["quant_%s_%s_q" % (dt, tag)], out["quant_%s_%s_s" % (dt, tag)] = q, s
+        for a in ACTS:
+            out["act_%s_%s_%s" % (a, dt, tag)] = O.ref2_gated_act(y, a)
+        for skip in (0, 1):
+            out["reduce_%s_skip%d_%s" % (dt, skip, tag)] = O.ref2_moe_reduce(rows, w, 3, bool(skip), threads=2)
+    return out
+
+
+def main():
+    O.build()
+    assert O.ref2_lib() is not None, "libzendnn_ref2.so unavailable (needs a reference checkout)"
+    here = os.path.dirname(os.path.abspath(__file__))
+    if len(sys.argv) > 1 and sys.argv[1] == "--scalar-child":
+        np.savez_compressed(sys.argv[2], **run("scalar"))
+        return
+    out = run("vec")
+    tmp = os.path.join(here, "_scalar_tmp.npz")
+    subprocess.check_call([sys.executable, os.path.abspath(__file__), "--scalar-child", tmp],
+                          env=dict(os.environ, ORACLE_REF_SCALAR="1"))
+    out.update(dict(np.load(tmp)))
+    os.remove(tmp)
+    x32, y32, rows32, w = inputs()
+    out.update(x32=x32, y32=y32, rows32=rows32, w=w)
+    path = os.path.join(here, "ref2_cases.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()

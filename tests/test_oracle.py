@@ -169,3 +169,73 @@ def test_fused_moe_flow_small(oracle):
     a, b = oracle.bf16_to_f32(out), oracle.bf16_to_f32(out2)
     assert np.abs(a).sum() > 1e-3            # anti-vacuity, as the reference's fused-MoE tests do
     assert np.allclose(a, b, rtol=0.05, atol=2e-3)
+
+
+# ---- the reference's own quantisation, gated-activation and weighted-reduce code (tests/golden/make_golden_ref2.py)
+ACTS = ["silu_and_mul", "gelu_and_mul", "swiglu_oai_mul"]
+
+
+@pytest.fixture(scope="module")
+def golden2():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref2_cases.npz"))
+
+
+def _as(oracle, a32, dt):
+    return oracle.f32_to_bf16(a32) if dt == "bf16" else a32
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_quant_per_token_equals_reference_kernels(oracle, golden2, dt):
+    """Scales and s8 values equal the reference's scalar kernel and its AVX-512 kernel bit for bit
+    (rows with inf / nan entries and an all-zero row included)."""
+    q, s = oracle.quant_per_token(_as(oracle, golden2["x32"], dt))
+    for tag in ("scalar", "vec"):
+        assert (s == golden2["quant_%s_%s_s" % (dt, tag)]).all(), tag
+        assert (q == golden2["quant_%s_%s_q" % (dt, tag)]).all(), tag
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("act", ACTS)
+def test_gated_act_equals_reference_scalar_path(oracle, golden2, act, dt):
+    """Bit-exact against the reference's scalar activation path; its AVX-512 path uses polynomial
+    exponentials and stays within 2 bf16 ulp (relative 1e-4 in f32 away from cancellation)."""
+    got = oracle.gated_act(_as(oracle, golden2["y32"], dt), act)
+    assert (got == golden2["act_%s_%s_scalar" % (act, dt)]).all()
+    vec = golden2["act_%s_%s_vec" % (act, dt)]
+    if dt == "bf16":
+        assert np.abs(got.astype(np.int32) - vec.astype(np.int32)).max() <= 2
+    else:
+        assert np.allclose(got, vec, rtol=2e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("skip", [0, 1])
+def test_weighted_reduce_equals_reference(oracle, golden2, dt, skip):
+    """The oracle's fused form (multiply, then fused multiply-adds) is the reference's AVX-512 path, its unfused form
+    the reference's scalar path: both bit for bit."""
+    rows = _as(oracle, golden2["rows32"], dt)
+    for tag, fused in (("vec", True), ("scalar", False)):
+        got = oracle.moe_weighted_reduce(rows, golden2["w"], 3, skip_weighted=bool(skip), fused=fused)
+        assert (got == golden2["reduce_%s_skip%d_%s" % (dt, skip, tag)]).all(), tag
+
+
+def test_live_reference_quant_act_reduce_if_present(oracle):
+    """Where oracle/_ref/libzendnn_ref2.so exists (built from a reference checkout) the same comparisons run live
+    on fresh inputs."""
+    if oracle.ref2_lib() is None:
+        pytest.skip("libzendnn_ref2.so not built")
+    rng = np.random.default_rng(5)
+    x = oracle.f32_to_bf16((rng.normal(size=(9, 1000)) * 5).astype(np.float32))
+    q, s = oracle.quant_per_token(x)
+    for native in (False, True):
+        r = oracle.ref2_quant_per_token(x, native=native)
+        if r is not None:
+            assert (r[0] == q).all() and (r[1] == s).all()
+    rows = oracle.f32_to_bf16(rng.normal(size=(40, 200)).astype(np.float32))
+    w = rng.uniform(0, 1, size=(10, 4)).astype(np.float32)
+    assert (oracle.ref2_moe_reduce(rows, w, 4) == oracle.moe_weighted_reduce(rows, w, 4, fused=True)).all()
+    y = oracle.f32_to_bf16((rng.normal(size=(8, 128)) * 2).astype(np.float32))
+    for act in ACTS:
+        d = np.abs(oracle.ref2_gated_act(y, act).astype(np.int32) - oracle.gated_act(y, act).astype(np.int32))
+        assert d.max() <= 2
