@@ -131,6 +131,36 @@ def ref2_moe_reduce(rows, weights, topk, skip_weighted=False, threads=1):
     return out if rc == 1 else None
 
 
+def ref2_dyn_scales(x, per_channel=True):
+    """Reference dynamic scales (compute_dynamic_quant_params) of a [M,N] matrix, symmetric s8 target."""
+    r = ref2_lib()
+    if r is None:
+        return None
+    x = np.ascontiguousarray(x)
+    M, N = x.shape
+    s = np.zeros(N if per_channel else 1, dtype=np.float32)
+    rc = r.ref2_dyn_scales(_p(x), DT["bf16"] if x.dtype == np.uint16 else DT["f32"], C.c_int64(M), C.c_int64(N),
+                           int(per_channel), _p(s))
+    return s if rc == 1 else None
+
+
+def ref2_granular(src, dst_dt, scale, zp=None):
+    """Reference static quantise / dequantise (scalar granular implementation).  scale [sr,sc] f32, zp [zr,zc] s32."""
+    r = ref2_lib()
+    if r is None:
+        return None
+    src = np.ascontiguousarray(src)
+    M, N = src.shape
+    names = {np.dtype(np.uint16): "bf16", np.dtype(np.float32): "f32", np.dtype(np.int8): "s8", np.dtype(np.uint8): "u8"}
+    dst = np.zeros((M, N), dtype={"s8": np.int8, "u8": np.uint8, "f32": np.float32, "bf16": np.uint16}[dst_dt])
+    sc = np.ascontiguousarray(np.asarray(scale, dtype=np.float32).reshape(np.asarray(scale).shape if np.asarray(scale).ndim == 2 else (1, -1)))
+    z = None if zp is None else np.ascontiguousarray(np.asarray(zp, dtype=np.int32).reshape(1, -1))
+    r.ref2_granular(_p(src), DT[names[src.dtype]], _p(dst), DT[dst_dt], C.c_int64(M), C.c_int64(N), _p(sc),
+                    C.c_int64(sc.shape[0]), C.c_int64(sc.shape[1]), _p(z), C.c_int64(1 if z is not None else 0),
+                    C.c_int64(z.shape[1] if z is not None else 0))
+    return dst
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

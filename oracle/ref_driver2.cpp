@@ -8,10 +8,14 @@
 //   reorder/reorder_data_type/dynamic_quant_impl/per_token_avx512_f32_fma_kernel.cpp
 //   matmul/group_matmul/group_matmul_moe_act.cpp
 //   matmul/group_matmul/group_matmul_moe_postop.cpp
+//   reorder/lowoha_reorder_utils.cpp (compute_dynamic_quant_params: per-channel / per-tensor dynamic scales)
+//   reorder/reorder_data_type/scalar_impl/scalar_granular_impl.cpp (static quantise / dequantise with granular scales)
 #include <cstdint>
 #include <vector>
 
 #include "lowoha_operators/matmul/group_matmul/group_matmul_direct.hpp"
+#include "lowoha_operators/reorder/lowoha_reorder_utils.hpp"
+#include "lowoha_operators/reorder/reorder_data_type/scalar_impl/scalar_kernels.hpp"
 
 namespace zendnnl { namespace lowoha { namespace reorder {
 void dynamic_per_token_quant_bf16_s8_ref(const uint16_t *, int8_t *, float *, int64_t, int64_t);
@@ -56,4 +60,35 @@ API int ref2_moe_reduce(const void **row_ptrs, const float *weights, int skip_we
   p.num_tokens = T; p.topk = topk; p.output = out; p.ldc_output = ld_out; p.topk_weights = weights;
   p.skip_weighted = skip_weighted != 0; p.row_ptrs = row_ptrs;
   return (int)group_matmul_moe_postop_execute(&p, D, num_threads, (zendnnl::common::data_type_t)dt);
+}
+
+// Dynamic scales of a [M,N] matrix (f32 or bf16 bits, contiguous): per_channel -> scale[N] (dims {1,N}), else one
+// scale (dims {1,1}); symmetric s8 target.  Returns the reference's status_t.
+API int ref2_dyn_scales(const void *src, int src_dt, int64_t M, int64_t N, int per_channel, float *scale) {
+  using namespace zendnnl::lowoha::reorder;
+  reorder_params_t p;
+  p.src_dtype = (zendnnl::common::data_type_t)src_dt; p.dst_dtype = zendnnl::common::data_type_t::s8;
+  p.src_shape = {M, N}; p.dst_shape = {M, N}; p.dynamic_quant = true; p.num_threads = 1;
+  p.quant_params.scale.buff = scale; p.quant_params.scale.dt = zendnnl::common::data_type_t::f32;
+  p.quant_params.scale.dims = per_channel ? std::vector<int64_t>{1, N} : std::vector<int64_t>{1, 1};
+  return (int)compute_dynamic_quant_params(src, p);
+}
+
+// Static quantise (src f32/bf16 -> dst s8/u8) or dequantise (src s8/u8 -> dst f32/bf16) of a contiguous [M,N]
+// matrix with scale dims {sr, sc} (f32) and optional zero point dims {zr, zc} (s32), through the reference's
+// scalar granular implementation.
+API int ref2_granular(const void *src, int src_dt, void *dst, int dst_dt, int64_t M, int64_t N, float *scale, int64_t sr,
+                      int64_t sc, int32_t *zp, int64_t zr, int64_t zc) {
+  using namespace zendnnl::lowoha::reorder;
+  reorder_params_t p;
+  p.src_dtype = (zendnnl::common::data_type_t)src_dt; p.dst_dtype = (zendnnl::common::data_type_t)dst_dt;
+  p.src_shape = {M, N}; p.dst_shape = {M, N}; p.num_threads = 1;
+  p.quant_params.scale.buff = scale; p.quant_params.scale.dt = zendnnl::common::data_type_t::f32;
+  p.quant_params.scale.dims = {sr, sc};
+  if (zp) {
+    p.quant_params.zero_point.buff = zp; p.quant_params.zero_point.dt = zendnnl::common::data_type_t::s32;
+    p.quant_params.zero_point.dims = {zr, zc};
+  }
+  reorder_granular_scaler_impl_2d(src, dst, p);
+  return 0;
 }

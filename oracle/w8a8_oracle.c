@@ -23,9 +23,11 @@
  *     bit; its AVX-512 path (polynomial exponentials) is within 2 bf16 ulp;
  *   - the weighted reduce equals the reference's AVX-512 path in its fused form and the
  *     reference's scalar path in its unfused form (group_matmul_moe_postop.cpp), bit for bit.
- * Per-channel weight quantisation and the static quantise / dequantise follow scalar reference
- * code without a compiled cross-check: pinned by formula.  The router (softmax / top-k /
- * renormalise) has no counterpart in the reference at all: parity unpinned.
+ *   - the per-channel / per-tensor dynamic scales equal compute_dynamic_quant_params
+ *     (lowoha_reorder_utils.cpp) and the static quantise / dequantise equal the reference's scalar
+ *     granular implementation (scalar_granular_impl.cpp), bit for bit.
+ * The router (softmax / top-k / renormalise) has no counterpart in the reference at all: parity
+ * unpinned.
  *
  * Build: see oracle/Makefile (gcc -O2 -fopenmp -ffp-contract=off; the VNNI loop is selected
  * at run time so the same .so runs on hosts without AVX-512).

@@ -1,5 +1,6 @@
 """Generates tests/golden/ref2_cases.npz from more of the REFERENCE's own code: the dynamic per-token
-quantisation kernels, the gated activations (AVX-512 and scalar paths) and the MoE weighted reduce.
+quantisation kernels, the gated activations (AVX-512 and scalar paths), the MoE weighted reduce, the per-channel /
+per-tensor dynamic scales and the static quantise / dequantise.
 
 Run in a container that has the reference checkout (default /root/reference) and AVX-512:
     python tests/golden/make_golden_ref2.py
@@ -32,6 +33,14 @@ def inputs():
     return x32, y32, rows32, w
 
 
+def weight_input():
+    rng = np.random.default_rng(78)
+    w32 = (rng.normal(size=(70, 45)) * 0.05).astype(np.float32)
+    w32[3, 4] = np.inf
+    w32[:, 7] = 0
+    return w32
+
+
 def run(tag):
     x32, y32, rows32, w = inputs()
     out = {}
@@ -46,6 +55,17 @@ def run(tag):
             out["act_%s_%s_%s" % (a, dt, tag)] = O.ref2_gated_act(y, a)
         for skip in (0, 1):
             out["reduce_%s_skip%d_%s" % (dt, skip, tag)] = O.ref2_moe_reduce(rows, w, 3, bool(skip), threads=2)
+    if tag == "vec":     # these reference functions have a single (scalar) implementation
+        w32 = weight_input()
+        for dt in ("bf16", "f32"):
+            wv = O.f32_to_bf16(w32) if dt == "bf16" else w32
+            sc = O.ref2_dyn_scales(wv, True)
+            out["dyn_pc_" + dt], out["dyn_pt_" + dt] = sc, O.ref2_dyn_scales(wv, False)
+            q = O.ref2_granular(wv, "s8", sc.reshape(1, -1))
+            out["qs8_" + dt] = q
+            out["qu8_" + dt] = O.ref2_granular(wv, "u8", np.array([[0.002]], dtype=np.float32), np.array([13], dtype=np.int32))
+            out["deq_" + dt] = O.ref2_granular(q, dt, sc.reshape(1, -1))
+        out["w32"] = w32
     return out
 
 

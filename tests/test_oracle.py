@@ -220,6 +220,21 @@ def test_weighted_reduce_equals_reference(oracle, golden2, dt, skip):
         assert (got == golden2["reduce_%s_skip%d_%s" % (dt, skip, tag)]).all(), tag
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_dynamic_scales_and_static_quant_equal_reference(oracle, golden2, dt):
+    """Per-channel / per-tensor dynamic scales (a column of zeros and an inf entry included), static quantise to s8 with
+    per-channel scales and to u8 with a zero point, and dequantise: all bit for bit."""
+    w = _as(oracle, golden2["w32"], dt)
+    sc = oracle.dyn_scales(w, per_channel=True).astype(np.float32).reshape(-1)
+    assert (sc == golden2["dyn_pc_" + dt]).all()
+    assert (np.asarray(oracle.dyn_scales(w, per_channel=False)).reshape(-1) == golden2["dyn_pt_" + dt]).all()
+    q = oracle.quant_static(w, sc.reshape(1, -1), None, "s8")
+    assert (q == golden2["qs8_" + dt]).all()
+    qu = oracle.quant_static(w, np.array([0.002], dtype=np.float32), np.array([13], dtype=np.int32), "u8")
+    assert (qu == golden2["qu8_" + dt]).all()
+    assert (oracle.dequant_static(q, sc.reshape(1, -1), None, dt) == golden2["deq_" + dt]).all()
+
+
 def test_live_reference_quant_act_reduce_if_present(oracle):
     """Where oracle/_ref/libzendnn_ref2.so exists (built from a reference checkout) the same comparisons run live
     on fresh inputs."""
