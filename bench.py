@@ -123,9 +123,6 @@ def run_ours(args, rank, world, local_rank):
     from zendnn_b200 import capi
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
     assert capi.lib.b200dnn_device_count() > 0
     rng = np.random.default_rng(1234 + rank)
     shapes = make_decode_inputs(rng)
@@ -168,13 +165,23 @@ def run_ours(args, rank, world, local_rank):
     inner = args.inner
     one_pass(stream)
     torch.cuda.synchronize()
+    if world > 1:
+        # the process group is created after the operands: the replicas exchange nothing, the group only
+        # serves the barrier and the max over ranks
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
     side = torch.cuda.Stream()
     graph = torch.cuda.CUDAGraph()
+    # one pass per graph by default; the host needs about 2.5 us to launch it (host_enqueue_ms_per_step in the output)
+    per_graph = max(1, min(inner, args.passes_per_graph))
+    while inner % per_graph:
+        per_graph -= 1
     with torch.cuda.graph(graph, stream=side):
-        one_pass(torch.cuda.current_stream().cuda_stream)
+        for _ in range(per_graph):
+            one_pass(torch.cuda.current_stream().cuda_stream)
 
     def step():
-        for _ in range(inner):
+        for _ in range(inner // per_graph):
             graph.replay()
 
     step_bytes *= inner
@@ -190,8 +197,10 @@ def run_ours(args, rank, world, local_rank):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
+    t_host = time.perf_counter()
     for _ in range(args.steps):
         step()
+    host_ms = (time.perf_counter() - t_host) * 1e3        # time the host needed to enqueue the timed region
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
@@ -199,9 +208,12 @@ def run_ours(args, rank, world, local_rank):
     clocks = sampler.stop()
     if world > 1:
         import torch.distributed as dist
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        every = [torch.zeros(1, device=dev) for _ in range(world)]
+        dist.all_gather(every, torch.tensor([ms], device=dev))
+        ms_per_rank = [round(float(v.item()) / args.steps, 4) for v in every]
+        ms = max(float(v.item()) for v in every)
+    else:
+        ms_per_rank = [round(ms / args.steps, 4)]
 
     # per-combination timing (device resident), for the breakdown
     per = {}
@@ -270,11 +282,12 @@ def run_ours(args, rank, world, local_rank):
                                "s8 per-token x s8 per-channel prepacked, bf16 out",
                    "gemm_launches_per_step": n_launch_step, "bytes_per_step": step_bytes,
                    "l2_policy": "weights rotate over >126 MB of distinct prepacked copies per shape",
-                   "passes_per_step": inner, "launch": "one CUDA graph per pass of the grid",
+                   "passes_per_step": inner, "launch": "CUDA graphs of %d passes of the grid" % per_graph,
                    "parallelism": "replicas" if world > 1 else "single"},
         "e2e": {"value": round(world * step_bytes / e2e_s / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
-        "gpu_launches": int(launches),
+        "gpu_launches": int(launches), "ms_per_step_by_rank": ms_per_rank,
+        "host_enqueue_ms_per_step": round(host_ms / args.steps, 3),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm"], 4),
@@ -484,6 +497,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode"])
     ap.add_argument("--inner", type=int, default=100, help="passes over the decode grid per step")
+    ap.add_argument("--passes-per-graph", type=int, default=1, help="passes captured in one CUDA graph")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill and MoE measurements reported under 'also'")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
