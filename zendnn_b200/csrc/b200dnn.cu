@@ -250,14 +250,29 @@ int32_t launch_decode_ring(const uint8_t *A, int64_t lda, bool a_unsigned, int M
   return B200DNN_SUCCESS;
 }
 
+// Tile width.  With at least one tile per SM the candidates are the multiples of 32 from 256 down to 128 (multiples of
+// 64 in the gated form) and the cost of a candidate is its number of waves over the SMs times (width + 16): the last,
+// partly filled wave of a persistent grid can cost more than a narrower tile does (M=2048, N=14336: 896 tiles of 256
+// columns are 7 waves on 148 SMs, 1024 tiles of 224 columns are 7 waves as well and each is an eighth shorter).
+// Smaller problems take the widest tile that still gives every SM one.
 int pick_bn(int m_tiles, int N, int sm_count, int gated) {
   int forced = env_int("B200DNN_TC_BN", 0);
   if (forced > 0) return forced;
-  const int cands[4] = {256, 128, 64, 32};
-  for (int i = 0; i < 4; ++i) {
+  const int step = gated ? 64 : 32;
+  if ((long long)m_tiles * ((N + 127) / 128) >= sm_count) {
+    int best = 256; long long best_cost = -1;
+    for (int bn = 256; bn >= 128; bn -= step) {
+      const long long tiles = (long long)m_tiles * ((N + bn - 1) / bn);
+      const long long cost = ((tiles + sm_count - 1) / sm_count) * (bn + 16);
+      if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
+    }
+    return best;
+  }
+  const int cands[3] = {128, 64, 32};
+  for (int i = 0; i < 3; ++i) {
     int bn = cands[i];
     if (gated && bn < 64) break;
-    if ((long long)m_tiles * ((N + bn - 1) / bn) >= sm_count || i == 3 || (gated && bn == 64)) return bn;
+    if ((long long)m_tiles * ((N + bn - 1) / bn) >= sm_count || i == 2 || (gated && bn == 64)) return bn;
   }
   return gated ? 64 : 32;
 }
