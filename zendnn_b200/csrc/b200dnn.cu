@@ -138,6 +138,20 @@ int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, c
 }
 
 // ------------------------------------------------------------------------------------ GEMM launchers
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device (the calls are serialised by the
+// runtime mutex): raises the limit to the largest size the kernel is launched with and remembers that it did.
+int32_t ensure_max_smem(const void *fn, int bytes = 227 * 1024) {
+  static std::map<std::pair<const void *, int>, bool> done;
+  int dev = 0;
+  B2_CUDA(cudaGetDevice(&dev));
+  bool &d = done[{fn, dev}];
+  if (!d) {
+    B2_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    d = true;
+  }
+  return B200DNN_SUCCESS;
+}
+
 int32_t launch_stream(const uint8_t *A, int64_t lda, bool a_unsigned, int M, int N, int K, const PackedWeight &pw,
                       const EpiParams &epi, cudaStream_t st) {
   Runtime &R = rt();
@@ -172,10 +186,10 @@ int32_t launch_stream(const uint8_t *A, int64_t lda, bool a_unsigned, int M, int
   }
   dim3 grid(tiles_n, ksplit, tiles_m);
   if (a_unsigned) {
-    B2_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B2_TRY(ensure_max_smem((const void *)stream_gemm_kernel<true>, 200 * 1024));
     stream_gemm_kernel<true><<<grid, 256, smem, st>>>(g, epi);
   } else {
-    B2_CUDA(cudaFuncSetAttribute(stream_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B2_TRY(ensure_max_smem((const void *)stream_gemm_kernel<false>, 200 * 1024));
     stream_gemm_kernel<false><<<grid, 256, smem, st>>>(g, epi);
   }
   B2_LAUNCHED();
@@ -199,7 +213,7 @@ int32_t launch_decode(const uint8_t *A, int64_t lda, bool a_unsigned, int M, int
   const size_t smem = (size_t)g.rows_staged * g.a_stride + (size_t)g.max_local_groups * 512 + decode_epi_bytes(g.max_local_groups);
   if (M > 16 || smem > 220 * 1024) return B200DNN_UNIMPLEMENTED;
   void (*kern)(DecodeGemmArgs, EpiParams) = a_unsigned ? decode_gemm_kernel<true> : decode_gemm_kernel<false>;
-  B2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  B2_TRY(ensure_max_smem((const void *)kern));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kDecodeWarps * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -238,7 +252,7 @@ int32_t launch_decode_ring(const uint8_t *A, int64_t lda, bool a_unsigned, int M
   g.stages = stages;
   const size_t smem = fixed + (size_t)stages * stage_bytes;
   void (*kern)(DecodeRingArgs, EpiParams) = a_unsigned ? decode_ring_kernel<true, R> : decode_ring_kernel<false, R>;
-  B2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+  B2_TRY(ensure_max_smem((const void *)kern));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3((kRingWarps + 1) * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -319,7 +333,7 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
   args.stages = stages;
   B2_TRY(make_map_wt(&map_b, pw0.wt, (uint64_t)pw0.Kp, (uint64_t)pw0.Np, (uint32_t)args.BN));
   const size_t smem = (size_t)stages * stage_bytes + 1024;
-  B2_CUDA(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel, kTcSmemBudget + 1024));   // the kernel also has static shared memory
   long long tiles = (long long)m_tiles_hint * args.n_tiles;
   int grid = (int)(tiles < R.sm_count ? (tiles > 0 ? tiles : 1) : R.sm_count);
   tc_gemm_kernel<<<grid, kTcThreads, smem, st>>>(map_a, map_b, args, epi);
