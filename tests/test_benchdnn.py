@@ -1,0 +1,65 @@
+"""The benchdnn-style driver (zendnn_b200/benchdnn.py): input-line parsing and the supported-subset decision on CPU,
+a few lines end to end on the GPU.  Line format: benchdnn/doc/matmul.md of the reference."""
+import pytest
+
+from zendnn_b200 import benchdnn as B
+
+
+def test_parse_full_line():
+    c = B.parse_line("64, 512, 256, 10, bf16:s8:bf16, true, f32, gelu_tanh, , aocl_dlp, true, false, false, 1.0, 0.0, "
+                     "per-channel, , f32, 3, true, per-token, 0, f32")
+    assert (c["m"], c["k"], c["n"], c["iters"]) == (64, 512, [256], 10)
+    assert (c["sdt"], c["wdt"], c["ddt"]) == ("bf16", "s8", "bf16")
+    assert c["bias"] and c["post_ops"] == ["gelu_tanh"] and c["dyn"] and c["sgran"] == "per-token" and c["warmup"] == 3
+    assert B.unsupported_reason(c) is None
+
+
+def test_parse_defaults_comments_and_pipeline():
+    assert B.parse_line("# a comment") is None and B.parse_line("   ") is None
+    c = B.parse_line("16, 128, 64:32, 5, u8:s8:bf16")
+    assert c["n"] == [64, 32] and c["is_weights_const"] and not c["bias"] and c["wgran"] == "per-channel"
+    assert c["alpha"] == 1.0 and c["beta"] == 0.0 and not c["dyn"]
+    with pytest.raises(ValueError):
+        B.parse_line("16, 128")
+    with pytest.raises(ValueError):
+        B.parse_line("16, 128, 64, 5, f32:f32")
+    with pytest.raises(ValueError):
+        B.parse_line("0, 128, 64, 5, u8:s8:bf16")
+
+
+@pytest.mark.parametrize("line,why", [
+    ("128, 256, 64, 1, f32:f32:f32, true, f32, relu", "weights f32"),
+    ("128, 256, 64, 1, bf16:s4:bf16, true, f32, , , x, true, false, false, 1.0, 0.0, per-group, 128, bf16", "weights s4"),
+    ("128, 256, 64, 1, bf16:s8:bf16, false, f32, , , x, true, false, false, 1.0, 0.0, per-channel, , f32, 0, true, per-group, 128, bf16",
+     "per-group source"),
+    ("128, 256, 64, 1, u8:s8:bf16, false, f32, , , x, true, true, false", "transposed source"),
+    ("128, 256, 64, 1, u8:s8:bf16, false, f32, , , x, true, false, false, 2.0, 0.0", "alpha"),
+    ("128, 256, 64, 1, bf16:s8:bf16", "without src_dynamic_quant"),
+])
+def test_unsupported_lines_are_reported(line, why):
+    r = B.unsupported_reason(B.parse_line(line))
+    assert r is not None and why.split()[0] in r
+    assert "unimplemented" in B.run_config(B.parse_line(line))[1]
+
+
+def test_result_row_has_the_reference_columns():
+    c = B.parse_line("16, 128, 64, 4, u8:s8:bf16")
+    cols = B.row(c, 2.0, "success").split(", ")
+    assert len(cols) == len(B.HEADER.split(", "))
+    assert cols[0] == "16" and cols[-1] == "success" and float(cols[-3]) == 0.5
+
+
+@pytest.mark.gpu
+def test_lines_run_on_the_gpu(tmp_path):
+    p = tmp_path / "inputs.txt"
+    p.write_text("# decode, prefill, pipeline, unsupported\n"
+                 "4, 512, 256, 3, bf16:s8:bf16, false, f32, , , aocl_dlp, true, false, false, 1.0, 0.0, per-channel, , f32, 1, true, per-token, 0, f32\n"
+                 "200, 256, 384, 3, u8:s8:bf16, true, f32, relu\n"
+                 "64, 256, 128:64, 2, bf16:s8:bf16, true, f32, gelu_tanh, , , true, false, true, 1.0, 0.0, per-channel, , f32, 0, true, per-token\n"
+                 "64, 256, 128, 2, f32:f32:f32\n")
+    cfgs = B.parse_file(str(p))
+    assert len(cfgs) == 4
+    results = [B.run_config(c, "warm", 2) for c in cfgs]
+    assert [r[1] for r in results[:3]] == ["success"] * 3, results
+    assert all(r[0] > 0 for r in results[:3])
+    assert results[3][1].startswith("unimplemented")

@@ -1,0 +1,259 @@
+"""Driver that accepts the reference benchmark's matmul inputs (benchdnn, `--op=matmul`): the same
+comma-separated input-file lines and the same command-line options, run through libb200dnn on cuda:0,
+with a CSV result table in the reference's column order.
+
+  python -m zendnn_b200.benchdnn --op=matmul --input_file=inputs.txt [--cache_mode=hot|warm] [--num_weight_buffers=N]
+  python -m zendnn_b200.benchdnn --op=matmul --m=4096 --k=4096 --n=4096 --iters=100 --sdt=bf16 --wdt=s8 --ddt=bf16 \\
+         --dynamic_quant=true --src_scale_granularity=per-token
+
+Input-file fields (benchdnn/doc/matmul.md of the reference): m, k, n[:n2...], iters, src:wei:dst, bias, bias_dt,
+post_ops (colon-separated), post_op_dt, kernel, is_weights_const, isTransA, isTransB, alpha, beta,
+weight_scale_granularity, weight_group_size, weight_scale_dt, warmup_iters, src_dynamic_quant,
+src_scale_granularity, src_group_size, src_scale_dt.  Lines starting with '#' and empty lines are skipped.
+
+What runs: the INT8 path of matmul_direct (u8|s8 source with static per-tensor scale and zero point, or bf16|f32
+source with src_dynamic_quant and per-token or per-tensor scales; s8 weights with per-channel or per-tensor scales;
+bf16|f32|s32 destination).  Everything else (f32/bf16 weights, s4 weights, per-group scales, transposed source,
+alpha/beta other than 1/0, batched lines) is reported as `unimplemented`, which is the status the library returns
+for it.  Multi-layer lines (n = a:b:c) run as a pipeline: layer i+1 consumes the bf16 output of layer i.
+`--cache_mode=warm` rotates over `--num_weight_buffers` weight copies (default: enough to exceed the L2 size), `hot`
+(default) reuses one; `cold` is accepted and treated as `warm` (there is no CPU cache to flush).
+"""
+import argparse
+import sys
+
+FIELDS = ["m", "k", "n", "iters", "dt", "bias", "bias_dt", "post_ops", "post_op_dt", "kernel", "is_weights_const",
+          "isTransA", "isTransB", "alpha", "beta", "weight_scale_granularity", "weight_group_size", "weight_scale_dt",
+          "warmup_iters", "src_dynamic_quant", "src_scale_granularity", "src_group_size", "src_scale_dt"]
+HEADER = ("M, K, N, Iterations, Data type, Bias Enabled, Bias Data type, Post Operation, PostOp Data type, Kernel name, "
+          "isWeightsConst, isTransA, isTransB, Alpha, Beta, Weight Scale Granularity, Weight Group Size, "
+          "Weight Scale Data type, Warmup iterations, Src Dynamic Quant, Src Scale Granularity, Src Group Size, "
+          "Src Scale Data type, Total time (ms) (all iters),  Avg time (ms), GFLOPS, Status")
+L2_BYTES = 126 << 20
+
+
+def _bool(s, default=False):
+    s = s.strip().lower()
+    if s == "":
+        return default
+    return s in ("true", "1")
+
+
+def _gran(s, default):
+    s = s.strip().lower()
+    table = {"per-channel": "per-channel", "channel": "per-channel", "per-group": "per-group", "group": "per-group",
+             "per-tensor": "per-tensor", "tensor": "per-tensor", "per-token": "per-token", "token": "per-token"}
+    return table.get(s, default)
+
+
+def parse_line(line):
+    """One input-file line -> config dict, or None for comments / blank lines.  Raises ValueError on a malformed line."""
+    text = line.split("#", 1)[0].strip() if line.lstrip().startswith("#") else line.strip()
+    if not text:
+        return None
+    parts = [p.strip() for p in text.split(",")]
+    if len(parts) < 5:
+        raise ValueError("expected at least m, k, n, iters, dt: %r" % line)
+    parts += [""] * (len(FIELDS) - len(parts))
+    f = dict(zip(FIELDS, parts))
+    dts = f["dt"].split(":")
+    if len(dts) != 3:
+        raise ValueError("dt must be src:weights:dst: %r" % f["dt"])
+    cfg = dict(
+        m=int(f["m"]), k=int(f["k"]), n=[int(v) for v in f["n"].split(":")], iters=int(f["iters"]),
+        sdt=dts[0], wdt=dts[1], ddt=dts[2], bias=_bool(f["bias"]), bias_dt=f["bias_dt"] or "f32",
+        post_ops=[p for p in f["post_ops"].split(":") if p], post_op_dt=f["post_op_dt"] or "f32", kernel=f["kernel"],
+        is_weights_const=_bool(f["is_weights_const"], True), transA=_bool(f["isTransA"]), transB=_bool(f["isTransB"]),
+        alpha=float(f["alpha"] or 1.0), beta=float(f["beta"] or 0.0),
+        wgran=_gran(f["weight_scale_granularity"], "per-channel"), wgroup=int(f["weight_group_size"] or 0),
+        wscale_dt=f["weight_scale_dt"] or "f32", warmup=int(f["warmup_iters"] or 0),
+        dyn=_bool(f["src_dynamic_quant"]), sgran=_gran(f["src_scale_granularity"], "per-tensor"),
+        sgroup=int(f["src_group_size"] or 0), sscale_dt=f["src_scale_dt"] or "f32")
+    if cfg["m"] <= 0 or cfg["k"] <= 0 or min(cfg["n"]) <= 0 or cfg["iters"] <= 0:
+        raise ValueError("m, k, n, iters must be positive: %r" % line)
+    return cfg
+
+
+def parse_file(path):
+    out = []
+    with open(path) as fh:
+        for no, line in enumerate(fh, 1):
+            try:
+                cfg = parse_line(line)
+            except ValueError as e:
+                raise ValueError("%s:%d: %s" % (path, no, e))
+            if cfg:
+                out.append(cfg)
+    return out
+
+
+def unsupported_reason(cfg):
+    """None when the line is inside the subset the library computes, else why not."""
+    if cfg["wdt"] != "s8":
+        return "weights %s (only s8)" % cfg["wdt"]
+    if cfg["dyn"]:
+        if cfg["sdt"] not in ("bf16", "f32"):
+            return "dynamic quantisation takes a bf16 or f32 source"
+        if cfg["sgran"] == "per-group":
+            return "per-group source scales"
+    elif cfg["sdt"] not in ("u8", "s8"):
+        return "source %s without src_dynamic_quant" % cfg["sdt"]
+    if cfg["ddt"] not in ("bf16", "f32", "s32"):
+        return "destination %s" % cfg["ddt"]
+    if cfg["wgran"] == "per-group":
+        return "per-group weight scales"
+    if cfg["transA"]:
+        return "transposed source"
+    if cfg["alpha"] != 1.0 or cfg["beta"] != 0.0:
+        return "alpha/beta other than 1/0"
+    known = {"relu", "gelu_tanh", "gelu_erf", "sigmoid", "swish", "tanh", "elu", "leaky_relu", "binary_add", "binary_mul"}
+    for p in cfg["post_ops"]:
+        if p not in known:
+            return "post-op %s" % p
+    if len(cfg["n"]) > 1 and cfg["ddt"] != "bf16" and not cfg["dyn"]:
+        return "pipeline lines need dynamic quantisation between layers"
+    return None
+
+
+def row(cfg, total_ms, status):
+    n = ":".join(str(v) for v in cfg["n"])
+    flops = 0.0
+    k = cfg["k"]
+    for nn in cfg["n"]:
+        flops += 2.0 * cfg["m"] * k * nn
+        k = nn
+    avg = total_ms / cfg["iters"] if total_ms else 0.0
+    gflops = flops / (avg * 1e6) if avg else 0.0
+    vals = [cfg["m"], cfg["k"], n, cfg["iters"], "%s:%s:%s" % (cfg["sdt"], cfg["wdt"], cfg["ddt"]), str(cfg["bias"]).lower(),
+            cfg["bias_dt"], ":".join(cfg["post_ops"]), cfg["post_op_dt"], cfg["kernel"], str(cfg["is_weights_const"]).lower(),
+            str(cfg["transA"]).lower(), str(cfg["transB"]).lower(), "%.2f" % cfg["alpha"], "%.2f" % cfg["beta"], cfg["wgran"],
+            cfg["wgroup"], cfg["wscale_dt"], cfg["warmup"], str(cfg["dyn"]).lower(), cfg["sgran"], cfg["sgroup"], cfg["sscale_dt"],
+            "%.2f" % total_ms, "%.4f" % avg, "%.2f" % gflops, status]
+    return ", ".join(str(v) for v in vals)
+
+
+def run_config(cfg, cache_mode="hot", num_weight_buffers=0):
+    """Runs one line on cuda:0.  Returns (total_ms over iters, status string)."""
+    why = unsupported_reason(cfg)
+    if why:
+        return 0.0, "unimplemented (%s)" % why
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=dev).manual_seed(0)
+    M = cfg["m"]
+    layers, k = [], cfg["k"]
+    tdt = {"bf16": torch.bfloat16, "f32": torch.float32, "s32": torch.int32}
+    for li, n in enumerate(cfg["n"]):
+        last = li == len(cfg["n"]) - 1
+        copies = 1
+        if cache_mode in ("warm", "cold"):
+            copies = num_weight_buffers if num_weight_buffers > 0 else max(2, -(-L2_BYTES // (k * n)) + 1)
+        shape = (n, k) if cfg["transB"] else (k, n)
+        ws = [torch.randint(-127, 128, shape, generator=g, dtype=torch.int8, device=dev) for _ in range(copies)]
+        wn = n if cfg["wgran"] == "per-channel" else 1
+        wscale = (torch.rand(wn, generator=g, device=dev) * 4e-4 + 1e-4)
+        if cfg["wscale_dt"] == "bf16":
+            wscale = wscale.to(torch.bfloat16)
+        bias = None
+        if cfg["bias"]:
+            bias = torch.randn(n, generator=g, device=dev)
+            if cfg["bias_dt"] == "bf16":
+                bias = bias.to(torch.bfloat16)
+        pos = []
+        for p in cfg["post_ops"]:
+            if p.startswith("binary"):
+                b = torch.randn(M, n, generator=g, device=dev)
+                pos.append(dict(type=p, buff=b.to(torch.bfloat16) if cfg["post_op_dt"] == "bf16" else b))
+            else:
+                pos.append(p)
+        ddt = cfg["ddt"] if last else "bf16"
+        out = torch.empty(M, n, dtype=tdt[ddt], device=dev)
+        layers.append(dict(k=k, n=n, ws=ws, wscale=wscale, bias=bias, pos=pos, out=out, ddt=ddt))
+        k = n
+    if cfg["dyn"]:
+        x = torch.randn(M, cfg["k"], generator=g, device=dev)
+        x = x.to(torch.bfloat16) if cfg["sdt"] == "bf16" else x
+    else:
+        lo, hi = (0, 256) if cfg["sdt"] == "u8" else (-127, 128)
+        x = torch.randint(lo, hi, (M, cfg["k"]), generator=g, device=dev, dtype=torch.uint8 if cfg["sdt"] == "u8" else torch.int8)
+    sscale = torch.tensor([0.02], device=dev)
+    szp = torch.tensor([128], dtype=torch.int32, device=dev) if cfg["sdt"] == "u8" else None
+
+    def descs(it):
+        ds, src, src_dt = [], x, cfg["sdt"]
+        for li, L in enumerate(layers):
+            w = L["ws"][it % len(L["ws"])]
+            dyn = cfg["dyn"] or li > 0
+            kw = {}
+            if dyn:
+                kw["src_scale"] = capi.quant(None, M if cfg["sgran"] == "per-token" or li > 0 else 1, capi.DT[cfg["sscale_dt"]])
+            else:
+                kw["src_scale"] = sscale
+                if szp is not None:
+                    kw["src_zp"] = szp
+            ds.append(capi.make_matmul(M, L["n"], L["k"], src, w, L["out"], src_dt=capi.DT[src_dt], dst_dt=capi.DT[L["ddt"]],
+                                       transB=cfg["transB"], bias=L["bias"], weights_const=cfg["is_weights_const"],
+                                       dynamic_quant=dyn, wei_scale=L["wscale"], postops=L["pos"], **kw))
+            src, src_dt = L["out"], "bf16"
+        return ds
+
+    n_sets = max(len(L["ws"]) for L in layers)
+    sets = [descs(i) for i in range(n_sets)]
+    for d in sets[0]:
+        stt = capi.matmul(d, st)
+        if stt != capi.SUCCESS:
+            return 0.0, ("unimplemented" if stt == capi.UNIMPLEMENTED else "failure") + " (%s)" % capi.last_error()
+    for i in range(cfg["warmup"]):
+        for d in sets[i % n_sets]:
+            capi.matmul(d, st)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(cfg["iters"]):
+        for d in sets[i % n_sets]:
+            capi.matmul(d, st)
+    e1.record()
+    torch.cuda.synchronize()
+    capi.lib.b200dnn_clear_caches()
+    return e0.elapsed_time(e1), "success"
+
+
+def config_from_args(a):
+    line = ", ".join(str(v) for v in [
+        a.m, a.k, a.n, a.iters, "%s:%s:%s" % (a.sdt, a.wdt, a.ddt), a.bias, a.bias_dt, a.post_ops, a.post_op_dt, a.kernel_name,
+        a.is_weights_const, a.isTransA, a.isTransB, a.alpha, a.beta, a.weight_scale_granularity, a.weight_group_size,
+        a.weight_scale_dt, a.warmup_iters, a.dynamic_quant, a.src_scale_granularity, a.src_group_size, a.src_scale_dt])
+    return parse_line(line)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description="benchdnn-style matmul driver over libb200dnn")
+    ap.add_argument("--op", default="matmul")
+    ap.add_argument("--input_file")
+    ap.add_argument("--cache_mode", default="hot")
+    ap.add_argument("--num_weight_buffers", type=int, default=0)
+    ap.add_argument("--ndims", type=int, default=2)
+    ap.add_argument("--lowoha", default="true")
+    for name, default in (("m", 0), ("k", 0), ("n", "0"), ("iters", 100), ("sdt", "f32"), ("wdt", "f32"), ("ddt", "f32"),
+                          ("bias", "false"), ("bias_dt", "f32"), ("post_ops", ""), ("post_op_dt", "f32"), ("kernel_name", ""),
+                          ("is_weights_const", "true"), ("isTransA", "false"), ("isTransB", "false"), ("alpha", 1.0),
+                          ("beta", 0.0), ("weight_scale_granularity", "per-channel"), ("weight_group_size", 0),
+                          ("weight_scale_dt", "f32"), ("warmup_iters", 0), ("dynamic_quant", "false"),
+                          ("src_scale_granularity", "per-tensor"), ("src_group_size", 0), ("src_scale_dt", "f32")):
+        ap.add_argument("--" + name, default=default)
+    a = ap.parse_args(argv)
+    if a.op != "matmul" or a.ndims != 2:
+        print("only --op=matmul with --ndims=2 is in scope of this library", file=sys.stderr)
+        return 2
+    cfgs = parse_file(a.input_file) if a.input_file else [config_from_args(a)]
+    print(HEADER)
+    for cfg in cfgs:
+        total, status = run_config(cfg, a.cache_mode.lower(), a.num_weight_buffers)
+        print(row(cfg, total, status), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
