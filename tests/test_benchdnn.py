@@ -63,3 +63,27 @@ def test_lines_run_on_the_gpu(tmp_path):
     assert [r[1] for r in results[:3]] == ["success"] * 3, results
     assert all(r[0] > 0 for r in results[:3])
     assert results[3][1].startswith("unimplemented")
+
+
+def test_parse_grp_lines():
+    c = B.parse_grp_line("8, 14:5:6:7:4:22:2:4, 4096, 28672, 200, bf16:bf16:bf16, true, 50, 2, 1, 4096")
+    assert c["ops"] == 8 and c["M"] == [14, 5, 6, 7, 4, 22, 2, 4] and (c["topk"], c["act"], c["n_down"]) == (2, 1, 4096)
+    assert "weights bf16" in B.grp_unsupported_reason(c)
+    c["wdt"] = "s8"
+    assert B.grp_unsupported_reason(c) is None
+    u = B.parse_grp_line("4, 32, 2880, 5760, 200, bf16:s8:bf16, true, 50, 4, 3, 2880, 1, 32")
+    assert u["M"] == [32] * 4 and u["total_experts"] == 32 and B.grp_unsupported_reason(u) is None
+    plain = B.parse_grp_line("8, 4, 4096, 14336, 200, bf16:s8:bf16, true, 50")
+    assert "fused" in B.grp_unsupported_reason(plain)
+    assert B.parse_grp_line("# comment") is None
+    with pytest.raises(ValueError):
+        B.parse_grp_line("8, 1:2:3, 4096, 28672, 200, bf16:s8:bf16, true, 50")
+    assert len(B.grp_row(c, 3.0, "success").split(", ")) == len(B.GRP_HEADER.split(", "))
+
+
+@pytest.mark.gpu
+def test_grp_lines_run_on_the_gpu():
+    for line in ("4, 10:0:7:3, 256, 512, 2, bf16:s8:bf16, true, 1, 2, 1, 256",
+                 "3, 8, 128, 256, 2, bf16:s8:bf16, true, 0, 0, 3, 128"):
+        total, status = B.run_grp_config(B.parse_grp_line(line))
+        assert status == "success" and total > 0, (line, status)

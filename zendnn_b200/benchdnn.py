@@ -1,5 +1,5 @@
-"""Driver that accepts the reference benchmark's matmul inputs (benchdnn, `--op=matmul`): the same
-comma-separated input-file lines and the same command-line options, run through libb200dnn on cuda:0,
+"""Driver that accepts the reference benchmark's inputs (benchdnn, `--op=matmul` and `--op=grp_matmul`): the same
+comma-separated input-file lines and, for matmul, the same command-line options, run through libb200dnn on cuda:0,
 with a CSV result table in the reference's column order.
 
   python -m zendnn_b200.benchdnn --op=matmul --input_file=inputs.txt [--cache_mode=hot|warm] [--num_weight_buffers=N]
@@ -18,6 +18,16 @@ alpha/beta other than 1/0, batched lines) is reported as `unimplemented`, which 
 for it.  Multi-layer lines (n = a:b:c) run as a pipeline: layer i+1 consumes the bf16 output of layer i.
 `--cache_mode=warm` rotates over `--num_weight_buffers` weight copies (default: enough to exceed the L2 size), `hot`
 (default) reuses one; `cold` is accepted and treated as `warm` (there is no CPU cache to flush).
+
+  python -m zendnn_b200.benchdnn --op=grp_matmul --input_file=trace.txt [--wdt_as=s8]
+
+grp_matmul lines (benchdnn/doc/grp_matmul.md): num_ops, M (one value or a colon-separated list per expert), K, N, iters,
+src:wei:dst, is_weights_const, warmup [, moe_topk [, gated_act [, N_down [, use_internal_alloc [, total_experts]]]]].
+What runs: the full fused block (gated_act 1..3, N_down > 0) with s8 weights and bf16 source and destination, i.e.
+group_matmul_direct's dynamic-INT8 fused MoE: gate|up GEMM -> gated activation -> down GEMM, plus the weighted
+reduce when moe_topk > 0 (row pointers expert by expert, weights 1/topk, as the reference driver builds them).  The
+reference's shipped traces are bf16:bf16:bf16; `--wdt_as=s8` runs their shapes with s8 weights instead.  Other lines are
+reported `unimplemented`.
 """
 import argparse
 import sys
@@ -220,6 +230,122 @@ def run_config(cfg, cache_mode="hot", num_weight_buffers=0):
     return e0.elapsed_time(e1), "success"
 
 
+# ------------------------------------------------------------------------------------------------ grp_matmul
+GRP_HEADER = ("ops, M, K, N, iters, warmup, dtypes, moe, gated_act, N_down, total_experts, Total time (ms) (all iters), "
+              "Avg time (ms), GFLOPS, Status")
+
+
+def parse_grp_line(line):
+    if not line.strip() or line.lstrip().startswith("#"):
+        return None
+    parts = [p.strip() for p in line.strip().split(",")]
+    if len(parts) < 8:
+        raise ValueError("expected num_ops, M, K, N, iters, dt, is_weights_const, warmup: %r" % line)
+    parts += [""] * (13 - len(parts))
+    ops = int(parts[0])
+    ms = [int(v) for v in parts[1].split(":")]
+    if len(ms) == 1:
+        ms = ms * ops
+    if len(ms) != ops:
+        raise ValueError("M lists %d values for %d ops: %r" % (len(ms), ops, line))
+    dts = parts[5].split(":")
+    if len(dts) != 3:
+        raise ValueError("dt must be src:weights:dst: %r" % parts[5])
+    cfg = dict(ops=ops, M=ms, k=int(parts[2]), n=int(parts[3]), iters=int(parts[4]), sdt=dts[0], wdt=dts[1], ddt=dts[2],
+               is_weights_const=_bool(parts[6], True), warmup=int(parts[7] or 0), topk=int(parts[8] or 0),
+               act=int(parts[9] or 0), n_down=int(parts[10] or 0), internal_alloc=int(parts[11] or 0),
+               total_experts=int(parts[12] or 0) or ops)
+    if ops <= 0 or cfg["k"] <= 0 or cfg["n"] <= 0 or cfg["iters"] <= 0 or min(ms) < 0 or cfg["total_experts"] < ops:
+        raise ValueError("bad sizes: %r" % line)
+    return cfg
+
+
+def grp_unsupported_reason(cfg):
+    if cfg["wdt"] != "s8":
+        return "weights %s (only s8; --wdt_as=s8 runs the shapes with s8 weights)" % cfg["wdt"]
+    if cfg["sdt"] != "bf16" or cfg["ddt"] != "bf16":
+        return "source/destination other than bf16"
+    if cfg["act"] not in (1, 2, 3) or cfg["n_down"] <= 0:
+        return "only the fused gate/up -> activation -> down block"
+    if cfg["n"] % 2:
+        return "odd N"
+    if cfg["topk"] > 0 and sum(cfg["M"]) % cfg["topk"]:
+        return "total M not divisible by moe_topk"
+    return None
+
+
+def grp_row(cfg, total_ms, status):
+    ms = cfg["M"]
+    mtxt = str(ms[0]) if len(set(ms)) == 1 else "%d-%d(%d)" % (min(ms), max(ms), sum(ms) // len(ms))
+    I = cfg["n"] // 2
+    flops = sum(2.0 * m * cfg["k"] * cfg["n"] + 2.0 * m * I * cfg["n_down"] for m in ms)
+    if cfg["topk"] > 0 and cfg["n_down"] > 0:
+        flops += 2.0 * (sum(ms) // cfg["topk"]) * cfg["n_down"] * cfg["topk"]
+    avg = total_ms / cfg["iters"] if total_ms else 0.0
+    vals = [cfg["ops"], mtxt, cfg["k"], cfg["n"], cfg["iters"], cfg["warmup"], "%s:%s:%s" % (cfg["sdt"], cfg["wdt"], cfg["ddt"]),
+            "topk=%d" % cfg["topk"] if cfg["topk"] else "off", cfg["act"], cfg["n_down"], cfg["total_experts"],
+            "%.2f" % total_ms, "%.4f" % avg, "%.2f" % (flops / (avg * 1e6) if avg else 0.0), status]
+    return ", ".join(str(v) for v in vals)
+
+
+def run_grp_config(cfg):
+    why = grp_unsupported_reason(cfg)
+    if why:
+        return 0.0, "unimplemented (%s)" % why
+    import ctypes as C
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=dev).manual_seed(0)
+    E, K, I, H = cfg["ops"], cfg["k"], cfg["n"] // 2, cfg["n_down"]
+    keep, ex = [], (capi.MoeExpert * E)()
+    total = sum(cfg["M"])
+    ptrs = (C.c_void_p * max(1, total))()
+    slot = 0
+    for e, m in enumerate(cfg["M"]):
+        w13 = torch.randint(-127, 128, (K, 2 * I), generator=g, dtype=torch.int8, device=dev)
+        w2 = torch.randint(-127, 128, (I, H), generator=g, dtype=torch.int8, device=dev)
+        s13 = torch.rand(2 * I, generator=g, device=dev) * 4e-4 + 1e-4
+        s2 = torch.rand(H, generator=g, device=dev) * 4e-4 + 1e-4
+        src = torch.randn(max(m, 1), K, generator=g, device=dev).to(torch.bfloat16)
+        dst = torch.empty(max(m, 1), H, dtype=torch.bfloat16, device=dev)
+        keep.append((w13, w2, s13, s2, src, dst))
+        x = ex[e]
+        x.M, x.src, x.lda = m, src.data_ptr(), K
+        x.w13, x.ldb13, x.w13_scale = w13.data_ptr(), 2 * I, s13.data_ptr()
+        x.w2, x.ldb2, x.w2_scale = w2.data_ptr(), H, s2.data_ptr()
+        x.dst_down, x.ldc_down = dst.data_ptr(), H
+        for r in range(m):      # row pointers expert by expert, as the reference driver builds them
+            ptrs[slot] = dst.data_ptr() + r * H * 2
+            slot += 1
+    topk = cfg["topk"]
+    T = total // topk if topk else 0
+    if topk:
+        w = torch.full((T, topk), 1.0 / topk, device=dev)
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        keep.append((w, out))
+
+    def call():
+        return capi.lib.b200dnn_fused_moe(E, ex, K, I, H, 0, cfg["act"], int(cfg["is_weights_const"]),
+                                          ptrs if topk else None, w.data_ptr() if topk else None, T, topk,
+                                          out.data_ptr() if topk else None, H, st)
+    stt = call()
+    if stt != capi.SUCCESS:
+        return 0.0, ("unimplemented" if stt == capi.UNIMPLEMENTED else "failure") + " (%s)" % capi.last_error()
+    for _ in range(cfg["warmup"]):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(cfg["iters"]):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    capi.lib.b200dnn_clear_caches()
+    return e0.elapsed_time(e1), "success"
+
+
 def config_from_args(a):
     line = ", ".join(str(v) for v in [
         a.m, a.k, a.n, a.iters, "%s:%s:%s" % (a.sdt, a.wdt, a.ddt), a.bias, a.bias_dt, a.post_ops, a.post_op_dt, a.kernel_name,
@@ -236,6 +362,7 @@ def main(argv=None):
     ap.add_argument("--num_weight_buffers", type=int, default=0)
     ap.add_argument("--ndims", type=int, default=2)
     ap.add_argument("--lowoha", default="true")
+    ap.add_argument("--wdt_as", default="", help="grp_matmul: run the lines with this weight type instead of the one in the file")
     for name, default in (("m", 0), ("k", 0), ("n", "0"), ("iters", 100), ("sdt", "f32"), ("wdt", "f32"), ("ddt", "f32"),
                           ("bias", "false"), ("bias_dt", "f32"), ("post_ops", ""), ("post_op_dt", "f32"), ("kernel_name", ""),
                           ("is_weights_const", "true"), ("isTransA", "false"), ("isTransB", "false"), ("alpha", 1.0),
@@ -244,8 +371,23 @@ def main(argv=None):
                           ("src_scale_granularity", "per-tensor"), ("src_group_size", 0), ("src_scale_dt", "f32")):
         ap.add_argument("--" + name, default=default)
     a = ap.parse_args(argv)
+    if a.op == "grp_matmul":
+        if not a.input_file:
+            print("--op=grp_matmul needs --input_file", file=sys.stderr)
+            return 2
+        print(GRP_HEADER)
+        with open(a.input_file) as fh:
+            for line in fh:
+                cfg = parse_grp_line(line)
+                if cfg is None:
+                    continue
+                if a.wdt_as:
+                    cfg["wdt"] = a.wdt_as
+                total, status = run_grp_config(cfg)
+                print(grp_row(cfg, total, status), flush=True)
+        return 0
     if a.op != "matmul" or a.ndims != 2:
-        print("only --op=matmul with --ndims=2 is in scope of this library", file=sys.stderr)
+        print("only --op=matmul with --ndims=2 and --op=grp_matmul are in scope of this library", file=sys.stderr)
         return 2
     cfgs = parse_file(a.input_file) if a.input_file else [config_from_args(a)]
     print(HEADER)

@@ -205,6 +205,8 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
   if (row_ptrs) {
     B2_CHECK(out && T > 0 && topk > 0 && ld_out >= H, B200DNN_FAILURE, "weighted reduce: bad argument");
     B2_CHECK(topk_weights, B200DNN_FAILURE, "weighted reduce: topk_weights is null");
+    B2_CHECK(!is_device_ptr(row_ptrs), B200DNN_UNIMPLEMENTED,
+             "weighted reduce: row_ptrs is an array in host memory (as in the reference); a device array is not accepted");
     const size_t ns = (size_t)T * topk;
     // translate the caller's row pointers (into dst_down buffers) to device addresses
     std::vector<const void *> dev_rows(ns);
