@@ -248,6 +248,13 @@ B200DNN_API int32_t b200dnn_moe_weighted_reduce_rows(const void *rows, int64_t l
  * (matmul/group_matmul/group_matmul_direct.hpp:683). */
 B200DNN_API int32_t b200dnn_clear_caches(void);
 
+/* Calls that take device pointers only enqueue work and return before it has run.  This waits for `stream` and
+ * reports whether any kernel of this library, since the last check, gave up on one of its bounded waits (it
+ * then left without writing its outputs): success, or failure with the code in b200dnn_last_error().  Calls with
+ * host buffers synchronise anyway and make this check themselves.  No reference counterpart (the reference is
+ * synchronous). */
+B200DNN_API int32_t b200dnn_stream_status(void *stream);
+
 #ifdef __cplusplus
 }
 #endif

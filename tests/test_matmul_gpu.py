@@ -257,3 +257,29 @@ def test_decode_kernel_forms(capi, oracle, monkeypatch, form, shape):
               postops=["relu"])
     ref = oracle.matmul_w8a8(A, W, "bf16", src_scale=sa, wei_scale=sw, bias=bias, postops=["relu"])
     assert (got == ref).all()
+
+
+@pytest.mark.parametrize("M", [1, 256])
+def test_bounded_waits_leave_a_status_and_a_usable_context(capi, oracle, monkeypatch, M):
+    """With the test hook that makes the producer issue no copies, every wait on data in the ring decode kernel (M = 1)
+    and in the tcgen05 kernel (M = 256) runs into its limit of about a second: the kernel leaves without hanging,
+    b200dnn_stream_status reports failure with the code, and the next call on the same context is correct."""
+    import torch
+    K, N = 512, 256
+    rng = np.random.default_rng(M)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    dA, dW = torch.from_numpy(A).cuda(), torch.from_numpy(W).cuda()
+    out = torch.zeros(M, N, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    d = capi.make_matmul(M, N, K, dA, dW, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["s32"], weights_const=False)
+    assert capi.lib.b200dnn_stream_status(st) == capi.SUCCESS
+    monkeypatch.setenv("B200DNN_TEST_NO_LOADS", "1")
+    assert capi.matmul(d, st) == capi.SUCCESS          # device pointers: the call only enqueues
+    assert capi.lib.b200dnn_stream_status(st) == capi.FAILURE
+    assert "gave up waiting" in capi.last_error()
+    monkeypatch.delenv("B200DNN_TEST_NO_LOADS")
+    assert capi.matmul(d, st) == capi.SUCCESS
+    assert capi.lib.b200dnn_stream_status(st) == capi.SUCCESS
+    assert (out.cpu().numpy() == oracle.gemm_s32(A, W)).all()
+    capi.lib.b200dnn_clear_caches()

@@ -55,7 +55,7 @@ EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b20
            "b200dnn_matmul", "b200dnn_matmul_static_scratch", "b200dnn_prepack_size", "b200dnn_prepack", "b200dnn_quant_per_token",
            "b200dnn_group_quant_per_token", "b200dnn_quant_dynamic", "b200dnn_quant_static",
            "b200dnn_dequant_static", "b200dnn_gated_act", "b200dnn_moe_weighted_reduce", "b200dnn_fused_moe",
-           "b200dnn_moe_route", "b200dnn_moe_layer", "b200dnn_clear_caches", "b200dnn_moe_sort_slots",
+           "b200dnn_moe_route", "b200dnn_moe_layer", "b200dnn_clear_caches", "b200dnn_stream_status", "b200dnn_moe_sort_slots",
            "b200dnn_quant_per_token_gather", "b200dnn_quant_per_token_scatter", "b200dnn_moe_experts_s8",
            "b200dnn_moe_weighted_reduce_rows"]
 
@@ -85,6 +85,7 @@ lib.b200dnn_moe_route.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
 lib.b200dnn_moe_layer.argtypes = [vp, i64, vp, i32, i32, i32, i32, C.POINTER(MoeExpert), i32, i32, i32, i32, i32, vp, i64, vp]
 
 
+lib.b200dnn_stream_status.argtypes = [vp]
 lib.b200dnn_moe_sort_slots.argtypes = [vp, i32, i32, vp, vp, vp]
 lib.b200dnn_quant_per_token_gather.argtypes = [vp, i32, i64, i64, vp, i32, i64, vp, i64, vp, vp]
 lib.b200dnn_quant_per_token_scatter.argtypes = [vp, i32, i64, i64, vp, i32, i64, vp, i64, vp, vp]

@@ -238,6 +238,7 @@ int32_t launch_decode_ring(const uint8_t *A, int64_t lda, bool a_unsigned, int M
   const int grid = g.groups < R_.sm_count ? g.groups : R_.sm_count;
   g.max_local_groups = (g.groups + grid - 1) / grid;
   g.status = R_.status;
+  g.test_no_loads = env_int("B200DNN_TEST_NO_LOADS", 0);   // see decode_ring.cuh; off unless a test sets it
   const size_t stage_bytes = (size_t)R * kRingWarps * 1024;
   const size_t fixed = ring_off_ring(g.rows_staged, g.a_stride, g.max_local_groups);
   const size_t budget = 227 * 1024;
@@ -312,7 +313,12 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
     default: break;
     }
   }
-  args.dbg = env_int("B200DNN_TC_DBG", 0);
+  args.test_no_loads = env_int("B200DNN_TEST_NO_LOADS", 0);   // see tc_gemm.cuh; off unless a test sets it
+#ifdef B200DNN_TIMING_EXPERIMENTS
+  args.dbg = env_int("B200DNN_TC_DBG", 0);    // parts of the epilogue switched off: results are invalid
+#else
+  args.dbg = 0;
+#endif
   args.BN = pick_bn(m_tiles_hint, N, R.sm_count, pw0.gated);
   B2_CHECK(args.BN % 32 == 0 && args.BN >= 32 && args.BN <= 256 && (!pw0.gated || args.BN % 64 == 0), B200DNN_FAILURE,
            "bad tile width %d", args.BN);
@@ -844,6 +850,12 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   // the synchronised call took that long, so the normal path pays nothing for the check.
   if (sync_path && std::chrono::steady_clock::now() - t_call > std::chrono::milliseconds(900)) B2_TRY(check_tc_status(st));
   return B200DNN_SUCCESS;
+}
+
+int32_t b200dnn_stream_status(void *stream) {
+  std::lock_guard<std::mutex> lk(rt().mu);
+  B2_TRY(rt().init());
+  return check_tc_status(as_stream(stream));
 }
 
 int32_t b200dnn_clear_caches(void) {

@@ -43,6 +43,7 @@ struct DecodeRingArgs {
   int max_local_groups;            // ceil(groups / gridDim.x)
   int stages;                      // ring depth
   int32_t *status;                 // device word: 0 ok
+  int test_no_loads;               // test hook: the producer issues no copies, so the consumers' bounded waits run out
 };
 
 constexpr int kRingMaxStages = 16;
@@ -106,9 +107,9 @@ __global__ void __launch_bounds__((kRingWarps + 1) * 32, 1) decode_ring_kernel(D
     };
     int st = 0;
     bool ok = true;
-    const int pre = n_stages < S ? n_stages : S;
+    const int pre = g.test_no_loads ? 0 : (n_stages < S ? n_stages : S);
     for (; st < pre; ++st) issue(st);
-    for (; st < n_stages; ++st) {
+    for (; st < n_stages && !g.test_no_loads; ++st) {
       if (st >= S && !mbar_wait(empty_bar(st % S), (uint32_t)((st / S) - 1) & 1u)) { ok = false; break; }
       issue(st);
     }

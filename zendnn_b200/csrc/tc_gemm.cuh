@@ -68,7 +68,10 @@ struct TcGemmArgs {
   int a_unsigned;
   int gated;                  // packed gate/up interleave: 0, 1 or 2 (see pack_kernels.cuh)
   int fast_act;               // FA_* code: which specialised epilogue loop to run
-  int dbg;                    // timing experiments (results invalid): 1 no epilogue work, 2 tensor-memory loads only, 3 no stores
+  int dbg;                    // timing experiments, only in builds with B200DNN_TIMING_EXPERIMENTS (results invalid):
+                              // 1 no epilogue work, 2 tensor-memory loads only, 3 no stores; otherwise 0
+  int test_no_loads;          // test hook: the producer issues no copies, so every wait on data runs out (bounded) and the
+                              // kernel must leave with a status code and a usable context
   int n_fastest;              // tile order: 0 = all row tiles of a column tile first, 1 = all column tiles of a row tile first
   int32_t *status;            // device word: 0 ok
 };
@@ -366,7 +369,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // (the whole warp walks the tiles so that the group lookup is a warp operation; lane 0 issues the copies)
     int stage = 0; uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < total_tiles && !a.test_no_loads; tile += gridDim.x) {
       // one decision for the whole warp (the lookup below uses warp-wide operations)
       if (!__shfl_sync(0xffffffffu, (ok && !s_err) ? 1 : 0, 0)) break;
       const TileCoord t = tc_tile_warp(a, tile, m_tiles, lane);
