@@ -34,10 +34,11 @@ int32_t upload_blob(const void *host, size_t bytes, cudaStream_t st, void **dev)
 
 int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const std::vector<PackedWeight> &pws,
                      const int32_t *row_off_dev, const int32_t *tile_prefix_dev, const TcGroupDesc *groups_dev,
-                     int m_tiles_bound, EpiParams epi, cudaStream_t st) {
+                     int m_tiles_bound, EpiParams epi, bool shared_dst, cudaStream_t st) {
   Runtime &Rt = rt();
   const int G = (int)pws.size();
   TcGemmArgs ta{};
+  ta.shared_dst = shared_dst ? 1 : 0;   // no group carries its own destination
   ta.n_groups = G; ta.row_off = row_off_dev; ta.tile_prefix = tile_prefix_dev; ta.groups = groups_dev;
   // one tensor map per expert, in device memory
   const PackedWeight &p0 = pws[0];
@@ -112,7 +113,7 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
   e1.wei_scale_dt = B200DNN_F32; e1.wei_scale_n = 2 * I;
   e1.dst = Z; e1.ldc = I; e1.dst_dt = B200DNN_BF16; e1.gated_act = act; e1.gated_I = I; e1.row_absmax = zmax;
   B2_TRY(grouped_gemm(A1_in, lda1, R, 2 * I, K, p13, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g13_dev,
-                      m_tiles_bound, e1, st));
+                      m_tiles_bound, e1, true, st));
 
   // 3. re-quantise the activated rows (from their bf16 values, as the reference does)
   RowQuantArgs q2{};
@@ -128,7 +129,7 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
   e2.wei_scale_dt = B200DNN_F32; e2.wei_scale_n = H;
   e2.dst = O; e2.ldc = H; e2.dst_dt = B200DNN_BF16;
   B2_TRY(grouped_gemm((const uint8_t *)A2, Iq, R, H, I, p2, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g2_dev,
-                      m_tiles_bound, e2, st));
+                      m_tiles_bound, e2, dst_down_dev == nullptr, st));
   if (O_out) { *O_out = O; *ldO_out = H; }
   return B200DNN_SUCCESS;
 }

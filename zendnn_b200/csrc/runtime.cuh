@@ -129,6 +129,20 @@ inline int32_t make_map_2d(CUtensorMap *m, const void *base, uint64_t inner_byte
   return B200DNN_SUCCESS;
 }
 
+// 2-D byte map over a row-major destination for TMA stores of [32 rows x 32 bytes] blocks (no swizzle).
+inline int32_t make_map_store(CUtensorMap *m, void *base, uint64_t row_bytes, uint64_t rows, uint64_t pitch_bytes) {
+  B2_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0 && pitch_bytes % 16 == 0 && row_bytes >= 32, B200DNN_FAILURE,
+           "TMA store destination must be 16-byte aligned with a 16-byte multiple pitch");
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = rt().encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B2_CHECK(r == CUDA_SUCCESS, B200DNN_FAILURE, "cuTensorMapEncodeTiled (store) failed with %d", (int)r);
+  return B200DNN_SUCCESS;
+}
+
 // 4-D uint8 tensor map over a block-interleaved packed weight Wt[Np/8][Kp/128][8][128] (pack_kernels.cuh).
 // Dimensions, innermost first: 128 bytes of K, 8 rows of a group, Kp/128 K-blocks, Np/8 groups.  The box
 // {128, 8, 1, box_rows/8} lands in shared memory as box_rows consecutive 128-byte rows (SWIZZLE_128B).

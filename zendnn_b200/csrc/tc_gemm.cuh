@@ -70,6 +70,8 @@ struct TcGemmArgs {
   int fast_act;               // FA_* code: which specialised epilogue loop to run
   int dbg;                    // timing experiments, only in builds with B200DNN_TIMING_EXPERIMENTS (results invalid):
                               // 1 no epilogue work, 2 tensor-memory loads only, 3 no stores; otherwise 0
+  int shared_dst;             // every group writes epi.dst at its global row (set by the caller); plain GEMM: 1
+  int tma_store;              // bf16 results of full 32-row blocks leave through TMA stores (map_c covers the shared destination)
   int test_no_loads;          // test hook: the producer issues no copies, so every wait on data runs out (bounded) and the
                               // kernel must leave with a status code and a usable context
   int n_fastest;              // tile order: 0 = all row tiles of a column tile first, 1 = all column tiles of a row tile first
@@ -233,6 +235,23 @@ __device__ __forceinline__ void warp_store_rows64(uint8_t *sbuf, const uint4 (&v
   warp_store_rows32(sbuf, v[2], v[3], g_row0 + 32, pitch_bytes, rows_valid, lane);
 }
 
+// The same [32 rows x 32 bytes] block as one TMA store: the lanes write their rows to the staging block (plain row-major),
+// one lane hands it to the copy engine and waits until the engine has read it.  Keeps the result off the load/store path.
+__device__ __forceinline__ void warp_tma_store_rows32(uint8_t *sbuf, const uint4 &v0, const uint4 &v1, const CUtensorMap *map,
+                                                      int x_bytes, int row, int lane) {
+  *reinterpret_cast<uint4 *>(sbuf + lane * 32) = v0;
+  *reinterpret_cast<uint4 *>(sbuf + lane * 32 + 16) = v1;
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  if (lane == 0) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x_bytes), "r"(row), "r"(smem_u32(sbuf)) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  }
+  __syncwarp();
+}
+
 struct EpiStore {          // where this warp's rows of the current tile go
   uint8_t *sbuf;           // the warp's staging block
   uint8_t *g_row0;         // address of (first row of the warp, column 0) in the destination
@@ -240,6 +259,8 @@ struct EpiStore {          // where this warp's rows of the current tile go
   int rows_valid;          // rows of the warp's 32 that exist in this tile
   bool coalesce;           // destination 16-byte aligned: use the staged path
   bool row_ok;             // this lane's row exists
+  const CUtensorMap *map_c;  // non-null: full blocks go out as TMA stores, coordinates (byte column, row)
+  int row_c;               // row coordinate of the warp's first row in map_c
 };
 
 // One 32-column chunk of one output row.
@@ -293,6 +314,10 @@ __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx 
       for (int p = 0; p < 4; ++p)
         v[p] = make_uint4(pack_bf16x2(x[8 * p], x[8 * p + 1]), pack_bf16x2(x[8 * p + 2], x[8 * p + 3]),
                           pack_bf16x2(x[8 * p + 4], x[8 * p + 5]), pack_bf16x2(x[8 * p + 6], x[8 * p + 7]));
+      if (es.map_c && es.rows_valid == 32) {
+        warp_tma_store_rows32(es.sbuf, v[0], v[1], es.map_c, pc0 * 2, es.row_c, lane);
+        warp_tma_store_rows32(es.sbuf, v[2], v[3], es.map_c, pc0 * 2 + 32, es.row_c, lane);
+      } else
       warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)pc0 * 2, es.pitch_bytes, es.rows_valid, lane);
     } else if (es.row_ok) {
       uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
@@ -322,13 +347,13 @@ __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx 
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
-               const TcGemmArgs a, const EpiParams epi) {
+               const __grid_constant__ CUtensorMap map_c, const TcGemmArgs a, const EpiParams epi) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * 8 + 8];
   __shared__ __align__(16) TileCols cols[2];
   __shared__ __align__(16) float row_scale[2][kTcBM];
   __shared__ TileMeta meta[2];
-  __shared__ __align__(16) uint8_t epi_stage[kTcEpiWarps][1024];
+  __shared__ __align__(128) uint8_t epi_stage[kTcEpiWarps][1024];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int s_err;
 
@@ -491,6 +516,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         es.rows_valid = min(32, max(0, tm.rows - q * 32));
         es.coalesce = ((reinterpret_cast<uintptr_t>(tm.dst) | (uintptr_t)es.pitch_bytes) & 15) == 0;
         es.row_ok = row_ok;
+        es.map_c = (a.tma_store && es.coalesce) ? &map_c : nullptr;
+        es.row_c = tm.m_dst0 + q * 32;
       }
       const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * a.BN);
       if (a.dbg == 1) {
@@ -566,6 +593,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint4 v[4];
 #pragma unroll
             for (int p4 = 0; p4 < 4; ++p4) v[p4] = make_uint4(pk[4 * p4], pk[4 * p4 + 1], pk[4 * p4 + 2], pk[4 * p4 + 3]);
+            if (es.map_c && es.rows_valid == 32) {
+              warp_tma_store_rows32(es.sbuf, v[0], v[1], es.map_c, j0 * 2, es.row_c, lane);
+              warp_tma_store_rows32(es.sbuf, v[2], v[3], es.map_c, j0 * 2 + 32, es.row_c, lane);
+            } else
             warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)j0 * 2, es.pitch_bytes, es.rows_valid, lane);
           } else if (row_ok) {
             uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + j0;
@@ -585,6 +616,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 
   // ---------------------------------------------------------------------- teardown
+  if (a.tma_store && warp >= 2 && warp < 2 + kTcEpiWarps && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   if (s_err) {
