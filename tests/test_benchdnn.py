@@ -87,3 +87,30 @@ def test_grp_lines_run_on_the_gpu():
                  "3, 8, 128, 256, 2, bf16:s8:bf16, true, 0, 0, 3, 128"):
         total, status = B.run_grp_config(B.parse_grp_line(line))
         assert status == "success" and total > 0, (line, status)
+
+
+def test_parse_reorder_lines():
+    c = B.parse_reorder_line("1, 2048, 512, 50, bf16, s8, reference, per_channel_row, 0, true, 0, 10")
+    assert (c["rows"], c["cols"], c["sdt"], c["ddt"], c["gran"], c["dyn"], c["warmup"]) == (2048, 512, "bf16", "s8", "per_channel_row", True, 10)
+    assert B.reorder_unsupported_reason(c) is None
+    assert B.parse_reorder_line("1, 64, 64, 10, f32, s8, reference, per_tensor, 0, false")["warmup"] == 2
+    for line, why in (("4, 1024, 768, 100, f32, u8, reference, per_group_col, 128, false, 8, 20", "batched"),
+                      ("1, 1024, 768, 100, f32, u8, reference, per_group_col, 128, false, 8, 20", "granularity"),
+                      ("1, 2048, 1024, 100, f16, s8, native, per_channel_row, 0, true, 0, 20", "f16"),
+                      ("1, 4096, 4096, 50, f32, u8, reference, per_channel_col, 0, true, 0, 10", "dynamic")):
+        r = B.reorder_unsupported_reason(B.parse_reorder_line(line))
+        assert r is not None and why in r, (line, r)
+    with pytest.raises(ValueError):
+        B.parse_reorder_line("1, 64, 64")
+    assert len(B.reorder_row(c, 1.0, "success").split(", ")) == len(B.REORDER_HEADER.split(", "))
+
+
+@pytest.mark.gpu
+def test_reorder_lines_run_on_the_gpu():
+    for line in ("1, 300, 520, 3, bf16, s8, reference, per_channel_row, 0, true, 0, 1",
+                 "1, 256, 384, 3, f32, s8, reference, per_channel_col, 0, true, 0, 1",
+                 "1, 256, 384, 3, f32, s8, reference, per_tensor, 0, true, 0, 1",
+                 "1, 128, 256, 3, f32, u8, reference, per_tensor, 0, false, 0, 1",
+                 "1, 128, 256, 3, s8, bf16, native, per_channel_col, 0, false, 0, 1"):
+        total, status = B.run_reorder_config(B.parse_reorder_line(line))
+        assert status == "success" and total > 0, (line, status)

@@ -28,6 +28,15 @@ group_matmul_direct's dynamic-INT8 fused MoE: gate|up GEMM -> gated activation -
 reduce when moe_topk > 0 (row pointers expert by expert, weights 1/topk, as the reference driver builds them).  The
 reference's shipped traces are bf16:bf16:bf16; `--wdt_as=s8` runs their shapes with s8 weights instead.  Other lines are
 reported `unimplemented`.
+
+  python -m zendnn_b200.benchdnn --op=reorder --input_file=reorder_inputs.txt
+
+reorder lines of the low-overhead API (benchdnn/doc/reorder.md): batch_size, rows, cols, iters, src_dtype, dst_dtype, algo,
+scale_granularity, group_size, dynamic_quant [, num_threads [, warmup_iters]].  What runs (batch_size 1): dynamic
+symmetric quantisation to s8 with one scale per row (`per_channel_row`, the per-token form), per column
+(`per_channel_col`) or per tensor; static quantisation of f32|bf16 to s8|u8 and static dequantisation of s8|u8 to
+f32|bf16 with per-tensor or per-column scales.  f16, per-group granularities, dynamic u8 and batches are reported
+`unimplemented`.
 """
 import argparse
 import sys
@@ -346,6 +355,108 @@ def run_grp_config(cfg):
     return e0.elapsed_time(e1), "success"
 
 
+# ------------------------------------------------------------------------------------------------ reorder
+REORDER_HEADER = ("batch, rows, cols, iters, src_dtype, dst_dtype, algo, scale_granularity, group_size, dynamic_quant, "
+                  "warmup_iters, Total time (ms) (all iters), Avg time (ms), GB/s, Status")
+
+
+def parse_reorder_line(line):
+    if not line.strip() or line.lstrip().startswith("#"):
+        return None
+    parts = [p.strip() for p in line.strip().split(",")]
+    if len(parts) < 10:
+        raise ValueError("expected batch, rows, cols, iters, src, dst, algo, granularity, group_size, dynamic_quant: %r" % line)
+    parts += [""] * (12 - len(parts))
+    cfg = dict(batch=int(parts[0]), rows=int(parts[1]), cols=int(parts[2]), iters=int(parts[3]), sdt=parts[4], ddt=parts[5],
+               algo=parts[6], gran=parts[7].lower(), group=int(parts[8] or 0), dyn=_bool(parts[9]),
+               threads=int(parts[10] or 0), warmup=int(parts[11]) if parts[11] else max(1, int(parts[3]) // 5))
+    if min(cfg["batch"], cfg["rows"], cfg["cols"], cfg["iters"]) <= 0:
+        raise ValueError("sizes must be positive: %r" % line)
+    return cfg
+
+
+def reorder_unsupported_reason(cfg):
+    if cfg["batch"] != 1:
+        return "batched reorder"
+    if "f16" in (cfg["sdt"], cfg["ddt"]) and "bf16" not in (cfg["sdt"], cfg["ddt"]):
+        return "f16"
+    if cfg["gran"] not in ("per_tensor", "per_channel_row", "per_channel_col"):
+        return "granularity %s" % cfg["gran"]
+    quant = cfg["sdt"] in ("f32", "bf16") and cfg["ddt"] in ("s8", "u8")
+    dequant = cfg["sdt"] in ("s8", "u8") and cfg["ddt"] in ("f32", "bf16")
+    if not (quant or dequant):
+        return "%s -> %s" % (cfg["sdt"], cfg["ddt"])
+    if cfg["dyn"]:
+        if not quant or cfg["ddt"] != "s8":
+            return "dynamic quantisation writes s8 from f32|bf16"
+    elif cfg["gran"] == "per_channel_row":
+        return "static per-row scales"
+    return None
+
+
+def reorder_row(cfg, total_ms, status):
+    esz = dict(f32=4, bf16=2, f16=2, s8=1, u8=1)
+    avg = total_ms / cfg["iters"] if total_ms else 0.0
+    bytes_moved = cfg["batch"] * cfg["rows"] * cfg["cols"] * (esz.get(cfg["sdt"], 0) + esz.get(cfg["ddt"], 0))
+    vals = [cfg["batch"], cfg["rows"], cfg["cols"], cfg["iters"], cfg["sdt"], cfg["ddt"], cfg["algo"], cfg["gran"], cfg["group"],
+            str(cfg["dyn"]).lower(), cfg["warmup"], "%.2f" % total_ms, "%.4f" % avg,
+            "%.1f" % (bytes_moved / (avg * 1e6) if avg else 0.0), status]
+    return ", ".join(str(v) for v in vals)
+
+
+def run_reorder_config(cfg):
+    why = reorder_unsupported_reason(cfg)
+    if why:
+        return 0.0, "unimplemented (%s)" % why
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=dev).manual_seed(0)
+    M, N = cfg["rows"], cfg["cols"]
+    tdt = dict(f32=torch.float32, bf16=torch.bfloat16, s8=torch.int8, u8=torch.uint8)
+    L = capi.lib
+    if cfg["sdt"] in ("f32", "bf16"):
+        src = torch.randn(M, N, generator=g, device=dev).to(tdt[cfg["sdt"]])
+    else:
+        lo, hi = (0, 256) if cfg["sdt"] == "u8" else (-127, 128)
+        src = torch.randint(lo, hi, (M, N), generator=g, device=dev, dtype=tdt[cfg["sdt"]])
+    dst = torch.empty(M, N, dtype=tdt[cfg["ddt"]], device=dev)
+    n_scale = N if cfg["gran"] == "per_channel_col" else 1
+    if cfg["dyn"]:
+        if cfg["gran"] == "per_channel_row":
+            scale = torch.empty(M, device=dev)
+            call = lambda: L.b200dnn_quant_per_token(src.data_ptr(), capi.DT[cfg["sdt"]], M, N, N, dst.data_ptr(), N,
+                                                     scale.data_ptr(), capi.DT["f32"], st)
+        else:
+            scale = torch.empty(n_scale, device=dev)
+            call = lambda: L.b200dnn_quant_dynamic(src.data_ptr(), capi.DT[cfg["sdt"]], M, N, N, int(n_scale > 1), dst.data_ptr(),
+                                                   N, scale.data_ptr(), st)
+    else:
+        scale = torch.rand(n_scale, generator=g, device=dev) * 0.05 + 0.01
+        zp = torch.full((1,), 128, dtype=torch.int32, device=dev) if "u8" in (cfg["sdt"], cfg["ddt"]) else None
+        zp_ptr, n_zp = (zp.data_ptr(), 1) if zp is not None else (None, 0)
+        if cfg["ddt"] in ("s8", "u8"):
+            call = lambda: L.b200dnn_quant_static(src.data_ptr(), capi.DT[cfg["sdt"]], M, N, N, scale.data_ptr(), n_scale, zp_ptr,
+                                                  n_zp, dst.data_ptr(), capi.DT[cfg["ddt"]], N, st)
+        else:
+            call = lambda: L.b200dnn_dequant_static(src.data_ptr(), capi.DT[cfg["sdt"]], M, N, N, scale.data_ptr(), n_scale, zp_ptr,
+                                                    n_zp, dst.data_ptr(), capi.DT[cfg["ddt"]], N, st)
+    stt = call()
+    if stt != capi.SUCCESS:
+        return 0.0, ("unimplemented" if stt == capi.UNIMPLEMENTED else "failure") + " (%s)" % capi.last_error()
+    for _ in range(cfg["warmup"]):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(cfg["iters"]):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1), "success"
+
+
 def config_from_args(a):
     line = ", ".join(str(v) for v in [
         a.m, a.k, a.n, a.iters, "%s:%s:%s" % (a.sdt, a.wdt, a.ddt), a.bias, a.bias_dt, a.post_ops, a.post_op_dt, a.kernel_name,
@@ -386,8 +497,21 @@ def main(argv=None):
                 total, status = run_grp_config(cfg)
                 print(grp_row(cfg, total, status), flush=True)
         return 0
+    if a.op == "reorder":
+        if not a.input_file or a.lowoha.lower() != "true":
+            print("--op=reorder needs --input_file and the low-overhead API (--lowoha=true)", file=sys.stderr)
+            return 2
+        print(REORDER_HEADER)
+        with open(a.input_file) as fh:
+            for line in fh:
+                cfg = parse_reorder_line(line)
+                if cfg is None:
+                    continue
+                total, status = run_reorder_config(cfg)
+                print(reorder_row(cfg, total, status), flush=True)
+        return 0
     if a.op != "matmul" or a.ndims != 2:
-        print("only --op=matmul with --ndims=2 and --op=grp_matmul are in scope of this library", file=sys.stderr)
+        print("only --op=matmul with --ndims=2, --op=grp_matmul and --op=reorder are in scope of this library", file=sys.stderr)
         return 2
     cfgs = parse_file(a.input_file) if a.input_file else [config_from_args(a)]
     print(HEADER)
