@@ -713,6 +713,7 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   B2_TRY(rt().init());
   Runtime &R = rt();
   R.ws.rewind();
+  R.small.begin();
   cudaStream_t st = as_stream(stream);
   const auto t_call = std::chrono::steady_clock::now();
   const int M = d->M, N = d->N, K = d->K;
@@ -777,7 +778,7 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   EpiParams epi;
   fill_epi(d, &epi);
   const void *src_dev = nullptr;
-  B2_TRY(stage_in(d->src, span_bytes(M, K, d->lda, d->src_dt), st, &src_dev));
+  B2_TRY(stage_in(d->src, span_bytes(M, K, d->lda, d->src_dt), st, &src_dev, &R.small));
   const uint8_t *A = (const uint8_t *)src_dev; int64_t lda = d->lda; bool a_unsigned = d->src_dt == B200DNN_U8;
   Staged o_scale;
   if (dyn) {
@@ -790,29 +791,30 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
     if (!sc) { sc = R.ws.alloc((size_t)M * 4); B2_CHECK(sc, B200DNN_FAILURE, "workspace allocation failed"); }
     RowQuantArgs qa{};
     qa.src = src_dev; qa.src_ld = d->lda; qa.dst = q; qa.dst_ld = Kq; qa.scale = sc; qa.scale_dt = sdt; qa.K = K; qa.gather_div = 1;
+    B2_TRY(R.small.flush(st, false));
     B2_TRY(launch_quant_rows(qa, d->src_dt, M, st));
     A = (const uint8_t *)q; lda = Kq; a_unsigned = false;
     epi.src_scale = sc; epi.src_scale_dt = sdt; epi.src_scale_n = M > 1 ? M : 1;
   } else if (d->src_scale.count > 0) {
     const void *p;
-    B2_TRY(stage_in(d->src_scale.buff, (size_t)d->src_scale.count * dt_size(d->src_scale.dt), st, &p));
+    B2_TRY(stage_in(d->src_scale.buff, (size_t)d->src_scale.count * dt_size(d->src_scale.dt), st, &p, &R.small));
     epi.src_scale = p; epi.src_scale_dt = d->src_scale.dt; epi.src_scale_n = (int32_t)d->src_scale.count;
   }
   if (d->wei_scale.count > 0) {
     const void *p;
-    B2_TRY(stage_in(d->wei_scale.buff, (size_t)d->wei_scale.count * dt_size(d->wei_scale.dt), st, &p));
+    B2_TRY(stage_in(d->wei_scale.buff, (size_t)d->wei_scale.count * dt_size(d->wei_scale.dt), st, &p, &R.small));
     epi.wei_scale = p; epi.wei_scale_dt = d->wei_scale.dt; epi.wei_scale_n = (int32_t)d->wei_scale.count;
   }
   if (d->src_zp.buff) {
     B2_CHECK(d->src_zp.dt == B200DNN_S32 || d->src_zp.dt == B200DNN_S8 || d->src_zp.dt == B200DNN_U8, B200DNN_UNIMPLEMENTED, "src zero-point dtype");
     const void *p;
-    B2_TRY(stage_in(d->src_zp.buff, dt_size(d->src_zp.dt), st, &p));
+    B2_TRY(stage_in(d->src_zp.buff, dt_size(d->src_zp.dt), st, &p, &R.small));
     epi.src_zp = p; epi.src_zp_dt = d->src_zp.dt; epi.has_zp = 1;
   }
   epi.colsum = pw.colsum;
   if (d->bias) {
     const void *p;
-    B2_TRY(stage_in(d->bias, (size_t)N * dt_size(d->bias_dt), st, &p));
+    B2_TRY(stage_in(d->bias, (size_t)N * dt_size(d->bias_dt), st, &p, &R.small));
     epi.bias = p;
   }
   for (int i = 0; i < d->n_postops; ++i) {
@@ -821,13 +823,14 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
     epi.po[i].buff = nullptr;
     if (p.type == PO_BINARY_ADD || p.type == PO_BINARY_MUL) {
       const void *b;
-      B2_TRY(stage_in(p.buff, p.ld ? span_bytes(M, N, p.ld, p.dt) : (size_t)N * dt_size(p.dt), st, &b));
+      B2_TRY(stage_in(p.buff, p.ld ? span_bytes(M, N, p.ld, p.dt) : (size_t)N * dt_size(p.dt), st, &b, &R.small));
       epi.po[i].buff = b;
     }
   }
   Staged o_dst;
   B2_TRY(stage_out(d->dst, span_bytes(M, N, d->ldc, d->dst_dt), st, &o_dst, d->ldc != N));
   epi.dst = o_dst.dev;
+  B2_TRY(R.small.flush(st, o_dst.copy_back || o_dst.sync));
 
   // ---- kernel choice: weight-streaming kernel for decode-sized M, tcgen05 otherwise
   const bool tc_ok = (lda % 16 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
