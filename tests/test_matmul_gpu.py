@@ -114,6 +114,39 @@ def test_decode_shapes_prepacked(capi, oracle, M, KN):
     assert (got2 == ref).all()
 
 
+@pytest.mark.parametrize("splits,bn", [("2", "128"), ("3", "256"), ("4", "128"), ("4", "256"), ("0", "0")])
+@pytest.mark.parametrize("shape", [(100, 1024, 1000), (200, 2064, 520), (128, 4096, 264), (300, 640, 4096)])
+def test_tc_split_form(capi, oracle, monkeypatch, splits, bn, shape):
+    """Small plain GEMMs run as clusters whose CTAs split the K blocks of a tile and add their int32 partial sums through
+    distributed shared memory: s32 bit-exact, and the float epilogue gives the bytes of the unsplit kernel."""
+    M, K, N = shape
+    if splits != "0":
+        monkeypatch.setenv("B200DNN_TC_KSPLIT", splits)
+        monkeypatch.setenv("B200DNN_TC_BN", bn)
+    rng = np.random.default_rng(K + N)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    sw = rng.uniform(1e-4, 5e-4, N).astype(np.float32)
+    bias = rng.normal(size=N).astype(np.float32)
+    acc = oracle.gemm_s32(A, W)
+    got = run(capi, M, N, K, A, W, "s32", weights_const=False, force_kernel=TC)
+    assert (got == acc).all()
+    kw = dict(weights_const=False, force_kernel=TC, src_scale=sa, wei_scale=sw, bias=bias, postops=["gelu_tanh"])
+    got = run(capi, M, N, K, A, W, "bf16", **kw)
+    monkeypatch.setenv("B200DNN_TC_KSPLIT", "1")
+    unsplit = run(capi, M, N, K, A, W, "bf16", **kw)
+    assert (got == unsplit).all(), int((got != unsplit).sum())
+    ref = oracle.matmul_w8a8(A, W, "bf16", src_scale=sa, wei_scale=sw, bias=bias, postops=["gelu_tanh"])
+    assert_bf16_close(got, ref, 1, "split form", atol=1e-5)
+    Au = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    monkeypatch.setenv("B200DNN_TC_KSPLIT", splits)
+    got = run(capi, M, N, K, Au, W, "f32", weights_const=False, force_kernel=TC, src_scale=np.array([0.02], dtype=np.float32),
+              wei_scale=sw, src_zp=np.array([128], dtype=np.int32), bias=bias, postops=["relu"])
+    ref = oracle.epilogue(oracle.gemm_s32(Au, W), "f32", [0.02], sw, 128, oracle.colsum(W), bias, ["relu"])
+    assert np.allclose(got, ref, rtol=2e-6, atol=1e-6)
+
+
 def test_scales_in_bf16_storage(capi, oracle):
     c = decode_case(oracle, 8, 512, 128, seed=3)
     sa16, sw16 = oracle.f32_to_bf16(c["sa"]), oracle.f32_to_bf16(c["sw"])

@@ -292,6 +292,81 @@ int pick_bn(int m_tiles, int N, int sm_count, int gated) {
   return gated ? 64 : 32;
 }
 
+// Split form for small plain GEMMs.  With fewer tiles than SMs the persistent kernel leaves SMs idle and, worse, too few
+// weight bytes in flight (stages x BN x 128 B per CTA) to cover the HBM latency: M = 128, N = K = 4096 streamed its weight
+// at 1.2 TB/s.  Clusters of 2 to 4 CTAs share one tile, each taking a share of the K blocks; the int32 partial sums are
+// added through distributed shared memory, so the result is the same bit for bit.  Chooses the (tile width, splits)
+// pair that puts the most CTAs on the device in one wave.
+#ifdef B200DNN_TIMING_EXPERIMENTS
+constexpr size_t kStampCtas = 4096;
+unsigned long long *stamp_buffer() {
+  static unsigned long long *p = nullptr;
+  if (!p && cudaMalloc(&p, kStampCtas * 8 * sizeof(unsigned long long)) != cudaSuccess) p = nullptr;
+  return p;
+}
+extern "C" __attribute__((visibility("default"))) int32_t b200dnn_debug_stamps(unsigned long long *host, int32_t ctas) {
+  if (!stamp_buffer() || ctas < 0 || (size_t)ctas > kStampCtas) return B200DNN_FAILURE;
+  return cudaMemcpy(host, stamp_buffer(), (size_t)ctas * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? B200DNN_SUCCESS : B200DNN_FAILURE;
+}
+#endif
+
+// CTAs that are resident at once when the split form is launched in clusters of s (clusters do not tile the GPCs perfectly)
+int split_room(int s) {
+  static int cache[5] = {0, 0, 0, 0, 0};
+  if (cache[s] == 0) {
+    cache[s] = -1;
+    if (ensure_max_smem((const void *)tc_gemm_kernel<true>, kTcSmemBudget + 1024) == B200DNN_SUCCESS) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3((unsigned)(s * 64)); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = kTcSmemBudget + 1024;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = (unsigned)s; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr; cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, tc_gemm_kernel<true>, &cfg) == cudaSuccess && n > 0) cache[s] = n * s;
+      else cudaGetLastError();
+      if (env_int("B200DNN_DEBUG", 0)) fprintf(stderr, "b200dnn: clusters of %d: %d resident CTAs\n", s, cache[s]);
+    }
+  }
+  return cache[s];
+}
+
+void pick_split(int m_tiles, int N, int k_blocks, int *bn, int *splits) {
+  const int forced = env_int("B200DNN_TC_KSPLIT", 0);   // 0 choose, 1 never, 2..4 that many
+  if (forced == 1) return;
+  const int sm = rt().sm_count;
+  const int room[5] = {0, 0, split_room(2), split_room(3), split_room(4)};
+  // Cost model fitted to measurements (microseconds, without the fixed cost of a launch): the stage ring is filled
+  // from L2 at about 100 GB/s per SM and 9.5 TB/s over the device (every CTA re-reads its rows of A, so wide tiles
+  // move fewer bytes); adding the partial sums costs about 1.6 us per extra CTA of the cluster and 128 columns of tile.
+  auto stream_us = [&](long long ctas, int b, int kb_per_cta, int waves) {
+    const double per_cta = (double)(kTcBM + b) * kTcBK * kb_per_cta;
+    const double dev = per_cta * (double)ctas / 9.5e6, one = per_cta * waves / 1.0e5;
+    return dev > one ? dev : one;
+  };
+  const long long tiles0 = (long long)m_tiles * ((N + *bn - 1) / *bn);
+  const double unsplit = stream_us(tiles0, *bn, k_blocks, (int)((tiles0 + sm - 1) / sm));
+  double best = forced >= 2 ? 1e30 : unsplit - 0.5;
+  int best_bn = 0, best_s = 1;
+  const int widths[3] = {256, 128, 64};
+  const int forced_bn = env_int("B200DNN_TC_BN", 0);
+  for (int w = 0; w < 3; ++w) {
+    const int b = forced_bn > 0 ? forced_bn : widths[w];
+    if (b % 32 != 0 || b < 32 || b > 256) continue;
+    const long long tiles = (long long)m_tiles * ((N + b - 1) / b);
+    for (int s = 2; s <= 4; ++s) {
+      if (forced >= 2 && s != forced) continue;
+      const int per = (k_blocks + s - 1) / s;
+      if (per * (s - 1) >= k_blocks || per < 2) continue;          // every CTA needs K blocks of its own
+      if ((b / 32) < s) continue;                                   // and at least one 32-column chunk to finish
+      if (forced < 2 && (room[s] <= 0 || tiles * s > room[s])) continue;   // one wave of resident clusters
+      const double cost = stream_us(tiles * s, b, per, 1) + 1.6 * (s - 1) * b / 128.0;
+      if (cost < best) { best = cost; best_bn = b; best_s = s; }
+    }
+  }
+  if (best_s > 1) { *bn = best_bn; *splits = best_s; }
+}
+
 // Plain or grouped tcgen05 GEMM.  A: [M_total, lda] device, 16-byte aligned rows.
 int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, int N, int K, const PackedWeight &pw0,
                   TcGemmArgs args, const EpiParams &epi, int m_tiles_hint, cudaStream_t st) {
@@ -314,12 +389,16 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
     }
   }
   args.test_no_loads = env_int("B200DNN_TEST_NO_LOADS", 0);   // see tc_gemm.cuh; off unless a test sets it
+  args.stamps = nullptr;
 #ifdef B200DNN_TIMING_EXPERIMENTS
   args.dbg = env_int("B200DNN_TC_DBG", 0);    // parts of the epilogue switched off: results are invalid
+  if (env_int("B200DNN_TC_STAMPS", 0)) args.stamps = stamp_buffer();
 #else
   args.dbg = 0;
 #endif
   args.BN = pick_bn(m_tiles_hint, N, R.sm_count, pw0.gated);
+  args.k_splits = 1;
+  if (args.n_groups <= 1 && !args.maps_b && !args.groups && !args.tile_prefix && !pw0.gated) pick_split(m_tiles_hint, N, args.k_blocks, &args.BN, &args.k_splits);
   B2_CHECK(args.BN % 32 == 0 && args.BN >= 32 && args.BN <= 256 && (!pw0.gated || args.BN % 64 == 0), B200DNN_FAILURE,
            "bad tile width %d", args.BN);
   args.n_tiles = (N + args.BN - 1) / args.BN;
@@ -339,7 +418,7 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
   args.stages = stages;
   B2_TRY(make_map_wt(&map_b, pw0.wt, (uint64_t)pw0.Kp, (uint64_t)pw0.Np, (uint32_t)args.BN));
   const size_t smem = (size_t)stages * stage_bytes + 1024;
-  B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel, kTcSmemBudget + 1024));   // the kernel also has static shared memory
+  B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<false>, kTcSmemBudget + 1024));   // the kernel also has static shared memory
   long long tiles = (long long)m_tiles_hint * args.n_tiles;
   int grid = (int)(tiles < R.sm_count ? (tiles > 0 ? tiles : 1) : R.sm_count);
   // bf16 results into one shared destination (plain GEMM, or a grouped GEMM whose groups all write epi.dst at their
@@ -356,7 +435,19 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
     if (can) B2_TRY(make_map_store(&map_c, epi.dst, (uint64_t)cols * 2, (uint64_t)M_total, (uint64_t)epi.ldc * 2));
     else map_c = map_a;
   }
-  tc_gemm_kernel<<<grid, kTcThreads, smem, st>>>(map_a, map_b, map_c, args, epi);
+  if (args.k_splits > 1) {
+    // one cluster of k_splits CTAs per tile; the partial sums need BN * 512 bytes of the stage ring
+    B2_CHECK((size_t)args.BN * 512 <= (size_t)stages * stage_bytes, B200DNN_FAILURE, "split form: stage ring smaller than the partial sums");
+    B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<true>, kTcSmemBudget + 1024));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(tiles * args.k_splits)); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)args.k_splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<true>, map_a, map_b, map_c, args, epi));
+  } else
+  tc_gemm_kernel<false><<<grid, kTcThreads, smem, st>>>(map_a, map_b, map_c, args, epi);
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
   return B200DNN_SUCCESS;

@@ -74,9 +74,19 @@ struct TcGemmArgs {
   int tma_store;              // bf16 results of full 32-row blocks leave through TMA stores (map_c covers the shared destination)
   int test_no_loads;          // test hook: the producer issues no copies, so every wait on data runs out (bounded) and the
                               // kernel must leave with a status code and a usable context
+  int k_splits;               // split form (tc_gemm_kernel<true>): the CTAs of a cluster each take a share of the K blocks of one
+                              // tile and add their int32 partial sums through distributed shared memory (exact in any order)
   int n_fastest;              // tile order: 0 = all row tiles of a column tile first, 1 = all column tiles of a row tile first
   int32_t *status;            // device word: 0 ok
+  unsigned long long *stamps; // timing experiments only (builds with B200DNN_TIMING_EXPERIMENTS): 8 timer values per CTA; else null
 };
+
+#ifdef B200DNN_TIMING_EXPERIMENTS
+#define TC_STAMP(i) do { if (a.stamps) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+                                          a.stamps[(size_t)blockIdx.x * 8 + (i)] = t_; } } while (0)
+#else
+#define TC_STAMP(i) do { } while (0)
+#endif
 
 // ---------------------------------------------------------------------------------------- PTX
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
@@ -107,6 +117,35 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+// every thread of every CTA of the cluster; the cluster's CTAs are scheduled together, so the wait ends once each thread
+// has left its own (bounded) waits
+__device__ __forceinline__ void cluster_sync_all() {
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_arrive_all() {
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_all() {
+  __syncwarp();
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t saddr, uint32_t rank) {
+  uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank)); return r;
+}
+__device__ __forceinline__ uint4 ld_cluster_v4(uint32_t caddr) {
+  uint4 v; asm volatile("ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(caddr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t saddr) {
+  uint4 v; asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t saddr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -345,6 +384,23 @@ __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx 
   }
 }
 
+__device__ __forceinline__ void tc_epi_dispatch(int fast_act, const EpiParams &epi, const EpiCtx &cx, const uint32_t (&r)[32],
+                                                const TileCols &tcols, int c0, int pc0, int N, int m_dst, bool has_bias,
+                                                const EpiStore &es, int lane) {
+  switch (fast_act) {
+  case FA_NONE: tc_epi_chunk<FA_NONE>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_RELU: tc_epi_chunk<FA_RELU>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_GELU_TANH: tc_epi_chunk<FA_GELU_TANH>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_GELU_ERF: tc_epi_chunk<FA_GELU_ERF>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_SIGMOID: tc_epi_chunk<FA_SIGMOID>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_SWISH: tc_epi_chunk<FA_SWISH>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_TANH: tc_epi_chunk<FA_TANH>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  default: tc_epi_chunk<FA_GENERIC>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  }
+}
+
+// SPLIT: launched in clusters of a.k_splits CTAs, one tile per cluster (see TcGemmArgs::k_splits); plain, non-gated form only.
+template <bool SPLIT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                const __grid_constant__ CUtensorMap map_c, const TcGemmArgs a, const EpiParams epi) {
@@ -358,6 +414,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __shared__ volatile int s_err;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) TC_STAMP(0);
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_bytes = kTcBM * kTcBK, b_bytes = (uint32_t)a.BN * kTcBK, stage_bytes = a_bytes + b_bytes;
   const int S = a.stages;
@@ -370,6 +427,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   auto cempty_bar = [&](int i) { return bar0 + 8u * (22 + i); };
 
   if (threadIdx.x == 0) {
+    // the copy engine reads the tensor maps from memory on first use: ask for them now
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    if (!a.maps_b) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b0) : "memory");
+    if (a.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
     for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), kTcEpiWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(cfull_bar(i), 1); mbar_init(cempty_bar(i), kTcEpiWarps); }
@@ -385,22 +446,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 0) TC_STAMP(1);
 
   const int m_tiles = a.tile_prefix ? a.tile_prefix[a.n_groups] : a.m_tiles_plain;
   const int total_tiles = m_tiles * a.n_tiles;
+  // persistent form: tiles blockIdx.x, blockIdx.x + gridDim.x, ... over all K blocks; split form: the cluster's one tile,
+  // this CTA's share of the K blocks
+  int tile0 = blockIdx.x, tile_step = gridDim.x, kb_begin = 0, kb_end = a.k_blocks;
+  uint32_t crank = 0;
+  if constexpr (SPLIT) {
+    crank = cluster_ctarank();
+    tile0 = blockIdx.x / a.k_splits; tile_step = total_tiles;
+    const int per = (a.k_blocks + a.k_splits - 1) / a.k_splits;
+    kb_begin = (int)crank * per; kb_end = min(a.k_blocks, kb_begin + per);
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     // (the whole warp walks the tiles so that the group lookup is a warp operation; lane 0 issues the copies)
     int stage = 0; uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && !a.test_no_loads; tile += gridDim.x) {
+    for (int tile = tile0; tile < total_tiles && !a.test_no_loads; tile += tile_step) {
       // one decision for the whole warp (the lookup below uses warp-wide operations)
       if (!__shfl_sync(0xffffffffu, (ok && !s_err) ? 1 : 0, 0)) break;
       const TileCoord t = tc_tile_warp(a, tile, m_tiles, lane);
       if (lane == 0) {
         const CUtensorMap *mb = a.maps_b ? a.maps_b + t.g : &map_b0;
-        for (int kb = 0; kb < a.k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { s_err = 1; atomicExch(a.status, 1); ok = false; break; }
           const uint32_t sa = smem0 + (uint32_t)stage * stage_bytes;
           mbar_expect_tx(full_bar(stage), stage_bytes);
@@ -415,24 +487,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       const uint32_t idesc = make_idesc_i8(a.a_unsigned, a.BN);
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !s_err; tile += gridDim.x) {
+      for (int tile = tile0; tile < total_tiles && !s_err; tile += tile_step) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { s_err = 2; atomicExch(a.status, 2); break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * a.BN);
         bool ok = true;
-        for (int kb = 0; kb < a.k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(full_bar(stage), phase)) { ok = false; break; }
+          if (kb == kb_begin && tile == tile0) TC_STAMP(2);
           tc_fence_after();
           const uint32_t sa = smem0 + (uint32_t)stage * stage_bytes;
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + a_bytes);
 #pragma unroll
           for (int k = 0; k < kTcBK / 32; ++k)
-            tc_mma_i8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            tc_mma_i8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, ((kb - kb_begin) | k) ? 1u : 0u);
           tc_commit(empty_bar(stage));
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
         if (!ok) { s_err = 3; atomicExch(a.status, 3); break; }
         tc_commit(tfull_bar(acc));
+        if (tile == tile0) TC_STAMP(3);
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -440,7 +514,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ------------------------------------------------------------------ operand warp
     const int32_t zp = load_zp(epi);
     int cb = 0; uint32_t cphase = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int tile = tile0; tile < total_tiles; tile += tile_step) {
       if (!__shfl_sync(0xffffffffu, s_err ? 0 : 1, 0)) break;
       const TileCoord t = tc_tile_warp(a, tile, m_tiles, lane);
       const void *wsp = epi.wei_scale; const int32_t *csp = epi.colsum; const void *bp = epi.bias;
@@ -492,7 +566,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int row_in_tile = q * 32 + lane;
     int acc = 0; uint32_t acc_phase = 0;
     int ob = 0; uint32_t ophase = 0;            // operand buffer of the current tile
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int tile = tile0; tile < total_tiles; tile += tile_step) {
       // everything from global memory was put into shared memory by the operand warp
       if (!mbar_wait(cfull_bar(ob), ophase)) { if (lane == 0) { s_err = 5; atomicExch(a.status, 5); } break; }
       const TileMeta tm = meta[ob];
@@ -505,6 +579,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       cx.s_src = row_scale[ob][row_in_tile];
       const int pc_tile = tm.nt * a.BN;
       if (!mbar_wait(tfull_bar(acc), acc_phase)) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
+      if (warp == 2 && lane == 0 && tile == tile0) TC_STAMP(4);
       tc_fence_after();
       const bool has_bias = tm.has_bias != 0;
       EpiStore es;
@@ -520,7 +595,25 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         es.row_c = tm.m_dst0 + q * 32;
       }
       const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * a.BN);
-      if (a.dbg == 1) {
+      if constexpr (SPLIT) {
+        // partial sums of this CTA's K blocks go to shared memory (the stage ring is free: every MMA that read it has
+        // completed); [chunk][row][32 x int32], the eight 16-byte units of a row XOR-swizzled by the row
+        const int nc = min(a.BN / 32, (a.N - pc_tile + 31) / 32);
+        const int per = (a.BN / 32 + kTcEpiParts - 1) / kTcEpiParts;
+        const int c_begin = part * per, c_end = min(nc, c_begin + per);
+        for (int c = c_begin; c < c_end; ++c) {
+          uint32_t r[32];
+          if (kb_end > kb_begin) { tc_ld32(taddr0 + (uint32_t)(c * 32), r); tc_wait_ld(); }
+          else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          const uint32_t base = smem0 + (uint32_t)((c * kTcBM + row_in_tile) * 128);
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            st_shared_v4(base + (uint32_t)((u ^ (row_in_tile & 7)) << 4), r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
+        }
+      } else if (a.dbg == 1) {
         // timing experiment: no epilogue work
       } else if (!a.gated) {
         if (a.dbg == 3) { es.coalesce = false; es.row_ok = false; }
@@ -537,16 +630,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 32; ++i) x ^= r[i];
             if (x == 0x12345678u) atomicExch(a.status, 99); continue; }
-          switch (a.fast_act) {
-          case FA_NONE: tc_epi_chunk<FA_NONE>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
-          case FA_RELU: tc_epi_chunk<FA_RELU>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
-          case FA_GELU_TANH: tc_epi_chunk<FA_GELU_TANH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
-          case FA_GELU_ERF: tc_epi_chunk<FA_GELU_ERF>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
-          case FA_SIGMOID: tc_epi_chunk<FA_SIGMOID>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
-          case FA_SWISH: tc_epi_chunk<FA_SWISH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
-          case FA_TANH: tc_epi_chunk<FA_TANH>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
-          default: tc_epi_chunk<FA_GENERIC>(epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane); break;
-          }
+          tc_epi_dispatch(a.fast_act, epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane);
         }
       } else {
         // gated: packed columns [g(32) u(32)] -> 32 outputs; dst is [rows, I] bf16
@@ -606,6 +690,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (row_ok && epi.row_absmax) atomicMax(epi.row_absmax + m_global, __float_as_uint(amax));
       }
+      if (warp == 2 && lane == 0 && tile == tile0) TC_STAMP(5);
       tc_fence_before();
       __syncwarp();
       // this warp is done with the accumulator and with the tile's operand buffer
@@ -615,8 +700,75 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   }
 
+  if constexpr (SPLIT) {
+    // ------------------------------------------------------------------ sum over the cluster, then the epilogue
+    cluster_sync_all();   // every CTA's partial sums are in its shared memory
+    bool arrived = false;
+    if (threadIdx.x == 0) TC_STAMP(6);
+    const bool healthy = __shfl_sync(0xffffffffu, s_err ? 0 : 1, 0) != 0;   // one decision per warp: the barriers below are warp-wide
+    if (warp >= 2 && warp < 2 + kTcEpiWarps && healthy && tile0 < total_tiles) {
+      const int ew = warp - 2, q = warp & 3, part = ew >> 2, row_in_tile = q * 32 + lane;
+      const TileMeta tm = meta[0];
+      const TileCols &tcols = cols[0];
+      const int m_dst = tm.m_dst0 + row_in_tile;
+      EpiCtx cx;
+      cx.wei_scale = nullptr; cx.colsum = nullptr; cx.bias = nullptr; cx.dst = tm.dst; cx.ldc = tm.ldc;
+      cx.s_src = row_scale[0][row_in_tile];
+      const int pc_tile = tm.nt * a.BN;
+      const bool has_bias = tm.has_bias != 0;
+      EpiStore es;
+      const int esz = epi.dst_dt == DT_BF16 ? 2 : 4;
+      es.sbuf = epi_stage[ew];
+      es.pitch_bytes = tm.ldc * esz;
+      es.g_row0 = reinterpret_cast<uint8_t *>(tm.dst) + (int64_t)(tm.m_dst0 + q * 32) * es.pitch_bytes;
+      es.rows_valid = min(32, max(0, tm.rows - q * 32));
+      es.coalesce = ((reinterpret_cast<uintptr_t>(tm.dst) | (uintptr_t)es.pitch_bytes) & 15) == 0;
+      es.row_ok = row_in_tile < tm.rows;
+      es.map_c = (a.tma_store && es.coalesce) ? &map_c : nullptr;
+      es.row_c = tm.m_dst0 + q * 32;
+      const int nc = min(a.BN / 32, (a.N - pc_tile + 31) / 32);
+      // chunk c is finished by CTA c % k_splits; its warp parts share that CTA's chunks.  First all sums: the warp's 32
+      // rows of a chunk are 4 KiB in a row, added over the CTAs with whole-warp contiguous reads (remote shared memory is
+      // slow when every lane asks for a different line) and written back in place (only this CTA reads its own copy of a
+      // chunk it finishes).
+      for (int c = (int)crank + a.k_splits * part; c < nc; c += a.k_splits * kTcEpiParts) {
+        const uint32_t blk = smem0 + (uint32_t)((c * kTcBM + q * 32) * 128) + (uint32_t)(lane * 16);
+        uint4 sum[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum[i] = ld_shared_v4(blk + (uint32_t)(i * 512));
+        for (int j = 0; j < a.k_splits; ++j) {
+          if (j == (int)crank) continue;
+          const uint32_t rb = cluster_map(blk, (uint32_t)j);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 v = ld_cluster_v4(rb + (uint32_t)(i * 512));
+            sum[i].x += v.x; sum[i].y += v.y; sum[i].z += v.z; sum[i].w += v.w;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) st_shared_v4(blk + (uint32_t)(i * 512), sum[i].x, sum[i].y, sum[i].z, sum[i].w);
+      }
+      cluster_arrive_all();   // this warp reads no neighbour any more
+      arrived = true;
+      for (int c = (int)crank + a.k_splits * part; c < nc; c += a.k_splits * kTcEpiParts) {
+        uint32_t r[32];
+        const uint32_t base = smem0 + (uint32_t)((c * kTcBM + row_in_tile) * 128);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint4 v = ld_shared_v4(base + (uint32_t)((u ^ (row_in_tile & 7)) << 4));
+          r[4 * u] = v.x; r[4 * u + 1] = v.y; r[4 * u + 2] = v.z; r[4 * u + 3] = v.w;
+        }
+        tc_epi_dispatch(a.fast_act, epi, cx, r, tcols, c * 32, pc_tile + c * 32, a.N, m_dst, has_bias, es, lane);
+      }
+    }
+    // nobody leaves while a neighbour may still read its shared memory: arrive as soon as the own reads are done,
+    // wait at the very end
+    if (!arrived) cluster_arrive_all();
+  }
+
   // ---------------------------------------------------------------------- teardown
   if (a.tma_store && warp >= 2 && warp < 2 + kTcEpiWarps && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if constexpr (SPLIT) cluster_wait_all();
   tc_fence_before();
   __syncthreads();
   if (s_err) {
@@ -624,6 +776,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int i = 0; i < 64; ++i) __nanosleep(20000);
     __syncthreads();
   }
+  if (threadIdx.x == 0) TC_STAMP(7);
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
