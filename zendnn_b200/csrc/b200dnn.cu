@@ -931,8 +931,9 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   if (which == 1 || which == 3) {
     int32_t rc = B200DNN_UNIMPLEMENTED;
     // decode kernel: 0 tiled only, 1 register-batch form, 2 ring form, 3..5 ring with that many groups per stage;
-    // default: ring for M <= 2 (measured faster there), register-batch form for 2 < M <= 16
-    const int dk = env_int("B200DNN_DECODE_KERNEL", M <= 2 ? 2 : 1);
+    // default: ring for M <= 2 and weights of 24 MB or more (measured faster there: 10.9 against 11.5 us at 45 MB, but
+    // 5.9 against 5.7 us at 16.8 MB), register-batch form otherwise
+    const int dk = env_int("B200DNN_DECODE_KERNEL", (M <= 2 && (long long)K * N >= (24ll << 20)) ? 2 : 1);
     const bool pdl = (d->flags & B200DNN_FLAG_STABLE_WEIGHTS) != 0 && env_int("B200DNN_PDL", 1) != 0;
     if (which == 1 && M <= 16 && dk >= 2) {
       // groups per stage: split the CTA's groups into equal sets of at most five
