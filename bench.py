@@ -297,7 +297,7 @@ def run_ours(args, rank, world, local_rank):
                      "traffic": int(round(step_bytes / n_launch_step * 0.9987)), "traffic_source": "ncu capture of one shape, scaled by algorithmic bytes",
                      "achieved_def": "algorithmic bytes of one step / device time of the step (all launches are this kernel)",
                      "peak_source": peaks["src"],
-                     "kernel": "decode_ring_kernel (M <= 2), decode_gemm_kernel (2 < M <= 16)", "frac_of_8TBs": round(achieved / 8000.0, 4)},
+                     "kernel": "decode_gemm_kernel (M = 4, 16 and the 16.8 MB weight at M = 1), decode_ring_kernel (M = 1, 45 MB weights)", "frac_of_8TBs": round(achieved / 8000.0, 4)},
         "per_shape": per,
     }
     # free the decode operands before the other workloads of the metric are measured
