@@ -115,6 +115,14 @@ def ep_moe_forward(x, logits, topk, num_experts, num_shared, ops, group=None, ti
     """One expert-parallel MoE layer for this rank's tokens.  x [T,K] bf16, logits [T,E] f32.
     `ops.all` holds this rank's routed experts (in local order) followed by the shared experts."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def mark(name):
+        # timing: a list that receives (phase name, CUDA event) pairs, for per-phase device times
+        if timing is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            timing.append((name, ev))
+    mark("start")
     T = x.shape[0]
     S = num_shared
     e_local = (num_experts + world - 1) // world
@@ -122,6 +130,7 @@ def ep_moe_forward(x, logits, topk, num_experts, num_shared, ops, group=None, ti
     keys = dispatch_keys(ids.reshape(-1).to(torch.int64), world, num_experts)
     counts, slot_to_row = ops.sort_slots(keys, world * e_local)
     R = T * topk
+    mark("route+sort")
 
     if world > 1:
         recv_counts = torch.empty_like(counts)
@@ -135,6 +144,7 @@ def ep_moe_forward(x, logits, topk, num_experts, num_shared, ops, group=None, ti
     else:
         group_rows = counts.cpu().tolist()
         R_recv, base_send = R, 0                                           # rows: [routed | shared]
+    mark("counts exchange")
     base_shared = R_recv
     n_rows = base_shared + S * T + (R if world > 1 else 0)
 
@@ -144,11 +154,13 @@ def ep_moe_forward(x, logits, topk, num_experts, num_shared, ops, group=None, ti
     slot_rows = torch.cat(cols, 1).contiguous()
     slot_w = w if S == 0 else torch.cat([w, torch.ones(T, S, dtype=w.dtype, device=w.device)], 1).contiguous()
     q, s = ops.quant_scatter(x, slot_rows, n_rows)
+    mark("quantise+scatter")
 
     if world > 1:
         dist.all_to_all_single(q[:R_recv], q[base_send:], recv_split, send_split, group=group)
         dist.all_to_all_single(s[:R_recv], s[base_send:], recv_split, send_split, group=group)
 
+    mark("dispatch all-to-all")
     # one grouped computation: (source rank, local expert) groups over the received rows, then the shared experts
     n_local = getattr(ops, "n_local", e_local)
     # local experts that do not exist on this rank (num_experts not divisible by world) get no rows by construction
@@ -158,7 +170,11 @@ def ep_moe_forward(x, logits, topk, num_experts, num_shared, ops, group=None, ti
     n_in = base_shared + S * T
     o = ops.new_rows(n_rows, x)
     ops.experts(q[:n_in], s[:n_in], group_rows, group_expert, o)
+    mark("experts")
 
     if world > 1:
         dist.all_to_all_single(o[base_send:], o[:R_recv], send_split, recv_split, group=group)
-    return ops.reduce_rows(o, slot_rows, slot_w)
+    mark("combine all-to-all")
+    y = ops.reduce_rows(o, slot_rows, slot_w)
+    mark("reduce")
+    return y
