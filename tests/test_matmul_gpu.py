@@ -308,6 +308,7 @@ def test_bounded_waits_leave_a_status_and_a_usable_context(capi, oracle, monkeyp
     d = capi.make_matmul(M, N, K, dA, dW, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["s32"], weights_const=False)
     assert capi.lib.b200dnn_stream_status(st) == capi.SUCCESS
     monkeypatch.setenv("B200DNN_TEST_NO_LOADS", "1")
+    monkeypatch.setenv("B200DNN_DECODE_KERNEL", "2")   # the ring form (by default only weights of 24 MB or more take it)
     assert capi.matmul(d, st) == capi.SUCCESS          # device pointers: the call only enqueues
     assert capi.lib.b200dnn_stream_status(st) == capi.FAILURE
     assert "gave up waiting" in capi.last_error()

@@ -129,9 +129,14 @@ int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, c
     B2_CUDA(cudaGetLastError());
     return B200DNN_SUCCESS;
   }
-  if (src_dt == B200DNN_BF16) quant_per_token_kernel<uint16_t><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
-  else if (src_dt == B200DNN_F32) quant_per_token_kernel<float><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
-  else return fail(B200DNN_UNIMPLEMENTED, "per-token quantisation takes f32 or bf16 input");
+  const bool short_row = a.K / E <= 2 * kQuantThreads;     // the whole row fits two cached vectors per thread
+  if (src_dt == B200DNN_BF16) {
+    if (short_row) quant_per_token_kernel<uint16_t, 2><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
+    else quant_per_token_kernel<uint16_t, kQuantRegVec><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
+  } else if (src_dt == B200DNN_F32) {
+    if (short_row) quant_per_token_kernel<float, 2><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
+    else quant_per_token_kernel<float, kQuantRegVec><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
+  } else return fail(B200DNN_UNIMPLEMENTED, "per-token quantisation takes f32 or bf16 input");
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
   return B200DNN_SUCCESS;

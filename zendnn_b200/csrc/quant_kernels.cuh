@@ -81,9 +81,11 @@ __device__ __forceinline__ float block_max(float v, float *sh) {
   return r;
 }
 
-// One CTA per row.  T = uint16_t (bf16 bits) or float.
-template <typename T>
-__global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuantArgs a) {
+// One CTA per row.  T = uint16_t (bf16 bits) or float; NV = 16-byte vectors of the row that a thread keeps in registers
+// between the two passes (2 for rows up to 512 vectors: few registers, six CTAs per SM; 8 for long rows, with the
+// register budget of four CTAs per SM: left to its own choice the compiler took 32 registers and spilled the cache).
+template <typename T, int NV>
+__global__ void __launch_bounds__(kQuantThreads, NV > 2 ? 4 : 6) quant_per_token_kernel(RowQuantArgs a) {
   __shared__ float sh[kQuantThreads / 32];
   constexpr int E = VecTraits<T>::kPer16B;
   const int r = blockIdx.x;
@@ -108,12 +110,12 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
   const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (K % E == 0) &&
                    (!dst || (reinterpret_cast<uintptr_t>(dst) % E) == 0);
   const int nvec = vec ? K / E : 0;
-  uint4 cache[kQuantRegVec];
+  uint4 cache[NV];
   float amax = 0.f;
   const bool need_amax = a.absmax_bits == nullptr;   // the row maximum may be given
   if (vec) {
 #pragma unroll
-    for (int j = 0; j < kQuantRegVec; ++j) {
+    for (int j = 0; j < NV; ++j) {
       int v = threadIdx.x + j * kQuantThreads;
       if (v < nvec) {
         cache[j] = reinterpret_cast<const uint4 *>(src)[v];
@@ -124,7 +126,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
         }
       }
     }
-    for (int v = threadIdx.x + kQuantRegVec * kQuantThreads; need_amax && v < nvec; v += kQuantThreads) {
+    for (int v = threadIdx.x + NV * kQuantThreads; need_amax && v < nvec; v += kQuantThreads) {
       uint4 q = reinterpret_cast<const uint4 *>(src)[v];
       const T *e = reinterpret_cast<const T *>(&q);
 #pragma unroll
@@ -166,11 +168,11 @@ __global__ void __launch_bounds__(kQuantThreads) quant_per_token_kernel(RowQuant
       } else put(dst, o, v);
     };
 #pragma unroll
-    for (int j = 0; j < kQuantRegVec; ++j) {
+    for (int j = 0; j < NV; ++j) {
       int v = threadIdx.x + j * kQuantThreads;
       if (v < nvec) emit(cache[j], v);
     }
-    for (int v = threadIdx.x + kQuantRegVec * kQuantThreads; v < nvec; v += kQuantThreads)
+    for (int v = threadIdx.x + NV * kQuantThreads; v < nvec; v += kQuantThreads)
       emit(reinterpret_cast<const uint4 *>(src)[v], v);
   } else {
     for (int k = threadIdx.x; k < K; k += kQuantThreads) {
