@@ -440,19 +440,35 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
     if (can) B2_TRY(make_map_store(&map_c, epi.dst, (uint64_t)cols * 2, (uint64_t)M_total, (uint64_t)epi.ldc * 2));
     else map_c = map_a;
   }
-  if (args.k_splits > 1) {
-    // one cluster of k_splits CTAs per tile; the partial sums need BN * 512 bytes of the stage ring
-    B2_CHECK((size_t)args.BN * 512 <= (size_t)stages * stage_bytes, B200DNN_FAILURE, "split form: stage ring smaller than the partial sums");
-    B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<true>, kTcSmemBudget + 1024));
+  // Both forms are launched with the programmatic-serialisation attribute: the kernel waits (griddepcontrol.wait) for
+  // everything before it in the stream before it touches global memory, so the ordering is that of a plain launch; what
+  // overlaps with the tail of the previous kernel is the launch itself.
+  {
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)(tiles * args.k_splits)); cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)args.k_splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<true>, map_a, map_b, map_c, args, epi));
-  } else
-  tc_gemm_kernel<false><<<grid, kTcThreads, smem, st>>>(map_a, map_b, map_c, args, epi);
+    cfg.blockDim = dim3(kTcThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (env_int("B200DNN_PDL", 1) != 0) {
+      attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[na].val.programmaticStreamSerializationAllowed = 1;
+      ++na;
+    }
+    if (args.k_splits > 1) {
+      // one cluster of k_splits CTAs per tile; the partial sums need BN * 512 bytes of the stage ring
+      B2_CHECK((size_t)args.BN * 512 <= (size_t)stages * stage_bytes, B200DNN_FAILURE, "split form: stage ring smaller than the partial sums");
+      B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<true>, kTcSmemBudget + 1024));
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = (unsigned)args.k_splits; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1;
+      ++na;
+      cfg.gridDim = dim3((unsigned)(tiles * args.k_splits));
+      cfg.attrs = attr; cfg.numAttrs = na;
+      B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<true>, map_a, map_b, map_c, args, epi));
+    } else {
+      cfg.gridDim = dim3((unsigned)grid);
+      cfg.attrs = attr; cfg.numAttrs = na;
+      B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<false>, map_a, map_b, map_c, args, epi));
+    }
+  }
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
   return B200DNN_SUCCESS;

@@ -413,6 +413,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int s_err;
 
+  // programmatic dependent launch: the next kernel of the stream may take this CTA's SM as soon as it is free; this
+  // kernel touches global memory only after griddepcontrol.wait below (the set-up before it uses none)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) TC_STAMP(0);
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -446,6 +449,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // everything before this launch in the stream is complete and visible
   if (threadIdx.x == 0) TC_STAMP(1);
 
   const int m_tiles = a.tile_prefix ? a.tile_prefix[a.n_groups] : a.m_tiles_plain;
