@@ -88,6 +88,9 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? 4 : 6) quant_per_token_kernel(RowQuantArgs a) {
   __shared__ float sh[kQuantThreads / 32];
   constexpr int E = VecTraits<T>::kPer16B;
+  // a GEMM launched as a programmatic dependent may start its set-up while this grid drains (it waits for the whole
+  // grid before it reads anything)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int r = blockIdx.x;
   const T *src; int8_t *dst; void *scale_out; int64_t scale_idx;
   if (a.n_groups > 0) {
@@ -190,6 +193,7 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? 4 : 6) quant_per_token
 template <typename T, int NV>
 __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs a, int rows) {
   constexpr int E = VecTraits<T>::kPer16B;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= rows) return;
   const int lane = threadIdx.x & 31;
