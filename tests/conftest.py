@@ -3,6 +3,9 @@ import sys
 
 import pytest
 
+# the library reads its tuning and test knobs once per process unless told otherwise; tests change them between calls
+os.environ.setdefault("B200DNN_ENV_DYNAMIC", "1")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

@@ -21,8 +21,20 @@ namespace {
 
 cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// Tuning and test knobs.  The environment is read once per knob (a lookup walks the whole environment, a microsecond
+// per call on a box with a few hundred variables, and a call asks for several); with B200DNN_ENV_DYNAMIC=1, which the
+// tests set, every call reads it afresh.  name must be a string literal (the cache is keyed by its address).  Callers
+// hold the runtime mutex.
 int env_int(const char *name, int dflt) {
+  static const bool dynamic = [] { const char *e = getenv("B200DNN_ENV_DYNAMIC"); return e && atoi(e) != 0; }();
+  if (dynamic) { const char *e = getenv(name); return e ? atoi(e) : dflt; }
+  struct Slot { const char *name; bool set; int value; };
+  static Slot slots[64];
+  static int n_slots = 0;
+  for (int i = 0; i < n_slots; ++i)
+    if (slots[i].name == name) return slots[i].set ? slots[i].value : dflt;
   const char *e = getenv(name);
+  if (n_slots < 64) { slots[n_slots].name = name; slots[n_slots].set = e != nullptr; slots[n_slots].value = e ? atoi(e) : 0; ++n_slots; }
   return e ? atoi(e) : dflt;
 }
 
