@@ -83,9 +83,9 @@ __device__ __forceinline__ float block_max(float v, float *sh) {
 
 // One CTA per row.  T = uint16_t (bf16 bits) or float; NV = 16-byte vectors of the row that a thread keeps in registers
 // between the two passes (2 for rows up to 512 vectors: few registers, six CTAs per SM; 8 for long rows, with the
-// register budget of four CTAs per SM: left to its own choice the compiler took 32 registers and spilled the cache).
+// register budget of four or five CTAs per SM: left to its own choice the compiler took 32 registers and spilled the cache).
 template <typename T, int NV>
-__global__ void __launch_bounds__(kQuantThreads, NV > 2 ? 4 : 6) quant_per_token_kernel(RowQuantArgs a) {
+__global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (sizeof(T) == 2 ? 5 : 4) : 6) quant_per_token_kernel(RowQuantArgs a) {
   __shared__ float sh[kQuantThreads / 32];
   constexpr int E = VecTraits<T>::kPer16B;
   // a GEMM launched as a programmatic dependent may start its set-up while this grid drains (it waits for the whole

@@ -36,7 +36,10 @@ def local_expert_index(e, world):
 def dispatch_keys(ids, world, num_experts):
     """Sort key of every (token,k) slot: destination rank major, local expert minor."""
     e_local = (num_experts + world - 1) // world
-    return ((ids % world) * e_local + ids // world).to(torch.int32)
+    ids = ids.to(torch.int32)                      # no-op for the router's int32 ids
+    if world == 1:
+        return ids
+    return (ids % world) * e_local + torch.div(ids, world, rounding_mode="floor")
 
 
 def experts_on_rank(rank, world, num_experts):
@@ -127,7 +130,7 @@ def ep_moe_forward(x, logits, topk, num_experts, num_shared, ops, group=None, ti
     S = num_shared
     e_local = (num_experts + world - 1) // world
     ids, w = ops.route(logits, topk)
-    keys = dispatch_keys(ids.reshape(-1).to(torch.int64), world, num_experts)
+    keys = dispatch_keys(ids.reshape(-1), world, num_experts)
     counts, slot_to_row = ops.sort_slots(keys, world * e_local)
     R = T * topk
     mark("route+sort")
