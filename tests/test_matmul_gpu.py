@@ -221,6 +221,27 @@ def test_device_pointers_and_weight_cache(capi, oracle):
     assert capi.lib.b200dnn_clear_caches() == capi.SUCCESS
 
 
+def test_host_inputs_with_device_output_back_to_back(capi, oracle):
+    """Small host inputs travel in one pinned block per call; with a device output the call returns before that block
+    has been read, and the next call must not overwrite it early: eight calls with different inputs, one sync."""
+    import torch
+    M, K, N = 4, 1024, 512
+    dev = torch.device("cuda:0")
+    cases = [decode_case(oracle, M, K, N, seed=20 + i) for i in range(8)]
+    W = torch.from_numpy(cases[0]["W"]).to(dev)
+    sw = torch.from_numpy(cases[0]["sw"]).to(dev)
+    outs = [torch.zeros(M, N, dtype=torch.bfloat16, device=dev) for _ in cases]
+    st = torch.cuda.current_stream().cuda_stream
+    for c, out in zip(cases, outs):
+        d = capi.make_matmul(M, N, K, c["A"], W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["bf16"], src_scale=c["sa"], wei_scale=sw)
+        assert capi.matmul(d, st) == capi.SUCCESS, capi.last_error()
+    torch.cuda.synchronize()
+    for c, out in zip(cases, outs):
+        ref = oracle.matmul_w8a8(c["A"], cases[0]["W"], "bf16", src_scale=c["sa"], wei_scale=cases[0]["sw"])
+        assert (out.view(torch.int16).cpu().numpy().view(np.uint16) == ref).all()
+    assert capi.lib.b200dnn_clear_caches() == capi.SUCCESS
+
+
 def test_contract_violations(capi):
     """Boundary contract: failures and unimplemented features are reported, nothing is computed."""
     A = np.zeros((4, 64), dtype=np.int8); W = np.zeros((64, 16), dtype=np.int8); out = np.zeros((4, 16), dtype=np.float32)
