@@ -111,13 +111,19 @@ B200DNN_API int32_t b200dnn_matmul(const b200dnn_matmul_t *desc, void *stream);
 /* No counterpart in the reference.  The same W8A8 matmul for callers that cannot allocate device
  * memory at call time (a server whose own pool already holds all free memory, a latency-bound loop
  * that cannot risk a blocking cudaMalloc): it never allocates.  The split-K scratch is a fixed
- * 8 MiB + 16 KiB device array inside the library, held by every GPU that loads it; shapes that need
- * more are rejected with failure.  Restrictions: every pointer is a device pointer, the weight is a
- * buffer written by b200dnn_prepack for this K and N (wei_format 'r'), no dynamic_quant.  The first
- * call on a device resolves the array's address (make that call before any stream capture).  All
- * calls share the array: calls that overlap on the GPU race, so keep them on one stream or
- * otherwise serialised. */
+ * 8 MiB + 16 KiB device array inside the library, held by every GPU that uses it until the process
+ * exits; split shapes that need more are rejected with failure (shapes that are not split over K use
+ * no scratch and are never rejected for it).  Restrictions, all checked: every pointer is a device
+ * pointer, the weight is a buffer written by b200dnn_prepack for this K and N (wei_format 'r'), no
+ * dynamic_quant.  The first call on a device is a warm-up: it loads the module that holds the array
+ * and resolves the array's address, so make it before the application's pool takes the remaining
+ * memory and before any stream capture.  All calls share the array: calls that overlap on the GPU
+ * race, so keep them on one stream or otherwise serialised. */
 B200DNN_API int32_t b200dnn_matmul_static_scratch(const b200dnn_matmul_t *desc, void *stream);
+/* No counterpart in the reference.  Bytes of the fixed array that b200dnn_matmul_static_scratch would use for this
+ * shape on a device with sm_count SMs (0 = the current device); 0 bytes for shapes that are not split.  Returns
+ * failure when the shape would be rejected.  Host arithmetic only. */
+B200DNN_API int32_t b200dnn_static_scratch_query(int32_t M, int32_t N, int32_t K, int32_t sm_count, size_t *bytes);
 
 /* weight_prepack_size (reorder/prepack/lowoha_prepack.cpp:285): bytes of the packed form of a
  * K x N s8 weight (multiple of 64).  gated != 0 selects the gate/up interleaved form used by
@@ -242,6 +248,60 @@ B200DNN_API int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, con
 B200DNN_API int32_t b200dnn_moe_weighted_reduce_rows(const void *rows, int64_t ld_rows, const int32_t *slot_rows,
                                                      const float *slot_weights, int32_t num_tokens, int32_t nslots,
                                                      int32_t D, int32_t dt, void *out, int64_t ld_out, void *stream);
+
+/* ---- Expert-parallel fused MoE across the GPUs of one node, one process per GPU (or several handles in one process).
+ * No counterpart in the reference (a single-process CPU library); the per-expert contract is group_matmul_direct's
+ * (matmul/lowoha_matmul.hpp:204-223: independent experts, M_e = 0 allowed).  Routed expert e lives on rank expert_rank[e],
+ * shared experts are replicated, tokens are data-parallel.  The token exchange is part of the library's own kernels
+ * (stores and loads over peer memory); NCCL carries only the per-expert row counts and two barriers per layer.  The
+ * result equals b200dnn_moe_layer on the same tokens bit for bit. ---- */
+typedef struct b200dnn_ep_config_t {
+  int32_t world, rank;          /* 1 <= world <= 8 */
+  int32_t num_experts;          /* routed experts over all ranks (<= 256) */
+  int32_t num_shared;           /* shared experts, applied to every token with weight 1 */
+  int32_t topk;
+  int32_t max_tokens;           /* largest T of a call on any rank: sizes the exchange buffers */
+  int32_t K, I, H;              /* hidden size, expert FFN width, output width */
+  int32_t transB, act;          /* as b200dnn_fused_moe */
+  int32_t capacity_rows;        /* rows one rank accepts from one source rank; 0 = max_tokens * topk, which can never overflow */
+  const int32_t *expert_rank;   /* host array [num_experts], owner of each routed expert; NULL = e % world */
+} b200dnn_ep_config_t;
+/* Allocates this rank's buffers on the current device (the only allocation of the layer).  All ranks must use the
+ * same configuration apart from `rank`. */
+B200DNN_API int32_t b200dnn_ep_create(const b200dnn_ep_config_t *cfg, void **handle);
+B200DNN_API int32_t b200dnn_ep_destroy(void *handle);
+B200DNN_API int32_t b200dnn_ep_local_expert_count(void *handle, int32_t *n_local);
+/* Weights of this rank: its routed experts in ascending expert id, then the shared experts (M/src/dst_down ignored;
+ * device or host weights, device scales).  Packed once and cached by address like every constant weight. */
+B200DNN_API int32_t b200dnn_ep_set_experts(void *handle, const b200dnn_moe_expert_t *experts, int32_t n);
+/* One process per GPU: rank 0 makes an id (128 bytes, an ncclUniqueId), the application carries it to the other ranks,
+ * every rank connects (collective: creates the communicator unless nccl_comm, an ncclComm_t, is given, and opens the
+ * peers' buffers through CUDA IPC). */
+B200DNN_API int32_t b200dnn_ep_nccl_unique_id(void *id128);
+B200DNN_API int32_t b200dnn_ep_connect_nccl(void *handle, const void *id128, void *nccl_comm);
+/* All ranks in one process (handles[r] is rank r; same device, or devices with peer access). */
+B200DNN_API int32_t b200dnn_ep_connect_local(void *const *handles, int32_t world);
+/* One MoE layer for this rank's T tokens (collective over the ranks; T may differ per rank and may be 0):
+ * x [T,K] bf16, logits [T,num_experts] f32 -> out [T,H] bf16.  Enqueues on `stream` and returns (device buffers). */
+B200DNN_API int32_t b200dnn_moe_layer_ep(void *handle, const void *x, int64_t ldx, const float *logits, int32_t T, void *out,
+                                         int64_t ld_out, void *stream);
+/* The same for handles that share a process: every rank's phases in turn on one stream (no NCCL). */
+B200DNN_API int32_t b200dnn_moe_layer_ep_local(void *const *handles, int32_t world, const void *const *x, int64_t ldx,
+                                               const float *const *logits, const int32_t *T, void *const *out, int64_t ld_out,
+                                               void *stream);
+/* Rows every rank received in the last layer (routed + shared): the load imbalance as numbers.  Synchronises. */
+B200DNN_API int32_t b200dnn_ep_rows_per_rank(void *handle, int32_t *rows, void *stream);
+/* Waits for `stream`; failure when a kernel gave up a bounded wait, rows were dropped (capacity_rows too small) or
+ * the communicator reports an asynchronous error (a rank that died). */
+B200DNN_API int32_t b200dnn_ep_status(void *handle, void *stream);
+
+/* Per-phase device times of b200dnn_moe_layer and b200dnn_moe_layer_ep calls on `stream` (CUDA events recorded by the
+ * library itself; off by default).  b200dnn_phase_times waits for the stream and returns the milliseconds of the last
+ * call: index 0 route + slot ranks, 1 count exchange, 2 quantise + dispatch, 3 barrier, 4 first GEMM with the gated
+ * activation, 5 requantisation, 6 second GEMM, 7 barrier, 8 combine + weighted reduce. */
+enum { B200DNN_PHASES = 9 };
+B200DNN_API int32_t b200dnn_phase_timing(void *stream, int32_t enable);
+B200DNN_API int32_t b200dnn_phase_times(void *stream, float *ms, int32_t n);
 
 /* Drops every cached packed weight / staged buffer: the counterpart of the reference's cache
  * clearing between tests (gtests/gtest_utils.cpp:77-118) and clear_fused_moe_scratch()

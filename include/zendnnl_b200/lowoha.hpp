@@ -242,6 +242,15 @@ ZENDNNL_B200_API void clear_fused_moe_scratch();
 // text of the last failure on the calling thread
 ZENDNNL_B200_API const char *last_error();
 }  // namespace matmul
+
+// Not in the reference (a CPU library has no streams).  The CUDA stream (a cudaStream_t passed as void*) on which the
+// calling thread's matmul_direct / group_matmul_direct / reorder_direct calls enqueue their work; nullptr, the default,
+// is the legacy default stream.  Per thread: two threads with two streams run concurrently and share no scratch.
+// Calls whose buffers are all device memory return as soon as the work is enqueued.
+namespace b200 {
+ZENDNNL_B200_API void set_stream(void *cuda_stream);
+ZENDNNL_B200_API void *get_stream();
+}  // namespace b200
 }  // namespace lowoha
 }  // namespace zendnnl
 

@@ -30,6 +30,12 @@ CASES = [
     (128, 512, 128, True, True, 1, "bf16"),
     (19, 1024, 96, True, True, 2, "bf16"),
     (12, 384, 64, True, True, 5, "f32"),
+    (24, 512, 64, True, True, 3, "bf16"),
+    (10, 256, 48, True, True, 4, "bf16"),
+    (15, 320, 80, True, False, 6, "bf16"),
+    (9, 192, 32, False, True, 3, "f32"),
+    (6, 448, 96, True, True, 4, "f32"),
+    (21, 128, 64, True, True, 6, "f32"),
 ]
 
 

@@ -59,7 +59,7 @@ def test_s32_bit_exact_small(capi, oracle, kernel, shape):
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_golden_reference_cases(capi, oracle, golden, kernel):
     """Outputs of the reference's own INT8 tile kernel (tests/golden): <= 1 bf16 ulp."""
-    fused = {0: [], 1: ["relu"], 2: ["gelu_tanh"], 5: ["swish"]}
+    fused = {0: [], 1: ["relu"], 2: ["gelu_tanh"], 3: ["gelu_erf"], 4: ["sigmoid"], 5: ["swish"], 6: ["tanh"]}
     i = 0
     while "c%d_meta" % i in golden:
         p = "c%d_" % i
@@ -145,6 +145,46 @@ def test_tc_split_form(capi, oracle, monkeypatch, splits, bn, shape):
               wei_scale=sw, src_zp=np.array([128], dtype=np.int32), bias=bias, postops=["relu"])
     ref = oracle.epilogue(oracle.gemm_s32(Au, W), "f32", [0.02], sw, 128, oracle.colsum(W), bias, ["relu"])
     assert np.allclose(got, ref, rtol=2e-6, atol=1e-6)
+
+
+ELTWISE = ["gelu_erf", "sigmoid", "tanh", "elu", "leaky_relu", "gelu_tanh", "swish", "relu"]
+
+
+def _postop(name):
+    if name == "elu":
+        return dict(type="elu", alpha=1.0)
+    if name == "leaky_relu":
+        return dict(type="leaky_relu", alpha=0.01)
+    return name
+
+
+@pytest.mark.parametrize("kernel", KERNELS + [pytest.param("split", id="tc-split")])
+@pytest.mark.parametrize("name", ELTWISE)
+def test_eltwise_postops_single_and_chained(capi, oracle, monkeypatch, kernel, name):
+    """Every element-wise post-op of the supported subset, alone (the specialised epilogue loops of the tcgen05 kernel)
+    and inside a chain (the generic loop), on every kernel form: bf16 within 1 ulp of the oracle, f32 within rel 1e-5
+    (the sigmoid family is evaluated with the fast exponential and reciprocal).  Reference definitions:
+    operators/matmul/matmul_ref_kernel.cpp:694-761."""
+    M, K, N = (200, 512, 264) if kernel in (TC, "split") else (12, 512, 264)
+    if kernel == "split":
+        monkeypatch.setenv("B200DNN_TC_KSPLIT", "2")
+        monkeypatch.setenv("B200DNN_TC_BN", "128")
+        kernel = TC
+    rng = np.random.default_rng(len(name) * 7 + M)
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    sw = rng.uniform(1e-4, 5e-4, N).astype(np.float32)     # pre-activations of order +-3: both tails of every activation
+    bias = rng.normal(size=N).astype(np.float32)
+    add = rng.normal(size=(1, N)).astype(np.float32)
+    for po in ([_postop(name)], [dict(type="binary_add", buff=add), _postop(name), dict(type="clip", alpha=-2.0, beta=2.0)]):
+        kw = dict(weights_const=False, force_kernel=kernel, src_scale=sa, wei_scale=sw, bias=bias, postops=po)
+        ref = oracle.matmul_w8a8(A, W, "bf16", src_scale=sa, wei_scale=sw, bias=bias, postops=po)
+        got = run(capi, M, N, K, A, W, "bf16", **kw)
+        assert_bf16_close(got, ref, 1, "%s x%d" % (name, len(po)), atol=1e-5)
+        ref32 = oracle.matmul_w8a8(A, W, "f32", src_scale=sa, wei_scale=sw, bias=bias, postops=po)
+        got32 = run(capi, M, N, K, A, W, "f32", **kw)
+        assert np.allclose(got32, ref32, rtol=1e-5, atol=1e-5), (name, float(np.abs(got32 - ref32).max()))
 
 
 def test_scales_in_bf16_storage(capi, oracle):

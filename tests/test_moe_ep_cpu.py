@@ -105,6 +105,45 @@ def test_placement_helpers():
     assert all(moe_ep.expert_owner(e, 4) == e % 4 and moe_ep.local_expert_index(e, 4) == e // 4 for e in range(8))
 
 
+def test_planned_placement_balances_a_skewed_histogram():
+    """Zipf-like loads: the planned map keeps the busiest rank near the mean, the modulo map does not; every rank gets at
+    most ceil(E / world) experts; the map is a pure function of the histogram."""
+    E, world = 64, 8
+    hist = [int(100000 / (r + 1) ** 1.1) for r in range(E)]
+    g = torch.Generator().manual_seed(5)
+    perm = torch.randperm(E, generator=g).tolist()
+    hist = [hist[perm[e]] for e in range(E)]
+    owner = moe_ep.plan_expert_placement(hist, world)
+    assert owner == moe_ep.plan_expert_placement(list(hist), world)
+    load = [sum(h for h, o in zip(hist, owner) if o == r) for r in range(world)]
+    naive = [sum(h for e, h in enumerate(hist) if e % world == r) for r in range(world)]
+    mean = sum(hist) / world
+    assert max(load) <= 1.1 * max(max(hist), mean)       # the busiest expert alone is a lower bound for any map
+    assert max(naive) > 1.1 * max(load)
+    assert max(owner.count(r) for r in range(world)) <= 8 and sorted(set(owner)) == list(range(world))
+    assert moe_ep.modulo_placement(5, 2) == [0, 1, 0, 1, 0]
+
+
+def _plan_worker(rank, world, port, E, topk, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    # every rank sees only its own tokens; the histogram is summed over the ranks before planning
+    _, logits = _inputs(256, 8, E, 100 + rank)
+    ids = torch.topk(logits, topk, dim=1).indices.reshape(-1)
+    hist = torch.bincount(ids, minlength=E)
+    dist.all_reduce(hist)
+    ret[rank] = moe_ep.plan_expert_placement(hist.tolist(), world)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_plan_the_same_placement():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_plan_worker, args=(2, _free_port(), 12, 3, ret), nprocs=2, join=True)
+    assert ret[0] == ret[1] and sorted(set(ret[0])) == [0, 1]
+
+
 def _absent_worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     if rank == 1:

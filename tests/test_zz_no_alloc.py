@@ -74,9 +74,42 @@ def test_static_scratch_rejects_what_it_cannot_hold(capi):
     d.dynamic_quant = 1                           # quantising the source would need workspace
     assert capi.lib.b200dnn_matmul_static_scratch(d, st) == capi.UNIMPLEMENTED
     d.dynamic_quant = 0
-    d.N = 200000                                  # far more output tiles than the fixed scratch covers
-    d.ldc = 200000
-    d.wei_scale.count = 200000                    # (rejected before any buffer is touched)
+    # nothing is staged, so a host pointer must be refused, not handed to the kernel
+    host_src = np.zeros((4, 256), dtype=np.int8)
+    src_dev = d.src
+    d.src = host_src.ctypes.data
     assert capi.lib.b200dnn_matmul_static_scratch(d, st) == capi.FAILURE
-    assert "static scratch" in capi.last_error()
+    assert "device pointers only" in capi.last_error()
+    d.src = src_dev
+    # a weight packed for another shape is refused (its header says K=256, N=64), not read out of bounds
+    d.N, d.ldc, d.wei_scale.count = 128, 128, 128
+    assert capi.lib.b200dnn_matmul_static_scratch(d, st) == capi.FAILURE
+    assert "prepacked weight is" in capi.last_error()
     torch.cuda.synchronize()
+
+
+def test_unsplit_shapes_need_no_scratch_and_steady_calls_allocate_nothing(capi):
+    """A shape with more output tiles than the fixed array has counters for is not split over K, uses no scratch and
+    must run (and equal the regular entry point); a steady-state call leaves the free device memory unchanged."""
+    import ctypes as C
+    import torch
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    M, K, N = 2048, 256, 4096                      # 128 x 128 = 16384 tiles, no split
+    need = C.c_size_t(123)
+    assert capi.lib.b200dnn_static_scratch_query(M, N, K, 0, C.byref(need)) == capi.SUCCESS and need.value == 0
+    descs, outs, keep = _case(capi, torch, dev, M, K, N, seed=7)
+    descs[0].force_kernel = 3                      # the same tiled streaming kernel through the regular entry point
+    capi.check(capi.lib.b200dnn_matmul(descs[0], st))
+    capi.check(capi.lib.b200dnn_matmul_static_scratch(descs[1], st))
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+    # steady state: the first call on the device is the warm-up (module load, symbol address); later calls allocate nothing
+    d2, o2, keep2 = _case(capi, torch, dev, 16, 4096, 1024, seed=3)
+    capi.check(capi.lib.b200dnn_matmul_static_scratch(d2[1], st))
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        capi.check(capi.lib.b200dnn_matmul_static_scratch(d2[1], st))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0

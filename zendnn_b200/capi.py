@@ -51,13 +51,26 @@ class MoeExpert(C.Structure):
                 ("dst_down", C.c_void_p), ("ldc_down", C.c_int64)]
 
 
+class EpConfig(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("num_experts", C.c_int32), ("num_shared", C.c_int32),
+                ("topk", C.c_int32), ("max_tokens", C.c_int32), ("K", C.c_int32), ("I", C.c_int32), ("H", C.c_int32),
+                ("transB", C.c_int32), ("act", C.c_int32), ("capacity_rows", C.c_int32), ("expert_rank", C.c_void_p)]
+
+
+PHASES = 9
+PHASE_NAMES = ["route+rank", "count exchange", "quantise+dispatch", "barrier", "gemm1+act", "requantise", "gemm2", "barrier",
+               "combine+reduce"]
+
 EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b200dnn_launch_count",
-           "b200dnn_matmul", "b200dnn_matmul_static_scratch", "b200dnn_prepack_size", "b200dnn_prepack", "b200dnn_quant_per_token",
+           "b200dnn_matmul", "b200dnn_matmul_static_scratch", "b200dnn_static_scratch_query", "b200dnn_prepack_size", "b200dnn_prepack", "b200dnn_quant_per_token",
            "b200dnn_group_quant_per_token", "b200dnn_quant_dynamic", "b200dnn_quant_static",
            "b200dnn_dequant_static", "b200dnn_gated_act", "b200dnn_moe_weighted_reduce", "b200dnn_fused_moe",
            "b200dnn_moe_route", "b200dnn_moe_layer", "b200dnn_clear_caches", "b200dnn_stream_status", "b200dnn_moe_sort_slots",
            "b200dnn_quant_per_token_gather", "b200dnn_quant_per_token_scatter", "b200dnn_moe_experts_s8",
-           "b200dnn_moe_weighted_reduce_rows"]
+           "b200dnn_moe_weighted_reduce_rows", "b200dnn_ep_create", "b200dnn_ep_destroy", "b200dnn_ep_local_expert_count",
+           "b200dnn_ep_set_experts", "b200dnn_ep_nccl_unique_id", "b200dnn_ep_connect_nccl", "b200dnn_ep_connect_local",
+           "b200dnn_moe_layer_ep", "b200dnn_moe_layer_ep_local", "b200dnn_ep_rows_per_rank", "b200dnn_ep_status",
+           "b200dnn_phase_timing", "b200dnn_phase_times"]
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -72,6 +85,7 @@ lib.b200dnn_launch_count.restype = C.c_int64
 i32, i64, vp = C.c_int32, C.c_int64, C.c_void_p
 lib.b200dnn_matmul.argtypes = [C.POINTER(MatmulDesc), vp]
 lib.b200dnn_matmul_static_scratch.argtypes = [C.POINTER(MatmulDesc), vp]
+lib.b200dnn_static_scratch_query.argtypes = [i32, i32, i32, i32, C.POINTER(C.c_size_t)]
 lib.b200dnn_prepack.argtypes = [vp, i64, i64, i64, i32, i32, vp, vp]
 lib.b200dnn_quant_per_token.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i32, vp]
 lib.b200dnn_group_quant_per_token.argtypes = [i32, vp, i32, vp, vp, vp, vp, vp, vp, i32, vp]
@@ -91,6 +105,21 @@ lib.b200dnn_quant_per_token_gather.argtypes = [vp, i32, i64, i64, vp, i32, i64, 
 lib.b200dnn_quant_per_token_scatter.argtypes = [vp, i32, i64, i64, vp, i32, i64, vp, i64, vp, vp]
 lib.b200dnn_moe_experts_s8.argtypes = [vp, i64, vp, i32, vp, vp, C.POINTER(MoeExpert), i32, i32, i32, i32, i32, vp, i64, vp]
 lib.b200dnn_moe_weighted_reduce_rows.argtypes = [vp, i64, vp, vp, i32, i32, i32, i32, vp, i64, vp]
+
+
+lib.b200dnn_ep_create.argtypes = [C.POINTER(EpConfig), C.POINTER(vp)]
+lib.b200dnn_ep_destroy.argtypes = [vp]
+lib.b200dnn_ep_local_expert_count.argtypes = [vp, C.POINTER(i32)]
+lib.b200dnn_ep_set_experts.argtypes = [vp, C.POINTER(MoeExpert), i32]
+lib.b200dnn_ep_nccl_unique_id.argtypes = [vp]
+lib.b200dnn_ep_connect_nccl.argtypes = [vp, vp, vp]
+lib.b200dnn_ep_connect_local.argtypes = [C.POINTER(vp), i32]
+lib.b200dnn_moe_layer_ep.argtypes = [vp, vp, i64, vp, i32, vp, i64, vp]
+lib.b200dnn_moe_layer_ep_local.argtypes = [C.POINTER(vp), i32, C.POINTER(vp), i64, C.POINTER(vp), C.POINTER(i32), C.POINTER(vp), i64, vp]
+lib.b200dnn_ep_rows_per_rank.argtypes = [vp, C.POINTER(i32), vp]
+lib.b200dnn_ep_status.argtypes = [vp, vp]
+lib.b200dnn_phase_timing.argtypes = [vp, i32]
+lib.b200dnn_phase_times.argtypes = [vp, C.POINTER(C.c_float), i32]
 
 
 class B200DNNError(RuntimeError):

@@ -7,6 +7,7 @@
 
 #include "runtime.cuh"
 #include "common.cuh"
+#include "matmul_validate.cuh"
 #include "quant_kernels.cuh"
 #include "pack_kernels.cuh"
 #include "stream_gemm.cuh"
@@ -23,14 +24,15 @@ cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
 // Tuning and test knobs.  The environment is read once per knob (a lookup walks the whole environment, a microsecond
 // per call on a box with a few hundred variables, and a call asks for several); with B200DNN_ENV_DYNAMIC=1, which the
-// tests set, every call reads it afresh.  name must be a string literal (the cache is keyed by its address).  Callers
-// hold the runtime mutex.
+// tests set, every call reads it afresh.  name must be a string literal (the cache is keyed by its address).
 int env_int(const char *name, int dflt) {
   static const bool dynamic = [] { const char *e = getenv("B200DNN_ENV_DYNAMIC"); return e && atoi(e) != 0; }();
   if (dynamic) { const char *e = getenv(name); return e ? atoi(e) : dflt; }
   struct Slot { const char *name; bool set; int value; };
   static Slot slots[64];
   static int n_slots = 0;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
   for (int i = 0; i < n_slots; ++i)
     if (slots[i].name == name) return slots[i].set ? slots[i].value : dflt;
   const char *e = getenv(name);
@@ -70,24 +72,42 @@ PackedWeight view_of(const void *dev_base, const PackHeader &h) {
   return pw;
 }
 
-// Resolves the weight argument of a GEMM to a packed device buffer.
+// A cache-owned packed weight was written on the stream of the call that first saw it: a call on another stream waits
+// for that work (until it has been seen complete once).  Callers hold the cache mutex.
+int32_t wait_ready(PackedWeight &pw, cudaStream_t st) {
+  if (pw.complete || !pw.ready || st == pw.ready_stream) return B200DNN_SUCCESS;
+  if (cudaEventQuery(pw.ready) == cudaSuccess) { pw.complete = true; return B200DNN_SUCCESS; }
+  cudaGetLastError();
+  B2_CUDA(cudaStreamWaitEvent(st, pw.ready, 0));
+  return B200DNN_SUCCESS;
+}
+int32_t mark_ready(PackedWeight &pw, cudaStream_t st) {
+  B2_CUDA(cudaEventCreateWithFlags(&pw.ready, cudaEventDisableTiming));
+  B2_CUDA(cudaEventRecord(pw.ready, st));
+  pw.ready_stream = st; pw.complete = false;
+  return B200DNN_SUCCESS;
+}
+
+// Resolves the weight argument of a GEMM to a packed device buffer.  The caches belong to the device and are shared
+// by all streams; the mutex is held while a new weight is packed (once per weight).
 int32_t resolve_weight(const void *weight, int wei_format, int64_t K, int64_t N, int64_t ldb, int transB, int gated,
                        int weights_const, cudaStream_t st, PackedWeight *pw) {
-  Runtime &R = rt();
+  DeviceShared &D = *rt().shared;
   if (wei_format == 'r') {
+    std::lock_guard<std::mutex> lk(D.cache_mu);
     if (is_device_ptr(weight)) {
-      auto it = R.packed_registry.find(weight);
-      if (it == R.packed_registry.end()) {
+      auto it = D.packed_registry.find(weight);
+      if (it == D.packed_registry.end()) {
         PackHeader h;
         B2_CUDA(cudaMemcpyAsync(&h, weight, sizeof h, cudaMemcpyDeviceToHost, st));
         B2_CUDA(cudaStreamSynchronize(st));
         B2_CHECK(h.magic == kPackMagic, B200DNN_FAILURE, "mem_format_b='r' but the weight buffer was not written by b200dnn_prepack");
-        it = R.packed_registry.emplace(weight, view_of(weight, h)).first;
+        it = D.packed_registry.emplace(weight, view_of(weight, h)).first;
       }
       *pw = it->second;
     } else {
-      auto it = R.host_packed.find(weight);
-      if (it == R.host_packed.end()) {
+      auto it = D.host_packed.find(weight);
+      if (it == D.host_packed.end()) {
         PackHeader h; memcpy(&h, weight, sizeof h);
         B2_CHECK(h.magic == kPackMagic, B200DNN_FAILURE, "mem_format_b='r' but the weight buffer was not written by b200dnn_prepack");
         size_t bytes = pack_bytes(h.K, h.N);
@@ -95,8 +115,10 @@ int32_t resolve_weight(const void *weight, int wei_format, int64_t K, int64_t N,
         B2_CUDA(cudaMalloc(&d, bytes));
         B2_CUDA(cudaMemcpyAsync(d, weight, bytes, cudaMemcpyHostToDevice, st));
         PackedWeight v = view_of(d, h); v.owned = d;
-        it = R.host_packed.emplace(weight, v).first;
+        B2_TRY(mark_ready(v, st));
+        it = D.host_packed.emplace(weight, v).first;
       }
+      B2_TRY(wait_ready(it->second, st));
       *pw = it->second;
     }
     B2_CHECK(pw->K == K && pw->N == N && pw->gated == gated, B200DNN_FAILURE,
@@ -107,18 +129,20 @@ int32_t resolve_weight(const void *weight, int wei_format, int64_t K, int64_t N,
   B2_CHECK(wei_format == 'n' || wei_format == 0, B200DNN_FAILURE, "mem_format_b must be 'n' or 'r'");
   auto key = std::make_tuple(weight, K, N, ldb, transB, gated);
   const bool cache = weights_const && env_int("ZENDNNL_MATMUL_WEIGHT_CACHE", 1) != 0;
+  std::unique_lock<std::mutex> lk(D.cache_mu, std::defer_lock);
   if (cache) {
-    auto it = R.wcache.find(key);
-    if (it != R.wcache.end()) { *pw = it->second; return B200DNN_SUCCESS; }
+    lk.lock();
+    auto it = D.wcache.find(key);
+    if (it != D.wcache.end()) { B2_TRY(wait_ready(it->second, st)); *pw = it->second; return B200DNN_SUCCESS; }
   }
   const int64_t wrows = transB ? N : K, wcols = transB ? K : N;
   const void *w_dev = nullptr;
   B2_TRY(stage_in(weight, span_bytes(wrows, wcols, ldb, B200DNN_S8), st, &w_dev));
   void *buf = nullptr;
   if (cache) B2_CUDA(cudaMalloc(&buf, pack_bytes(K, N)));
-  else { buf = R.ws.alloc(pack_bytes(K, N)); B2_CHECK(buf, B200DNN_FAILURE, "workspace allocation failed"); }
+  else { buf = rt().ws.alloc(pack_bytes(K, N)); B2_CHECK(buf, B200DNN_FAILURE, "workspace allocation failed"); }
   B2_TRY(pack_into(w_dev, K, N, ldb, transB, gated, buf, st, pw));
-  if (cache) { pw->owned = buf; R.wcache.emplace(key, *pw); }
+  if (cache) { pw->owned = buf; B2_TRY(mark_ready(*pw, st)); D.wcache.emplace(key, *pw); }
   return B200DNN_SUCCESS;
 }
 
@@ -132,7 +156,8 @@ int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, c
                        (!a.dst || ((reinterpret_cast<uintptr_t>(a.dst) % E) == 0 && a.dst_ld % E == 0));
   if (aligned && rows >= 64 && a.K / E <= 32 * 8 && (src_dt == B200DNN_BF16 || src_dt == B200DNN_F32)) {
     const int nv = (a.K / E + 31) / 32;
-    const unsigned grid = (unsigned)((rows + 7) / 8);
+    unsigned grid = (unsigned)((rows + 7) / 8);
+    if (a.n_rows_dev && grid > (unsigned)(rt().sm_count * 16)) grid = (unsigned)(rt().sm_count * 16);   // the warps stride over the rows
 #define B2_QW(T, NV) quant_per_token_warp_kernel<T, NV><<<grid, 256, 0, st>>>(a, (int)rows)
     if (src_dt == B200DNN_BF16) { if (nv <= 2) B2_QW(uint16_t, 2); else if (nv <= 4) B2_QW(uint16_t, 4); else if (nv <= 8) B2_QW(uint16_t, 8); else B2_QW(uint16_t, 16); }
     else { if (nv <= 2) B2_QW(float, 2); else if (nv <= 4) B2_QW(float, 4); else if (nv <= 8) B2_QW(float, 8); else B2_QW(float, 16); }
@@ -142,12 +167,14 @@ int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, c
     return B200DNN_SUCCESS;
   }
   const bool short_row = a.K / E <= 2 * kQuantThreads;     // the whole row fits two cached vectors per thread
+  unsigned grid_rows = (unsigned)rows;
+  if (a.n_rows_dev && grid_rows > (unsigned)(rt().sm_count * 32)) grid_rows = (unsigned)(rt().sm_count * 32);   // the CTAs stride over the rows
   if (src_dt == B200DNN_BF16) {
-    if (short_row) quant_per_token_kernel<uint16_t, 2><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
-    else quant_per_token_kernel<uint16_t, kQuantRegVec><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
+    if (short_row) quant_per_token_kernel<uint16_t, 2><<<grid_rows, kQuantThreads, 0, st>>>(a);
+    else quant_per_token_kernel<uint16_t, kQuantRegVec><<<grid_rows, kQuantThreads, 0, st>>>(a);
   } else if (src_dt == B200DNN_F32) {
-    if (short_row) quant_per_token_kernel<float, 2><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
-    else quant_per_token_kernel<float, kQuantRegVec><<<(unsigned)rows, kQuantThreads, 0, st>>>(a);
+    if (short_row) quant_per_token_kernel<float, 2><<<grid_rows, kQuantThreads, 0, st>>>(a);
+    else quant_per_token_kernel<float, kQuantRegVec><<<grid_rows, kQuantThreads, 0, st>>>(a);
   } else return fail(B200DNN_UNIMPLEMENTED, "per-token quantisation takes f32 or bf16 input");
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
@@ -155,16 +182,15 @@ int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, c
 }
 
 // ------------------------------------------------------------------------------------ GEMM launchers
-// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device (the calls are serialised by the
-// runtime mutex): raises the limit to the largest size the kernel is launched with and remembers that it did.
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel and device: raises the limit to the largest size
+// the kernel is launched with and remembers that it did.
 int32_t ensure_max_smem(const void *fn, int bytes = 227 * 1024) {
-  static std::map<std::pair<const void *, int>, bool> done;
-  int dev = 0;
-  B2_CUDA(cudaGetDevice(&dev));
-  bool &d = done[{fn, dev}];
-  if (!d) {
+  DeviceShared &D = *rt().shared;
+  std::lock_guard<std::mutex> lk(D.attr_mu);
+  int &have = D.smem_limit[fn];
+  if (have < bytes) {
     B2_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    d = true;
+    have = bytes;
   }
   return B200DNN_SUCCESS;
 }
@@ -329,7 +355,7 @@ extern "C" __attribute__((visibility("default"))) int32_t b200dnn_debug_stamps(u
 
 // CTAs that are resident at once when the split form is launched in clusters of s (clusters do not tile the GPCs perfectly)
 int split_room(int s) {
-  static int cache[5] = {0, 0, 0, 0, 0};
+  int *cache = rt().shared->split_room;   // per device; two threads may both compute the same value
   if (cache[s] == 0) {
     cache[s] = -1;
     if (ensure_max_smem((const void *)tc_gemm_kernel<true>, kTcSmemBudget + 1024) == B200DNN_SUCCESS) {
@@ -486,17 +512,10 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
   return B200DNN_SUCCESS;
 }
 
-// reads back the tcgen05 status word (only on paths that synchronise anyway)
+// the stream has been drained: report a kernel that gave up on one of its bounded waits
 int32_t check_tc_status(cudaStream_t st) {
-  Runtime &R = rt();
-  B2_CUDA(cudaMemcpyAsync(R.status_host, R.status, 4, cudaMemcpyDeviceToHost, st));
   B2_CUDA(cudaStreamSynchronize(st));
-  if (*R.status_host != 0) {
-    int code = *R.status_host;
-    cudaMemsetAsync(R.status, 0, 4, st);
-    return fail(B200DNN_FAILURE, "a GEMM kernel gave up waiting on a barrier (code %d)", code);
-  }
-  return B200DNN_SUCCESS;
+  return read_status();
 }
 
 int32_t fill_epi(const b200dnn_matmul_t *d, EpiParams *e) {
@@ -525,10 +544,7 @@ size_t b200dnn_prepack_size(int64_t K, int64_t N, int32_t gated) {
 
 int32_t b200dnn_prepack(const void *weight, int64_t K, int64_t N, int64_t ldb, int32_t transB, int32_t gated, void *dst,
                         void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(weight && dst && K > 0 && N > 0, B200DNN_FAILURE, "prepack: null pointer or non-positive dimension");
   B2_CHECK(ldb >= (transB ? K : N), B200DNN_FAILURE, "prepack: ldb=%lld too small", (long long)ldb);
   const void *w_dev = nullptr;
@@ -537,17 +553,21 @@ int32_t b200dnn_prepack(const void *weight, int64_t K, int64_t N, int64_t ldb, i
   B2_TRY(stage_out(dst, pack_bytes(K, N), st, &out));
   PackedWeight pw;
   B2_TRY(pack_into(w_dev, K, N, ldb, transB, gated, out.dev, st, &pw));
-  if (!out.copy_back && !out.sync) rt().packed_registry[dst] = pw;
-  else rt().host_packed.erase(dst);
+  {
+    DeviceShared &D = *rt().shared;
+    std::lock_guard<std::mutex> lk(D.cache_mu);
+    if (!out.copy_back && !out.sync) D.packed_registry[dst] = pw;
+    else {
+      auto it = D.host_packed.find(dst);
+      if (it != D.host_packed.end()) { if (it->second.owned) cudaFree(it->second.owned); if (it->second.ready) cudaEventDestroy(it->second.ready); D.host_packed.erase(it); }
+    }
+  }
   return finish_out({&out}, st);
 }
 
 int32_t b200dnn_quant_per_token(const void *src, int32_t src_dt, int64_t M, int64_t K, int64_t src_ld, void *dst,
                                 int64_t dst_ld, void *scale, int32_t scale_dt, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(src && scale, B200DNN_FAILURE, "dynamic quantisation needs src and a scale buffer");
   B2_CHECK(M > 0 && K > 0 && src_ld >= K && (!dst || dst_ld >= K), B200DNN_FAILURE, "bad shape or stride");
   B2_CHECK(scale_dt == B200DNN_F32 || scale_dt == B200DNN_BF16, B200DNN_UNIMPLEMENTED, "scale dtype must be f32 or bf16");
@@ -566,20 +586,20 @@ int32_t b200dnn_quant_per_token(const void *src, int32_t src_dt, int64_t M, int6
 int32_t b200dnn_group_quant_per_token(int32_t num_groups, const void *const *src, int32_t src_dt, const int32_t *M,
                                       const int32_t *K, const int64_t *src_ld, void *const *dst, const int64_t *dst_ld,
                                       void *const *scale, int32_t scale_dt, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(num_groups > 0 && src && M && K && src_ld && dst && dst_ld && scale, B200DNN_FAILURE, "null argument");
   // groups with the same K share one launch; the reference allows K to differ per group, handled per K value
   std::vector<Staged> outs;
   outs.reserve(2 * num_groups);
   std::vector<const void *> s_dev(num_groups); std::vector<void *> d_dev(num_groups), sc_dev(num_groups);
   std::vector<int32_t> row_off(num_groups + 1, 0);
+  // one launch serves groups of one row length: K of the first group that has rows; a different K elsewhere is refused
+  int Kc = 0; for (int g = 0; g < num_groups; ++g) if (M[g] > 0) { Kc = K[g]; break; }
   for (int g = 0; g < num_groups; ++g) {
     row_off[g + 1] = row_off[g] + (M[g] > 0 ? M[g] : 0);
     if (M[g] <= 0) { s_dev[g] = nullptr; d_dev[g] = nullptr; sc_dev[g] = nullptr; continue; }
-    B2_CHECK(K[g] == K[0] || M[0] <= 0, B200DNN_UNIMPLEMENTED, "group_dynamic_quant: differing K per group");
+    B2_CHECK(K[g] == Kc, B200DNN_UNIMPLEMENTED, "group_dynamic_quant: differing K per group (group %d has K=%d, the first group with rows has K=%d)", g, K[g], Kc);
+    B2_CHECK(K[g] > 0 && (!dst[g] || dst_ld[g] >= K[g]), B200DNN_FAILURE, "group %d: bad K or destination stride", g);
     B2_CHECK(src[g] && scale[g] && src_ld[g] >= K[g], B200DNN_FAILURE, "group %d: null pointer or bad stride", g);
     B2_TRY(stage_in(src[g], span_bytes(M[g], K[g], src_ld[g], src_dt), st, &s_dev[g]));
     Staged a, b;
@@ -587,20 +607,18 @@ int32_t b200dnn_group_quant_per_token(int32_t num_groups, const void *const *src
     B2_TRY(stage_out(scale[g], (size_t)M[g] * dt_size(scale_dt), st, &b));
     d_dev[g] = a.dev; sc_dev[g] = b.dev; outs.push_back(a); outs.push_back(b);
   }
-  int Kc = 0; for (int g = 0; g < num_groups; ++g) if (M[g] > 0) { Kc = K[g]; break; }
   if (row_off[num_groups] == 0) return B200DNN_SUCCESS;
   // device tables
   const size_t tb = sizeof(void *) * num_groups;
-  uint8_t *tab = (uint8_t *)rt().ws.alloc(3 * tb + 2 * sizeof(int64_t) * num_groups + sizeof(int32_t) * (num_groups + 1));
-  B2_CHECK(tab, B200DNN_FAILURE, "workspace allocation failed");
   std::vector<uint8_t> host(3 * tb + 2 * sizeof(int64_t) * num_groups + sizeof(int32_t) * (num_groups + 1));
   uint8_t *h = host.data();
   memcpy(h, s_dev.data(), tb); memcpy(h + tb, d_dev.data(), tb); memcpy(h + 2 * tb, sc_dev.data(), tb);
   memcpy(h + 3 * tb, src_ld, sizeof(int64_t) * num_groups);
   memcpy(h + 3 * tb + sizeof(int64_t) * num_groups, dst_ld, sizeof(int64_t) * num_groups);
   memcpy(h + 3 * tb + 2 * sizeof(int64_t) * num_groups, row_off.data(), sizeof(int32_t) * (num_groups + 1));
-  B2_CUDA(cudaMemcpyAsync(tab, h, host.size(), cudaMemcpyHostToDevice, st));
-  B2_CUDA(cudaStreamSynchronize(st));   // host table goes out of scope
+  void *tab_dev = nullptr;
+  B2_TRY(upload_blob(h, host.size(), st, &tab_dev));
+  uint8_t *tab = (uint8_t *)tab_dev;
   RowQuantArgs a{};
   a.n_groups = num_groups; a.K = Kc; a.scale_dt = scale_dt; a.gather_div = 1;
   a.g_src = (const void *const *)tab; a.g_dst = (void *const *)(tab + tb); a.g_scale = (void *const *)(tab + 2 * tb);
@@ -615,10 +633,7 @@ int32_t b200dnn_group_quant_per_token(int32_t num_groups, const void *const *src
 
 int32_t b200dnn_quant_dynamic(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t src_ld, int32_t per_channel,
                               void *dst, int64_t dst_ld, float *scale, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(src && scale && M > 0 && N > 0 && src_ld >= N && (!dst || dst_ld >= N), B200DNN_FAILURE, "bad argument");
   B2_CHECK(src_dt == B200DNN_BF16 || src_dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "source must be f32 or bf16");
   const void *s_dev = nullptr;
@@ -651,10 +666,7 @@ int32_t b200dnn_quant_dynamic(const void *src, int32_t src_dt, int64_t M, int64_
 int32_t b200dnn_quant_static(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t src_ld, const float *scale,
                              int64_t n_scale, const int32_t *zp, int64_t n_zp, void *dst, int32_t dst_dt, int64_t dst_ld,
                              void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(src && dst && scale && M > 0 && N > 0 && src_ld >= N && dst_ld >= N, B200DNN_FAILURE, "bad argument");
   B2_CHECK((n_scale == 1 || n_scale == N) && (!zp || n_zp == 1 || n_zp == N), B200DNN_UNIMPLEMENTED, "scale / zero-point granularity");
   B2_CHECK((src_dt == B200DNN_BF16 || src_dt == B200DNN_F32) && (dst_dt == B200DNN_S8 || dst_dt == B200DNN_U8), B200DNN_UNIMPLEMENTED, "dtype combination");
@@ -677,10 +689,7 @@ int32_t b200dnn_quant_static(const void *src, int32_t src_dt, int64_t M, int64_t
 int32_t b200dnn_dequant_static(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t src_ld, const float *scale,
                                int64_t n_scale, const int32_t *zp, int64_t n_zp, void *dst, int32_t dst_dt, int64_t dst_ld,
                                void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(src && dst && scale && M > 0 && N > 0 && src_ld >= N && dst_ld >= N, B200DNN_FAILURE, "bad argument");
   B2_CHECK((n_scale == 1 || n_scale == N) && (!zp || n_zp == 1 || n_zp == N), B200DNN_UNIMPLEMENTED, "scale / zero-point granularity");
   B2_CHECK((src_dt == B200DNN_S8 || src_dt == B200DNN_U8) && (dst_dt == B200DNN_F32 || dst_dt == B200DNN_BF16), B200DNN_UNIMPLEMENTED, "dtype combination");
@@ -698,10 +707,7 @@ int32_t b200dnn_dequant_static(const void *src, int32_t src_dt, int64_t M, int64
 }
 
 int32_t b200dnn_gated_act(void *buf, int32_t dt, int64_t M, int64_t N, int64_t ldc, int32_t act, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(buf && M > 0 && N > 0 && N % 2 == 0 && ldc >= N, B200DNN_FAILURE, "bad argument");
   B2_CHECK(act >= 1 && act <= 3, B200DNN_FAILURE, "unknown gated activation %d", act);
   B2_CHECK(dt == B200DNN_BF16 || dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "gated activation on f32 or bf16 only");
@@ -716,34 +722,32 @@ int32_t b200dnn_gated_act(void *buf, int32_t dt, int64_t M, int64_t N, int64_t l
 
 int32_t b200dnn_moe_weighted_reduce(const void *const *row_ptrs, const float *topk_weights, int32_t T, int32_t topk,
                                     int32_t D, int32_t skip_weighted, int32_t dt, void *out, int64_t ld_out, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(row_ptrs && out && T > 0 && topk > 0 && D > 0 && ld_out >= D, B200DNN_FAILURE, "bad argument");
   B2_CHECK(skip_weighted || topk_weights, B200DNN_FAILURE, "topk_weights is null");
   B2_CHECK(dt == B200DNN_BF16 || dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "weighted reduce on f32 or bf16 only");
   const size_t nslot = (size_t)T * topk;
-  // row_ptrs is a host array (the reference's contract); rows on the host are staged row by row
+  // row_ptrs is a host array (the reference's contract).  Rows in host memory are gathered into one pinned slab and
+  // sent with one copy (a copy per row costs microseconds each: 8192 of them at 4096 tokens x top-2).
   std::vector<const void *> dev_rows(nslot);
   const bool rows_on_device = is_device_ptr(row_ptrs[0]);
   if (rows_on_device) {
     for (size_t i = 0; i < nslot; ++i) { B2_CHECK(row_ptrs[i], B200DNN_FAILURE, "row_ptrs[%zu] is null", i); dev_rows[i] = row_ptrs[i]; }
   } else {
-    const size_t rb = (size_t)D * dt_size(dt);
-    uint8_t *slab = (uint8_t *)rt().ws.alloc(nslot * ((rb + 15) & ~size_t(15)));
-    B2_CHECK(slab, B200DNN_FAILURE, "workspace allocation failed");
-    const size_t pitch = (rb + 15) & ~size_t(15);
+    const size_t rb = (size_t)D * dt_size(dt), pitch = (rb + 15) & ~size_t(15);
+    uint8_t *slab = (uint8_t *)rt().ws.alloc(nslot * pitch);
+    uint8_t *pin = rt().pinned_slab(nslot * pitch);
+    B2_CHECK(slab && pin, B200DNN_FAILURE, "staging allocation failed");
     for (size_t i = 0; i < nslot; ++i) {
       B2_CHECK(row_ptrs[i], B200DNN_FAILURE, "row_ptrs[%zu] is null", i);
-      B2_CUDA(cudaMemcpyAsync(slab + i * pitch, row_ptrs[i], rb, cudaMemcpyHostToDevice, st));
+      memcpy(pin + i * pitch, row_ptrs[i], rb);
       dev_rows[i] = slab + i * pitch;
     }
+    B2_CUDA(cudaMemcpyAsync(slab, pin, nslot * pitch, cudaMemcpyHostToDevice, st));
+    B2_CUDA(cudaStreamSynchronize(st));   // the pinned slab is reused by the next call
   }
-  void *tab = rt().ws.alloc(nslot * sizeof(void *));
-  B2_CHECK(tab, B200DNN_FAILURE, "workspace allocation failed");
-  B2_CUDA(cudaMemcpyAsync(tab, dev_rows.data(), nslot * sizeof(void *), cudaMemcpyHostToDevice, st));
-  B2_CUDA(cudaStreamSynchronize(st));
+  void *tab = nullptr;
+  B2_TRY(upload_blob(dev_rows.data(), nslot * sizeof(void *), st, &tab));
   const void *w_dev = nullptr;
   if (!skip_weighted) B2_TRY(stage_in(topk_weights, nslot * 4, st, &w_dev));
   Staged o;
@@ -792,10 +796,7 @@ extern "C" {
 
 int32_t b200dnn_moe_route(const float *logits, int32_t T, int32_t E, int32_t topk, int32_t renorm, int32_t *ids,
                           float *weights, int32_t *expert_counts, int32_t *slot_to_row, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(logits && ids && T > 0 && E > 0 && topk > 0 && topk <= E && topk <= kMaxTopk, B200DNN_FAILURE, "bad argument");
   const void *l_dev;
   B2_TRY(stage_in(logits, (size_t)T * E * 4, st, &l_dev));
@@ -833,68 +834,11 @@ int32_t b200dnn_moe_route(const float *logits, int32_t T, int32_t E, int32_t top
 // -------------------------------------------------------------------------------------------- matmul
 int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   B2_CHECK(d, B200DNN_FAILURE, "null descriptor");
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
+  B2_ENTER(stream);
   Runtime &R = rt();
-  R.ws.rewind();
-  R.small.begin();
-  cudaStream_t st = as_stream(stream);
-  const auto t_call = std::chrono::steady_clock::now();
   const int M = d->M, N = d->N, K = d->K;
-  // ---- contract checks (matmul/lowoha_matmul_utils.cpp:180-420, INT8 subset)
-  B2_CHECK(d->src && d->weight && d->dst, B200DNN_FAILURE, "null src, weight or dst");
-  B2_CHECK(M > 0 && N > 0 && K > 0, B200DNN_FAILURE, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
-  B2_CHECK(d->lda >= K && d->ldc >= N, B200DNN_FAILURE, "lda/ldc smaller than the row length");
-  B2_CHECK(d->wei_format == 'r' || d->ldb >= (d->transB ? K : N), B200DNN_FAILURE, "ldb smaller than the row length");
-  B2_CHECK(d->wei_dt == B200DNN_S8, B200DNN_UNIMPLEMENTED, "only s8 weights are implemented (wei dtype %d)", d->wei_dt);
-  B2_CHECK(d->dst_dt == B200DNN_BF16 || d->dst_dt == B200DNN_F32 || d->dst_dt == B200DNN_S32, B200DNN_UNIMPLEMENTED,
-           "dst dtype %d is not implemented for the INT8 path", d->dst_dt);
-  B2_CHECK(d->n_postops >= 0 && d->n_postops <= B200DNN_MAX_POSTOPS, B200DNN_FAILURE, "too many post-ops");
+  B2_TRY(validate_matmul_desc(d));
   const bool dyn = d->dynamic_quant != 0;
-  if (dyn) {
-    B2_CHECK(d->src_dt == B200DNN_BF16 || d->src_dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "dynamic quantisation takes a bf16 or f32 source");
-    B2_CHECK(d->src_scale.count == M || (M == 1 && d->src_scale.count == 1) || d->src_scale.count == 0, B200DNN_UNIMPLEMENTED,
-             "dynamic quantisation is per-token only (src scale count %lld, M %d)", (long long)d->src_scale.count, M);
-    B2_CHECK(d->src_zp.buff == nullptr, B200DNN_UNIMPLEMENTED, "asymmetric dynamic quantisation is not implemented");
-  } else {
-    B2_CHECK(d->src_dt == B200DNN_S8 || d->src_dt == B200DNN_U8, B200DNN_UNIMPLEMENTED, "src dtype %d without dynamic_quant", d->src_dt);
-    B2_CHECK(d->src_scale.count == 0 || d->src_scale.buff, B200DNN_FAILURE, "src scale buffer is null");
-    B2_CHECK(d->src_scale.count == 0 || d->src_scale.count == 1 || d->src_scale.count == M, B200DNN_UNIMPLEMENTED,
-             "src scale must be per-tensor or per-token");
-  }
-  const bool per_token = d->src_scale.count > 1 || (dyn && M > 1);
-  if (per_token) {
-    // per-token rules: symmetric source, float destination, per-channel weight scale of N elements
-    // (matmul/lowoha_matmul_utils.cpp:252-292)
-    B2_CHECK(d->src_zp.buff == nullptr, B200DNN_FAILURE, "per-token source scale does not allow a zero-point");
-    B2_CHECK(dyn || d->src_dt == B200DNN_S8, B200DNN_FAILURE, "per-token source scale needs a symmetric s8 source");
-    B2_CHECK(d->dst_dt != B200DNN_S32, B200DNN_FAILURE, "per-token source scale needs an f32 or bf16 destination");
-    B2_CHECK(d->wei_scale.count == N, B200DNN_FAILURE, "per-token source scale needs a per-channel weight scale of N elements");
-  }
-  B2_CHECK(d->wei_scale.count == 0 || d->wei_scale.count == 1 || d->wei_scale.count == N, B200DNN_UNIMPLEMENTED,
-           "weight scale must be per-tensor or per-channel");
-  B2_CHECK(d->wei_scale.count == 0 || d->wei_scale.buff, B200DNN_FAILURE, "weight scale buffer is null");
-  B2_CHECK(d->src_zp.buff == nullptr || d->src_zp.count <= 1, B200DNN_UNIMPLEMENTED, "src zero-point must be per-tensor");
-  auto scale_dt_ok = [](int32_t dt) { return dt == B200DNN_F32 || dt == B200DNN_BF16; };
-  B2_CHECK(d->src_scale.count == 0 || !d->src_scale.buff || scale_dt_ok(d->src_scale.dt), B200DNN_UNIMPLEMENTED, "src scale dtype");
-  B2_CHECK(d->wei_scale.count == 0 || scale_dt_ok(d->wei_scale.dt), B200DNN_UNIMPLEMENTED, "weight scale dtype");
-  B2_CHECK(!d->bias || scale_dt_ok(d->bias_dt), B200DNN_UNIMPLEMENTED, "bias dtype %d", d->bias_dt);
-  if (d->dst_dt == B200DNN_S32)
-    B2_CHECK(d->src_scale.count == 0 && d->wei_scale.count == 0 && !d->bias && d->n_postops == 0, B200DNN_UNIMPLEMENTED,
-             "s32 destination returns raw compensated accumulators: no scales, bias or post-ops");
-  for (int i = 0; i < d->n_postops; ++i) {
-    const b200dnn_postop_t &p = d->postops[i];
-    switch (p.type) {
-    case PO_RELU: case PO_LEAKY_RELU: case PO_GELU_TANH: case PO_GELU_ERF: case PO_SIGMOID: case PO_SWISH: case PO_TANH: case PO_ELU: break;
-    case PO_CLIP: B2_CHECK(isfinite(p.alpha) && isfinite(p.beta), B200DNN_FAILURE, "clip bounds must be finite"); break;
-    case PO_BINARY_ADD: case PO_BINARY_MUL:
-      B2_CHECK(p.buff && (p.dt == B200DNN_F32 || p.dt == B200DNN_BF16), B200DNN_FAILURE, "binary post-op needs an f32 or bf16 operand");
-      B2_CHECK(p.ld == 0 || p.ld >= N, B200DNN_FAILURE, "binary post-op leading dimension");
-      break;
-    case PO_MISH: return fail(B200DNN_FAILURE, "mish is rejected on the INT8 path");
-    default: return fail(B200DNN_UNIMPLEMENTED, "post-op %d is not implemented", p.type);
-    }
-  }
 
   // ---- operands on the device
   PackedWeight pw;
@@ -986,33 +930,62 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
     ta.n_groups = 1; ta.m_tiles_plain = (M + kTcBM - 1) / kTcBM; ta.shared_dst = 1;
     B2_TRY(launch_tc(A, lda, a_unsigned, M, N, K, pw, ta, epi, ta.m_tiles_plain, st));
   }
-  const bool sync_path = o_dst.copy_back || o_scale.copy_back || o_dst.sync || o_scale.sync;
-  B2_TRY(finish_out({&o_dst, &o_scale}, st));
-  // A kernel that gave up on a barrier spent about a second waiting: the status word is read back only when
-  // the synchronised call took that long, so the normal path pays nothing for the check.
-  if (sync_path && std::chrono::steady_clock::now() - t_call > std::chrono::milliseconds(900)) B2_TRY(check_tc_status(st));
-  return B200DNN_SUCCESS;
+  return finish_out({&o_dst, &o_scale}, st);   // calls that synchronise read the status word there
 }
 
 int32_t b200dnn_stream_status(void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  return check_tc_status(as_stream(stream));
+  B2_ENTER(stream);
+  B2_CUDA(cudaStreamSynchronize(st));
+  return read_status();
+}
+
+int32_t b200dnn_phase_timing(void *stream, int32_t enable) {
+  B2_ENTER(stream);
+  rt().timing = enable != 0;
+  rt().n_tev = 0;
+  return B200DNN_SUCCESS;
+}
+
+int32_t b200dnn_phase_times(void *stream, float *ms, int32_t n) {
+  B2_ENTER(stream);
+  B2_CHECK(ms && n > 0, B200DNN_FAILURE, "bad argument");
+  B2_CUDA(cudaStreamSynchronize(st));
+  Runtime &R = rt();
+  for (int i = 0; i < n; ++i) ms[i] = 0.f;
+  for (size_t i = 1; i < R.n_tev; ++i) {
+    float t = 0.f;
+    B2_CUDA(cudaEventElapsedTime(&t, R.tev[i - 1], R.tev[i]));
+    if (R.tphase[i] >= 0 && R.tphase[i] < n) ms[R.tphase[i]] += t;
+  }
+  return B200DNN_SUCCESS;
 }
 
 int32_t b200dnn_clear_caches(void) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  Runtime &R = rt();
-  if (device_count() > 0) cudaDeviceSynchronize();
-  for (auto &kv : R.wcache) if (kv.second.owned) cudaFree(kv.second.owned);
-  R.wcache.clear();
-  for (auto &kv : R.host_packed) if (kv.second.owned) cudaFree(kv.second.owned);
-  R.host_packed.clear();
-  R.packed_registry.clear();
-  R.ws.release();
+  if (device_count() <= 0) return B200DNN_SUCCESS;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  for (int dev = 0; dev < 64; ++dev) {
+    DeviceShared *D;
+    { std::lock_guard<std::mutex> lk(devices_mu()); D = device_slot(dev); }
+    if (!D) continue;
+    cudaSetDevice(dev);
+    cudaDeviceSynchronize();
+    {
+      std::lock_guard<std::mutex> lk(D->cache_mu);
+      for (auto &kv : D->wcache) { if (kv.second.owned) cudaFree(kv.second.owned); if (kv.second.ready) cudaEventDestroy(kv.second.ready); }
+      D->wcache.clear();
+      for (auto &kv : D->host_packed) { if (kv.second.owned) cudaFree(kv.second.owned); if (kv.second.ready) cudaEventDestroy(kv.second.ready); }
+      D->host_packed.clear();
+      D->packed_registry.clear();
+    }
+    std::lock_guard<std::mutex> lk(D->ctx_mu);
+    for (auto &kv : D->ctxs) { std::lock_guard<std::mutex> lk2(kv.second->mu); kv.second->release_buffers(); }
+  }
+  cudaSetDevice(cur);
   return B200DNN_SUCCESS;
 }
 
 }  // extern "C"
 
 #include "moe_api.cuh"
+#include "moe_ep.cuh"

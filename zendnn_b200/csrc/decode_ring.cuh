@@ -114,7 +114,7 @@ __global__ void __launch_bounds__((kRingWarps + 1) * 32, 1) decode_ring_kernel(D
       issue(st);
     }
     if (!ok) {
-      if (lane == 0) { s_err = 1; atomicExch(g.status, 11); }
+      if (lane == 0) { s_err = 1; report_status(g.status, 11); }
       // copies in flight must land before the CTA leaves
       const int first = st > S ? st - S : 0;
       for (int q = first; q < st; ++q) mbar_wait(full_bar(q % S), (uint32_t)(q / S) & 1u);
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__((kRingWarps + 1) * 32, 1) decode_ring_kernel(D
         lo1 = *reinterpret_cast<const uint4 *>(ap + 16);
         if (hi_rows) { hi0 = *reinterpret_cast<const uint4 *>(ap + a_hi_off); hi1 = *reinterpret_cast<const uint4 *>(ap + 16 + a_hi_off); }
       }
-      if (!mbar_wait(full_bar(slot), (uint32_t)(st / S) & 1u)) { ok = false; if (lane == 0) { s_err = 1; atomicExch(g.status, 13); } break; }
+      if (!mbar_wait(full_bar(slot), (uint32_t)(st / S) & 1u)) { ok = false; if (lane == 0) { s_err = 1; report_status(g.status, 13); } break; }
       if (c < g.blocks) {
         const uint8_t *wp = ring + (size_t)slot * kStageBytes + w_lane;
         const int ngrp = n_local - set * R;

@@ -25,6 +25,7 @@ using zendnnl::common::data_type_t;
 using zendnnl::error_handling::status_t;
 
 thread_local std::string g_shim_error;
+thread_local void *g_stream = nullptr;   // the calling thread's CUDA stream (b200::set_stream)
 
 status_t shim_fail(status_t s, const char *msg) { g_shim_error = msg; return s; }
 status_t from_c(int32_t rc) {
@@ -45,6 +46,11 @@ template <class Q> b200dnn_quant_t flat_quant(const Q &q) {
   return o;
 }
 }  // namespace
+
+namespace b200 {
+void set_stream(void *cuda_stream) { g_stream = cuda_stream; }
+void *get_stream() { return g_stream; }
+}  // namespace b200
 
 // =========================================================================================== matmul
 namespace matmul {
@@ -102,7 +108,7 @@ status_t matmul_direct(const char layout, const bool transA, const bool transB, 
   status_t st = flatten(layout, transA, transB, M, N, K, alpha, src, lda, weight, ldb, bias, beta, dst, ldc, is_weights_const,
                         batch_params, params, &d);
   if (st != status_t::success) return st;
-  return from_c(b200dnn_matmul(&d, nullptr));
+  return from_c(b200dnn_matmul(&d, g_stream));
 }
 
 status_t group_matmul_moe_act_execute(const grp_matmul_gated_act_params *act_params, const std::vector<void *> &dst,
@@ -115,7 +121,7 @@ status_t group_matmul_moe_act_execute(const grp_matmul_gated_act_params *act_par
     if (M[i] <= 0) continue;
     if (!dst[i]) return shim_fail(status_t::failure, "gated activation: null dst");
     status_t st = from_c(b200dnn_gated_act(dst[i], static_cast<int32_t>(dst_dtype), M[i], N[i], ldc[i],
-                                           static_cast<int32_t>(act_params->act), nullptr));
+                                           static_cast<int32_t>(act_params->act), g_stream));
     if (st != status_t::success) return st;
   }
   return status_t::success;
@@ -128,7 +134,7 @@ status_t group_matmul_moe_postop_execute(const group_matmul_moe_postop_params *p
     return shim_fail(status_t::failure, "moe post-op: bad argument");
   if (!p->skip_weighted && !p->topk_weights) return shim_fail(status_t::failure, "moe post-op: topk_weights is null");
   return from_c(b200dnn_moe_weighted_reduce(p->row_ptrs, p->topk_weights, p->num_tokens, p->topk, D, p->skip_weighted ? 1 : 0,
-                                            static_cast<int32_t>(dst_elem), p->output, p->ldc_output, nullptr));
+                                            static_cast<int32_t>(dst_elem), p->output, p->ldc_output, g_stream));
 }
 
 void clear_fused_moe_scratch() { b200dnn_clear_caches(); }
@@ -200,7 +206,7 @@ status_t group_matmul_direct(const std::vector<char> &layout, const std::vector<
                                     moe_postop ? reinterpret_cast<const void *const *>(moe_postop->row_ptrs) : nullptr,
                                     moe_postop ? moe_postop->topk_weights : nullptr, moe_postop ? moe_postop->num_tokens : 0,
                                     moe_postop ? moe_postop->topk : 0, moe_postop ? moe_postop->output : nullptr,
-                                    moe_postop ? moe_postop->ldc_output : 0, nullptr));
+                                    moe_postop ? moe_postop->ldc_output : 0, g_stream));
   }
 
   // ---- plain grouped mode: every expert's GEMM, experts with M == 0 skipped (group_matmul_parallel_common.hpp:1240-1248)
@@ -243,7 +249,7 @@ status_t weight_prepack_into(const void *weights, const reorder_params_t &params
   if (pp.sym_group_size != 0 && pp.sym_group_size != pp.K)
     return shim_fail(status_t::unimplemented, "prepack: per-group symmetric quantisation is not implemented");
   return from_c(b200dnn_prepack(weights, pp.K, pp.N, pp.ldb > 0 ? pp.ldb : (pp.transposed ? pp.K : pp.N), pp.transposed ? 1 : 0, 0,
-                                dst, nullptr));
+                                dst, g_stream));
 }
 
 status_t reorder_direct(const void *src, void *dst, reorder_params_t &params) {
@@ -271,10 +277,10 @@ status_t reorder_direct(const void *src, void *dst, reorder_params_t &params) {
     if (zp.buff) return shim_fail(status_t::unimplemented, "reorder: asymmetric dynamic quantisation is not implemented");
     if (!src_float || (dst && params.dst_dtype != data_type_t::s8)) return shim_fail(status_t::unimplemented, "reorder: dynamic quantisation is f32|bf16 -> s8");
     if (per_token || (ns == M && M == 1 && N > 1 && sc.dims.size() == 2 && sc.dims[1] == 1))
-      return from_c(b200dnn_quant_per_token(src, sdt, M, N, src_ld, dst, N, sc.buff, static_cast<int32_t>(sc.dt), nullptr));
+      return from_c(b200dnn_quant_per_token(src, sdt, M, N, src_ld, dst, N, sc.buff, static_cast<int32_t>(sc.dt), g_stream));
     if (sc.dt != data_type_t::f32) return shim_fail(status_t::unimplemented, "reorder: per-channel / per-tensor scales are f32");
-    if (per_channel) return from_c(b200dnn_quant_dynamic(src, sdt, M, N, src_ld, 1, dst, N, static_cast<float *>(sc.buff), nullptr));
-    if (ns == 1) return from_c(b200dnn_quant_dynamic(src, sdt, M, N, src_ld, 0, dst, N, static_cast<float *>(sc.buff), nullptr));
+    if (per_channel) return from_c(b200dnn_quant_dynamic(src, sdt, M, N, src_ld, 1, dst, N, static_cast<float *>(sc.buff), g_stream));
+    if (ns == 1) return from_c(b200dnn_quant_dynamic(src, sdt, M, N, src_ld, 0, dst, N, static_cast<float *>(sc.buff), g_stream));
     return shim_fail(status_t::unimplemented, "reorder: per-group dynamic quantisation is not implemented");
   }
   if (!dst) return shim_fail(status_t::failure, "reorder: null dst");
@@ -290,10 +296,10 @@ status_t reorder_direct(const void *src, void *dst, reorder_params_t &params) {
   const bool src_int = params.src_dtype == data_type_t::s8 || params.src_dtype == data_type_t::u8;
   if (src_float && dst_int)
     return from_c(b200dnn_quant_static(src, sdt, M, N, src_ld, static_cast<const float *>(sc.buff), ns,
-                                       static_cast<const int32_t *>(zp.buff), nz, dst, ddt, N, nullptr));
+                                       static_cast<const int32_t *>(zp.buff), nz, dst, ddt, N, g_stream));
   if (src_int && (params.dst_dtype == data_type_t::f32 || params.dst_dtype == data_type_t::bf16))
     return from_c(b200dnn_dequant_static(src, sdt, M, N, src_ld, static_cast<const float *>(sc.buff), ns,
-                                         static_cast<const int32_t *>(zp.buff), nz, dst, ddt, N, nullptr));
+                                         static_cast<const int32_t *>(zp.buff), nz, dst, ddt, N, g_stream));
   return shim_fail(status_t::unimplemented, "reorder: dtype combination is not implemented");
 }
 
@@ -314,7 +320,7 @@ status_t group_dynamic_quant(const std::vector<const void *> &src, const std::ve
   }
   return from_c(b200dnn_group_quant_per_token(static_cast<int32_t>(G), src.data(), static_cast<int32_t>(params.src_dtype), m.data(),
                                               k.data(), sld.data(), dst.data(), dld.data(), scale.data(),
-                                              static_cast<int32_t>(params.scale_dtype), nullptr));
+                                              static_cast<int32_t>(params.scale_dtype), g_stream));
 }
 
 }  // namespace reorder

@@ -8,6 +8,13 @@ namespace b200 {
 
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s
 
+// The status word lives in pinned host memory mapped into the device (the host reads it after draining the stream):
+// a plain system-scope store, no atomic.  Any one of several codes written at once may win.
+__device__ __forceinline__ void report_status(int32_t *status, int32_t code) {
+  *reinterpret_cast<volatile int32_t *>(status) = code;
+  __threadfence_system();
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));

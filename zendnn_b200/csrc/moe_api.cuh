@@ -22,16 +22,6 @@ __global__ void tile_prefix_kernel(const int32_t *row_off, int n_groups, int32_t
   }
 }
 
-// Uploads a host blob into workspace memory and waits for the copy (the blob is a local).
-int32_t upload_blob(const void *host, size_t bytes, cudaStream_t st, void **dev) {
-  void *d = rt().ws.alloc(bytes);
-  B2_CHECK(d, B200DNN_FAILURE, "workspace allocation failed");
-  B2_CUDA(cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, st));
-  B2_CUDA(cudaStreamSynchronize(st));
-  *dev = d;
-  return B200DNN_SUCCESS;
-}
-
 int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const std::vector<PackedWeight> &pws,
                      const int32_t *row_off_dev, const int32_t *tile_prefix_dev, const TcGroupDesc *groups_dev,
                      int m_tiles_bound, EpiParams epi, bool shared_dst, cudaStream_t st) {
@@ -50,7 +40,7 @@ int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const s
     B2_TRY(make_map_wt(&maps[g], pws[g].wt, (uint64_t)p0.Kp, (uint64_t)p0.Np, (uint32_t)BN));
   }
   void *maps_dev = nullptr;
-  B2_TRY(upload_blob(maps.data(), sizeof(CUtensorMap) * G, st, &maps_dev));
+  B2_TRY(cached_blob(maps.data(), sizeof(CUtensorMap) * G, st, &maps_dev));
   ta.maps_b = (const CUtensorMap *)maps_dev;
   // launch_tc picks the same BN from the same inputs
   return launch_tc(A, lda, false, R, N, K, p0, ta, epi, m_tiles_bound, st);
@@ -64,7 +54,7 @@ struct ExpertWeightsIn {
 int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, int H, int transB, int act, int weights_const,
                  RowQuantArgs qa, int32_t src_dt, int R, const int32_t *row_off_dev, const int32_t *tile_prefix_dev,
                  int m_tiles_bound, const std::vector<void *> *dst_down_dev, const std::vector<int64_t> *ldc_down,
-                 void **O_out, int64_t *ldO_out, cudaStream_t st) {
+                 void **O_out, int64_t *ldO_out, cudaStream_t st, void *O_given = nullptr) {
   Runtime &Rt = rt();
   B2_CHECK(act >= 1 && act <= 3, B200DNN_UNIMPLEMENTED, "fused MoE needs a gated activation (got %d)", act);
   B2_CHECK(I % kGateGranule == 0, B200DNN_UNIMPLEMENTED, "expert FFN width must be a multiple of %d", kGateGranule);
@@ -82,8 +72,9 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
     g2[g] = TcGroupDesc{s2, p2[g].colsum, nullptr, dst_down_dev ? (*dst_down_dev)[g] : nullptr, ldc_down ? (*ldc_down)[g] : 0};
   }
   void *g13_dev, *g2_dev;
-  B2_TRY(upload_blob(g13.data(), sizeof(TcGroupDesc) * G, st, &g13_dev));
-  B2_TRY(upload_blob(g2.data(), sizeof(TcGroupDesc) * G, st, &g2_dev));
+  B2_TRY(cached_blob(g13.data(), sizeof(TcGroupDesc) * G, st, &g13_dev));
+  if (dst_down_dev) B2_TRY(upload_blob(g2.data(), sizeof(TcGroupDesc) * G, st, &g2_dev));   // carries the caller's output pointers: not cached
+  else B2_TRY(cached_blob(g2.data(), sizeof(TcGroupDesc) * G, st, &g2_dev));
 
   const int64_t Kq = round_up(K, 16), Iq = round_up(I, 16);
   int8_t *A1 = (int8_t *)Rt.ws.alloc((size_t)R * Kq);
@@ -106,6 +97,7 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
     qa.dst = A1; qa.dst_ld = Kq; qa.scale = s1; qa.scale_dt = B200DNN_F32; qa.K = K;
     B2_TRY(launch_quant_rows(qa, src_dt, qa.scatter ? qa.scatter_rows : R, st));
   }
+  rt().mark(2);
 
   // 2. first GEMM with the gated epilogue -> Z (bf16, [R, I]) and per-row max |Z|
   EpiParams e1{};
@@ -114,22 +106,25 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
   e1.dst = Z; e1.ldc = I; e1.dst_dt = B200DNN_BF16; e1.gated_act = act; e1.gated_I = I; e1.row_absmax = zmax;
   B2_TRY(grouped_gemm(A1_in, lda1, R, 2 * I, K, p13, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g13_dev,
                       m_tiles_bound, e1, true, st));
+  rt().mark(4);
 
   // 3. re-quantise the activated rows (from their bf16 values, as the reference does)
   RowQuantArgs q2{};
   q2.src = Z; q2.src_ld = I; q2.dst = A2; q2.dst_ld = Iq; q2.scale = s2v; q2.scale_dt = B200DNN_F32; q2.K = I;
   q2.absmax_bits = zmax; q2.gather_div = 1;
   B2_TRY(launch_quant_rows(q2, B200DNN_BF16, R, st));
+  rt().mark(5);
 
   // 4. second GEMM -> O
-  uint16_t *O = nullptr;
-  if (!dst_down_dev) { O = (uint16_t *)Rt.ws.alloc((size_t)R * H * 2); B2_CHECK(O, B200DNN_FAILURE, "workspace allocation failed"); }
+  uint16_t *O = (uint16_t *)O_given;     // dense [R, H] rows of the caller, when given
+  if (!dst_down_dev && !O) { O = (uint16_t *)Rt.ws.alloc((size_t)R * H * 2); B2_CHECK(O, B200DNN_FAILURE, "workspace allocation failed"); }
   EpiParams e2{};
   e2.src_scale = s2v; e2.src_scale_dt = B200DNN_F32; e2.src_scale_n = R > 1 ? R : 2;
   e2.wei_scale_dt = B200DNN_F32; e2.wei_scale_n = H;
   e2.dst = O; e2.ldc = H; e2.dst_dt = B200DNN_BF16;
   B2_TRY(grouped_gemm((const uint8_t *)A2, Iq, R, H, I, p2, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g2_dev,
                       m_tiles_bound, e2, dst_down_dev == nullptr, st));
+  rt().mark(6);
   if (O_out) { *O_out = O; *ldO_out = H; }
   return B200DNN_SUCCESS;
 }
@@ -140,11 +135,8 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
                                      int32_t transB, int32_t act, int32_t weights_const, const void *const *row_ptrs,
                                      const float *topk_weights, int32_t T, int32_t topk, void *out, int64_t ld_out,
                                      void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
+  B2_ENTER(stream);
   Runtime &Rt = rt();
-  Rt.ws.rewind();
-  cudaStream_t st = as_stream(stream);
   B2_CHECK(G > 0 && ex && K > 0 && I > 0 && H > 0, B200DNN_FAILURE, "bad argument");
   std::vector<int32_t> row_off(G + 1, 0), tile_prefix(G + 1, 0);
   for (int g = 0; g < G; ++g) {
@@ -248,11 +240,8 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
 extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *logits, int32_t T, int32_t E, int32_t S,
                                      int32_t topk, const b200dnn_moe_expert_t *ex, int32_t K, int32_t I, int32_t H,
                                      int32_t transB, int32_t act, void *out, int64_t ld_out, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
+  B2_ENTER(stream);
   Runtime &Rt = rt();
-  Rt.ws.rewind();
-  cudaStream_t st = as_stream(stream);
   B2_CHECK(x && logits && ex && out && T > 0 && E > 0 && S >= 0 && topk > 0 && topk <= E && topk <= kMaxTopk, B200DNN_FAILURE, "bad argument");
   B2_CHECK(ldx >= K && ld_out >= H, B200DNN_FAILURE, "leading dimension too small");
   const int G = E + S, ns = topk + S, R = T * ns;
@@ -269,6 +258,7 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   float *slot_w = (float *)Rt.ws.alloc((size_t)R * 4);
   int32_t *row_token = (int32_t *)Rt.ws.alloc((size_t)R * 4);
   B2_CHECK(ids && w && rank && cnt && row_off && tile_prefix && slot_rows && slot_w && row_token, B200DNN_FAILURE, "workspace allocation failed");
+  rt().mark(-1);
   B2_TRY(launch_route_topk((const float *)l_dev, T, E, topk, 1, ids, w, st));
   B2_TRY(launch_expert_rank(ids, T * topk, E, rank, cnt, st));
   expert_offsets_kernel<<<1, 32, 0, st>>>(cnt, E, S, T, row_off);
@@ -278,6 +268,7 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   build_maps_kernel<<<(unsigned)((R + 255) / 256), 256, 0, st>>>(ids, rank, w, row_off, T, topk, E, S, slot_rows, slot_w, row_token);
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
+  rt().mark(0);
 
   std::vector<ExpertWeightsIn> ew(G);
   for (int g = 0; g < G; ++g) ew[g] = ExpertWeightsIn{ex[g].w13, ex[g].ldb13, ex[g].w13_scale, ex[g].w2, ex[g].ldb2, ex[g].w2_scale};
@@ -298,9 +289,8 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   moe_reduce_kernel<<<(unsigned)T, 256, (sizeof(void *) + 4) * ns, st>>>(ra);
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
-  B2_TRY(finish_out({&o_out}, st));
-  if (o_out.copy_back || o_out.sync) B2_TRY(check_tc_status(st));
-  return B200DNN_SUCCESS;
+  rt().mark(8);
+  return finish_out({&o_out}, st);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -316,11 +306,8 @@ __global__ void slot_rows_kernel(const int32_t *keys, const int32_t *rank, const
 
 extern "C" int32_t b200dnn_moe_sort_slots(const int32_t *keys, int32_t nslots, int32_t nkeys, int32_t *counts,
                                           int32_t *slot_to_row, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
+  B2_ENTER(stream);
   Runtime &Rt = rt();
-  Rt.ws.rewind();
-  cudaStream_t st = as_stream(stream);
   B2_CHECK(keys && counts && slot_to_row && nslots > 0 && nkeys > 0, B200DNN_FAILURE, "bad argument");
   const void *k_dev;
   B2_TRY(stage_in(keys, (size_t)nslots * 4, st, &k_dev));
@@ -342,10 +329,7 @@ extern "C" int32_t b200dnn_moe_sort_slots(const int32_t *keys, int32_t nslots, i
 extern "C" int32_t b200dnn_quant_per_token_gather(const void *src, int32_t src_dt, int64_t K, int64_t src_ld,
                                                   const int32_t *row_src, int32_t row_div, int64_t R, void *dst,
                                                   int64_t dst_ld, float *scale, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(src && row_src && dst && scale && K > 0 && R > 0 && src_ld >= K && dst_ld >= K && row_div > 0, B200DNN_FAILURE, "bad argument");
   B2_CHECK(is_device_ptr(src) && is_device_ptr(row_src) && is_device_ptr(dst) && is_device_ptr(scale), B200DNN_UNIMPLEMENTED,
            "gathered quantisation takes device pointers only");
@@ -358,10 +342,7 @@ extern "C" int32_t b200dnn_quant_per_token_gather(const void *src, int32_t src_d
 extern "C" int32_t b200dnn_quant_per_token_scatter(const void *src, int32_t src_dt, int64_t K, int64_t src_ld,
                                                    const int32_t *dst_rows, int32_t n_dst, int64_t T, void *dst,
                                                    int64_t dst_ld, float *scale, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(src && dst_rows && dst && scale && K > 0 && T > 0 && src_ld >= K && dst_ld >= K && n_dst > 0 && n_dst <= 32,
            B200DNN_FAILURE, "bad argument");
   B2_CHECK(is_device_ptr(src) && is_device_ptr(dst_rows) && is_device_ptr(dst) && is_device_ptr(scale), B200DNN_UNIMPLEMENTED,
@@ -377,11 +358,8 @@ extern "C" int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, cons
                                           const int32_t *group_rows, const int32_t *group_expert,
                                           const b200dnn_moe_expert_t *experts, int32_t K, int32_t I, int32_t H,
                                           int32_t transB, int32_t act, void *out, int64_t ld_out, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
+  B2_ENTER(stream);
   Runtime &Rt = rt();
-  Rt.ws.rewind();
-  cudaStream_t st = as_stream(stream);
   B2_CHECK(rows_s8 && row_scale && group_rows && group_expert && experts && out && n_groups > 0, B200DNN_FAILURE, "bad argument");
   B2_CHECK(is_device_ptr(rows_s8) && is_device_ptr(row_scale) && is_device_ptr(out), B200DNN_UNIMPLEMENTED,
            "the expert-parallel building block takes device buffers only");
@@ -406,20 +384,15 @@ extern "C" int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, cons
   RowQuantArgs qa{};
   qa.src = rows_s8; qa.src_ld = lda; qa.scale = const_cast<float *>(row_scale);
   void *O = nullptr; int64_t ldO = 0;
-  // O is produced in workspace and copied out: moe_core owns the layout of its result
-  B2_TRY(moe_core(n_groups, ew, K, I, H, transB, act, 1, qa, B200DNN_S8, R, row_off_dev, tile_prefix_dev, tile_prefix[n_groups],
-                  nullptr, nullptr, &O, &ldO, st));
-  B2_CUDA(cudaMemcpyAsync(out, O, (size_t)R * H * 2, cudaMemcpyDeviceToDevice, st));
-  return B200DNN_SUCCESS;
+  // the second GEMM writes the caller's dense rows directly
+  return moe_core(n_groups, ew, K, I, H, transB, act, 1, qa, B200DNN_S8, R, row_off_dev, tile_prefix_dev, tile_prefix[n_groups],
+                  nullptr, nullptr, &O, &ldO, st, out);
 }
 
 extern "C" int32_t b200dnn_moe_weighted_reduce_rows(const void *rows, int64_t ld_rows, const int32_t *slot_rows,
                                                     const float *slot_weights, int32_t num_tokens, int32_t nslots, int32_t D,
                                                     int32_t dt, void *out, int64_t ld_out, void *stream) {
-  std::lock_guard<std::mutex> lk(rt().mu);
-  B2_TRY(rt().init());
-  rt().ws.rewind();
-  cudaStream_t st = as_stream(stream);
+  B2_ENTER(stream);
   B2_CHECK(rows && slot_rows && slot_weights && out && num_tokens > 0 && nslots > 0 && D > 0 && ld_rows >= D && ld_out >= D,
            B200DNN_FAILURE, "bad argument");
   B2_CHECK(dt == B200DNN_BF16 || dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "weighted reduce on f32 or bf16 only");

@@ -42,6 +42,9 @@ __global__ void __launch_bounds__(256) gated_act_kernel(T *buf, int64_t N, int64
 struct ReduceArgs {
   const void *const *row_ptrs;
   const void *base; int64_t ld; const int32_t *slot_rows;
+  // expert-parallel combine: slot (t,k)'s row lives in peer_base[slot_peer[slot]] (another GPU's output buffer mapped into
+  // this process; the loads cross NVLink) instead of `base`
+  const int32_t *slot_peer; const void *peer_base[8]; int32_t row_cap;   // rows at or beyond row_cap do not exist
   const float *w; int skip_weighted;
   int nslots, D, dt;
   void *out; int64_t ld_out;
@@ -55,7 +58,12 @@ __global__ void __launch_bounds__(256) moe_reduce_kernel(ReduceArgs a) {
     const int64_t slot = (int64_t)t * a.nslots + k;
     const void *p;
     if (a.row_ptrs) p = a.row_ptrs[slot];
-    else p = reinterpret_cast<const uint8_t *>(a.base) + (int64_t)a.slot_rows[slot] * a.ld * (a.dt == DT_BF16 ? 2 : 4);
+    else {
+      const void *b = a.slot_peer ? a.peer_base[a.slot_peer[slot]] : a.base;
+      int32_t row = a.slot_rows[slot];
+      if (a.row_cap && (row < 0 || row >= a.row_cap)) row = 0;   // dropped by an overflowing receive buffer (reported separately)
+      p = reinterpret_cast<const uint8_t *>(b) + (int64_t)row * a.ld * (a.dt == DT_BF16 ? 2 : 4);
+    }
     rows[k] = p;
     ws[k] = a.skip_weighted ? 1.f : a.w[slot];
   }

@@ -50,6 +50,12 @@ struct RowQuantArgs {
   // scatter form: source row r is quantised once and written to the rows scatter[r*scatter_n + j] of dst / scale
   // (entries < 0 skipped): a token routed to several experts is quantised once, not once per expert
   const int32_t *scatter; int32_t scatter_n; int32_t scatter_rows;
+  // scatter across GPUs (expert-parallel dispatch): destination j of source row r lives on peer scatter_peer[r*scatter_n+j],
+  // whose row buffers are peer_dst / peer_scale (addresses of peer memory mapped into this process; plain stores cross
+  // NVLink).  Rows at or beyond scatter_cap are not written (the receiver's buffer ends there); *overflow is set instead.
+  const int32_t *scatter_peer; int8_t *peer_dst[8]; float *peer_scale[8]; int32_t scatter_cap; int32_t *overflow;
+  // number of rows when only the device knows it (rows received from other GPUs): the grid then strides over the rows
+  const int32_t *n_rows_dev;
   int32_t K;
   // grouped form (used when n_groups > 0): row r belongs to the group with row_off[g] <= r < row_off[g+1]
   int32_t n_groups;
@@ -91,7 +97,8 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (sizeof(T) == 2 ? 5 : 
   // a GEMM launched as a programmatic dependent may start its set-up while this grid drains (it waits for the whole
   // grid before it reads anything)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int r = blockIdx.x;
+  const int row_limit = a.n_rows_dev ? *a.n_rows_dev : (int)gridDim.x;
+  for (int r = blockIdx.x; r < row_limit; r += gridDim.x) {
   const T *src; int8_t *dst; void *scale_out; int64_t scale_idx;
   if (a.n_groups > 0) {
     int g = 0;
@@ -102,13 +109,14 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (sizeof(T) == 2 ? 5 : 
     scale_out = a.g_scale[g]; scale_idx = lr;
   } else {
     int64_t sr = r;
-    if (a.gather) { int32_t s = a.gather[r]; if (s < 0) return; sr = s / a.gather_div; }
+    if (a.gather) { int32_t s = a.gather[r]; if (s < 0) continue; sr = s / a.gather_div; }
     src = reinterpret_cast<const T *>(a.src) + sr * a.src_ld;
     dst = a.dst ? a.dst + (int64_t)r * a.dst_ld : nullptr;
     scale_out = a.scale; scale_idx = r;
   }
   const int32_t *sc = (a.scatter && a.n_groups == 0) ? a.scatter + (int64_t)r * a.scatter_n : nullptr;
-  if (sc) dst = a.dst;     // row offsets are applied per destination
+  const int32_t *sp = (sc && a.scatter_peer) ? a.scatter_peer + (int64_t)r * a.scatter_n : nullptr;
+  if (sc) dst = sp ? a.peer_dst[0] : a.dst;     // row offsets (and the peer's base) are applied per destination
   const int K = a.K;
   const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (K % E == 0) &&
                    (!dst || (reinterpret_cast<uintptr_t>(dst) % E) == 0);
@@ -143,18 +151,19 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (sizeof(T) == 2 ? 5 : 
   float scale;
   if (a.absmax_bits) scale = scale_from_absmax(__uint_as_float(a.absmax_bits[r]));
   else scale = scale_from_absmax(block_max(amax, sh));
-  if (threadIdx.x == 0 && scale_out) {
+  if (threadIdx.x == 0 && (scale_out || sp)) {
     if (sc) {
       for (int j = 0; j < a.scatter_n; ++j) {
         const int d = sc[j];
         if (d < 0) continue;
-        if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(scale_out)[d] = f32_to_bf16_bits(scale);
+        if (sp) { if (d < a.scatter_cap) a.peer_scale[sp[j]][d] = scale; else if (a.overflow) *a.overflow = 1; }
+        else if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(scale_out)[d] = f32_to_bf16_bits(scale);
         else reinterpret_cast<float *>(scale_out)[d] = scale;
       }
     } else if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(scale_out)[scale_idx] = f32_to_bf16_bits(scale);
     else reinterpret_cast<float *>(scale_out)[scale_idx] = scale;
   }
-  if (!dst) return;
+  if (!dst) continue;
   const float rinv = __frcp_rn(scale);
   if (vec) {
     auto put = [&](int8_t *row, const int8_t (&o)[E], int v) {
@@ -166,7 +175,9 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (sizeof(T) == 2 ? 5 : 
       __align__(8) int8_t o[E];
 #pragma unroll
       for (int i = 0; i < E; ++i) o[i] = quant_sym_r(elem_to_f32<T>(e[i]), scale, rinv);
-      if (sc) {
+      if (sp) {
+        for (int j = 0; j < a.scatter_n; ++j) { const int d = sc[j]; if (d >= 0 && d < a.scatter_cap) put(a.peer_dst[sp[j]] + (int64_t)d * a.dst_ld, o, v); }
+      } else if (sc) {
         for (int j = 0; j < a.scatter_n; ++j) { const int d = sc[j]; if (d >= 0) put(dst + (int64_t)d * a.dst_ld, o, v); }
       } else put(dst, o, v);
     };
@@ -180,11 +191,14 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (sizeof(T) == 2 ? 5 : 
   } else {
     for (int k = threadIdx.x; k < K; k += kQuantThreads) {
       const int8_t qv = quant_sym_r(elem_to_f32<T>(src[k]), scale, rinv);
-      if (sc) {
+      if (sp) {
+        for (int j = 0; j < a.scatter_n; ++j) { const int d = sc[j]; if (d >= 0 && d < a.scatter_cap) a.peer_dst[sp[j]][(int64_t)d * a.dst_ld + k] = qv; }
+      } else if (sc) {
         for (int j = 0; j < a.scatter_n; ++j) { const int d = sc[j]; if (d >= 0) dst[(int64_t)d * a.dst_ld + k] = qv; }
       } else dst[k] = qv;
     }
   }
+  }   // rows of this CTA
 }
 
 // One warp per row, for short rows (K <= 32 * NV * elements-per-16-bytes): the row lives in the
@@ -194,14 +208,15 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs a, int rows) {
   constexpr int E = VecTraits<T>::kPer16B;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (r >= rows) return;
   const int lane = threadIdx.x & 31;
+  const int row_limit = a.n_rows_dev ? min(rows, *a.n_rows_dev) : rows;
+  for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < row_limit; r += gridDim.x * 8) {
   int64_t sr = r;
-  if (a.gather) { int32_t s = a.gather[r]; if (s < 0) return; sr = s / a.gather_div; }
+  if (a.gather) { int32_t s = a.gather[r]; if (s < 0) continue; sr = s / a.gather_div; }
   const T *src = reinterpret_cast<const T *>(a.src) + sr * a.src_ld;
   const int32_t *sc = a.scatter ? a.scatter + (int64_t)r * a.scatter_n : nullptr;
-  int8_t *dst = a.dst ? (sc ? a.dst : a.dst + (int64_t)r * a.dst_ld) : nullptr;
+  const int32_t *sp = (sc && a.scatter_peer) ? a.scatter_peer + (int64_t)r * a.scatter_n : nullptr;
+  int8_t *dst = sp ? a.peer_dst[0] : (a.dst ? (sc ? a.dst : a.dst + (int64_t)r * a.dst_ld) : nullptr);
   const int nvec = a.K / E;
   uint4 cache[NV];
 #pragma unroll
@@ -223,8 +238,13 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     scale = scale_from_absmax(amax);
   }
-  if (a.scale) {
-    if (sc) {
+  if (a.scale || sp) {
+    if (sp) {
+      if (lane < a.scatter_n && sc[lane] >= 0) {
+        if (sc[lane] < a.scatter_cap) a.peer_scale[sp[lane]][sc[lane]] = scale;
+        else if (a.overflow) *a.overflow = 1;
+      }
+    } else if (sc) {
       if (lane < a.scatter_n && sc[lane] >= 0) {
         if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(a.scale)[sc[lane]] = f32_to_bf16_bits(scale);
         else reinterpret_cast<float *>(a.scale)[sc[lane]] = scale;
@@ -234,7 +254,7 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
       else reinterpret_cast<float *>(a.scale)[r] = scale;
     }
   }
-  if (!dst) return;
+  if (!dst) continue;
   const float rinv = __frcp_rn(scale);
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
@@ -247,8 +267,8 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
       if (sc) {
         for (int jj = 0; jj < a.scatter_n; ++jj) {
           const int d = sc[jj];
-          if (d < 0) continue;
-          int8_t *row = dst + (int64_t)d * a.dst_ld;
+          if (d < 0 || (sp && d >= a.scatter_cap)) continue;
+          int8_t *row = (sp ? a.peer_dst[sp[jj]] : dst) + (int64_t)d * a.dst_ld;
           if (E == 8) reinterpret_cast<uint2 *>(row)[v] = *reinterpret_cast<uint2 *>(o);
           else reinterpret_cast<uint32_t *>(row)[v] = *reinterpret_cast<uint32_t *>(o);
         }
@@ -256,6 +276,7 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
       else reinterpret_cast<uint32_t *>(dst)[v] = *reinterpret_cast<uint32_t *>(o);
     }
   }
+  }   // rows of this warp
 }
 
 // ---- per-channel / per-tensor dynamic scales over a [M,N] matrix -----------------------------

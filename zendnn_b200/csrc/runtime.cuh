@@ -78,12 +78,16 @@ struct PackedWeight {
   int64_t K = 0, N = 0, Kp = 0, Np = 0;
   int gated = 0; int64_t I = 0;
   void *owned = nullptr;   // cache-owned device buffer
+  // cache-owned buffers are packed on the stream of the call that first saw the weight; calls on other streams wait
+  // for this event until it has been seen complete once
+  cudaEvent_t ready = nullptr; cudaStream_t ready_stream = nullptr; bool complete = true;
 };
 
-// Small host inputs of one call (activations of a decode step, scales, zero point, bias) are gathered into one pinned
-// block and sent with a single copy: every separate copy costs a few microseconds of enqueue time.
+// Small host inputs of one call (activations of a decode step, scales, zero point, bias, descriptor tables) are
+// gathered into one pinned block and sent with as few copies as possible: every separate copy costs a few
+// microseconds of enqueue time, and a pinned source lets the call return without waiting for the copy.
 struct SmallBatch {
-  static constexpr size_t kCap = 64 << 10, kMaxItem = 16 << 10;
+  static constexpr size_t kCap = 1 << 20, kMaxItem = 256 << 10, kBatchItem = 16 << 10;
   uint8_t *pinned = nullptr, *dev = nullptr;
   size_t used = 0, sent = 0;
   cudaEvent_t ev = nullptr; bool in_flight = false;   // the last copy may still be reading `pinned`
@@ -92,9 +96,9 @@ struct SmallBatch {
     used = sent = 0;
   }
   // returns the device address the bytes will have after flush(), or nullptr when they do not fit
-  void *add(const void *p, size_t bytes) {
+  void *add(const void *p, size_t bytes, size_t max_item = kBatchItem) {
     const size_t room = (bytes + 255) & ~size_t(255);
-    if (!pinned || bytes > kMaxItem || used + room > kCap) return nullptr;
+    if (!pinned || bytes > max_item || used + room > kCap) return nullptr;
     memcpy(pinned + used, p, bytes);
     void *d = dev + used; used += room;
     return d;
@@ -107,46 +111,212 @@ struct SmallBatch {
     if (!will_sync) { B2_CUDA(cudaEventRecord(ev, st)); in_flight = true; }
     return B200DNN_SUCCESS;
   }
+  void release() {
+    if (ev) { cudaEventSynchronize(ev); cudaEventDestroy(ev); ev = nullptr; }
+    if (pinned) { cudaFreeHost(pinned); pinned = nullptr; }
+    if (dev) { cudaFree(dev); dev = nullptr; }
+    in_flight = false; used = sent = 0;
+  }
 };
 
-struct Runtime {
-  std::mutex mu;
-  Workspace ws;
-  SmallBatch small;
-  uint32_t *counters = nullptr; size_t n_counters = 0;   // split-K tile counters, kept zero between launches
-  int32_t *status = nullptr;                              // device status word of the tcgen05 kernel
-  int32_t *status_host = nullptr;                         // pinned mirror
+struct Runtime;
+
+// State shared by every stream of one device: the weight caches (mutex-protected, as the reference's are:
+// matmul/backends/aocl/aocl_kernel.cpp:349,394) and per-device facts.
+struct DeviceShared {
+  int dev = -1, sm_count = 0;
+  PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  std::mutex cache_mu;
   std::map<std::tuple<const void *, int64_t, int64_t, int64_t, int, int>, PackedWeight> wcache;
   std::map<const void *, PackedWeight> packed_registry;   // buffers written by b200dnn_prepack (device address)
   std::map<const void *, PackedWeight> host_packed;       // host-resident prepacked buffers uploaded once
+  std::mutex ctx_mu;
+  std::map<cudaStream_t, Runtime *> ctxs;
+  std::mutex attr_mu;
+  std::map<const void *, int> smem_limit;                 // kernels whose dynamic shared-memory limit was raised
+  int split_room[5] = {0, 0, 0, 0, 0};
+};
+
+// Descriptor tables that depend only on the caller's weight pointers (per-expert epilogue pointers, tensor maps) are
+// kept on the device and found again by their bytes, so that a steady-state MoE call uploads nothing.
+struct BlobCache {
+  struct Entry { std::vector<uint8_t> bytes; void *dev; };
+  std::vector<Entry> entries;
+  void *find(const void *host, size_t n) const {
+    for (const Entry &e : entries)
+      if (e.bytes.size() == n && memcmp(e.bytes.data(), host, n) == 0) return e.dev;
+    return nullptr;
+  }
+  void release() { for (Entry &e : entries) cudaFree(e.dev); entries.clear(); }
+};
+
+// Everything a call touches besides the weight caches: one per (device, stream).  Calls on different streams (from
+// different host threads) share nothing here; calls on one stream are serialised by `mu` and by the stream itself.
+struct Runtime {
+  std::mutex mu;
+  DeviceShared *shared = nullptr;
+  cudaStream_t stream = nullptr;
+  Workspace ws;
+  SmallBatch small;
+  BlobCache blobs;
+  uint8_t *slab = nullptr; size_t slab_cap = 0;           // pinned staging for large gathered host inputs
+  uint32_t *counters = nullptr; size_t n_counters = 0;   // split-K tile counters, kept zero between launches
+  int32_t *status = nullptr;                              // status word the kernels write: device view of mapped pinned memory
+  volatile int32_t *status_host = nullptr;                // host view of the same word
   PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
   int sm_count = 0;
+  // optional per-phase device times of the MoE entry points (b200dnn_phase_timing): events on this stream
+  bool timing = false;
+  std::vector<cudaEvent_t> tev; std::vector<int> tphase; size_t n_tev = 0;
+  // mark(p): phase p ends here; mark(-1): a timed call starts
+  void mark(int phase) {
+    if (!timing) return;
+    if (phase < 0) n_tev = 0;
+    if (n_tev == tev.size()) {
+      cudaEvent_t e = nullptr;
+      if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return; }
+      tev.push_back(e); tphase.push_back(0);
+    }
+    tphase[n_tev] = phase;
+    cudaEventRecord(tev[n_tev], stream);
+    ++n_tev;
+  }
 
-  int32_t init() {
-    if (counters) return B200DNN_SUCCESS;
-    B2_CHECK(device_count() > 0, B200DNN_FAILURE, "no CUDA device: libb200dnn has no CPU fallback");
-    cudaDeviceProp prop; int dev = 0;
-    B2_CUDA(cudaGetDevice(&dev));
-    B2_CUDA(cudaGetDeviceProperties(&prop, dev));
-    B2_CHECK(prop.major == 10, B200DNN_FAILURE, "device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
-    sm_count = prop.multiProcessorCount;
+  int32_t init(DeviceShared *sh, cudaStream_t st) {
+    shared = sh; stream = st; encode = sh->encode; sm_count = sh->sm_count;
     n_counters = 1 << 16;
     B2_CUDA(cudaMalloc(&counters, n_counters * sizeof(uint32_t)));
     B2_CUDA(cudaMemset(counters, 0, n_counters * sizeof(uint32_t)));
-    B2_CUDA(cudaMalloc(&status, 256));
-    B2_CUDA(cudaMemset(status, 0, 256));
-    B2_CUDA(cudaMallocHost(&status_host, 256));
+    void *h = nullptr, *d = nullptr;
+    B2_CUDA(cudaHostAlloc(&h, 256, cudaHostAllocMapped));
+    memset(h, 0, 256);
+    B2_CUDA(cudaHostGetDevicePointer(&d, h, 0));
+    status_host = (volatile int32_t *)h; status = (int32_t *)d;
     B2_CUDA(cudaMallocHost(&small.pinned, SmallBatch::kCap));
     B2_CUDA(cudaMalloc(&small.dev, SmallBatch::kCap));
     B2_CUDA(cudaEventCreateWithFlags(&small.ev, cudaEventDisableTiming));
+    return B200DNN_SUCCESS;
+  }
+  uint8_t *pinned_slab(size_t bytes) {
+    if (bytes > slab_cap) {
+      if (slab) cudaFreeHost(slab);
+      slab = nullptr; slab_cap = 0;
+      if (cudaMallocHost(&slab, bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+      slab_cap = bytes;
+    }
+    return slab;
+  }
+  void release_buffers() { ws.release(); blobs.release(); if (slab) { cudaFreeHost(slab); slab = nullptr; slab_cap = 0; } }
+};
+
+inline std::mutex &devices_mu() { static std::mutex m; return m; }
+inline DeviceShared *&device_slot(int dev) { static DeviceShared *slots[64] = {nullptr}; return slots[dev]; }
+
+// State of the CURRENT device (created at the first call made with that device current).  A call never touches
+// another device's buffers: which state it gets is decided by cudaGetDevice at its start.
+inline int32_t device_shared(DeviceShared **out) {
+  B2_CHECK(device_count() > 0, B200DNN_FAILURE, "no CUDA device: libb200dnn has no CPU fallback");
+  int dev = 0;
+  B2_CUDA(cudaGetDevice(&dev));
+  B2_CHECK(dev >= 0 && dev < 64, B200DNN_FAILURE, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(devices_mu());
+  DeviceShared *&slot = device_slot(dev);
+  if (!slot) {
+    cudaDeviceProp prop;
+    B2_CUDA(cudaGetDeviceProperties(&prop, dev));
+    B2_CHECK(prop.major == 10, B200DNN_FAILURE, "device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
     void *fn = nullptr; cudaDriverEntryPointQueryResult qres;
     B2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
     B2_CHECK(fn && qres == cudaDriverEntryPointSuccess, B200DNN_FAILURE, "cuTensorMapEncodeTiled not available from the driver");
-    encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+    DeviceShared *sh = new DeviceShared();
+    sh->dev = dev; sh->sm_count = prop.multiProcessorCount; sh->encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+    slot = sh;
+  }
+  *out = slot;
+  return B200DNN_SUCCESS;
+}
+
+inline Runtime *&current_rt() { static thread_local Runtime *r = nullptr; return r; }
+// The context of the call in progress on this thread (set by CallGuard).
+inline Runtime &rt() { return *current_rt(); }
+
+// Entered at the top of every C-ABI entry point: finds (or creates) the context of (current device, stream), takes its
+// lock for the duration of the call and rewinds its workspace.
+struct CallGuard {
+  Runtime *r = nullptr, *prev = nullptr;
+  int32_t enter(cudaStream_t st) {
+    DeviceShared *sh = nullptr;
+    B2_TRY(device_shared(&sh));
+    {
+      std::lock_guard<std::mutex> lk(sh->ctx_mu);
+      auto it = sh->ctxs.find(st);
+      if (it == sh->ctxs.end()) {
+        Runtime *n = new Runtime();
+        int32_t rc = n->init(sh, st);
+        if (rc != B200DNN_SUCCESS) { delete n; return rc; }
+        it = sh->ctxs.emplace(st, n).first;
+      }
+      r = it->second;
+    }
+    r->mu.lock();
+    prev = current_rt(); current_rt() = r;
+    r->ws.rewind();
+    r->small.begin();
     return B200DNN_SUCCESS;
   }
+  ~CallGuard() { if (r) { current_rt() = prev; r->mu.unlock(); } }
 };
-inline Runtime &rt() { static Runtime r; return r; }
+#define B2_ENTER(stream_ptr)                                       \
+  b200::CallGuard guard__;                                         \
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_ptr);    \
+  B2_TRY(guard__.enter(st))
+
+// After the stream has been drained: did a kernel of this context give up on one of its bounded waits since the last
+// check?  The kernels write the code into mapped pinned memory, so the check is one host load.
+inline int32_t read_status() {
+  Runtime &R = rt();
+  const int32_t code = *R.status_host;
+  if (code != 0) {
+    *R.status_host = 0;
+    return fail(B200DNN_FAILURE, "a GEMM kernel gave up waiting on a barrier (code %d)", code);
+  }
+  return B200DNN_SUCCESS;
+}
+
+// Sends a host table to workspace memory without waiting for the copy: it travels through the call's pinned block.
+// Tables too large for the block are copied synchronously.
+inline int32_t upload_blob(const void *host, size_t bytes, cudaStream_t st, void **dev) {
+  Runtime &R = rt();
+  if (void *d = R.small.add(host, bytes, SmallBatch::kMaxItem)) {
+    B2_TRY(R.small.flush(st, false));
+    *dev = d;
+    return B200DNN_SUCCESS;
+  }
+  void *d = R.ws.alloc(bytes);
+  B2_CHECK(d, B200DNN_FAILURE, "workspace allocation failed");
+  B2_CUDA(cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, st));
+  B2_CUDA(cudaStreamSynchronize(st));
+  *dev = d;
+  return B200DNN_SUCCESS;
+}
+// The same for tables that depend only on the caller's weight pointers: kept on the device and found again by their
+// bytes, so a repeated call uploads nothing.
+inline int32_t cached_blob(const void *host, size_t bytes, cudaStream_t st, void **dev) {
+  Runtime &R = rt();
+  if (void *d = R.blobs.find(host, bytes)) { *dev = d; return B200DNN_SUCCESS; }
+  if (R.blobs.entries.size() >= 256) {      // bounded: start again (nothing in flight may still read the old tables)
+    B2_CUDA(cudaStreamSynchronize(st));
+    R.blobs.release();
+  }
+  void *d = nullptr;
+  B2_CUDA(cudaMalloc(&d, bytes ? bytes : 16));
+  B2_CUDA(cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, st));
+  B2_CUDA(cudaStreamSynchronize(st));
+  BlobCache::Entry e; e.bytes.assign((const uint8_t *)host, (const uint8_t *)host + bytes); e.dev = d;
+  R.blobs.entries.push_back(std::move(e));
+  *dev = d;
+  return B200DNN_SUCCESS;
+}
 
 // 2-D uint8 tensor map [rows][row_bytes used of pitch] with a [box_rows x 128 B] box, SWIZZLE_128B.
 inline int32_t make_map_2d(CUtensorMap *m, const void *base, uint64_t inner_bytes, uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows) {
@@ -239,7 +409,10 @@ inline int32_t finish_out(std::initializer_list<Staged *> outs, cudaStream_t st)
   for (Staged *s : outs)
     if (s->copy_back) { B2_CUDA(cudaMemcpyAsync(s->host, s->dev, s->bytes, cudaMemcpyDeviceToHost, st)); any = true; }
     else if (s->sync) any = true;
-  if (any) B2_CUDA(cudaStreamSynchronize(st));   // (polling cudaStreamQuery instead was measured 4 us slower per call; spinning on a pinned flag written by a stream-ordered cuStreamWriteValue32 was no faster)
+  if (any) {
+    B2_CUDA(cudaStreamSynchronize(st));   // (polling cudaStreamQuery instead was measured 4 us slower per call; spinning on a pinned flag written by a stream-ordered cuStreamWriteValue32 was no faster)
+    return read_status();
+  }
   return B200DNN_SUCCESS;
 }
 

@@ -10,9 +10,13 @@
 // b200dnn_prepack.
 //
 // The scratch (split-K partial sums + one arrival counter per output tile) lives in the file-scope
-// array below: kScratchBytes of device memory held by every GPU that loads this library, from load
-// until exit.  Shapes whose split-K scratch would not fit are rejected with an error; nothing is
-// truncated.  In host code the array's name is only a handle, not a device address, so the address
+// array below: kScratchBytes of device memory on every GPU that uses this library, held until the
+// process exits.  With CUDA's lazy module loading the array is committed when this file's module is
+// first loaded on a device, which can be as late as the first call made there: treat the first call
+// on each device as a warm-up and make it BEFORE the application's pool takes the remaining memory
+// (and before any stream capture).  Shapes whose split-K scratch would not fit are rejected with an
+// error; nothing is truncated.  Shapes that are not split use no scratch at all and are never
+// rejected for it.  In host code the array's name is only a handle, not a device address, so the address
 // is resolved with cudaGetSymbolAddress once per device (with that device current) on the first
 // call made on that device, and that pointer is what the kernel receives.  Because that first call
 // does this set-up, make it before starting any stream capture.
@@ -26,6 +30,8 @@
 
 #include "runtime.cuh"
 #include "common.cuh"
+#include "matmul_validate.cuh"
+#include "pack_kernels.cuh"
 #include "stream_gemm.cuh"
 
 using namespace b200;
@@ -61,69 +67,114 @@ int32_t scratch_for_current_device(void **out) {
   return B200DNN_SUCCESS;
 }
 
+// Split of the streaming kernel for one shape on a device with sm_count SMs, and the bytes of the fixed array a launch
+// of it would use (0 when the shape is not split: the kernel then touches neither partial sums nor counters).
+struct StaticPlan { int tiles_n, tiles_m, ksplit, chunks_total, chunks_per_cta; size_t tiles, need; };
+StaticPlan plan_for(int M, int N, int K, int sm_count) {
+  StaticPlan p{};
+  const int64_t Kp = round_up(K, 128);
+  p.chunks_total = (int)(Kp / 64);
+  p.tiles_n = (N + 31) / 32; p.tiles_m = (M + 15) / 16;
+  int ksplit = 1;
+  while ((long long)p.tiles_n * p.tiles_m * ksplit < 2ll * sm_count && p.chunks_total / (ksplit * 2) >= 16) ksplit *= 2;
+  p.chunks_per_cta = (p.chunks_total + ksplit - 1) / ksplit;
+  p.ksplit = (p.chunks_total + p.chunks_per_cta - 1) / p.chunks_per_cta;
+  p.tiles = (size_t)p.tiles_n * p.tiles_m;
+  p.need = p.ksplit > 1 ? p.tiles * p.ksplit * 16 * 32 * sizeof(int32_t) : 0;
+  return p;
+}
+bool plan_fits(const StaticPlan &p) { return p.ksplit <= 1 || (p.tiles <= (size_t)kMaxTiles && p.need <= kPartialBytes); }
+
 }  // namespace
+
+// Bytes of the fixed scratch a call of b200dnn_matmul_static_scratch with this shape uses on a device with sm_count
+// SMs (0 = the current device), in *bytes (0 for shapes that are not split); failure when the shape does not fit.
+// Pure arithmetic with an explicit sm_count, so a caller can size-check its shapes ahead of time.
+extern "C" int32_t b200dnn_static_scratch_query(int32_t M, int32_t N, int32_t K, int32_t sm_count, size_t *bytes) {
+  B2_CHECK(M > 0 && N > 0 && K > 0 && bytes, B200DNN_FAILURE, "bad argument");
+  if (sm_count <= 0) {
+    int dev = 0;
+    B2_CHECK(device_count() > 0, B200DNN_FAILURE, "no CUDA device and no sm_count given");
+    B2_CUDA(cudaGetDevice(&dev));
+    B2_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const StaticPlan p = plan_for(M, N, K, sm_count);
+  *bytes = p.need + (p.ksplit > 1 ? p.tiles * sizeof(uint32_t) : 0);
+  B2_CHECK(plan_fits(p), B200DNN_FAILURE,
+           "shape M=%d N=%d K=%d needs %zu bytes of split-K scratch in %zu tiles; the static scratch holds %zu bytes and %d tiles",
+           M, N, K, p.need, p.tiles, kPartialBytes, kMaxTiles);
+  return B200DNN_SUCCESS;
+}
 
 extern "C" int32_t b200dnn_matmul_static_scratch(const b200dnn_matmul_t *d, void *stream) {
   B2_CHECK(d, B200DNN_FAILURE, "null descriptor");
   B2_CHECK(device_count() > 0, B200DNN_FAILURE, "no CUDA device: libb200dnn has no CPU fallback");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int M = d->M, N = d->N, K = d->K;
-  B2_CHECK(d->src && d->weight && d->dst, B200DNN_FAILURE, "null src, weight or dst");
-  B2_CHECK(M > 0 && N > 0 && K > 0 && d->lda >= K && d->ldc >= N, B200DNN_FAILURE, "bad shape or leading dimension");
+  // the contract of b200dnn_matmul, then what this entry point leaves out
+  B2_TRY(validate_matmul_desc(d));
   B2_CHECK(d->wei_format == 'r', B200DNN_UNIMPLEMENTED, "static-scratch matmul takes a prepacked weight (mem_format_b='r') only");
   B2_CHECK(!d->dynamic_quant, B200DNN_UNIMPLEMENTED, "static-scratch matmul does not quantise the source (it would need workspace)");
-  B2_CHECK(d->src_dt == B200DNN_S8 || d->src_dt == B200DNN_U8, B200DNN_UNIMPLEMENTED, "source must be s8 or u8");
-  B2_CHECK(d->wei_dt == B200DNN_S8, B200DNN_UNIMPLEMENTED, "weights must be s8");
-  B2_CHECK(d->dst_dt == B200DNN_BF16 || d->dst_dt == B200DNN_F32 || d->dst_dt == B200DNN_S32, B200DNN_UNIMPLEMENTED, "dst dtype");
-  B2_CHECK(d->n_postops >= 0 && d->n_postops <= B200DNN_MAX_POSTOPS, B200DNN_FAILURE, "too many post-ops");
-  B2_CHECK(d->src_scale.count == 0 || d->src_scale.count == 1 || d->src_scale.count == M, B200DNN_UNIMPLEMENTED, "src scale granularity");
-  B2_CHECK(d->wei_scale.count == 0 || d->wei_scale.count == 1 || d->wei_scale.count == N, B200DNN_UNIMPLEMENTED, "weight scale granularity");
-  B2_CHECK((d->src_scale.count == 0 || d->src_scale.buff) && (d->wei_scale.count == 0 || d->wei_scale.buff), B200DNN_FAILURE, "null scale buffer");
-  if (d->dst_dt == B200DNN_S32)
-    B2_CHECK(d->src_scale.count == 0 && d->wei_scale.count == 0 && !d->bias && d->n_postops == 0, B200DNN_UNIMPLEMENTED,
-             "s32 destination returns raw compensated accumulators");
-  for (int i = 0; i < d->n_postops; ++i) {
-    const int t = d->postops[i].type;
-    B2_CHECK(t == PO_RELU || t == PO_LEAKY_RELU || t == PO_GELU_TANH || t == PO_GELU_ERF || t == PO_SIGMOID || t == PO_SWISH ||
-             t == PO_TANH || t == PO_ELU || t == PO_CLIP || ((t == PO_BINARY_ADD || t == PO_BINARY_MUL) && d->postops[i].buff),
-             B200DNN_UNIMPLEMENTED, "post-op %d", t);
+  // nothing is staged: a host pointer would go straight into the kernel and fault the GPU (classifying a pointer allocates nothing)
+  B2_CHECK(is_device_ptr(d->src) && is_device_ptr(d->weight) && is_device_ptr(d->dst), B200DNN_FAILURE,
+           "static-scratch matmul takes device pointers only (src, weight, dst)");
+  B2_CHECK((d->src_scale.count == 0 || is_device_ptr(d->src_scale.buff)) && (d->wei_scale.count == 0 || is_device_ptr(d->wei_scale.buff)) &&
+           (!d->src_zp.buff || is_device_ptr(d->src_zp.buff)) && (!d->bias || is_device_ptr(d->bias)), B200DNN_FAILURE,
+           "static-scratch matmul takes device pointers only (scales, zero-point, bias)");
+  for (int i = 0; i < d->n_postops; ++i)
+    if (d->postops[i].type == PO_BINARY_ADD || d->postops[i].type == PO_BINARY_MUL)
+      B2_CHECK(is_device_ptr(d->postops[i].buff), B200DNN_FAILURE, "static-scratch matmul takes device pointers only (post-op %d operand)", i);
+
+  // the weight must be a buffer that b200dnn_prepack wrote for this K and N, plain (not the gate/up interleaved) form:
+  // looked up in the host-side registry of packed buffers, else its header is read once (a 256-byte copy; no allocation)
+  DeviceShared *D = nullptr;
+  B2_TRY(device_shared(&D));
+  PackedWeight pw;
+  {
+    std::lock_guard<std::mutex> lk(D->cache_mu);
+    auto it = D->packed_registry.find(d->weight);
+    if (it == D->packed_registry.end()) {
+      PackHeader h;
+      B2_CUDA(cudaMemcpyAsync(&h, d->weight, sizeof h, cudaMemcpyDeviceToHost, st));
+      B2_CUDA(cudaStreamSynchronize(st));
+      B2_CHECK(h.magic == kPackMagic, B200DNN_FAILURE, "the weight buffer was not written by b200dnn_prepack");
+      PackedWeight v;
+      const uint8_t *b = reinterpret_cast<const uint8_t *>(d->weight);
+      v.colsum = reinterpret_cast<const int32_t *>(b + kPackHeaderBytes);
+      v.wt = reinterpret_cast<const int8_t *>(b + kPackHeaderBytes + h.Np * 4);
+      v.K = h.K; v.N = h.N; v.Kp = h.Kp; v.Np = h.Np; v.gated = h.gated; v.I = h.I;
+      it = D->packed_registry.emplace(d->weight, v).first;
+    }
+    pw = it->second;
   }
+  B2_CHECK(pw.K == K && pw.N == N && pw.gated == 0, B200DNN_FAILURE,
+           "prepacked weight is K=%lld N=%lld gated=%d, call asks for K=%d N=%d plain", (long long)pw.K, (long long)pw.N, pw.gated, K, N);
 
   void *scratch = nullptr;
   B2_TRY(scratch_for_current_device(&scratch));
 
-  // geometry: the same decomposition the allocating path uses, bounded by the fixed scratch
-  int sm_count = 148;
-  {
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  }
-  const int64_t Kp = round_up(K, 128), Np = round_up(N, 128);
+  // geometry: the same decomposition the allocating path uses, bounded by the fixed scratch when the shape is split
+  const StaticPlan pl = plan_for(M, N, K, D->sm_count);
   StreamGemmArgs g{};
   g.A = reinterpret_cast<const uint8_t *>(d->src); g.lda = d->lda; g.M = M; g.N = N; g.K = K;
-  const uint8_t *base = reinterpret_cast<const uint8_t *>(d->weight);
-  g.Wt = reinterpret_cast<const int8_t *>(base + kPackHeaderBytes + Np * 4); g.Kp = (int)Kp;
+  g.Wt = pw.wt; g.Kp = (int)pw.Kp;
   g.nb = 4; g.kw = 2;
-  g.chunks_total = (int)(Kp / 64);
-  const int tiles_n = (N + 31) / 32, tiles_m = (M + 15) / 16;
-  int ksplit = 1;
-  while (tiles_n * tiles_m * ksplit < 2 * sm_count && g.chunks_total / (ksplit * 2) >= 16) ksplit *= 2;
-  g.chunks_per_cta = (g.chunks_total + ksplit - 1) / ksplit;
-  ksplit = (g.chunks_total + g.chunks_per_cta - 1) / g.chunks_per_cta;
+  g.chunks_total = pl.chunks_total; g.chunks_per_cta = pl.chunks_per_cta;
+  const int ksplit = pl.ksplit;
   const int kbytes = g.chunks_per_cta * 64;
   g.a_stride = (int)round_up(kbytes, 128) + 64;
   size_t smem = (size_t)16 * g.a_stride;
   if (smem < 4096) smem = 4096;
   B2_CHECK(smem <= 200 * 1024, B200DNN_FAILURE, "K = %d is too large for the static-scratch kernel", K);
-  const size_t tiles = (size_t)tiles_n * tiles_m;
-  const size_t need = ksplit > 1 ? tiles * ksplit * 16 * 32 * sizeof(int32_t) : 0;
-  B2_CHECK(tiles <= (size_t)kMaxTiles && need <= kPartialBytes, B200DNN_FAILURE,
+  B2_CHECK(plan_fits(pl), B200DNN_FAILURE,
            "shape M=%d N=%d K=%d needs %zu bytes of split-K scratch in %zu tiles; the static scratch holds %zu bytes and %d tiles",
-           M, N, K, need, tiles, kPartialBytes, kMaxTiles);
-  g.partial = reinterpret_cast<int32_t *>(scratch);
-  g.counters = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(scratch) + kPartialBytes);
-  // the counters must be zero when the kernel starts, whatever an earlier call left behind
-  if (ksplit > 1) B2_CUDA(cudaMemsetAsync(g.counters, 0, tiles * sizeof(uint32_t), st));
+           M, N, K, pl.need, pl.tiles, kPartialBytes, kMaxTiles);
+  if (ksplit > 1) {
+    g.partial = reinterpret_cast<int32_t *>(scratch);
+    g.counters = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(scratch) + kPartialBytes);
+    // the counters must be zero when the kernel starts, whatever an earlier call left behind
+    B2_CUDA(cudaMemsetAsync(g.counters, 0, pl.tiles * sizeof(uint32_t), st));
+  }
 
   EpiParams e;
   memset(&e, 0, sizeof e);
@@ -131,13 +182,13 @@ extern "C" int32_t b200dnn_matmul_static_scratch(const b200dnn_matmul_t *d, void
   e.src_scale = d->src_scale.count ? d->src_scale.buff : nullptr; e.src_scale_dt = d->src_scale.dt; e.src_scale_n = (int32_t)d->src_scale.count;
   e.wei_scale = d->wei_scale.count ? d->wei_scale.buff : nullptr; e.wei_scale_dt = d->wei_scale.dt; e.wei_scale_n = (int32_t)d->wei_scale.count;
   if (d->src_zp.buff) { e.src_zp = d->src_zp.buff; e.src_zp_dt = d->src_zp.dt; e.has_zp = 1; }
-  e.colsum = reinterpret_cast<const int32_t *>(base + kPackHeaderBytes);
+  e.colsum = pw.colsum;
   e.bias = d->bias; e.bias_dt = d->bias_dt; e.n_po = d->n_postops;
   for (int i = 0; i < d->n_postops; ++i) {
     e.po[i].type = d->postops[i].type; e.po[i].dt = d->postops[i].dt; e.po[i].buff = d->postops[i].buff;
     e.po[i].ld = d->postops[i].ld; e.po[i].alpha = d->postops[i].alpha; e.po[i].beta = d->postops[i].beta;
   }
-  dim3 grid(tiles_n, ksplit, tiles_m);
+  dim3 grid(pl.tiles_n, ksplit, pl.tiles_m);
   if (d->src_dt == B200DNN_U8) stream_gemm_kernel<true><<<grid, 256, smem, st>>>(g, e);
   else stream_gemm_kernel<false><<<grid, 256, smem, st>>>(g, e);
   B2_LAUNCHED();

@@ -477,7 +477,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (lane == 0) {
         const CUtensorMap *mb = a.maps_b ? a.maps_b + t.g : &map_b0;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { s_err = 1; atomicExch(a.status, 1); ok = false; break; }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { s_err = 1; report_status(a.status, 1); ok = false; break; }
           const uint32_t sa = smem0 + (uint32_t)stage * stage_bytes;
           mbar_expect_tx(full_bar(stage), stage_bytes);
           tma_load_2d(sa, &map_a, kb * kTcBK, t.row0, full_bar(stage));
@@ -492,7 +492,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t idesc = make_idesc_i8(a.a_unsigned, a.BN);
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
       for (int tile = tile0; tile < total_tiles && !s_err; tile += tile_step) {
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { s_err = 2; atomicExch(a.status, 2); break; }
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { s_err = 2; report_status(a.status, 2); break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * a.BN);
         bool ok = true;
@@ -508,7 +508,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_commit(empty_bar(stage));
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
-        if (!ok) { s_err = 3; atomicExch(a.status, 3); break; }
+        if (!ok) { s_err = 3; report_status(a.status, 3); break; }
         tc_commit(tfull_bar(acc));
         if (tile == tile0) TC_STAMP(3);
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -548,7 +548,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         rs[j] = (epi.src_scale_n && r < t.rows) ? load_as_f32(epi.src_scale, epi.src_scale_dt, epi.src_scale_n > 1 ? t.row0 + r : 0) : 1.0f;
       }
       // the buffer is free when the epilogue warps have left the tile that used it two tiles ago
-      if (!__all_sync(0xffffffffu, mbar_wait(cempty_bar(cb), cphase ^ 1u))) { if (lane == 0) { s_err = 6; atomicExch(a.status, 6); } break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(cempty_bar(cb), cphase ^ 1u))) { if (lane == 0) { s_err = 6; report_status(a.status, 6); } break; }
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         if (lane + 32 * j < a.BN) { cols[cb].ws[lane + 32 * j] = cw[j]; cols[cb].bias[lane + 32 * j] = cbv[j]; cols[cb].comp[lane + 32 * j] = ck[j]; }
@@ -572,7 +572,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int ob = 0; uint32_t ophase = 0;            // operand buffer of the current tile
     for (int tile = tile0; tile < total_tiles; tile += tile_step) {
       // everything from global memory was put into shared memory by the operand warp
-      if (!mbar_wait(cfull_bar(ob), ophase)) { if (lane == 0) { s_err = 5; atomicExch(a.status, 5); } break; }
+      if (!mbar_wait(cfull_bar(ob), ophase)) { if (lane == 0) { s_err = 5; report_status(a.status, 5); } break; }
       const TileMeta tm = meta[ob];
       const TileCols &tcols = cols[ob];
       const bool row_ok = row_in_tile < tm.rows;
@@ -582,7 +582,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       cx.wei_scale = nullptr; cx.colsum = nullptr; cx.bias = nullptr; cx.dst = tm.dst; cx.ldc = tm.ldc;
       cx.s_src = row_scale[ob][row_in_tile];
       const int pc_tile = tm.nt * a.BN;
-      if (!mbar_wait(tfull_bar(acc), acc_phase)) { if (lane == 0) { s_err = 4; atomicExch(a.status, 4); } break; }
+      if (!mbar_wait(tfull_bar(acc), acc_phase)) { if (lane == 0) { s_err = 4; report_status(a.status, 4); } break; }
       if (warp == 2 && lane == 0 && tile == tile0) TC_STAMP(4);
       tc_fence_after();
       const bool has_bias = tm.has_bias != 0;
@@ -633,7 +633,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (a.dbg == 2) { uint32_t x = 0;
 #pragma unroll
             for (int i = 0; i < 32; ++i) x ^= r[i];
-            if (x == 0x12345678u) atomicExch(a.status, 99); continue; }
+            if (x == 0x12345678u) report_status(a.status, 99); continue; }
           tc_epi_dispatch(a.fast_act, epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane);
         }
       } else {

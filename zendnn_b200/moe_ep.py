@@ -1,28 +1,125 @@
-"""Expert-parallel fused MoE over several GPUs (one process per GPU, torch.distributed / NCCL).
+"""Expert-parallel fused MoE over several GPUs (one process per GPU).
 
-The reference (a single-process CPU library) has no multi-device path; this module is the one place
-where the W8A8 hot path has a real exchange step.  Placement: expert e lives on rank e % world (its
-local index is e // world); tokens are data-parallel, every rank routes its own tokens.  Per layer:
+Two layers live here.
 
-  route local tokens -> sort (token,k) slots by (destination rank, local expert) -> quantise every
-  token once to s8 + one f32 scale and write it to the send rows of all its slots (1 byte per element
-  crosses NVLink instead of 2) and, for the replicated shared experts, to their local rows ->
-  all-to-all dispatch (rows, scales; counts exchanged first) -> ONE grouped expert computation over the
-  received rows (one group per (source rank, local expert)) and the shared experts' rows -> all-to-all
-  combine of the bf16 expert outputs -> weighted reduce on the owning rank.
-  One buffer holds [received rows | shared-expert rows | send rows] (the same layout for the outputs), so
-  the exchanges and the reduce work on views of it and nothing is concatenated or copied.
+`EpLayer` is the product path: a thin binding of the library's own expert-parallel entry point
+(b200dnn_moe_layer_ep, include/b200dnn.h).  The whole layer runs inside the library on the caller's stream: tokens are
+quantised once and stored straight into the receive buffers of the GPUs that own their experts (peer memory over
+NVLink), the grouped GEMMs read only local memory, and the weighted reduce loads the output rows back from the owners.
+NCCL carries the per-expert row counts and two barriers; torch.distributed is used once, to hand the communicator id
+to the other ranks.  `plan_expert_placement` chooses which rank owns which expert from a histogram of routed rows.
 
-Per-row arithmetic does not depend on where a row is computed, so the result equals the single-GPU
-result bit for bit.
+`ep_moe_forward` below is the same exchange written over torch.distributed all-to-all calls with a pluggable `ops`
+object.  It serves machines whose GPUs cannot map each other's memory and the CPU tests of the exchange logic
+(gloo ranks with a stand-in `ops`).
 
-The device work goes through an `ops` object.  `CapiOps` binds libb200dnn (CUDA); tests drive the
-same orchestration on CPU ranks (gloo) with a stand-in `ops` to check the exchange logic.
+The reference (a single-process CPU library) has no multi-device path.  Placement in `ep_moe_forward`: expert e lives
+on rank e % world (local index e // world); every rank routes its own tokens, sorts the (token,k) slots by
+(destination rank, local expert), quantises every token once into the send rows of all its slots, exchanges counts,
+rows and scales with all-to-all calls, runs one grouped expert computation over (source rank, local expert) groups
+and the shared experts' rows, returns the bf16 outputs with a second all-to-all and reduces on the owning rank.
+Per-row arithmetic does not depend on where a row is computed, so both layers equal the single-GPU result bit for bit.
 """
 import ctypes as C
 
 import torch
 import torch.distributed as dist
+
+
+def plan_expert_placement(rows_per_expert, world, experts_per_rank=None):
+    """Owner rank of every routed expert, balancing the rows each rank computes.
+
+    rows_per_expert: how many (token,k) slots each expert received on a calibration batch (all ranks together).
+    Longest-processing-time greedy: experts in descending load, each to the rank with the fewest rows so far among
+    the ranks that still have room (experts_per_rank, default ceil(E / world), bounds the weights a rank holds).
+    Ties go to the lower rank and the lower expert id, so every rank computes the same map from the same histogram.
+    Returns a list of length E."""
+    E = len(rows_per_expert)
+    cap = experts_per_rank if experts_per_rank else (E + world - 1) // world
+    assert cap * world >= E, "not enough room for %d experts on %d ranks" % (E, world)
+    order = sorted(range(E), key=lambda e: (-int(rows_per_expert[e]), e))
+    load, count, owner = [0] * world, [0] * world, [0] * E
+    for e in order:
+        r = min((r for r in range(world) if count[r] < cap), key=lambda r: (load[r], r))
+        owner[e] = r
+        load[r] += int(rows_per_expert[e])
+        count[r] += 1
+    return owner
+
+
+def modulo_placement(num_experts, world):
+    return [e % world for e in range(num_experts)]
+
+
+class EpLayer:
+    """One rank of the library's expert-parallel MoE layer (b200dnn_moe_layer_ep).
+
+    experts: this rank's routed experts in ascending expert id, then the shared experts; each a dict with CUDA
+    tensors w13 [K,2I] s8, s13 [2I] f32, w2 [I,H] s8, s2 [H] f32.  expert_rank: owner of every routed expert
+    (default e % world).  With world > 1, `connect()` must be called by all ranks (it uses torch.distributed, any
+    backend, only to broadcast the communicator id)."""
+
+    def __init__(self, rank, world, num_experts, num_shared, topk, max_tokens, K, I, H, experts, expert_rank=None,
+                 act="silu_and_mul", capacity_rows=0):
+        from . import capi
+        self.capi, self.rank, self.world = capi, rank, world
+        self.K, self.I, self.H, self.E = K, I, H, num_experts
+        cfg = capi.EpConfig()
+        cfg.world, cfg.rank, cfg.num_experts, cfg.num_shared, cfg.topk = world, rank, num_experts, num_shared, topk
+        cfg.max_tokens, cfg.K, cfg.I, cfg.H, cfg.transB, cfg.act = max_tokens, K, I, H, 0, capi.ACT[act]
+        cfg.capacity_rows = capacity_rows
+        self._map = None
+        if expert_rank is not None:
+            self._map = (C.c_int32 * num_experts)(*[int(r) for r in expert_rank])
+            cfg.expert_rank = C.cast(self._map, C.c_void_p)
+        self.handle = C.c_void_p()
+        capi.check(capi.lib.b200dnn_ep_create(C.byref(cfg), C.byref(self.handle)))
+        self.experts = list(experts)
+        self.struct = (capi.MoeExpert * max(1, len(self.experts)))()
+        for i, e in enumerate(self.experts):
+            s = self.struct[i]
+            s.w13, s.ldb13, s.w13_scale = e["w13"].data_ptr(), 2 * I, e["s13"].data_ptr()
+            s.w2, s.ldb2, s.w2_scale = e["w2"].data_ptr(), H, e["s2"].data_ptr()
+        capi.check(capi.lib.b200dnn_ep_set_experts(self.handle, self.struct, len(self.experts)))
+
+    def connect(self, group=None):
+        if self.world == 1:
+            return
+        ident = (C.c_uint8 * 128)()
+        if self.rank == 0:
+            self.capi.check(self.capi.lib.b200dnn_ep_nccl_unique_id(ident))
+        box = [bytes(ident)]
+        dist.broadcast_object_list(box, src=0, group=group)
+        ident = (C.c_uint8 * 128).from_buffer_copy(box[0])
+        self.capi.check(self.capi.lib.b200dnn_ep_connect_nccl(self.handle, ident, None))
+
+    def forward(self, x, logits, out=None, stream=None):
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty(T, self.H, dtype=torch.bfloat16, device=x.device)
+        st = stream if stream is not None else (torch.cuda.current_stream().cuda_stream if x.is_cuda else None)
+        self.capi.check(self.capi.lib.b200dnn_moe_layer_ep(self.handle, x.data_ptr(), x.stride(0) if T else self.K,
+                                                           logits.data_ptr(), T, out.data_ptr(), out.stride(0) if T else self.H, st))
+        return out
+
+    def rows_per_rank(self):
+        rows = (C.c_int32 * self.world)()
+        self.capi.check(self.capi.lib.b200dnn_ep_rows_per_rank(self.handle, rows, torch.cuda.current_stream().cuda_stream))
+        return list(rows)
+
+    def status(self):
+        return self.capi.lib.b200dnn_ep_status(self.handle, torch.cuda.current_stream().cuda_stream)
+
+    def close(self):
+        if self.handle:
+            self.capi.lib.b200dnn_ep_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def expert_owner(e, world):
