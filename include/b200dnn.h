@@ -296,12 +296,19 @@ B200DNN_API int32_t b200dnn_ep_rows_per_rank(void *handle, int32_t *rows, void *
 B200DNN_API int32_t b200dnn_ep_status(void *handle, void *stream);
 
 /* Per-phase device times of b200dnn_moe_layer and b200dnn_moe_layer_ep calls on `stream` (CUDA events recorded by the
- * library itself; off by default).  b200dnn_phase_times waits for the stream and returns the milliseconds of the last
- * call: index 0 route + slot ranks, 1 count exchange, 2 quantise + dispatch, 3 barrier, 4 first GEMM with the gated
+ * library itself; off by default).  b200dnn_phase_times waits for the stream and returns the mean milliseconds per call
+ * over the calls made since timing was switched on (their number in *calls, which may be NULL): index 0 route + slot ranks, 1 count exchange, 2 quantise + dispatch, 3 barrier, 4 first GEMM with the gated
  * activation, 5 requantisation, 6 second GEMM, 7 barrier, 8 combine + weighted reduce. */
 enum { B200DNN_PHASES = 9 };
 B200DNN_API int32_t b200dnn_phase_timing(void *stream, int32_t enable);
-B200DNN_API int32_t b200dnn_phase_times(void *stream, float *ms, int32_t n);
+B200DNN_API int32_t b200dnn_phase_times(void *stream, float *ms, int32_t n, int32_t *calls);
+
+/* Measurement aid, no reference counterpart: the issue-bound rate of the int8 tensor-core instruction the GEMM
+ * kernels use (tcgen05.mma kind::i8, M128 x N256 x K32, operands resident in shared memory, no global loads), on every
+ * SM at once.  `launches` launches of `iters` K-blocks each run back to back; *ms is their device time, *ops the
+ * operations performed (2 per multiply-add), so ops / ms / 1e9 is TOPS.  A short run gives the burst rate, a run of
+ * seconds the rate under the power cap. */
+B200DNN_API int32_t b200dnn_measure_int8_peak(int32_t iters, int32_t launches, float *ms, double *ops, void *stream);
 
 /* Drops every cached packed weight / staged buffer: the counterpart of the reference's cache
  * clearing between tests (gtests/gtest_utils.cpp:77-118) and clear_fused_moe_scratch()

@@ -187,6 +187,34 @@ def test_eltwise_postops_single_and_chained(capi, oracle, monkeypatch, kernel, n
         assert np.allclose(got32, ref32, rtol=1e-5, atol=1e-5), (name, float(np.abs(got32 - ref32).max()))
 
 
+@pytest.mark.parametrize("bn", ["0", "96", "128", "160", "224", "256"])
+@pytest.mark.parametrize("shape", [(257, 1024, 264), (600, 512, 1000), (1024, 2048, 512), (130, 4096, 128), (900, 384, 2100)])
+def test_tc_pair_form(capi, oracle, monkeypatch, bn, shape):
+    """The two-CTA form of the tcgen05 kernel (cta_group::2: each CTA of a pair loads its 128 rows of A and half of the
+    weight tile, the leader issues M256 MMAs for both): s32 bit-exact for ragged M and N, and the float epilogue gives the
+    bytes of the single-CTA form."""
+    M, K, N = shape
+    monkeypatch.setenv("B200DNN_TC_PAIR", "1")
+    monkeypatch.setenv("B200DNN_TC_BN", bn)
+    rng = np.random.default_rng(M + N)
+    W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    for src in ("u8", "s8"):
+        A = rng.integers(0, 256, (M, K), dtype=np.uint8) if src == "u8" else rng.integers(-128, 128, (M, K), dtype=np.int8)
+        got = run(capi, M, N, K, A, W, "s32", weights_const=False, force_kernel=TC)
+        assert (got == oracle.gemm_s32(A, W)).all(), (src, "pair form s32")
+    sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    sw = rng.uniform(1e-4, 5e-4, N).astype(np.float32)
+    bias = rng.normal(size=N).astype(np.float32)
+    kw = dict(weights_const=False, force_kernel=TC, src_scale=sa, wei_scale=sw, bias=bias, postops=["gelu_tanh"])
+    got = run(capi, M, N, K, A, W, "bf16", **kw)
+    monkeypatch.setenv("B200DNN_TC_PAIR", "0")
+    monkeypatch.setenv("B200DNN_TC_BN", "0")
+    single = run(capi, M, N, K, A, W, "bf16", **kw)
+    assert (got == single).all(), int((got != single).sum())
+    got32 = run(capi, M, N, K, A, W, "f32", weights_const=False, force_kernel=TC, src_scale=sa, wei_scale=sw)
+    assert np.array_equal(got32, oracle.matmul_w8a8(A, W, "f32", src_scale=sa, wei_scale=sw))
+
+
 def test_scales_in_bf16_storage(capi, oracle):
     c = decode_case(oracle, 8, 512, 128, seed=3)
     sa16, sw16 = oracle.f32_to_bf16(c["sa"]), oracle.f32_to_bf16(c["sw"])
@@ -377,4 +405,50 @@ def test_bounded_waits_leave_a_status_and_a_usable_context(capi, oracle, monkeyp
     assert capi.matmul(d, st) == capi.SUCCESS
     assert capi.lib.b200dnn_stream_status(st) == capi.SUCCESS
     assert (out.cpu().numpy() == oracle.gemm_s32(A, W)).all()
+    capi.lib.b200dnn_clear_caches()
+
+
+def test_two_host_threads_on_two_streams(capi, oracle):
+    """The entry points are re-entrant like the reference's (lowoha_operators/matmul/lowoha_matmul.hpp:95-99): two host
+    threads, each on its own stream, interleave dynamic-quantisation GEMMs (which use library workspace) and split-K
+    streaming GEMMs (which use workspace and tile counters) without sharing scratch.  Every result is checked."""
+    import threading
+    import torch
+    dev = torch.device("cuda:0")
+    jobs = []
+    for i, (M, K, N, kernel) in enumerate([(48, 1024, 512, 2), (7, 4096, 256, 3)]):
+        rng = np.random.default_rng(40 + i)
+        x = oracle.f32_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+        qw, sw = oracle.quant_weights_per_channel(oracle.f32_to_bf16((rng.normal(size=(K, N)) * 0.02).astype(np.float32)))
+        qa, sa = oracle.quant_per_token(x)
+        ref = oracle.matmul_w8a8(qa, qw, "bf16", src_scale=sa, wei_scale=sw)
+        jobs.append(dict(M=M, K=K, N=N, kernel=kernel, ref=ref, stream=torch.cuda.Stream(),
+                         x=torch.from_numpy(x.view(np.int16)).to(dev), W=torch.from_numpy(qw).to(dev), sw=torch.from_numpy(sw).to(dev),
+                         outs=[torch.zeros(M, N, dtype=torch.bfloat16, device=dev) for _ in range(40)], err=None))
+
+    def work(j):
+        try:
+            st = j["stream"].cuda_stream
+            for out in j["outs"]:
+                d = capi.make_matmul(j["M"], j["N"], j["K"], j["x"], j["W"], out, src_dt=capi.DT["bf16"], dst_dt=capi.DT["bf16"],
+                                     dynamic_quant=True, src_scale=capi.quant(None, count=j["M"], dt=capi.DT["f32"]), wei_scale=j["sw"],
+                                     force_kernel=j["kernel"])
+                if capi.matmul(d, st) != capi.SUCCESS:
+                    raise RuntimeError(capi.last_error())
+            if capi.lib.b200dnn_stream_status(st) != capi.SUCCESS:
+                raise RuntimeError(capi.last_error())
+        except Exception as e:      # reported by the main thread
+            j["err"] = e
+
+    torch.cuda.synchronize()
+    threads = [threading.Thread(target=work, args=(j,)) for j in jobs]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    for j in jobs:
+        assert j["err"] is None, j["err"]
+        for out in j["outs"]:
+            assert (out.view(torch.int16).cpu().numpy().view(np.uint16) == j["ref"]).all()
     capi.lib.b200dnn_clear_caches()

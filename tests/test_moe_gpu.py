@@ -90,8 +90,11 @@ def _experts(oracle, rng, E, H, I):
 
 @pytest.mark.parametrize("T,H,I,E,k,act", [(48, 128, 64, 4, 2, "silu_and_mul"), (300, 256, 160, 6, 2, "silu_and_mul"),
                                            (64, 128, 96, 3, 1, "gelu_and_mul"), (64, 128, 64, 4, 2, "swiglu_oai_mul")])
-def test_fused_moe_reference_contract(capi, oracle, T, H, I, E, k, act):
-    """Rows gathered by the caller, per-expert dst_down, row_ptrs + top-k weights: the group_matmul_direct contract."""
+@pytest.mark.parametrize("pair", ["0", "1"])
+def test_fused_moe_reference_contract(capi, oracle, monkeypatch, pair, T, H, I, E, k, act):
+    """Rows gathered by the caller, per-expert dst_down, row_ptrs + top-k weights: the group_matmul_direct contract.
+    pair: the grouped GEMMs run in the single-CTA form or in the two-CTA (cta_group::2) form."""
+    monkeypatch.setenv("B200DNN_TC_PAIR", pair)
     rng = np.random.default_rng(T + I)
     x = oracle.f32_to_bf16(rng.normal(size=(T, H)).astype(np.float32))
     logits = rng.normal(size=(T, E)).astype(np.float32)
@@ -126,9 +129,11 @@ def test_fused_moe_reference_contract(capi, oracle, T, H, I, E, k, act):
     capi.lib.b200dnn_clear_caches()
 
 
-@pytest.mark.parametrize("T,H,I,E,k,S", [(256, 256, 128, 8, 2, 0), (512, 128, 96, 16, 4, 2)])
-def test_moe_layer_end_to_end(capi, oracle, T, H, I, E, k, S):
+@pytest.mark.parametrize("T,H,I,E,k,S", [(256, 256, 128, 8, 2, 0), (512, 128, 96, 16, 4, 2), (1500, 256, 320, 4, 2, 1)])
+@pytest.mark.parametrize("pair", ["0", "1"])
+def test_moe_layer_end_to_end(capi, oracle, monkeypatch, pair, T, H, I, E, k, S):
     """Router + permutation + fused MoE + un-permute on the device; shared experts see every token with weight 1."""
+    monkeypatch.setenv("B200DNN_TC_PAIR", pair)
     rng = np.random.default_rng(E)
     x = oracle.f32_to_bf16(rng.normal(size=(T, H)).astype(np.float32))
     bias = np.log(np.arange(1, E + 1, dtype=np.float64) ** -1.1)      # skewed load

@@ -58,8 +58,8 @@ class EpConfig(C.Structure):
 
 
 PHASES = 9
-PHASE_NAMES = ["route+rank", "count exchange", "quantise+dispatch", "barrier", "gemm1+act", "requantise", "gemm2", "barrier",
-               "combine+reduce"]
+PHASE_NAMES = ["route+rank", "count exchange", "quantise+dispatch", "barrier after dispatch", "gemm1+act", "requantise", "gemm2",
+               "barrier before combine", "combine+reduce"]
 
 EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b200dnn_launch_count",
            "b200dnn_matmul", "b200dnn_matmul_static_scratch", "b200dnn_static_scratch_query", "b200dnn_prepack_size", "b200dnn_prepack", "b200dnn_quant_per_token",
@@ -70,7 +70,7 @@ EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b20
            "b200dnn_moe_weighted_reduce_rows", "b200dnn_ep_create", "b200dnn_ep_destroy", "b200dnn_ep_local_expert_count",
            "b200dnn_ep_set_experts", "b200dnn_ep_nccl_unique_id", "b200dnn_ep_connect_nccl", "b200dnn_ep_connect_local",
            "b200dnn_moe_layer_ep", "b200dnn_moe_layer_ep_local", "b200dnn_ep_rows_per_rank", "b200dnn_ep_status",
-           "b200dnn_phase_timing", "b200dnn_phase_times"]
+           "b200dnn_phase_timing", "b200dnn_phase_times", "b200dnn_measure_int8_peak"]
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -119,7 +119,8 @@ lib.b200dnn_moe_layer_ep_local.argtypes = [C.POINTER(vp), i32, C.POINTER(vp), i6
 lib.b200dnn_ep_rows_per_rank.argtypes = [vp, C.POINTER(i32), vp]
 lib.b200dnn_ep_status.argtypes = [vp, vp]
 lib.b200dnn_phase_timing.argtypes = [vp, i32]
-lib.b200dnn_phase_times.argtypes = [vp, C.POINTER(C.c_float), i32]
+lib.b200dnn_phase_times.argtypes = [vp, C.POINTER(C.c_float), i32, C.POINTER(i32)]
+lib.b200dnn_measure_int8_peak.argtypes = [i32, i32, C.POINTER(C.c_float), C.POINTER(C.c_double), vp]
 
 
 class B200DNNError(RuntimeError):

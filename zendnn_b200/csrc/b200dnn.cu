@@ -147,7 +147,8 @@ int32_t resolve_weight(const void *weight, int wei_format, int64_t K, int64_t N,
 }
 
 // ------------------------------------------------------------------------------------ quant helpers
-int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, cudaStream_t st) {
+template <bool EP>
+int32_t launch_quant_rows_t(const RowQuantArgs &a, int32_t src_dt, int64_t rows, cudaStream_t st) {
   if (rows <= 0) return B200DNN_SUCCESS;
   // short, aligned, non-grouped rows: one warp per row
   const int E = src_dt == B200DNN_BF16 ? 8 : 4;
@@ -157,8 +158,8 @@ int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, c
   if (aligned && rows >= 64 && a.K / E <= 32 * 8 && (src_dt == B200DNN_BF16 || src_dt == B200DNN_F32)) {
     const int nv = (a.K / E + 31) / 32;
     unsigned grid = (unsigned)((rows + 7) / 8);
-    if (a.n_rows_dev && grid > (unsigned)(rt().sm_count * 16)) grid = (unsigned)(rt().sm_count * 16);   // the warps stride over the rows
-#define B2_QW(T, NV) quant_per_token_warp_kernel<T, NV><<<grid, 256, 0, st>>>(a, (int)rows)
+    if (EP && a.n_rows_dev && grid > (unsigned)(rt().sm_count * 16)) grid = (unsigned)(rt().sm_count * 16);   // the warps stride over the rows
+#define B2_QW(T, NV) quant_per_token_warp_kernel<T, NV, EP><<<grid, 256, 0, st>>>(a, (int)rows)
     if (src_dt == B200DNN_BF16) { if (nv <= 2) B2_QW(uint16_t, 2); else if (nv <= 4) B2_QW(uint16_t, 4); else if (nv <= 8) B2_QW(uint16_t, 8); else B2_QW(uint16_t, 16); }
     else { if (nv <= 2) B2_QW(float, 2); else if (nv <= 4) B2_QW(float, 4); else if (nv <= 8) B2_QW(float, 8); else B2_QW(float, 16); }
 #undef B2_QW
@@ -168,17 +169,21 @@ int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, c
   }
   const bool short_row = a.K / E <= 2 * kQuantThreads;     // the whole row fits two cached vectors per thread
   unsigned grid_rows = (unsigned)rows;
-  if (a.n_rows_dev && grid_rows > (unsigned)(rt().sm_count * 32)) grid_rows = (unsigned)(rt().sm_count * 32);   // the CTAs stride over the rows
+  if (EP && a.n_rows_dev && grid_rows > (unsigned)(rt().sm_count * 32)) grid_rows = (unsigned)(rt().sm_count * 32);   // the CTAs stride over the rows
   if (src_dt == B200DNN_BF16) {
-    if (short_row) quant_per_token_kernel<uint16_t, 2><<<grid_rows, kQuantThreads, 0, st>>>(a);
-    else quant_per_token_kernel<uint16_t, kQuantRegVec><<<grid_rows, kQuantThreads, 0, st>>>(a);
+    if (short_row) quant_per_token_kernel<uint16_t, 2, EP><<<grid_rows, kQuantThreads, 0, st>>>(a);
+    else quant_per_token_kernel<uint16_t, kQuantRegVec, EP><<<grid_rows, kQuantThreads, 0, st>>>(a);
   } else if (src_dt == B200DNN_F32) {
-    if (short_row) quant_per_token_kernel<float, 2><<<grid_rows, kQuantThreads, 0, st>>>(a);
-    else quant_per_token_kernel<float, kQuantRegVec><<<grid_rows, kQuantThreads, 0, st>>>(a);
+    if (short_row) quant_per_token_kernel<float, 2, EP><<<grid_rows, kQuantThreads, 0, st>>>(a);
+    else quant_per_token_kernel<float, kQuantRegVec, EP><<<grid_rows, kQuantThreads, 0, st>>>(a);
   } else return fail(B200DNN_UNIMPLEMENTED, "per-token quantisation takes f32 or bf16 input");
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
   return B200DNN_SUCCESS;
+}
+int32_t launch_quant_rows(const RowQuantArgs &a, int32_t src_dt, int64_t rows, cudaStream_t st) {
+  if (a.n_rows_dev || a.scatter_peer) return launch_quant_rows_t<true>(a, src_dt, rows, st);
+  return launch_quant_rows_t<false>(a, src_dt, rows, st);
 }
 
 // ------------------------------------------------------------------------------------ GEMM launchers
@@ -313,9 +318,21 @@ int32_t launch_decode_ring(const uint8_t *A, int64_t lda, bool a_unsigned, int M
 // partly filled wave of a persistent grid can cost more than a narrower tile does (M=2048, N=14336: 896 tiles of 256
 // columns are 7 waves on 148 SMs, 1024 tiles of 224 columns are 7 waves as well and each is an eighth shorter).
 // Smaller problems take the widest tile that still gives every SM one.
-int pick_bn(int m_tiles, int N, int sm_count, int gated) {
+int pick_bn(int m_tiles, int N, int sm_count, int gated, int pair = 0) {
   int forced = env_int("B200DNN_TC_BN", 0);
   if (forced > 0) return forced;
+  if (pair) {
+    // pair form: m_tiles counts 256-row tiles, one per CTA pair; each CTA's half of the tile must hold whole
+    // 64-column gate/up blocks in the gated form (and whole 8-row weight groups always)
+    const int pairs = sm_count / 2, pstep = gated ? 128 : 32;
+    int best = 256; long long best_cost = -1;
+    for (int bn = 256; bn >= 128; bn -= pstep) {
+      const long long tiles = (long long)m_tiles * ((N + bn - 1) / bn);
+      const long long cost = ((tiles + pairs - 1) / pairs) * (bn + 16);
+      if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
+    }
+    return best;
+  }
   const int step = gated ? 64 : 32;
   if ((long long)m_tiles * ((N + 127) / 128) >= sm_count) {
     int best = 256; long long best_cost = -1;
@@ -410,6 +427,17 @@ void pick_split(int m_tiles, int N, int k_blocks, int *bn, int *splits) {
   if (best_s > 1) { *bn = best_bn; *splits = best_s; }
 }
 
+// Rows of a row tile for a GEMM over about `rows` rows: 256 (pair form, two CTAs per tile) for large problems, else 128.
+// B200DNN_TC_PAIR: -1 (default) by size, 0 never, 1 whenever the shape allows.
+int tc_tile_rows(long long rows, int N) {
+  const int mode = env_int("B200DNN_TC_PAIR", -1);
+  if (mode == 0 || N < 128) return kTcBM;
+  if (mode == 1) return 2 * kTcBM;
+  // worth it once every CTA pair has several tiles: the pair form wastes up to 255 rows at the end of a group
+  const long long tiles = ((rows + 255) / 256) * ((N + 255) / 256);
+  return tiles >= 2LL * (rt().sm_count / 2) ? 2 * kTcBM : kTcBM;
+}
+
 // Plain or grouped tcgen05 GEMM.  A: [M_total, lda] device, 16-byte aligned rows.
 int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, int N, int K, const PackedWeight &pw0,
                   TcGemmArgs args, const EpiParams &epi, int m_tiles_hint, cudaStream_t st) {
@@ -439,11 +467,13 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
 #else
   args.dbg = 0;
 #endif
-  args.BN = pick_bn(m_tiles_hint, N, R.sm_count, pw0.gated);
+  args.BN = pick_bn(m_tiles_hint, N, R.sm_count, pw0.gated, args.pair);
   args.k_splits = 1;
-  if (args.n_groups <= 1 && !args.maps_b && !args.groups && !args.tile_prefix && !pw0.gated) pick_split(m_tiles_hint, N, args.k_blocks, &args.BN, &args.k_splits);
+  if (!args.pair && args.n_groups <= 1 && !args.maps_b && !args.groups && !args.tile_prefix && !pw0.gated) pick_split(m_tiles_hint, N, args.k_blocks, &args.BN, &args.k_splits);
   B2_CHECK(args.BN % 32 == 0 && args.BN >= 32 && args.BN <= 256 && (!pw0.gated || args.BN % 64 == 0), B200DNN_FAILURE,
            "bad tile width %d", args.BN);
+  B2_CHECK(!args.pair || (args.BN % 32 == 0 && args.BN >= 64 && (!pw0.gated || args.BN % 128 == 0)), B200DNN_FAILURE,
+           "bad tile width %d for the pair form", args.BN);
   args.n_tiles = (N + args.BN - 1) / args.BN;
   // Tile order.  Sweeping the row tiles under one column tile keeps that weight slice hot and re-reads the
   // activations once per column tile.  When the weight of a group is small enough to stay in L2 and the
@@ -453,13 +483,13 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
     const long long w_bytes = (long long)pw0.Kp * pw0.Np, a_bytes = (long long)M_total * K;
     args.n_fastest = env_int("B200DNN_TC_ORDER", (w_bytes <= (32ll << 20) && a_bytes > w_bytes) ? 1 : 0);
   }
-  const int stage_bytes = kTcBM * kTcBK + args.BN * kTcBK;
+  const int stage_bytes = kTcBM * kTcBK + (args.pair ? args.BN / 2 : args.BN) * kTcBK;   // per CTA
   int stages = kTcSmemBudget / stage_bytes;
   if (stages > 8) stages = 8;
   int forced_stages = env_int("B200DNN_TC_STAGES", 0);
   if (forced_stages > 0 && forced_stages <= stages) stages = forced_stages;
   args.stages = stages;
-  B2_TRY(make_map_wt(&map_b, pw0.wt, (uint64_t)pw0.Kp, (uint64_t)pw0.Np, (uint32_t)args.BN));
+  B2_TRY(make_map_wt(&map_b, pw0.wt, (uint64_t)pw0.Kp, (uint64_t)pw0.Np, (uint32_t)(args.pair ? args.BN / 2 : args.BN)));
   const size_t smem = (size_t)stages * stage_bytes + 1024;
   B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<false>, kTcSmemBudget + 1024));   // the kernel also has static shared memory
   long long tiles = (long long)m_tiles_hint * args.n_tiles;
@@ -491,7 +521,17 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
       attr[na].val.programmaticStreamSerializationAllowed = 1;
       ++na;
     }
-    if (args.k_splits > 1) {
+    if (args.pair) {
+      // clusters of two CTAs, one [256 x BN] tile at a time per cluster, persistent over the tiles
+      B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<false, true>, kTcSmemBudget + 1024));
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = 2; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1;
+      ++na;
+      const long long pairs = tiles < R.sm_count / 2 ? (tiles > 0 ? tiles : 1) : R.sm_count / 2;
+      cfg.gridDim = dim3((unsigned)(2 * pairs));
+      cfg.attrs = attr; cfg.numAttrs = na;
+      B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<false, true>, map_a, map_b, map_c, args, epi));
+    } else if (args.k_splits > 1) {
       // one cluster of k_splits CTAs per tile; the partial sums need BN * 512 bytes of the stage ring
       B2_CHECK((size_t)args.BN * 512 <= (size_t)stages * stage_bytes, B200DNN_FAILURE, "split form: stage ring smaller than the partial sums");
       B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<true>, kTcSmemBudget + 1024));
@@ -927,7 +967,9 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
     B2_TRY(rc);
   } else {
     TcGemmArgs ta{};
-    ta.n_groups = 1; ta.m_tiles_plain = (M + kTcBM - 1) / kTcBM; ta.shared_dst = 1;
+    const int tile_rows = tc_tile_rows(M, N);
+    ta.pair = tile_rows > kTcBM ? 1 : 0;
+    ta.n_groups = 1; ta.m_tiles_plain = (M + tile_rows - 1) / tile_rows; ta.shared_dst = 1;
     B2_TRY(launch_tc(A, lda, a_unsigned, M, N, K, pw, ta, epi, ta.m_tiles_plain, st));
   }
   return finish_out({&o_dst, &o_scale}, st);   // calls that synchronise read the status word there
@@ -946,17 +988,23 @@ int32_t b200dnn_phase_timing(void *stream, int32_t enable) {
   return B200DNN_SUCCESS;
 }
 
-int32_t b200dnn_phase_times(void *stream, float *ms, int32_t n) {
+int32_t b200dnn_phase_times(void *stream, float *ms, int32_t n, int32_t *calls) {
   B2_ENTER(stream);
   B2_CHECK(ms && n > 0, B200DNN_FAILURE, "bad argument");
   B2_CUDA(cudaStreamSynchronize(st));
   Runtime &R = rt();
   for (int i = 0; i < n; ++i) ms[i] = 0.f;
-  for (size_t i = 1; i < R.n_tev; ++i) {
+  int n_calls = 0;
+  for (size_t i = 0; i < R.n_tev; ++i) {
+    if (R.tphase[i] < 0) { ++n_calls; continue; }      // a call starts here
+    if (i == 0) continue;
     float t = 0.f;
     B2_CUDA(cudaEventElapsedTime(&t, R.tev[i - 1], R.tev[i]));
-    if (R.tphase[i] >= 0 && R.tphase[i] < n) ms[R.tphase[i]] += t;
+    if (R.tphase[i] < n) ms[R.tphase[i]] += t;
   }
+  if (n_calls > 0) for (int i = 0; i < n; ++i) ms[i] /= (float)n_calls;
+  if (calls) *calls = n_calls;
+  R.n_tev = 0;
   return B200DNN_SUCCESS;
 }
 

@@ -14,30 +14,31 @@
 
 namespace {
 
-__global__ void tile_prefix_kernel(const int32_t *row_off, int n_groups, int32_t *tile_prefix) {
+__global__ void tile_prefix_kernel(const int32_t *row_off, int n_groups, int32_t *tile_prefix, int tile_rows) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     int acc = 0;
-    for (int g = 0; g < n_groups; ++g) { tile_prefix[g] = acc; acc += (row_off[g + 1] - row_off[g] + kTcBM - 1) / kTcBM; }
+    for (int g = 0; g < n_groups; ++g) { tile_prefix[g] = acc; acc += (row_off[g + 1] - row_off[g] + tile_rows - 1) / tile_rows; }
     tile_prefix[n_groups] = acc;
   }
 }
 
 int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const std::vector<PackedWeight> &pws,
                      const int32_t *row_off_dev, const int32_t *tile_prefix_dev, const TcGroupDesc *groups_dev,
-                     int m_tiles_bound, EpiParams epi, bool shared_dst, cudaStream_t st) {
+                     int m_tiles_bound, EpiParams epi, bool shared_dst, cudaStream_t st, int tile_rows = kTcBM) {
   Runtime &Rt = rt();
   const int G = (int)pws.size();
   TcGemmArgs ta{};
+  ta.pair = tile_rows > kTcBM ? 1 : 0;  // tile_prefix_dev and m_tiles_bound count tiles of tile_rows rows
   ta.shared_dst = shared_dst ? 1 : 0;   // no group carries its own destination
   ta.n_groups = G; ta.row_off = row_off_dev; ta.tile_prefix = tile_prefix_dev; ta.groups = groups_dev;
   // one tensor map per expert, in device memory
   const PackedWeight &p0 = pws[0];
-  const int BN = pick_bn(m_tiles_bound, N, Rt.sm_count, p0.gated);
+  const int BN = pick_bn(m_tiles_bound, N, Rt.sm_count, p0.gated, ta.pair);
   std::vector<CUtensorMap> maps(G);
   for (int g = 0; g < G; ++g) {
     B2_CHECK(pws[g].Kp == p0.Kp && pws[g].Np == p0.Np && pws[g].gated == p0.gated, B200DNN_UNIMPLEMENTED,
              "experts of one grouped GEMM must share K and N");
-    B2_TRY(make_map_wt(&maps[g], pws[g].wt, (uint64_t)p0.Kp, (uint64_t)p0.Np, (uint32_t)BN));
+    B2_TRY(make_map_wt(&maps[g], pws[g].wt, (uint64_t)p0.Kp, (uint64_t)p0.Np, (uint32_t)(ta.pair ? BN / 2 : BN)));
   }
   void *maps_dev = nullptr;
   B2_TRY(cached_blob(maps.data(), sizeof(CUtensorMap) * G, st, &maps_dev));
@@ -54,7 +55,7 @@ struct ExpertWeightsIn {
 int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, int H, int transB, int act, int weights_const,
                  RowQuantArgs qa, int32_t src_dt, int R, const int32_t *row_off_dev, const int32_t *tile_prefix_dev,
                  int m_tiles_bound, const std::vector<void *> *dst_down_dev, const std::vector<int64_t> *ldc_down,
-                 void **O_out, int64_t *ldO_out, cudaStream_t st, void *O_given = nullptr) {
+                 void **O_out, int64_t *ldO_out, cudaStream_t st, void *O_given = nullptr, int tile_rows = kTcBM) {
   Runtime &Rt = rt();
   B2_CHECK(act >= 1 && act <= 3, B200DNN_UNIMPLEMENTED, "fused MoE needs a gated activation (got %d)", act);
   B2_CHECK(I % kGateGranule == 0, B200DNN_UNIMPLEMENTED, "expert FFN width must be a multiple of %d", kGateGranule);
@@ -105,7 +106,7 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
   e1.wei_scale_dt = B200DNN_F32; e1.wei_scale_n = 2 * I;
   e1.dst = Z; e1.ldc = I; e1.dst_dt = B200DNN_BF16; e1.gated_act = act; e1.gated_I = I; e1.row_absmax = zmax;
   B2_TRY(grouped_gemm(A1_in, lda1, R, 2 * I, K, p13, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g13_dev,
-                      m_tiles_bound, e1, true, st));
+                      m_tiles_bound, e1, true, st, tile_rows));
   rt().mark(4);
 
   // 3. re-quantise the activated rows (from their bf16 values, as the reference does)
@@ -123,7 +124,7 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
   e2.wei_scale_dt = B200DNN_F32; e2.wei_scale_n = H;
   e2.dst = O; e2.ldc = H; e2.dst_dt = B200DNN_BF16;
   B2_TRY(grouped_gemm((const uint8_t *)A2, Iq, R, H, I, p2, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g2_dev,
-                      m_tiles_bound, e2, dst_down_dev == nullptr, st));
+                      m_tiles_bound, e2, dst_down_dev == nullptr, st, tile_rows));
   rt().mark(6);
   if (O_out) { *O_out = O; *ldO_out = H; }
   return B200DNN_SUCCESS;
@@ -139,10 +140,13 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
   Runtime &Rt = rt();
   B2_CHECK(G > 0 && ex && K > 0 && I > 0 && H > 0, B200DNN_FAILURE, "bad argument");
   std::vector<int32_t> row_off(G + 1, 0), tile_prefix(G + 1, 0);
+  long long rows_all = 0;
+  for (int g = 0; g < G; ++g) rows_all += ex[g].M > 0 ? ex[g].M : 0;
+  const int tile_rows = tc_tile_rows(rows_all, H < 2 * I ? H : 2 * I);
   for (int g = 0; g < G; ++g) {
     B2_CHECK(ex[g].M >= 0, B200DNN_FAILURE, "expert %d: negative M", g);
     row_off[g + 1] = row_off[g] + ex[g].M;
-    tile_prefix[g + 1] = tile_prefix[g] + (ex[g].M + kTcBM - 1) / kTcBM;
+    tile_prefix[g + 1] = tile_prefix[g] + (ex[g].M + tile_rows - 1) / tile_rows;
     if (ex[g].M > 0) {
       B2_CHECK(ex[g].src && ex[g].dst_down, B200DNN_FAILURE, "expert %d: null src or dst_down", g);
       B2_CHECK(ex[g].lda >= K && ex[g].ldc_down >= H, B200DNN_FAILURE, "expert %d: leading dimension too small", g);
@@ -192,7 +196,7 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
   qa.src = X; qa.src_ld = K;
 
   B2_TRY(moe_core(G, ew, K, I, H, transB, act, weights_const, qa, B200DNN_BF16, R, row_off_dev, tile_prefix_dev,
-                  tile_prefix[G], &dst_dev, &ldc_down, nullptr, nullptr, st));
+                  tile_prefix[G], &dst_dev, &ldc_down, nullptr, nullptr, st, nullptr, tile_rows));
 
   Staged o_out; o_out.copy_back = false;
   if (row_ptrs) {
@@ -263,7 +267,8 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   B2_TRY(launch_expert_rank(ids, T * topk, E, rank, cnt, st));
   expert_offsets_kernel<<<1, 32, 0, st>>>(cnt, E, S, T, row_off);
   B2_LAUNCHED();
-  tile_prefix_kernel<<<1, 32, 0, st>>>(row_off, G, tile_prefix);
+  const int tile_rows = tc_tile_rows(R, H < 2 * I ? H : 2 * I);
+  tile_prefix_kernel<<<1, 32, 0, st>>>(row_off, G, tile_prefix, tile_rows);
   B2_LAUNCHED();
   build_maps_kernel<<<(unsigned)((R + 255) / 256), 256, 0, st>>>(ids, rank, w, row_off, T, topk, E, S, slot_rows, slot_w, row_token);
   B2_LAUNCHED();
@@ -278,8 +283,9 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   if (ns <= 32) { qa.scatter = slot_rows; qa.scatter_n = ns; qa.scatter_rows = T; }
   else qa.gather = row_token;
   void *O = nullptr; int64_t ldO = 0;
-  const int m_tiles_bound = (R + kTcBM - 1) / kTcBM + G;
-  B2_TRY(moe_core(G, ew, K, I, H, transB, act, 1, qa, B200DNN_BF16, R, row_off, tile_prefix, m_tiles_bound, nullptr, nullptr, &O, &ldO, st));
+  const int m_tiles_bound = (R + tile_rows - 1) / tile_rows + G;
+  B2_TRY(moe_core(G, ew, K, I, H, transB, act, 1, qa, B200DNN_BF16, R, row_off, tile_prefix, m_tiles_bound, nullptr, nullptr, &O, &ldO, st,
+                  nullptr, tile_rows));
 
   Staged o_out;
   B2_TRY(stage_out(out, span_bytes(T, H, ld_out, B200DNN_BF16), st, &o_out, ld_out != H));
@@ -366,10 +372,13 @@ extern "C" int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, cons
   B2_CHECK(ld_out == H, B200DNN_UNIMPLEMENTED, "output rows must be dense (ld_out == H)");
   std::vector<int32_t> row_off(n_groups + 1, 0), tile_prefix(n_groups + 1, 0);
   std::vector<ExpertWeightsIn> ew(n_groups);
+  long long rows_all = 0;
+  for (int g = 0; g < n_groups; ++g) rows_all += group_rows[g] > 0 ? group_rows[g] : 0;
+  const int tile_rows = tc_tile_rows(rows_all, H < 2 * I ? H : 2 * I);
   for (int g = 0; g < n_groups; ++g) {
     B2_CHECK(group_rows[g] >= 0 && group_expert[g] >= 0, B200DNN_FAILURE, "group %d: negative row count or expert id", g);
     row_off[g + 1] = row_off[g] + group_rows[g];
-    tile_prefix[g + 1] = tile_prefix[g] + (group_rows[g] + kTcBM - 1) / kTcBM;
+    tile_prefix[g + 1] = tile_prefix[g] + (group_rows[g] + tile_rows - 1) / tile_rows;
     const b200dnn_moe_expert_t &e = experts[group_expert[g]];
     ew[g] = ExpertWeightsIn{e.w13, e.ldb13, e.w13_scale, e.w2, e.ldb2, e.w2_scale};
   }
@@ -386,7 +395,7 @@ extern "C" int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, cons
   void *O = nullptr; int64_t ldO = 0;
   // the second GEMM writes the caller's dense rows directly
   return moe_core(n_groups, ew, K, I, H, transB, act, 1, qa, B200DNN_S8, R, row_off_dev, tile_prefix_dev, tile_prefix[n_groups],
-                  nullptr, nullptr, &O, &ldO, st, out);
+                  nullptr, nullptr, &O, &ldO, st, out, tile_rows);
 }
 
 extern "C" int32_t b200dnn_moe_weighted_reduce_rows(const void *rows, int64_t ld_rows, const int32_t *slot_rows,

@@ -94,7 +94,7 @@ __global__ void ep_set_int_kernel(int32_t *p, int32_t v) { if (threadIdx.x == 0 
 // dst_base[e]: row, inside the receive buffer of expert e's owner, of this rank's first row for e.
 // This rank's groups (shared experts, then its routed experts in ascending id): row_off, tile_prefix, n_rows.
 __global__ void __launch_bounds__(256) ep_offsets_kernel(const int32_t *all_counts, const int32_t *expert_rank, int world, int me, int E, int S,
-                                                         int cap_total, int32_t *dst_base, int32_t *row_off, int32_t *tile_prefix,
+                                                         int cap_total, int tile_rows, int32_t *dst_base, int32_t *row_off, int32_t *tile_prefix,
                                                          int32_t *n_rows, int32_t *rank_rows, int32_t *status) {
   __shared__ int tot[256], before_me[256];
   const int stride = E + 1;
@@ -109,11 +109,11 @@ __global__ void __launch_bounds__(256) ep_offsets_kernel(const int32_t *all_coun
     for (int d = 0; d < world; ++d) run[d] = S * all_counts[d * stride + E];
     const int t_me = all_counts[me * stride + E];
     int g = 0, acc = 0, tiles = 0;
-    for (int s = 0; s < S; ++s) { row_off[g] = acc; tile_prefix[g] = tiles; acc += t_me; tiles += (t_me + kTcBM - 1) / kTcBM; ++g; }
+    for (int s = 0; s < S; ++s) { row_off[g] = acc; tile_prefix[g] = tiles; acc += t_me; tiles += (t_me + tile_rows - 1) / tile_rows; ++g; }
     for (int e = 0; e < E; ++e) {
       const int d = expert_rank[e];
       dst_base[e] = run[d] + before_me[e];
-      if (d == me) { row_off[g] = acc; tile_prefix[g] = tiles; acc += tot[e]; tiles += (tot[e] + kTcBM - 1) / kTcBM; ++g; }
+      if (d == me) { row_off[g] = acc; tile_prefix[g] = tiles; acc += tot[e]; tiles += (tot[e] + tile_rows - 1) / tile_rows; ++g; }
       run[d] += tot[e];
     }
     row_off[g] = acc; tile_prefix[g] = tiles;
@@ -142,6 +142,13 @@ __global__ void ep_slot_maps_kernel(const int32_t *ids, const int32_t *rank, con
   } else { slot_rows[i] = (j - topk) * T + t; slot_peer[i] = me; slot_w[i] = 1.0f; }
 }
 
+// Row tile of this rank's grouped GEMMs, from what a balanced routing would give it (the real row count is known only
+// on the device); the offsets kernel and the GEMM launches must agree on it.
+int ep_tile_rows(const EpCtx &c, int T) {
+  const b200dnn_ep_config_t &f = c.cfg;
+  return tc_tile_rows((long long)T * (f.num_shared + f.topk), f.H < 2 * f.I ? f.H : 2 * f.I);
+}
+
 // ---- the phases of one layer on one rank (see the head of this file)
 int32_t ep_phase_route(EpCtx &c, const void *x_dev, const float *logits_dev, int T, cudaStream_t st) {
   const b200dnn_ep_config_t &f = c.cfg;
@@ -161,7 +168,7 @@ int32_t ep_phase_route(EpCtx &c, const void *x_dev, const float *logits_dev, int
 int32_t ep_phase_dispatch(EpCtx &c, const void *x_dev, int64_t ldx, int T, cudaStream_t st) {
   const b200dnn_ep_config_t &f = c.cfg;
   const int E = f.num_experts, S = f.num_shared, ns = f.topk + S;
-  ep_offsets_kernel<<<1, 256, 0, st>>>(c.all_counts, c.expert_rank_dev, f.world, f.rank, E, S, (int)c.cap_total, c.dst_base, c.row_off,
+  ep_offsets_kernel<<<1, 256, 0, st>>>(c.all_counts, c.expert_rank_dev, f.world, f.rank, E, S, (int)c.cap_total, ep_tile_rows(c, T), c.dst_base, c.row_off,
                                        c.tile_prefix, c.n_rows, c.rank_rows, rt().status);
   B2_LAUNCHED();
   if (T > 0) {
@@ -202,7 +209,8 @@ int32_t ep_phase_experts(EpCtx &c, int T, cudaStream_t st) {
   const int R = (int)c.cap_total;
   // what a balanced routing would give this rank; only shapes the tile width and the grid, the tiles come from the device tables
   const int64_t expect = (int64_t)T * (f.num_shared + f.topk);
-  const int m_tiles_hint = (int)((expect + kTcBM - 1) / kTcBM) + G;
+  const int tile_rows = ep_tile_rows(c, T);
+  const int m_tiles_hint = (int)((expect + tile_rows - 1) / tile_rows) + G;
   B2_CUDA(cudaMemsetAsync(c.zmax, 0, (size_t)R * 4, st));
   const uint8_t *A1 = c.xbuf + c.off_q;
   const float *s1 = reinterpret_cast<const float *>(c.xbuf + c.off_scale);
@@ -210,7 +218,7 @@ int32_t ep_phase_experts(EpCtx &c, int T, cudaStream_t st) {
   e1.src_scale = s1; e1.src_scale_dt = B200DNN_F32; e1.src_scale_n = R > 1 ? R : 2;
   e1.wei_scale_dt = B200DNN_F32; e1.wei_scale_n = 2 * I;
   e1.dst = c.Z; e1.ldc = I; e1.dst_dt = B200DNN_BF16; e1.gated_act = f.act; e1.gated_I = I; e1.row_absmax = c.zmax;
-  B2_TRY(grouped_gemm(A1, c.Kq, R, 2 * I, K, p13, c.row_off, c.tile_prefix, (const TcGroupDesc *)g13_dev, m_tiles_hint, e1, true, st));
+  B2_TRY(grouped_gemm(A1, c.Kq, R, 2 * I, K, p13, c.row_off, c.tile_prefix, (const TcGroupDesc *)g13_dev, m_tiles_hint, e1, true, st, tile_rows));
   rt().mark(4);
   RowQuantArgs q2{};
   q2.src = c.Z; q2.src_ld = I; q2.dst = c.A2; q2.dst_ld = c.Iq; q2.scale = c.s2; q2.scale_dt = B200DNN_F32; q2.K = I;
@@ -222,7 +230,7 @@ int32_t ep_phase_experts(EpCtx &c, int T, cudaStream_t st) {
   e2.wei_scale_dt = B200DNN_F32; e2.wei_scale_n = H;
   e2.dst = c.xbuf + c.off_o; e2.ldc = H; e2.dst_dt = B200DNN_BF16;
   B2_TRY(grouped_gemm((const uint8_t *)c.A2, c.Iq, R, H, I, p2, c.row_off, c.tile_prefix, (const TcGroupDesc *)g2_dev,
-                      m_tiles_hint, e2, true, st));
+                      m_tiles_hint, e2, true, st, tile_rows));
   rt().mark(6);
   return B200DNN_SUCCESS;
 }

@@ -90,15 +90,17 @@ __device__ __forceinline__ float block_max(float v, float *sh) {
 // One CTA per row.  T = uint16_t (bf16 bits) or float; NV = 16-byte vectors of the row that a thread keeps in registers
 // between the two passes (2 for rows up to 512 vectors: few registers, six CTAs per SM; 8 for long rows, with the
 // register budget of four or five CTAs per SM: left to its own choice the compiler took 32 registers and spilled the cache).
-template <typename T, int NV>
-__global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (sizeof(T) == 2 ? 5 : 4) : 6) quant_per_token_kernel(RowQuantArgs a) {
+// EP: the expert-parallel forms (row count known only on the device: the CTAs stride over the rows; scatter into other
+// GPUs' receive buffers).  They are a separate instantiation so that the plain form keeps its register budget.
+template <typename T, int NV, bool EP>
+__global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (EP ? 4 : (sizeof(T) == 2 ? 5 : 4)) : 6) quant_per_token_kernel(RowQuantArgs a) {
   __shared__ float sh[kQuantThreads / 32];
   constexpr int E = VecTraits<T>::kPer16B;
   // a GEMM launched as a programmatic dependent may start its set-up while this grid drains (it waits for the whole
   // grid before it reads anything)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int row_limit = a.n_rows_dev ? *a.n_rows_dev : (int)gridDim.x;
-  for (int r = blockIdx.x; r < row_limit; r += gridDim.x) {
+  const int row_limit = (EP && a.n_rows_dev) ? *a.n_rows_dev : (int)gridDim.x;
+  for (int r = blockIdx.x; r < row_limit; r += EP ? (int)gridDim.x : row_limit) {
   const T *src; int8_t *dst; void *scale_out; int64_t scale_idx;
   if (a.n_groups > 0) {
     int g = 0;
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (sizeof(T) == 2 ? 5 : 
     scale_out = a.scale; scale_idx = r;
   }
   const int32_t *sc = (a.scatter && a.n_groups == 0) ? a.scatter + (int64_t)r * a.scatter_n : nullptr;
-  const int32_t *sp = (sc && a.scatter_peer) ? a.scatter_peer + (int64_t)r * a.scatter_n : nullptr;
+  const int32_t *sp = (EP && sc && a.scatter_peer) ? a.scatter_peer + (int64_t)r * a.scatter_n : nullptr;
   if (sc) dst = sp ? a.peer_dst[0] : a.dst;     // row offsets (and the peer's base) are applied per destination
   const int K = a.K;
   const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (K % E == 0) &&
@@ -204,18 +206,18 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (sizeof(T) == 2 ? 5 : 
 // One warp per row, for short rows (K <= 32 * NV * elements-per-16-bytes): the row lives in the
 // lanes' registers, the abs-max is a shuffle reduction, no shared memory and no CTA barrier.
 // Requires 16-byte aligned rows and K a multiple of the vector width (the launcher checks).
-template <typename T, int NV>
+template <typename T, int NV, bool EP>
 __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs a, int rows) {
   constexpr int E = VecTraits<T>::kPer16B;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
-  const int row_limit = a.n_rows_dev ? min(rows, *a.n_rows_dev) : rows;
-  for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < row_limit; r += gridDim.x * 8) {
+  const int row_limit = (EP && a.n_rows_dev) ? min(rows, *a.n_rows_dev) : rows;
+  for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < row_limit; r += EP ? (int)gridDim.x * 8 : row_limit) {
   int64_t sr = r;
   if (a.gather) { int32_t s = a.gather[r]; if (s < 0) continue; sr = s / a.gather_div; }
   const T *src = reinterpret_cast<const T *>(a.src) + sr * a.src_ld;
   const int32_t *sc = a.scatter ? a.scatter + (int64_t)r * a.scatter_n : nullptr;
-  const int32_t *sp = (sc && a.scatter_peer) ? a.scatter_peer + (int64_t)r * a.scatter_n : nullptr;
+  const int32_t *sp = (EP && sc && a.scatter_peer) ? a.scatter_peer + (int64_t)r * a.scatter_n : nullptr;
   int8_t *dst = sp ? a.peer_dst[0] : (a.dst ? (sc ? a.dst : a.dst + (int64_t)r * a.dst_ld) : nullptr);
   const int nvec = a.K / E;
   uint4 cache[NV];

@@ -53,6 +53,15 @@ inline bool is_device_ptr(const void *p) {
   return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
 }
 
+// Allocations made while the calling thread captures a stream into a CUDA graph (a first call on a new stream, a
+// workspace that has to grow): the capture mode is relaxed for the duration of the allocation, which is not part of
+// the captured work.
+struct RelaxedCapture {
+  cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+  RelaxedCapture() { if (cudaThreadExchangeStreamCaptureMode(&mode) != cudaSuccess) cudaGetLastError(); }
+  ~RelaxedCapture() { if (cudaThreadExchangeStreamCaptureMode(&mode) != cudaSuccess) cudaGetLastError(); }
+};
+
 // ---- workspace: bump allocator over device blocks, rewound at the start of every API call -------
 struct Workspace {
   struct Block { uint8_t *p; size_t cap, used; };
@@ -65,6 +74,7 @@ struct Workspace {
       if (b.cap - b.used >= bytes) { void *r = b.p + b.used; b.used += bytes; return r; }
     size_t cap = bytes > (size_t(64) << 20) ? bytes : (size_t(64) << 20);
     void *p = nullptr;
+    RelaxedCapture relaxed;
     if (cudaMalloc(&p, cap) != cudaSuccess) { cudaGetLastError(); return nullptr; }
     blocks.push_back({(uint8_t *)p, cap, bytes});
     return p;
@@ -170,8 +180,7 @@ struct Runtime {
   std::vector<cudaEvent_t> tev; std::vector<int> tphase; size_t n_tev = 0;
   // mark(p): phase p ends here; mark(-1): a timed call starts
   void mark(int phase) {
-    if (!timing) return;
-    if (phase < 0) n_tev = 0;
+    if (!timing || n_tev >= 65536) return;     // every call since timing was switched on keeps its own events
     if (n_tev == tev.size()) {
       cudaEvent_t e = nullptr;
       if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return; }
@@ -185,8 +194,17 @@ struct Runtime {
   int32_t init(DeviceShared *sh, cudaStream_t st) {
     shared = sh; stream = st; encode = sh->encode; sm_count = sh->sm_count;
     n_counters = 1 << 16;
+    RelaxedCapture relaxed;     // the first call on a stream may come while that stream is being captured
     B2_CUDA(cudaMalloc(&counters, n_counters * sizeof(uint32_t)));
-    B2_CUDA(cudaMemset(counters, 0, n_counters * sizeof(uint32_t)));
+    {
+      // zeroed on a stream of its own: the legacy default stream must not be touched during a capture
+      cudaStream_t tmp = nullptr;
+      B2_CUDA(cudaStreamCreateWithFlags(&tmp, cudaStreamNonBlocking));
+      cudaError_t e = cudaMemsetAsync(counters, 0, n_counters * sizeof(uint32_t), tmp);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(tmp);
+      cudaStreamDestroy(tmp);
+      B2_CUDA(e);
+    }
     void *h = nullptr, *d = nullptr;
     B2_CUDA(cudaHostAlloc(&h, 256, cudaHostAllocMapped));
     memset(h, 0, 256);
@@ -309,7 +327,10 @@ inline int32_t cached_blob(const void *host, size_t bytes, cudaStream_t st, void
     R.blobs.release();
   }
   void *d = nullptr;
-  B2_CUDA(cudaMalloc(&d, bytes ? bytes : 16));
+  {
+    RelaxedCapture relaxed;
+    B2_CUDA(cudaMalloc(&d, bytes ? bytes : 16));
+  }
   B2_CUDA(cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, st));
   B2_CUDA(cudaStreamSynchronize(st));
   BlobCache::Entry e; e.bytes.assign((const uint8_t *)host, (const uint8_t *)host + bytes); e.dev = d;

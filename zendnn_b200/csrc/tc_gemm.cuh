@@ -26,6 +26,13 @@
 // the epilogue keeps its own shared-memory traffic small.
 // Grouped form: A is one [rows x K] matrix holding every expert's rows back to back; row offsets
 // and the cumulative tile counts live in device memory, so no host round trip is needed after routing.
+// Pair form (tc_gemm_kernel<false, true>, large plain and grouped GEMMs): clusters of two CTAs on neighbouring SMs
+// work on one [256 x BN] tile with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and its own half
+// (BN/2 rows) of the weight tile with plain, non-multicast TMA copies that complete on the leader CTA's barrier; the
+// leader's MMA warp issues M256 MMAs for both, the tensor cores exchange the weight halves between the two shared
+// memories themselves, and each CTA's epilogue warps finish the 128 rows whose accumulators sit in its own tensor
+// memory.  Per MMA a CTA's shared memory takes half the weight bytes it takes in the single-CTA form, and shared-memory
+// bandwidth (copy engine writing, tensor core reading) is what bounds the single-CTA form.
 // Every wait is bounded: on expiry the kernel records a code in *status and leaves.
 #pragma once
 #include <cuda.h>
@@ -60,9 +67,9 @@ struct TcGemmArgs {
   int k_blocks;               // Kp / 128
   int BN, stages;
   int n_tiles;                // ceil(N / BN)
-  int m_tiles_plain;          // plain form: ceil(M / 128)
+  int m_tiles_plain;          // plain form: ceil(M / 128), or ceil(M / 256) in the pair form
   const int32_t *row_off;     // grouped: [n_groups+1] first row of each group (device)
-  const int32_t *tile_prefix; // grouped: [n_groups+1] cumulative 128-row tiles (device)
+  const int32_t *tile_prefix; // grouped: [n_groups+1] cumulative row tiles (128 rows each; 256 in the pair form) (device)
   const CUtensorMap *maps_b;  // grouped: one map per group (device memory); plain: null
   const TcGroupDesc *groups;  // grouped, optional: per-group epilogue pointers (local row index)
   int a_unsigned;
@@ -77,6 +84,7 @@ struct TcGemmArgs {
   int k_splits;               // split form (tc_gemm_kernel<true>): the CTAs of a cluster each take a share of the K blocks of one
                               // tile and add their int32 partial sums through distributed shared memory (exact in any order)
   int n_fastest;              // tile order: 0 = all row tiles of a column tile first, 1 = all column tiles of a row tile first
+  int pair;                   // pair form (tc_gemm_kernel<false, true>): row tiles are 256 rows, m_tiles_plain / tile_prefix count those
   int32_t *status;            // device word: 0 ok
   unsigned long long *stamps; // timing experiments only (builds with B200DNN_TIMING_EXPERIMENTS): 8 timer values per CTA; else null
 };
@@ -98,6 +106,30 @@ __device__ __forceinline__ void tma_load_wt(uint32_t dst, const CUtensorMap *map
   asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
                ::"r"(dst), "l"(map), "r"(0), "r"(0), "r"(kblock), "r"(group), "r"(bar) : "memory");
 }
+// pair form: the copy lands in this CTA's shared memory, its bytes are counted on the barrier `bar` of the leader CTA
+// (a shared::cluster address); no multicast
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_wt_pair(uint32_t dst, const CUtensorMap *map, int kblock, int group, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+               ::"r"(dst), "l"(map), "r"(0), "r"(0), "r"(kblock), "r"(group), "r"(bar) : "memory");
+}
+// completion of the pair's MMAs, signalled on the barrier at the same offset in both CTAs
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}"
+               ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// arrive on a barrier of another CTA of the cluster (shared::cluster address from cluster_map)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -117,6 +149,19 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+// 32 contiguous bytes of one row in one instruction: every lane writes a whole sector of its own row, so the stores of a
+// warp are full sectors without any exchange between the lanes.  The address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void *p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
 }
 __device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 // every thread of every CTA of the cluster; the cluster's CTAs are scheduled together, so the wait ends once each thread
@@ -155,39 +200,23 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 // instruction descriptor, kind::i8: D = s32, A = u8|s8, B = s8, both K-major, M = 128, N = BN
-__host__ __device__ inline uint32_t make_idesc_i8(int a_unsigned, int BN) {
-  return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
+__host__ __device__ inline uint32_t make_idesc_i8(int a_unsigned, int BN, int M = kTcBM) {
+  return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 struct TileCoord { int g, row0, rows, m_local0, nt; };
 
-__device__ __forceinline__ TileCoord tc_tile(const TcGemmArgs &a, int tile, int m_tiles) {
-  TileCoord t;
-  int mt;
-  if (a.n_fastest) { mt = tile / a.n_tiles; t.nt = tile - mt * a.n_tiles; }
-  else { t.nt = tile / m_tiles; mt = tile - t.nt * m_tiles; }
-  if (!a.tile_prefix) {
-    t.g = 0; t.m_local0 = mt * kTcBM; t.row0 = t.m_local0; t.rows = min(kTcBM, a.M_total - t.row0);
-  } else {
-    int g = 0;
-    while (g + 1 < a.n_groups && mt >= a.tile_prefix[g + 1]) ++g;
-    t.g = g;
-    t.m_local0 = (mt - a.tile_prefix[g]) * kTcBM;
-    t.row0 = a.row_off[g] + t.m_local0;
-    t.rows = min(kTcBM, a.row_off[g + 1] - t.row0);
-  }
-  return t;
-}
-
 // Same mapping computed by a whole warp: the group of a row tile is the number of prefix entries
 // tile_prefix[1..n_groups) that are <= the tile index (empty groups repeat a prefix value and are skipped).
-__device__ __forceinline__ TileCoord tc_tile_warp(const TcGemmArgs &a, int tile, int m_tiles, int lane) {
+// tile_m: rows of a tile (128, or 256 in the pair form); sub: this CTA's first row inside the tile (pair form: 128 for
+// the second CTA).  rows may be 0 for the second CTA of a pair at the end of a group.
+__device__ __forceinline__ TileCoord tc_tile_warp(const TcGemmArgs &a, int tile, int m_tiles, int lane, int tile_m = kTcBM, int sub = 0) {
   TileCoord t;
   int mt;
   if (a.n_fastest) { mt = tile / a.n_tiles; t.nt = tile - mt * a.n_tiles; }
   else { t.nt = tile / m_tiles; mt = tile - t.nt * m_tiles; }
   if (!a.tile_prefix) {
-    t.g = 0; t.m_local0 = mt * kTcBM; t.row0 = t.m_local0; t.rows = min(kTcBM, a.M_total - t.row0);
+    t.g = 0; t.m_local0 = mt * tile_m + sub; t.row0 = t.m_local0; t.rows = max(0, min(kTcBM, a.M_total - t.row0));
     return t;
   }
   int g = 0;
@@ -197,9 +226,9 @@ __device__ __forceinline__ TileCoord tc_tile_warp(const TcGemmArgs &a, int tile,
     g += __popc(__ballot_sync(0xffffffffu, le));
   }
   t.g = g;
-  t.m_local0 = (mt - a.tile_prefix[g]) * kTcBM;
+  t.m_local0 = (mt - a.tile_prefix[g]) * tile_m + sub;
   t.row0 = a.row_off[g] + t.m_local0;
-  t.rows = min(kTcBM, a.row_off[g + 1] - t.row0);
+  t.rows = max(0, min(kTcBM, a.row_off[g + 1] - t.row0));
   return t;
 }
 
@@ -297,12 +326,14 @@ struct EpiStore {          // where this warp's rows of the current tile go
   int64_t pitch_bytes;
   int rows_valid;          // rows of the warp's 32 that exist in this tile
   bool coalesce;           // destination 16-byte aligned: use the staged path
+  bool v8;                 // destination and pitch 32-byte aligned: every lane stores 32-byte pieces of its own row directly
   bool row_ok;             // this lane's row exists
   const CUtensorMap *map_c;  // non-null: full blocks go out as TMA stores, coordinates (byte column, row)
   int row_c;               // row coordinate of the warp's first row in map_c
 };
 
-// One 32-column chunk of one output row.
+// One 32-column chunk of one output row.  Results leave, in this order of preference, as 32-byte stores of the lane's own
+// row (destination 32-byte aligned), through the warp's staging block (16-byte aligned), or element by element.
 template <int ACT>
 __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx &cx, const uint32_t (&r)[32], const TileCols &tc,
                                              int c0, int pc0, int N, int m_dst, bool has_bias, const EpiStore &es, int lane) {
@@ -311,7 +342,18 @@ __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx 
     int32_t y[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) y[i] = has_zp ? (int32_t)r[i] - tc.comp[c0 + i] : (int32_t)r[i];
-    if (es.coalesce && pc0 + 32 <= N) {
+    if (es.v8 && pc0 + 32 <= N) {
+      if (es.row_ok) {
+        uint8_t *o = reinterpret_cast<uint8_t *>(cx.dst) + ((int64_t)m_dst * cx.ldc + pc0) * 4;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          uint32_t v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = (uint32_t)y[8 * p + i];
+          st_global_v8(o + 32 * p, v);
+        }
+      }
+    } else if (es.coalesce && pc0 + 32 <= N) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint4 v[4];
@@ -327,59 +369,72 @@ __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx 
     }
     return;
   }
-  float x[32];
+  // two halves of 16 columns: fewer values live at once
 #pragma unroll
-  for (int i = 0; i < 32; i += 4) {
-    // shared memory is the busiest resource of this kernel (the tensor core reads its operands from it):
-    // bias and compensation are fetched only when they exist
-    const float4 w4 = *reinterpret_cast<const float4 *>(&tc.ws[c0 + i]);
-    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    int4 k4 = make_int4(0, 0, 0, 0);
-    if (has_bias) b4 = *reinterpret_cast<const float4 *>(&tc.bias[c0 + i]);
-    if (has_zp) k4 = *reinterpret_cast<const int4 *>(&tc.comp[c0 + i]);
-    const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
-    const int kv[4] = {k4.x, k4.y, k4.z, k4.w};
+  for (int h = 0; h < 2; ++h) {
+    float x[16];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float v = __fmul_rn(__fmul_rn((float)((int32_t)r[i + j] - kv[j]), cx.s_src), wv[j]);
-      if (has_bias) v = __fadd_rn(v, bv[j]);
-      x[i + j] = tc_act<ACT>(epi, v, m_dst, pc0 + i + j);
+    for (int i = 0; i < 16; i += 4) {
+      // shared memory is the busiest resource of this kernel (the tensor core reads its operands from it):
+      // bias and compensation are fetched only when they exist
+      const int ci = c0 + 16 * h + i;
+      const float4 w4 = *reinterpret_cast<const float4 *>(&tc.ws[ci]);
+      float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      int4 k4 = make_int4(0, 0, 0, 0);
+      if (has_bias) b4 = *reinterpret_cast<const float4 *>(&tc.bias[ci]);
+      if (has_zp) k4 = *reinterpret_cast<const int4 *>(&tc.comp[ci]);
+      const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+      const int kv[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float v = __fmul_rn(__fmul_rn((float)((int32_t)r[16 * h + i + j] - kv[j]), cx.s_src), wv[j]);
+        if (has_bias) v = __fadd_rn(v, bv[j]);
+        x[i + j] = tc_act<ACT>(epi, v, m_dst, pc0 + 16 * h + i + j);
+      }
     }
-  }
-  if (epi.dst_dt == DT_BF16) {
-    if (es.coalesce && pc0 + 32 <= N) {
-      uint4 v[4];
+    const int pc = pc0 + 16 * h;          // first column of this half
+    const bool full = pc + 16 <= N;
+    if (epi.dst_dt == DT_BF16) {
+      uint32_t pk[8];
 #pragma unroll
-      for (int p = 0; p < 4; ++p)
-        v[p] = make_uint4(pack_bf16x2(x[8 * p], x[8 * p + 1]), pack_bf16x2(x[8 * p + 2], x[8 * p + 3]),
-                          pack_bf16x2(x[8 * p + 4], x[8 * p + 5]), pack_bf16x2(x[8 * p + 6], x[8 * p + 7]));
-      if (es.map_c && es.rows_valid == 32) {
-        warp_tma_store_rows32(es.sbuf, v[0], v[1], es.map_c, pc0 * 2, es.row_c, lane);
-        warp_tma_store_rows32(es.sbuf, v[2], v[3], es.map_c, pc0 * 2 + 32, es.row_c, lane);
-      } else
-      warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)pc0 * 2, es.pitch_bytes, es.rows_valid, lane);
-    } else if (es.row_ok) {
-      uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+      for (int i = 0; i < 8; ++i) pk[i] = pack_bf16x2(x[2 * i], x[2 * i + 1]);
+      if (es.map_c && es.rows_valid == 32 && full) {
+        warp_tma_store_rows32(es.sbuf, make_uint4(pk[0], pk[1], pk[2], pk[3]), make_uint4(pk[4], pk[5], pk[6], pk[7]), es.map_c, pc * 2, es.row_c, lane);
+      } else if (es.v8 && full) {
+        if (es.row_ok) st_global_v8(reinterpret_cast<uint8_t *>(cx.dst) + ((int64_t)m_dst * cx.ldc + pc) * 2, pk);
+      } else if (es.coalesce && full) {
+        warp_store_rows32(es.sbuf, make_uint4(pk[0], pk[1], pk[2], pk[3]), make_uint4(pk[4], pk[5], pk[6], pk[7]),
+                          es.g_row0 + (size_t)pc * 2, es.pitch_bytes, es.rows_valid, lane);
+      } else if (es.row_ok) {
+        uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (pc0 + i < N) o[i] = f32_to_bf16_bits(x[i]);
-    }
-  } else {
-    if (es.coalesce && pc0 + 32 <= N) {
+        for (int i = 0; i < 16; ++i)
+          if (pc + i < N) o[i] = (uint16_t)(pk[i >> 1] >> ((i & 1) * 16));
+      }
+    } else {
+      if (es.v8 && full) {
+        if (es.row_ok) {
+          uint8_t *o = reinterpret_cast<uint8_t *>(cx.dst) + ((int64_t)m_dst * cx.ldc + pc) * 4;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+          for (int p = 0; p < 2; ++p) {
+            uint32_t v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __float_as_uint(x[8 * p + i]);
+            st_global_v8(o + 32 * p, v);
+          }
+        }
+      } else if (es.coalesce && full) {
         uint4 v[4];
 #pragma unroll
         for (int p = 0; p < 4; ++p)
-          v[p] = make_uint4(__float_as_uint(x[16 * h + 4 * p]), __float_as_uint(x[16 * h + 4 * p + 1]),
-                            __float_as_uint(x[16 * h + 4 * p + 2]), __float_as_uint(x[16 * h + 4 * p + 3]));
-        warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)(pc0 + 16 * h) * 4, es.pitch_bytes, es.rows_valid, lane);
-      }
-    } else if (es.row_ok) {
-      float *o = reinterpret_cast<float *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc0;
+          v[p] = make_uint4(__float_as_uint(x[4 * p]), __float_as_uint(x[4 * p + 1]), __float_as_uint(x[4 * p + 2]), __float_as_uint(x[4 * p + 3]));
+        warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)pc * 4, es.pitch_bytes, es.rows_valid, lane);
+      } else if (es.row_ok) {
+        float *o = reinterpret_cast<float *>(cx.dst) + (int64_t)m_dst * cx.ldc + pc;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (pc0 + i < N) o[i] = x[i];
+        for (int i = 0; i < 16; ++i)
+          if (pc + i < N) o[i] = x[i];
+      }
     }
   }
 }
@@ -400,7 +455,8 @@ __device__ __forceinline__ void tc_epi_dispatch(int fast_act, const EpiParams &e
 }
 
 // SPLIT: launched in clusters of a.k_splits CTAs, one tile per cluster (see TcGemmArgs::k_splits); plain, non-gated form only.
-template <bool SPLIT>
+// PAIR: launched in clusters of two CTAs that share [256 x BN] tiles through cta_group::2 MMAs (see the head of this file).
+template <bool SPLIT, bool PAIR = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                const __grid_constant__ CUtensorMap map_c, const TcGemmArgs a, const EpiParams epi) {
@@ -419,8 +475,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) TC_STAMP(0);
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t a_bytes = kTcBM * kTcBK, b_bytes = (uint32_t)a.BN * kTcBK, stage_bytes = a_bytes + b_bytes;
+  static_assert(!(SPLIT && PAIR), "the split form and the pair form are separate kernels");
+  // pair form: this CTA holds its 128 rows of A and its half of the tile's weight rows
+  const uint32_t a_bytes = kTcBM * kTcBK, b_bytes = (uint32_t)(PAIR ? a.BN / 2 : a.BN) * kTcBK, stage_bytes = a_bytes + b_bytes;
   const int S = a.stages;
+  uint32_t crank = 0;
+  if constexpr (SPLIT || PAIR) crank = cluster_ctarank();
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (8 + s); };
@@ -435,18 +495,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (!a.maps_b) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b0) : "memory");
     if (a.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
     for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), kTcEpiWarps); }
+    // pair form: the epilogue warps of both CTAs release the accumulator on the leader's barrier
+    for (int i = 0; i < 2; ++i) { mbar_init(tfull_bar(i), 1); mbar_init(tempty_bar(i), PAIR ? 2 * kTcEpiWarps : kTcEpiWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(cfull_bar(i), 1); mbar_init(cempty_bar(i), kTcEpiWarps); }
     s_err = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      // the same warp of both CTAs allocates for the pair
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // the partner's barriers exist before anything of this CTA signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   asm volatile("griddepcontrol.wait;" ::: "memory");   // everything before this launch in the stream is complete and visible
@@ -457,9 +525,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // persistent form: tiles blockIdx.x, blockIdx.x + gridDim.x, ... over all K blocks; split form: the cluster's one tile,
   // this CTA's share of the K blocks
   int tile0 = blockIdx.x, tile_step = gridDim.x, kb_begin = 0, kb_end = a.k_blocks;
-  uint32_t crank = 0;
+  constexpr int tile_m = PAIR ? 2 * kTcBM : kTcBM;
+  const int sub = PAIR ? (int)crank * kTcBM : 0;
+  if constexpr (PAIR) { tile0 = blockIdx.x >> 1; tile_step = gridDim.x >> 1; }
   if constexpr (SPLIT) {
-    crank = cluster_ctarank();
     tile0 = blockIdx.x / a.k_splits; tile_step = total_tiles;
     const int per = (a.k_blocks + a.k_splits - 1) / a.k_splits;
     kb_begin = (int)crank * per; kb_end = min(a.k_blocks, kb_begin + per);
@@ -473,23 +542,31 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int tile = tile0; tile < total_tiles && !a.test_no_loads; tile += tile_step) {
       // one decision for the whole warp (the lookup below uses warp-wide operations)
       if (!__shfl_sync(0xffffffffu, (ok && !s_err) ? 1 : 0, 0)) break;
-      const TileCoord t = tc_tile_warp(a, tile, m_tiles, lane);
+      const TileCoord t = tc_tile_warp(a, tile, m_tiles, lane, tile_m, sub);
       if (lane == 0) {
         const CUtensorMap *mb = a.maps_b ? a.maps_b + t.g : &map_b0;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u)) { s_err = 1; report_status(a.status, 1); ok = false; break; }
           const uint32_t sa = smem0 + (uint32_t)stage * stage_bytes;
-          mbar_expect_tx(full_bar(stage), stage_bytes);
-          tma_load_2d(sa, &map_a, kb * kTcBK, t.row0, full_bar(stage));
-          tma_load_wt(sa + a_bytes, mb, kb, (t.nt * a.BN) >> 3, full_bar(stage));
+          if constexpr (PAIR) {
+            // both CTAs' copies are counted on the leader's barrier; the leader expects the bytes of both
+            const uint32_t lead_bar = cluster_map(full_bar(stage), 0);
+            if (crank == 0) mbar_expect_tx(full_bar(stage), 2 * stage_bytes);
+            tma_load_2d_pair(sa, &map_a, kb * kTcBK, t.row0, lead_bar);
+            tma_load_wt_pair(sa + a_bytes, mb, kb, (t.nt * a.BN + (int)crank * (a.BN / 2)) >> 3, lead_bar);
+          } else {
+            mbar_expect_tx(full_bar(stage), stage_bytes);
+            tma_load_2d(sa, &map_a, kb * kTcBK, t.row0, full_bar(stage));
+            tma_load_wt(sa + a_bytes, mb, kb, (t.nt * a.BN) >> 3, full_bar(stage));
+          }
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_i8(a.a_unsigned, a.BN);
+    if (lane == 0 && (!PAIR || crank == 0)) {      // pair form: the leader issues for both CTAs
+      const uint32_t idesc = make_idesc_i8(a.a_unsigned, a.BN, tile_m);
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
       for (int tile = tile0; tile < total_tiles && !s_err; tile += tile_step) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { s_err = 2; report_status(a.status, 2); break; }
@@ -503,13 +580,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t sa = smem0 + (uint32_t)stage * stage_bytes;
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + a_bytes);
 #pragma unroll
-          for (int k = 0; k < kTcBK / 32; ++k)
-            tc_mma_i8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, ((kb - kb_begin) | k) ? 1u : 0u);
-          tc_commit(empty_bar(stage));
+          for (int k = 0; k < kTcBK / 32; ++k) {
+            if constexpr (PAIR) tc_mma_i8_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, ((kb - kb_begin) | k) ? 1u : 0u);
+            else tc_mma_i8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, ((kb - kb_begin) | k) ? 1u : 0u);
+          }
+          if constexpr (PAIR) tc_commit_pair(empty_bar(stage)); else tc_commit(empty_bar(stage));
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
         if (!ok) { s_err = 3; report_status(a.status, 3); break; }
-        tc_commit(tfull_bar(acc));
+        if constexpr (PAIR) tc_commit_pair(tfull_bar(acc)); else tc_commit(tfull_bar(acc));
         if (tile == tile0) TC_STAMP(3);
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
@@ -520,7 +599,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int cb = 0; uint32_t cphase = 0;
     for (int tile = tile0; tile < total_tiles; tile += tile_step) {
       if (!__shfl_sync(0xffffffffu, s_err ? 0 : 1, 0)) break;
-      const TileCoord t = tc_tile_warp(a, tile, m_tiles, lane);
+      const TileCoord t = tc_tile_warp(a, tile, m_tiles, lane, tile_m, sub);
       const void *wsp = epi.wei_scale; const int32_t *csp = epi.colsum; const void *bp = epi.bias;
       void *dst = epi.dst; int64_t ldc = epi.ldc; int m_dst0 = t.row0;
       if (a.groups) {
@@ -594,6 +673,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         es.g_row0 = reinterpret_cast<uint8_t *>(tm.dst) + (int64_t)(tm.m_dst0 + q * 32) * es.pitch_bytes;
         es.rows_valid = min(32, max(0, tm.rows - q * 32));
         es.coalesce = ((reinterpret_cast<uintptr_t>(tm.dst) | (uintptr_t)es.pitch_bytes) & 15) == 0;
+        es.v8 = ((reinterpret_cast<uintptr_t>(tm.dst) | (uintptr_t)es.pitch_bytes) & 31) == 0;
         es.row_ok = row_ok;
         es.map_c = (a.tma_store && es.coalesce) ? &map_c : nullptr;
         es.row_c = tm.m_dst0 + q * 32;
@@ -637,68 +717,78 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_epi_dispatch(a.fast_act, epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane);
         }
       } else {
-        // gated: packed columns [g(32) u(32)] -> 32 outputs; dst is [rows, I] bf16
-        float amax = 0.f;
+        // gated: packed columns [g(32) u(32)] -> 32 outputs; dst is [rows, I] bf16.  Sixteen outputs at a time: their
+        // 32 bytes leave as one store of the lane's own row; the row maximum is taken on the bf16 bit patterns (two per
+        // instruction; magnitudes order like integers, non-finite values do not count)
+        uint32_t amax2 = 0u;
         for (int c = part; c < a.BN / 64; c += kTcEpiParts) {
           const int pc0 = pc_tile + c * 64;
           if (pc0 >= a.N) break;
-          uint32_t rg[32], ru[32];
-          tc_ld32(taddr0 + (uint32_t)(c * 64), rg);
-          tc_ld32(taddr0 + (uint32_t)(c * 64 + 32), ru);
-          tc_wait_ld();
           const int j0 = pc0 / 2;   // first output column of this pair of chunks
-          const int cg = c * 64, cu = c * 64 + 32;
-          uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 wg4 = *reinterpret_cast<const float4 *>(&tcols.ws[cg + i]);
-            const float4 wu4 = *reinterpret_cast<const float4 *>(&tcols.ws[cu + i]);
-            const float wg[4] = {wg4.x, wg4.y, wg4.z, wg4.w}, wu[4] = {wu4.x, wu4.y, wu4.z, wu4.w};
-            float bg[4] = {0.f, 0.f, 0.f, 0.f}, bu[4] = {0.f, 0.f, 0.f, 0.f};
-            if (has_bias) {
-              const float4 bg4 = *reinterpret_cast<const float4 *>(&tcols.bias[cg + i]);
-              const float4 bu4 = *reinterpret_cast<const float4 *>(&tcols.bias[cu + i]);
-              bg[0] = bg4.x; bg[1] = bg4.y; bg[2] = bg4.z; bg[3] = bg4.w;
-              bu[0] = bu4.x; bu[1] = bu4.y; bu[2] = bu4.z; bu[3] = bu4.w;
+          for (int h = 0; h < 2; ++h) {
+            uint32_t rg[16], ru[16];
+            tc_ld16(taddr0 + (uint32_t)(c * 64 + 16 * h), rg);
+            tc_ld16(taddr0 + (uint32_t)(c * 64 + 32 + 16 * h), ru);
+            tc_wait_ld();
+            const int cg = c * 64 + 16 * h, cu = cg + 32;
+            uint32_t pk[8];
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              const float4 wg4 = *reinterpret_cast<const float4 *>(&tcols.ws[cg + i]);
+              const float4 wu4 = *reinterpret_cast<const float4 *>(&tcols.ws[cu + i]);
+              const float wg[4] = {wg4.x, wg4.y, wg4.z, wg4.w}, wu[4] = {wu4.x, wu4.y, wu4.z, wu4.w};
+              float bg[4] = {0.f, 0.f, 0.f, 0.f}, bu[4] = {0.f, 0.f, 0.f, 0.f};
+              if (has_bias) {
+                const float4 bg4 = *reinterpret_cast<const float4 *>(&tcols.bias[cg + i]);
+                const float4 bu4 = *reinterpret_cast<const float4 *>(&tcols.bias[cu + i]);
+                bg[0] = bg4.x; bg[1] = bg4.y; bg[2] = bg4.z; bg[3] = bg4.w;
+                bu[0] = bu4.x; bu[1] = bu4.y; bu[2] = bu4.z; bu[3] = bu4.w;
+              }
+              float z[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float gv = __fmul_rn(__fmul_rn((float)(int32_t)rg[i + j], cx.s_src), wg[j]);
+                float uv = __fmul_rn(__fmul_rn((float)(int32_t)ru[i + j], cx.s_src), wu[j]);
+                if (has_bias) { gv = __fadd_rn(gv, bg[j]); uv = __fadd_rn(uv, bu[j]); }
+                if (epi.gated_act == ACT_SILU_MUL) z[j] = __fmul_rn(fast_sigmoid_mul(gv, gv), uv);
+                else z[j] = gated_f32(epi.gated_act, gv, uv);
+              }
+              pk[i >> 1] = pack_bf16x2(z[0], z[1]);
+              pk[(i >> 1) + 1] = pack_bf16x2(z[2], z[3]);
+#pragma unroll
+              for (int q2 = 0; q2 < 2; ++q2) {
+                uint32_t mag = pk[(i >> 1) + q2] & 0x7FFF7FFFu;
+                mag &= ~__vcmpgeu2(mag, 0x7F807F80u);          // infinities and NaNs do not enter the maximum
+                amax2 = __vmaxu2(amax2, mag);
+              }
             }
-            uint16_t zb[4];
+            const int jc = j0 + 16 * h;
+            if (es.v8) {
+              if (row_ok) st_global_v8(reinterpret_cast<uint8_t *>(cx.dst) + ((int64_t)m_dst * cx.ldc + jc) * 2, pk);
+            } else if (es.coalesce) {
+              warp_store_rows32(es.sbuf, make_uint4(pk[0], pk[1], pk[2], pk[3]), make_uint4(pk[4], pk[5], pk[6], pk[7]),
+                                es.g_row0 + (size_t)jc * 2, es.pitch_bytes, es.rows_valid, lane);
+            } else if (row_ok) {
+              uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + jc;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float gv = __fmul_rn(__fmul_rn((float)(int32_t)rg[i + j], cx.s_src), wg[j]);
-              float uv = __fmul_rn(__fmul_rn((float)(int32_t)ru[i + j], cx.s_src), wu[j]);
-              if (has_bias) { gv = __fadd_rn(gv, bg[j]); uv = __fadd_rn(uv, bu[j]); }
-              float z;
-              if (epi.gated_act == ACT_SILU_MUL) z = __fmul_rn(fast_sigmoid_mul(gv, gv), uv);
-              else z = gated_f32(epi.gated_act, gv, uv);
-              zb[j] = f32_to_bf16_bits(z);
-              const float az = fabsf(bf16_bits_to_f32(zb[j]));
-              if (finite_f32(az)) amax = fmaxf(amax, az);
+              for (int i = 0; i < 16; ++i) o[i] = (uint16_t)(pk[i >> 1] >> ((i & 1) * 16));
             }
-            pk[i >> 1] = (uint32_t)zb[0] | ((uint32_t)zb[1] << 16);
-            pk[(i >> 1) + 1] = (uint32_t)zb[2] | ((uint32_t)zb[3] << 16);
-          }
-          if (es.coalesce) {
-            uint4 v[4];
-#pragma unroll
-            for (int p4 = 0; p4 < 4; ++p4) v[p4] = make_uint4(pk[4 * p4], pk[4 * p4 + 1], pk[4 * p4 + 2], pk[4 * p4 + 3]);
-            if (es.map_c && es.rows_valid == 32) {
-              warp_tma_store_rows32(es.sbuf, v[0], v[1], es.map_c, j0 * 2, es.row_c, lane);
-              warp_tma_store_rows32(es.sbuf, v[2], v[3], es.map_c, j0 * 2 + 32, es.row_c, lane);
-            } else
-            warp_store_rows64(es.sbuf, v, es.g_row0 + (size_t)j0 * 2, es.pitch_bytes, es.rows_valid, lane);
-          } else if (row_ok) {
-            uint16_t *o = reinterpret_cast<uint16_t *>(cx.dst) + (int64_t)m_dst * cx.ldc + j0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = (uint16_t)(pk[i >> 1] >> ((i & 1) * 16));
           }
         }
-        if (row_ok && epi.row_absmax) atomicMax(epi.row_absmax + m_global, __float_as_uint(amax));
+        if (row_ok && epi.row_absmax) {
+          const uint32_t m16 = max(amax2 & 0xFFFFu, amax2 >> 16);
+          atomicMax(epi.row_absmax + m_global, m16 << 16);     // the bf16 magnitude as float bits
+        }
       }
       if (warp == 2 && lane == 0 && tile == tile0) TC_STAMP(5);
       tc_fence_before();
       __syncwarp();
       // this warp is done with the accumulator and with the tile's operand buffer
-      if (lane == 0) { mbar_arrive(tempty_bar(acc)); mbar_arrive(cempty_bar(ob)); }
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(cluster_map(tempty_bar(acc), 0)); else mbar_arrive(tempty_bar(acc));
+        mbar_arrive(cempty_bar(ob));
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       if (++ob == 2) { ob = 0; ophase ^= 1u; }
     }
@@ -727,6 +817,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       es.g_row0 = reinterpret_cast<uint8_t *>(tm.dst) + (int64_t)(tm.m_dst0 + q * 32) * es.pitch_bytes;
       es.rows_valid = min(32, max(0, tm.rows - q * 32));
       es.coalesce = ((reinterpret_cast<uintptr_t>(tm.dst) | (uintptr_t)es.pitch_bytes) & 15) == 0;
+      es.v8 = ((reinterpret_cast<uintptr_t>(tm.dst) | (uintptr_t)es.pitch_bytes) & 31) == 0;
       es.row_ok = row_in_tile < tm.rows;
       es.map_c = (a.tma_store && es.coalesce) ? &map_c : nullptr;
       es.row_c = tm.m_dst0 + q * 32;
@@ -775,6 +866,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if constexpr (SPLIT) cluster_wait_all();
   tc_fence_before();
   __syncthreads();
+  // pair form: neither CTA frees its tensor memory or leaves while the partner may still issue into it or signal its barriers
+  if constexpr (PAIR) cluster_sync_all();
   if (s_err) {
     // give copies that may still be in flight time to land before shared memory is released
     for (int i = 0; i < 64; ++i) __nanosleep(20000);
@@ -783,7 +876,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0) TC_STAMP(7);
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 

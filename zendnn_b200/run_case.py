@@ -97,6 +97,17 @@ def _moe(args):
     ops = 2 * T * (k + S) * (H * 2 * I + I * H)
     print("moe %s: %.1f us per layer, %.0f tokens/s, %.0f TOPS (wall %.1f us)" %
           (args.config, ms * 1e3, T / ms * 1e3, ops / ms / 1e9, (time.perf_counter() - t0) / args.reps * 1e6))
+    # per-phase device times, recorded by the library itself
+    import ctypes as C
+    capi.check(capi.lib.b200dnn_phase_timing(st, 1))
+    for _ in range(args.reps):
+        call()
+    buf = (C.c_float * capi.PHASES)()
+    capi.check(capi.lib.b200dnn_phase_times(st, buf, capi.PHASES, None))
+    capi.check(capi.lib.b200dnn_phase_timing(st, 0))
+    rows = T * (k + S)
+    print("  phases (us): " + ", ".join("%s %.1f" % (n, v * 1e3) for n, v in zip(capi.PHASE_NAMES, buf) if v > 0))
+    print("  gemm1 %.0f TOPS, gemm2 %.0f TOPS" % (2.0 * rows * H * 2 * I / buf[4] / 1e9, 2.0 * rows * I * H / buf[6] / 1e9))
 
 
 def main():
