@@ -184,8 +184,20 @@ typedef struct b200dnn_moe_expert_t {
   const void *w2;        /* s8 [I, H] (transB: [H, I]) */
   int64_t ldb2;
   const float *w2_scale; /* [H] */
-  void *dst_down;        /* [M,H] bf16, row stride ldc_down */
+  void *dst_down;        /* [M,H] bf16, row stride ldc_down.  NULL (b200dnn_fused_moe only): the result is written back
+                          * into `src` with row stride lda, the reference's src-reuse mode
+                          * (matmul/group_matmul/group_matmul_direct.hpp:500-566); lda >= H then */
   int64_t ldc_down;
+  const void *bias13;    /* optional bias of the first GEMM, [2I] in the caller's column order, added before the activation
+                          * (matmul/group_matmul/custom_kernel/ukernel/int8_microkernel.cpp:161-177) */
+  int32_t bias13_dt;     /* f32 | bf16 */
+  int32_t reserved2;
+  const void *bias2;     /* optional bias of the second GEMM, [H] (grp_matmul_fused_moe_params::bias_down) */
+  int32_t bias2_dt;
+  int32_t reserved3;
+  void *dst_op1;         /* optional (b200dnn_fused_moe only): the activated output of the first GEMM, [M,I] bf16 with row
+                          * stride ldc_op1, which the reference leaves in the caller's dst[] (group_matmul_direct.hpp:489-497) */
+  int64_t ldc_op1;
 } b200dnn_moe_expert_t;
 
 /* group_matmul_direct with fused_moe + gated_act (+ optional moe_postop), dynamic per-token INT8

@@ -363,7 +363,7 @@ def router_topk(logits, k, renorm=True):
     return ids, w
 
 
-def fused_moe(x_bf16, ids, weights, w13, s13, w2, s2, act="silu_and_mul", round_before_act=False):
+def fused_moe(x_bf16, ids, weights, w13, s13, w2, s2, act="silu_and_mul", round_before_act=False, b13=None, b2=None):
     """Dynamic-INT8 fused MoE data flow of group_matmul_direct
     (group_matmul/group_matmul_fused_moe.cpp:906-1078; test convention
     gtests/group_matmul/test_fused_moe.cpp:2565-2676).
@@ -374,7 +374,9 @@ def fused_moe(x_bf16, ids, weights, w13, s13, w2, s2, act="silu_and_mul", round_
     reduce.  round_before_act selects the separate-pass form (Op1 output rounded to bf16 before
     the activation, group_matmul_moe_act.cpp:110-117); default is the fused-epilogue form
     (group_matmul_act_avx512.hpp:62-70).  Returns (out [T,H] bf16-bits, expert row outputs
-    [T*k, H] in slot order)."""
+    [T*k, H] in slot order).  b13[e] [2I] / b2[e] [H]: optional f32 biases, added after the dequantisation and before
+    the activation (group_matmul/custom_kernel/ukernel/int8_microkernel.cpp:161-177) / to the down projection
+    (grp_matmul_fused_moe_params::bias_down)."""
     T, H = x_bf16.shape
     k = ids.shape[1]
     E = len(w13)
@@ -389,16 +391,16 @@ def fused_moe(x_bf16, ids, weights, w13, s13, w2, s2, act="silu_and_mul", round_
         acc1 = gemm_s32(q1, w13[e])
         I = acc1.shape[1] // 2
         if round_before_act:
-            y = epilogue(acc1, "bf16", sc1, s13[e])
+            y = epilogue(acc1, "bf16", sc1, s13[e], bias=None if b13 is None else b13[e])
             z = gated_act(y, act)
         else:
-            y = epilogue(acc1, "f32", sc1, s13[e])
+            y = epilogue(acc1, "f32", sc1, s13[e], bias=None if b13 is None else b13[e])
             if act == "swiglu_oai_mul":
                 z = gated_act_f32_pairs(y[:, 0::2], y[:, 1::2], act)
             else:
                 z = gated_act_f32_pairs(y[:, :I], y[:, I:], act)
         q2, sc2 = quant_per_token(z)
-        o = matmul_w8a8(q2, w2[e], "bf16", src_scale=sc2, wei_scale=s2[e])
+        o = matmul_w8a8(q2, w2[e], "bf16", src_scale=sc2, wei_scale=s2[e], bias=None if b2 is None else b2[e])
         slot_out[slots] = o
     out = moe_weighted_reduce(slot_out, weights, k)
     return out, slot_out

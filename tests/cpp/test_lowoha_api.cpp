@@ -241,7 +241,10 @@ static void test_reorder_and_prepack() {
   CHECK(maxerr <= 0.5f * s1 + 1e-6f, "quant/dequant round trip error %g", maxerr);
 }
 
-static void test_fused_moe_vs_two_call() {
+// with_bias: f32 biases on both GEMMs (grp_matmul_fused_moe_params::bias_down); want_op1: the activated output of the first
+// GEMM must appear in the caller's dst[]; reuse_src: dst_down left empty, the result comes back in src[] (the reference's
+// mode 2).  Mirrors zendnnl/gtests/group_matmul/test_fused_moe.cpp:1791-2045 (bias), :2491-2721 (dynamic INT8, both passes).
+static void test_fused_moe_vs_two_call(bool with_bias, bool want_op1, bool reuse_src) {
   // 4 experts (one without tokens), top-2, hidden 128, FFN 64: fused group_matmul_direct against the same
   // data flow made of single calls (quantise, matmul f32, SiLU*up in this file, quantise, matmul).
   Rng r(4);
@@ -261,7 +264,8 @@ static void test_fused_moe_vs_two_call() {
   std::vector<float> tw((size_t)T * topk);
   const int choices[3] = {0, 1, 3};
   for (int t = 0; t < T; ++t) { int a = r.ri(0, 2), b = (a + 1 + r.ri(0, 1)) % 3; ids[t * 2] = choices[a]; ids[t * 2 + 1] = choices[b]; tw[t * 2] = r.rf(0.2f, 0.8f); tw[t * 2 + 1] = 1.0f - tw[t * 2]; }
-  std::vector<std::vector<uint16_t>> src(E), down(E);
+  std::vector<std::vector<uint16_t>> src(E), down(E), op1(E);
+  std::vector<std::vector<float>> B13(E), B2(E);
   std::vector<std::vector<int>> slot_of(E);
   for (int e = 0; e < E; ++e)
     for (int s = 0; s < T * topk; ++s)
@@ -279,16 +283,29 @@ static void test_fused_moe_vs_two_call() {
     if (src[e].empty()) src[e].resize(H);
     down[e].assign((size_t)std::max(Mv[e], 1) * H, 0);
     srcv[e] = src[e].data(); wv[e] = W13[e].data();
-    for (int i = 0; i < Mv[e]; ++i) row_ptrs[slot_of[e][i]] = down[e].data() + (size_t)i * H;
+    B13[e].resize(2 * I); B2[e].resize(H);
+    for (auto &v : B13[e]) v = with_bias ? r.rf(-0.5f, 0.5f) : 0.f;
+    for (auto &v : B2[e]) v = with_bias ? r.rf(-0.5f, 0.5f) : 0.f;
+    if (with_bias) biasv[e] = B13[e].data();
+    op1[e].assign((size_t)std::max(Mv[e], 1) * 2 * I, 0);      // dst[e] is [M, ldc = 2I]: the activated values fill its first I columns
+    if (want_op1) dstv[e] = op1[e].data();
     matmul_params &p = params[e];
     p.dtypes.src = data_type_t::bf16; p.dtypes.wei = data_type_t::s8; p.dtypes.dst = data_type_t::bf16; p.dtypes.compute = data_type_t::s8;
+    p.dtypes.bias = data_type_t::f32;
     p.dynamic_quant = true;
     p.quant_params.src_scale.dt = data_type_t::f32; p.quant_params.src_scale.dims = {std::max(Mv[e], 1), 1};
     p.quant_params.wei_scale.buff = S13[e].data(); p.quant_params.wei_scale.dt = data_type_t::f32; p.quant_params.wei_scale.dims = {1, 2 * I};
-    fused.down_weight.push_back(W2[e].data()); fused.N_down.push_back(H); fused.ldb_down.push_back(H); fused.bias_down.push_back(nullptr);
+    fused.down_weight.push_back(W2[e].data()); fused.N_down.push_back(H); fused.ldb_down.push_back(H);
+    fused.bias_down.push_back(with_bias ? B2[e].data() : nullptr);
     grp_matmul_fused_moe_params::down_weight_quant_t ds; ds.buff = S2[e].data(); ds.dt = data_type_t::f32; ds.dims = {1, H};
-    fused.down_scale.push_back(ds); fused.dst_down.push_back(down[e].data()); fused.ldc_down.push_back(H);
+    fused.down_scale.push_back(ds);
+    if (!reuse_src) { fused.dst_down.push_back(down[e].data()); fused.ldc_down.push_back(H); }
+    // the rows the weighted reduce reads: the expert's dst_down, or its src buffer in the src-reuse mode (H == K here)
+    uint16_t *res = reuse_src ? src[e].data() : down[e].data();
+    for (int i = 0; i < Mv[e]; ++i) row_ptrs[slot_of[e][i]] = res + (size_t)i * H;
   }
+  if (with_bias) fused.bias_dt_down = data_type_t::f32;
+  const std::vector<std::vector<uint16_t>> src_in = src;     // the src-reuse mode overwrites src
   std::vector<uint16_t> out((size_t)T * H, 0);
   group_matmul_moe_postop_params post; post.num_tokens = T; post.topk = topk; post.output = out.data(); post.ldc_output = H;
   post.topk_weights = tw.data(); post.row_ptrs = row_ptrs.data();
@@ -301,25 +318,34 @@ static void test_fused_moe_vs_two_call() {
   int bad = 0, worst = 0;
   for (int e = 0; e < E; ++e) {
     const int M = Mv[e]; if (M == 0) continue;
-    std::vector<int8_t> q1; std::vector<float> s1; per_token_quant(src[e], M, H, q1, s1);
+    std::vector<int8_t> q1; std::vector<float> s1; per_token_quant(src_in[e], M, H, q1, s1);
+    const std::vector<uint16_t> &got_down = reuse_src ? src[e] : down[e];
     std::vector<int32_t> a1 = gemm_s32(q1, H, W13[e], 2 * I, false, M, 2 * I, H);
     std::vector<uint16_t> Z((size_t)M * I);
     for (int m = 0; m < M; ++m) for (int n = 0; n < I; ++n) {
-      float g = (float)a1[(size_t)m * 2 * I + n]; g = g * s1[m]; g = g * S13[e][n];
-      float u = (float)a1[(size_t)m * 2 * I + I + n]; u = u * s1[m]; u = u * S13[e][I + n];
+      float g = (float)a1[(size_t)m * 2 * I + n]; g = g * s1[m]; g = g * S13[e][n]; g = g + B13[e][n];
+      float u = (float)a1[(size_t)m * 2 * I + I + n]; u = u * s1[m]; u = u * S13[e][I + n]; u = u + B13[e][I + n];
       float sg = 1.0f / (1.0f + std::exp(-g));
       Z[(size_t)m * I + n] = f2bf((g * sg) * u);
+    }
+    if (want_op1) {
+      int bad1 = 0;
+      for (int m = 0; m < M; ++m) for (int n = 0; n < I; ++n) {
+        const uint16_t got = op1[e][(size_t)m * 2 * I + n], want = Z[(size_t)m * I + n];
+        bad1 += ulp_diff(got, want) > 1 && std::fabs(bf2f(got) - bf2f(want)) > 1e-5f;
+      }
+      CHECK(bad1 == 0, "expert %d: activated first-GEMM output in dst[]: %d elements beyond 1 ulp", e, bad1);
     }
     std::vector<int8_t> q2; std::vector<float> s2; per_token_quant(Z, M, I, q2, s2);
     std::vector<int32_t> a2 = gemm_s32(q2, I, W2[e], H, false, M, H, I);
     down_ref[e].resize((size_t)M * H);
     for (int m = 0; m < M; ++m) for (int n = 0; n < H; ++n) {
-      float x = (float)a2[(size_t)m * H + n]; x = x * s2[m]; x = x * S2[e][n];
+      float x = (float)a2[(size_t)m * H + n]; x = x * s2[m]; x = x * S2[e][n]; x = x + B2[e][n];
       down_ref[e][(size_t)m * H + n] = f2bf(x);
       // a one-ulp change of one activated value can move a few outputs: accept 2 bf16 ulp or 1 % of the row scale
-      int d = ulp_diff(down[e][(size_t)m * H + n], f2bf(x));
+      int d = ulp_diff(got_down[(size_t)m * H + n], f2bf(x));
       worst = std::max(worst, d);
-      if (d > 2 && std::fabs(bf2f(down[e][(size_t)m * H + n]) - x) > 8e-3f * std::fabs(x) + 2e-3f) ++bad;
+      if (d > 2 && std::fabs(bf2f(got_down[(size_t)m * H + n]) - x) > 8e-3f * std::fabs(x) + 2e-3f) ++bad;
     }
   }
   CHECK(bad == 0, "fused MoE down outputs: %d elements out of tolerance (worst %d ulp)", bad, worst);
@@ -362,13 +388,17 @@ static void test_contract_violations() {
   CHECK(group_matmul_direct(lay, f2, f2, M2, N2, K2, one, s2, ld, w2, ldn, b2, zero, d2, ldn, f2, ps) == status_t::success, "plain grouped call: %s", last_error());
 }
 
+#define RUN(call) do { std::fprintf(stderr, "running %s\n", #call); call; } while (0)
+
 int main() {
-  test_int8_u8_zp_bias_relu();
-  test_int8_sym_quant_per_token();
-  test_int8_dynamic_gemm();
-  test_reorder_and_prepack();
-  test_fused_moe_vs_two_call();
-  test_contract_violations();
+  RUN(test_int8_u8_zp_bias_relu());
+  RUN(test_int8_sym_quant_per_token());
+  RUN(test_int8_dynamic_gemm());
+  RUN(test_reorder_and_prepack());
+  RUN(test_fused_moe_vs_two_call(false, false, false));
+  RUN(test_fused_moe_vs_two_call(true, true, false));
+  RUN(test_fused_moe_vs_two_call(true, false, true));
+  RUN(test_contract_violations());
   std::printf("%d checks, %d failures\n", g_checks, g_fail);
   return g_fail ? 1 : 0;
 }

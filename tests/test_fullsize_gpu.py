@@ -104,5 +104,5 @@ def test_moe_full_size_sampled_tokens(capi, oracle, T, H, I, E, k, S, zipf):
     w2 = [keep[e][2].cpu().numpy() if e in need else empty for e in range(E + S)]
     s2 = [keep[e][3].cpu().numpy() for e in range(E + S)]
     ref, _ = oracle.fused_moe(_u16(x[ti]), ids_all, w_all, w13, s13, w2, s2)
-    assert_bf16_close(_u16(out[ti]), ref, 2, "sampled tokens", row_atol_frac=8e-3)
+    assert_bf16_close(_u16(out[ti]), ref, 1, "sampled tokens")
     capi.lib.b200dnn_clear_caches()

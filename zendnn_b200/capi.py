@@ -48,7 +48,10 @@ class MoeExpert(C.Structure):
     _fields_ = [("M", C.c_int32), ("reserved", C.c_int32), ("src", C.c_void_p), ("lda", C.c_int64),
                 ("w13", C.c_void_p), ("ldb13", C.c_int64), ("w13_scale", C.c_void_p),
                 ("w2", C.c_void_p), ("ldb2", C.c_int64), ("w2_scale", C.c_void_p),
-                ("dst_down", C.c_void_p), ("ldc_down", C.c_int64)]
+                ("dst_down", C.c_void_p), ("ldc_down", C.c_int64),
+                ("bias13", C.c_void_p), ("bias13_dt", C.c_int32), ("reserved2", C.c_int32),
+                ("bias2", C.c_void_p), ("bias2_dt", C.c_int32), ("reserved3", C.c_int32),
+                ("dst_op1", C.c_void_p), ("ldc_op1", C.c_int64)]
 
 
 class EpConfig(C.Structure):

@@ -173,8 +173,15 @@ status_t group_matmul_direct(const std::vector<char> &layout, const std::vector<
     if (fused->down_weight.size() < num_ops || fused->N_down.size() < num_ops || fused->ldb_down.size() < num_ops ||
         fused->down_scale.size() < num_ops)
       return shim_fail(status_t::failure, "fused MoE: down-projection vectors are shorter than the number of experts");
-    if (fused->dst_down.size() < num_ops || fused->ldc_down.size() < num_ops)
-      return shim_fail(status_t::unimplemented, "fused MoE: writing the result back into src[] (empty dst_down) is not implemented");
+    // mode (1): caller-allocated dst_down; mode (2), dst_down empty: the result is written back into src[]
+    // (group_matmul_direct.hpp:500-566: matched src/dst precision and lda >= N_down are preconditions)
+    const bool reuse_src = fused->dst_down.empty();
+    if (!reuse_src && (fused->dst_down.size() < num_ops || fused->ldc_down.size() < num_ops))
+      return shim_fail(status_t::failure, "fused MoE: dst_down / ldc_down are shorter than the number of experts");
+    bool any_bias_down = false;
+    for (size_t i = 0; i < num_ops && i < fused->bias_down.size(); ++i) any_bias_down |= fused->bias_down[i] != nullptr;
+    if (any_bias_down && fused->bias_dt_down == data_type_t::none)
+      return shim_fail(status_t::failure, "fused MoE: bias_down given without bias_dt_down");
     const matmul_params &p0 = params[0];
     if (!(p0.dynamic_quant && p0.dtypes.src == data_type_t::bf16 && p0.dtypes.wei == data_type_t::s8 &&
           p0.dtypes.dst == data_type_t::bf16))
@@ -185,8 +192,7 @@ status_t group_matmul_direct(const std::vector<char> &layout, const std::vector<
         return shim_fail(status_t::unimplemented, "fused MoE: experts must share K, N, N_down and transB");
       if (layout[i] != 'r' && layout[i] != 'R') return shim_fail(status_t::failure, "fused MoE requires row-major layout");
       if (transA[i] || alpha[i] != 1.0f || beta[i] != 0.0f) return shim_fail(status_t::unimplemented, "fused MoE: transA / alpha / beta");
-      if (bias[i] || (i < fused->bias_down.size() && fused->bias_down[i]))
-        return shim_fail(status_t::unimplemented, "fused MoE: bias is not implemented");
+      if (reuse_src && lda[i] < fused->N_down[i]) return shim_fail(status_t::failure, "fused MoE: src-reuse mode needs lda >= N_down");
       const auto &ws = params[i].quant_params.wei_scale;
       if (!ws.buff || ws.dt != data_type_t::f32 || nelem(ws.dims) != N[i])
         return shim_fail(status_t::failure, "fused MoE: per-channel f32 weight scale of N elements required");
@@ -198,7 +204,11 @@ status_t group_matmul_direct(const std::vector<char> &layout, const std::vector<
       e.M = M[i]; e.src = src[i]; e.lda = lda[i];
       e.w13 = weight[i]; e.ldb13 = ldb[i]; e.w13_scale = static_cast<const float *>(ws.buff);
       e.w2 = fused->down_weight[i]; e.ldb2 = fused->ldb_down[i]; e.w2_scale = static_cast<const float *>(ds.buff);
-      e.dst_down = fused->dst_down[i]; e.ldc_down = fused->ldc_down[i];
+      if (!reuse_src) { e.dst_down = fused->dst_down[i]; e.ldc_down = fused->ldc_down[i]; }
+      e.bias13 = bias[i]; e.bias13_dt = static_cast<int32_t>(params[i].dtypes.bias);
+      if (i < fused->bias_down.size()) { e.bias2 = fused->bias_down[i]; e.bias2_dt = static_cast<int32_t>(fused->bias_dt_down); }
+      // mode (1): the activated output of the first GEMM stays visible in the caller's dst[] (group_matmul_direct.hpp:489-497)
+      if (!reuse_src && i < dst.size() && dst[i] && i < ldc.size()) { e.dst_op1 = dst[i]; e.ldc_op1 = ldc[i]; }
     }
     const bool wconst = is_weights_const[0] && p0.weight_cache_type != 0;
     return from_c(b200dnn_fused_moe(static_cast<int32_t>(num_ops), ex.data(), K[0], N[0] / 2, fused->N_down[0], transB[0] ? 1 : 0,

@@ -49,28 +49,49 @@ int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const s
 
 struct ExpertWeightsIn {
   const void *w13; int64_t ldb13; const float *s13; const void *w2; int64_t ldb2; const float *s2;
+  const void *b13 = nullptr; int32_t b13_dt = 0; const void *b2 = nullptr; int32_t b2_dt = 0;   // optional biases
 };
+inline ExpertWeightsIn expert_in(const b200dnn_moe_expert_t &e) {
+  ExpertWeightsIn w{e.w13, e.ldb13, e.w13_scale, e.w2, e.ldb2, e.w2_scale};
+  w.b13 = e.bias13; w.b13_dt = e.bias13_dt; w.b2 = e.bias2; w.b2_dt = e.bias2_dt;
+  return w;
+}
 
 // Shared core: rows already laid out expert by expert in device memory as the gather described by qa.
 int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, int H, int transB, int act, int weights_const,
                  RowQuantArgs qa, int32_t src_dt, int R, const int32_t *row_off_dev, const int32_t *tile_prefix_dev,
                  int m_tiles_bound, const std::vector<void *> *dst_down_dev, const std::vector<int64_t> *ldc_down,
-                 void **O_out, int64_t *ldO_out, cudaStream_t st, void *O_given = nullptr, int tile_rows = kTcBM) {
+                 void **O_out, int64_t *ldO_out, cudaStream_t st, void *O_given = nullptr, int tile_rows = kTcBM,
+                 const uint16_t **Z_out = nullptr) {
   Runtime &Rt = rt();
   B2_CHECK(act >= 1 && act <= 3, B200DNN_UNIMPLEMENTED, "fused MoE needs a gated activation (got %d)", act);
   B2_CHECK(I % kGateGranule == 0, B200DNN_UNIMPLEMENTED, "expert FFN width must be a multiple of %d", kGateGranule);
   const int gated = act == ACT_SWIGLU_OAI ? 2 : 1;
   std::vector<PackedWeight> p13(G), p2(G);
   std::vector<TcGroupDesc> g13(G), g2(G);
+  int32_t b13_dt = 0, b2_dt = 0;
   for (int g = 0; g < G; ++g) {
     B2_CHECK(ew[g].w13 && ew[g].w2 && ew[g].s13 && ew[g].s2, B200DNN_FAILURE, "expert %d: null weight or scale", g);
     B2_TRY(resolve_weight(ew[g].w13, 'n', K, 2 * (int64_t)I, ew[g].ldb13, transB, gated, weights_const, st, &p13[g]));
     B2_TRY(resolve_weight(ew[g].w2, 'n', I, H, ew[g].ldb2, transB, 0, weights_const, st, &p2[g]));
-    const void *s13, *s2;
+    const void *s13, *s2, *b13 = nullptr, *b2 = nullptr;
     B2_TRY(stage_in(ew[g].s13, (size_t)2 * I * 4, st, &s13));
     B2_TRY(stage_in(ew[g].s2, (size_t)H * 4, st, &s2));
-    g13[g] = TcGroupDesc{s13, p13[g].colsum, nullptr, nullptr, 0};
-    g2[g] = TcGroupDesc{s2, p2[g].colsum, nullptr, dst_down_dev ? (*dst_down_dev)[g] : nullptr, ldc_down ? (*ldc_down)[g] : 0};
+    // biases: one dtype per GEMM (the reference has one bias dtype per pass); an expert may have none
+    if (ew[g].b13) {
+      B2_CHECK(ew[g].b13_dt == B200DNN_F32 || ew[g].b13_dt == B200DNN_BF16, B200DNN_UNIMPLEMENTED, "expert %d: bias dtype %d", g, ew[g].b13_dt);
+      B2_CHECK(b13_dt == 0 || b13_dt == ew[g].b13_dt, B200DNN_UNIMPLEMENTED, "the experts' first-GEMM biases must share one dtype");
+      b13_dt = ew[g].b13_dt;
+      B2_TRY(stage_in(ew[g].b13, (size_t)2 * I * dt_size(b13_dt), st, &b13));
+    }
+    if (ew[g].b2) {
+      B2_CHECK(ew[g].b2_dt == B200DNN_F32 || ew[g].b2_dt == B200DNN_BF16, B200DNN_UNIMPLEMENTED, "expert %d: down bias dtype %d", g, ew[g].b2_dt);
+      B2_CHECK(b2_dt == 0 || b2_dt == ew[g].b2_dt, B200DNN_UNIMPLEMENTED, "the experts' second-GEMM biases must share one dtype");
+      b2_dt = ew[g].b2_dt;
+      B2_TRY(stage_in(ew[g].b2, (size_t)H * dt_size(b2_dt), st, &b2));
+    }
+    g13[g] = TcGroupDesc{s13, p13[g].colsum, b13, nullptr, 0};
+    g2[g] = TcGroupDesc{s2, p2[g].colsum, b2, dst_down_dev ? (*dst_down_dev)[g] : nullptr, ldc_down ? (*ldc_down)[g] : 0};
   }
   void *g13_dev, *g2_dev;
   B2_TRY(cached_blob(g13.data(), sizeof(TcGroupDesc) * G, st, &g13_dev));
@@ -105,6 +126,7 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
   e1.src_scale = s1_in; e1.src_scale_dt = B200DNN_F32; e1.src_scale_n = R > 1 ? R : 2;  // always per-row
   e1.wei_scale_dt = B200DNN_F32; e1.wei_scale_n = 2 * I;
   e1.dst = Z; e1.ldc = I; e1.dst_dt = B200DNN_BF16; e1.gated_act = act; e1.gated_I = I; e1.row_absmax = zmax;
+  e1.bias_dt = b13_dt;
   B2_TRY(grouped_gemm(A1_in, lda1, R, 2 * I, K, p13, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g13_dev,
                       m_tiles_bound, e1, true, st, tile_rows));
   rt().mark(4);
@@ -122,10 +144,11 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
   EpiParams e2{};
   e2.src_scale = s2v; e2.src_scale_dt = B200DNN_F32; e2.src_scale_n = R > 1 ? R : 2;
   e2.wei_scale_dt = B200DNN_F32; e2.wei_scale_n = H;
-  e2.dst = O; e2.ldc = H; e2.dst_dt = B200DNN_BF16;
+  e2.dst = O; e2.ldc = H; e2.dst_dt = B200DNN_BF16; e2.bias_dt = b2_dt;
   B2_TRY(grouped_gemm((const uint8_t *)A2, Iq, R, H, I, p2, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g2_dev,
                       m_tiles_bound, e2, dst_down_dev == nullptr, st, tile_rows));
   rt().mark(6);
+  if (Z_out) *Z_out = Z;
   if (O_out) { *O_out = O; *ldO_out = H; }
   return B200DNN_SUCCESS;
 }
@@ -148,8 +171,11 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
     row_off[g + 1] = row_off[g] + ex[g].M;
     tile_prefix[g + 1] = tile_prefix[g] + (ex[g].M + tile_rows - 1) / tile_rows;
     if (ex[g].M > 0) {
-      B2_CHECK(ex[g].src && ex[g].dst_down, B200DNN_FAILURE, "expert %d: null src or dst_down", g);
-      B2_CHECK(ex[g].lda >= K && ex[g].ldc_down >= H, B200DNN_FAILURE, "expert %d: leading dimension too small", g);
+      B2_CHECK(ex[g].src, B200DNN_FAILURE, "expert %d: null src", g);
+      // dst_down == NULL: the reference's src-reuse mode, the result goes back into src with row stride lda
+      B2_CHECK(ex[g].lda >= K && (ex[g].dst_down ? ex[g].ldc_down >= H : ex[g].lda >= H), B200DNN_FAILURE,
+               "expert %d: leading dimension too small", g);
+      B2_CHECK(!ex[g].dst_op1 || ex[g].ldc_op1 >= I, B200DNN_FAILURE, "expert %d: ldc_op1 too small", g);
     }
   }
   const int R = row_off[G];
@@ -160,11 +186,13 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
   std::vector<int64_t> src_ld(G), ldc_down(G);
   std::vector<Staged> outs(G);
   for (int g = 0; g < G; ++g) {
-    src_ld[g] = ex[g].lda; ldc_down[g] = ex[g].ldc_down;
+    src_ld[g] = ex[g].lda; ldc_down[g] = ex[g].dst_down ? ex[g].ldc_down : ex[g].lda;
     outs[g].copy_back = false;
     if (ex[g].M == 0) continue;
     B2_TRY(stage_in(ex[g].src, span_bytes(ex[g].M, K, ex[g].lda, B200DNN_BF16), st, &src_dev[g]));
-    B2_TRY(stage_out(ex[g].dst_down, span_bytes(ex[g].M, H, ex[g].ldc_down, B200DNN_BF16), st, &outs[g], ex[g].ldc_down != H));
+    // the rows are copied out of src and quantised before the second GEMM runs, so src may take the result
+    void *dst_host = ex[g].dst_down ? ex[g].dst_down : const_cast<void *>(ex[g].src);
+    B2_TRY(stage_out(dst_host, span_bytes(ex[g].M, H, ldc_down[g], B200DNN_BF16), st, &outs[g], ldc_down[g] != H));
     dst_dev[g] = outs[g].dev;
   }
   // blob: src ptrs | src ld | row_off | tile_prefix
@@ -181,7 +209,7 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
   const int32_t *row_off_dev = (const int32_t *)(b + o_ro), *tile_prefix_dev = (const int32_t *)(b + o_tp);
 
   std::vector<ExpertWeightsIn> ew(G);
-  for (int g = 0; g < G; ++g) ew[g] = ExpertWeightsIn{ex[g].w13, ex[g].ldb13, ex[g].w13_scale, ex[g].w2, ex[g].ldb2, ex[g].w2_scale};
+  for (int g = 0; g < G; ++g) ew[g] = expert_in(ex[g]);
 
   // the experts' rows are first laid back to back in one bf16 slab, then quantised in one launch
   RowQuantArgs qa{};
@@ -195,8 +223,19 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
   }
   qa.src = X; qa.src_ld = K;
 
+  const uint16_t *Z = nullptr;
   B2_TRY(moe_core(G, ew, K, I, H, transB, act, weights_const, qa, B200DNN_BF16, R, row_off_dev, tile_prefix_dev,
-                  tile_prefix[G], &dst_dev, &ldc_down, nullptr, nullptr, st, nullptr, tile_rows));
+                  tile_prefix[G], &dst_dev, &ldc_down, nullptr, nullptr, st, nullptr, tile_rows, &Z));
+  // the activated output of the first GEMM, for callers that want it (the reference leaves it in dst[])
+  std::vector<Staged> op1_outs;
+  for (int g = 0; g < G; ++g) {
+    if (ex[g].M == 0 || !ex[g].dst_op1) continue;
+    Staged o1;
+    B2_TRY(stage_out(ex[g].dst_op1, span_bytes(ex[g].M, I, ex[g].ldc_op1, B200DNN_BF16), st, &o1, ex[g].ldc_op1 != I));
+    B2_CUDA(cudaMemcpy2DAsync(o1.dev, (size_t)ex[g].ldc_op1 * 2, Z + (size_t)row_off[g] * I, (size_t)I * 2, (size_t)I * 2,
+                              (size_t)ex[g].M, cudaMemcpyDefault, st));
+    op1_outs.push_back(o1);
+  }
 
   Staged o_out; o_out.copy_back = false;
   if (row_ptrs) {
@@ -213,11 +252,11 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
       const void *dp = nullptr;
       for (int g = 0; g < G && !dp; ++g) {
         if (ex[g].M == 0) continue;
-        const uint8_t *lo = (const uint8_t *)ex[g].dst_down;
-        const uint8_t *hi = lo + span_bytes(ex[g].M, H, ex[g].ldc_down, B200DNN_BF16);
+        const uint8_t *lo = (const uint8_t *)(ex[g].dst_down ? ex[g].dst_down : ex[g].src);
+        const uint8_t *hi = lo + span_bytes(ex[g].M, H, ldc_down[g], B200DNN_BF16);
         if (p >= lo && p < hi) dp = (const uint8_t *)dst_dev[g] + (p - lo);
       }
-      B2_CHECK(dp, B200DNN_FAILURE, "row_ptrs[%zu] does not point into any dst_down buffer", i);
+      B2_CHECK(dp, B200DNN_FAILURE, "row_ptrs[%zu] does not point into any expert's output buffer", i);
       dev_rows[i] = dp;
     }
     void *tab, *w_dev;
@@ -235,6 +274,10 @@ extern "C" int32_t b200dnn_fused_moe(int32_t G, const b200dnn_moe_expert_t *ex, 
   }
   bool any = o_out.copy_back || o_out.sync;
   for (auto &s : outs) if (s.sync) any = true;
+  for (auto &s : op1_outs) {
+    if (s.sync) any = true;
+    if (s.copy_back) { B2_CUDA(cudaMemcpyAsync(s.host, s.dev, s.bytes, cudaMemcpyDeviceToHost, st)); any = true; }
+  }
   for (auto &s : outs) if (s.copy_back) { B2_CUDA(cudaMemcpyAsync(s.host, s.dev, s.bytes, cudaMemcpyDeviceToHost, st)); any = true; }
   if (o_out.copy_back) B2_CUDA(cudaMemcpyAsync(o_out.host, o_out.dev, o_out.bytes, cudaMemcpyDeviceToHost, st));
   if (any) { B2_CUDA(cudaStreamSynchronize(st)); B2_TRY(check_tc_status(st)); }
@@ -276,7 +319,7 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   rt().mark(0);
 
   std::vector<ExpertWeightsIn> ew(G);
-  for (int g = 0; g < G; ++g) ew[g] = ExpertWeightsIn{ex[g].w13, ex[g].ldb13, ex[g].w13_scale, ex[g].w2, ex[g].ldb2, ex[g].w2_scale};
+  for (int g = 0; g < G; ++g) ew[g] = expert_in(ex[g]);
   RowQuantArgs qa{};
   // every token is quantised once and written to the rows of all its slots (routed and shared experts)
   qa.src = x_dev; qa.src_ld = ldx; qa.gather_div = 1;
@@ -380,7 +423,7 @@ extern "C" int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, cons
     row_off[g + 1] = row_off[g] + group_rows[g];
     tile_prefix[g + 1] = tile_prefix[g] + (group_rows[g] + tile_rows - 1) / tile_rows;
     const b200dnn_moe_expert_t &e = experts[group_expert[g]];
-    ew[g] = ExpertWeightsIn{e.w13, e.ldb13, e.w13_scale, e.w2, e.ldb2, e.w2_scale};
+    ew[g] = expert_in(e);
   }
   const int R = row_off[n_groups];
   if (R == 0) return B200DNN_SUCCESS;

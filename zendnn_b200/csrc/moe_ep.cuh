@@ -196,13 +196,18 @@ int32_t ep_phase_experts(EpCtx &c, int T, cudaStream_t st) {
   const int gated = f.act == ACT_SWIGLU_OAI ? 2 : 1;
   std::vector<PackedWeight> p13(G), p2(G);
   std::vector<TcGroupDesc> g13(G), g2(G);
+  int32_t b13_dt = 0, b2_dt = 0;
   for (int g = 0; g < G; ++g) {
     const ExpertWeightsIn &e = c.ew[g];
     B2_TRY(resolve_weight(e.w13, 'n', K, 2 * (int64_t)I, e.ldb13, f.transB, gated, 1, st, &p13[g]));
     B2_TRY(resolve_weight(e.w2, 'n', I, H, e.ldb2, f.transB, 0, 1, st, &p2[g]));
-    g13[g] = TcGroupDesc{e.s13, p13[g].colsum, nullptr, nullptr, 0};
-    g2[g] = TcGroupDesc{e.s2, p2[g].colsum, nullptr, nullptr, 0};
+    if (e.b13) { B2_CHECK(b13_dt == 0 || b13_dt == e.b13_dt, B200DNN_UNIMPLEMENTED, "the experts' first-GEMM biases must share one dtype"); b13_dt = e.b13_dt; }
+    if (e.b2) { B2_CHECK(b2_dt == 0 || b2_dt == e.b2_dt, B200DNN_UNIMPLEMENTED, "the experts' second-GEMM biases must share one dtype"); b2_dt = e.b2_dt; }
+    g13[g] = TcGroupDesc{e.s13, p13[g].colsum, e.b13, nullptr, 0};
+    g2[g] = TcGroupDesc{e.s2, p2[g].colsum, e.b2, nullptr, 0};
   }
+  B2_CHECK((b13_dt == 0 || b13_dt == B200DNN_F32 || b13_dt == B200DNN_BF16) && (b2_dt == 0 || b2_dt == B200DNN_F32 || b2_dt == B200DNN_BF16),
+           B200DNN_UNIMPLEMENTED, "bias dtype must be f32 or bf16");
   void *g13_dev, *g2_dev;
   B2_TRY(cached_blob(g13.data(), sizeof(TcGroupDesc) * G, st, &g13_dev));
   B2_TRY(cached_blob(g2.data(), sizeof(TcGroupDesc) * G, st, &g2_dev));
@@ -218,6 +223,7 @@ int32_t ep_phase_experts(EpCtx &c, int T, cudaStream_t st) {
   e1.src_scale = s1; e1.src_scale_dt = B200DNN_F32; e1.src_scale_n = R > 1 ? R : 2;
   e1.wei_scale_dt = B200DNN_F32; e1.wei_scale_n = 2 * I;
   e1.dst = c.Z; e1.ldc = I; e1.dst_dt = B200DNN_BF16; e1.gated_act = f.act; e1.gated_I = I; e1.row_absmax = c.zmax;
+  e1.bias_dt = b13_dt;
   B2_TRY(grouped_gemm(A1, c.Kq, R, 2 * I, K, p13, c.row_off, c.tile_prefix, (const TcGroupDesc *)g13_dev, m_tiles_hint, e1, true, st, tile_rows));
   rt().mark(4);
   RowQuantArgs q2{};
@@ -228,7 +234,7 @@ int32_t ep_phase_experts(EpCtx &c, int T, cudaStream_t st) {
   EpiParams e2{};
   e2.src_scale = c.s2; e2.src_scale_dt = B200DNN_F32; e2.src_scale_n = R > 1 ? R : 2;
   e2.wei_scale_dt = B200DNN_F32; e2.wei_scale_n = H;
-  e2.dst = c.xbuf + c.off_o; e2.ldc = H; e2.dst_dt = B200DNN_BF16;
+  e2.dst = c.xbuf + c.off_o; e2.ldc = H; e2.dst_dt = B200DNN_BF16; e2.bias_dt = b2_dt;
   B2_TRY(grouped_gemm((const uint8_t *)c.A2, c.Iq, R, H, I, p2, c.row_off, c.tile_prefix, (const TcGroupDesc *)g2_dev,
                       m_tiles_hint, e2, true, st, tile_rows));
   rt().mark(6);
@@ -365,7 +371,9 @@ int32_t b200dnn_ep_set_experts(void *handle, const b200dnn_moe_expert_t *ex, int
     B2_CHECK(is_device_ptr(ex[i].w13_scale) && is_device_ptr(ex[i].w2_scale), B200DNN_UNIMPLEMENTED, "expert %d: scales must be device memory", i);
     // the caller lists its routed experts first, then the shared ones; the groups run shared first
     const int g = i < c->n_local ? S + i : i - c->n_local;
-    c->ew[g] = ExpertWeightsIn{ex[i].w13, ex[i].ldb13, ex[i].w13_scale, ex[i].w2, ex[i].ldb2, ex[i].w2_scale};
+    B2_CHECK((!ex[i].bias13 || is_device_ptr(ex[i].bias13)) && (!ex[i].bias2 || is_device_ptr(ex[i].bias2)), B200DNN_UNIMPLEMENTED,
+             "expert %d: biases must be device memory", i);
+    c->ew[g] = expert_in(ex[i]);
   }
   c->have_experts = true;
   return B200DNN_SUCCESS;
