@@ -161,6 +161,24 @@ def ref2_granular(src, dst_dt, scale, zp=None):
     return dst
 
 
+def ref2_int8_ukernel(A, B, src_scale, wei_scale, bias=None, act="none"):
+    """The reference's group DQ-INT8 micro-kernel (custom_kernel/ukernel/int8_microkernel.cpp) over A s8 [M,K] x
+    B s8 [K,N]: exact s32 compensation, x src scale, x weight scale, + bias, optional gated activation, bf16 out
+    ([M,N], or [M,N/2] for the gated forms).  None if unavailable."""
+    r = ref2_lib()
+    if r is None or not hasattr(r, "ref2_int8_ukernel"):
+        return None
+    A = np.ascontiguousarray(A, dtype=np.int8); B = np.ascontiguousarray(B, dtype=np.int8)
+    M, K = A.shape
+    N = B.shape[1]
+    kind = {"none": 0, "swiglu_oai_mul": 1, "silu_and_mul": 2, "gelu_and_mul": 3}[act]
+    sa = np.ascontiguousarray(src_scale, dtype=np.float32); sw = np.ascontiguousarray(wei_scale, dtype=np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    out = np.zeros((M, N if kind == 0 else N // 2), dtype=np.uint16)
+    rc = r.ref2_int8_ukernel(_p(A), _p(B), M, N, K, _p(sa), _p(sw), _p(b), kind, _p(out))
+    return out if rc == 0 else None
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

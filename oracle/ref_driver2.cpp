@@ -10,8 +10,14 @@
 //   matmul/group_matmul/group_matmul_moe_postop.cpp
 //   reorder/lowoha_reorder_utils.cpp (compute_dynamic_quant_params: per-channel / per-tensor dynamic scales)
 //   reorder/reorder_data_type/scalar_impl/scalar_granular_impl.cpp (static quantise / dequantise with granular scales)
+//   matmul/group_matmul/custom_kernel/ukernel/int8_microkernel.cpp (the DQ-INT8 tile micro-kernel of group_matmul_direct:
+//     VNNI GEMM, exact s32 compensation, x src scale, x weight scale, + bias, gated activation in registers)
 #include <cstdint>
+#include <cstdlib>
+#include <cstring>
 #include <vector>
+
+#include "lowoha_operators/matmul/group_matmul/custom_kernel/ukernel/int8_microkernel.hpp"
 
 #include "lowoha_operators/matmul/group_matmul/group_matmul_direct.hpp"
 #include "lowoha_operators/reorder/lowoha_reorder_utils.hpp"
@@ -90,5 +96,43 @@ API int ref2_granular(const void *src, int src_dt, void *dst, int dst_dt, int64_
     p.quant_params.zero_point.dims = {zr, zc};
   }
   reorder_granular_scaler_impl_2d(src, dst, p);
+  return 0;
+}
+
+// The reference's DQ-INT8 micro-kernel (s8 symmetric source) over a whole [M,K] x [K,N] problem.  The driver does what
+// the kernel's contract asks of its caller (custom_kernel/pack.hpp:212-232): per block of 32 packed columns, the weight
+// bytes as [K/4][32][4] followed by the 32 int32 column sums; for silu_and_mul / gelu_and_mul the caller's split halves
+// [gate | up] are re-ordered into (g0,u0,g1,u1,...) pairs, and the per-column scales and bias follow the same order.
+// act: the kernel's ActKind (0 none, 1 swiglu_oai_mul, 2 silu_and_mul, 3 gelu_and_mul).  K % 4 == 0, N % 32 == 0.
+// out: bf16 bits, [M,N] for act 0, else [M,N/2].  Returns 0 on success.
+API int ref2_int8_ukernel(const int8_t *A, const int8_t *B, int M, int N, int K, const float *src_scale, const float *wei_scale,
+                          const float *bias, int act, uint16_t *out) {
+  using namespace zendnnl::lowoha::matmul::custom_kernel;
+  if (!avx512vnni_available() || K % 4 != 0 || N % 32 != 0 || M <= 0) return -1;
+  const int NR = 32, I = N / 2, kq = K / 4;
+  auto src_col = [&](int p) { return (act == 2 || act == 3) ? ((p & 1) ? I + p / 2 : p / 2) : p; };
+  const size_t slab_bytes = (size_t)kq * NR * 4 + NR * sizeof(int32_t);
+  int8_t *slab = static_cast<int8_t *>(aligned_alloc(64, (slab_bytes + 63) / 64 * 64));
+  std::vector<float> ws(NR), bs(NR);
+  for (int ob = 0; ob < N / NR; ++ob) {
+    int32_t *comp = reinterpret_cast<int32_t *>(slab + (size_t)kq * NR * 4);
+    for (int c = 0; c < NR; ++c) {
+      const int sc = src_col(ob * NR + c);
+      int32_t sum = 0;
+      for (int k = 0; k < K; ++k) { const int8_t v = B[(size_t)k * N + sc]; slab[((size_t)(k / 4) * NR + c) * 4 + (k % 4)] = v; sum += v; }
+      comp[c] = sum; ws[c] = wei_scale[sc]; bs[c] = bias ? bias[sc] : 0.f;
+    }
+    for (int m = 0; m < M;) {
+      const int MR = M - m >= 8 ? 8 : M - m;
+      int8_ukernel_fn_t fn = select_int8_ukernel(MR, 2, IntCompute::kS8_Sym, static_cast<ActKind>(act), DstDt::kBf16);
+      if (!fn) { free(slab); return -2; }
+      void *full = act == 0 ? out + (size_t)m * N + ob * NR : nullptr;
+      void *tight = act == 0 ? nullptr : out + (size_t)m * I + ob * (NR / 2);
+      fn(reinterpret_cast<const uint8_t *>(A) + (size_t)m * K, K, slab, src_scale + m, nullptr, ws.data(), ScaleKind::kF32,
+         bias ? bs.data() : nullptr, bias ? BiasKind::fp32 : BiasKind::none, full, act == 0 ? N : 0, tight, act == 0 ? 0 : I, K);
+      m += MR;
+    }
+  }
+  free(slab);
   return 0;
 }

@@ -41,6 +41,22 @@ def weight_input():
     return w32
 
 
+def ukernel_inputs():
+    """Inputs of the group DQ-INT8 micro-kernel cases: s8 activations with per-token scales, s8 weights with per-channel
+    scales, an f32 bias.  M is not a multiple of the kernel's row block, K and N are the smallest legal multiples."""
+    rng = np.random.default_rng(79)
+    M, K, N = 21, 256, 128
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    sw = rng.uniform(1e-4, 5e-4, N).astype(np.float32)
+    bias = rng.normal(size=N).astype(np.float32)
+    return A, B, sa, sw, bias
+
+
+UK_ACTS = ["none", "silu_and_mul", "gelu_and_mul", "swiglu_oai_mul"]
+
+
 def run(tag):
     x32, y32, rows32, w = inputs()
     out = {}
@@ -66,6 +82,12 @@ def run(tag):
             out["qu8_" + dt] = O.ref2_granular(wv, "u8", np.array([[0.002]], dtype=np.float32), np.array([13], dtype=np.int32))
             out["deq_" + dt] = O.ref2_granular(q, dt, sc.reshape(1, -1))
         out["w32"] = w32
+        A, B, sa, sw, bias = ukernel_inputs()
+        for a in UK_ACTS:
+            for hb in (0, 1):
+                r = O.ref2_int8_ukernel(A, B, sa, sw, bias if hb else None, a)
+                assert r is not None, "the reference micro-kernel needs AVX-512 VNNI"
+                out["uk_%s_bias%d" % (a, hb)] = r
     return out
 
 

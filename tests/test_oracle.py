@@ -254,3 +254,61 @@ def test_live_reference_quant_act_reduce_if_present(oracle):
     for act in ACTS:
         d = np.abs(oracle.ref2_gated_act(y, act).astype(np.int32) - oracle.gated_act(y, act).astype(np.int32))
         assert d.max() <= 2
+
+
+def _ukernel_inputs():
+    # the same seeded inputs as tests/golden/make_golden_ref2.py::ukernel_inputs
+    rng = np.random.default_rng(79)
+    M, K, N = 21, 256, 128
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    sw = rng.uniform(1e-4, 5e-4, N).astype(np.float32)
+    bias = rng.normal(size=N).astype(np.float32)
+    return A, B, sa, sw, bias
+
+
+def _oracle_dq_int8(oracle, A, B, sa, sw, bias, act):
+    """The oracle's statement of the group DQ-INT8 tile arithmetic: exact s32, x src scale, x weight scale, + bias
+    (the order the GPU epilogues implement), then the gated activation on the f32 values, one rounding to bf16."""
+    if act == "none":
+        return oracle.matmul_w8a8(A, B, "bf16", src_scale=sa, wei_scale=sw, bias=bias)
+    y = oracle.epilogue(oracle.gemm_s32(A, B), "f32", sa, sw, bias=bias)
+    I = B.shape[1] // 2
+    if act == "swiglu_oai_mul":
+        return oracle.gated_act_f32_pairs(y[:, 0::2], y[:, 1::2], act)
+    return oracle.gated_act_f32_pairs(y[:, :I], y[:, I:], act)
+
+
+@pytest.mark.parametrize("act", ["none", "silu_and_mul", "gelu_and_mul", "swiglu_oai_mul"])
+@pytest.mark.parametrize("has_bias", [0, 1])
+def test_dq_int8_tile_arithmetic_equals_reference_microkernel(oracle, golden2, act, has_bias):
+    """Outputs of the reference's own DQ-INT8 micro-kernel (matmul/group_matmul/custom_kernel/ukernel/int8_microkernel.cpp,
+    driven by oracle/ref_driver2.cpp): the dequantisation order (exact s32 compensation, two multiplies, bias) is equal
+    bit for bit; the gated forms, which the reference evaluates with polynomial exponentials, within 1 bf16 ulp
+    (its gelu_and_mul is the tanh form, |gelu_tanh - gelu_erf| <= 1.5e-3: 2 ulp there)."""
+    A, B, sa, sw, bias = _ukernel_inputs()
+    ref = golden2["uk_%s_bias%d" % (act, has_bias)]
+    got = _oracle_dq_int8(oracle, A, B, sa, sw, bias if has_bias else None, act)
+    d = np.abs(got.astype(np.int32) - ref.astype(np.int32))
+    if act == "none":
+        assert d.max() == 0
+    else:
+        assert d.max() <= (2 if act == "gelu_and_mul" else 1)
+        assert (d == 0).mean() > 0.99
+
+
+def test_live_reference_microkernel_if_present(oracle):
+    if oracle.ref2_lib() is None or oracle.ref2_int8_ukernel(*_ukernel_inputs()[:4]) is None:
+        pytest.skip("reference micro-kernel not built or no AVX-512 VNNI on this host")
+    rng = np.random.default_rng(11)
+    M, K, N = 37, 512, 192
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    sw = rng.uniform(1e-4, 5e-4, N).astype(np.float32)
+    bias = rng.normal(size=N).astype(np.float32)
+    assert (oracle.ref2_int8_ukernel(A, B, sa, sw, bias, "none") == _oracle_dq_int8(oracle, A, B, sa, sw, bias, "none")).all()
+    ref = oracle.ref2_int8_ukernel(A, B, sa, sw, None, "silu_and_mul")
+    got = _oracle_dq_int8(oracle, A, B, sa, sw, None, "silu_and_mul")
+    assert np.abs(ref.astype(np.int32) - got.astype(np.int32)).max() <= 1

@@ -697,10 +697,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int u = 0; u < 8; ++u)
             st_shared_v4(base + (uint32_t)((u ^ (row_in_tile & 7)) << 4), r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
         }
+#ifdef B200DNN_TIMING_EXPERIMENTS
       } else if (a.dbg == 1) {
         // timing experiment: no epilogue work
+#endif
       } else if (!a.gated) {
-        if (a.dbg == 3) { es.coalesce = false; es.row_ok = false; }
+#ifdef B200DNN_TIMING_EXPERIMENTS
+        if (a.dbg == 3) { es.coalesce = false; es.v8 = false; es.row_ok = false; es.map_c = nullptr; }
+#endif
         // this warp's chunks: a contiguous share of the tile's 32-column chunks that lie inside N
         const int nc = min(a.BN / 32, (a.N - pc_tile + 31) / 32);
         const int per = (a.BN / 32 + kTcEpiParts - 1) / kTcEpiParts;
@@ -710,10 +714,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_ld32(taddr0 + (uint32_t)(c * 32), r);
           tc_wait_ld();
           const int pc0 = pc_tile + c * 32;
+#ifdef B200DNN_TIMING_EXPERIMENTS
           if (a.dbg == 2) { uint32_t x = 0;
 #pragma unroll
             for (int i = 0; i < 32; ++i) x ^= r[i];
             if (x == 0x12345678u) report_status(a.status, 99); continue; }
+#endif
           tc_epi_dispatch(a.fast_act, epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane);
         }
       } else {
@@ -764,7 +770,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               }
             }
             const int jc = j0 + 16 * h;
-            if (es.v8) {
+            if (es.map_c && es.rows_valid == 32) {
+              warp_tma_store_rows32(es.sbuf, make_uint4(pk[0], pk[1], pk[2], pk[3]), make_uint4(pk[4], pk[5], pk[6], pk[7]), es.map_c,
+                                    jc * 2, es.row_c, lane);
+            } else if (es.v8) {
               if (row_ok) st_global_v8(reinterpret_cast<uint8_t *>(cx.dst) + ((int64_t)m_dst * cx.ldc + jc) * 2, pk);
             } else if (es.coalesce) {
               warp_store_rows32(es.sbuf, make_uint4(pk[0], pk[1], pk[2], pk[3]), make_uint4(pk[4], pk[5], pk[6], pk[7]),
