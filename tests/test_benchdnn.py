@@ -1,5 +1,6 @@
 """The benchdnn-style driver (zendnn_b200/benchdnn.py): input-line parsing and the supported-subset decision on CPU,
 a few lines end to end on the GPU.  Line format: benchdnn/doc/matmul.md of the reference."""
+import numpy as np
 import pytest
 
 from zendnn_b200 import benchdnn as B
@@ -63,6 +64,46 @@ def test_lines_run_on_the_gpu(tmp_path):
     assert [r[1] for r in results[:3]] == ["success"] * 3, results
     assert all(r[0] > 0 for r in results[:3])
     assert results[3][1].startswith("unimplemented")
+
+
+def _u16(a):
+    return a.view(np.uint16) if a.dtype == np.int16 else a
+
+
+@pytest.mark.gpu
+def test_matmul_lines_compute_what_the_oracle_computes(oracle):
+    """The driver's operands and results of each line against the oracle's statement of the same matmul_direct call:
+    static u8 + zero point with bias and relu; dynamic per-token bf16 source with gelu_tanh; a transposed weight with a
+    dense binary_add operand; a two-layer pipeline whose second layer quantises the first layer's bf16 output."""
+    from helpers import assert_bf16_close
+    lines = ["200, 256, 384, 2, u8:s8:bf16, true, f32, relu",
+             "37, 512, 256, 2, bf16:s8:bf16, true, f32, gelu_tanh, , , true, false, true, 1.0, 0.0, per-channel, , f32, 0, true, per-token",
+             "64, 256, 128, 2, s8:s8:f32, false, f32, binary_add, , , true, false, true",
+             "64, 256, 128:64, 2, bf16:s8:bf16, true, f32, gelu_tanh, , , true, false, true, 1.0, 0.0, per-channel, , f32, 0, true, per-token"]
+    for line in lines:
+        cfg, cap = B.parse_line(line), {}
+        total, status = B.run_config(cfg, capture=cap)
+        assert status == "success" and total > 0, (line, status)
+        src = _u16(cap["x"])
+        for li, L in enumerate(cap["layers"]):
+            w = L["w"].T if cfg["transB"] else L["w"]
+            if cfg["dyn"] or li > 0:
+                qa, sa = oracle.quant_per_token(src if src.dtype != np.float32 else src)
+                kw = dict(src_scale=sa)
+            else:
+                qa, kw = src, dict(src_scale=cap["sscale"], src_zp=cap["szp"] or 0)
+            pos = [dict(p, buff=_u16(p["buff"])) if isinstance(p, dict) else p for p in L["pos"]]
+            ws = _u16(L["wscale"])
+            ws = oracle.bf16_to_f32(ws) if ws.dtype == np.uint16 else ws
+            bias = None if L["bias"] is None else _u16(L["bias"])
+            bias = oracle.bf16_to_f32(bias) if bias is not None and bias.dtype == np.uint16 else bias
+            ref = oracle.matmul_w8a8(qa, np.ascontiguousarray(w), L["ddt"], wei_scale=ws, bias=bias, postops=pos, **kw)
+            got = _u16(L["out"])
+            if L["ddt"] == "bf16":
+                assert_bf16_close(got, ref, 1, "%s (layer %d)" % (line, li), atol=1e-5)
+            else:
+                assert np.allclose(got, ref, rtol=1e-5, atol=1e-5), line
+            src = got          # the next layer of a pipeline reads this layer's output
 
 
 def test_parse_grp_lines():

@@ -151,8 +151,9 @@ def row(cfg, total_ms, status):
     return ", ".join(str(v) for v in vals)
 
 
-def run_config(cfg, cache_mode="hot", num_weight_buffers=0):
-    """Runs one line on cuda:0.  Returns (total_ms over iters, status string)."""
+def run_config(cfg, cache_mode="hot", num_weight_buffers=0, capture=None):
+    """Runs one line on cuda:0.  Returns (total_ms over iters, status string).  capture: a dict that receives host
+    copies of the operands and results of the first weight set (for checks against a CPU statement of the line)."""
     why = unsupported_reason(cfg)
     if why:
         return 0.0, "unimplemented (%s)" % why
@@ -235,6 +236,19 @@ def run_config(cfg, cache_mode="hot", num_weight_buffers=0):
             capi.matmul(d, st)
     e1.record()
     torch.cuda.synchronize()
+    if capture is not None:
+        for d in sets[0]:
+            capi.matmul(d, st)
+        torch.cuda.synchronize()
+
+        def host(t):
+            if t is None:
+                return None
+            return (t.view(torch.int16) if t.dtype == torch.bfloat16 else t).cpu().numpy()
+        capture.update(x=host(x), sscale=host(sscale), szp=None if szp is None else 128,
+                       layers=[dict(w=host(L["ws"][0]), wscale=host(L["wscale"]), bias=host(L["bias"]), out=host(L["out"]), ddt=L["ddt"],
+                                    pos=[dict(p, buff=host(p["buff"])) if isinstance(p, dict) else p for p in L["pos"]])
+                               for L in layers])
     capi.lib.b200dnn_clear_caches()
     return e0.elapsed_time(e1), "success"
 
