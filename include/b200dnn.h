@@ -41,7 +41,7 @@ extern "C" {
 #define B200DNN_FAILURE 0
 #define B200DNN_UNIMPLEMENTED (-1)
 
-enum { B200DNN_F32 = 1, B200DNN_BF16 = 3, B200DNN_S32 = 4, B200DNN_S8 = 7, B200DNN_U8 = 11 };
+enum { B200DNN_F32 = 1, B200DNN_BF16 = 3, B200DNN_S32 = 4, B200DNN_S8 = 7, B200DNN_S4 = 8, B200DNN_U8 = 11 };
 enum { B200DNN_MAX_POSTOPS = 8 };
 /* b200dnn_matmul_t::flags.  STABLE_WEIGHTS: the (prepacked or cached) weight was written before
  * any work still pending on the stream, so the decode kernel may start streaming it while the
@@ -107,6 +107,14 @@ B200DNN_API int64_t b200dnn_launch_count(void);
 
 /* matmul_direct, INT8 path (matmul/lowoha_matmul.cpp:278): C = postops(dequant(A*B) + bias). */
 B200DNN_API int32_t b200dnn_matmul(const b200dnn_matmul_t *desc, void *stream);
+
+/* group_matmul_direct, plain parallel mode (matmul/lowoha_matmul.hpp:204-223; dispatch
+ * matmul/group_matmul/group_matmul_parallel_common.hpp:1240-1248): num_ops independent GEMMs, each with its own source,
+ * weight, bias and destination; descriptors with M == 0 are skipped.  The result is that of num_ops b200dnn_matmul
+ * calls.  When the active descriptors share K, N, the dtypes, the quantisation form (s8 rows with per-token f32 scales,
+ * or bf16 / f32 rows with dynamic_quant and no caller-side scale buffer), per-channel f32 weight scales and the same
+ * element-wise post-ops, all of them run in ONE grouped tcgen05 launch; otherwise one launch per descriptor. */
+B200DNN_API int32_t b200dnn_group_matmul(int32_t num_ops, const b200dnn_matmul_t *descs, void *stream);
 
 /* No counterpart in the reference.  The same W8A8 matmul for callers that cannot allocate device
  * memory at call time (a server whose own pool already holds all free memory, a latency-bound loop

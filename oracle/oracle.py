@@ -53,6 +53,7 @@ def lib():
         _lib = C.CDLL(path)
         _lib.orc_gemm_s32.restype = C.c_int
         _lib.orc_epilogue.restype = C.c_int
+        _lib.orc_group_scaled_gemm.restype = C.c_int
     return _lib
 
 
@@ -102,6 +103,19 @@ def ref2_quant_per_token(x, native=False):
     if r is None or (native and not r.ref2_avx512()):
         return None
     rc = r.ref2_quant_per_token(_p(x), int(x.dtype == np.uint16), _p(q), _p(s), C.c_int64(M), C.c_int64(K), int(native))
+    return (q, s) if rc == 0 else None
+
+
+def ref2_quant_per_group(x, G):
+    """Reference per-group dynamic quantisation (AVX-512 kernel), scale layout {M,G}.  None if unavailable."""
+    r = ref2_lib()
+    x = np.ascontiguousarray(x)
+    M, K = x.shape
+    if r is None or not r.ref2_avx512() or not hasattr(r, "ref2_quant_per_group"):
+        return None
+    q = np.zeros((M, K), dtype=np.int8)
+    s = np.zeros((M, G), dtype=np.float32)
+    rc = r.ref2_quant_per_group(_p(x), int(x.dtype == np.uint16), _p(q), _p(s), C.c_int64(M), C.c_int64(K), C.c_int64(G))
     return (q, s) if rc == 0 else None
 
 
@@ -291,6 +305,67 @@ def matmul_w8a8(A, B, dst_dt="bf16", transB=False, src_scale=None, wei_scale=Non
     acc = gemm_s32(A, B, transB)
     cs = colsum(B, transB) if src_zp != 0 else None
     return epilogue(acc, dst_dt, src_scale, wei_scale, src_zp, cs, bias, postops, order)
+
+
+def matmul_group_scaled(A, B, src_scale, wei_scale, dst_dt="bf16", bias=None, postops=()):
+    """Per-group symmetric INT8 matmul_direct (and W4A8 after the s4 -> s8 widening), the reference's scalar formula
+    (operators/matmul/matmul_ref_kernel.cpp:961-1003): A s8 [M,K], B s8 [K,N], src_scale f32 [M,G] or [M] / [M,1]
+    (per-token, broadcast over the groups), wei_scale f32 [G,N]."""
+    A = np.ascontiguousarray(A, dtype=np.int8)
+    B = np.ascontiguousarray(B, dtype=np.int8)
+    M, K = A.shape
+    N = B.shape[1]
+    ws = np.ascontiguousarray(np.asarray(wei_scale, dtype=np.float32).reshape(-1, N))
+    G = ws.shape[0]
+    ss = np.ascontiguousarray(np.asarray(src_scale, dtype=np.float32).reshape(M, -1))
+    keep = []
+    b = None if bias is None else np.ascontiguousarray(bias)
+    po = _postops(list(postops), keep)
+    out = np.empty((M, N), dtype={"bf16": np.uint16, "f32": np.float32}[dst_dt])
+    rc = lib().orc_group_scaled_gemm(_p(A), C.c_int64(K), _p(B), C.c_int64(N), M, N, K, G, _p(ss), ss.shape[1], _p(ws),
+                                     _p(b), 0 if b is None else _dt_of(b), po, len(postops), _p(out), DT[dst_dt], C.c_int64(N))
+    assert rc == 0, "bad group count"
+    return out
+
+
+def pack_s4(W, transB=False, ldb=None):
+    """Signed 4-bit weights as the reference stores them (matmul/backends/aocl/aocl_kernel.cpp:145-160): element (k,n)
+    lives at physical index k*ldb+n (transB: n*ldb+k), two per byte, even index in the low nibble.  W int8 [K,N] with
+    values in [-8,7] -> uint8 bytes."""
+    W = np.asarray(W, dtype=np.int8)
+    assert W.min() >= -8 and W.max() <= 7
+    K, N = W.shape
+    P = W.T if transB else W                       # physical rows
+    rows, cols = P.shape
+    ldb = cols if ldb is None else ldb
+    flat = np.zeros(rows * ldb + (rows * ldb) % 2, dtype=np.uint8)
+    idx = (np.arange(rows)[:, None] * ldb + np.arange(cols)[None, :]).reshape(-1)
+    flat[idx] = P.reshape(-1).astype(np.uint8) & 0xF
+    return (flat[0::2] | (flat[1::2] << 4)).astype(np.uint8)
+
+
+def unpack_s4(packed, K, N, transB=False, ldb=None):
+    """Inverse of pack_s4: sign-extended nibble codes, int8 [K,N] (the reference's cvt_s4_to_s8)."""
+    rows, cols = (N, K) if transB else (K, N)
+    ldb = cols if ldb is None else ldb
+    b = np.asarray(packed, dtype=np.uint8)
+    flat = np.empty(b.size * 2, dtype=np.uint8)
+    flat[0::2] = b & 0xF
+    flat[1::2] = b >> 4
+    idx = np.arange(rows)[:, None] * ldb + np.arange(cols)[None, :]
+    v = flat[idx].astype(np.int8)
+    v = np.where(v & 8, v | np.int8(-16), v).astype(np.int8)
+    return np.ascontiguousarray(v.T) if transB else v
+
+
+def quant_per_group(x, G):
+    """Dynamic symmetric quantisation with G groups along K per row (scale buffer {M,G}): the per-token rule applied to
+    every group of K/G elements (reorder/lowoha_reorder.cpp:318-390).  Returns (s8 [M,K], f32 [M,G])."""
+    x = np.ascontiguousarray(x)
+    M, K = x.shape
+    assert K % G == 0
+    q, s = quant_per_token(x.reshape(M * G, K // G))
+    return q.reshape(M, K), s.reshape(M, G)
 
 
 def quant_per_token(x, scales_only=False):

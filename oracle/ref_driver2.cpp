@@ -22,6 +22,7 @@
 #include "lowoha_operators/matmul/group_matmul/group_matmul_direct.hpp"
 #include "lowoha_operators/reorder/lowoha_reorder_utils.hpp"
 #include "lowoha_operators/reorder/reorder_data_type/scalar_impl/scalar_kernels.hpp"
+#include "lowoha_operators/reorder/reorder_data_type/dynamic_quant_impl/dynamic_kernels.hpp"
 
 namespace zendnnl { namespace lowoha { namespace reorder {
 void dynamic_per_token_quant_bf16_s8_ref(const uint16_t *, int8_t *, float *, int64_t, int64_t);
@@ -48,6 +49,16 @@ API int ref2_quant_per_token(const void *src, int is_bf16, int8_t *dst, float *s
     if (native) dynamic_per_token_quant_f32_s8_native((const float *)src, dst, scale, M, K);
     else dynamic_per_token_quant_f32_s8_ref((const float *)src, dst, scale, M, K);
   }
+  return 0;
+}
+
+// Per-group dynamic quantisation along K (scale layout {M,G}), the reference's AVX-512 kernel
+// (reorder/reorder_data_type/dynamic_quant_impl/per_group_avx512_f32_fma_kernel.cpp).
+API int ref2_quant_per_group(const void *src, int is_bf16, int8_t *dst, float *scale, int64_t M, int64_t K, int64_t G) {
+  using namespace zendnnl::lowoha::reorder;
+  if (!ref2_avx512()) return -1;
+  if (is_bf16) dynamic_per_group_quant_bf16_s8_native((const uint16_t *)src, dst, scale, M, K, G);
+  else dynamic_per_group_quant_f32_s8_native((const float *)src, dst, scale, M, K, G);
   return 0;
 }
 

@@ -322,6 +322,38 @@ ORC_API int orc_epilogue(const int32_t *acc, int64_t ldacc, int M, int N, int or
   return 0;
 }
 
+/* Group-scaled symmetric INT8 GEMM (per-group source scales {M,G} x per-group weight scales {G,N}) and W4A8 after the
+ * s4 -> s8 widening: operators/matmul/matmul_ref_kernel.cpp:961-1003 -- per output element, groups in order,
+ *   sum += ((float)group_sum * src_scale[m,g]) * wei_scale[g,n]      (f32, one rounding per operation)
+ * then the bias and the post-ops (:1053 ff.).  src_cols = G, or 1 for a per-token source scale broadcast over the
+ * groups (backends/aocl/aocl_kernel.cpp:163-230 expands {M,1} to {M,G} before the GEMM).  B is [K,N] row-major s8. */
+ORC_API int orc_group_scaled_gemm(const int8_t *A, int64_t lda, const int8_t *B, int64_t ldb, int M, int N, int K, int G,
+                                  const float *src_scale, int src_cols, const float *wei_scale,
+                                  const void *bias, int bias_dt, const orc_postop *po, int npo,
+                                  void *dst, int dst_dt, int64_t ldc) {
+  if (G <= 0 || K % G != 0 || (src_cols != 1 && src_cols != G)) return -1;
+  const int gs = K / G;
+  #pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    for (int n = 0; n < N; ++n) {
+      float sum = 0.0f;
+      for (int g = 0; g < G; ++g) {
+        int32_t gsum = 0;
+        for (int k = g * gs; k < (g + 1) * gs; ++k) gsum += (int32_t)A[(int64_t)m * lda + k] * (int32_t)B[(int64_t)k * ldb + n];
+        float v = (float)gsum * src_scale[(int64_t)m * src_cols + (src_cols > 1 ? g : 0)];
+        v = v * wei_scale[(int64_t)g * N + n];
+        sum = sum + v;
+      }
+      float x = sum;
+      if (bias) x = x + load_as_f32(bias, bias_dt, n);
+      for (int i = 0; i < npo; ++i) x = apply_postop(&po[i], x, m, n);
+      if (dst_dt == DT_BF16) ((uint16_t *)dst)[(int64_t)m * ldc + n] = f32_to_bf16(x);
+      else ((float *)dst)[(int64_t)m * ldc + n] = x;
+    }
+  }
+  return 0;
+}
+
 /* ======================================================================================
  * Quantisation.
  * ====================================================================================== */

@@ -6,6 +6,7 @@
 // (zendnnl/gtests/reorder/test_dynamic_quant.cpp) and TestFusedMoEQuantDynINT8.BothPasses compared
 // with a two-call unfused run (zendnnl/gtests/group_matmul/test_fused_moe.cpp:2491,
 // moe_test_utils.hpp:1387).  Needs a GPU.  Exit code 0 = all checks passed.
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -134,6 +135,108 @@ static void test_int8_sym_quant_per_token() {
     int bad = 0;
     for (int m = 0; m < M; ++m) for (int n = 0; n < N; ++n) { float x = (float)acc[(size_t)m * N + n]; x = x * sa[m]; x = x * ws[n]; bad += C[(size_t)m * N + n] != x; }
     CHECK(bad == 0, "per-token M=%d: %d mismatching f32 elements", M, bad);
+  }
+}
+
+// TestMatmul.INT8_SYM_QUANT_PER_GROUP_* (zendnnl/gtests/test_matmul.cpp:1049): s8 source with {M,G} scales, s8 weights with
+// {G,N} scales; reference definition operators/matmul/matmul_ref_kernel.cpp:961-1003 (groups in order, f32)
+static void test_int8_sym_quant_per_group() {
+  Rng r(11);
+  for (int M : {3, 150}) {
+    for (int gs : {8, 64}) {
+      const int K = 256, N = 72, G = K / gs;
+      std::vector<int8_t> A((size_t)M * K), W((size_t)K * N);
+      std::vector<float> sa((size_t)M * G), ws((size_t)G * N), bias(N);
+      for (auto &v : A) v = (int8_t)r.ri(-127, 127);
+      for (auto &v : W) v = (int8_t)r.ri(-127, 127);
+      for (auto &v : sa) v = r.rf(0.005f, 0.05f);
+      for (auto &v : ws) v = r.rf(0.001f, 0.01f);
+      for (auto &v : bias) v = r.rn();
+      std::vector<uint16_t> C((size_t)M * N, 0);
+      matmul_params p;
+      p.dtypes.src = data_type_t::s8; p.dtypes.wei = data_type_t::s8; p.dtypes.dst = data_type_t::bf16; p.dtypes.bias = data_type_t::f32;
+      p.quant_params.src_scale.buff = sa.data(); p.quant_params.src_scale.dt = data_type_t::f32; p.quant_params.src_scale.dims = {M, G};
+      p.quant_params.wei_scale.buff = ws.data(); p.quant_params.wei_scale.dt = data_type_t::f32; p.quant_params.wei_scale.dims = {G, N};
+      matmul_batch_params_t bp;
+      status_t st = matmul_direct('r', false, false, M, N, K, 1.0f, A.data(), K, W.data(), N, bias.data(), 0.0f, C.data(), N, false, bp, p);
+      CHECK(st == status_t::success, "per-group M=%d gs=%d: %s", M, gs, last_error());
+      int worst = 0;
+      for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+          float sum = 0.f;
+          for (int g = 0; g < G; ++g) {
+            int32_t acc = 0;
+            for (int k = g * gs; k < (g + 1) * gs; ++k) acc += (int32_t)A[(size_t)m * K + k] * (int32_t)W[(size_t)k * N + n];
+            float v = (float)acc * sa[(size_t)m * G + g]; v = v * ws[(size_t)g * N + n]; sum = sum + v;
+          }
+          worst = std::max(worst, ulp_diff(C[(size_t)m * N + n], f2bf(sum + bias[n])));
+        }
+      CHECK(worst <= 1, "per-group M=%d gs=%d: %d bf16 ulp", M, gs, worst);
+    }
+  }
+}
+
+// TestMatmul.W4A8_BF16 (zendnnl/gtests/test_matmul.cpp:266): bf16 source quantised by the library, packed s4 weights
+// (two per byte, even index low; backends/aocl/aocl_kernel.cpp:145-160), {G,N} weight scales, bf16 out
+static void test_w4a8_bf16() {
+  Rng r(12);
+  const int M = 20, K = 256, N = 48, gs = 32, G = K / gs;
+  std::vector<uint16_t> X((size_t)M * K);
+  for (auto &v : X) v = f2bf(r.rn());
+  std::vector<int8_t> W((size_t)K * N);
+  for (auto &v : W) v = (int8_t)r.ri(-8, 7);
+  std::vector<uint8_t> W4((size_t)K * N / 2);
+  for (size_t i = 0; i < W4.size(); ++i) W4[i] = (uint8_t)((W[2 * i] & 0xF) | ((W[2 * i + 1] & 0xF) << 4));
+  std::vector<float> ws((size_t)G * N);
+  for (auto &v : ws) v = r.rf(0.001f, 0.01f);
+  std::vector<int8_t> q; std::vector<float> sa;
+  per_token_quant(X, M, K, q, sa);
+  for (int per_group = 0; per_group < 2; ++per_group) {
+    std::vector<float> sg((size_t)M * G);
+    std::vector<int8_t> qg((size_t)M * K);
+    if (per_group) {
+      for (int m = 0; m < M; ++m)
+        for (int g = 0; g < G; ++g) {
+          std::vector<uint16_t> seg(X.begin() + (size_t)m * K + g * gs, X.begin() + (size_t)m * K + (g + 1) * gs);
+          std::vector<int8_t> qs; std::vector<float> ss;
+          per_token_quant(seg, 1, gs, qs, ss);
+          sg[(size_t)m * G + g] = ss[0];
+          std::copy(qs.begin(), qs.end(), qg.begin() + (size_t)m * K + g * gs);
+        }
+    } else {
+      qg = q;
+      for (int m = 0; m < M; ++m) for (int g = 0; g < G; ++g) sg[(size_t)m * G + g] = sa[m];
+    }
+    std::vector<uint16_t> C((size_t)M * N, 0);
+    std::vector<float> scale_out((size_t)M * (per_group ? G : 1), 0.f);
+    matmul_params p;
+    p.dtypes.src = data_type_t::bf16; p.dtypes.wei = data_type_t::s4; p.dtypes.dst = data_type_t::bf16; p.dtypes.compute = data_type_t::s8;
+    p.dynamic_quant = true;
+    p.quant_params.src_scale.buff = scale_out.data(); p.quant_params.src_scale.dt = data_type_t::f32;
+    p.quant_params.src_scale.dims = {M, per_group ? G : 1};
+    p.quant_params.wei_scale.buff = ws.data(); p.quant_params.wei_scale.dt = data_type_t::f32; p.quant_params.wei_scale.dims = {G, N};
+    matmul_batch_params_t bp;
+    status_t st = matmul_direct('r', false, false, M, N, K, 1.0f, X.data(), K, W4.data(), N, nullptr, 0.0f, C.data(), N, true, bp, p);
+    CHECK(st == status_t::success, "W4A8 per_group=%d: %s", per_group, last_error());
+    int worst = 0, bad_scale = 0;
+    for (int m = 0; m < M; ++m) {
+      for (int g = 0; g < (per_group ? G : 1); ++g) bad_scale += scale_out[(size_t)m * (per_group ? G : 1) + g] != sg[(size_t)m * G + g];
+      for (int n = 0; n < N; ++n) {
+        float sum = 0.f;
+        for (int g = 0; g < G; ++g) {
+          int32_t acc = 0;
+          for (int k = g * gs; k < (g + 1) * gs; ++k) acc += (int32_t)qg[(size_t)m * K + k] * (int32_t)W[(size_t)k * N + n];
+          float v = (float)acc * sg[(size_t)m * G + g]; v = v * ws[(size_t)g * N + n]; sum = sum + v;
+        }
+        worst = std::max(worst, ulp_diff(C[(size_t)m * N + n], f2bf(sum)));
+      }
+    }
+    CHECK(bad_scale == 0, "W4A8 per_group=%d: %d source scales differ", per_group, bad_scale);
+    CHECK(worst <= 1, "W4A8 per_group=%d: %d bf16 ulp", per_group, worst);
+    // the reference's refusals: s8 compute is required; an f32 destination is refused
+    matmul_params bad = p; bad.dtypes.compute = data_type_t::none;
+    CHECK(matmul_direct('r', false, false, M, N, K, 1.0f, X.data(), K, W4.data(), N, nullptr, 0.0f, C.data(), N, true, bp, bad) == status_t::failure,
+          "W4A8 without s8 compute accepted");
   }
 }
 
@@ -371,7 +474,9 @@ static void test_contract_violations() {
   CHECK(matmul_direct('r', true, false, 4, 16, 64, 1.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p) == status_t::unimplemented, "transA not reported");
   CHECK(matmul_direct('r', false, false, 4, 16, 64, 2.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p) == status_t::unimplemented, "alpha != 1 not reported");
   matmul_params p4 = p; p4.dtypes.wei = data_type_t::s4;
-  CHECK(matmul_direct('r', false, false, 4, 16, 64, 1.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p4) == status_t::unimplemented, "s4 weights not reported");
+  CHECK(matmul_direct('r', false, false, 4, 16, 64, 1.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p4) == status_t::failure, "s4 weights with a pre-quantised s8 source accepted");
+  p4.dtypes.wei = data_type_t::u4;
+  CHECK(matmul_direct('r', false, false, 4, 16, 64, 1.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p4) == status_t::unimplemented, "u4 weights not reported");
   matmul_params pm = p; matmul_post_op mish; mish.po_type = post_op_type_t::mish; pm.postop_.push_back(mish);
   CHECK(matmul_direct('r', false, false, 4, 16, 64, 1.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, pm) == status_t::failure, "mish accepted on INT8");
   // group: active_matmul > total_matmul, short vectors
@@ -390,10 +495,25 @@ static void test_contract_violations() {
 
 #define RUN(call) do { std::fprintf(stderr, "running %s\n", #call); call; } while (0)
 
-int main() {
+// one refused call (transA is refused in the shim, before any device work): with the reference's log knobs set the
+// caller sees one line for it on stderr, without them none
+static int log_line_only() {
+  matmul_params p;
+  p.dtypes.src = data_type_t::s8; p.dtypes.wei = data_type_t::s8; p.dtypes.dst = data_type_t::bf16;
+  matmul_batch_params_t bp;
+  int8_t a[8] = {0}, w[8] = {0};
+  uint16_t d[4] = {0};
+  status_t st = matmul_direct('r', true, false, 2, 2, 4, 1.0f, a, 4, w, 2, nullptr, 0.0f, d, 2, true, bp, p);
+  return st == status_t::success ? 1 : 0;
+}
+
+int main(int argc, char **argv) {
+  if (argc > 1 && std::string(argv[1]) == "--log-line") return log_line_only();
   RUN(test_int8_u8_zp_bias_relu());
   RUN(test_int8_sym_quant_per_token());
   RUN(test_int8_dynamic_gemm());
+  RUN(test_int8_sym_quant_per_group());
+  RUN(test_w4a8_bf16());
   RUN(test_reorder_and_prepack());
   RUN(test_fused_moe_vs_two_call(false, false, false));
   RUN(test_fused_moe_vs_two_call(true, true, false));

@@ -54,6 +54,7 @@ def ukernel_inputs():
     return A, B, sa, sw, bias
 
 
+PG_GROUPS = [2, 4, 8, 16]
 UK_ACTS = ["none", "silu_and_mul", "gelu_and_mul", "swiglu_oai_mul"]
 
 
@@ -82,6 +83,15 @@ def run(tag):
             out["qu8_" + dt] = O.ref2_granular(wv, "u8", np.array([[0.002]], dtype=np.float32), np.array([13], dtype=np.int32))
             out["deq_" + dt] = O.ref2_granular(q, dt, sc.reshape(1, -1))
         out["w32"] = w32
+        # per-group dynamic quantisation along K (the reference has the AVX-512 kernel only); x32 has K = 96 ... use G that divides it
+        for dt in ("bf16", "f32"):
+            x = O.f32_to_bf16(x32) if dt == "bf16" else x32
+            for G in PG_GROUPS:
+                if x.shape[1] % G:
+                    continue
+                r = O.ref2_quant_per_group(x, G)
+                assert r is not None, "the reference per-group kernel needs AVX-512"
+                out["pg_%s_G%d_q" % (dt, G)], out["pg_%s_G%d_s" % (dt, G)] = r
         A, B, sa, sw, bias = ukernel_inputs()
         for a in UK_ACTS:
             for hb in (0, 1):

@@ -32,6 +32,27 @@ def test_cpp_caller_compiles_and_links():
         assert name in syms, name
 
 
+def test_per_call_log_line_follows_the_reference_env_knobs():
+    """ZENDNNL_API_LOG_LEVEL >= info prints one line per call, ZENDNNL_ENABLE_PROFILER + ZENDNNL_PROFILE_LOG_LEVEL=4 adds the
+    timed line (reference: lowoha_operators/matmul/lowoha_matmul.cpp:468-506, common/config_manager.cpp:273-330); unset, the
+    call prints nothing.  The call here is refused in the shim, so no device is needed."""
+    exe = _compile()
+    env = {k: v for k, v in os.environ.items() if not k.startswith("ZENDNNL_")}
+    quiet = subprocess.run([exe, "--log-line"], capture_output=True, text=True, timeout=120, env=env)
+    assert quiet.returncode == 0 and "LOWOHA matmul_direct" not in quiet.stderr
+    api = subprocess.run([exe, "--log-line"], capture_output=True, text=True, timeout=120, env=dict(env, ZENDNNL_API_LOG_LEVEL="info"))
+    lines = [l for l in api.stderr.splitlines() if "LOWOHA matmul_direct" in l]
+    assert len(lines) == 1 and "M=2, N=2, K=4" in lines[0] and "transA=true" in lines[0] and "input_dtype=s8" in lines[0]
+    assert "output_dtype=bf16" in lines[0] and "time=" not in lines[0]
+    prof = subprocess.run([exe, "--log-line"], capture_output=True, text=True, timeout=120,
+                          env=dict(env, ZENDNNL_ENABLE_PROFILER="1", ZENDNNL_PROFILE_LOG_LEVEL="4"))
+    lines = [l for l in prof.stderr.splitlines() if "LOWOHA matmul_direct" in l]
+    assert len(lines) == 1 and "time=" in lines[0] and " ms" in lines[0]
+    # the profiler alone, at the default profile level, stays silent as the reference's does
+    off = subprocess.run([exe, "--log-line"], capture_output=True, text=True, timeout=120, env=dict(env, ZENDNNL_ENABLE_PROFILER="1"))
+    assert "LOWOHA matmul_direct" not in off.stderr
+
+
 @pytest.mark.gpu
 def test_cpp_caller_runs():
     exe = _compile()

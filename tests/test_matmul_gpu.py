@@ -321,6 +321,8 @@ def test_contract_violations(capi):
     d = mk(); d.lda = 8
     assert capi.matmul(d) == capi.FAILURE
     d = mk(); d.wei_dt = capi.DT["s4"]
+    assert capi.matmul(d) == capi.FAILURE                # s4 weights with a pre-quantised source: refused as in the reference
+    d = mk(); d.wei_dt = capi.DT["u4"]
     assert capi.matmul(d) == capi.UNIMPLEMENTED
     d = mk(src_dt=capi.DT["f32"])
     assert capi.matmul(d) == capi.UNIMPLEMENTED          # float source without dynamic_quant
@@ -452,3 +454,140 @@ def test_two_host_threads_on_two_streams(capi, oracle):
         for out in j["outs"]:
             assert (out.view(torch.int16).cpu().numpy().view(np.uint16) == j["ref"]).all()
     capi.lib.b200dnn_clear_caches()
+
+
+def test_two_devices_in_one_process(capi, oracle):
+    """Library state belongs to the device that is current when a call starts: the same process calls on cuda:0 and on
+    cuda:1 in turn (weights cached per device, scratch per device) and both results are right."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    c = decode_case(oracle, 4, 1024, 512, seed=31)
+    ref = oracle.matmul_w8a8(c["A"], c["W"], "bf16", src_scale=c["sa"], wei_scale=c["sw"])
+    M2, K2, N2 = 300, 512, 384
+    rng = np.random.default_rng(32)
+    A2 = rng.integers(-128, 128, (M2, K2), dtype=np.int8); W2 = rng.integers(-128, 128, (K2, N2), dtype=np.int8)
+    for rnd in range(2):
+        for dev_id in (0, 1):
+            torch.cuda.set_device(dev_id)
+            dev = torch.device("cuda", dev_id)
+            A, W = torch.from_numpy(c["A"]).to(dev), torch.from_numpy(c["W"]).to(dev)
+            sa, sw = torch.from_numpy(c["sa"]).to(dev), torch.from_numpy(c["sw"]).to(dev)
+            out = torch.zeros(4, 512, dtype=torch.bfloat16, device=dev)
+            d = capi.make_matmul(4, 512, 1024, A, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["bf16"], src_scale=sa, wei_scale=sw,
+                                 weights_const=False)
+            st = torch.cuda.current_stream().cuda_stream
+            assert capi.matmul(d, st) == capi.SUCCESS, capi.last_error()
+            assert capi.lib.b200dnn_stream_status(st) == capi.SUCCESS, capi.last_error()
+            assert (out.view(torch.int16).cpu().numpy().view(np.uint16) == ref).all(), (rnd, dev_id)
+            # host buffers through the tcgen05 path on the same device
+            got = run(capi, M2, N2, K2, A2, W2, "s32", weights_const=False, force_kernel=TC)
+            assert (got == oracle.gemm_s32(A2, W2)).all(), (rnd, dev_id)
+    torch.cuda.set_device(0)
+    capi.lib.b200dnn_clear_caches()
+
+
+def _group_case(capi, oracle, Ms, K, N, *, dyn, dst, bias_on, postops, rng, ldc_pad=0):
+    """Build the descriptors of a plain grouped call; returns (array of descriptors, outputs, expected outputs, keepalive)."""
+    G = len(Ms)
+    descs = (capi.MatmulDesc * G)()
+    outs, refs, keep = [], [], []
+    for g, M in enumerate(Ms):
+        W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+        sw = rng.uniform(1e-4, 5e-4, N).astype(np.float32)
+        bias = rng.normal(size=N).astype(np.float32) if bias_on[g] else None
+        rows = max(M, 1)
+        ldc = N + ldc_pad
+        out = np.zeros((rows, ldc), dtype=np.uint16 if dst == "bf16" else np.float32)
+        if dyn:
+            X = oracle.f32_to_bf16(rng.normal(size=(rows, K)).astype(np.float32))
+            A, sa = oracle.quant_per_token(X)
+            d = capi.make_matmul(M, N, K, X, W, out, src_dt=capi.DT["bf16"], dst_dt=capi.DT[dst], ldc=ldc, bias=bias,
+                                 wei_scale=sw, dynamic_quant=True, weights_const=False, postops=postops)
+            keep += [X]
+        else:
+            A = rng.integers(-128, 128, (rows, K), dtype=np.int8)
+            sa = rng.uniform(0.01, 0.05, rows).astype(np.float32)
+            d = capi.make_matmul(M, N, K, A, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT[dst], ldc=ldc, bias=bias,
+                                 src_scale=capi.quant(sa, count=M), wei_scale=sw, weights_const=False, postops=postops)
+        descs[g] = d
+        keep += [A, sa, W, sw, bias]
+        outs.append(out)
+        refs.append(oracle.matmul_w8a8(A[:M], W, dst, src_scale=sa[:M], wei_scale=sw, bias=bias, postops=list(postops)) if M else None)
+    return descs, outs, refs, keep
+
+
+@pytest.mark.parametrize("dyn", [False, True], ids=["s8-rows", "bf16-dynamic"])
+@pytest.mark.parametrize("dst", ["bf16", "f32"])
+def test_group_matmul_one_grouped_launch(capi, oracle, dyn, dst):
+    """The plain (parallel) mode of group_matmul_direct (reference: matmul/lowoha_matmul.hpp:204-223, experts with M == 0
+    skipped, group_matmul_parallel_common.hpp:1240-1248): experts of one shape run as ONE grouped tcgen05 launch whose
+    results are those of separate matmul calls -- checked against the oracle per expert, with ragged and empty experts, a
+    bias on some experts only, padded destinations, and by the number of kernels launched."""
+    rng = np.random.default_rng(17 + dyn)
+    Ms, K, N = [200, 0, 37, 130, 1, 300], 256, 392
+    bias_on = [True, False, False, True, True, False]
+    po = ("relu",)
+    descs, outs, refs, keep = _group_case(capi, oracle, Ms, K, N, dyn=dyn, dst=dst, bias_on=bias_on, postops=po, rng=rng, ldc_pad=8)
+    for g in range(len(Ms)):
+        descs[g].weights_const = 1          # packed once, on the first call
+    capi.check(capi.lib.b200dnn_group_matmul(len(Ms), descs, None))
+    for o in outs:
+        o[:] = 0
+    n0 = capi.lib.b200dnn_launch_count()
+    capi.check(capi.lib.b200dnn_group_matmul(len(Ms), descs, None))
+    launched = capi.lib.b200dnn_launch_count() - n0
+    active = sum(1 for m in Ms if m)
+    assert launched < active, "expected one grouped launch (plus one quantisation launch), saw %d launches" % launched
+    capi.lib.b200dnn_clear_caches()
+    for g, M in enumerate(Ms):
+        if not M:
+            assert not outs[g].any()
+            continue
+        got = outs[g][:M, :N]
+        if dst == "bf16":
+            assert_bf16_close(got, refs[g], 1, "expert %d" % g, atol=1e-5)
+        else:
+            assert np.allclose(got, refs[g], rtol=1e-5, atol=1e-5), g
+        assert not outs[g][:, N:].any(), "padding columns of expert %d were written" % g
+
+
+def test_group_matmul_equals_separate_calls_bit_for_bit(capi, oracle, monkeypatch):
+    """Grouped launch against the same descriptors run one by one (B200DNN_GROUPED_PLAIN=0): identical bytes."""
+    rng = np.random.default_rng(5)
+    Ms, K, N = [129, 64, 0, 257], 512, 264
+    descs, outs, refs, keep = _group_case(capi, oracle, Ms, K, N, dyn=False, dst="bf16", bias_on=[True] * 4, postops=(), rng=rng)
+    capi.check(capi.lib.b200dnn_group_matmul(len(Ms), descs, None))
+    grouped = [o.copy() for o in outs]
+    for o in outs:
+        o[:] = 0
+    monkeypatch.setenv("B200DNN_GROUPED_PLAIN", "0")
+    capi.check(capi.lib.b200dnn_group_matmul(len(Ms), descs, None))
+    for g in range(len(Ms)):
+        assert (grouped[g] == outs[g]).all(), g
+
+
+def test_group_matmul_mixed_shapes_run_one_by_one(capi, oracle):
+    """Experts that do not share one shape (here: differing N, and one decode-sized expert with a zero point) still
+    compute, one launch each."""
+    rng = np.random.default_rng(9)
+    G = 3
+    descs = (capi.MatmulDesc * G)()
+    outs, refs, keep = [], [], []
+    for g, (M, K, N) in enumerate([(40, 256, 128), (150, 256, 264), (3, 512, 136)]):
+        A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+        W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+        sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+        sw = rng.uniform(1e-4, 5e-4, N).astype(np.float32)
+        out = np.zeros((M, N), dtype=np.uint16)
+        descs[g] = capi.make_matmul(M, N, K, A, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["bf16"], src_scale=sa, wei_scale=sw,
+                                    weights_const=False)
+        keep += [A, W, sa, sw]
+        outs.append(out)
+        refs.append(oracle.matmul_w8a8(A, W, "bf16", src_scale=sa, wei_scale=sw))
+    capi.check(capi.lib.b200dnn_group_matmul(G, descs, None))
+    for g in range(G):
+        assert (outs[g] == refs[g]).all(), g
+    # a negative M is refused
+    descs[1].M = -1
+    assert capi.lib.b200dnn_group_matmul(G, descs, None) == capi.FAILURE

@@ -312,3 +312,73 @@ def test_live_reference_microkernel_if_present(oracle):
     ref = oracle.ref2_int8_ukernel(A, B, sa, sw, None, "silu_and_mul")
     got = _oracle_dq_int8(oracle, A, B, sa, sw, None, "silu_and_mul")
     assert np.abs(ref.astype(np.int32) - got.astype(np.int32)).max() <= 1
+
+
+def test_group_scaled_oracle_reduces_to_the_per_token_form(oracle):
+    """With one group the per-group definition (operators/matmul/matmul_ref_kernel.cpp:961-1003) is the per-token
+    epilogue order that the golden reference cases pin: (acc * src_scale[m]) * wei_scale[n] + bias."""
+    rng = np.random.default_rng(0)
+    M, K, N = 9, 96, 40
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    sw = rng.uniform(1e-3, 5e-3, N).astype(np.float32)
+    bias = rng.normal(size=N).astype(np.float32)
+    for dst in ("bf16", "f32"):
+        a = oracle.matmul_w8a8(A, B, dst, src_scale=sa, wei_scale=sw, bias=bias, postops=["gelu_tanh"])
+        b = oracle.matmul_group_scaled(A, B, sa, sw[None, :], dst, bias=bias, postops=["gelu_tanh"])
+        assert (a == b).all()
+    # several groups: the same sums written with numpy, one f32 rounding per operation, groups in order
+    G = 4
+    sag = rng.uniform(0.01, 0.05, (M, G)).astype(np.float32)
+    swg = rng.uniform(1e-3, 5e-3, (G, N)).astype(np.float32)
+    ref = np.zeros((M, N), np.float32)
+    for g in range(G):
+        ks = slice(g * K // G, (g + 1) * K // G)
+        acc = (A[:, ks].astype(np.int32) @ B[ks].astype(np.int32)).astype(np.float32)
+        ref = ref + (acc * sag[:, g:g + 1]) * swg[g][None, :]
+    assert (oracle.matmul_group_scaled(A, B, sag, swg, "f32") == ref).all()
+    # a per-token source scale is the same scale in every group
+    assert (oracle.matmul_group_scaled(A, B, sa, swg, "f32") ==
+            oracle.matmul_group_scaled(A, B, np.repeat(sa[:, None], G, 1), swg, "f32")).all()
+
+
+def test_s4_packing_follows_the_reference_index_rule(oracle):
+    """Element (k,n) at physical index k*ldb+n (transB: n*ldb+k), even index in the low nibble, sign-extended on the way
+    out (matmul/backends/aocl/aocl_kernel.cpp:33-42,145-160)."""
+    W = np.array([[-8, 7, 1], [2, -1, 0], [3, -3, 5], [-7, 6, -2]], dtype=np.int8)     # K=4, N=3
+    p = oracle.pack_s4(W)
+    assert p[0] == ((7 & 0xF) << 4 | (-8 & 0xF)) and p[1] == ((2 & 0xF) << 4 | 1)
+    assert (oracle.unpack_s4(p, 4, 3) == W).all()
+    pt = oracle.pack_s4(W, transB=True)
+    assert pt[0] == ((2 & 0xF) << 4 | (-8 & 0xF))
+    assert (oracle.unpack_s4(pt, 4, 3, transB=True) == W).all()
+    rng = np.random.default_rng(1)
+    W = rng.integers(-8, 8, (64, 24), dtype=np.int8)
+    assert (oracle.unpack_s4(oracle.pack_s4(W, ldb=30), 64, 24, ldb=30) == W).all()
+
+
+def test_per_group_dynamic_quant_is_the_per_token_rule_on_each_group(oracle):
+    rng = np.random.default_rng(2)
+    x = oracle.f32_to_bf16(rng.normal(size=(6, 128)).astype(np.float32))
+    q, s = oracle.quant_per_group(x, 4)
+    for g in range(4):
+        qg, sg = oracle.quant_per_token(np.ascontiguousarray(x[:, g * 32:(g + 1) * 32]))
+        assert (q[:, g * 32:(g + 1) * 32] == qg).all() and (s[:, g] == sg).all()
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_per_group_dynamic_quant_equals_reference_kernel(oracle, golden2, dt):
+    """The oracle's per-group quantisation against the reference's AVX-512 per-group kernel
+    (reorder/reorder_data_type/dynamic_quant_impl/per_group_avx512_f32_fma_kernel.cpp), rows with inf / nan and an all-zero
+    row included: scales and s8 codes bit for bit."""
+    x = _as(oracle, golden2["x32"], dt)
+    seen = 0
+    for G in (2, 4, 8, 16):
+        if "pg_%s_G%d_q" % (dt, G) not in golden2.files:
+            continue
+        q, s = oracle.quant_per_group(x, G)
+        assert (s == golden2["pg_%s_G%d_s" % (dt, G)]).all(), G
+        assert (q == golden2["pg_%s_G%d_q" % (dt, G)]).all(), G
+        seen += 1
+    assert seen >= 3

@@ -74,6 +74,44 @@ def test_group_dynamic_quant(capi, oracle):
         assert (q[:m] == q_ref).all() and (s[:m] == s_ref).all()
 
 
+def test_group_dynamic_quant_with_differing_row_lengths(capi, oracle):
+    """The reference lets K differ per group (lowoha_operators/reorder/lowoha_reorder.cpp:279-400): groups of one row
+    length share a launch, every group gets its own K -- also when the first group is empty and a smaller group follows a
+    larger one (a group must never be read or written with another group's row length)."""
+    rng = np.random.default_rng(4)
+    Ms, Ks = [0, 6, 4, 3, 5], [128, 256, 64, 256, 100]
+    G = len(Ms)
+    xs = [oracle.f32_to_bf16(rng.normal(size=(max(m, 1), k)).astype(np.float32)) for m, k in zip(Ms, Ks)]
+    qs = [np.full((max(m, 1) + 1, k), 7, dtype=np.int8) for m, k in zip(Ms, Ks)]     # one guard row each
+    ss = [np.full(max(m, 1) + 1, -1.0, dtype=np.float32) for m in Ms]
+    arr = lambda xs_: (C.c_void_p * G)(*[x.ctypes.data for x in xs_])
+    Mv = (C.c_int32 * G)(*Ms); Kv = (C.c_int32 * G)(*Ks); ld = (C.c_int64 * G)(*Ks)
+    st = capi.lib.b200dnn_group_quant_per_token(G, arr(xs), capi.DT["bf16"], Mv, Kv, ld, arr(qs), ld, arr(ss), capi.DT["f32"], None)
+    assert st == capi.SUCCESS, capi.last_error()
+    for m, x, q, s in zip(Ms, xs, qs, ss):
+        assert (q[m:] == 7).all() and (s[m:] == -1.0).all(), "rows beyond M were written"
+        if m:
+            q_ref, s_ref = oracle.quant_per_token(x[:m])
+            assert (q[:m] == q_ref).all() and (s[:m] == s_ref).all()
+
+
+@pytest.mark.parametrize("G", [2, 8, 32])
+def test_per_group_dynamic_quant_through_the_per_token_entry(capi, oracle, G):
+    """Per-group dynamic quantisation along K (scale layout {M,G}; reference kernel
+    reorder/reorder_data_type/dynamic_quant_impl/per_group_avx512_f32_fma_kernel.cpp, to which the oracle is pinned): the
+    C++ shims pass every (row, group) as a row of K/G elements."""
+    rng = np.random.default_rng(G)
+    M, K = 19, 256
+    x = oracle.f32_to_bf16((rng.normal(size=(M, K)) * rng.uniform(0.01, 30, size=(M, 1))).astype(np.float32))
+    x[3, 5] = 0x7F80     # +inf
+    q = np.zeros((M, K), dtype=np.int8); s = np.zeros((M, G), dtype=np.float32)
+    gs = K // G
+    st = capi.lib.b200dnn_quant_per_token(capi.ptr(x), capi.DT["bf16"], M * G, gs, gs, capi.ptr(q), gs, capi.ptr(s), capi.DT["f32"], None)
+    assert st == capi.SUCCESS, capi.last_error()
+    q_ref, s_ref = oracle.quant_per_group(x, G)
+    assert (q == q_ref).all() and (s == s_ref).all()
+
+
 @pytest.mark.parametrize("K,N", [(64, 16), (300, 40), (4096, 1024)])
 def test_per_channel_weight_quant(capi, oracle, K, N):
     rng = np.random.default_rng(K)

@@ -67,7 +67,7 @@ PHASE_NAMES = ["route+rank", "count exchange", "quantise+dispatch", "barrier aft
 EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b200dnn_launch_count",
            "b200dnn_matmul", "b200dnn_matmul_static_scratch", "b200dnn_static_scratch_query", "b200dnn_prepack_size", "b200dnn_prepack", "b200dnn_quant_per_token",
            "b200dnn_group_quant_per_token", "b200dnn_quant_dynamic", "b200dnn_quant_static",
-           "b200dnn_dequant_static", "b200dnn_gated_act", "b200dnn_moe_weighted_reduce", "b200dnn_fused_moe",
+           "b200dnn_dequant_static", "b200dnn_gated_act", "b200dnn_moe_weighted_reduce", "b200dnn_fused_moe", "b200dnn_group_matmul",
            "b200dnn_moe_route", "b200dnn_moe_layer", "b200dnn_clear_caches", "b200dnn_stream_status", "b200dnn_moe_sort_slots",
            "b200dnn_quant_per_token_gather", "b200dnn_quant_per_token_scatter", "b200dnn_moe_experts_s8",
            "b200dnn_moe_weighted_reduce_rows", "b200dnn_ep_create", "b200dnn_ep_destroy", "b200dnn_ep_local_expert_count",
@@ -97,6 +97,7 @@ lib.b200dnn_quant_static.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i64, v
 lib.b200dnn_dequant_static.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i64, vp, i32, i64, vp]
 lib.b200dnn_gated_act.argtypes = [vp, i32, i64, i64, i64, i32, vp]
 lib.b200dnn_moe_weighted_reduce.argtypes = [vp, vp, i32, i32, i32, i32, i32, vp, i64, vp]
+lib.b200dnn_group_matmul.argtypes = [i32, C.POINTER(MatmulDesc), vp]
 lib.b200dnn_fused_moe.argtypes = [i32, C.POINTER(MoeExpert), i32, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, i64, vp]
 lib.b200dnn_moe_route.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
 lib.b200dnn_moe_layer.argtypes = [vp, i64, vp, i32, i32, i32, i32, C.POINTER(MoeExpert), i32, i32, i32, i32, i32, vp, i64, vp]
@@ -175,10 +176,10 @@ def quant(buf, count=None, dt=None):
 
 def make_matmul(M, N, K, src, weight, dst, *, src_dt, dst_dt, lda=None, ldb=None, ldc=None, transB=False,
                 bias=None, bias_dt=None, wei_format="n", weights_const=True, dynamic_quant=False,
-                src_scale=None, wei_scale=None, src_zp=None, postops=(), force_kernel=0, flags=0):
+                src_scale=None, wei_scale=None, src_zp=None, postops=(), force_kernel=0, flags=0, wei_dt=None):
     d = MatmulDesc()
     d.M, d.N, d.K, d.transB = M, N, K, int(transB)
-    d.src_dt, d.wei_dt, d.dst_dt = src_dt, DT["s8"], dst_dt
+    d.src_dt, d.wei_dt, d.dst_dt = src_dt, (DT["s8"] if wei_dt is None else wei_dt), dst_dt
     d.bias_dt = bias_dt if bias_dt is not None else (dt_of(bias) if bias is not None else 0)
     d.lda = lda if lda is not None else K
     d.ldb = ldb if ldb is not None else (K if transB else N)

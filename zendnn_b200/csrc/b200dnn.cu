@@ -3,6 +3,7 @@
 // (matmul/lowoha_matmul_utils.cpp:180-420) for the supported subset; everything else returns
 // unimplemented, never a different computation.
 #include <cudaTypedefs.h>
+#include <algorithm>
 #include <chrono>
 
 #include "runtime.cuh"
@@ -568,6 +569,8 @@ int32_t fill_epi(const b200dnn_matmul_t *d, EpiParams *e) {
 
 }  // namespace
 
+#include "gs_api.cuh"
+
 // =========================================================================================== C ABI
 extern "C" {
 
@@ -628,17 +631,14 @@ int32_t b200dnn_group_quant_per_token(int32_t num_groups, const void *const *src
                                       void *const *scale, int32_t scale_dt, void *stream) {
   B2_ENTER(stream);
   B2_CHECK(num_groups > 0 && src && M && K && src_ld && dst && dst_ld && scale, B200DNN_FAILURE, "null argument");
-  // groups with the same K share one launch; the reference allows K to differ per group, handled per K value
+  // groups of one row length share a launch; the reference lets K differ per group (reorder/lowoha_reorder.cpp:279-400):
+  // one launch per distinct K
   std::vector<Staged> outs;
   outs.reserve(2 * num_groups);
   std::vector<const void *> s_dev(num_groups); std::vector<void *> d_dev(num_groups), sc_dev(num_groups);
-  std::vector<int32_t> row_off(num_groups + 1, 0);
-  // one launch serves groups of one row length: K of the first group that has rows; a different K elsewhere is refused
-  int Kc = 0; for (int g = 0; g < num_groups; ++g) if (M[g] > 0) { Kc = K[g]; break; }
+  std::vector<int> distinct_k;
   for (int g = 0; g < num_groups; ++g) {
-    row_off[g + 1] = row_off[g] + (M[g] > 0 ? M[g] : 0);
     if (M[g] <= 0) { s_dev[g] = nullptr; d_dev[g] = nullptr; sc_dev[g] = nullptr; continue; }
-    B2_CHECK(K[g] == Kc, B200DNN_UNIMPLEMENTED, "group_dynamic_quant: differing K per group (group %d has K=%d, the first group with rows has K=%d)", g, K[g], Kc);
     B2_CHECK(K[g] > 0 && (!dst[g] || dst_ld[g] >= K[g]), B200DNN_FAILURE, "group %d: bad K or destination stride", g);
     B2_CHECK(src[g] && scale[g] && src_ld[g] >= K[g], B200DNN_FAILURE, "group %d: null pointer or bad stride", g);
     B2_TRY(stage_in(src[g], span_bytes(M[g], K[g], src_ld[g], src_dt), st, &s_dev[g]));
@@ -646,25 +646,30 @@ int32_t b200dnn_group_quant_per_token(int32_t num_groups, const void *const *src
     B2_TRY(stage_out(dst[g], span_bytes(M[g], K[g], dst_ld[g], B200DNN_S8), st, &a, dst[g] && dst_ld[g] != K[g]));
     B2_TRY(stage_out(scale[g], (size_t)M[g] * dt_size(scale_dt), st, &b));
     d_dev[g] = a.dev; sc_dev[g] = b.dev; outs.push_back(a); outs.push_back(b);
+    if (std::find(distinct_k.begin(), distinct_k.end(), K[g]) == distinct_k.end()) distinct_k.push_back(K[g]);
   }
-  if (row_off[num_groups] == 0) return B200DNN_SUCCESS;
-  // device tables
-  const size_t tb = sizeof(void *) * num_groups;
-  std::vector<uint8_t> host(3 * tb + 2 * sizeof(int64_t) * num_groups + sizeof(int32_t) * (num_groups + 1));
-  uint8_t *h = host.data();
-  memcpy(h, s_dev.data(), tb); memcpy(h + tb, d_dev.data(), tb); memcpy(h + 2 * tb, sc_dev.data(), tb);
-  memcpy(h + 3 * tb, src_ld, sizeof(int64_t) * num_groups);
-  memcpy(h + 3 * tb + sizeof(int64_t) * num_groups, dst_ld, sizeof(int64_t) * num_groups);
-  memcpy(h + 3 * tb + 2 * sizeof(int64_t) * num_groups, row_off.data(), sizeof(int32_t) * (num_groups + 1));
-  void *tab_dev = nullptr;
-  B2_TRY(upload_blob(h, host.size(), st, &tab_dev));
-  uint8_t *tab = (uint8_t *)tab_dev;
-  RowQuantArgs a{};
-  a.n_groups = num_groups; a.K = Kc; a.scale_dt = scale_dt; a.gather_div = 1;
-  a.g_src = (const void *const *)tab; a.g_dst = (void *const *)(tab + tb); a.g_scale = (void *const *)(tab + 2 * tb);
-  a.g_src_ld = (const int64_t *)(tab + 3 * tb); a.g_dst_ld = (const int64_t *)(tab + 3 * tb + sizeof(int64_t) * num_groups);
-  a.row_off = (const int32_t *)(tab + 3 * tb + 2 * sizeof(int64_t) * num_groups);
-  B2_TRY(launch_quant_rows(a, src_dt, row_off[num_groups], st));
+  if (distinct_k.empty()) return B200DNN_SUCCESS;
+  for (int Kc : distinct_k) {
+    // groups of another row length have no rows in this launch
+    std::vector<int32_t> row_off(num_groups + 1, 0);
+    for (int g = 0; g < num_groups; ++g) row_off[g + 1] = row_off[g] + ((M[g] > 0 && K[g] == Kc) ? M[g] : 0);
+    const size_t tb = sizeof(void *) * num_groups;
+    std::vector<uint8_t> host(3 * tb + 2 * sizeof(int64_t) * num_groups + sizeof(int32_t) * (num_groups + 1));
+    uint8_t *h = host.data();
+    memcpy(h, s_dev.data(), tb); memcpy(h + tb, d_dev.data(), tb); memcpy(h + 2 * tb, sc_dev.data(), tb);
+    memcpy(h + 3 * tb, src_ld, sizeof(int64_t) * num_groups);
+    memcpy(h + 3 * tb + sizeof(int64_t) * num_groups, dst_ld, sizeof(int64_t) * num_groups);
+    memcpy(h + 3 * tb + 2 * sizeof(int64_t) * num_groups, row_off.data(), sizeof(int32_t) * (num_groups + 1));
+    void *tab_dev = nullptr;
+    B2_TRY(upload_blob(h, host.size(), st, &tab_dev));
+    uint8_t *tab = (uint8_t *)tab_dev;
+    RowQuantArgs a{};
+    a.n_groups = num_groups; a.K = Kc; a.scale_dt = scale_dt; a.gather_div = 1;
+    a.g_src = (const void *const *)tab; a.g_dst = (void *const *)(tab + tb); a.g_scale = (void *const *)(tab + 2 * tb);
+    a.g_src_ld = (const int64_t *)(tab + 3 * tb); a.g_dst_ld = (const int64_t *)(tab + 3 * tb + sizeof(int64_t) * num_groups);
+    a.row_off = (const int32_t *)(tab + 3 * tb + 2 * sizeof(int64_t) * num_groups);
+    B2_TRY(launch_quant_rows(a, src_dt, row_off[num_groups], st));
+  }
   bool any = false;
   for (auto &s : outs) { if (s.copy_back) { B2_CUDA(cudaMemcpyAsync(s.host, s.dev, s.bytes, cudaMemcpyDeviceToHost, st)); any = true; } else if (s.sync) any = true; }
   if (any) B2_CUDA(cudaStreamSynchronize(st));
@@ -875,6 +880,7 @@ int32_t b200dnn_moe_route(const float *logits, int32_t T, int32_t E, int32_t top
 int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   B2_CHECK(d, B200DNN_FAILURE, "null descriptor");
   B2_ENTER(stream);
+  if (is_group_scaled(d)) return matmul_group_scaled(d, st);   // per-group scales and W4A8: own validation and kernel
   Runtime &R = rt();
   const int M = d->M, N = d->N, K = d->K;
   B2_TRY(validate_matmul_desc(d));
@@ -1037,3 +1043,4 @@ int32_t b200dnn_clear_caches(void) {
 
 #include "moe_api.cuh"
 #include "moe_ep.cuh"
+#include "group_api.cuh"

@@ -1,0 +1,209 @@
+// Host side of the group-scaled INT8 matmul (per-group scales, W4A8): detection, the reference's contract checks
+// (matmul/lowoha_matmul_utils.cpp:72-178), weight preparation with the weight cache, source quantisation and the launch
+// of gs_gemm_kernel.  Included by b200dnn.cu in front of the C ABI.
+#pragma once
+#include "gs_gemm.cuh"
+
+namespace {
+
+// weight-cache layout codes stored in the `gated` slot of the cache key
+constexpr int kGsLayoutS8 = 16, kGsLayoutS4 = 17;
+
+// A descriptor takes this path when its weights are 4-bit or one of its scales has more than one value per row /
+// column ({M,G} source scales, {G,N} weight scales).
+inline bool is_group_scaled(const b200dnn_matmul_t *d) {
+  if (d->wei_dt == B200DNN_S4) return true;
+  if (d->N > 0 && d->wei_scale.count > d->N) return true;
+  if (d->M > 0 && d->src_scale.count > d->M) return true;
+  return false;
+}
+
+struct GsPlan { int G; int gs; bool w4; bool dyn; int src_cols; };
+
+int32_t validate_group_scaled(const b200dnn_matmul_t *d, GsPlan *p) {
+  const int M = d->M, N = d->N, K = d->K;
+  B2_CHECK(d->src && d->weight && d->dst, B200DNN_FAILURE, "null src, weight or dst");
+  B2_CHECK(M > 0 && N > 0 && K > 0, B200DNN_FAILURE, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
+  B2_CHECK(d->lda >= K && d->ldc >= N && d->ldb >= (d->transB ? K : N), B200DNN_FAILURE, "leading dimension smaller than the row length");
+  B2_CHECK(d->wei_dt == B200DNN_S8 || d->wei_dt == B200DNN_S4, B200DNN_UNIMPLEMENTED, "weight dtype %d (s8 and s4 are implemented)", d->wei_dt);
+  B2_CHECK(d->wei_format == 'n' || d->wei_format == 0, B200DNN_UNIMPLEMENTED, "prepacked weights are not implemented for per-group scales / s4 weights");
+  B2_CHECK(d->n_postops >= 0 && d->n_postops <= B200DNN_MAX_POSTOPS, B200DNN_FAILURE, "too many post-ops");
+  const bool w4 = d->wei_dt == B200DNN_S4, dyn = d->dynamic_quant != 0;
+  if (w4) {
+    // W4A8 contract, in the reference's words (lowoha_matmul_utils.cpp:72-100)
+    B2_CHECK(d->src_dt != B200DNN_S8, B200DNN_FAILURE, "W4A8 requires bf16 source with dynamic_quant=true (pre-quantized s8 source is not supported)");
+    B2_CHECK(d->src_dt != B200DNN_U8, B200DNN_FAILURE, "S4 weights do not support u8 source; W4A8 requires bf16 source with dynamic_quant=true");
+    B2_CHECK(dyn && d->src_dt == B200DNN_BF16, B200DNN_UNIMPLEMENTED, "s4 weights are implemented for W4A8 only (bf16 source, dynamic_quant)");
+    B2_CHECK(d->dst_dt == B200DNN_BF16, B200DNN_FAILURE, "W4A8 dynamic quantization requires bf16 output");
+  } else if (dyn) {
+    B2_CHECK(d->src_dt == B200DNN_BF16 || d->src_dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "dynamic quantisation takes a bf16 or f32 source");
+  } else {
+    B2_CHECK(d->src_dt == B200DNN_S8, B200DNN_FAILURE, "per-group source scales need a symmetric s8 source");
+  }
+  B2_CHECK(d->dst_dt == B200DNN_BF16 || d->dst_dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "per-group scales need a bf16 or f32 destination");
+  B2_CHECK(!d->src_zp.buff, B200DNN_FAILURE, "per-group / W4A8 supports symmetric quantization only");
+  // weight scales {G,N}
+  const auto &ws = d->wei_scale;
+  B2_CHECK(ws.buff, B200DNN_FAILURE, "per-group / W4A8 requires quant_params.wei_scale.buff");
+  B2_CHECK(ws.dt == B200DNN_F32 || ws.dt == B200DNN_BF16, B200DNN_FAILURE, "weight scale supports only f32 or bf16 data type");
+  B2_CHECK(ws.count >= N && ws.count % N == 0, B200DNN_FAILURE, "weight scale dims must be {G,N} (count %lld, N %d)", (long long)ws.count, N);
+  const int64_t G = ws.count / N;
+  B2_CHECK(K % G == 0, B200DNN_FAILURE, "K must be divisible by the weight group count (K=%d, G=%lld)", K, (long long)G);
+  const int64_t gs = K / G;
+  B2_CHECK(gs % 4 == 0, B200DNN_FAILURE, "K/G must be a multiple of 4 (got group_size=%lld)", (long long)gs);
+  B2_CHECK(gs == 4 || gs == 8 || gs == 16 || gs % 32 == 0, B200DNN_UNIMPLEMENTED,
+           "group sizes 4, 8, 16 and multiples of 32 are implemented (got %lld)", (long long)gs);
+  // source scales {M,G}, or {M,1} when the library quantises per token
+  const auto &ss = d->src_scale;
+  int src_cols;
+  if (ss.count == (int64_t)M * G) src_cols = (int)G;
+  else if (dyn && (ss.count == M || ss.count == 0)) src_cols = 1;
+  else if (dyn && ss.count == 1) return fail(B200DNN_UNIMPLEMENTED, "per-tensor dynamic source scale is not implemented with per-group weight scales");
+  else return fail(B200DNN_FAILURE, "source scale dims must be {M,G}%s (count %lld, M %d, G %lld)", dyn ? " or {M,1}" : "", (long long)ss.count, M, (long long)G);
+  if (!dyn) B2_CHECK(ss.buff && ss.dt == B200DNN_F32, ss.buff ? B200DNN_UNIMPLEMENTED : B200DNN_FAILURE, "per-group source scales: an f32 buffer is required");
+  else B2_CHECK(!ss.buff || ss.dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "dynamic per-group source scales are written as f32");
+  B2_CHECK(!d->bias || d->bias_dt == B200DNN_F32 || d->bias_dt == B200DNN_BF16, B200DNN_UNIMPLEMENTED, "bias dtype %d", d->bias_dt);
+  for (int i = 0; i < d->n_postops; ++i) {
+    const b200dnn_postop_t &po = d->postops[i];
+    switch (po.type) {
+    case PO_RELU: case PO_LEAKY_RELU: case PO_GELU_TANH: case PO_GELU_ERF: case PO_SIGMOID: case PO_SWISH: case PO_TANH: case PO_ELU: case PO_CLIP: break;
+    case PO_BINARY_ADD: case PO_BINARY_MUL:
+      B2_CHECK(po.buff && (po.dt == B200DNN_F32 || po.dt == B200DNN_BF16), B200DNN_FAILURE, "binary post-op needs an f32 or bf16 operand");
+      B2_CHECK(po.ld == 0 || po.ld >= N, B200DNN_FAILURE, "binary post-op leading dimension");
+      break;
+    case PO_MISH: return fail(B200DNN_FAILURE, "mish is rejected on the INT8 path");
+    default: return fail(B200DNN_UNIMPLEMENTED, "post-op %d is not implemented", po.type);
+    }
+  }
+  p->G = (int)G; p->gs = (int)gs; p->w4 = w4; p->dyn = dyn; p->src_cols = src_cols;
+  return B200DNN_SUCCESS;
+}
+
+// [N][Kp] s8 / [N][Kp/2] s4 copy of the weight, cached per (pointer, shape, layout) like the packed tcgen05 weights.
+int32_t resolve_gs_weight(const b200dnn_matmul_t *d, bool w4, int64_t Kp, cudaStream_t st, PackedWeight *pw) {
+  DeviceShared &D = *rt().shared;
+  const int K = d->K, N = d->N;
+  auto key = std::make_tuple(d->weight, (int64_t)K, (int64_t)N, (int64_t)d->ldb, (int)d->transB, w4 ? kGsLayoutS4 : kGsLayoutS8);
+  const bool cache = d->weights_const && env_int("ZENDNNL_MATMUL_WEIGHT_CACHE", 1) != 0;
+  std::unique_lock<std::mutex> lk(D.cache_mu, std::defer_lock);
+  if (cache) {
+    lk.lock();
+    auto it = D.wcache.find(key);
+    if (it != D.wcache.end()) { B2_TRY(wait_ready(it->second, st)); *pw = it->second; return B200DNN_SUCCESS; }
+  }
+  const int64_t wrows = d->transB ? N : K, wcols = d->transB ? K : N;
+  const size_t src_bytes = w4 ? (size_t)(((wrows - 1) * d->ldb + wcols + 1) / 2) : span_bytes(wrows, wcols, d->ldb, B200DNN_S8);
+  const void *w_dev = nullptr;
+  B2_TRY(stage_in(d->weight, src_bytes, st, &w_dev));
+  const size_t bytes = (size_t)N * (w4 ? Kp / 2 : Kp);
+  void *buf = nullptr;
+  if (cache) B2_CUDA(cudaMalloc(&buf, bytes));
+  else { buf = rt().ws.alloc(bytes); B2_CHECK(buf, B200DNN_FAILURE, "workspace allocation failed"); }
+  const int64_t threads = (Kp / 2) * N;
+  gs_pack_weight_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const uint8_t *)w_dev, d->ldb, d->transB, w4 ? 1 : 0, K, N, (int)Kp, (uint8_t *)buf);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  *pw = PackedWeight{};
+  pw->wt = (const int8_t *)buf; pw->K = K; pw->N = N; pw->Kp = Kp; pw->Np = N; pw->gated = w4 ? kGsLayoutS4 : kGsLayoutS8;
+  if (cache) { pw->owned = buf; B2_TRY(mark_ready(*pw, st)); D.wcache.emplace(key, *pw); }
+  return B200DNN_SUCCESS;
+}
+
+template <int NT, int CH>
+int32_t launch_gs_t(const GsGemmArgs &a, const EpiParams &epi, cudaStream_t st) {
+  dim3 grid((unsigned)((a.N + NT * 8 - 1) / (NT * 8)), (unsigned)((a.M + a.MT * 16 - 1) / (a.MT * 16)));
+  if (a.w4) gs_gemm_kernel<NT, CH, true><<<grid, kGsWarps * 32, 0, st>>>(a, epi);
+  else gs_gemm_kernel<NT, CH, false><<<grid, kGsWarps * 32, 0, st>>>(a, epi);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return B200DNN_SUCCESS;
+}
+
+// The whole call; the caller holds the call guard (B2_ENTER) and has checked is_group_scaled().
+int32_t matmul_group_scaled(const b200dnn_matmul_t *d, cudaStream_t st) {
+  Runtime &R = rt();
+  GsPlan p;
+  B2_TRY(validate_group_scaled(d, &p));
+  const int M = d->M, N = d->N, K = d->K;
+  const int64_t Kp = round_up(K, 64);
+  PackedWeight pw;
+  B2_TRY(resolve_gs_weight(d, p.w4, Kp, st, &pw));
+
+  // ---- source rows: s8 [M][Kp], zero padded, and f32 scales [M][src_cols]
+  int8_t *A = (int8_t *)R.ws.alloc((size_t)M * Kp);
+  B2_CHECK(A, B200DNN_FAILURE, "workspace allocation failed");
+  if (Kp != K) B2_CUDA(cudaMemsetAsync(A, 0, (size_t)M * Kp, st));
+  const void *src_dev = nullptr;
+  B2_TRY(stage_in(d->src, span_bytes(M, K, d->lda, d->src_dt), st, &src_dev));
+  Staged o_scale; o_scale.copy_back = false;
+  const float *sa = nullptr;
+  if (p.dyn) {
+    const int64_t n_sc = (int64_t)M * p.src_cols;
+    B2_TRY(stage_out(const_cast<void *>(d->src_scale.buff), (size_t)n_sc * 4, st, &o_scale));
+    float *sc = (float *)o_scale.dev;
+    if (!sc) { sc = (float *)R.ws.alloc((size_t)n_sc * 4); B2_CHECK(sc, B200DNN_FAILURE, "workspace allocation failed"); }
+    RowQuantArgs qa{};
+    qa.gather_div = 1; qa.scale = sc; qa.scale_dt = B200DNN_F32;
+    if (p.src_cols == 1) {
+      qa.src = src_dev; qa.src_ld = d->lda; qa.dst = A; qa.dst_ld = Kp; qa.K = K;
+      B2_TRY(launch_quant_rows(qa, d->src_dt, M, st));
+    } else {
+      // every (row, group) is a row of gs elements; needs rows that follow each other without gaps
+      const size_t esz = dt_size(d->src_dt);
+      const void *xs = src_dev;
+      if (d->lda != K) {
+        void *x = R.ws.alloc((size_t)M * K * esz);
+        B2_CHECK(x, B200DNN_FAILURE, "workspace allocation failed");
+        B2_CUDA(cudaMemcpy2DAsync(x, (size_t)K * esz, src_dev, (size_t)d->lda * esz, (size_t)K * esz, (size_t)M, cudaMemcpyDeviceToDevice, st));
+        xs = x;
+      }
+      int8_t *q = A;
+      if (Kp != K) { q = (int8_t *)R.ws.alloc((size_t)M * K); B2_CHECK(q, B200DNN_FAILURE, "workspace allocation failed"); }
+      qa.src = xs; qa.src_ld = p.gs; qa.dst = q; qa.dst_ld = p.gs; qa.K = p.gs;
+      B2_TRY(launch_quant_rows(qa, d->src_dt, (int64_t)M * p.G, st));
+      if (q != A) B2_CUDA(cudaMemcpy2DAsync(A, (size_t)Kp, q, (size_t)K, (size_t)K, (size_t)M, cudaMemcpyDeviceToDevice, st));
+    }
+    sa = sc;
+  } else {
+    B2_CUDA(cudaMemcpy2DAsync(A, (size_t)Kp, src_dev, (size_t)d->lda, (size_t)K, (size_t)M, cudaMemcpyDefault, st));
+    const void *s = nullptr;
+    B2_TRY(stage_in(d->src_scale.buff, (size_t)M * p.src_cols * 4, st, &s));
+    sa = (const float *)s;
+  }
+
+  // ---- epilogue operands
+  EpiParams epi;
+  fill_epi(d, &epi);
+  const void *ws_dev = nullptr;
+  B2_TRY(stage_in(d->wei_scale.buff, (size_t)d->wei_scale.count * dt_size(d->wei_scale.dt), st, &ws_dev));
+  if (d->bias) { const void *b; B2_TRY(stage_in(d->bias, (size_t)N * dt_size(d->bias_dt), st, &b)); epi.bias = b; }
+  for (int i = 0; i < d->n_postops; ++i) {
+    const b200dnn_postop_t &po = d->postops[i];
+    epi.po[i].type = po.type; epi.po[i].dt = po.dt; epi.po[i].ld = po.ld; epi.po[i].alpha = po.alpha; epi.po[i].beta = po.beta;
+    epi.po[i].buff = nullptr;
+    if (po.type == PO_BINARY_ADD || po.type == PO_BINARY_MUL) {
+      const void *b;
+      B2_TRY(stage_in(po.buff, po.ld ? span_bytes(M, N, po.ld, po.dt) : (size_t)N * dt_size(po.dt), st, &b));
+      epi.po[i].buff = b;
+    }
+  }
+  Staged o_dst;
+  B2_TRY(stage_out(d->dst, span_bytes(M, N, d->ldc, d->dst_dt), st, &o_dst, d->ldc != N));
+  epi.dst = o_dst.dev;
+
+  GsGemmArgs a{};
+  a.A = A; a.lda = Kp; a.sa = sa; a.sa_cols = p.src_cols;
+  a.W = (const uint8_t *)pw.wt; a.w_row = p.w4 ? Kp / 2 : Kp; a.w4 = p.w4 ? 1 : 0;
+  a.sw = ws_dev; a.sw_dt = d->wei_scale.dt;
+  a.M = M; a.N = N; a.K = K; a.Kp = (int)Kp; a.gs = p.gs; a.G = p.G;
+  a.MT = M <= 16 ? 1 : (M <= 32 ? 2 : (M <= 64 ? 4 : 8));
+  const bool ch64 = p.gs % 64 == 0;
+  const bool narrow = M <= 64;     // few rows: more CTAs along N
+  int32_t rc;
+  if (narrow) rc = ch64 ? launch_gs_t<4, 64>(a, epi, st) : launch_gs_t<4, 32>(a, epi, st);
+  else rc = ch64 ? launch_gs_t<8, 64>(a, epi, st) : launch_gs_t<8, 32>(a, epi, st);
+  B2_TRY(rc);
+  return finish_out({&o_dst, &o_scale}, st);
+}
+
+}  // namespace

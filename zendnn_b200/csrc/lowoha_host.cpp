@@ -11,9 +11,12 @@
 #include "zendnnl_b200/lowoha.hpp"
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <sstream>
 
 #include "b200dnn.h"
 
@@ -45,6 +48,41 @@ template <class Q> b200dnn_quant_t flat_quant(const Q &q) {
   o.count = n > 0 ? n : (q.buff ? 1 : 0);
   return o;
 }
+
+// The reference's log knobs (common/config_manager.cpp:273-330, levels common/logging_support.hpp:31-38):
+// ZENDNNL_API_LOG_LEVEL >= 3 (or "info" / "verbose") prints one line per call, ZENDNNL_ENABLE_PROFILER=1 with
+// ZENDNNL_PROFILE_LOG_LEVEL >= 4 (or "verbose") adds the call's host time.  Read once.
+int env_level(const char *name) {
+  const char *e = std::getenv(name);
+  if (!e || !*e) return 0;
+  if (!std::strcmp(e, "error")) return 1;
+  if (!std::strcmp(e, "warning")) return 2;
+  if (!std::strcmp(e, "info")) return 3;
+  if (!std::strcmp(e, "verbose")) return 4;
+  return std::atoi(e);
+}
+bool apilog_info() { static const bool v = env_level("ZENDNNL_API_LOG_LEVEL") >= 3; return v; }
+bool profile_on() {
+  static const bool v = [] { const char *e = std::getenv("ZENDNNL_ENABLE_PROFILER"); return e && std::atoi(e) != 0 && env_level("ZENDNNL_PROFILE_LOG_LEVEL") >= 4; }();
+  return v;
+}
+const char *dt_name(data_type_t d) {
+  switch (d) {
+  case data_type_t::f32: return "f32"; case data_type_t::bf16: return "bf16"; case data_type_t::s32: return "s32";
+  case data_type_t::s8: return "s8"; case data_type_t::u8: return "u8"; case data_type_t::s4: return "s4";
+  case data_type_t::u4: return "u4"; case data_type_t::f16: return "f16"; case data_type_t::none: return "none";
+  default: return "other";
+  }
+}
+struct CallTimer {
+  std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
+  double ms() const { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count(); }
+};
+// one line in the shape of the reference's (lowoha_operators/matmul/lowoha_matmul.cpp:472-506)
+void log_call(const std::string &text, status_t st, const CallTimer &t, const void *weight = nullptr) {
+  if (apilog_info()) std::fprintf(stderr, "[ZENDNNL API INFO] %s, kernel=b200dnn, status=%d\n", text.c_str(), static_cast<int>(st));
+  if (profile_on()) std::fprintf(stderr, "[ZENDNNL PROFILE] %s, kernel=b200dnn, weight_address=%p, time=%.4f ms (host time of the call; device-pointer calls only enqueue)\n", text.c_str(), weight, t.ms());
+}
 }  // namespace
 
 namespace b200 {
@@ -72,6 +110,13 @@ status_t flatten(const char layout, const bool transA, const bool transB, const 
     return shim_fail(status_t::unimplemented, "requantised (s8/u8) destinations are not implemented");
   if (p.quant_params.wei_zp.buff) return shim_fail(status_t::unimplemented, "weight zero-points are not implemented");
   if (p.postop_.size() > B200DNN_MAX_POSTOPS) return shim_fail(status_t::failure, "too many post-ops");
+  // W4A8 (s4 weights, bf16 source quantised by the library): the reference wants s8 compute and 2-D scale dims
+  // (lowoha_matmul_utils.cpp:101-145); the remaining rules are checked behind the C ABI
+  if (p.dynamic_quant && p.dtypes.wei == data_type_t::s4 && p.dtypes.src == data_type_t::bf16) {
+    if (p.dtypes.compute != data_type_t::s8) return shim_fail(status_t::failure, "W4A8 dynamic quantization requires s8 compute");
+    if (p.quant_params.wei_scale.dims.size() != 2) return shim_fail(status_t::failure, "W4A8 requires weight scale dims {G,N}");
+    if (p.quant_params.src_scale.dims.size() != 2) return shim_fail(status_t::failure, "W4A8 requires source scale dims {1,1}, {M,1}, or {M,G}");
+  }
   std::memset(d, 0, sizeof *d);
   d->M = M; d->N = N; d->K = K; d->transB = transB ? 1 : 0;
   d->src_dt = static_cast<int32_t>(p.dtypes.src); d->wei_dt = static_cast<int32_t>(p.dtypes.wei);
@@ -105,10 +150,22 @@ status_t matmul_direct(const char layout, const bool transA, const bool transB, 
                        const void *bias, const float beta, void *dst, const int ldc, const bool is_weights_const,
                        const matmul_batch_params_t &batch_params, const matmul_params &params) {
   b200dnn_matmul_t d;
+  const CallTimer timer;
   status_t st = flatten(layout, transA, transB, M, N, K, alpha, src, lda, weight, ldb, bias, beta, dst, ldc, is_weights_const,
                         batch_params, params, &d);
-  if (st != status_t::success) return st;
-  return from_c(b200dnn_matmul(&d, g_stream));
+  if (st == status_t::success) st = from_c(b200dnn_matmul(&d, g_stream));
+  if (apilog_info() || profile_on()) {
+    std::ostringstream ss;
+    ss << "LOWOHA matmul_direct: M=" << M << ", N=" << N << ", K=" << K << ", alpha=" << alpha << ", beta=" << beta << ", lda=" << lda
+       << ", ldb=" << ldb << ", ldc=" << ldc << ", transA=" << (transA ? "true" : "false") << ", transB=" << (transB ? "true" : "false")
+       << ", input_dtype=" << dt_name(params.dtypes.src) << ", weight_dtype=" << dt_name(params.dtypes.wei)
+       << ", output_dtype=" << dt_name(params.dtypes.dst) << ", bias_dtype=" << dt_name(params.dtypes.bias)
+       << ", bias=" << (bias ? "true" : "false") << ", is_weights_const=" << (is_weights_const ? "true" : "false")
+       << ", post_ops=" << params.postop_.size() << ", Batch_A=" << batch_params.Batch_A << ", Batch_B=" << batch_params.Batch_B
+       << ", plugin_op=" << params.plugin_op << ", dynamic_quant=" << (params.dynamic_quant ? "true" : "false");
+    log_call(ss.str(), st, timer, weight);
+  }
+  return st;
 }
 
 status_t group_matmul_moe_act_execute(const grp_matmul_gated_act_params *act_params, const std::vector<void *> &dst,
@@ -139,7 +196,7 @@ status_t group_matmul_moe_postop_execute(const group_matmul_moe_postop_params *p
 
 void clear_fused_moe_scratch() { b200dnn_clear_caches(); }
 
-status_t group_matmul_direct(const std::vector<char> &layout, const std::vector<bool> &transA, const std::vector<bool> &transB,
+static status_t group_matmul_impl(const std::vector<char> &layout, const std::vector<bool> &transA, const std::vector<bool> &transB,
                              const std::vector<int> &M, const std::vector<int> &N, const std::vector<int> &K,
                              const std::vector<float> &alpha, const std::vector<const void *> &src, const std::vector<int> &lda,
                              const std::vector<const void *> &weight, const std::vector<int> &ldb,
@@ -221,11 +278,17 @@ status_t group_matmul_direct(const std::vector<char> &layout, const std::vector<
 
   // ---- plain grouped mode: every expert's GEMM, experts with M == 0 skipped (group_matmul_parallel_common.hpp:1240-1248)
   if (!at_least(dst.size())) return shim_fail(status_t::failure, "group_matmul_direct: dst vector too short");
-  const matmul_batch_params_t bp;
-  for (size_t i = 0; i < num_ops; ++i) {
-    if (M[i] == 0) continue;
-    status_t st = matmul_direct(layout[i], transA[i], transB[i], M[i], N[i], K[i], alpha[i], src[i], lda[i], weight[i], ldb[i],
-                                bias[i], beta[i], dst[i], ldc[i], is_weights_const[i], bp, params[i]);
+  // one C call for the whole group: experts of one shape share a grouped launch, the rest run one by one
+  {
+    const matmul_batch_params_t bp;
+    std::vector<b200dnn_matmul_t> descs(num_ops);
+    for (size_t i = 0; i < num_ops; ++i) {
+      if (M[i] == 0) { std::memset(&descs[i], 0, sizeof descs[i]); continue; }
+      status_t st = flatten(layout[i], transA[i], transB[i], M[i], N[i], K[i], alpha[i], src[i], lda[i], weight[i], ldb[i], bias[i],
+                            beta[i], dst[i], ldc[i], is_weights_const[i], bp, params[i], &descs[i]);
+      if (st != status_t::success) return st;
+    }
+    status_t st = from_c(b200dnn_group_matmul(static_cast<int32_t>(num_ops), descs.data(), g_stream));
     if (st != status_t::success) return st;
   }
   if (act != grp_matmul_gated_act_t::none) {
@@ -239,6 +302,34 @@ status_t group_matmul_direct(const std::vector<char> &layout, const std::vector<
     return group_matmul_moe_postop_execute(moe_postop, D, 0, params[0].dtypes.dst);
   }
   return status_t::success;
+}
+
+status_t group_matmul_direct(const std::vector<char> &layout, const std::vector<bool> &transA, const std::vector<bool> &transB,
+                             const std::vector<int> &M, const std::vector<int> &N, const std::vector<int> &K,
+                             const std::vector<float> &alpha, const std::vector<const void *> &src, const std::vector<int> &lda,
+                             const std::vector<const void *> &weight, const std::vector<int> &ldb,
+                             const std::vector<const void *> &bias, const std::vector<float> &beta,
+                             const std::vector<void *> &dst, const std::vector<int> &ldc,
+                             const std::vector<bool> &is_weights_const, const std::vector<matmul_params> &params,
+                             const group_matmul_moe_postop_params *moe_postop, const grp_matmul_gated_act_params *gated_act,
+                             const grp_matmul_fused_moe_params *fused) {
+  const CallTimer timer;
+  const status_t st = group_matmul_impl(layout, transA, transB, M, N, K, alpha, src, lda, weight, ldb, bias, beta, dst, ldc, is_weights_const,
+                                        params, moe_postop, gated_act, fused);
+  if (apilog_info() || profile_on()) {
+    long rows = 0;
+    for (int m : M) rows += m;
+    std::ostringstream ss;
+    ss << "LOWOHA group_matmul_direct: num_ops=" << M.size() << ", total_M=" << rows << ", N=" << (N.empty() ? 0 : N[0])
+       << ", K=" << (K.empty() ? 0 : K[0]) << ", input_dtype=" << (params.empty() ? "none" : dt_name(params[0].dtypes.src))
+       << ", weight_dtype=" << (params.empty() ? "none" : dt_name(params[0].dtypes.wei))
+       << ", output_dtype=" << (params.empty() ? "none" : dt_name(params[0].dtypes.dst))
+       << ", active_matmul=" << (params.empty() ? 0 : params[0].active_matmul)
+       << ", mode=" << (fused ? "fused_moe" : (src.size() == 1 && M.size() > 1 ? "sequential" : "parallel"))
+       << ", gated_act=" << (gated_act ? "true" : "false") << ", moe_postop=" << (moe_postop ? "true" : "false");
+    log_call(ss.str(), st, timer, weight.empty() ? nullptr : weight[0]);
+  }
+  return st;
 }
 }  // namespace matmul
 
@@ -262,7 +353,7 @@ status_t weight_prepack_into(const void *weights, const reorder_params_t &params
                                 dst, g_stream));
 }
 
-status_t reorder_direct(const void *src, void *dst, reorder_params_t &params) {
+static status_t reorder_impl(const void *src, void *dst, reorder_params_t &params) {
   if (params.is_prepack) return weight_prepack_into(src, params, dst);
   if (!src) return shim_fail(status_t::failure, "reorder: null src");
   if (!params.is_2d()) return shim_fail(status_t::unimplemented, "reorder: only 2-D shapes are implemented");
@@ -291,7 +382,15 @@ status_t reorder_direct(const void *src, void *dst, reorder_params_t &params) {
     if (sc.dt != data_type_t::f32) return shim_fail(status_t::unimplemented, "reorder: per-channel / per-tensor scales are f32");
     if (per_channel) return from_c(b200dnn_quant_dynamic(src, sdt, M, N, src_ld, 1, dst, N, static_cast<float *>(sc.buff), g_stream));
     if (ns == 1) return from_c(b200dnn_quant_dynamic(src, sdt, M, N, src_ld, 0, dst, N, static_cast<float *>(sc.buff), g_stream));
-    return shim_fail(status_t::unimplemented, "reorder: per-group dynamic quantisation is not implemented");
+    // per-group along K: scale dims {M, G}; every (row, group) is quantised like a token
+    // (reorder/reorder_data_type/dynamic_quant_impl/dynamic_dispatch.cpp:255-353)
+    if (sc.dims.size() == 2 && sc.dims[0] == M && sc.dims[1] > 1 && N % sc.dims[1] == 0) {
+      if (src_ld != N) return shim_fail(status_t::unimplemented, "reorder: per-group dynamic quantisation needs contiguous rows");
+      const int64_t G = sc.dims[1], gs = N / G;
+      if (sc.dt != data_type_t::f32 && sc.dt != data_type_t::bf16) return shim_fail(status_t::unimplemented, "reorder: per-group scales are f32 or bf16");
+      return from_c(b200dnn_quant_per_token(src, sdt, M * G, gs, gs, dst, gs, sc.buff, static_cast<int32_t>(sc.dt), g_stream));
+    }
+    return shim_fail(status_t::unimplemented, "reorder: this scale granularity is not implemented for dynamic quantisation");
   }
   if (!dst) return shim_fail(status_t::failure, "reorder: null dst");
   if (!sc.buff || sc.dt != data_type_t::f32) return shim_fail(status_t::unimplemented, "reorder: static (de)quantisation needs an f32 scale");
@@ -313,22 +412,62 @@ status_t reorder_direct(const void *src, void *dst, reorder_params_t &params) {
   return shim_fail(status_t::unimplemented, "reorder: dtype combination is not implemented");
 }
 
+status_t reorder_direct(const void *src, void *dst, reorder_params_t &params) {
+  const CallTimer timer;
+  const status_t st = reorder_impl(src, dst, params);
+  if (apilog_info() || profile_on()) {
+    std::ostringstream ss;
+    ss << "LOWOHA reorder_direct" << (params.is_prepack ? " (Prepack)" : params.dynamic_quant ? "" : " (Static_Quantize)")
+       << ": M=" << (params.is_2d() ? params.M() : 0) << ", K=" << (params.is_2d() ? params.N() : 0)
+       << ", src_dtype=" << dt_name(params.src_dtype) << ", dst_dtype=" << dt_name(params.dst_dtype)
+       << ", dynamic_quant=" << (params.dynamic_quant ? "true" : "false");
+    log_call(ss.str(), st, timer, src);
+  }
+  return st;
+}
+
 status_t group_dynamic_quant(const std::vector<const void *> &src, const std::vector<int> &M, const std::vector<int> &K,
                              const std::vector<std::vector<int64_t>> &src_strides, const std::vector<void *> &dst,
                              const std::vector<std::vector<int64_t>> &dst_strides, const std::vector<void *> &scale,
                              const group_dynamic_quant_params_t &params) {
-  const size_t G = params.num_groups > 0 ? static_cast<size_t>(params.num_groups) : src.size();
-  if (G == 0 || src.size() < G || M.size() < G || K.size() < G || dst.size() < G || scale.size() < G)
-    return shim_fail(status_t::failure, "group_dynamic_quant: vectors shorter than num_groups");
-  if (params.dst_dtype != data_type_t::s8) return shim_fail(status_t::unimplemented, "group_dynamic_quant: s8 destination only");
-  std::vector<int32_t> m(G), k(G);
-  std::vector<int64_t> sld(G), dld(G);
-  for (size_t i = 0; i < G; ++i) {
-    m[i] = M[i]; k[i] = K[i];
-    sld[i] = (i < src_strides.size() && !src_strides[i].empty()) ? src_strides[i][0] : K[i];
-    dld[i] = (i < dst_strides.size() && !dst_strides[i].empty()) ? dst_strides[i][0] : K[i];
+  // one entry per expert; params.num_groups is the GRANULARITY: <= 1 per token, > 1 that many groups along K with a
+  // {M_i, G} scale buffer (reorder/lowoha_reorder_common.hpp:335-360, checks reorder/lowoha_reorder.cpp:279-372)
+  const size_t num_ops = M.size();
+  if (num_ops == 0) return shim_fail(status_t::failure, "group_dynamic_quant: M vector is empty");
+  if (src.size() != num_ops || K.size() != num_ops || dst.size() != num_ops || scale.size() != num_ops ||
+      (!src_strides.empty() && src_strides.size() != num_ops) || (!dst_strides.empty() && dst_strides.size() != num_ops))
+    return shim_fail(status_t::failure, "group_dynamic_quant: vector size mismatch");
+  if (params.dst_dtype != data_type_t::s8) return shim_fail(status_t::failure, "group_dynamic_quant: only s8 destination is supported");
+  if (params.src_dtype != data_type_t::bf16 && params.src_dtype != data_type_t::f32)
+    return shim_fail(status_t::failure, "group_dynamic_quant: only bf16/f32 source is supported");
+  if (params.scale_dtype != data_type_t::f32 && params.scale_dtype != data_type_t::bf16)
+    return shim_fail(status_t::failure, "group_dynamic_quant: scale dtype must be f32 or bf16");
+  const int64_t G = params.num_groups;
+  const bool per_group = G > 1;
+  std::vector<int32_t> m(num_ops), k(num_ops);
+  std::vector<int64_t> sld(num_ops), dld(num_ops);
+  for (size_t i = 0; i < num_ops; ++i) {
+    int64_t s_ld = K[i], d_ld = K[i];
+    if (!src_strides.empty() && !src_strides[i].empty()) {
+      if (src_strides[i].size() != 2 || src_strides[i][1] != 1) return shim_fail(status_t::failure, "group_dynamic_quant: src_strides must be empty or {row_stride, 1}");
+      s_ld = src_strides[i][0];
+    }
+    if (!dst_strides.empty() && !dst_strides[i].empty()) {
+      if (dst_strides[i].size() != 2 || dst_strides[i][1] != 1) return shim_fail(status_t::failure, "group_dynamic_quant: dst_strides must be empty or {row_stride, 1}");
+      d_ld = dst_strides[i][0];
+    }
+    if (M[i] < 0 || K[i] <= 0 || s_ld < K[i] || d_ld < K[i]) return shim_fail(status_t::failure, "group_dynamic_quant: invalid shape or stride");
+    m[i] = M[i]; k[i] = K[i]; sld[i] = s_ld; dld[i] = d_ld;
+    if (M[i] == 0) continue;      // experts without rows are not validated further, as in the reference
+    if (per_group && K[i] % G != 0) return shim_fail(status_t::failure, "group_dynamic_quant: per-group requires K % num_groups == 0");
+    if (!src[i] || !dst[i] || !scale[i]) return shim_fail(status_t::failure, "group_dynamic_quant: null active buffer");
+    if (per_group) {
+      // every (row, group) becomes a row of K/G elements; that view needs rows without gaps
+      if (s_ld != K[i] || d_ld != K[i]) return shim_fail(status_t::unimplemented, "group_dynamic_quant: per-group needs contiguous rows");
+      m[i] = static_cast<int32_t>(M[i] * G); k[i] = static_cast<int32_t>(K[i] / G); sld[i] = k[i]; dld[i] = k[i];
+    }
   }
-  return from_c(b200dnn_group_quant_per_token(static_cast<int32_t>(G), src.data(), static_cast<int32_t>(params.src_dtype), m.data(),
+  return from_c(b200dnn_group_quant_per_token(static_cast<int32_t>(num_ops), src.data(), static_cast<int32_t>(params.src_dtype), m.data(),
                                               k.data(), sld.data(), dst.data(), dld.data(), scale.data(),
                                               static_cast<int32_t>(params.scale_dtype), g_stream));
 }

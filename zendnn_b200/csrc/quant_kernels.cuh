@@ -37,6 +37,57 @@ __device__ __forceinline__ int8_t quant_sym_r(float v, float scale, float rinv) 
   return quant_sym(v, scale);
 }
 
+// The same fast path for a whole 16-byte vector, on packed f32x2 arithmetic: per pair of elements
+//   m = v*rinv + 1.5*2^23 (one fused rounding: the integer nearest to the product), t' = 1.5*2^23 - m = -round,
+//   d = v*rinv + t' (the product's distance from that integer),
+// three packed instructions instead of eight scalar ones, and ONE near-tie test per vector: the largest |d| (a
+// NaN-propagating maximum, so non-finite inputs fail the test as well) must stay below 0.499.  Returns false when the
+// vector needs the exact division; o[] then holds nothing useful.
+__device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void f32x2_unpack(uint64_t r, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(r)); }
+__device__ __forceinline__ uint64_t f32x2_fma(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ float max_nan_abs(float e, float d) { float r; asm("{ .reg .f32 t; abs.f32 t, %2; max.NaN.f32 %0, %1, t; }" : "=f"(r) : "f"(e), "f"(d)); return r; }
+
+template <int PAIRS>
+__device__ __forceinline__ bool quant_pairs_fast(const float (&v)[2 * PAIRS], float rinv, uint32_t (&m_bits)[2 * PAIRS]) {
+  const uint64_t rinv2 = f32x2_pack(rinv, rinv), magic2 = f32x2_pack(12582912.0f, 12582912.0f), neg1 = f32x2_pack(-1.0f, -1.0f);
+  float e = 0.f;
+#pragma unroll
+  for (int p = 0; p < PAIRS; ++p) {
+    const uint64_t v2 = f32x2_pack(v[2 * p], v[2 * p + 1]);
+    const uint64_t m2 = f32x2_fma(v2, rinv2, magic2);
+    const uint64_t tn = f32x2_fma(m2, neg1, magic2);
+    const uint64_t d2 = f32x2_fma(v2, rinv2, tn);
+    float m0, m1, d0, d1;
+    f32x2_unpack(m2, m0, m1); f32x2_unpack(d2, d0, d1);
+    m_bits[2 * p] = __float_as_uint(m0); m_bits[2 * p + 1] = __float_as_uint(m1);
+    e = max_nan_abs(max_nan_abs(e, d0), d1);
+  }
+  return e < 0.499f;
+}
+// low bytes of four words -> one word
+__device__ __forceinline__ uint32_t low_bytes4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+// 8 bf16 (one uint4) -> 8 s8 (uint2); 4 f32 (one uint4) -> 4 s8 (one word)
+__device__ __forceinline__ bool quant_vec_fast(const uint4 &q, float rinv, uint2 *out, uint16_t /*tag: bf16*/) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  uint32_t m[8];
+  const bool ok = quant_pairs_fast<4>(v, rinv, m);
+  out->x = low_bytes4(m[0], m[1], m[2], m[3]); out->y = low_bytes4(m[4], m[5], m[6], m[7]);
+  return ok;
+}
+__device__ __forceinline__ bool quant_vec_fast(const uint4 &q, float rinv, uint32_t *out, float /*tag: f32*/) {
+  const float v[4] = {__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w)};
+  uint32_t m[4];
+  const bool ok = quant_pairs_fast<2>(v, rinv, m);
+  *out = low_bytes4(m[0], m[1], m[2], m[3]);
+  return ok;
+}
+
 // Where the rows of one per-token quantisation come from and go to.  Rows can be a plain
 // strided matrix, a gather of rows of a matrix (MoE dispatch), or the concatenation of several
 // matrices (group_dynamic_quant / the per-expert src[] of group_matmul_direct).
@@ -75,6 +126,23 @@ template <> struct VecTraits<float> { static constexpr int kPer16B = 4; };
 template <typename T> __device__ __forceinline__ float elem_to_f32(T v);
 template <> __device__ __forceinline__ float elem_to_f32<uint16_t>(uint16_t v) { return bf16_bits_to_f32(v); }
 template <> __device__ __forceinline__ float elem_to_f32<float>(float v) { return v; }
+
+// One 16-byte vector of the row: the packed fast path, or the exact division for a vector with a near-tie or a
+// non-finite element.
+template <typename T>
+__device__ __forceinline__ void quant_vec(const uint4 &q, float scale, float rinv, int8_t (&o)[VecTraits<T>::kPer16B]) {
+  if (sizeof(T) == 2) {
+    uint2 pk;
+    if (quant_vec_fast(q, rinv, &pk, uint16_t{})) { *reinterpret_cast<uint2 *>(o) = pk; return; }
+  } else {
+    uint32_t pk;
+    if (quant_vec_fast(q, rinv, &pk, float{})) { *reinterpret_cast<uint32_t *>(o) = pk; return; }
+  }
+  const T *e = reinterpret_cast<const T *>(&q);
+#pragma unroll
+  for (int i = 0; i < VecTraits<T>::kPer16B; ++i) o[i] = quant_sym(elem_to_f32<T>(e[i]), scale);
+}
+
 
 __device__ __forceinline__ float block_max(float v, float *sh) {
 #pragma unroll
@@ -173,10 +241,8 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (EP ? 4 : (sizeof(T) =
       else reinterpret_cast<uint32_t *>(row)[v] = *reinterpret_cast<const uint32_t *>(o);
     };
     auto emit = [&](const uint4 &q, int v) {
-      const T *e = reinterpret_cast<const T *>(&q);
       __align__(8) int8_t o[E];
-#pragma unroll
-      for (int i = 0; i < E; ++i) o[i] = quant_sym_r(elem_to_f32<T>(e[i]), scale, rinv);
+      quant_vec<T>(q, scale, rinv, o);
       if (sp) {
         for (int j = 0; j < a.scatter_n; ++j) { const int d = sc[j]; if (d >= 0 && d < a.scatter_cap) put(a.peer_dst[sp[j]] + (int64_t)d * a.dst_ld, o, v); }
       } else if (sc) {
@@ -262,10 +328,8 @@ __global__ void __launch_bounds__(256) quant_per_token_warp_kernel(RowQuantArgs 
   for (int j = 0; j < NV; ++j) {
     const int v = lane + j * 32;
     if (v < nvec) {
-      const T *e = reinterpret_cast<const T *>(&cache[j]);
       __align__(8) int8_t o[E];
-#pragma unroll
-      for (int i = 0; i < E; ++i) o[i] = quant_sym_r(elem_to_f32<T>(e[i]), scale, rinv);
+      quant_vec<T>(cache[j], scale, rinv, o);
       if (sc) {
         for (int jj = 0; jj < a.scatter_n; ++jj) {
           const int d = sc[jj];

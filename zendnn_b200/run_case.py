@@ -2,6 +2,7 @@
 
   python -m zendnn_b200.run_case matmul <auto|decode|tc> M K N [--copies C] [--reps R] [--act gelu_tanh] [--bias] [--dyn]
   python -m zendnn_b200.run_case moe <c4|c5> [--reps R]
+  python -m zendnn_b200.run_case gs <w4a8|s8> M K N --gs G [--copies C] [--reps R]
 
 matmul: s8 per-token activations x s8 per-channel prepacked weight -> bf16; `--copies` distinct prepacked
 weights are used in turn (pick copies * K * N above the L2 size to keep the weight stream in HBM);
@@ -54,6 +55,47 @@ def _matmul(args):
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (args.reps * len(descs))
     print("matmul %s M%d K%d N%d: %.2f us per call (stream order, not graph-replayed)" % (args.kernel, M, K, N, us))
+
+
+def _gs(args):
+    """Group-scaled forms: w4a8 = bf16 activations quantised per token by the library x packed s4 weights with {K/gs, N}
+    scales; s8 = s8 activations with {M, K/gs} scales x s8 weights with {K/gs, N} scales.  Distinct weights in turn, cached
+    by the library after the first call."""
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    M, K, N, gs = args.M, args.K, args.N, args.gs
+    G = K // gs
+    g = torch.Generator(device=dev).manual_seed(0)
+    w4 = args.form == "w4a8"
+    weights = [torch.randint(0, 256, (K * N // 2,), generator=g, dtype=torch.uint8, device=dev) if w4 else
+               torch.randint(-127, 128, (K, N), generator=g, dtype=torch.int8, device=dev) for _ in range(args.copies)]
+    sw = torch.rand(G, N, generator=g, device=dev) * 4e-3 + 1e-3
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    if w4:
+        A = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+        kw = dict(src_dt=capi.DT["bf16"], dynamic_quant=True, src_scale=capi.quant(None, M, capi.DT["f32"]), wei_dt=capi.DT["s4"])
+    else:
+        A = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8, device=dev)
+        sa = torch.rand(M, G, generator=g, device=dev) * 0.04 + 0.01
+        kw = dict(src_dt=capi.DT["s8"], src_scale=capi.quant(sa, M * G, capi.DT["f32"]))
+    descs = [capi.make_matmul(M, N, K, A, w, out, dst_dt=capi.DT["bf16"], wei_scale=capi.quant(sw, G * N, capi.DT["f32"]),
+                              weights_const=True, **kw) for w in weights]
+    for d in descs:
+        capi.check(capi.matmul(d, st))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.reps):
+        for d in descs:
+            capi.check(capi.matmul(d, st))
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.reps * len(descs))
+    wbytes = K * N / (2 if w4 else 1)
+    print("gs %s M%d K%d N%d group %d: %.2f us per call, weight stream %.0f GB/s, %.1f TOPS" %
+          (args.form, M, K, N, gs, us, wbytes / us / 1e3, 2.0 * M * K * N / us / 1e6))
 
 
 def _moe(args):
@@ -123,11 +165,17 @@ def main():
     m.add_argument("--act", default=None)
     m.add_argument("--bias", action="store_true")
     m.add_argument("--dyn", action="store_true")
+    q = sub.add_parser("gs")
+    q.add_argument("form", choices=["w4a8", "s8"])
+    q.add_argument("M", type=int); q.add_argument("K", type=int); q.add_argument("N", type=int)
+    q.add_argument("--gs", type=int, default=128)
+    q.add_argument("--copies", type=int, default=4)
+    q.add_argument("--reps", type=int, default=20)
     e = sub.add_parser("moe")
     e.add_argument("config", choices=["c4", "c5"])
     e.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()
-    (_matmul if args.what == "matmul" else _moe)(args)
+    {"matmul": _matmul, "moe": _moe, "gs": _gs}[args.what](args)
 
 
 if __name__ == "__main__":
