@@ -383,8 +383,13 @@ def run_ours(args, rank, world, local_rank):
         "ms_per_step_by_rank": [round(v * inner, 4) for v in head["ms_per_layer_by_rank"]],
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(sustained, 1), "unit": "TOP/s",
-                     "frac": round(achieved / sustained, 4), "traffic": None,
-                     "kernel": "tc_gemm_kernel<false>, grouped form: the two GEMM launches of a layer (gate|up with the gated epilogue, down)",
+                     "frac": round(achieved / sustained, 4),
+                     # DRAM bytes per launch from one ncu capture of a 4096-token single-GPU layer ((1.677 + 0.289 + 1.435 + 0.085) GB
+                     # over the two launches), scaled by this rank's rows; the algorithmic bytes of such a launch are 0.93 GB
+                     "traffic": int(round(1.743e9 * my_rows / 8192.0)),
+                     "traffic_source": "ncu capture of the two grouped launches of one configuration-4 layer on one GPU "
+                                       "(dram__bytes_read + dram__bytes_write, mean per launch), scaled by the rank's rows",
+                     "kernel": "tc_gemm_kernel<false, true>, grouped two-CTA form: the two GEMM launches of a layer (gate|up with the gated epilogue, down)",
                      "achieved_def": "2*rows*H*2I + 2*rows*I*H operations of this rank's rows / mean device time of the two launches per layer "
                                      "(CUDA events recorded by the library on the launching stream inside the timed region)",
                      "peak_source": "int8 tensor rate measured in this run (b200dnn_measure_int8_peak, 2 s run under the power cap); "
@@ -565,10 +570,50 @@ def run_decode_grid(torch, capi, dev, peaks, passes=200):
     return res
 
 
+def run_w4a8_grid(torch, capi, dev, peaks, decode_per_shape):
+    """W4A8 on the decode shapes (the first "next" row of the scope): bf16 activations quantised per token by the library,
+    packed s4 weights with {K/128, N} f32 scales, bf16 out.  Distinct weights per shape in turn (more than the L2 in total,
+    prepared once by the library's weight cache), one pass per shape is a CUDA graph.  Weight bytes are K*N/2."""
+    g = torch.Generator(device="cpu").manual_seed(99)
+    stream = torch.cuda.current_stream().cuda_stream
+    side = torch.cuda.Stream()
+    gs, out = 128, {}
+    for (K, N) in DECODE_KN:
+        copies = max(2, int(140e6 // (K * N // 2)) + 1)
+        ws = [torch.randint(0, 256, (K * N // 2,), dtype=torch.uint8, generator=g).to(dev) for _ in range(copies)]
+        sw = (torch.rand(K // gs, N, generator=g) * 4e-3 + 1e-3).to(dev)
+        for M in (1, 16):
+            A = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+            o = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            ds = [capi.make_matmul(M, N, K, A, w, o, src_dt=capi.DT["bf16"], dst_dt=capi.DT["bf16"], wei_dt=capi.DT["s4"],
+                                   dynamic_quant=True, src_scale=capi.quant(None, count=M, dt=capi.DT["f32"]),
+                                   wei_scale=capi.quant(sw, count=(K // gs) * N, dt=capi.DT["f32"]), weights_const=True) for w in ws]
+            for d in ds:
+                capi.check(capi.matmul(d, stream))
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for d in ds:
+                    capi.check(capi.matmul(d, torch.cuda.current_stream().cuda_stream))
+            ms = _time_events(torch, graph.replay, 20, warm=3) / len(ds)
+            key = "M%d_K%d_N%d" % (M, K, N)
+            gbs = (K * N / 2) / ms / 1e6
+            w8 = (decode_per_shape or {}).get(key, {}).get("us")
+            out[key] = dict(us=round(ms * 1e3, 2), weight_gbs=round(gbs, 1), frac_of_hbm=round(gbs / peaks["hbm"], 3),
+                            w8a8_us=w8, launches_per_call=2)
+            del graph, ds, A, o
+        del ws, sw
+        capi.lib.b200dnn_clear_caches()
+        torch.cuda.empty_cache()
+    return {"what": "W4A8 matmul_direct (bf16 source quantised per token + group-scaled GEMM, group 128) on the decode shapes; "
+                    "w8a8_us is the pre-quantised W8A8 call of the same shape from the decode grid", "per_shape": out}
+
+
 def run_single_gpu_extras(torch, capi, dev, peaks, int8_peak):
     """The other parts of the metric, on one GPU: decode HBM GB/s (configuration 2) and prefill TOPS (configurations 3, 1)."""
     st = torch.cuda.current_stream().cuda_stream
     out = {"decode_grid": run_decode_grid(torch, capi, dev, peaks)}
+    out["w4a8_decode"] = run_w4a8_grid(torch, capi, dev, peaks, out["decode_grid"].get("per_shape"))
     g = torch.Generator(device="cpu").manual_seed(7)
 
     def gemm(M, K, N, dyn, act, copies=1):

@@ -147,6 +147,12 @@ B200DNN_API int32_t b200dnn_prepack(const void *weight, int64_t K, int64_t N, in
  * scales only) and M scales (scale_dt f32|bf16). */
 B200DNN_API int32_t b200dnn_quant_per_token(const void *src, int32_t src_dt, int64_t M, int64_t K, int64_t src_ld,
                                 void *dst, int64_t dst_ld, void *scale, int32_t scale_dt, void *stream);
+/* Per-token ASYMMETRIC dynamic quantisation, f32|bf16 -> u8 with one f32 scale and one s32 zero point per row
+ * (reorder_direct with a zero-point buffer; reorder/reorder_data_type/scalar_impl/dynamic_per_token_ref_kernel.cpp:38-56,128-183).
+ * dst may be NULL (scales and zero points only). */
+B200DNN_API int32_t b200dnn_quant_per_token_asym(const void *src, int32_t src_dt, int64_t M, int64_t K, int64_t src_ld, void *dst,
+                                                 int64_t dst_ld, float *scale, int32_t *zero_point, void *stream);
+
 /* group_dynamic_quant (reorder/lowoha_reorder.cpp:279): the same over num_groups tensors;
  * groups with M[i]==0 are skipped. */
 B200DNN_API int32_t b200dnn_group_quant_per_token(int32_t num_groups, const void *const *src, int32_t src_dt,
@@ -268,6 +274,20 @@ B200DNN_API int32_t b200dnn_moe_experts_s8(const void *rows_s8, int64_t lda, con
 B200DNN_API int32_t b200dnn_moe_weighted_reduce_rows(const void *rows, int64_t ld_rows, const int32_t *slot_rows,
                                                      const float *slot_weights, int32_t num_tokens, int32_t nslots,
                                                      int32_t D, int32_t dt, void *out, int64_t ld_out, void *stream);
+
+/* ---- N-column sharding of one large matmul_direct over the GPUs of a node (one process per GPU; no counterpart in
+ * the reference).  Rank r computes the column block [n0, n1) of dst from its column block of the weight, the matching
+ * slices of the per-channel weight scales, the bias and the binary post-op operands, and the whole (replicated) source:
+ * no reduction, so every output element is the one a single GPU computes.  A GEMM narrower than 8 tiles of 256 columns
+ * is not split (sharded = 0: every rank computes all of it).  Blocks are whole 128-column tiles. ---- */
+B200DNN_API int32_t b200dnn_nshard_range(int64_t N, int32_t world, int32_t rank, int64_t *n0, int64_t *n1, int32_t *sharded);
+/* id128: the bytes of b200dnn_ep_nccl_unique_id made on one rank, or nccl_comm: an existing ncclComm_t; both NULL: no
+ * communicator (enough when the blocks are not gathered). */
+B200DNN_API int32_t b200dnn_nshard_create(int32_t world, int32_t rank, const void *id128, void *nccl_comm, void **handle);
+B200DNN_API int32_t b200dnn_nshard_destroy(void *handle);
+/* desc describes the WHOLE problem, weights in the caller's layout ('n').  gather != 0: afterwards every rank holds the whole
+ * dst (device memory; collective over the communicator, enqueued on `stream`). */
+B200DNN_API int32_t b200dnn_matmul_nshard(void *handle, const b200dnn_matmul_t *desc, int32_t gather, void *stream);
 
 /* ---- Expert-parallel fused MoE across the GPUs of one node, one process per GPU (or several handles in one process).
  * No counterpart in the reference (a single-process CPU library); the per-expert contract is group_matmul_direct's

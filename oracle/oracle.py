@@ -358,6 +358,31 @@ def unpack_s4(packed, K, N, transB=False, ldb=None):
     return np.ascontiguousarray(v.T) if transB else v
 
 
+def quant_per_token_asym(x):
+    """Asymmetric per-token dynamic quantisation: x [M,K] f32 or bf16-bits -> (u8 [M,K], f32 scales [M], s32 zero points [M])."""
+    x = np.ascontiguousarray(x)
+    M, K = x.shape
+    q = np.empty((M, K), dtype=np.uint8)
+    s = np.empty(M, dtype=np.float32)
+    z = np.empty(M, dtype=np.int32)
+    lib().orc_quant_per_token_asym(_p(x), _dt_of(x), C.c_int64(M), C.c_int64(K), C.c_int64(K), _p(q), C.c_int64(K), _p(s), _p(z))
+    return q, s, z
+
+
+def ref2_quant_per_token_asym(x, native=False):
+    """Reference asymmetric per-token quantisation (scalar kernel, or the AVX-512 one).  None if unavailable."""
+    r = ref2_lib()
+    x = np.ascontiguousarray(x)
+    M, K = x.shape
+    if r is None or (native and not r.ref2_avx512()) or not hasattr(r, "ref2_quant_per_token_u8"):
+        return None
+    q = np.zeros((M, K), dtype=np.uint8)
+    s = np.zeros(M, dtype=np.float32)
+    z = np.zeros(M, dtype=np.int32)
+    rc = r.ref2_quant_per_token_u8(_p(x), int(x.dtype == np.uint16), _p(q), _p(s), _p(z), C.c_int64(M), C.c_int64(K), int(native))
+    return (q, s, z) if rc == 0 else None
+
+
 def quant_per_group(x, G):
     """Dynamic symmetric quantisation with G groups along K per row (scale buffer {M,G}): the per-token rule applied to
     every group of K/G elements (reorder/lowoha_reorder.cpp:318-390).  Returns (s8 [M,K], f32 [M,G])."""

@@ -52,6 +52,20 @@ API int ref2_quant_per_token(const void *src, int is_bf16, int8_t *dst, float *s
   return 0;
 }
 
+// Asymmetric per-token quantisation to u8 with one f32 scale and one s32 zero point per row.
+API int ref2_quant_per_token_u8(const void *src, int is_bf16, uint8_t *dst, float *scale, int32_t *zp, int64_t M, int64_t K, int native) {
+  using namespace zendnnl::lowoha::reorder;
+  if (native && !ref2_avx512()) return -1;
+  if (is_bf16) {
+    if (native) dynamic_per_token_quant_bf16_u8_native((const uint16_t *)src, dst, scale, zp, M, K);
+    else dynamic_per_token_quant_bf16_u8_ref((const uint16_t *)src, dst, scale, zp, M, K);
+  } else {
+    if (native) dynamic_per_token_quant_f32_u8_native((const float *)src, dst, scale, zp, M, K);
+    else dynamic_per_token_quant_f32_u8_ref((const float *)src, dst, scale, zp, M, K);
+  }
+  return 0;
+}
+
 // Per-group dynamic quantisation along K (scale layout {M,G}), the reference's AVX-512 kernel
 // (reorder/reorder_data_type/dynamic_quant_impl/per_group_avx512_f32_fma_kernel.cpp).
 API int ref2_quant_per_group(const void *src, int is_bf16, int8_t *dst, float *scale, int64_t M, int64_t K, int64_t G) {

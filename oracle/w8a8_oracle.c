@@ -32,6 +32,7 @@
  * Build: see oracle/Makefile (gcc -O2 -fopenmp -ffp-contract=off; the VNNI loop is selected
  * at run time so the same .so runs on hosts without AVX-512).
  */
+#include <float.h>
 #include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -320,6 +321,36 @@ ORC_API int orc_epilogue(const int32_t *acc, int64_t ldacc, int M, int N, int or
     }
   }
   return 0;
+}
+
+/* Per-token ASYMMETRIC dynamic quantisation to u8: reorder/reorder_data_type/scalar_impl/
+ * dynamic_per_token_ref_kernel.cpp:38-56 (scale and zero point) and :128-183 (rows): min / max over finite values (a row
+ * without finite values counts as all zero), max <= min -> max = min + 1, scale = (max - min) / 255 clamped to 1e-10,
+ * zp = round(-min / scale) in double (half away from zero), q = clamp(nearbyint(v / scale) + zp, 0, 255); non-finite -> 0. */
+ORC_API void orc_quant_per_token_asym(const void *src, int src_dt, int64_t M, int64_t K, int64_t src_stride,
+                                      uint8_t *dst, int64_t dst_stride, float *scales, int32_t *zps) {
+  #pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    float lo = FLT_MAX, hi = -FLT_MAX;
+    for (int64_t j = 0; j < K; ++j) {
+      float v = load_as_f32(src, src_dt, m * src_stride + j);
+      if (isfinite(v)) { if (v < lo) lo = v; if (v > hi) hi = v; }
+    }
+    if (lo == FLT_MAX && hi == -FLT_MAX) { lo = 0.0f; hi = 0.0f; }
+    if (hi <= lo) hi = lo + 1.0f;
+    float scale = (hi - lo) / 255.0f;
+    if (scale < 1e-10f) scale = 1e-10f;
+    double zd = round((double)(-lo) / (double)scale);
+    int32_t zp = zd < -2147483648.0 ? INT32_MIN : (zd > 2147483647.0 ? INT32_MAX : (int32_t)zd);
+    scales[m] = scale; zps[m] = zp;
+    if (!dst) continue;
+    for (int64_t j = 0; j < K; ++j) {
+      float v = load_as_f32(src, src_dt, m * src_stride + j);
+      int32_t q = 0;
+      if (isfinite(v)) { q = (int32_t)nearbyintf(v / scale) + zp; if (q < 0) q = 0; if (q > 255) q = 255; }
+      dst[m * dst_stride + j] = (uint8_t)q;
+    }
+  }
 }
 
 /* Group-scaled symmetric INT8 GEMM (per-group source scales {M,G} x per-group weight scales {G,N}) and W4A8 after the

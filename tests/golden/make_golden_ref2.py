@@ -68,6 +68,9 @@ def run(tag):
         native = tag == "vec"
         q, s = O.ref2_quant_per_token(x, native=native)
         out["quant_%s_%s_q" % (dt, tag)], out["quant_%s_%s_s" % (dt, tag)] = q, s
+        r = O.ref2_quant_per_token_asym(x, native=native)
+        assert r is not None
+        out["quantu8_%s_%s_q" % (dt, tag)], out["quantu8_%s_%s_s" % (dt, tag)], out["quantu8_%s_%s_z" % (dt, tag)] = r
         for a in ACTS:
             out["act_%s_%s_%s" % (a, dt, tag)] = O.ref2_gated_act(y, a)
         for skip in (0, 1):

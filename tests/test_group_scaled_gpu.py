@@ -24,7 +24,7 @@ def _call(capi, d):
     assert st == capi.SUCCESS, capi.last_error()
 
 
-SHAPES = [(1, 64, 16), (5, 128, 24), (16, 256, 72), (40, 192, 130), (100, 512, 264), (200, 1024, 96)]
+SHAPES = [(1, 64, 16), (5, 128, 24), (16, 256, 72), (3, 1024, 40), (12, 2048, 200), (40, 192, 130), (100, 512, 264), (200, 1024, 96)]
 
 
 @pytest.mark.parametrize("gs", [4, 8, 16, 32, 64, 128, 0], ids=lambda g: "gs%s" % (g or "K"))

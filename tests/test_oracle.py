@@ -382,3 +382,15 @@ def test_per_group_dynamic_quant_equals_reference_kernel(oracle, golden2, dt):
         assert (q == golden2["pg_%s_G%d_q" % (dt, G)]).all(), G
         seen += 1
     assert seen >= 3
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_asymmetric_per_token_quant_equals_reference_kernels(oracle, golden2, dt):
+    """u8 codes, f32 scales and s32 zero points equal the reference's scalar kernel and its AVX-512 kernel bit for bit
+    (reorder/reorder_data_type/scalar_impl/dynamic_per_token_ref_kernel.cpp:38-56,128-183; rows with inf / nan entries and
+    an all-zero row included)."""
+    q, s, z = oracle.quant_per_token_asym(_as(oracle, golden2["x32"], dt))
+    for tag in ("scalar", "vec"):
+        assert (s == golden2["quantu8_%s_%s_s" % (dt, tag)]).all(), tag
+        assert (z == golden2["quantu8_%s_%s_z" % (dt, tag)]).all(), tag
+        assert (q == golden2["quantu8_%s_%s_q" % (dt, tag)]).all(), tag

@@ -95,6 +95,33 @@ def test_group_dynamic_quant_with_differing_row_lengths(capi, oracle):
             assert (q[:m] == q_ref).all() and (s[:m] == s_ref).all()
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("shape", [(1, 64), (7, 300), (33, 4096), (5, 11008)])
+def test_asymmetric_per_token_quant(capi, oracle, shape, dt):
+    """f32|bf16 -> u8 with one scale and one zero point per row, bit for bit against the oracle (itself pinned to both
+    reference kernels): ordinary rows, a row with inf / nan entries, an all-zero row, a constant row, a strided source."""
+    M, K = shape
+    rng = np.random.default_rng(M + K)
+    x32 = (rng.normal(size=(M, K)) * rng.uniform(0.01, 30, size=(M, 1)) + rng.normal(size=(M, 1))).astype(np.float32)
+    if M > 4:
+        x32[0, :3] = [np.inf, -np.inf, np.nan]
+        x32[1, :] = 0
+        x32[2, :] = 3.25
+        x32[3, :] = np.abs(x32[3, :])          # a row without negative values
+    x = oracle.f32_to_bf16(x32) if dt == "bf16" else x32
+    ld = K + 8
+    xs = np.zeros((M, ld), dtype=x.dtype); xs[:, :K] = x
+    q = np.full((M, K), 99, dtype=np.uint8); s = np.zeros(M, dtype=np.float32); z = np.zeros(M, dtype=np.int32)
+    st = capi.lib.b200dnn_quant_per_token_asym(capi.ptr(xs), capi.DT[dt], M, K, ld, capi.ptr(q), K, capi.ptr(s), capi.ptr(z), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    q_ref, s_ref, z_ref = oracle.quant_per_token_asym(x)
+    assert (s == s_ref).all() and (z == z_ref).all() and (q == q_ref).all()
+    # scales and zero points only
+    s2 = np.zeros(M, dtype=np.float32); z2 = np.zeros(M, dtype=np.int32)
+    st = capi.lib.b200dnn_quant_per_token_asym(capi.ptr(xs), capi.DT[dt], M, K, ld, None, 0, capi.ptr(s2), capi.ptr(z2), None)
+    assert st == capi.SUCCESS and (s2 == s_ref).all() and (z2 == z_ref).all()
+
+
 @pytest.mark.parametrize("G", [2, 8, 32])
 def test_per_group_dynamic_quant_through_the_per_token_entry(capi, oracle, G):
     """Per-group dynamic quantisation along K (scale layout {M,G}; reference kernel

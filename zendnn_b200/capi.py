@@ -66,8 +66,8 @@ PHASE_NAMES = ["route+rank", "count exchange", "quantise+dispatch", "barrier aft
 
 EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b200dnn_launch_count",
            "b200dnn_matmul", "b200dnn_matmul_static_scratch", "b200dnn_static_scratch_query", "b200dnn_prepack_size", "b200dnn_prepack", "b200dnn_quant_per_token",
-           "b200dnn_group_quant_per_token", "b200dnn_quant_dynamic", "b200dnn_quant_static",
-           "b200dnn_dequant_static", "b200dnn_gated_act", "b200dnn_moe_weighted_reduce", "b200dnn_fused_moe", "b200dnn_group_matmul",
+           "b200dnn_group_quant_per_token", "b200dnn_quant_per_token_asym", "b200dnn_quant_dynamic", "b200dnn_quant_static",
+           "b200dnn_dequant_static", "b200dnn_gated_act", "b200dnn_moe_weighted_reduce", "b200dnn_fused_moe", "b200dnn_group_matmul", "b200dnn_nshard_range", "b200dnn_nshard_create", "b200dnn_nshard_destroy", "b200dnn_matmul_nshard",
            "b200dnn_moe_route", "b200dnn_moe_layer", "b200dnn_clear_caches", "b200dnn_stream_status", "b200dnn_moe_sort_slots",
            "b200dnn_quant_per_token_gather", "b200dnn_quant_per_token_scatter", "b200dnn_moe_experts_s8",
            "b200dnn_moe_weighted_reduce_rows", "b200dnn_ep_create", "b200dnn_ep_destroy", "b200dnn_ep_local_expert_count",
@@ -97,6 +97,11 @@ lib.b200dnn_quant_static.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i64, v
 lib.b200dnn_dequant_static.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i64, vp, i32, i64, vp]
 lib.b200dnn_gated_act.argtypes = [vp, i32, i64, i64, i64, i32, vp]
 lib.b200dnn_moe_weighted_reduce.argtypes = [vp, vp, i32, i32, i32, i32, i32, vp, i64, vp]
+lib.b200dnn_quant_per_token_asym.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, vp, vp]
+lib.b200dnn_nshard_range.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64), C.POINTER(i32)]
+lib.b200dnn_nshard_create.argtypes = [i32, i32, vp, vp, C.POINTER(vp)]
+lib.b200dnn_nshard_destroy.argtypes = [vp]
+lib.b200dnn_matmul_nshard.argtypes = [vp, C.POINTER(MatmulDesc), i32, vp]
 lib.b200dnn_group_matmul.argtypes = [i32, C.POINTER(MatmulDesc), vp]
 lib.b200dnn_fused_moe.argtypes = [i32, C.POINTER(MoeExpert), i32, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, i64, vp]
 lib.b200dnn_moe_route.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]

@@ -79,7 +79,7 @@ int32_t validate_group_scaled(const b200dnn_matmul_t *d, GsPlan *p) {
   return B200DNN_SUCCESS;
 }
 
-// [N][Kp] s8 / [N][Kp/2] s4 copy of the weight, cached per (pointer, shape, layout) like the packed tcgen05 weights.
+// blocked s8 / s4 copy of the weight (layout in gs_gemm.cuh), cached per (pointer, shape, layout) like the packed tcgen05 weights.
 int32_t resolve_gs_weight(const b200dnn_matmul_t *d, bool w4, int64_t Kp, cudaStream_t st, PackedWeight *pw) {
   DeviceShared &D = *rt().shared;
   const int K = d->K, N = d->N;
@@ -95,11 +95,12 @@ int32_t resolve_gs_weight(const b200dnn_matmul_t *d, bool w4, int64_t Kp, cudaSt
   const size_t src_bytes = w4 ? (size_t)(((wrows - 1) * d->ldb + wcols + 1) / 2) : span_bytes(wrows, wcols, d->ldb, B200DNN_S8);
   const void *w_dev = nullptr;
   B2_TRY(stage_in(d->weight, src_bytes, st, &w_dev));
-  const size_t bytes = (size_t)N * (w4 ? Kp / 2 : Kp);
+  const int64_t np8 = (N + 7) / 8 * 8;
+  const size_t bytes = (size_t)np8 * (w4 ? Kp / 2 : Kp);
   void *buf = nullptr;
   if (cache) B2_CUDA(cudaMalloc(&buf, bytes));
   else { buf = rt().ws.alloc(bytes); B2_CHECK(buf, B200DNN_FAILURE, "workspace allocation failed"); }
-  const int64_t threads = (Kp / 2) * N;
+  const int64_t threads = (Kp / 2) * np8;
   gs_pack_weight_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const uint8_t *)w_dev, d->ldb, d->transB, w4 ? 1 : 0, K, N, (int)Kp, (uint8_t *)buf);
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
@@ -116,6 +117,61 @@ int32_t launch_gs_t(const GsGemmArgs &a, const EpiParams &epi, cudaStream_t st) 
   else gs_gemm_kernel<NT, CH, false><<<grid, kGsWarps * 32, 0, st>>>(a, epi);
   B2_LAUNCHED();
   B2_CUDA(cudaGetLastError());
+  return B200DNN_SUCCESS;
+}
+
+// The decode form: M <= 16, at least eight groups of a multiple of 32 elements, f32 weight scales, even N, activations
+// that leave room for a ring of at least four slots per lane in shared memory.
+template <int CH, bool W4, int R>
+int32_t launch_gs_decode_r(const GsDecodeArgs &da, const EpiParams &epi, size_t smem, int grid, cudaStream_t st) {
+  B2_TRY(ensure_max_smem((const void *)gs_decode_kernel<CH, W4, R>, (int)smem));
+  gs_decode_kernel<CH, W4, R><<<grid, kGsWarps * 32, smem, st>>>(da, epi);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  return B200DNN_SUCCESS;
+}
+template <int CH, bool W4>
+int32_t launch_gs_decode_t(const GsGemmArgs &a, const EpiParams &epi, cudaStream_t st, bool *done) {
+  *done = false;
+  GsDecodeArgs da{};
+  da.g = a;
+  da.rows_staged = a.M;
+  // row stride of the staged activations: the lanes of a quarter warp (16-byte loads) or half warp (8-byte loads) read
+  // distinct bank groups when the stride is 64 (32) bytes off a multiple of 128
+  da.a_stride = CH == 64 ? (a.Kp % 128 == 64 ? a.Kp : a.Kp + 64) : a.Kp + 32;
+  constexpr int slot_w = 32 * 2 * (W4 ? CH / 8 : CH / 4), slot_s = 32 * 2 * 8;     // bytes per warp and ring slot (see the kernel)
+  const int chunks = a.gs / CH;
+  const size_t fixed = (size_t)da.rows_staged * da.a_stride + (size_t)((da.rows_staged * a.sa_cols + 3) & ~3) * 4 +
+                       (size_t)2 * kGsWarps * 16 * 17 * 4;
+  // ring depth and CTAs per SM: whatever keeps the most copies in flight per SM (ties: more CTAs, which also evens out the tiles)
+  const size_t sm_bytes = (size_t)226 * 1024;     // per SM, with 1 KiB per CTA reserved by the system
+  int best_r = 0, best_ctas = 0, best_score = -1;
+  size_t best_smem = 0;
+  const int items_per_tile = ((a.G + kGsWarps - 1) / kGsWarps) * chunks;      // of one warp: more in flight than that spans tiles
+  for (int r : {16, 12, 8, 6, 4}) {
+    const int rs = (r + chunks - 1) / chunks + 1;
+    const size_t smem = fixed + (size_t)kGsWarps * ((size_t)r * slot_w + (size_t)rs * slot_s);
+    if (smem > (size_t)224 * 1024) continue;
+    int ctas = (int)(sm_bytes / (smem + 1024));
+    if (ctas > 3) ctas = 3;                       // 72-88 registers x 256 threads
+    const int score = ctas * ((r - 1) < items_per_tile ? (r - 1) : items_per_tile);
+    if (score > best_score || (score == best_score && ctas > best_ctas)) { best_score = score; best_r = r; best_ctas = ctas; best_smem = smem; }
+  }
+  if (best_r == 0) return B200DNN_SUCCESS;        // the general kernel takes it
+  da.scale_slots = (best_r + chunks - 1) / chunks + 1;
+  const size_t smem = best_smem;
+  const int tiles = (a.N + 15) / 16;
+  // persistent CTAs (one tile per CTA, left to the hardware's scheduler, measured slower: 18.3 against 15.4 us at M = 1, K = 4096, N = 11008)
+  const int slots = rt().sm_count * best_ctas;
+  const int grid = tiles < slots ? tiles : slots;
+  switch (best_r) {
+  case 16: B2_TRY((launch_gs_decode_r<CH, W4, 16>(da, epi, smem, grid, st))); break;
+  case 12: B2_TRY((launch_gs_decode_r<CH, W4, 12>(da, epi, smem, grid, st))); break;
+  case 8: B2_TRY((launch_gs_decode_r<CH, W4, 8>(da, epi, smem, grid, st))); break;
+  case 6: B2_TRY((launch_gs_decode_r<CH, W4, 6>(da, epi, smem, grid, st))); break;
+  default: B2_TRY((launch_gs_decode_r<CH, W4, 4>(da, epi, smem, grid, st))); break;
+  }
+  *done = true;
   return B200DNN_SUCCESS;
 }
 
@@ -193,15 +249,26 @@ int32_t matmul_group_scaled(const b200dnn_matmul_t *d, cudaStream_t st) {
 
   GsGemmArgs a{};
   a.A = A; a.lda = Kp; a.sa = sa; a.sa_cols = p.src_cols;
-  a.W = (const uint8_t *)pw.wt; a.w_row = p.w4 ? Kp / 2 : Kp; a.w4 = p.w4 ? 1 : 0;
+  a.W = (const uint8_t *)pw.wt; a.w4 = p.w4 ? 1 : 0;
   a.sw = ws_dev; a.sw_dt = d->wei_scale.dt;
   a.M = M; a.N = N; a.K = K; a.Kp = (int)Kp; a.gs = p.gs; a.G = p.G;
   a.MT = M <= 16 ? 1 : (M <= 32 ? 2 : (M <= 64 ? 4 : 8));
   const bool ch64 = p.gs % 64 == 0;
-  const bool narrow = M <= 64;     // few rows: more CTAs along N
+  // (the decode form addresses the weight and the scales with 32-bit offsets)
+  if (M <= 16 && p.G >= kGsWarps && p.gs % 32 == 0 && d->wei_scale.dt == B200DNN_F32 && N % 2 == 0 &&
+      (int64_t)(N + 8) * Kp < (int64_t)1 << 32 && (int64_t)p.G * N < (int64_t)1 << 30 &&
+      (reinterpret_cast<uintptr_t>(ws_dev) & 7) == 0 && env_int("B200DNN_GS_DECODE", 1) != 0) {
+    bool done = false;
+    int32_t rcd;
+    if (p.w4) rcd = ch64 ? launch_gs_decode_t<64, true>(a, epi, st, &done) : launch_gs_decode_t<32, true>(a, epi, st, &done);
+    else rcd = ch64 ? launch_gs_decode_t<64, false>(a, epi, st, &done) : launch_gs_decode_t<32, false>(a, epi, st, &done);
+    B2_TRY(rcd);
+    if (done) return finish_out({&o_dst, &o_scale}, st);
+  }
+  // few rows: narrower CTAs, so that a decode-shaped call has a few CTAs per SM
   int32_t rc;
-  if (narrow) rc = ch64 ? launch_gs_t<4, 64>(a, epi, st) : launch_gs_t<4, 32>(a, epi, st);
-  else rc = ch64 ? launch_gs_t<8, 64>(a, epi, st) : launch_gs_t<8, 32>(a, epi, st);
+  if (M <= 16) rc = ch64 ? launch_gs_t<2, 64>(a, epi, st) : launch_gs_t<2, 32>(a, epi, st);
+  else rc = ch64 ? launch_gs_t<4, 64>(a, epi, st) : launch_gs_t<4, 32>(a, epi, st);   // (eight column tiles per warp need a CTA's whole register file)
   B2_TRY(rc);
   return finish_out({&o_dst, &o_scale}, st);
 }

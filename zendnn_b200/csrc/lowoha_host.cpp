@@ -375,7 +375,14 @@ static status_t reorder_impl(const void *src, void *dst, reorder_params_t &param
   if (params.dynamic_quant) {
     // the caller owns the scale buffer (lowoha_reorder_utils.cpp:524-528); dst == null computes scales only
     if (!sc.buff) return shim_fail(status_t::failure, "reorder: dynamic quantisation needs a scale buffer");
-    if (zp.buff) return shim_fail(status_t::unimplemented, "reorder: asymmetric dynamic quantisation is not implemented");
+    if (zp.buff) {
+      // asymmetric: f32|bf16 -> u8, one scale and one s32 zero point per token (scale and zero-point dims {M,1})
+      if (!src_float || (dst && params.dst_dtype != data_type_t::u8)) return shim_fail(status_t::unimplemented, "reorder: asymmetric dynamic quantisation is f32|bf16 -> u8");
+      const bool tok = per_token || (ns == M && M == 1);
+      if (!tok || zp.dims != sc.dims) return shim_fail(status_t::unimplemented, "reorder: asymmetric dynamic quantisation is implemented per token");
+      if (sc.dt != data_type_t::f32 || zp.dt != data_type_t::s32) return shim_fail(status_t::unimplemented, "reorder: asymmetric scales are f32, zero points s32");
+      return from_c(b200dnn_quant_per_token_asym(src, sdt, M, N, src_ld, dst, N, static_cast<float *>(sc.buff), static_cast<int32_t *>(zp.buff), g_stream));
+    }
     if (!src_float || (dst && params.dst_dtype != data_type_t::s8)) return shim_fail(status_t::unimplemented, "reorder: dynamic quantisation is f32|bf16 -> s8");
     if (per_token || (ns == M && M == 1 && N > 1 && sc.dims.size() == 2 && sc.dims[1] == 1))
       return from_c(b200dnn_quant_per_token(src, sdt, M, N, src_ld, dst, N, sc.buff, static_cast<int32_t>(sc.dt), g_stream));

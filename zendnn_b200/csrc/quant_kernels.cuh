@@ -269,6 +269,93 @@ __global__ void __launch_bounds__(kQuantThreads, NV > 2 ? (EP ? 4 : (sizeof(T) =
   }   // rows of this CTA
 }
 
+// Per-token ASYMMETRIC dynamic quantisation to u8 (one f32 scale and one s32 zero point per row):
+// reorder/reorder_data_type/scalar_impl/dynamic_per_token_ref_kernel.cpp:38-56,128-183.  One CTA per row; min and max over
+// the finite values, scale = (max - min) / 255, zp = round(-min / scale) in double, q = clamp(rne(v / scale) + zp, 0, 255).
+// Not a hot path (the INT8 GEMMs take symmetric per-token rows), so the row is read twice and divided exactly.
+template <typename T>
+__global__ void __launch_bounds__(kQuantThreads) quant_per_token_asym_kernel(const T *src, int64_t src_ld, int K, uint8_t *dst, int64_t dst_ld,
+                                                                            float *scales, int32_t *zps) {
+  __shared__ float sh[kQuantThreads / 32];
+  const int r = blockIdx.x;
+  const T *row = src + (int64_t)r * src_ld;
+  float lo = 3.402823466e+38f, hi = -3.402823466e+38f;
+  for (int k = threadIdx.x; k < K; k += kQuantThreads) {
+    const float v = elem_to_f32<T>(row[k]);
+    if (finite_f32(v)) { lo = fminf(lo, v); hi = fmaxf(hi, v); }
+  }
+  hi = block_max(hi, sh);
+  lo = -block_max(-lo, sh);
+  if (lo == 3.402823466e+38f && hi == -3.402823466e+38f) { lo = 0.f; hi = 0.f; }
+  if (hi <= lo) hi = __fadd_rn(lo, 1.0f);
+  float scale = __fdiv_rn(__fsub_rn(hi, lo), 255.0f);
+  if (scale < 1e-10f) scale = 1e-10f;
+  const double zd = round((double)(-lo) / (double)scale);
+  const int32_t zp = zd < -2147483648.0 ? (int32_t)0x80000000 : (zd > 2147483647.0 ? 0x7fffffff : (int32_t)zd);
+  if (threadIdx.x == 0) { scales[r] = scale; zps[r] = zp; }
+  if (!dst) return;
+  uint8_t *out = dst + (int64_t)r * dst_ld;
+  for (int k = threadIdx.x; k < K; k += kQuantThreads) {
+    const float v = elem_to_f32<T>(row[k]);
+    int q = 0;
+    if (finite_f32(v)) {
+      // nearbyint(v / scale) + zp without leaving the int range: the quotient is clamped first (any value beyond
+      // +-2^30 saturates the result anyway)
+      const float t = fminf(fmaxf(rintf(__fdiv_rn(v, scale)), -1073741824.f), 1073741824.f);
+      const long long qq = (long long)t + (long long)zp;
+      q = qq < 0 ? 0 : (qq > 255 ? 255 : (int)qq);
+    }
+    out[k] = (uint8_t)q;
+  }
+}
+
+// Rows whose abs-max is already known (the re-quantisation between the two MoE GEMMs: the first GEMM's epilogue left the
+// row maxima): a pure stream.  One warp per row at a time, U 16-byte loads in flight per lane, no shared memory and no
+// barrier, so the warps of an SM drift apart and loads, arithmetic and stores of different rows overlap (a CTA per row
+// that loads, then converts, then stores ran its phases in step with its neighbours: 110 us for 352 MB).
+// Requires 16-byte aligned rows, K a multiple of the vector width, plain rows (no gather, scatter or groups).
+template <typename T, int U>
+__global__ void __launch_bounds__(256) quant_known_absmax_kernel(RowQuantArgs a, int rows, int segs, int seg_len) {
+  constexpr int E = VecTraits<T>::kPer16B;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int lane = threadIdx.x & 31;
+  const int row_limit = a.n_rows_dev ? min(rows, *a.n_rows_dev) : rows;
+  const int nvec = a.K / E;
+  // a work item is one segment of one row (seg_len vectors, a multiple of 32); the warps take the items in turn
+  const long long items = (long long)row_limit * segs;
+  for (long long it = blockIdx.x * 8 + (threadIdx.x >> 5); it < items; it += (long long)gridDim.x * 8) {
+    const int r = (int)(it / segs), sg = (int)(it - (long long)r * segs);
+    const float scale = scale_from_absmax(__uint_as_float(a.absmax_bits[r]));
+    if (lane == 0 && sg == 0 && a.scale) {
+      if (a.scale_dt == DT_BF16) reinterpret_cast<uint16_t *>(a.scale)[r] = f32_to_bf16_bits(scale);
+      else reinterpret_cast<float *>(a.scale)[r] = scale;
+    }
+    if (!a.dst) continue;
+    const float rinv = __frcp_rn(scale);
+    const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.src) + (int64_t)r * a.src_ld);
+    int8_t *dst = a.dst + (int64_t)r * a.dst_ld;
+    const int v_end = min(nvec, (sg + 1) * seg_len);
+    for (int v0 = sg * seg_len + lane; v0 < v_end; v0 += 32 * U) {
+      uint4 q[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * 32;
+        if (v < v_end) asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q[u].x), "=r"(q[u].y), "=r"(q[u].z), "=r"(q[u].w) : "l"(src + v));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * 32;
+        if (v < v_end) {
+          __align__(8) int8_t o[E];
+          quant_vec<T>(q[u], scale, rinv, o);
+          if (E == 8) reinterpret_cast<uint2 *>(dst)[v] = *reinterpret_cast<uint2 *>(o);
+          else reinterpret_cast<uint32_t *>(dst)[v] = *reinterpret_cast<uint32_t *>(o);
+        }
+      }
+    }
+  }
+}
+
 // One warp per row, for short rows (K <= 32 * NV * elements-per-16-bytes): the row lives in the
 // lanes' registers, the abs-max is a shuffle reduction, no shared memory and no CTA barrier.
 // Requires 16-byte aligned rows and K a multiple of the vector width (the launcher checks).
