@@ -432,6 +432,7 @@ def run_ours(args, rank, world, local_rank):
         runner5.close()
         if world > 1:
             line["ep_parity"] = ep_parity(torch, dist, capi, dev, rank, world, stream)
+            also["nshard_prefill"] = run_nshard(torch, dist, capi, dev, rank, world, stream, sustained)
         else:
             also.update(run_single_gpu_extras(torch, capi, dev, peaks, sustained))
     line["also"] = also
@@ -607,6 +608,57 @@ def run_w4a8_grid(torch, capi, dev, peaks, decode_per_shape):
         torch.cuda.empty_cache()
     return {"what": "W4A8 matmul_direct (bf16 source quantised per token + group-scaled GEMM, group 128) on the decode shapes; "
                     "w8a8_us is the pre-quantised W8A8 call of the same shape from the decode grid", "per_shape": out}
+
+
+def run_nshard(torch, dist, capi, dev, rank, world, stream, int8_peak):
+    """One prefill GEMM of configuration 3 (M 2048, K 4096, N 14336; bf16 source quantised per token, f32 bias, GELU(tanh), bf16
+    out) split by N columns over the ranks (b200dnn_matmul_nshard): every rank quantises the whole source and computes its
+    column block; with gather = 1 every rank ends with the whole result.  Max over ranks of the device time per call; the
+    sharded result is compared with the rank's own unsharded call."""
+    import ctypes as C
+    M, K, N = 2048, 4096, 14336
+    g = torch.Generator(device="cpu").manual_seed(5)
+    W = torch.randint(-127, 128, (K, N), dtype=torch.int8, generator=g).to(dev)
+    sw = (torch.rand(N, generator=g) * 0.009 + 0.001).to(dev)
+    bias = torch.randn(N, generator=g).to(dev)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+    box = [None]
+    if rank == 0:
+        ident = (C.c_uint8 * 128)()
+        capi.check(capi.lib.b200dnn_ep_nccl_unique_id(ident))
+        box[0] = bytes(ident)
+    dist.broadcast_object_list(box, src=0)
+    ident = (C.c_uint8 * 128).from_buffer_copy(box[0])
+    h = C.c_void_p()
+    capi.check(capi.lib.b200dnn_nshard_create(world, rank, ident, None, C.byref(h)))
+    mk = lambda o: capi.make_matmul(M, N, K, A, W, o, src_dt=capi.DT["bf16"], dst_dt=capi.DT["bf16"], dynamic_quant=True,
+                                    src_scale=capi.quant(None, count=M, dt=capi.DT["f32"]), wei_scale=sw, bias=bias,
+                                    postops=["gelu_tanh"], weights_const=True)
+    whole = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    capi.check(capi.matmul(mk(whole), stream))
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    d = mk(out)
+    res = {}
+    for gather in (0, 1):
+        call = lambda: capi.check(capi.lib.b200dnn_matmul_nshard(h, C.byref(d), gather, stream))
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = _time_events(torch, call, 20, warm=0)
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res["gathered" if gather else "column_blocks"] = {"ms": round(float(t[0]), 4), "tops": round(2.0 * M * N * K / float(t[0]) / 1e9, 1)}
+    torch.cuda.synchronize()
+    same = torch.tensor([int(torch.equal(out, whole))], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    ms1 = _time_events(torch, lambda: capi.check(capi.matmul(mk(whole), stream)), 20, warm=2)
+    res.update({"what": "configuration-3 GEMM (quantise + GEMM + bias + GELU) split by N columns over %d GPUs; ms = max over ranks per call" % world,
+                "unsharded_ms_rank0": round(ms1, 4), "equals_unsharded": "bit-exact" if int(same[0]) else "differs",
+                "frac_of_int8_peak_all_gpus": round(res["column_blocks"]["tops"] / (int8_peak * world), 4)})
+    capi.check(capi.lib.b200dnn_nshard_destroy(h))
+    capi.lib.b200dnn_clear_caches()
+    return res
 
 
 def run_single_gpu_extras(torch, capi, dev, peaks, int8_peak):

@@ -158,3 +158,32 @@ def test_contract(capi, oracle):
     d = mk(M, N, K, A, np.zeros((K, N), np.int8), out, src_dt=capi.DT["s8"], dst_dt=capi.DT["bf16"],
            src_scale=capi.quant(sa, count=M * G), wei_scale=capi.quant(sw, count=G * N), src_zp=np.array([3], np.int32), weights_const=False)
     assert capi.matmul(d) == capi.FAILURE
+
+
+def test_decode_form_agrees_with_the_general_kernel(capi, oracle, monkeypatch):
+    """The decode form (persistent CTAs, cp.async rings) and the general kernel on the same call: identical source scales,
+    outputs within 1 bf16 ulp of each other and of the oracle."""
+    M, K, N, gs = 7, 2048, 328, 128
+    G = K // gs
+    rng = np.random.default_rng(21)
+    X = oracle.f32_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    X[2, 5] = 0x7FC0          # a NaN entry: ignored by the abs-max, quantised to 0
+    W = rng.integers(-8, 8, (K, N), dtype=np.int8)
+    sw = rng.uniform(1e-3, 5e-3, (G, N)).astype(np.float32)
+    packed = oracle.pack_s4(W)
+    A, sa = oracle.quant_per_token(X)
+    ref = oracle.matmul_group_scaled(A, W, sa, sw, "bf16")
+    outs = {}
+    for name, env in (("decode", {}), ("general", {"B200DNN_GS_DECODE": "0"})):
+        monkeypatch.delenv("B200DNN_GS_DECODE", raising=False)
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        out = np.zeros((M, N), dtype=np.uint16)
+        sc = np.zeros(M, dtype=np.float32)
+        d = capi.make_matmul(M, N, K, X, packed, out, src_dt=capi.DT["bf16"], dst_dt=capi.DT["bf16"], src_scale=capi.quant(sc, count=M),
+                             wei_scale=capi.quant(sw, count=G * N), weights_const=False, dynamic_quant=True, wei_dt=capi.DT["s4"])
+        _call(capi, d)
+        assert (sc == sa).all(), name
+        assert_bf16_close(out, ref, 1, name, atol=1e-5)
+        outs[name] = out
+    assert_bf16_close(outs["general"], outs["decode"], 1, "general against decode form", atol=1e-5)

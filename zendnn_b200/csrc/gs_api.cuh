@@ -185,48 +185,6 @@ int32_t matmul_group_scaled(const b200dnn_matmul_t *d, cudaStream_t st) {
   PackedWeight pw;
   B2_TRY(resolve_gs_weight(d, p.w4, Kp, st, &pw));
 
-  // ---- source rows: s8 [M][Kp], zero padded, and f32 scales [M][src_cols]
-  int8_t *A = (int8_t *)R.ws.alloc((size_t)M * Kp);
-  B2_CHECK(A, B200DNN_FAILURE, "workspace allocation failed");
-  if (Kp != K) B2_CUDA(cudaMemsetAsync(A, 0, (size_t)M * Kp, st));
-  const void *src_dev = nullptr;
-  B2_TRY(stage_in(d->src, span_bytes(M, K, d->lda, d->src_dt), st, &src_dev));
-  Staged o_scale; o_scale.copy_back = false;
-  const float *sa = nullptr;
-  if (p.dyn) {
-    const int64_t n_sc = (int64_t)M * p.src_cols;
-    B2_TRY(stage_out(const_cast<void *>(d->src_scale.buff), (size_t)n_sc * 4, st, &o_scale));
-    float *sc = (float *)o_scale.dev;
-    if (!sc) { sc = (float *)R.ws.alloc((size_t)n_sc * 4); B2_CHECK(sc, B200DNN_FAILURE, "workspace allocation failed"); }
-    RowQuantArgs qa{};
-    qa.gather_div = 1; qa.scale = sc; qa.scale_dt = B200DNN_F32;
-    if (p.src_cols == 1) {
-      qa.src = src_dev; qa.src_ld = d->lda; qa.dst = A; qa.dst_ld = Kp; qa.K = K;
-      B2_TRY(launch_quant_rows(qa, d->src_dt, M, st));
-    } else {
-      // every (row, group) is a row of gs elements; needs rows that follow each other without gaps
-      const size_t esz = dt_size(d->src_dt);
-      const void *xs = src_dev;
-      if (d->lda != K) {
-        void *x = R.ws.alloc((size_t)M * K * esz);
-        B2_CHECK(x, B200DNN_FAILURE, "workspace allocation failed");
-        B2_CUDA(cudaMemcpy2DAsync(x, (size_t)K * esz, src_dev, (size_t)d->lda * esz, (size_t)K * esz, (size_t)M, cudaMemcpyDeviceToDevice, st));
-        xs = x;
-      }
-      int8_t *q = A;
-      if (Kp != K) { q = (int8_t *)R.ws.alloc((size_t)M * K); B2_CHECK(q, B200DNN_FAILURE, "workspace allocation failed"); }
-      qa.src = xs; qa.src_ld = p.gs; qa.dst = q; qa.dst_ld = p.gs; qa.K = p.gs;
-      B2_TRY(launch_quant_rows(qa, d->src_dt, (int64_t)M * p.G, st));
-      if (q != A) B2_CUDA(cudaMemcpy2DAsync(A, (size_t)Kp, q, (size_t)K, (size_t)K, (size_t)M, cudaMemcpyDeviceToDevice, st));
-    }
-    sa = sc;
-  } else {
-    B2_CUDA(cudaMemcpy2DAsync(A, (size_t)Kp, src_dev, (size_t)d->lda, (size_t)K, (size_t)M, cudaMemcpyDefault, st));
-    const void *s = nullptr;
-    B2_TRY(stage_in(d->src_scale.buff, (size_t)M * p.src_cols * 4, st, &s));
-    sa = (const float *)s;
-  }
-
   // ---- epilogue operands
   EpiParams epi;
   fill_epi(d, &epi);
@@ -247,25 +205,74 @@ int32_t matmul_group_scaled(const b200dnn_matmul_t *d, cudaStream_t st) {
   B2_TRY(stage_out(d->dst, span_bytes(M, N, d->ldc, d->dst_dt), st, &o_dst, d->ldc != N));
   epi.dst = o_dst.dev;
 
+  const void *src_dev = nullptr;
+  B2_TRY(stage_in(d->src, span_bytes(M, K, d->lda, d->src_dt), st, &src_dev));
+  Staged o_scale; o_scale.copy_back = false;
+  if (p.dyn) B2_TRY(stage_out(const_cast<void *>(d->src_scale.buff), (size_t)M * p.src_cols * 4, st, &o_scale));
+
   GsGemmArgs a{};
-  a.A = A; a.lda = Kp; a.sa = sa; a.sa_cols = p.src_cols;
+  a.sa_cols = p.src_cols;
   a.W = (const uint8_t *)pw.wt; a.w4 = p.w4 ? 1 : 0;
   a.sw = ws_dev; a.sw_dt = d->wei_scale.dt;
   a.M = M; a.N = N; a.K = K; a.Kp = (int)Kp; a.gs = p.gs; a.G = p.G;
   a.MT = M <= 16 ? 1 : (M <= 32 ? 2 : (M <= 64 ? 4 : 8));
   const bool ch64 = p.gs % 64 == 0;
+
+  // ---- source rows for the kernels that do not quantise themselves: s8 [M][Kp], zero padded, and f32 scales [M][src_cols]
+  auto prepare_source = [&]() -> int32_t {
+    int8_t *A = (int8_t *)R.ws.alloc((size_t)M * Kp);
+    B2_CHECK(A, B200DNN_FAILURE, "workspace allocation failed");
+    if (Kp != K) B2_CUDA(cudaMemsetAsync(A, 0, (size_t)M * Kp, st));
+    const float *sa = nullptr;
+    if (p.dyn) {
+      const int64_t n_sc = (int64_t)M * p.src_cols;
+      float *sc = (float *)o_scale.dev;
+      if (!sc) { sc = (float *)R.ws.alloc((size_t)n_sc * 4); B2_CHECK(sc, B200DNN_FAILURE, "workspace allocation failed"); }
+      RowQuantArgs qa{};
+      qa.gather_div = 1; qa.scale = sc; qa.scale_dt = B200DNN_F32;
+      if (p.src_cols == 1) {
+        qa.src = src_dev; qa.src_ld = d->lda; qa.dst = A; qa.dst_ld = Kp; qa.K = K;
+        B2_TRY(launch_quant_rows(qa, d->src_dt, M, st));
+      } else {
+        // every (row, group) is a row of gs elements; needs rows that follow each other without gaps
+        const size_t esz = dt_size(d->src_dt);
+        const void *xs = src_dev;
+        if (d->lda != K) {
+          void *x = R.ws.alloc((size_t)M * K * esz);
+          B2_CHECK(x, B200DNN_FAILURE, "workspace allocation failed");
+          B2_CUDA(cudaMemcpy2DAsync(x, (size_t)K * esz, src_dev, (size_t)d->lda * esz, (size_t)K * esz, (size_t)M, cudaMemcpyDeviceToDevice, st));
+          xs = x;
+        }
+        int8_t *q = A;
+        if (Kp != K) { q = (int8_t *)R.ws.alloc((size_t)M * K); B2_CHECK(q, B200DNN_FAILURE, "workspace allocation failed"); }
+        qa.src = xs; qa.src_ld = p.gs; qa.dst = q; qa.dst_ld = p.gs; qa.K = p.gs;
+        B2_TRY(launch_quant_rows(qa, d->src_dt, (int64_t)M * p.G, st));
+        if (q != A) B2_CUDA(cudaMemcpy2DAsync(A, (size_t)Kp, q, (size_t)K, (size_t)K, (size_t)M, cudaMemcpyDeviceToDevice, st));
+      }
+      sa = sc;
+    } else {
+      B2_CUDA(cudaMemcpy2DAsync(A, (size_t)Kp, src_dev, (size_t)d->lda, (size_t)K, (size_t)M, cudaMemcpyDefault, st));
+      const void *sp = nullptr;
+      B2_TRY(stage_in(d->src_scale.buff, (size_t)M * p.src_cols * 4, st, &sp));
+      sa = (const float *)sp;
+    }
+    a.A = A; a.lda = Kp; a.sa = sa;
+    return B200DNN_SUCCESS;
+  };
+
   // (the decode form addresses the weight and the scales with 32-bit offsets)
   if (M <= 16 && p.G >= kGsWarps && p.gs % 32 == 0 && d->wei_scale.dt == B200DNN_F32 && N % 2 == 0 &&
       (int64_t)(N + 8) * Kp < (int64_t)1 << 32 && (int64_t)p.G * N < (int64_t)1 << 30 &&
       (reinterpret_cast<uintptr_t>(ws_dev) & 7) == 0 && env_int("B200DNN_GS_DECODE", 1) != 0) {
+    B2_TRY(prepare_source());
     bool done = false;
     int32_t rcd;
     if (p.w4) rcd = ch64 ? launch_gs_decode_t<64, true>(a, epi, st, &done) : launch_gs_decode_t<32, true>(a, epi, st, &done);
     else rcd = ch64 ? launch_gs_decode_t<64, false>(a, epi, st, &done) : launch_gs_decode_t<32, false>(a, epi, st, &done);
     B2_TRY(rcd);
     if (done) return finish_out({&o_dst, &o_scale}, st);
-  }
-  // few rows: narrower CTAs, so that a decode-shaped call has a few CTAs per SM
+  } else B2_TRY(prepare_source());
+  // few rows: narrower CTAs, so that a call with few rows still has a few CTAs per SM
   int32_t rc;
   if (M <= 16) rc = ch64 ? launch_gs_t<2, 64>(a, epi, st) : launch_gs_t<2, 32>(a, epi, st);
   else rc = ch64 ? launch_gs_t<4, 64>(a, epi, st) : launch_gs_t<4, 32>(a, epi, st);   // (eight column tiles per warp need a CTA's whole register file)
