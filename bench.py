@@ -399,9 +399,9 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(sustained, 1), "unit": "TOP/s",
                      "frac": round(achieved / sustained, 4),
-                     # DRAM bytes per launch from one ncu capture of a 4096-token single-GPU layer ((1.677 + 0.289 + 1.435 + 0.085) GB
+                     # DRAM bytes per launch from one ncu capture of a 4096-token single-GPU layer ((1.553 + 0.280 + 1.003 + 0.078) GB
                      # over the two launches), scaled by this rank's rows; the algorithmic bytes of such a launch are 0.93 GB
-                     "traffic": int(round(1.743e9 * my_rows / 8192.0)),
+                     "traffic": int(round(1.457e9 * my_rows / 8192.0)),
                      "traffic_source": "ncu capture of the two grouped launches of one configuration-4 layer on one GPU "
                                        "(dram__bytes_read + dram__bytes_write, mean per launch), scaled by the rank's rows",
                      "kernel": "tc_gemm_kernel<false, true>, grouped two-CTA form: the two GEMM launches of a layer (gate|up with the gated epilogue, down)",

@@ -503,9 +503,24 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
   // activations once per column tile.  When the weight of a group is small enough to stay in L2 and the
   // activations are the larger operand (many rows, as in a fine-grained MoE), the column tiles of one row tile
   // run together instead: activations are read once, the weight is re-read from L2.
+  // Which one moves fewer DRAM bytes is estimated from what the L2 can keep (ncu on the down projection of a
+  // Mixtral-like layer, 14336 x 4096 per expert: column-tile-major read the 117 MB of activations once per wave of tiles,
+  // 1.43 GB for 0.59 GB of operands; row-tile-major finishes an expert in about one wave).
   {
-    const long long w_bytes = (long long)pw0.Kp * pw0.Np, a_bytes = (long long)M_total * K;
-    args.n_fastest = env_int("B200DNN_TC_ORDER", (w_bytes <= (32ll << 20) && a_bytes > w_bytes) ? 1 : 0);
+    const long long kL2 = 96ll << 20;                                   // what a sweep can count on, of 126 MB
+    const long long w_group = (long long)pw0.Kp * pw0.Np, groups = args.n_groups > 0 ? args.n_groups : 1;
+    const long long w_all = w_group * groups, a_bytes = (long long)M_total * K;
+    const long long conc = R.sm_count / (args.pair ? 2 : 1);           // tiles in flight
+    const long long tiles_all = (long long)m_tiles_hint * args.n_tiles;
+    const long long waves = (tiles_all + conc - 1) / conc;
+    // column-tile-major: the activations survive between the waves only if they fit beside the weight slices in flight
+    const long long a_reads = (a_bytes + w_all / (args.n_tiles > 0 ? args.n_tiles : 1) <= kL2) ? 1 : (waves < args.n_tiles ? waves : args.n_tiles);
+    const long long traffic_col = w_all + a_bytes * a_reads;
+    // row-tile-major: a group's weight is read again for every wave of that group's row tiles unless it stays in L2
+    const long long tiles_group = ((long long)m_tiles_hint + groups - 1) / groups * args.n_tiles;
+    const long long w_reads = (w_group <= kL2 / 2) ? 1 : (tiles_group + conc - 1) / conc;
+    const long long traffic_row = a_bytes + w_all * w_reads;
+    args.n_fastest = env_int("B200DNN_TC_ORDER", traffic_row < traffic_col ? 1 : 0);
   }
   const int stage_bytes = kTcBM * kTcBK + (args.pair ? args.BN / 2 : args.BN) * kTcBK;   // per CTA
   int stages = kTcSmemBudget / stage_bytes;
