@@ -14,14 +14,6 @@
 
 namespace {
 
-__global__ void tile_prefix_kernel(const int32_t *row_off, int n_groups, int32_t *tile_prefix, int tile_rows) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    int acc = 0;
-    for (int g = 0; g < n_groups; ++g) { tile_prefix[g] = acc; acc += (row_off[g + 1] - row_off[g] + tile_rows - 1) / tile_rows; }
-    tile_prefix[n_groups] = acc;
-  }
-}
-
 int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const std::vector<PackedWeight> &pws,
                      const int32_t *row_off_dev, const int32_t *tile_prefix_dev, const TcGroupDesc *groups_dev,
                      int m_tiles_bound, EpiParams epi, bool shared_dst, cudaStream_t st, int tile_rows = kTcBM) {
@@ -308,10 +300,8 @@ extern "C" int32_t b200dnn_moe_layer(const void *x, int64_t ldx, const float *lo
   rt().mark(-1);
   B2_TRY(launch_route_topk((const float *)l_dev, T, E, topk, 1, ids, w, st));
   B2_TRY(launch_expert_rank(ids, T * topk, E, rank, cnt, st));
-  expert_offsets_kernel<<<1, 32, 0, st>>>(cnt, E, S, T, row_off);
-  B2_LAUNCHED();
   const int tile_rows = tc_tile_rows(R, H < 2 * I ? H : 2 * I);
-  tile_prefix_kernel<<<1, 32, 0, st>>>(row_off, G, tile_prefix, tile_rows);
+  expert_offsets_kernel<<<1, 32, 0, st>>>(cnt, E, S, T, row_off, tile_prefix, tile_rows);
   B2_LAUNCHED();
   build_maps_kernel<<<(unsigned)((R + 255) / 256), 256, 0, st>>>(ids, rank, w, row_off, T, topk, E, S, slot_rows, slot_w, row_token);
   B2_LAUNCHED();

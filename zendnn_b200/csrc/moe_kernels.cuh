@@ -266,15 +266,32 @@ __global__ void __launch_bounds__(kRankChunk) rank_assign_kernel(const int32_t *
   }
 }
 
-// Device-side expert offsets.  counts[0..E) are the routed experts' rows; shared experts (if any) get T
-// rows each.  Writes row_off[E+S+1].
-__global__ void expert_offsets_kernel(const int32_t *counts, int E, int S, int T, int32_t *row_off) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    int acc = 0;
-    for (int e = 0; e < E; ++e) { row_off[e] = acc; acc += counts[e]; }
-    for (int s = 0; s < S; ++s) { row_off[E + s] = acc; acc += T; }
-    row_off[E + S] = acc;
+// Device-side expert offsets, one warp: counts[0..E) are the routed experts' rows; shared experts (if any) get T rows each.
+// Writes row_off[E+S+1] and, when tile_prefix is given, the running number of row tiles (tile_rows rows each) per group,
+// tile_prefix[E+S+1], which the grouped GEMM reads.
+__global__ void expert_offsets_kernel(const int32_t *counts, int E, int S, int T, int32_t *row_off, int32_t *tile_prefix = nullptr,
+                                      int tile_rows = 1) {
+  if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+  const int lane = threadIdx.x, G = E + S;
+  int row_carry = 0, tile_carry = 0;
+  for (int base = 0; base < G; base += 32) {
+    const int g = base + lane;
+    const int rows = g < E ? counts[g] : (g < G ? T : 0);
+    const int tiles = (rows + tile_rows - 1) / tile_rows;
+    int rsum = rows, tsum = tiles;       // inclusive scans over the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int r = __shfl_up_sync(0xffffffffu, rsum, o), t = __shfl_up_sync(0xffffffffu, tsum, o);
+      if (lane >= o) { rsum += r; tsum += t; }
+    }
+    if (g < G) {
+      row_off[g] = row_carry + rsum - rows;
+      if (tile_prefix) tile_prefix[g] = tile_carry + tsum - tiles;
+    }
+    row_carry += __shfl_sync(0xffffffffu, rsum, 31);
+    tile_carry += __shfl_sync(0xffffffffu, tsum, 31);
   }
+  if (lane == 0) { row_off[G] = row_carry; if (tile_prefix) tile_prefix[G] = tile_carry; }
 }
 
 // slot -> row (expert-sorted order) and row -> source token; shared-expert rows follow the routed ones.
