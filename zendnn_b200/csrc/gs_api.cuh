@@ -138,7 +138,7 @@ int32_t launch_gs_decode_t(const GsGemmArgs &a, const EpiParams &epi, cudaStream
   da.rows_staged = a.M;
   // row stride of the staged activations: the lanes of a quarter warp (16-byte loads) or half warp (8-byte loads) read
   // distinct bank groups when the stride is 64 (32) bytes off a multiple of 128
-  da.a_stride = CH == 64 ? (a.Kp % 128 == 64 ? a.Kp : a.Kp + 64) : a.Kp + 32;
+  da.a_stride = CH == 128 ? a.Kp + 16 : (CH == 64 ? (a.Kp % 128 == 64 ? a.Kp : a.Kp + 64) : a.Kp + 32);   // (128-k chunks: two 16-byte loads, 32 bytes apart per lane)
   constexpr int slot_w = 32 * 2 * (W4 ? CH / 8 : CH / 4), slot_s = 32 * 2 * 8;     // bytes per warp and ring slot (see the kernel)
   const int chunks = a.gs / CH;
   const size_t fixed = (size_t)da.rows_staged * da.a_stride + (size_t)((da.rows_staged * a.sa_cols + 3) & ~3) * 4 +
@@ -153,7 +153,7 @@ int32_t launch_gs_decode_t(const GsGemmArgs &a, const EpiParams &epi, cudaStream
     const size_t smem = fixed + (size_t)kGsWarps * ((size_t)r * slot_w + (size_t)rs * slot_s);
     if (smem > (size_t)224 * 1024) continue;
     int ctas = (int)(sm_bytes / (smem + 1024));
-    if (ctas > 3) ctas = 3;                       // 72-88 registers x 256 threads
+    if (ctas > (CH == 128 ? 2 : 3)) ctas = CH == 128 ? 2 : 3;      // 72-88 registers x 256 threads (87-96 with 128-k chunks)
     const int score = ctas * ((r - 1) < items_per_tile ? (r - 1) : items_per_tile);
     if (score > best_score || (score == best_score && ctas > best_ctas)) { best_score = score; best_r = r; best_ctas = ctas; best_smem = smem; }
   }
@@ -267,8 +267,9 @@ int32_t matmul_group_scaled(const b200dnn_matmul_t *d, cudaStream_t st) {
     B2_TRY(prepare_source());
     bool done = false;
     int32_t rcd;
-    if (p.w4) rcd = ch64 ? launch_gs_decode_t<64, true>(a, epi, st, &done) : launch_gs_decode_t<32, true>(a, epi, st, &done);
-    else rcd = ch64 ? launch_gs_decode_t<64, false>(a, epi, st, &done) : launch_gs_decode_t<32, false>(a, epi, st, &done);
+    const bool ch128 = p.gs % 128 == 0 && env_int("B200DNN_GS_CH128", 1) != 0;     // fewer, larger items per group
+    if (p.w4) rcd = ch128 ? launch_gs_decode_t<128, true>(a, epi, st, &done) : ch64 ? launch_gs_decode_t<64, true>(a, epi, st, &done) : launch_gs_decode_t<32, true>(a, epi, st, &done);
+    else rcd = ch128 ? launch_gs_decode_t<128, false>(a, epi, st, &done) : ch64 ? launch_gs_decode_t<64, false>(a, epi, st, &done) : launch_gs_decode_t<32, false>(a, epi, st, &done);
     B2_TRY(rcd);
     if (done) return finish_out({&o_dst, &o_scale}, st);
   } else B2_TRY(prepare_source());

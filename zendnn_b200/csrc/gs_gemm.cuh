@@ -282,8 +282,11 @@ struct GsDecodeArgs {
 };
 
 template <int BYTES>
-__device__ __forceinline__ void gs_cp_async(uint32_t dst, const void *src) {
-  if (BYTES == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+__device__ __forceinline__ void gs_cp_async(uint32_t dst, const void *src, uint32_t plane = 0) {
+  if (BYTES == 32) {      // two 16-byte halves, `plane` bytes apart in shared memory (each half next to the other lanes' halves)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + plane), "l"(reinterpret_cast<const uint8_t *>(src) + 16) : "memory");
+  } else if (BYTES == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
   else if (BYTES == 8) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
   else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -291,6 +294,16 @@ __device__ __forceinline__ void gs_cp_async(uint32_t dst, const void *src) {
 __device__ __forceinline__ uint4 lds16(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
 __device__ __forceinline__ uint2 lds8(uint32_t a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
 __device__ __forceinline__ uint32_t lds4(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+// NW consecutive words from shared memory; the second 16 bytes of an eight-word piece sit `plane` bytes further on
+template <int NW>
+__device__ __forceinline__ void lds_words(uint32_t a, uint32_t plane, uint32_t (&r)[NW]) {
+  if (NW == 1) r[0] = lds4(a);
+  else if (NW == 2) { const uint2 v = lds8(a); r[0] = v.x; r[NW > 1 ? 1 : 0] = v.y; }
+  else {
+    const uint4 v = lds16(a); r[0] = v.x; r[NW > 1 ? 1 : 0] = v.y; r[NW > 2 ? 2 : 0] = v.z; r[NW > 3 ? 3 : 0] = v.w;
+    if (NW == 8) { const uint4 w = lds16(a + plane); r[NW > 4 ? 4 : 0] = w.x; r[NW > 5 ? 5 : 0] = w.y; r[NW > 6 ? 6 : 0] = w.z; r[NW > 7 ? 7 : 0] = w.w; }
+  }
+}
 
 template <int CH, bool W4, int R>
 __global__ void __launch_bounds__(kGsWarps * 32, 2) gs_decode_kernel(GsDecodeArgs da, EpiParams epi) {
@@ -309,7 +322,8 @@ __global__ void __launch_bounds__(kGsWarps * 32, 2) gs_decode_kernel(GsDecodeArg
   float *s_sa = reinterpret_cast<float *>(gs_smem + (size_t)da.rows_staged * da.a_stride);
   float *red = s_sa + ((da.rows_staged * g.sa_cols + 3) & ~3);   // [2][8 warps][16][17]
   uint8_t *ring = reinterpret_cast<uint8_t *>(red + 2 * kGsWarps * 16 * 17);
-  const uint32_t ring_w = smem_u32(ring) + (uint32_t)(warp * R * SLOTW) + (uint32_t)lane * PB;      // this lane's first weight piece
+  constexpr int PU = PB > 16 ? 16 : PB;            // a lane's piece is stored as PB / PU planes of PU bytes, lanes side by side
+  const uint32_t ring_w = smem_u32(ring) + (uint32_t)(warp * R * SLOTW) + (uint32_t)lane * PU;      // this lane's first weight piece
   const uint32_t ring_s = smem_u32(ring) + (uint32_t)(kGsWarps * R * SLOTW) + (uint32_t)(warp * RS * SLOTS) + (uint32_t)lane * 8;
   const bool hi_rows = da.rows_staged > 8;
   const int shift = W4 ? 4 : 0;
@@ -318,7 +332,8 @@ __global__ void __launch_bounds__(kGsWarps * 32, 2) gs_decode_kernel(GsDecodeArg
   const int chunks = g.gs / CH;
   const uint32_t nblk = (uint32_t)(g.Kp >> 6);
   const int last_ct = (g.N + 7) / 8 - 1;
-  const uint32_t lane_w = (uint32_t)lg * CHB + (uint32_t)((lt * PIECE) >> SH);
+  // this lane's piece of a chunk: k = lt * PIECE onwards, which may lie in the chunk's second 64-k block
+  const uint32_t lane_w = (uint32_t)((lt * PIECE) >> 6) * (8u * CHB) + (uint32_t)lg * CHB + (uint32_t)(((lt * PIECE) & 63) >> SH);
   const float *swp = reinterpret_cast<const float *>(g.sw);
 
   // ---- load side: cursor, and the parts of the addresses that change only with the tile
@@ -340,7 +355,7 @@ __global__ void __launch_bounds__(kGsWarps * 32, 2) gs_decode_kernel(GsDecodeArg
       const bool last = l_c == chunks - 1;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        gs_cp_async<PB>(dw + j * 32 * PB, g.W + l_wbase[j] + koff);
+        gs_cp_async<PB>(dw + j * 32 * PB, g.W + l_wbase[j] + koff, 32u * PU);
         if (last) gs_cp_async<8>(ds + j * 32 * 8, swp + (uint32_t)l_grp * (uint32_t)g.N + l_n0[j]);
       }
       if (last) {
@@ -389,12 +404,9 @@ __global__ void __launch_bounds__(kGsWarps * 32, 2) gs_decode_kernel(GsDecodeArg
         c_slot = c_slot + 1 == R ? 0 : c_slot + 1;
         const uint32_t kb = (uint32_t)(grp * g.gs + c * CH);
         uint32_t ral[NR], rah[NR], al[NR], ah[NR];
-        if (CH == 64) { const uint4 v = lds16(a_lo + kb); ral[0] = v.x; ral[1] = v.y; ral[NR > 2 ? 2 : 0] = v.z; ral[NR > 3 ? 3 : 0] = v.w; }
-        else { const uint2 v = lds8(a_lo + kb); ral[0] = v.x; ral[1] = v.y; }
-        if (hi_rows) {
-          if (CH == 64) { const uint4 v = lds16(a_hi + kb); rah[0] = v.x; rah[1] = v.y; rah[NR > 2 ? 2 : 0] = v.z; rah[NR > 3 ? 3 : 0] = v.w; }
-          else { const uint2 v = lds8(a_hi + kb); rah[0] = v.x; rah[1] = v.y; }
-        } else {
+        lds_words<NR>(a_lo + kb, 16u, ral);
+        if (hi_rows) lds_words<NR>(a_hi + kb, 16u, rah);
+        else {
 #pragma unroll
           for (int i = 0; i < NR; ++i) rah[i] = 0;
         }
@@ -403,9 +415,7 @@ __global__ void __launch_bounds__(kGsWarps * 32, 2) gs_decode_kernel(GsDecodeArg
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
           uint32_t rb[RW], b[NR];
-          if (PB == 16) { const uint4 v = lds16(sw_ + j * 32 * PB); rb[0] = v.x; rb[RW > 1 ? 1 : 0] = v.y; rb[RW > 2 ? 2 : 0] = v.z; rb[RW > 3 ? 3 : 0] = v.w; }
-          else if (PB == 8) { const uint2 v = lds8(sw_ + j * 32 * PB); rb[0] = v.x; rb[RW > 1 ? 1 : 0] = v.y; }
-          else rb[0] = lds4(sw_ + j * 32 * PB);
+          lds_words<RW>(sw_ + j * 32 * PB, 32u * PU, rb);
           gs_expand_b<CH, W4>(rb, b);
 #pragma unroll
           for (int i = 0; i < NR; i += 2) mma_m16n8k32<false>(acc[j], al[i], ah[i], al[i + 1], ah[i + 1], b[i], b[i + 1]);
