@@ -52,7 +52,8 @@ enum { B200DNN_FLAG_STABLE_WEIGHTS = 1 };
 
 /* One scale / zero-point tensor: matmul_quantization_params_t::matmul_quant_t
  * (matmul/lowoha_common.hpp:67-86).  count = number of elements: 1 per-tensor,
- * M per-token ({M,1}), N per-channel ({1,N}); 0 = absent. */
+ * M per-token ({M,1}), N per-channel ({1,N}); 0 = absent.  Per-group forms: M*G for a source scale of dims {M,G},
+ * G*N for a weight scale of dims {G,N} (G groups along K; the library derives G from the counts). */
 typedef struct b200dnn_quant_t {
   const void *buff;
   int32_t dt;

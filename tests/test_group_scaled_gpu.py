@@ -187,3 +187,26 @@ def test_decode_form_agrees_with_the_general_kernel(capi, oracle, monkeypatch):
         assert_bf16_close(out, ref, 1, name, atol=1e-5)
         outs[name] = out
     assert_bf16_close(outs["general"], outs["decode"], 1, "general against decode form", atol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(12, 2048, 200), (100, 512, 264)], ids=lambda s: "M%d_K%d_N%d" % s)
+def test_w4a8_per_tensor_source_scale(capi, oracle, shape):
+    """The third source granularity the reference's W4A8 contract allows, scale dims {1,1} (lowoha_matmul_utils.cpp:160-178):
+    one dynamic scale for the whole source (abs-max / 127, then the static quantise), used for every group."""
+    M, K, N = shape
+    gs = 128
+    G = K // gs
+    rng = np.random.default_rng(M + N)
+    X = oracle.f32_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    W = rng.integers(-8, 8, (K, N), dtype=np.int8)
+    sw = rng.uniform(1e-3, 5e-3, (G, N)).astype(np.float32)
+    s = oracle.dyn_scales(X, per_channel=False)
+    A = oracle.quant_static(X, s)
+    ref = oracle.matmul_group_scaled(A, W, np.repeat(s, M), sw, "bf16")
+    out = np.zeros((M, N), dtype=np.uint16)
+    sc = np.zeros(1, dtype=np.float32)
+    d = capi.make_matmul(M, N, K, X, oracle.pack_s4(W), out, src_dt=capi.DT["bf16"], dst_dt=capi.DT["bf16"], src_scale=capi.quant(sc, count=1),
+                         wei_scale=capi.quant(sw, count=G * N), weights_const=False, dynamic_quant=True, wei_dt=capi.DT["s4"])
+    _call(capi, d)
+    assert (sc == s).all()
+    assert_bf16_close(out, ref, 1, "w4a8 per-tensor source scale", atol=1e-5)

@@ -18,7 +18,7 @@ inline bool is_group_scaled(const b200dnn_matmul_t *d) {
   return false;
 }
 
-struct GsPlan { int G; int gs; bool w4; bool dyn; int src_cols; };
+struct GsPlan { int G; int gs; bool w4; bool dyn; int src_cols; bool src_per_tensor; };
 
 int32_t validate_group_scaled(const b200dnn_matmul_t *d, GsPlan *p) {
   const int M = d->M, N = d->N, K = d->K;
@@ -56,9 +56,10 @@ int32_t validate_group_scaled(const b200dnn_matmul_t *d, GsPlan *p) {
   // source scales {M,G}, or {M,1} when the library quantises per token
   const auto &ss = d->src_scale;
   int src_cols;
+  bool per_tensor = false;
   if (ss.count == (int64_t)M * G) src_cols = (int)G;
   else if (dyn && (ss.count == M || ss.count == 0)) src_cols = 1;
-  else if (dyn && ss.count == 1) return fail(B200DNN_UNIMPLEMENTED, "per-tensor dynamic source scale is not implemented with per-group weight scales");
+  else if (dyn && ss.count == 1) { src_cols = 1; per_tensor = true; }      // {1,1}: one scale for the whole source
   else return fail(B200DNN_FAILURE, "source scale dims must be {M,G}%s (count %lld, M %d, G %lld)", dyn ? " or {M,1}" : "", (long long)ss.count, M, (long long)G);
   if (!dyn) B2_CHECK(ss.buff && ss.dt == B200DNN_F32, ss.buff ? B200DNN_UNIMPLEMENTED : B200DNN_FAILURE, "per-group source scales: an f32 buffer is required");
   else B2_CHECK(!ss.buff || ss.dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "dynamic per-group source scales are written as f32");
@@ -75,7 +76,7 @@ int32_t validate_group_scaled(const b200dnn_matmul_t *d, GsPlan *p) {
     default: return fail(B200DNN_UNIMPLEMENTED, "post-op %d is not implemented", po.type);
     }
   }
-  p->G = (int)G; p->gs = (int)gs; p->w4 = w4; p->dyn = dyn; p->src_cols = src_cols;
+  p->G = (int)G; p->gs = (int)gs; p->w4 = w4; p->dyn = dyn; p->src_cols = src_cols; p->src_per_tensor = per_tensor;
   return B200DNN_SUCCESS;
 }
 
@@ -108,6 +109,12 @@ int32_t resolve_gs_weight(const b200dnn_matmul_t *d, bool w4, int64_t Kp, cudaSt
   pw->wt = (const int8_t *)buf; pw->K = K; pw->N = N; pw->Kp = Kp; pw->Np = N; pw->gated = w4 ? kGsLayoutS4 : kGsLayoutS8;
   if (cache) { pw->owned = buf; B2_TRY(mark_ready(*pw, st)); D.wcache.emplace(key, *pw); }
   return B200DNN_SUCCESS;
+}
+
+// one f32 value replicated n times (a per-tensor source scale as the per-row scales the kernels read)
+__global__ void gs_fill_f32_kernel(float *dst, const float *value, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = *value;
 }
 
 template <int NT, int CH>
@@ -208,7 +215,7 @@ int32_t matmul_group_scaled(const b200dnn_matmul_t *d, cudaStream_t st) {
   const void *src_dev = nullptr;
   B2_TRY(stage_in(d->src, span_bytes(M, K, d->lda, d->src_dt), st, &src_dev));
   Staged o_scale; o_scale.copy_back = false;
-  if (p.dyn) B2_TRY(stage_out(const_cast<void *>(d->src_scale.buff), (size_t)M * p.src_cols * 4, st, &o_scale));
+  if (p.dyn) B2_TRY(stage_out(const_cast<void *>(d->src_scale.buff), (size_t)(p.src_per_tensor ? 1 : M * p.src_cols) * 4, st, &o_scale));
 
   GsGemmArgs a{};
   a.sa_cols = p.src_cols;
@@ -224,7 +231,31 @@ int32_t matmul_group_scaled(const b200dnn_matmul_t *d, cudaStream_t st) {
     B2_CHECK(A, B200DNN_FAILURE, "workspace allocation failed");
     if (Kp != K) B2_CUDA(cudaMemsetAsync(A, 0, (size_t)M * Kp, st));
     const float *sa = nullptr;
-    if (p.dyn) {
+    if (p.dyn && p.src_per_tensor) {
+      // one dynamic scale for the whole source (the reference's per-tensor rule: abs-max over the finite values / 127, then
+      // the static quantise; reorder/lowoha_reorder_utils.cpp:708-766), replicated per row for the kernels
+      uint32_t *amax = (uint32_t *)R.ws.alloc(4);
+      float *s1 = (float *)o_scale.dev;
+      if (!s1) s1 = (float *)R.ws.alloc(4);
+      float *sc = (float *)R.ws.alloc((size_t)M * 4);
+      B2_CHECK(amax && s1 && sc, B200DNN_FAILURE, "workspace allocation failed");
+      B2_CUDA(cudaMemsetAsync(amax, 0, 4, st));
+      dim3 grid((unsigned)((K + 255) / 256), (unsigned)(M < 64 ? 1 : (M / 64 > 256 ? 256 : M / 64)));
+      dim3 g2((unsigned)((K + 255) / 256), (unsigned)(M > 1024 ? 1024 : M));
+      if (d->src_dt == B200DNN_BF16) {
+        absmax_cols_kernel<uint16_t><<<grid, 256, 0, st>>>((const uint16_t *)src_dev, M, K, d->lda, 0, amax);
+        scales_from_absmax_kernel<<<1, 32, 0, st>>>(amax, 1, s1);
+        quant_static_kernel<uint16_t><<<g2, 256, 0, st>>>((const uint16_t *)src_dev, M, K, d->lda, s1, 1, nullptr, 0, A, B200DNN_S8, Kp);
+      } else {
+        absmax_cols_kernel<float><<<grid, 256, 0, st>>>((const float *)src_dev, M, K, d->lda, 0, amax);
+        scales_from_absmax_kernel<<<1, 32, 0, st>>>(amax, 1, s1);
+        quant_static_kernel<float><<<g2, 256, 0, st>>>((const float *)src_dev, M, K, d->lda, s1, 1, nullptr, 0, A, B200DNN_S8, Kp);
+      }
+      gs_fill_f32_kernel<<<(unsigned)((M + 255) / 256), 256, 0, st>>>(sc, s1, M);
+      B2_LAUNCHED(); B2_LAUNCHED(); B2_LAUNCHED(); B2_LAUNCHED();
+      B2_CUDA(cudaGetLastError());
+      sa = sc;
+    } else if (p.dyn) {
       const int64_t n_sc = (int64_t)M * p.src_cols;
       float *sc = (float *)o_scale.dev;
       if (!sc) { sc = (float *)R.ws.alloc((size_t)n_sc * 4); B2_CHECK(sc, B200DNN_FAILURE, "workspace allocation failed"); }
