@@ -80,7 +80,7 @@ typedef struct b200dnn_matmul_t {
   int32_t transB;        /* 0: weight is [K,ldb]; 1: weight is [N,ldb] */
   int32_t src_dt;        /* u8 | s8, or bf16 | f32 together with dynamic_quant */
   int32_t wei_dt;        /* s8 */
-  int32_t dst_dt;        /* bf16 | f32 | s32 */
+  int32_t dst_dt;        /* bf16 | f32 | s32, or s8 | u8 with dst_scale (requantised destination) */
   int32_t bias_dt;       /* f32 | bf16; ignored when bias == NULL */
   int64_t lda, ldb, ldc; /* in elements */
   const void *src;
@@ -97,6 +97,12 @@ typedef struct b200dnn_matmul_t {
   b200dnn_postop_t postops[B200DNN_MAX_POSTOPS];
   int32_t force_kernel;  /* for tests: 0 auto, 1 weight-streaming kernels, 2 tcgen05 kernel, 3 tiled streaming kernel only */
   int32_t flags;         /* B200DNN_FLAG_* */
+  /* requantised integer destination (dst_dt s8 | u8): after bias and post-ops, q = rne(clamp(x * dst_scale + dst_zp)), the
+   * last step of the reference's epilogue chain (matmul/backends/aocl/aocl_postop.cpp:1339-1453; definition
+   * operators/matmul/matmul_ref_kernel.cpp:155-192,770-797).  dst_scale: per-tensor f32 (count 1; absent = 1); dst_zp:
+   * optional, per-tensor s32.  Ignored for float and s32 destinations. */
+  b200dnn_quant_t dst_scale;
+  b200dnn_quant_t dst_zp;
 } b200dnn_matmul_t;
 
 B200DNN_API const char *b200dnn_last_error(void);

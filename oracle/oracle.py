@@ -307,6 +307,19 @@ def matmul_w8a8(A, B, dst_dt="bf16", transB=False, src_scale=None, wei_scale=Non
     return epilogue(acc, dst_dt, src_scale, wei_scale, src_zp, cs, bias, postops, order)
 
 
+def requant_dst(x, dst_dt, dst_scale=None, dst_zp=None):
+    """Requantised matmul destination over the f32 epilogue result: x * dst_scale + dst_zp in f32
+    (operators/matmul/matmul_ref_kernel.cpp:770-797), clamp to the range of the type and nearbyint (:155-192)."""
+    x = np.asarray(x, dtype=np.float32)
+    if dst_scale is not None:
+        x = x * np.float32(np.asarray(dst_scale, dtype=np.float32).reshape(-1)[0])
+    if dst_zp is not None:
+        x = x + np.float32(int(np.asarray(dst_zp).reshape(-1)[0]))
+    lo, hi, t = (0.0, 255.0, np.uint8) if dst_dt == "u8" else (-128.0, 127.0, np.int8)
+    x = np.where(x < lo, np.float32(lo), np.where(x > hi, np.float32(hi), x))
+    return np.rint(np.nan_to_num(x, nan=0.0)).astype(t)
+
+
 def matmul_group_scaled(A, B, src_scale, wei_scale, dst_dt="bf16", bias=None, postops=()):
     """Per-group symmetric INT8 matmul_direct (and W4A8 after the s4 -> s8 widening), the reference's scalar formula
     (operators/matmul/matmul_ref_kernel.cpp:961-1003): A s8 [M,K], B s8 [K,N], src_scale f32 [M,G] or [M] / [M,1]

@@ -176,6 +176,53 @@ static void test_int8_sym_quant_per_group() {
   }
 }
 
+// INT8 with a quantised u8 / s8 output tensor: dst_scale and dst_zp close the epilogue chain
+// (backends/aocl/aocl_postop.cpp:1421-1448), clamp and nearbyint as operators/matmul/matmul_ref_kernel.cpp:155-192
+static void test_int8_requantised_dst() {
+  Rng r(13);
+  const int M = 70, K = 192, N = 88;
+  std::vector<uint8_t> A((size_t)M * K);
+  std::vector<int8_t> W((size_t)K * N);
+  std::vector<float> ws(N), bias(N);
+  for (auto &v : A) v = (uint8_t)r.ri(0, 255);
+  for (auto &v : W) v = (int8_t)r.ri(-127, 127);
+  for (auto &v : ws) v = r.rf(0.002f, 0.01f);
+  for (auto &v : bias) v = r.rn();
+  float ss = 0.02f, ds = 2.0f;
+  int32_t zp = 128, dzp = 11;
+  std::vector<int32_t> acc = gemm_s32(A, K, W, N, false, M, N, K);
+  std::vector<int32_t> colsum(N, 0);
+  for (int k = 0; k < K; ++k) for (int n = 0; n < N; ++n) colsum[n] += W[(size_t)k * N + n];
+  for (int is_u8 = 0; is_u8 < 2; ++is_u8) {
+    std::vector<uint8_t> C((size_t)M * N, 0);
+    matmul_params p;
+    p.dtypes.src = data_type_t::u8; p.dtypes.wei = data_type_t::s8; p.dtypes.dst = is_u8 ? data_type_t::u8 : data_type_t::s8;
+    p.dtypes.bias = data_type_t::f32;
+    p.quant_params.src_scale.buff = &ss; p.quant_params.src_scale.dt = data_type_t::f32; p.quant_params.src_scale.dims = {1};
+    p.quant_params.src_zp.buff = &zp; p.quant_params.src_zp.dt = data_type_t::s32; p.quant_params.src_zp.dims = {1};
+    p.quant_params.wei_scale.buff = ws.data(); p.quant_params.wei_scale.dt = data_type_t::f32; p.quant_params.wei_scale.dims = {1, N};
+    p.quant_params.dst_scale.buff = &ds; p.quant_params.dst_scale.dt = data_type_t::f32; p.quant_params.dst_scale.dims = {1};
+    p.quant_params.dst_zp.buff = &dzp; p.quant_params.dst_zp.dt = data_type_t::s32; p.quant_params.dst_zp.dims = {1};
+    matmul_batch_params_t bp;
+    status_t st = matmul_direct('r', false, false, M, N, K, 1.0f, A.data(), K, W.data(), N, bias.data(), 0.0f, C.data(), N, false, bp, p);
+    CHECK(st == status_t::success, "requantised dst (u8=%d): %s", is_u8, last_error());
+    int worst = 0, off = 0;
+    for (int m = 0; m < M; ++m)
+      for (int n = 0; n < N; ++n) {
+        float x = (float)(acc[(size_t)m * N + n] - zp * colsum[n]);
+        x = x * ss; x = x * ws[n]; x = x + bias[n];
+        x = x * ds; x = x + (float)dzp;
+        const float lo = is_u8 ? 0.f : -128.f, hi = is_u8 ? 255.f : 127.f;
+        x = x < lo ? lo : (x > hi ? hi : x);
+        const int want = (int)std::nearbyint(x);
+        const int got = is_u8 ? (int)C[(size_t)m * N + n] : (int)(int8_t)C[(size_t)m * N + n];
+        worst = std::max(worst, std::abs(want - got));
+        off += want != got;
+      }
+    CHECK(worst <= 1 && off * 500 <= M * N, "requantised dst (u8=%d): worst step %d, %d of %d differ", is_u8, worst, off, M * N);
+  }
+}
+
 // TestMatmul.W4A8_BF16 (zendnnl/gtests/test_matmul.cpp:266): bf16 source quantised by the library, packed s4 weights
 // (two per byte, even index low; backends/aocl/aocl_kernel.cpp:145-160), {G,N} weight scales, bf16 out
 static void test_w4a8_bf16() {
@@ -514,6 +561,7 @@ int main(int argc, char **argv) {
   RUN(test_int8_dynamic_gemm());
   RUN(test_int8_sym_quant_per_group());
   RUN(test_w4a8_bf16());
+  RUN(test_int8_requantised_dst());
   RUN(test_reorder_and_prepack());
   RUN(test_fused_moe_vs_two_call(false, false, false));
   RUN(test_fused_moe_vs_two_call(true, true, false));

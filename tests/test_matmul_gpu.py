@@ -24,7 +24,7 @@ def capi():
 
 
 def run(capi, M, N, K, A, W, dst_dt, **kw):
-    out = np.zeros((M, N), dtype={"bf16": np.uint16, "f32": np.float32, "s32": np.int32}[dst_dt])
+    out = np.zeros((M, N), dtype={"bf16": np.uint16, "f32": np.float32, "s32": np.int32, "s8": np.int8, "u8": np.uint8}[dst_dt])
     d = capi.make_matmul(M, N, K, A, W, out, src_dt=capi.dt_of(A) if "src_dt" not in kw else kw.pop("src_dt"),
                          dst_dt=capi.DT[dst_dt], **kw)
     st = capi.matmul(d)
@@ -591,3 +591,52 @@ def test_group_matmul_mixed_shapes_run_one_by_one(capi, oracle):
     # a negative M is refused
     descs[1].M = -1
     assert capi.lib.b200dnn_group_matmul(G, descs, None) == capi.FAILURE
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("dst", ["s8", "u8"])
+def test_requantised_integer_destination(capi, oracle, kernel, dst):
+    """s8 / u8 destinations: q = rne(clamp(x * dst_scale + dst_zp)) after bias and post-ops, as the reference's INT8
+    cases with a quantised output tensor (zendnnl/gtests/test_matmul.cpp INT8; the definition is
+    operators/matmul/matmul_ref_kernel.cpp:155-192,770-797).  A value whose f32 result sits within an ulp of a rounding
+    boundary may land one step away: at most 0.2 % of the elements, never more than one step."""
+    rng = np.random.default_rng(77)
+    for M, K, N in [(4, 256, 136), (130, 384, 200), (300, 512, 1024)]:
+        A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+        W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+        ss = np.array([0.02], dtype=np.float32)
+        ws = rng.uniform(0.002, 0.01, N).astype(np.float32)
+        bias = rng.standard_normal(N).astype(np.float32)
+        zp_src = np.array([128], dtype=np.int32)
+        ds = np.array([2.5], dtype=np.float32)
+        dz = np.array([17 if dst == "u8" else -5], dtype=np.int32)
+        for postops, use_zp, tol in (([], True, 1), (["relu"], False, 1), (["gelu_tanh"], True, 1)):
+            x = oracle.matmul_w8a8(A, W, "f32", src_scale=ss, wei_scale=ws, src_zp=128, bias=bias, postops=postops)
+            ref = oracle.requant_dst(x, dst, ds, dz if use_zp else None)
+            got = run(capi, M, N, K, A, W, dst, weights_const=False, force_kernel=kernel, src_scale=ss, wei_scale=ws,
+                      src_zp=zp_src, bias=bias, postops=postops, dst_scale=ds, dst_zp=dz if use_zp else None)
+            diff = np.abs(got.astype(np.int32) - ref.astype(np.int32))
+            assert diff.max() <= tol and (diff != 0).mean() < 2e-3, (M, K, N, postops, int(diff.max()), float((diff != 0).mean()))
+            assert len(np.unique(got)) > 20       # the case covers the range, saturated ends included
+    # strided destination, no scale (clamp and round only), device memory
+    M, K, N, ldc = 33, 128, 72, 80
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    ws = np.full(1, 1e-3, dtype=np.float32)
+    out = np.full((M, ldc), 99, dtype={"s8": np.int8, "u8": np.uint8}[dst])
+    d = capi.make_matmul(M, N, K, A, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT[dst], ldc=ldc, weights_const=False,
+                         force_kernel=kernel, wei_scale=ws)
+    assert capi.matmul(d) == capi.SUCCESS, capi.last_error()
+    ref = oracle.requant_dst(oracle.matmul_w8a8(A, W, "f32", wei_scale=ws), dst)
+    assert np.abs(out[:, :N].astype(np.int32) - ref).max() <= 1 and (out[:, :N] != ref).mean() < 2e-3 and (out[:, N:] == 99).all()
+
+
+def test_requantised_destination_contract(capi):
+    M, K, N = 8, 64, 32
+    A = np.zeros((M, K), dtype=np.int8); W = np.zeros((K, N), dtype=np.int8); out = np.zeros((M, N), dtype=np.int8)
+    per_channel = np.ones(N, dtype=np.float32)
+    d = capi.make_matmul(M, N, K, A, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["s8"], weights_const=False, dst_scale=per_channel)
+    assert capi.matmul(d) == capi.FAILURE and "per-tensor" in capi.last_error()
+    d = capi.make_matmul(M, N, K, A, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["s8"], weights_const=False,
+                         dst_zp=np.zeros(1, dtype=np.int32))
+    assert capi.matmul(d) == capi.UNIMPLEMENTED

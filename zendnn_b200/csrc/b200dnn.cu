@@ -1003,6 +1003,16 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   Staged o_dst;
   B2_TRY(stage_out(d->dst, span_bytes(M, N, d->ldc, d->dst_dt), st, &o_dst, d->ldc != N));
   epi.dst = o_dst.dev;
+  // requantised integer destination: the GEMM writes f32 into the workspace, one more pass scales, shifts, clamps and rounds
+  const bool requant = d->dst_dt == B200DNN_S8 || d->dst_dt == B200DNN_U8;
+  const void *dst_scale_dev = nullptr, *dst_zp_dev = nullptr;
+  if (requant) {
+    float *tmp = (float *)R.ws.alloc((size_t)M * N * 4);
+    B2_CHECK(tmp, B200DNN_FAILURE, "workspace allocation failed");
+    epi.dst = tmp; epi.ldc = N; epi.dst_dt = B200DNN_F32;
+    if (d->dst_scale.buff) B2_TRY(stage_in(d->dst_scale.buff, 4, st, &dst_scale_dev, &R.small));
+    if (d->dst_zp.buff) B2_TRY(stage_in(d->dst_zp.buff, 4, st, &dst_zp_dev, &R.small));
+  }
   B2_TRY(R.small.flush(st, o_dst.copy_back || o_dst.sync));
 
   // ---- kernel choice: weight-streaming kernel for decode-sized M, tcgen05 otherwise
@@ -1036,6 +1046,13 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
     ta.pair = tile_rows > kTcBM ? 1 : 0;
     ta.n_groups = 1; ta.m_tiles_plain = (M + tile_rows - 1) / tile_rows; ta.shared_dst = 1;
     B2_TRY(launch_tc(A, lda, a_unsigned, M, N, K, pw, ta, epi, ta.m_tiles_plain, st));
+  }
+  if (requant) {
+    const int64_t n = (int64_t)M * N;
+    requant_dst_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const float *)epi.dst, M, N, (const float *)dst_scale_dev,
+                                                                    (const int32_t *)dst_zp_dev, o_dst.dev, d->dst_dt, d->ldc);
+    B2_LAUNCHED();
+    B2_CUDA(cudaGetLastError());
   }
   return finish_out({&o_dst, &o_scale}, st);   // calls that synchronise read the status word there
 }

@@ -106,8 +106,9 @@ status_t flatten(const char layout, const bool transA, const bool transB, const 
   if (bp.Batch_A != 1 || bp.Batch_B != 1) return shim_fail(status_t::unimplemented, "batched matmul is not implemented");
   if (alpha != 1.0f || beta != 0.0f) return shim_fail(status_t::unimplemented, "only alpha = 1, beta = 0 is implemented");
   if (p.packing.pack_format_b != 0) return shim_fail(status_t::unimplemented, "GGML-packed weights are not implemented");
-  if (p.quant_params.dst_scale.buff || p.quant_params.dst_zp.buff)
-    return shim_fail(status_t::unimplemented, "requantised (s8/u8) destinations are not implemented");
+  const bool int_dst = p.dtypes.dst == data_type_t::s8 || p.dtypes.dst == data_type_t::u8;
+  if (!int_dst && (p.quant_params.dst_scale.buff || p.quant_params.dst_zp.buff))
+    return shim_fail(status_t::unimplemented, "a destination scale or zero point is implemented for s8/u8 destinations only");
   if (p.quant_params.wei_zp.buff) return shim_fail(status_t::unimplemented, "weight zero-points are not implemented");
   if (p.postop_.size() > B200DNN_MAX_POSTOPS) return shim_fail(status_t::failure, "too many post-ops");
   // W4A8 (s4 weights, bf16 source quantised by the library): the reference wants s8 compute and 2-D scale dims
@@ -130,6 +131,11 @@ status_t flatten(const char layout, const bool transA, const bool transB, const 
   d->wei_scale = flat_quant(p.quant_params.wei_scale);
   d->src_zp = flat_quant(p.quant_params.src_zp);
   if (!p.quant_params.src_zp.buff) d->src_zp.count = 0;
+  if (int_dst) {
+    d->dst_scale = flat_quant(p.quant_params.dst_scale);
+    d->dst_zp = flat_quant(p.quant_params.dst_zp);
+    if (!p.quant_params.dst_zp.buff) d->dst_zp.count = 0;
+  }
   d->n_postops = static_cast<int32_t>(p.postop_.size());
   for (int i = 0; i < d->n_postops; ++i) {
     const matmul_post_op &po = p.postop_[i];

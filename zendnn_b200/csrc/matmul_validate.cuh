@@ -28,8 +28,17 @@ inline int32_t validate_matmul_desc(const b200dnn_matmul_t *d) {
   B2_CHECK(d->lda >= K && d->ldc >= N, B200DNN_FAILURE, "lda/ldc smaller than the row length");
   B2_CHECK(d->wei_format == 'r' || d->ldb >= (d->transB ? K : N), B200DNN_FAILURE, "ldb smaller than the row length");
   B2_CHECK(d->wei_dt == B200DNN_S8, B200DNN_UNIMPLEMENTED, "only s8 weights are implemented (wei dtype %d)", d->wei_dt);
-  B2_CHECK(d->dst_dt == B200DNN_BF16 || d->dst_dt == B200DNN_F32 || d->dst_dt == B200DNN_S32, B200DNN_UNIMPLEMENTED,
+  const bool int_dst = d->dst_dt == B200DNN_S8 || d->dst_dt == B200DNN_U8;
+  B2_CHECK(d->dst_dt == B200DNN_BF16 || d->dst_dt == B200DNN_F32 || d->dst_dt == B200DNN_S32 || int_dst, B200DNN_UNIMPLEMENTED,
            "dst dtype %d is not implemented for the INT8 path", d->dst_dt);
+  if (int_dst) {
+    // requantised destination: per-tensor scale (matmul/lowoha_matmul_utils.cpp:307-309), optional per-tensor zero point
+    // (without a scale the result is clamped and rounded as it is)
+    B2_CHECK(!d->dst_scale.buff || d->dst_scale.count == 1, B200DNN_FAILURE, "Destination quant scale supports only per-tensor");
+    B2_CHECK(!d->dst_scale.buff || d->dst_scale.dt == B200DNN_F32, B200DNN_UNIMPLEMENTED, "dst_scale must be f32");
+    B2_CHECK(d->dst_scale.buff || !d->dst_zp.buff, B200DNN_UNIMPLEMENTED, "a destination zero point needs a destination scale");
+    B2_CHECK(!d->dst_zp.buff || (d->dst_zp.count == 1 && d->dst_zp.dt == B200DNN_S32), B200DNN_UNIMPLEMENTED, "dst zero point must be one s32 value");
+  }
   B2_CHECK(d->n_postops >= 0 && d->n_postops <= B200DNN_MAX_POSTOPS, B200DNN_FAILURE, "too many post-ops");
   const bool dyn = d->dynamic_quant != 0;
   if (dyn) {

@@ -476,6 +476,23 @@ __global__ void quant_static_kernel(const T *src, int64_t M, int64_t N, int64_t 
     else reinterpret_cast<int8_t *>(dst)[m * dst_ld + n] = (int8_t)q;
   }
 }
+// Requantised matmul destination: q = rne(clamp(x * dst_scale + dst_zp)) over an f32 [M,N] result
+// (operators/matmul/matmul_ref_kernel.cpp:770-797 scale and zero point, :155-192 clamp, then nearbyint).
+__global__ void requant_dst_kernel(const float *src, int64_t M, int64_t N, const float *scale, const int32_t *zp, void *dst,
+                                   int32_t dst_dt, int64_t ldc) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * N) return;
+  const int64_t m = i / N, n = i - m * N;
+  float x = src[i];
+  if (scale) x = __fmul_rn(x, *scale);
+  if (zp) x = __fadd_rn(x, (float)*zp);
+  const float lo = dst_dt == DT_U8 ? 0.f : -128.f, hi = dst_dt == DT_U8 ? 255.f : 127.f;
+  x = x < lo ? lo : (x > hi ? hi : x);      // (a NaN passes both comparisons and converts to 0)
+  const int q = __float2int_rn(x);
+  if (dst_dt == DT_U8) reinterpret_cast<uint8_t *>(dst)[m * ldc + n] = (uint8_t)q;
+  else reinterpret_cast<int8_t *>(dst)[m * ldc + n] = (int8_t)q;
+}
+
 __global__ void dequant_static_kernel(const void *src, int32_t src_dt, int64_t M, int64_t N, int64_t ld,
                                       const float *scale, int64_t n_scale, const int32_t *zp, int64_t n_zp,
                                       void *dst, int32_t dst_dt, int64_t dst_ld) {
