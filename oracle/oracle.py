@@ -307,6 +307,23 @@ def matmul_w8a8(A, B, dst_dt="bf16", transB=False, src_scale=None, wei_scale=Non
     return epilogue(acc, dst_dt, src_scale, wei_scale, src_zp, cs, bias, postops, order)
 
 
+def matmul_bf16(A, B, dst_dt="bf16", transB=False, bias=None, postops=()):
+    """bf16 x bf16 matmul_direct: A [M,K] and B [K,N] ([N,K] with transB) as bf16 bit patterns (uint16); exact
+    products summed in double, one rounding to f32, bias, post-ops, RNE to dst."""
+    A = np.ascontiguousarray(A, dtype=np.uint16)
+    B = np.ascontiguousarray(B, dtype=np.uint16)
+    M, K = A.shape
+    N = B.shape[0] if transB else B.shape[1]
+    keep = []
+    b = None if bias is None else np.ascontiguousarray(bias)
+    po = _postops(list(postops), keep)
+    out = np.empty((M, N), dtype={"bf16": np.uint16, "f32": np.float32}[dst_dt])
+    rc = lib().orc_matmul_bf16(_p(A), C.c_int64(K), _p(B), C.c_int64(B.shape[1]), int(bool(transB)), M, N, K,
+                               _p(b), 0 if b is None else _dt_of(b), po, len(postops), _p(out), DT[dst_dt], C.c_int64(N))
+    assert rc == 0
+    return out
+
+
 def requant_dst(x, dst_dt, dst_scale=None, dst_zp=None):
     """Requantised matmul destination over the f32 epilogue result: x * dst_scale + dst_zp in f32
     (operators/matmul/matmul_ref_kernel.cpp:770-797), clamp to the range of the type and nearbyint (:155-192)."""

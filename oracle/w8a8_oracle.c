@@ -268,6 +268,7 @@ static inline float apply_postop(const orc_postop *p, float x, int m, int n) {
   case PO_SIGMOID: return po_sigmoid(x);
   case PO_SWISH: return po_swish(x, 1.0f);
   case PO_TANH: return tanhf(x);
+  case PO_MISH: return x * tanhf(fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))));   /* matmul_ref_kernel.cpp:755-761 */
   case PO_CLIP: { float lo = p->alpha, hi = p->beta; x = x > lo ? x : lo; return x > hi ? hi : x; }
   case PO_BINARY_ADD: return x + load_as_f32(p->buff, p->dt, p->ld ? (int64_t)m * p->ld + n : n);
   case PO_BINARY_MUL: return x * load_as_f32(p->buff, p->dt, p->ld ? (int64_t)m * p->ld + n : n);
@@ -314,6 +315,32 @@ ORC_API int orc_epilogue(const int32_t *acc, int64_t ldacc, int M, int N, int or
         if (n_src_scale > 0) x = x * src_scale[n_src_scale > 1 ? m : 0];
         if (n_wei_scale > 0) x = x * wei_scale[n_wei_scale > 1 ? n : 0];
       }
+      if (bias) x = x + load_as_f32(bias, bias_dt, n);
+      for (int i = 0; i < npo; ++i) x = apply_postop(&po[i], x, m, n);
+      if (dst_dt == DT_BF16) ((uint16_t *)dst)[(int64_t)m * ldc + n] = f32_to_bf16(x);
+      else ((float *)dst)[(int64_t)m * ldc + n] = x;
+    }
+  }
+  return 0;
+}
+
+/* bf16 x bf16 matmul_direct (no quantisation): acc[m,n] = sum_k A[m,k]*B[k,n] over the exact bf16 products, summed
+ * here in double and rounded once to f32 (the reference's kernels sum in f32 in an order of their own; its scalar
+ * definition is operators/matmul/matmul_ref_kernel.cpp compute_matmul), then + bias, post-ops in list order, RNE to dst.
+ * B is [K,ldb] or, with transB, [N,ldb]. */
+ORC_API int orc_matmul_bf16(const uint16_t *A, int64_t lda, const uint16_t *B, int64_t ldb, int transB, int M, int N, int K,
+                            const void *bias, int bias_dt, const orc_postop *po, int npo, void *dst, int dst_dt, int64_t ldc) {
+  if (dst_dt != DT_BF16 && dst_dt != DT_F32) return -1;
+  #pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    for (int n = 0; n < N; ++n) {
+      double acc = 0.0;
+      for (int k = 0; k < K; ++k) {
+        const float a = bf16_to_f32(A[(int64_t)m * lda + k]);
+        const float b = bf16_to_f32(transB ? B[(int64_t)n * ldb + k] : B[(int64_t)k * ldb + n]);
+        acc += (double)a * (double)b;
+      }
+      float x = (float)acc;
       if (bias) x = x + load_as_f32(bias, bias_dt, n);
       for (int i = 0; i < npo; ++i) x = apply_postop(&po[i], x, m, n);
       if (dst_dt == DT_BF16) ((uint16_t *)dst)[(int64_t)m * ldc + n] = f32_to_bf16(x);

@@ -1,0 +1,119 @@
+"""GPU parity tests of the bf16 x bf16 form of b200dnn_matmul (matmul_direct with dtypes bf16:bf16:bf16|f32, the
+reference's non-quantised path and the dtype of its MoE traces) against the CPU oracle, which sums the exact bf16
+products in double.  Tolerance, stated per element: the f32 sum may differ from the exact one by the accumulation
+error of the tensor core, bounded here by 2^-17 * sum_k |a||b| (the reference's own gtests allow K * 9.76e-4 + 1e-2*|ref|,
+zendnnl/gtests/Readme.md "Tolerance Calculation"); a bf16 destination adds its rounding, 2^-8 * |ref|."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from zendnn_b200 import capi as c
+    assert c.lib.b200dnn_device_count() > 0, "no CUDA device"
+    return c
+
+
+def make(oracle, rng, M, K, N, transB=False, wstd=1.0):
+    A = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    W = oracle.f32_to_bf16((rng.standard_normal((N, K) if transB else (K, N)) * wstd).astype(np.float32))
+    return A, W
+
+
+def abs_dot(oracle, A, W, transB):
+    a = np.abs(oracle.bf16_to_f32(A)).astype(np.float64)
+    w = np.abs(oracle.bf16_to_f32(W)).astype(np.float64)
+    return a @ (w.T if transB else w)
+
+
+def run(capi, M, N, K, A, W, dst_dt, **kw):
+    out = np.zeros((M, N), dtype={"bf16": np.uint16, "f32": np.float32}[dst_dt])
+    d = capi.make_matmul(M, N, K, A, W, out, src_dt=capi.DT["bf16"], wei_dt=capi.DT["bf16"], dst_dt=capi.DT[dst_dt], **kw)
+    st = capi.matmul(d)
+    assert st == capi.SUCCESS, capi.last_error()
+    return out
+
+
+def check(oracle, got, ref_f32, bound, dst_dt, what):
+    g = oracle.bf16_to_f32(got) if dst_dt == "bf16" else got
+    tol = bound * 2.0 ** -17 + (np.abs(ref_f32) * 2.0 ** -8 if dst_dt == "bf16" else 0.0) + 1e-30
+    err = np.abs(g.astype(np.float64) - ref_f32)
+    assert (err <= tol).all(), "%s: %d of %d outside the bound, worst err/bound %.3g" % (
+        what, int((err > tol).sum()), err.size, float((err / tol).max()))
+
+
+SHAPES = [(1, 64, 16), (5, 100, 24), (16, 256, 64), (33, 260, 80), (130, 384, 200), (257, 1024, 264), (300, 4096, 1024)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dst", ["bf16", "f32"])
+def test_plain_gemm(capi, oracle, shape, dst):
+    M, K, N = shape
+    rng = np.random.default_rng(M * 7 + K)
+    for transB in (False, True):
+        A, W = make(oracle, rng, M, K, N, transB)
+        ref = oracle.matmul_bf16(A, W, "f32", transB=transB).astype(np.float64)
+        got = run(capi, M, N, K, A, W, dst, weights_const=False, transB=transB)
+        check(oracle, got, ref, abs_dot(oracle, A, W, transB), dst, "%s transB=%d" % (shape, transB))
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+def test_pair_form_and_bias(capi, oracle, monkeypatch, pair):
+    """Both tile forms (one CTA per 128-row tile, two CTAs per 256-row tile), f32 and bf16 bias."""
+    monkeypatch.setenv("B200DNN_TC_PAIR", str(pair))
+    rng = np.random.default_rng(3 + pair)
+    for M, K, N in [(512, 512, 768), (700, 1000, 520)]:
+        A, W = make(oracle, rng, M, K, N, wstd=0.05)
+        for bias in (rng.standard_normal(N).astype(np.float32), oracle.f32_to_bf16(rng.standard_normal(N).astype(np.float32))):
+            ref = oracle.matmul_bf16(A, W, "f32", bias=bias).astype(np.float64)
+            got = run(capi, M, N, K, A, W, "bf16", weights_const=False, bias=bias)
+            check(oracle, got, ref, abs_dot(oracle, A, W, False) + 1.0, "bf16", "pair=%d %s" % (pair, (M, K, N)))
+
+
+@pytest.mark.parametrize("name", ["relu", "gelu_tanh", "gelu_erf", "sigmoid", "swish", "tanh", "elu", "leaky_relu", "mish"])
+def test_eltwise_postops(capi, oracle, name):
+    from helpers import assert_bf16_close
+    rng = np.random.default_rng(11)
+    M, K, N = 150, 256, 136
+    A, W = make(oracle, rng, M, K, N, wstd=0.08)
+    bias = rng.standard_normal(N).astype(np.float32)
+    po = [dict(type=name, alpha=1.0)] if name == "elu" else [name]
+    ref = oracle.matmul_bf16(A, W, "bf16", bias=bias, postops=po)
+    got = run(capi, M, N, K, A, W, "bf16", weights_const=False, bias=bias, postops=po)
+    assert_bf16_close(got, ref, 1, name, atol=2e-4)
+
+
+def test_postop_chain_strides_and_cache(capi, oracle):
+    from helpers import assert_bf16_close
+    rng = np.random.default_rng(12)
+    M, K, N, lda, ldc = 70, 192, 72, 200, 96
+    Afull = oracle.f32_to_bf16(rng.standard_normal((M, lda)).astype(np.float32))
+    A = np.ascontiguousarray(Afull[:, :K])
+    W = oracle.f32_to_bf16((rng.standard_normal((K, N)) * 0.1).astype(np.float32))
+    add = rng.normal(size=(1, N)).astype(np.float32)
+    mul = rng.normal(size=(M, N)).astype(np.float32)
+    po = [dict(type="binary_add", buff=add), "swish", dict(type="binary_mul", buff=mul), dict(type="clip", alpha=-0.5, beta=0.75)]
+    ref = oracle.matmul_bf16(A, W, "bf16", postops=po)
+    out = np.full((M, ldc), 0x4040, dtype=np.uint16)
+    d = capi.make_matmul(M, N, K, Afull, W, out, src_dt=capi.DT["bf16"], wei_dt=capi.DT["bf16"], dst_dt=capi.DT["bf16"],
+                         lda=lda, ldc=ldc, weights_const=True, postops=po)
+    for _ in range(2):                         # the second call takes the cached pack
+        out[:] = 0x4040
+        assert capi.matmul(d) == capi.SUCCESS, capi.last_error()
+        assert_bf16_close(out[:, :N], ref, 1, "chain", atol=2e-4)
+        assert (out[:, N:] == 0x4040).all()
+
+
+def test_contract(capi):
+    M, K, N = 8, 64, 32
+    A = np.zeros((M, K), dtype=np.uint16); W = np.zeros((K, N), dtype=np.uint16); out = np.zeros((M, N), dtype=np.uint16)
+    bf = capi.DT["bf16"]
+    one = np.ones(1, dtype=np.float32)
+    d = capi.make_matmul(M, N, K, A, W, out, src_dt=bf, wei_dt=bf, dst_dt=bf, src_scale=one)
+    assert capi.matmul(d) == capi.FAILURE and "only supported for INT8" in capi.last_error()
+    d = capi.make_matmul(M, N, K, A, W, out, src_dt=bf, wei_dt=bf, dst_dt=capi.DT["s32"])
+    assert capi.matmul(d) == capi.UNIMPLEMENTED
+    d = capi.make_matmul(M, N, K, A, W, out, src_dt=bf, wei_dt=bf, dst_dt=bf, lda=K - 1)
+    assert capi.matmul(d) == capi.FAILURE

@@ -462,7 +462,8 @@ int tc_tile_rows(long long rows, int N) {
   return tiles >= 2LL * (rt().sm_count / 2) ? 2 * kTcBM : kTcBM;
 }
 
-// Plain or grouped tcgen05 GEMM.  A: [M_total, lda] device, 16-byte aligned rows.
+// Plain or grouped tcgen05 GEMM.  A: [M_total, lda] device, 16-byte aligned rows.  bf16 form (args.f16): K and lda count
+// bytes (two per element) and pw0 holds a bf16 pack.
 int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, int N, int K, const PackedWeight &pw0,
                   TcGemmArgs args, const EpiParams &epi, int m_tiles_hint, cudaStream_t st) {
   Runtime &R = rt();
@@ -493,7 +494,7 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
 #endif
   args.BN = pick_bn(m_tiles_hint, N, R.sm_count, pw0.gated, args.pair);
   args.k_splits = 1;
-  if (!args.pair && args.n_groups <= 1 && !args.maps_b && !args.groups && !args.tile_prefix && !pw0.gated) pick_split(m_tiles_hint, N, args.k_blocks, &args.BN, &args.k_splits);
+  if (!args.f16 && !args.pair && args.n_groups <= 1 && !args.maps_b && !args.groups && !args.tile_prefix && !pw0.gated) pick_split(m_tiles_hint, N, args.k_blocks, &args.BN, &args.k_splits);
   B2_CHECK(args.BN % 32 == 0 && args.BN >= 32 && args.BN <= 256 && (!pw0.gated || args.BN % 64 == 0), B200DNN_FAILURE,
            "bad tile width %d", args.BN);
   B2_CHECK(!args.pair || (args.BN % 32 == 0 && args.BN >= 64 && (!pw0.gated || args.BN % 128 == 0)), B200DNN_FAILURE,
@@ -569,7 +570,10 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
       const long long pairs = tiles < R.sm_count / 2 ? (tiles > 0 ? tiles : 1) : R.sm_count / 2;
       cfg.gridDim = dim3((unsigned)(2 * pairs));
       cfg.attrs = attr; cfg.numAttrs = na;
-      B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<false, true>, map_a, map_b, map_c, args, epi));
+      if (args.f16) {
+        B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<false, true, true>, kTcSmemBudget + 1024));
+        B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<false, true, true>, map_a, map_b, map_c, args, epi));
+      } else B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<false, true>, map_a, map_b, map_c, args, epi));
     } else if (args.k_splits > 1) {
       // one cluster of k_splits CTAs per tile; the partial sums need BN * 512 bytes of the stage ring
       B2_CHECK((size_t)args.BN * 512 <= (size_t)stages * stage_bytes, B200DNN_FAILURE, "split form: stage ring smaller than the partial sums");
@@ -583,7 +587,10 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
     } else {
       cfg.gridDim = dim3((unsigned)grid);
       cfg.attrs = attr; cfg.numAttrs = na;
-      B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<false>, map_a, map_b, map_c, args, epi));
+      if (args.f16) {
+        B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<false, false, true>, kTcSmemBudget + 1024));
+        B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<false, false, true>, map_a, map_b, map_c, args, epi));
+      } else B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<false>, map_a, map_b, map_c, args, epi));
     }
   }
   B2_LAUNCHED();
@@ -608,6 +615,7 @@ int32_t fill_epi(const b200dnn_matmul_t *d, EpiParams *e) {
 }  // namespace
 
 #include "gs_api.cuh"
+#include "bf16_api.cuh"
 
 // =========================================================================================== C ABI
 extern "C" {
@@ -940,6 +948,7 @@ int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   B2_CHECK(d, B200DNN_FAILURE, "null descriptor");
   B2_ENTER(stream);
   if (is_group_scaled(d)) return matmul_group_scaled(d, st);   // per-group scales and W4A8: own validation and kernel
+  if (is_bf16_matmul(d)) return matmul_bf16(d, st);             // bf16 x bf16: own validation, the kernel's bf16 form
   Runtime &R = rt();
   const int M = d->M, N = d->N, K = d->K;
   B2_TRY(validate_matmul_desc(d));

@@ -92,6 +92,7 @@ __device__ __forceinline__ float apply_postop(const PostOp &p, float x, int m, i
   case PO_SIGMOID: return act_sigmoid(x);
   case PO_SWISH: return __fmul_rn(x, act_sigmoid(x));
   case PO_TANH: return tanhf(x);
+  case PO_MISH: return __fmul_rn(x, tanhf(__fadd_rn(fmaxf(x, 0.0f), log1pf(expf(-fabsf(x))))));   // x * tanh(softplus(x))
   case PO_CLIP: { float lo = p.alpha, hi = p.beta; x = x > lo ? x : lo; return x > hi ? hi : x; }
   case PO_BINARY_ADD: return __fadd_rn(x, load_as_f32(p.buff, p.dt, p.ld ? (int64_t)m * p.ld + n : n));
   case PO_BINARY_MUL: return __fmul_rn(x, load_as_f32(p.buff, p.dt, p.ld ? (int64_t)m * p.ld + n : n));

@@ -95,6 +95,37 @@ static __global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t *W
   }
 }
 
+// bf16 weight into the same byte layout (a packed row holds 2*K bytes of K, zero-padded to Kp bytes): the tcgen05
+// kernel's bf16 form reads the same [BN rows x 128 B] boxes, 64 elements of K each.
+// grid: (Kp/128, Np/32); block 256.  Each CTA moves a [64 k][32 n] tile of 2-byte elements through shared memory.
+static __global__ void __launch_bounds__(256) pack_weight_bf16_kernel(const uint16_t *W, int64_t ldb, int transB, int64_t K, int64_t N,
+                                                               int64_t Kp, int gated, int64_t I, uint8_t *Wt) {
+  __shared__ uint16_t tile[32][64 + 2];
+  const int64_t k0 = (int64_t)blockIdx.x * 64, pn0 = (int64_t)blockIdx.y * 32;
+  const int64_t n0 = packed_to_logical(pn0, gated, I);
+  const int64_t nstep = gated == 2 ? 2 : 1;
+  const int tid = threadIdx.x;
+  if (!transB) {
+    for (int i = tid; i < 64 * 32; i += 256) {
+      int kk = i >> 5, nn = i & 31;
+      int64_t k = k0 + kk, n = n0 + nn * nstep;
+      tile[nn][kk] = (k < K && pn0 + nn < N) ? W[k * ldb + n] : (uint16_t)0;
+    }
+  } else {
+    for (int i = tid; i < 64 * 32; i += 256) {
+      int nn = i >> 6, kk = i & 63;
+      int64_t k = k0 + kk, n = n0 + nn * nstep;
+      tile[nn][kk] = (k < K && pn0 + nn < N) ? W[n * ldb + k] : (uint16_t)0;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < 32 * 32; i += 256) {
+    int nn = i >> 5, k2 = i & 31;
+    const uint32_t v = (uint32_t)tile[nn][2 * k2] | ((uint32_t)tile[nn][2 * k2 + 1] << 16);
+    *reinterpret_cast<uint32_t *>(Wt + wt_offset(pn0 + nn, (k0 + 2 * k2) * 2, Kp)) = v;
+  }
+}
+
 // one warp per packed row
 static __global__ void __launch_bounds__(256) pack_colsum_kernel(const int8_t *Wt, int64_t Np, int64_t Kp, int32_t *colsum) {
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);

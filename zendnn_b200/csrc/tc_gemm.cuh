@@ -85,6 +85,7 @@ struct TcGemmArgs {
                               // tile and add their int32 partial sums through distributed shared memory (exact in any order)
   int n_fastest;              // tile order: 0 = all row tiles of a column tile first, 1 = all column tiles of a row tile first
   int pair;                   // pair form (tc_gemm_kernel<false, true>): row tiles are 256 rows, m_tiles_plain / tile_prefix count those
+  int f16;                    // bf16 x bf16 form (tc_gemm_kernel<.., .., true>): kind::f16 MMAs, f32 accumulators, no scales
   int32_t *status;            // device word: 0 ok
   unsigned long long *stamps; // timing experiments only (builds with B200DNN_TIMING_EXPERIMENTS): 8 timer values per CTA; else null
 };
@@ -194,6 +195,18 @@ __device__ __forceinline__ void st_shared_v4(uint32_t saddr, uint32_t x, uint32_
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// bf16 x bf16 -> f32, M x N x 16 (32 bytes of K per instruction, as kind::i8)
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}"
+               ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // K-major, SWIZZLE_128B shared-memory operand descriptor: 8-row groups 1024 B apart
 // (stride byte offset), leading byte offset unused for swizzled K-major, descriptor version 1.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
@@ -202,6 +215,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 // instruction descriptor, kind::i8: D = s32, A = u8|s8, B = s8, both K-major, M = 128, N = BN
 __host__ __device__ inline uint32_t make_idesc_i8(int a_unsigned, int BN, int M = kTcBM) {
   return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// instruction descriptor, kind::f16: D = f32, A = B = bf16, both K-major
+__host__ __device__ inline uint32_t make_idesc_bf16(int BN, int M = kTcBM) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 struct TileCoord { int g, row0, rows, m_local0, nt; };
@@ -334,11 +352,18 @@ struct EpiStore {          // where this warp's rows of the current tile go
 
 // One 32-column chunk of one output row.  Results leave, in this order of preference, as 32-byte stores of the lane's own
 // row (destination 32-byte aligned), through the warp's staging block (16-byte aligned), or element by element.
-template <int ACT>
+// accumulator -> f32 before bias: the dequantising chain of the INT8 forms, or the f32 sum of the bf16 form as it is
+template <bool F16>
+__device__ __forceinline__ float tc_acc_f32(uint32_t r, int comp, float s_src, float w) {
+  if constexpr (F16) return __uint_as_float(r);
+  else return __fmul_rn(__fmul_rn((float)((int32_t)r - comp), s_src), w);
+}
+
+template <int ACT, bool F16>
 __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx &cx, const uint32_t (&r)[32], const TileCols &tc,
                                              int c0, int pc0, int N, int m_dst, bool has_bias, const EpiStore &es, int lane) {
-  const bool has_zp = epi.has_zp != 0;
-  if (epi.dst_dt == DT_S32) {
+  const bool has_zp = !F16 && epi.has_zp != 0;
+  if (!F16 && epi.dst_dt == DT_S32) {
     int32_t y[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) y[i] = has_zp ? (int32_t)r[i] - tc.comp[c0 + i] : (int32_t)r[i];
@@ -378,7 +403,8 @@ __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx 
       // shared memory is the busiest resource of this kernel (the tensor core reads its operands from it):
       // bias and compensation are fetched only when they exist
       const int ci = c0 + 16 * h + i;
-      const float4 w4 = *reinterpret_cast<const float4 *>(&tc.ws[ci]);
+      float4 w4 = make_float4(1.f, 1.f, 1.f, 1.f);
+      if constexpr (!F16) w4 = *reinterpret_cast<const float4 *>(&tc.ws[ci]);
       float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
       int4 k4 = make_int4(0, 0, 0, 0);
       if (has_bias) b4 = *reinterpret_cast<const float4 *>(&tc.bias[ci]);
@@ -387,7 +413,7 @@ __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx 
       const int kv[4] = {k4.x, k4.y, k4.z, k4.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float v = __fmul_rn(__fmul_rn((float)((int32_t)r[16 * h + i + j] - kv[j]), cx.s_src), wv[j]);
+        float v = tc_acc_f32<F16>(r[16 * h + i + j], kv[j], cx.s_src, wv[j]);
         if (has_bias) v = __fadd_rn(v, bv[j]);
         x[i + j] = tc_act<ACT>(epi, v, m_dst, pc0 + 16 * h + i + j);
       }
@@ -439,24 +465,27 @@ __device__ __forceinline__ void tc_epi_chunk(const EpiParams &epi, const EpiCtx 
   }
 }
 
+template <bool F16>
 __device__ __forceinline__ void tc_epi_dispatch(int fast_act, const EpiParams &epi, const EpiCtx &cx, const uint32_t (&r)[32],
                                                 const TileCols &tcols, int c0, int pc0, int N, int m_dst, bool has_bias,
                                                 const EpiStore &es, int lane) {
   switch (fast_act) {
-  case FA_NONE: tc_epi_chunk<FA_NONE>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
-  case FA_RELU: tc_epi_chunk<FA_RELU>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
-  case FA_GELU_TANH: tc_epi_chunk<FA_GELU_TANH>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
-  case FA_GELU_ERF: tc_epi_chunk<FA_GELU_ERF>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
-  case FA_SIGMOID: tc_epi_chunk<FA_SIGMOID>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
-  case FA_SWISH: tc_epi_chunk<FA_SWISH>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
-  case FA_TANH: tc_epi_chunk<FA_TANH>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
-  default: tc_epi_chunk<FA_GENERIC>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_NONE: tc_epi_chunk<FA_NONE, F16>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_RELU: tc_epi_chunk<FA_RELU, F16>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_GELU_TANH: tc_epi_chunk<FA_GELU_TANH, F16>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_GELU_ERF: tc_epi_chunk<FA_GELU_ERF, F16>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_SIGMOID: tc_epi_chunk<FA_SIGMOID, F16>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_SWISH: tc_epi_chunk<FA_SWISH, F16>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  case FA_TANH: tc_epi_chunk<FA_TANH, F16>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
+  default: tc_epi_chunk<FA_GENERIC, F16>(epi, cx, r, tcols, c0, pc0, N, m_dst, has_bias, es, lane); break;
   }
 }
 
 // SPLIT: launched in clusters of a.k_splits CTAs, one tile per cluster (see TcGemmArgs::k_splits); plain, non-gated form only.
 // PAIR: launched in clusters of two CTAs that share [256 x BN] tiles through cta_group::2 MMAs (see the head of this file).
-template <bool SPLIT, bool PAIR = false>
+// F16: the bf16 x bf16 form (kind::f16 MMAs over the same byte tiles, f32 accumulators); not with SPLIT, whose partial sums
+// are added as integers.
+template <bool SPLIT, bool PAIR = false, bool F16 = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                const __grid_constant__ CUtensorMap map_c, const TcGemmArgs a, const EpiParams epi) {
@@ -476,6 +505,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0) TC_STAMP(0);
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   static_assert(!(SPLIT && PAIR), "the split form and the pair form are separate kernels");
+  static_assert(!(SPLIT && F16), "the split form adds int32 partial sums");
   // pair form: this CTA holds its 128 rows of A and its half of the tile's weight rows
   const uint32_t a_bytes = kTcBM * kTcBK, b_bytes = (uint32_t)(PAIR ? a.BN / 2 : a.BN) * kTcBK, stage_bytes = a_bytes + b_bytes;
   const int S = a.stages;
@@ -566,7 +596,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && (!PAIR || crank == 0)) {      // pair form: the leader issues for both CTAs
-      const uint32_t idesc = make_idesc_i8(a.a_unsigned, a.BN, tile_m);
+      const uint32_t idesc = F16 ? make_idesc_bf16(a.BN, tile_m) : make_idesc_i8(a.a_unsigned, a.BN, tile_m);
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
       for (int tile = tile0; tile < total_tiles && !s_err; tile += tile_step) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) { s_err = 2; report_status(a.status, 2); break; }
@@ -581,8 +611,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + a_bytes);
 #pragma unroll
           for (int k = 0; k < kTcBK / 32; ++k) {
-            if constexpr (PAIR) tc_mma_i8_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, ((kb - kb_begin) | k) ? 1u : 0u);
-            else tc_mma_i8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, ((kb - kb_begin) | k) ? 1u : 0u);
+            const uint32_t accum = ((kb - kb_begin) | k) ? 1u : 0u;
+            if constexpr (PAIR && F16) tc_mma_bf16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+            else if constexpr (PAIR) tc_mma_i8_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+            else if constexpr (F16) tc_mma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
+            else tc_mma_i8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accum);
           }
           if constexpr (PAIR) tc_commit_pair(empty_bar(stage)); else tc_commit(empty_bar(stage));
           if (++stage == S) { stage = 0; phase ^= 1u; }
@@ -720,7 +753,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int i = 0; i < 32; ++i) x ^= r[i];
             if (x == 0x12345678u) report_status(a.status, 99); continue; }
 #endif
-          tc_epi_dispatch(a.fast_act, epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane);
+          tc_epi_dispatch<F16>(a.fast_act, epi, cx, r, tcols, c * 32, pc0, a.N, m_dst, has_bias, es, lane);
         }
       } else {
         // gated: packed columns [g(32) u(32)] -> 32 outputs; dst is [rows, I] bf16.  Sixteen outputs at a time: their
@@ -754,8 +787,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               float z[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                float gv = __fmul_rn(__fmul_rn((float)(int32_t)rg[i + j], cx.s_src), wg[j]);
-                float uv = __fmul_rn(__fmul_rn((float)(int32_t)ru[i + j], cx.s_src), wu[j]);
+                float gv = tc_acc_f32<F16>(rg[i + j], 0, cx.s_src, wg[j]);
+                float uv = tc_acc_f32<F16>(ru[i + j], 0, cx.s_src, wu[j]);
                 if (has_bias) { gv = __fadd_rn(gv, bg[j]); uv = __fadd_rn(uv, bu[j]); }
                 if (epi.gated_act == ACT_SILU_MUL) z[j] = __fmul_rn(fast_sigmoid_mul(gv, gv), uv);
                 else z[j] = gated_f32(epi.gated_act, gv, uv);
@@ -862,7 +895,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint4 v = ld_shared_v4(base + (uint32_t)((u ^ (row_in_tile & 7)) << 4));
           r[4 * u] = v.x; r[4 * u + 1] = v.y; r[4 * u + 2] = v.z; r[4 * u + 3] = v.w;
         }
-        tc_epi_dispatch(a.fast_act, epi, cx, r, tcols, c * 32, pc_tile + c * 32, a.N, m_dst, has_bias, es, lane);
+        tc_epi_dispatch<false>(a.fast_act, epi, cx, r, tcols, c * 32, pc_tile + c * 32, a.N, m_dst, has_bias, es, lane);
       }
     }
     // nobody leaves while a neighbour may still read its shared memory: arrive as soon as the own reads are done,
