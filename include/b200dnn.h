@@ -196,15 +196,17 @@ B200DNN_API int32_t b200dnn_moe_weighted_reduce(const void *const *row_ptrs, con
  * (matmul/lowoha_matmul.hpp:204-223, matmul/group_matmul/group_matmul_direct.hpp:406-577). */
 typedef struct b200dnn_moe_expert_t {
   int32_t M;             /* rows routed to this expert (0 allowed: skipped) */
-  int32_t reserved;
+  int32_t wei_dt;        /* 0 or B200DNN_S8: s8 weights with scales, both GEMMs on dynamically quantised rows;
+                          * B200DNN_BF16: bf16 weights, no quantisation and no scales (the reference's bf16:bf16:bf16 fused
+                          * MoE, matmul/group_matmul/custom_kernel/ukernel/bf16_microkernel.hpp).  One value for all experts. */
   const void *src;       /* [M,K] bf16 rows gathered by the caller, row stride lda */
   int64_t lda;
-  const void *w13;       /* s8 [K, 2I] = [gate | up] (transB: [2I, K]) */
+  const void *w13;       /* s8 | bf16 [K, 2I] = [gate | up] (transB: [2I, K]) */
   int64_t ldb13;
-  const float *w13_scale; /* [2I] */
-  const void *w2;        /* s8 [I, H] (transB: [H, I]) */
+  const float *w13_scale; /* [2I] (s8 weights) */
+  const void *w2;        /* s8 | bf16 [I, H] (transB: [H, I]) */
   int64_t ldb2;
-  const float *w2_scale; /* [H] */
+  const float *w2_scale; /* [H] (s8 weights) */
   void *dst_down;        /* [M,H] bf16, row stride ldc_down.  NULL (b200dnn_fused_moe only): the result is written back
                           * into `src` with row stride lda, the reference's src-reuse mode
                           * (matmul/group_matmul/group_matmul_direct.hpp:500-566); lda >= H then */

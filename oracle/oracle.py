@@ -554,6 +554,35 @@ def fused_moe(x_bf16, ids, weights, w13, s13, w2, s2, act="silu_and_mul", round_
     return out, slot_out
 
 
+def fused_moe_bf16(x_bf16, ids, weights, w13, w2, act="silu_and_mul", b13=None, b2=None):
+    """bf16:bf16:bf16 fused MoE of group_matmul_direct (no quantisation): per expert Y = X·W13 (+bias) in f32, gated
+    activation on the f32 pairs, Z rounded to bf16, O = bf16(Z·W2 (+bias)), then the top-k weighted reduce
+    (group_matmul/custom_kernel/ukernel/bf16_microkernel.hpp: activation in registers on the f32 accumulators).
+    w13[e] bf16 bits [H,2I] ([gate|up]; element-interleaved for swiglu_oai_mul), w2[e] bf16 bits [I,H].
+    Returns (out [T,H], expert row outputs [T*k,H] in slot order, Z rows [T*k,I])."""
+    T, H = x_bf16.shape
+    k = ids.shape[1]
+    E = len(w13)
+    I = w13[0].shape[1] // 2
+    slot_out = np.zeros((T * k, H), dtype=np.uint16)
+    slot_z = np.zeros((T * k, I), dtype=np.uint16)
+    flat = ids.reshape(-1)
+    for e in range(E):
+        slots = np.nonzero(flat == e)[0]
+        if slots.size == 0:
+            continue
+        xe = np.ascontiguousarray(x_bf16[slots // k])
+        y = matmul_bf16(xe, w13[e], "f32", bias=None if b13 is None else b13[e])
+        if act == "swiglu_oai_mul":
+            z = gated_act_f32_pairs(y[:, 0::2], y[:, 1::2], act)
+        else:
+            z = gated_act_f32_pairs(y[:, :I], y[:, I:], act)
+        slot_z[slots] = z
+        slot_out[slots] = matmul_bf16(z, w2[e], "bf16", bias=None if b2 is None else b2[e])
+    out = moe_weighted_reduce(slot_out, weights, k)
+    return out, slot_out, slot_z
+
+
 def ref_int8_matmul(A_u8, B_s8, src_zp, src_scale, wei_scale, bias=None, fused_op=0, dst_dt="bf16"):
     """Runs the compiled reference tile kernel (per-tensor src scale/zp).  None if unavailable."""
     r = ref_lib()

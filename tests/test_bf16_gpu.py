@@ -3,6 +3,8 @@ reference's non-quantised path and the dtype of its MoE traces) against the CPU 
 products in double.  Tolerance, stated per element: the f32 sum may differ from the exact one by the accumulation
 error of the tensor core, bounded here by 2^-17 * sum_k |a||b| (the reference's own gtests allow K * 9.76e-4 + 1e-2*|ref|,
 zendnnl/gtests/Readme.md "Tolerance Calculation"); a bf16 destination adds its rounding, 2^-8 * |ref|."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -117,3 +119,93 @@ def test_contract(capi):
     assert capi.matmul(d) == capi.UNIMPLEMENTED
     d = capi.make_matmul(M, N, K, A, W, out, src_dt=bf, wei_dt=bf, dst_dt=bf, lda=K - 1)
     assert capi.matmul(d) == capi.FAILURE
+
+
+# ---------------------------------------------------------------------------------- fused MoE, bf16 weights
+def _bf16_experts(oracle, rng, E, H, I):
+    w13 = [oracle.f32_to_bf16((rng.normal(size=(H, 2 * I)) * 0.05).astype(np.float32)) for _ in range(E)]
+    w2 = [oracle.f32_to_bf16((rng.normal(size=(I, H)) * 0.05).astype(np.float32)) for _ in range(E)]
+    return w13, w2
+
+
+def _close(oracle, got, ref, what):
+    """bf16 results of a chain of two GEMMs: a one-ulp difference of an intermediate Z element (its f32 value sits on a
+    rounding boundary) moves a down-projection output by up to 2^-8 |z||w|; accepted: 2 bf16 ulp or 0.4 % of the row maximum."""
+    from helpers import assert_bf16_close
+    assert_bf16_close(got, ref, 2, what, row_atol_frac=4e-3)
+
+
+@pytest.mark.parametrize("T,H,I,E,k,act", [(48, 128, 64, 4, 2, "silu_and_mul"), (300, 256, 160, 6, 2, "silu_and_mul"),
+                                           (64, 136, 96, 3, 1, "gelu_and_mul"), (64, 128, 64, 4, 2, "swiglu_oai_mul")])
+@pytest.mark.parametrize("pair", ["0", "1"])
+def test_fused_moe_bf16_reference_contract(capi, oracle, monkeypatch, pair, T, H, I, E, k, act):
+    """group_matmul_direct in fused-MoE mode with bf16:bf16:bf16 experts: rows gathered by the caller, per-expert dst_down,
+    the activated first-GEMM output in dst_op1, row_ptrs + top-k weights."""
+    monkeypatch.setenv("B200DNN_TC_PAIR", pair)
+    rng = np.random.default_rng(T + I)
+    x = oracle.f32_to_bf16(rng.normal(size=(T, H)).astype(np.float32))
+    logits = rng.normal(size=(T, E)).astype(np.float32)
+    logits[:, 1] = -1e4                      # expert 1 receives no token
+    ids, w = oracle.router_topk(logits, k)
+    w13, w2 = _bf16_experts(oracle, rng, E, H, I)
+    b13 = [rng.normal(size=2 * I).astype(np.float32) * 0.2 for _ in range(E)]
+    out_ref, slot_ref, z_ref = oracle.fused_moe_bf16(x, ids, w, w13, w2, act, b13=b13)
+    flat = ids.reshape(-1)
+    keep, dsts, zs, experts = [], [], [], (capi.MoeExpert * E)()
+    ptrs = (C.c_void_p * (T * k))()
+    for e in range(E):
+        slots = np.nonzero(flat == e)[0]
+        src = np.ascontiguousarray(x[slots // k]) if slots.size else np.zeros((1, H), dtype=np.uint16)
+        dst = np.zeros((max(slots.size, 1), H), dtype=np.uint16)
+        z = np.zeros((max(slots.size, 1), I), dtype=np.uint16)
+        keep.append(src); dsts.append(dst); zs.append(z)
+        ex = experts[e]
+        ex.M = int(slots.size); ex.wei_dt = capi.DT["bf16"]; ex.src = src.ctypes.data; ex.lda = H
+        ex.w13 = w13[e].ctypes.data; ex.ldb13 = 2 * I
+        ex.w2 = w2[e].ctypes.data; ex.ldb2 = H
+        ex.bias13 = b13[e].ctypes.data; ex.bias13_dt = capi.DT["f32"]
+        ex.dst_down = dst.ctypes.data; ex.ldc_down = H
+        ex.dst_op1 = z.ctypes.data; ex.ldc_op1 = I
+        for r, s in enumerate(slots):
+            ptrs[int(s)] = dst.ctypes.data + r * dst.strides[0]
+    out = np.zeros((T, H), dtype=np.uint16)
+    st = capi.lib.b200dnn_fused_moe(E, experts, H, I, H, 0, capi.ACT[act], 0, ptrs, capi.ptr(w), T, k, capi.ptr(out), H, None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert np.abs(oracle.bf16_to_f32(out)).sum() > 1e-3
+    from helpers import assert_bf16_close
+    for e in range(E):
+        slots = np.nonzero(flat == e)[0]
+        if slots.size:
+            assert_bf16_close(zs[e][:slots.size], z_ref[slots], 1, "expert %d activated output" % e, atol=1e-4)
+            _close(oracle, dsts[e][:slots.size], slot_ref[slots], "expert %d down output" % e)
+    _close(oracle, out, out_ref, "moe output")
+    capi.lib.b200dnn_clear_caches()
+
+
+@pytest.mark.parametrize("T,H,I,E,k,S", [(256, 256, 128, 8, 2, 0), (512, 128, 96, 16, 4, 2), (1500, 256, 320, 4, 2, 1)])
+def test_moe_layer_bf16_end_to_end(capi, oracle, T, H, I, E, k, S):
+    """Router + permutation + bf16 fused MoE + un-permute on the device; shared experts see every token with weight 1."""
+    rng = np.random.default_rng(E)
+    x = oracle.f32_to_bf16(rng.normal(size=(T, H)).astype(np.float32))
+    skew = np.log(np.arange(1, E + 1, dtype=np.float64) ** -1.1)
+    logits = (rng.normal(size=(T, E)) + rng.permutation(skew)).astype(np.float32)
+    w13, w2 = _bf16_experts(oracle, rng, E + S, H, I)
+    b2 = [rng.normal(size=H).astype(np.float32) * 0.2 for _ in range(E + S)]
+    ids, w = oracle.router_topk(logits, k)
+    ids_all = np.concatenate([ids, np.tile(np.arange(E, E + S, dtype=np.int32), (T, 1))], axis=1)
+    w_all = np.concatenate([w, np.ones((T, S), dtype=np.float32)], axis=1)
+    out_ref, _, _ = oracle.fused_moe_bf16(x, ids_all, w_all, w13, w2, b2=b2)
+    experts = (capi.MoeExpert * (E + S))()
+    for e in range(E + S):
+        ex = experts[e]
+        ex.wei_dt = capi.DT["bf16"]
+        ex.w13 = w13[e].ctypes.data; ex.ldb13 = 2 * I
+        ex.w2 = w2[e].ctypes.data; ex.ldb2 = H
+        ex.bias2 = b2[e].ctypes.data; ex.bias2_dt = capi.DT["f32"]
+    out = np.zeros((T, H), dtype=np.uint16)
+    st = capi.lib.b200dnn_moe_layer(capi.ptr(x), H, capi.ptr(logits), T, E, S, k, experts, H, I, H, 0, capi.ACT["silu_and_mul"],
+                                    capi.ptr(out), H, None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert np.abs(oracle.bf16_to_f32(out)).sum() > 1e-3
+    _close(oracle, out, out_ref, "moe layer")
+    capi.lib.b200dnn_clear_caches()

@@ -46,7 +46,7 @@ FLAG_STABLE_WEIGHTS = 1
 
 
 class MoeExpert(C.Structure):
-    _fields_ = [("M", C.c_int32), ("reserved", C.c_int32), ("src", C.c_void_p), ("lda", C.c_int64),
+    _fields_ = [("M", C.c_int32), ("wei_dt", C.c_int32), ("src", C.c_void_p), ("lda", C.c_int64),
                 ("w13", C.c_void_p), ("ldb13", C.c_int64), ("w13_scale", C.c_void_p),
                 ("w2", C.c_void_p), ("ldb2", C.c_int64), ("w2_scale", C.c_void_p),
                 ("dst_down", C.c_void_p), ("ldc_down", C.c_int64),

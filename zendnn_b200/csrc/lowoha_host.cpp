@@ -233,8 +233,9 @@ static status_t group_matmul_impl(const std::vector<char> &layout, const std::ve
   if (fused) {
     // ---- fused MoE: Op1 (gate|up) -> gated activation -> per-token requantisation -> Op2 (down) [-> weighted reduce]
     if (act == grp_matmul_gated_act_t::none) return shim_fail(status_t::failure, "fused MoE needs a gated activation");
+    const bool wants_scales = !params.empty() && params[0].dtypes.wei == data_type_t::s8;
     if (fused->down_weight.size() < num_ops || fused->N_down.size() < num_ops || fused->ldb_down.size() < num_ops ||
-        fused->down_scale.size() < num_ops)
+        (wants_scales && fused->down_scale.size() < num_ops))
       return shim_fail(status_t::failure, "fused MoE: down-projection vectors are shorter than the number of experts");
     // mode (1): caller-allocated dst_down; mode (2), dst_down empty: the result is written back into src[]
     // (group_matmul_direct.hpp:500-566: matched src/dst precision and lda >= N_down are preconditions)
@@ -246,9 +247,13 @@ static status_t group_matmul_impl(const std::vector<char> &layout, const std::ve
     if (any_bias_down && fused->bias_dt_down == data_type_t::none)
       return shim_fail(status_t::failure, "fused MoE: bias_down given without bias_dt_down");
     const matmul_params &p0 = params[0];
-    if (!(p0.dynamic_quant && p0.dtypes.src == data_type_t::bf16 && p0.dtypes.wei == data_type_t::s8 &&
-          p0.dtypes.dst == data_type_t::bf16))
-      return shim_fail(status_t::unimplemented, "fused MoE is implemented for dynamic per-token INT8 (bf16 src, s8 weights, bf16 dst)");
+    const bool moe_int8 = p0.dynamic_quant && p0.dtypes.src == data_type_t::bf16 && p0.dtypes.wei == data_type_t::s8 &&
+                          p0.dtypes.dst == data_type_t::bf16;
+    const bool moe_bf16 = !p0.dynamic_quant && p0.dtypes.src == data_type_t::bf16 && p0.dtypes.wei == data_type_t::bf16 &&
+                          p0.dtypes.dst == data_type_t::bf16;
+    if (!moe_int8 && !moe_bf16)
+      return shim_fail(status_t::unimplemented,
+                       "fused MoE is implemented for dynamic per-token INT8 (bf16 src, s8 weights, bf16 dst) and for bf16:bf16:bf16");
     std::vector<b200dnn_moe_expert_t> ex(num_ops);
     for (size_t i = 0; i < num_ops; ++i) {
       if (N[i] != N[0] || K[i] != K[0] || fused->N_down[i] != fused->N_down[0] || transB[i] != transB[0])
@@ -257,16 +262,18 @@ static status_t group_matmul_impl(const std::vector<char> &layout, const std::ve
       if (transA[i] || alpha[i] != 1.0f || beta[i] != 0.0f) return shim_fail(status_t::unimplemented, "fused MoE: transA / alpha / beta");
       if (reuse_src && lda[i] < fused->N_down[i]) return shim_fail(status_t::failure, "fused MoE: src-reuse mode needs lda >= N_down");
       const auto &ws = params[i].quant_params.wei_scale;
-      if (!ws.buff || ws.dt != data_type_t::f32 || nelem(ws.dims) != N[i])
+      if (moe_int8 && (!ws.buff || ws.dt != data_type_t::f32 || nelem(ws.dims) != N[i]))
         return shim_fail(status_t::failure, "fused MoE: per-channel f32 weight scale of N elements required");
-      const auto &ds = fused->down_scale[i];
-      if (!ds.buff || ds.dt != data_type_t::f32 || nelem(ds.dims) != fused->N_down[i])
+      static const grp_matmul_fused_moe_params::down_weight_quant_t no_scale{};
+      const auto &ds = moe_int8 ? fused->down_scale[i] : no_scale;
+      if (moe_int8 && (!ds.buff || ds.dt != data_type_t::f32 || nelem(ds.dims) != fused->N_down[i]))
         return shim_fail(status_t::failure, "fused MoE: per-channel f32 down_scale of N_down elements required");
       b200dnn_moe_expert_t &e = ex[i];
       std::memset(&e, 0, sizeof e);
       e.M = M[i]; e.src = src[i]; e.lda = lda[i];
-      e.w13 = weight[i]; e.ldb13 = ldb[i]; e.w13_scale = static_cast<const float *>(ws.buff);
-      e.w2 = fused->down_weight[i]; e.ldb2 = fused->ldb_down[i]; e.w2_scale = static_cast<const float *>(ds.buff);
+      e.wei_dt = moe_bf16 ? B200DNN_BF16 : B200DNN_S8;
+      e.w13 = weight[i]; e.ldb13 = ldb[i]; e.w13_scale = moe_int8 ? static_cast<const float *>(ws.buff) : nullptr;
+      e.w2 = fused->down_weight[i]; e.ldb2 = fused->ldb_down[i]; e.w2_scale = moe_int8 ? static_cast<const float *>(ds.buff) : nullptr;
       if (!reuse_src) { e.dst_down = fused->dst_down[i]; e.ldc_down = fused->ldc_down[i]; }
       e.bias13 = bias[i]; e.bias13_dt = static_cast<int32_t>(params[i].dtypes.bias);
       if (i < fused->bias_down.size()) { e.bias2 = fused->bias_down[i]; e.bias2_dt = static_cast<int32_t>(fused->bias_dt_down); }

@@ -16,11 +16,12 @@ namespace {
 
 int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const std::vector<PackedWeight> &pws,
                      const int32_t *row_off_dev, const int32_t *tile_prefix_dev, const TcGroupDesc *groups_dev,
-                     int m_tiles_bound, EpiParams epi, bool shared_dst, cudaStream_t st, int tile_rows = kTcBM) {
+                     int m_tiles_bound, EpiParams epi, bool shared_dst, cudaStream_t st, int tile_rows = kTcBM, bool f16 = false) {
   Runtime &Rt = rt();
   const int G = (int)pws.size();
   TcGemmArgs ta{};
   ta.pair = tile_rows > kTcBM ? 1 : 0;  // tile_prefix_dev and m_tiles_bound count tiles of tile_rows rows
+  ta.f16 = f16 ? 1 : 0;                 // bf16 form: lda and K count bytes, pws hold bf16 packs
   ta.shared_dst = shared_dst ? 1 : 0;   // no group carries its own destination
   ta.n_groups = G; ta.row_off = row_off_dev; ta.tile_prefix = tile_prefix_dev; ta.groups = groups_dev;
   // one tensor map per expert, in device memory
@@ -42,11 +43,126 @@ int32_t grouped_gemm(const uint8_t *A, int64_t lda, int R, int N, int K, const s
 struct ExpertWeightsIn {
   const void *w13; int64_t ldb13; const float *s13; const void *w2; int64_t ldb2; const float *s2;
   const void *b13 = nullptr; int32_t b13_dt = 0; const void *b2 = nullptr; int32_t b2_dt = 0;   // optional biases
+  int32_t wei_dt = 0;
 };
 inline ExpertWeightsIn expert_in(const b200dnn_moe_expert_t &e) {
   ExpertWeightsIn w{e.w13, e.ldb13, e.w13_scale, e.w2, e.ldb2, e.w2_scale};
   w.b13 = e.bias13; w.b13_dt = e.bias13_dt; w.b2 = e.bias2; w.b2_dt = e.bias2_dt;
+  w.wei_dt = e.wei_dt;
   return w;
+}
+
+// rows of a bf16 matrix copied to their slots: source row r goes to the rows scatter[r*n + j] of dst (entries < 0 skipped),
+// or, gather form, output row r comes from source row gather[r] / div.  One CTA per source (scatter) or output (gather) row.
+__global__ void __launch_bounds__(256) moe_place_rows_bf16_kernel(const uint16_t *src, int64_t src_ld, const int32_t *scatter, int n,
+                                                                  const int32_t *gather, int div, uint16_t *dst, int64_t dst_ld, int K) {
+  const int r = blockIdx.x;
+  const uint16_t *s;
+  if (gather) {
+    const int g = gather[r];
+    if (g < 0) return;
+    s = src + (int64_t)(g / div) * src_ld;
+    uint16_t *d = dst + (int64_t)r * dst_ld;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) d[k] = s[k];
+    return;
+  }
+  s = src + (int64_t)r * src_ld;
+  const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0 && src_ld % 8 == 0 && dst_ld % 8 == 0 && K % 8 == 0;
+  if (vec) {
+    for (int k = threadIdx.x; k < K / 8; k += blockDim.x) {
+      const uint4 v = reinterpret_cast<const uint4 *>(s)[k];
+      for (int j = 0; j < n; ++j) {
+        const int row = scatter[r * n + j];
+        if (row >= 0) reinterpret_cast<uint4 *>(dst + (int64_t)row * dst_ld)[k] = v;
+      }
+    }
+  } else {
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+      const uint16_t v = s[k];
+      for (int j = 0; j < n; ++j) {
+        const int row = scatter[r * n + j];
+        if (row >= 0) dst[(int64_t)row * dst_ld + k] = v;
+      }
+    }
+  }
+}
+
+// bf16 weights: no quantisation.  X (rows in expert order, bf16) -> GEMM(w13) + gated activation -> Z bf16 -> GEMM(w2) -> O,
+// both GEMMs on the tcgen05 kernel's bf16 form with f32 accumulation
+// (reference: matmul/group_matmul/custom_kernel/ukernel/bf16_microkernel.hpp, gated epilogue on the f32 accumulators).
+int32_t moe_core_bf16(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, int H, int transB, int act, int weights_const,
+                      RowQuantArgs qa, int32_t src_dt, int R, const int32_t *row_off_dev, const int32_t *tile_prefix_dev,
+                      int m_tiles_bound, const std::vector<void *> *dst_down_dev, const std::vector<int64_t> *ldc_down,
+                      void **O_out, int64_t *ldO_out, cudaStream_t st, void *O_given, int tile_rows, const uint16_t **Z_out) {
+  Runtime &Rt = rt();
+  B2_CHECK(src_dt == B200DNN_BF16, B200DNN_UNIMPLEMENTED, "bf16 experts take bf16 rows");
+  B2_CHECK(!qa.scatter_peer && !qa.n_rows_dev, B200DNN_UNIMPLEMENTED, "the expert-parallel exchange is built for s8 experts");
+  const int gated = act == ACT_SWIGLU_OAI ? 2 : 1;
+  std::vector<PackedWeight> p13(G), p2(G);
+  std::vector<TcGroupDesc> g13(G), g2(G);
+  int32_t b13_dt = 0, b2_dt = 0;
+  for (int g = 0; g < G; ++g) {
+    B2_CHECK(ew[g].w13 && ew[g].w2, B200DNN_FAILURE, "expert %d: null weight", g);
+    B2_TRY(resolve_bf16_weight(ew[g].w13, K, 2 * (int64_t)I, ew[g].ldb13, transB, gated, weights_const, st, &p13[g]));
+    B2_TRY(resolve_bf16_weight(ew[g].w2, I, H, ew[g].ldb2, transB, 0, weights_const, st, &p2[g]));
+    const void *b13 = nullptr, *b2 = nullptr;
+    if (ew[g].b13) {
+      B2_CHECK(ew[g].b13_dt == B200DNN_F32 || ew[g].b13_dt == B200DNN_BF16, B200DNN_UNIMPLEMENTED, "expert %d: bias dtype %d", g, ew[g].b13_dt);
+      B2_CHECK(b13_dt == 0 || b13_dt == ew[g].b13_dt, B200DNN_UNIMPLEMENTED, "the experts' first-GEMM biases must share one dtype");
+      b13_dt = ew[g].b13_dt;
+      B2_TRY(stage_in(ew[g].b13, (size_t)2 * I * dt_size(b13_dt), st, &b13));
+    }
+    if (ew[g].b2) {
+      B2_CHECK(ew[g].b2_dt == B200DNN_F32 || ew[g].b2_dt == B200DNN_BF16, B200DNN_UNIMPLEMENTED, "expert %d: down bias dtype %d", g, ew[g].b2_dt);
+      B2_CHECK(b2_dt == 0 || b2_dt == ew[g].b2_dt, B200DNN_UNIMPLEMENTED, "the experts' second-GEMM biases must share one dtype");
+      b2_dt = ew[g].b2_dt;
+      B2_TRY(stage_in(ew[g].b2, (size_t)H * dt_size(b2_dt), st, &b2));
+    }
+    g13[g] = TcGroupDesc{nullptr, nullptr, b13, nullptr, 0};
+    g2[g] = TcGroupDesc{nullptr, nullptr, b2, dst_down_dev ? (*dst_down_dev)[g] : nullptr, ldc_down ? (*ldc_down)[g] : 0};
+  }
+  void *g13_dev, *g2_dev;
+  B2_TRY(cached_blob(g13.data(), sizeof(TcGroupDesc) * G, st, &g13_dev));
+  if (dst_down_dev) B2_TRY(upload_blob(g2.data(), sizeof(TcGroupDesc) * G, st, &g2_dev));
+  else B2_TRY(cached_blob(g2.data(), sizeof(TcGroupDesc) * G, st, &g2_dev));
+
+  // 1. rows in expert order, at a pitch the copy engine accepts
+  const int64_t Kq = round_up(K, 8);
+  const uint16_t *X = (const uint16_t *)qa.src; int64_t ldx = qa.src_ld;
+  const bool placed = qa.scatter || qa.gather;
+  if (placed || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(X) & 15) != 0) {
+    uint16_t *Xs = (uint16_t *)Rt.ws.alloc((size_t)R * Kq * 2);
+    B2_CHECK(Xs, B200DNN_FAILURE, "workspace allocation failed");
+    if (qa.scatter)
+      moe_place_rows_bf16_kernel<<<(unsigned)qa.scatter_rows, 256, 0, st>>>(X, ldx, qa.scatter, qa.scatter_n, nullptr, 1, Xs, Kq, K);
+    else if (qa.gather)
+      moe_place_rows_bf16_kernel<<<(unsigned)R, 256, 0, st>>>(X, ldx, nullptr, 0, qa.gather, qa.gather_div, Xs, Kq, K);
+    else B2_CUDA(cudaMemcpy2DAsync(Xs, (size_t)Kq * 2, X, (size_t)ldx * 2, (size_t)K * 2, (size_t)R, cudaMemcpyDeviceToDevice, st));
+    if (placed) { B2_LAUNCHED(); B2_CUDA(cudaGetLastError()); }
+    X = Xs; ldx = Kq;
+  }
+  rt().mark(2);
+
+  // 2. first GEMM with the gated epilogue -> Z (bf16, [R, I])
+  uint16_t *Z = (uint16_t *)Rt.ws.alloc((size_t)R * I * 2);
+  B2_CHECK(Z, B200DNN_FAILURE, "workspace allocation failed");
+  EpiParams e1{};
+  e1.dst = Z; e1.ldc = I; e1.dst_dt = B200DNN_BF16; e1.gated_act = act; e1.gated_I = I; e1.bias_dt = b13_dt;
+  B2_TRY(grouped_gemm((const uint8_t *)X, ldx * 2, R, 2 * I, 2 * K, p13, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g13_dev,
+                      m_tiles_bound, e1, true, st, tile_rows, true));
+  rt().mark(4);
+
+  // 3. second GEMM reads Z as it is -> O
+  uint16_t *O = (uint16_t *)O_given;
+  if (!dst_down_dev && !O) { O = (uint16_t *)Rt.ws.alloc((size_t)R * H * 2); B2_CHECK(O, B200DNN_FAILURE, "workspace allocation failed"); }
+  EpiParams e2{};
+  e2.dst = O; e2.ldc = H; e2.dst_dt = B200DNN_BF16; e2.bias_dt = b2_dt;
+  B2_TRY(grouped_gemm((const uint8_t *)Z, (int64_t)I * 2, R, H, 2 * I, p2, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)g2_dev,
+                      m_tiles_bound, e2, dst_down_dev == nullptr, st, tile_rows, true));
+  rt().mark(6);
+  if (Z_out) *Z_out = Z;
+  if (O_out) { *O_out = O; *ldO_out = H; }
+  return B200DNN_SUCCESS;
 }
 
 // Shared core: rows already laid out expert by expert in device memory as the gather described by qa.
@@ -59,6 +175,12 @@ int32_t moe_core(int G, const std::vector<ExpertWeightsIn> &ew, int K, int I, in
   B2_CHECK(act >= 1 && act <= 3, B200DNN_UNIMPLEMENTED, "fused MoE needs a gated activation (got %d)", act);
   B2_CHECK(I % kGateGranule == 0, B200DNN_UNIMPLEMENTED, "expert FFN width must be a multiple of %d", kGateGranule);
   const int gated = act == ACT_SWIGLU_OAI ? 2 : 1;
+  const bool wbf16 = ew[0].wei_dt == B200DNN_BF16;
+  for (int g = 0; g < G; ++g)
+    B2_CHECK((ew[g].wei_dt == B200DNN_BF16) == wbf16 && (wbf16 || ew[g].wei_dt == 0 || ew[g].wei_dt == B200DNN_S8), B200DNN_UNIMPLEMENTED,
+             "expert %d: weight dtype %d (all experts s8, or all bf16)", g, ew[g].wei_dt);
+  if (wbf16) return moe_core_bf16(G, ew, K, I, H, transB, act, weights_const, qa, src_dt, R, row_off_dev, tile_prefix_dev, m_tiles_bound,
+                                  dst_down_dev, ldc_down, O_out, ldO_out, st, O_given, tile_rows, Z_out);
   std::vector<PackedWeight> p13(G), p2(G);
   std::vector<TcGroupDesc> g13(G), g2(G);
   int32_t b13_dt = 0, b2_dt = 0;

@@ -3,10 +3,12 @@
   python -m zendnn_b200.run_case matmul <auto|decode|tc> M K N [--copies C] [--reps R] [--act gelu_tanh] [--bias] [--dyn]
   python -m zendnn_b200.run_case moe <c4|c5> [--reps R]
   python -m zendnn_b200.run_case gs <w4a8|s8> M K N --gs G [--copies C] [--reps R]
+  python -m zendnn_b200.run_case bf16 M K N [--copies C] [--reps R] [--act gelu_tanh] [--bias]
 
 matmul: s8 per-token activations x s8 per-channel prepacked weight -> bf16; `--copies` distinct prepacked
 weights are used in turn (pick copies * K * N above the L2 size to keep the weight stream in HBM);
-`--dyn` passes bf16 activations with dynamic_quant.  moe: b200dnn_moe_layer at the shapes of the two MoE
+`--dyn` passes bf16 activations with dynamic_quant.  bf16: bf16 activations x bf16 weights (cached by the library
+after the first call) -> bf16.  moe: b200dnn_moe_layer at the shapes of the two MoE
 configurations (c4: 4096 tokens, hidden 4096, FFN 14336, 8 experts top-2; c5: 16384 tokens, hidden 2048,
 FFN 1408, 64 experts top-6 + 2 shared, Zipf-skewed routing).  Prints the mean time per call.
 """
@@ -55,6 +57,34 @@ def _matmul(args):
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (args.reps * len(descs))
     print("matmul %s M%d K%d N%d: %.2f us per call (stream order, not graph-replayed)" % (args.kernel, M, K, N, us))
+
+
+def _bf16(args):
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    M, K, N = args.M, args.K, args.N
+    g = torch.Generator(device=dev).manual_seed(0)
+    weights = [(torch.randn(K, N, generator=g, device=dev) * 0.02).to(torch.bfloat16) for _ in range(args.copies)]
+    A = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g, device=dev) if args.bias else None
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    bf = capi.DT["bf16"]
+    descs = [capi.make_matmul(M, N, K, A, w, out, src_dt=bf, wei_dt=bf, dst_dt=bf, bias=bias,
+                              postops=[args.act] if args.act else [], flags=capi.FLAG_STABLE_WEIGHTS) for w in weights]
+    for d in descs:
+        capi.check(capi.matmul(d, st))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.reps):
+        for d in descs:
+            capi.check(capi.matmul(d, st))
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.reps * len(descs))
+    print("bf16 M%d K%d N%d: %.2f us per call, %.0f TFLOP/s (stream order, not graph-replayed)" % (M, K, N, us, 2.0 * M * K * N / us / 1e6))
 
 
 def _gs(args):
@@ -178,11 +208,17 @@ def main():
     q.add_argument("--gs", type=int, default=128)
     q.add_argument("--copies", type=int, default=4)
     q.add_argument("--reps", type=int, default=20)
+    b = sub.add_parser("bf16")
+    b.add_argument("M", type=int); b.add_argument("K", type=int); b.add_argument("N", type=int)
+    b.add_argument("--copies", type=int, default=2)
+    b.add_argument("--reps", type=int, default=5)
+    b.add_argument("--act", default=None)
+    b.add_argument("--bias", action="store_true")
     e = sub.add_parser("moe")
     e.add_argument("config", choices=["c4", "c5"])
     e.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()
-    {"matmul": _matmul, "moe": _moe, "gs": _gs}[args.what](args)
+    {"matmul": _matmul, "moe": _moe, "gs": _gs, "bf16": _bf16}[args.what](args)
 
 
 if __name__ == "__main__":
