@@ -176,6 +176,42 @@ static void test_int8_sym_quant_per_group() {
   }
 }
 
+// bf16:bf16:bf16 matmul_direct with bias and GELU (the reference's non-quantised path): f32 accumulation, 1 bf16 ulp against a
+// double-precision sum (plus the f32 accumulation slack of a 320-term sum)
+static void test_bf16_matmul_direct() {
+  Rng r(14);
+  const int M = 90, K = 320, N = 104;
+  std::vector<uint16_t> A((size_t)M * K), W((size_t)K * N), C((size_t)M * N, 0);
+  std::vector<float> bias(N);
+  for (auto &v : A) v = f2bf(r.rn());
+  for (auto &v : W) v = f2bf(r.rn() * 0.06f);
+  for (auto &v : bias) v = r.rn();
+  matmul_params p;
+  p.dtypes.src = data_type_t::bf16; p.dtypes.wei = data_type_t::bf16; p.dtypes.dst = data_type_t::bf16; p.dtypes.bias = data_type_t::f32;
+  matmul_post_op po; po.po_type = post_op_type_t::gelu_tanh;
+  p.postop_.push_back(po);
+  matmul_batch_params_t bp;
+  status_t st = matmul_direct('r', false, false, M, N, K, 1.0f, A.data(), K, W.data(), N, bias.data(), 0.0f, C.data(), N, true, bp, p);
+  CHECK(st == status_t::success, "bf16 matmul_direct: %s", last_error());
+  int worst = 0;
+  for (int m = 0; m < M; ++m)
+    for (int n = 0; n < N; ++n) {
+      double acc = 0.0;
+      for (int k = 0; k < K; ++k) acc += (double)bf2f(A[(size_t)m * K + k]) * (double)bf2f(W[(size_t)k * N + n]);
+      const float x = (float)acc + bias[n];
+      const float c = 0.79788458347320556640625f;
+      const float y = 0.5f * x * (1.0f + std::tanh(c * x * (1.0f + 0.044715f * x * x)));
+      const uint16_t want = f2bf(y);
+      if (std::fabs(bf2f(C[(size_t)m * N + n]) - y) > 1e-4f) worst = std::max(worst, ulp_diff(C[(size_t)m * N + n], want));
+    }
+  CHECK(worst <= 1, "bf16 matmul_direct: %d bf16 ulp", worst);
+  // quantisation parameters are refused outside INT8 / W4A8 (lowoha_matmul_utils.cpp:227-233)
+  float one = 1.0f;
+  p.quant_params.src_scale.buff = &one; p.quant_params.src_scale.dt = data_type_t::f32; p.quant_params.src_scale.dims = {1};
+  st = matmul_direct('r', false, false, M, N, K, 1.0f, A.data(), K, W.data(), N, bias.data(), 0.0f, C.data(), N, true, bp, p);
+  CHECK(st == status_t::failure, "bf16 matmul_direct with a source scale must fail (got %d)", (int)st);
+}
+
 // INT8 with a quantised u8 / s8 output tensor: dst_scale and dst_zp close the epilogue chain
 // (backends/aocl/aocl_postop.cpp:1421-1448), clamp and nearbyint as operators/matmul/matmul_ref_kernel.cpp:155-192
 static void test_int8_requantised_dst() {
@@ -562,6 +598,7 @@ int main(int argc, char **argv) {
   RUN(test_int8_sym_quant_per_group());
   RUN(test_w4a8_bf16());
   RUN(test_int8_requantised_dst());
+  RUN(test_bf16_matmul_direct());
   RUN(test_reorder_and_prepack());
   RUN(test_fused_moe_vs_two_call(false, false, false));
   RUN(test_fused_moe_vs_two_call(true, true, false));

@@ -80,6 +80,7 @@ def test_matmul_lines_compute_what_the_oracle_computes(oracle):
              "37, 512, 256, 2, bf16:s8:bf16, true, f32, gelu_tanh, , , true, false, true, 1.0, 0.0, per-channel, , f32, 0, true, per-token",
              "64, 256, 128, 2, s8:s8:f32, false, f32, binary_add, , , true, false, true",
              "64, 256, 128:64, 2, bf16:s8:bf16, true, f32, gelu_tanh, , , true, false, true, 1.0, 0.0, per-channel, , f32, 0, true, per-token"]
+    lines.append("70, 256, 128:64, 2, bf16:bf16:bf16, true, f32, gelu_tanh")
     for line in lines:
         cfg, cap = B.parse_line(line), {}
         total, status = B.run_config(cfg, capture=cap)
@@ -87,6 +88,11 @@ def test_matmul_lines_compute_what_the_oracle_computes(oracle):
         src = _u16(cap["x"])
         for li, L in enumerate(cap["layers"]):
             w = L["w"].T if cfg["transB"] else L["w"]
+            if cfg["wdt"] == "bf16":
+                ref = oracle.matmul_bf16(src, np.ascontiguousarray(_u16(w)), "bf16", bias=L["bias"], postops=L["pos"])
+                src = _u16(L["out"])
+                assert_bf16_close(src, ref, 1, "%s (layer %d)" % (line, li), atol=1e-4)
+                continue
             if cfg["dyn"] or li > 0:
                 qa, sa = oracle.quant_per_token(src if src.dtype != np.float32 else src)
                 kw = dict(src_scale=sa)
@@ -109,7 +115,9 @@ def test_matmul_lines_compute_what_the_oracle_computes(oracle):
 def test_parse_grp_lines():
     c = B.parse_grp_line("8, 14:5:6:7:4:22:2:4, 4096, 28672, 200, bf16:bf16:bf16, true, 50, 2, 1, 4096")
     assert c["ops"] == 8 and c["M"] == [14, 5, 6, 7, 4, 22, 2, 4] and (c["topk"], c["act"], c["n_down"]) == (2, 1, 4096)
-    assert "weights bf16" in B.grp_unsupported_reason(c)
+    assert B.grp_unsupported_reason(c) is None            # the reference's shipped traces run as written
+    c["wdt"] = "f32"
+    assert "weights f32" in B.grp_unsupported_reason(c)
     c["wdt"] = "s8"
     assert B.grp_unsupported_reason(c) is None
     u = B.parse_grp_line("4, 32, 2880, 5760, 200, bf16:s8:bf16, true, 50, 4, 3, 2880, 1, 32")
@@ -125,7 +133,9 @@ def test_parse_grp_lines():
 @pytest.mark.gpu
 def test_grp_lines_run_on_the_gpu():
     for line in ("4, 10:0:7:3, 256, 512, 2, bf16:s8:bf16, true, 1, 2, 1, 256",
-                 "3, 8, 128, 256, 2, bf16:s8:bf16, true, 0, 0, 3, 128"):
+                 "3, 8, 128, 256, 2, bf16:s8:bf16, true, 0, 0, 3, 128",
+                 "4, 10:0:7:3, 256, 512, 2, bf16:bf16:bf16, true, 1, 2, 1, 256",
+                 "3, 8, 128, 256, 2, bf16:bf16:bf16, true, 0, 0, 3, 128"):
         total, status = B.run_grp_config(B.parse_grp_line(line))
         assert status == "success" and total > 0, (line, status)
 

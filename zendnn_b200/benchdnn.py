@@ -13,7 +13,8 @@ src_scale_granularity, src_group_size, src_scale_dt.  Lines starting with '#' an
 
 What runs: the INT8 path of matmul_direct (u8|s8 source with static per-tensor scale and zero point, or bf16|f32
 source with src_dynamic_quant and per-token or per-tensor scales; s8 weights with per-channel or per-tensor scales;
-bf16|f32|s32 destination).  Everything else (f32/bf16 weights, s4 weights, per-group scales, transposed source,
+bf16|f32|s32 destination) and the bf16 x bf16 path (bf16:bf16:bf16|f32, no quantisation).  Everything else (f32
+weights, s4 weights, per-group scales, transposed source,
 alpha/beta other than 1/0, batched lines) is reported as `unimplemented`, which is the status the library returns
 for it.  Multi-layer lines (n = a:b:c) run as a pipeline: layer i+1 consumes the bf16 output of layer i.
 `--cache_mode=warm` rotates over `--num_weight_buffers` weight copies (default: enough to exceed the L2 size), `hot`
@@ -23,11 +24,11 @@ for it.  Multi-layer lines (n = a:b:c) run as a pipeline: layer i+1 consumes the
 
 grp_matmul lines (benchdnn/doc/grp_matmul.md): num_ops, M (one value or a colon-separated list per expert), K, N, iters,
 src:wei:dst, is_weights_const, warmup [, moe_topk [, gated_act [, N_down [, use_internal_alloc [, total_experts]]]]].
-What runs: the full fused block (gated_act 1..3, N_down > 0) with s8 weights and bf16 source and destination, i.e.
-group_matmul_direct's dynamic-INT8 fused MoE: gate|up GEMM -> gated activation -> down GEMM, plus the weighted
-reduce when moe_topk > 0 (row pointers expert by expert, weights 1/topk, as the reference driver builds them).  The
-reference's shipped traces are bf16:bf16:bf16; `--wdt_as=s8` runs their shapes with s8 weights instead.  Other lines are
-reported `unimplemented`.
+What runs: the full fused block (gated_act 1..3, N_down > 0) with s8 or bf16 weights and bf16 source and destination, i.e.
+group_matmul_direct's fused MoE (dynamic INT8 with s8 weights, no quantisation with bf16 weights): gate|up GEMM ->
+gated activation -> down GEMM, plus the weighted reduce when moe_topk > 0 (row pointers expert by expert, weights
+1/topk, as the reference driver builds them).  The reference's shipped traces are bf16:bf16:bf16 and run as written;
+`--wdt_as=s8` runs their shapes with s8 weights instead.  Other lines are reported `unimplemented`.
 
   python -m zendnn_b200.benchdnn --op=reorder --input_file=reorder_inputs.txt
 
@@ -108,9 +109,15 @@ def parse_file(path):
 
 def unsupported_reason(cfg):
     """None when the line is inside the subset the library computes, else why not."""
-    if cfg["wdt"] != "s8":
-        return "weights %s (only s8)" % cfg["wdt"]
-    if cfg["dyn"]:
+    bf16 = cfg["wdt"] == "bf16" and cfg["sdt"] == "bf16" and not cfg["dyn"]
+    if cfg["wdt"] != "s8" and not bf16:
+        return "weights %s with source %s (s8 weights, or bf16 x bf16)" % (cfg["wdt"], cfg["sdt"])
+    if bf16:
+        if cfg["ddt"] not in ("bf16", "f32"):
+            return "destination %s" % cfg["ddt"]
+        if len(cfg["n"]) > 1 and cfg["ddt"] != "bf16":
+            return "pipeline lines need a bf16 destination between layers"
+    elif cfg["dyn"]:
         if cfg["sdt"] not in ("bf16", "f32"):
             return "dynamic quantisation takes a bf16 or f32 source"
         if cfg["sgran"] == "per-group":
@@ -129,7 +136,7 @@ def unsupported_reason(cfg):
     for p in cfg["post_ops"]:
         if p not in known:
             return "post-op %s" % p
-    if len(cfg["n"]) > 1 and cfg["ddt"] != "bf16" and not cfg["dyn"]:
+    if len(cfg["n"]) > 1 and cfg["ddt"] != "bf16" and not cfg["dyn"] and not bf16:
         return "pipeline lines need dynamic quantisation between layers"
     return None
 
@@ -164,6 +171,7 @@ def run_config(cfg, cache_mode="hot", num_weight_buffers=0, capture=None):
     g = torch.Generator(device=dev).manual_seed(0)
     M = cfg["m"]
     layers, k = [], cfg["k"]
+    wbf16 = cfg["wdt"] == "bf16"
     tdt = {"bf16": torch.bfloat16, "f32": torch.float32, "s32": torch.int32}
     for li, n in enumerate(cfg["n"]):
         last = li == len(cfg["n"]) - 1
@@ -171,7 +179,10 @@ def run_config(cfg, cache_mode="hot", num_weight_buffers=0, capture=None):
         if cache_mode in ("warm", "cold"):
             copies = num_weight_buffers if num_weight_buffers > 0 else max(2, -(-L2_BYTES // (k * n)) + 1)
         shape = (n, k) if cfg["transB"] else (k, n)
-        ws = [torch.randint(-127, 128, shape, generator=g, dtype=torch.int8, device=dev) for _ in range(copies)]
+        if wbf16:
+            ws = [(torch.randn(shape, generator=g, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        else:
+            ws = [torch.randint(-127, 128, shape, generator=g, dtype=torch.int8, device=dev) for _ in range(copies)]
         wn = n if cfg["wgran"] == "per-channel" else 1
         wscale = (torch.rand(wn, generator=g, device=dev) * 4e-4 + 1e-4)
         if cfg["wscale_dt"] == "bf16":
@@ -192,7 +203,7 @@ def run_config(cfg, cache_mode="hot", num_weight_buffers=0, capture=None):
         out = torch.empty(M, n, dtype=tdt[ddt], device=dev)
         layers.append(dict(k=k, n=n, ws=ws, wscale=wscale, bias=bias, pos=pos, out=out, ddt=ddt))
         k = n
-    if cfg["dyn"]:
+    if cfg["dyn"] or wbf16:
         x = torch.randn(M, cfg["k"], generator=g, device=dev)
         x = x.to(torch.bfloat16) if cfg["sdt"] == "bf16" else x
     else:
@@ -205,9 +216,11 @@ def run_config(cfg, cache_mode="hot", num_weight_buffers=0, capture=None):
         ds, src, src_dt = [], x, cfg["sdt"]
         for li, L in enumerate(layers):
             w = L["ws"][it % len(L["ws"])]
-            dyn = cfg["dyn"] or li > 0
+            dyn = (cfg["dyn"] or li > 0) and not wbf16
             kw = {}
-            if dyn:
+            if wbf16:
+                kw["wei_dt"] = capi.DT["bf16"]
+            elif dyn:
                 kw["src_scale"] = capi.quant(None, M if cfg["sgran"] == "per-token" or li > 0 else 1, capi.DT[cfg["sscale_dt"]])
             else:
                 kw["src_scale"] = sscale
@@ -215,7 +228,7 @@ def run_config(cfg, cache_mode="hot", num_weight_buffers=0, capture=None):
                     kw["src_zp"] = szp
             ds.append(capi.make_matmul(M, L["n"], L["k"], src, w, L["out"], src_dt=capi.DT[src_dt], dst_dt=capi.DT[L["ddt"]],
                                        transB=cfg["transB"], bias=L["bias"], weights_const=cfg["is_weights_const"],
-                                       dynamic_quant=dyn, wei_scale=L["wscale"], postops=L["pos"], **kw))
+                                       dynamic_quant=dyn, wei_scale=None if wbf16 else L["wscale"], postops=L["pos"], **kw))
             src, src_dt = L["out"], "bf16"
         return ds
 
@@ -284,8 +297,8 @@ def parse_grp_line(line):
 
 
 def grp_unsupported_reason(cfg):
-    if cfg["wdt"] != "s8":
-        return "weights %s (only s8; --wdt_as=s8 runs the shapes with s8 weights)" % cfg["wdt"]
+    if cfg["wdt"] not in ("s8", "bf16"):
+        return "weights %s (s8 or bf16)" % cfg["wdt"]
     if cfg["sdt"] != "bf16" or cfg["ddt"] != "bf16":
         return "source/destination other than bf16"
     if cfg["act"] not in (1, 2, 3) or cfg["n_down"] <= 0:
@@ -322,13 +335,18 @@ def run_grp_config(cfg):
     st = torch.cuda.current_stream().cuda_stream
     g = torch.Generator(device=dev).manual_seed(0)
     E, K, I, H = cfg["ops"], cfg["k"], cfg["n"] // 2, cfg["n_down"]
+    wbf16 = cfg["wdt"] == "bf16"
     keep, ex = [], (capi.MoeExpert * E)()
     total = sum(cfg["M"])
     ptrs = (C.c_void_p * max(1, total))()
     slot = 0
     for e, m in enumerate(cfg["M"]):
-        w13 = torch.randint(-127, 128, (K, 2 * I), generator=g, dtype=torch.int8, device=dev)
-        w2 = torch.randint(-127, 128, (I, H), generator=g, dtype=torch.int8, device=dev)
+        if wbf16:
+            w13 = (torch.randn(K, 2 * I, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            w2 = (torch.randn(I, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        else:
+            w13 = torch.randint(-127, 128, (K, 2 * I), generator=g, dtype=torch.int8, device=dev)
+            w2 = torch.randint(-127, 128, (I, H), generator=g, dtype=torch.int8, device=dev)
         s13 = torch.rand(2 * I, generator=g, device=dev) * 4e-4 + 1e-4
         s2 = torch.rand(H, generator=g, device=dev) * 4e-4 + 1e-4
         src = torch.randn(max(m, 1), K, generator=g, device=dev).to(torch.bfloat16)
@@ -336,6 +354,7 @@ def run_grp_config(cfg):
         keep.append((w13, w2, s13, s2, src, dst))
         x = ex[e]
         x.M, x.src, x.lda = m, src.data_ptr(), K
+        x.wei_dt = capi.DT["bf16"] if wbf16 else capi.DT["s8"]
         x.w13, x.ldb13, x.w13_scale = w13.data_ptr(), 2 * I, s13.data_ptr()
         x.w2, x.ldb2, x.w2_scale = w2.data_ptr(), H, s2.data_ptr()
         x.dst_down, x.ldc_down = dst.data_ptr(), H

@@ -1,7 +1,7 @@
 """Run one configured case of the library a few times on cuda:0 (for profilers and quick timing).
 
   python -m zendnn_b200.run_case matmul <auto|decode|tc> M K N [--copies C] [--reps R] [--act gelu_tanh] [--bias] [--dyn]
-  python -m zendnn_b200.run_case moe <c4|c5> [--reps R]
+  python -m zendnn_b200.run_case moe <c4|c5> [--reps R] [--wdt s8|bf16]
   python -m zendnn_b200.run_case gs <w4a8|s8> M K N --gs G [--copies C] [--reps R]
   python -m zendnn_b200.run_case bf16 M K N [--copies C] [--reps R] [--act gelu_tanh] [--bias]
 
@@ -145,6 +145,13 @@ def _moe(args):
     G = E + S
     keep, ex = [], (capi.MoeExpert * G)()
     for e in range(G):
+        if args.wdt == "bf16":
+            w13 = (torch.randn(H, 2 * I, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            w2 = (torch.randn(I, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            keep.append((w13, w2))
+            ex[e].wei_dt = capi.DT["bf16"]
+            ex[e].w13, ex[e].ldb13, ex[e].w2, ex[e].ldb2 = w13.data_ptr(), 2 * I, w2.data_ptr(), H
+            continue
         w13 = torch.randint(-127, 128, (H, 2 * I), generator=g, dtype=torch.int8, device=dev)
         w2 = torch.randint(-127, 128, (I, H), generator=g, dtype=torch.int8, device=dev)
         s13 = torch.rand(2 * I, generator=g, device=dev) * 4e-4 + 1e-4
@@ -217,6 +224,7 @@ def main():
     e = sub.add_parser("moe")
     e.add_argument("config", choices=["c4", "c5"])
     e.add_argument("--reps", type=int, default=3)
+    e.add_argument("--wdt", choices=["s8", "bf16"], default="s8", help="expert weights: s8 (dynamic INT8) or bf16 (no quantisation)")
     args = ap.parse_args()
     {"matmul": _matmul, "moe": _moe, "gs": _gs, "bf16": _bf16}[args.what](args)
 
