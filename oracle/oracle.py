@@ -193,6 +193,23 @@ def ref2_int8_ukernel(A, B, src_scale, wei_scale, bias=None, act="none"):
     return out if rc == 0 else None
 
 
+def ref2_bf16_ukernel(A, B, bias=None, act="none"):
+    """The reference's group bf16 micro-kernel (custom_kernel/ukernel/bf16_microkernel.cpp) over A bf16 [M,K] x B bf16 [K,N]
+    (bit patterns): f32 accumulation, + bias, optional gated activation, bf16 out ([M,N], or [M,N/2] gated).
+    None if unavailable (library not built, or no AVX512-BF16 on this host)."""
+    r = ref2_lib()
+    if r is None or not hasattr(r, "ref2_bf16_ukernel"):
+        return None
+    A = np.ascontiguousarray(A, dtype=np.uint16); B = np.ascontiguousarray(B, dtype=np.uint16)
+    M, K = A.shape
+    N = B.shape[1]
+    kind = {"none": 0, "swiglu_oai_mul": 1, "silu_and_mul": 2, "gelu_and_mul": 3}[act]
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    out = np.zeros((M, N if kind == 0 else N // 2), dtype=np.uint16)
+    rc = r.ref2_bf16_ukernel(_p(A), _p(B), M, N, K, _p(b), kind, _p(out))
+    return out if rc == 0 else None
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

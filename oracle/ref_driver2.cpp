@@ -12,12 +12,15 @@
 //   reorder/reorder_data_type/scalar_impl/scalar_granular_impl.cpp (static quantise / dequantise with granular scales)
 //   matmul/group_matmul/custom_kernel/ukernel/int8_microkernel.cpp (the DQ-INT8 tile micro-kernel of group_matmul_direct:
 //     VNNI GEMM, exact s32 compensation, x src scale, x weight scale, + bias, gated activation in registers)
+//   matmul/group_matmul/custom_kernel/ukernel/bf16_microkernel.cpp (the bf16 tile micro-kernel of group_matmul_direct:
+//     VDPBF16PS GEMM with f32 accumulators, + bias, gated activation in registers)
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
 #include <vector>
 
 #include "lowoha_operators/matmul/group_matmul/custom_kernel/ukernel/int8_microkernel.hpp"
+#include "lowoha_operators/matmul/group_matmul/custom_kernel/ukernel/bf16_microkernel.hpp"
 
 #include "lowoha_operators/matmul/group_matmul/group_matmul_direct.hpp"
 #include "lowoha_operators/reorder/lowoha_reorder_utils.hpp"
@@ -154,6 +157,40 @@ API int ref2_int8_ukernel(const int8_t *A, const int8_t *B, int M, int N, int K,
       void *full = act == 0 ? out + (size_t)m * N + ob * NR : nullptr;
       void *tight = act == 0 ? nullptr : out + (size_t)m * I + ob * (NR / 2);
       fn(reinterpret_cast<const uint8_t *>(A) + (size_t)m * K, K, slab, src_scale + m, nullptr, ws.data(), ScaleKind::kF32,
+         bias ? bs.data() : nullptr, bias ? BiasKind::fp32 : BiasKind::none, full, act == 0 ? N : 0, tight, act == 0 ? 0 : I, K);
+      m += MR;
+    }
+  }
+  free(slab);
+  return 0;
+}
+
+// The group bf16 micro-kernel over A bf16 [M,K] x B bf16 [K,N] (row-major, caller's column order: [gate | up] halves for
+// act 2 and 3, element-interleaved pairs for act 1), f32 bias [N] or null.  B is packed here as the kernel reads it:
+// 32-column slabs, K-pair-major, element (k, c) at ((k/2)*32 + c)*2 + k%2; the gated forms that take split halves get their
+// columns interleaved by the pack, as the reference's prepack does.  act: 0 none, 1 swiglu_oai_mul, 2 silu_and_mul,
+// 3 gelu_and_mul.  K % 2 == 0, N % 32 == 0.  out: bf16 bits, [M,N] for act 0, else [M,N/2].
+API int ref2_bf16_ukernel(const uint16_t *A, const uint16_t *B, int M, int N, int K, const float *bias, int act, uint16_t *out) {
+  using namespace zendnnl::lowoha::matmul::custom_kernel;
+  using zendnnl::common::bfloat16_t;
+  if (!avx512bf16_available() || K % 2 != 0 || N % 32 != 0 || M <= 0) return -1;
+  const int NR = 32, I = N / 2, kp = K / 2;
+  auto src_col = [&](int p) { return (act == 2 || act == 3) ? ((p & 1) ? I + p / 2 : p / 2) : p; };
+  uint16_t *slab = static_cast<uint16_t *>(aligned_alloc(64, ((size_t)kp * NR * 2 * 2 + 63) / 64 * 64));
+  std::vector<float> bs(NR);
+  for (int ob = 0; ob < N / NR; ++ob) {
+    for (int c = 0; c < NR; ++c) {
+      const int sc = src_col(ob * NR + c);
+      for (int k = 0; k < K; ++k) slab[((size_t)(k / 2) * NR + c) * 2 + (k % 2)] = B[(size_t)k * N + sc];
+      bs[c] = bias ? bias[sc] : 0.f;
+    }
+    for (int m = 0; m < M;) {
+      const int MR = M - m >= 8 ? 8 : M - m;
+      ukernel_fn_t fn = select_ukernel(MR, 2, static_cast<ActKind>(act), DstDt::kBf16);
+      if (!fn) { free(slab); return -2; }
+      void *full = act == 0 ? out + (size_t)m * N + ob * NR : nullptr;
+      void *tight = act == 0 ? nullptr : out + (size_t)m * I + ob * (NR / 2);
+      fn(reinterpret_cast<const bfloat16_t *>(A) + (size_t)m * K, K, reinterpret_cast<const bfloat16_t *>(slab),
          bias ? bs.data() : nullptr, bias ? BiasKind::fp32 : BiasKind::none, full, act == 0 ? N : 0, tight, act == 0 ? 0 : I, K);
       m += MR;
     }

@@ -54,6 +54,16 @@ def ukernel_inputs():
     return A, B, sa, sw, bias
 
 
+def ukernel_bf16_inputs():
+    """Inputs of the group bf16 micro-kernel cases: bf16 activations and weights (bit patterns), an f32 bias."""
+    rng = np.random.default_rng(80)
+    M, K, N = 21, 256, 128
+    A = O.f32_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    B = O.f32_to_bf16((rng.normal(size=(K, N)) * 0.06).astype(np.float32))
+    bias = rng.normal(size=N).astype(np.float32)
+    return A, B, bias
+
+
 PG_GROUPS = [2, 4, 8, 16]
 UK_ACTS = ["none", "silu_and_mul", "gelu_and_mul", "swiglu_oai_mul"]
 
@@ -101,6 +111,12 @@ def run(tag):
                 r = O.ref2_int8_ukernel(A, B, sa, sw, bias if hb else None, a)
                 assert r is not None, "the reference micro-kernel needs AVX-512 VNNI"
                 out["uk_%s_bias%d" % (a, hb)] = r
+        A, B, bias = ukernel_bf16_inputs()
+        for a in UK_ACTS:
+            for hb in (0, 1):
+                r = O.ref2_bf16_ukernel(A, B, bias if hb else None, a)
+                assert r is not None, "the reference bf16 micro-kernel needs AVX512-BF16"
+                out["ukbf_%s_bias%d" % (a, hb)] = r
     return out
 
 

@@ -18,6 +18,12 @@ def capi():
     return c
 
 
+@pytest.fixture(scope="module")
+def golden2():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref2_cases.npz"))
+
+
 def make(oracle, rng, M, K, N, transB=False, wstd=1.0):
     A = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
     W = oracle.f32_to_bf16((rng.standard_normal((N, K) if transB else (K, N)) * wstd).astype(np.float32))
@@ -59,6 +65,22 @@ def test_plain_gemm(capi, oracle, shape, dst):
         ref = oracle.matmul_bf16(A, W, "f32", transB=transB).astype(np.float64)
         got = run(capi, M, N, K, A, W, dst, weights_const=False, transB=transB)
         check(oracle, got, ref, abs_dot(oracle, A, W, transB), dst, "%s transB=%d" % (shape, transB))
+
+
+@pytest.mark.parametrize("has_bias", [0, 1])
+def test_against_reference_microkernel_outputs(capi, oracle, golden2, has_bias):
+    """The committed outputs of the reference's own bf16 micro-kernel (tests/golden, generated from the compiled reference
+    by tests/golden/make_golden_ref2.py): it sums in f32 in its own order, so at least 99 % of the elements are equal and none
+    is further than 2 bf16 ulp."""
+    from helpers import bf16_ulp_diff
+    rng = np.random.default_rng(80)             # the inputs of make_golden_ref2.py::ukernel_bf16_inputs
+    M, K, N = 21, 256, 128
+    A = oracle.f32_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    B = oracle.f32_to_bf16((rng.normal(size=(K, N)) * 0.06).astype(np.float32))
+    bias = rng.normal(size=N).astype(np.float32)
+    got = run(capi, M, N, K, A, B, "bf16", weights_const=False, bias=bias if has_bias else None)
+    d = bf16_ulp_diff(got, golden2["ukbf_none_bias%d" % has_bias])
+    assert d.max() <= 2 and (d == 0).mean() > 0.99, (int(d.max()), float((d == 0).mean()))
 
 
 @pytest.mark.parametrize("pair", [0, 1])

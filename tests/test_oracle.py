@@ -314,6 +314,35 @@ def test_live_reference_microkernel_if_present(oracle):
     assert np.abs(ref.astype(np.int32) - got.astype(np.int32)).max() <= 1
 
 
+def _oracle_bf16_tile(oracle, A, B, bias, act):
+    if act == "none":
+        return oracle.matmul_bf16(A, B, "bf16", bias=bias)
+    y = oracle.matmul_bf16(A, B, "f32", bias=bias)
+    I = B.shape[1] // 2
+    if act == "swiglu_oai_mul":
+        return oracle.gated_act_f32_pairs(y[:, 0::2], y[:, 1::2], act)
+    return oracle.gated_act_f32_pairs(y[:, :I], y[:, I:], act)
+
+
+@pytest.mark.parametrize("act", ["none", "silu_and_mul", "gelu_and_mul", "swiglu_oai_mul"])
+@pytest.mark.parametrize("has_bias", [0, 1])
+def test_bf16_tile_arithmetic_against_reference_microkernel(oracle, golden2, act, has_bias):
+    """Outputs of the reference's own bf16 micro-kernel (matmul/group_matmul/custom_kernel/ukernel/bf16_microkernel.cpp, driven
+    by oracle/ref_driver2.cpp) against the oracle's bf16 GEMM (exact products summed in double) and gated activation on the
+    f32 values.  The kernel sums in f32 in its own order and evaluates the activations with polynomial exponentials: at
+    least 99 % of the elements are equal, none is further than 2 bf16 ulp."""
+    from helpers import bf16_ulp_diff
+    rng = np.random.default_rng(80)             # the same seeded inputs as tests/golden/make_golden_ref2.py::ukernel_bf16_inputs
+    M, K, N = 21, 256, 128
+    A = oracle.f32_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    B = oracle.f32_to_bf16((rng.normal(size=(K, N)) * 0.06).astype(np.float32))
+    bias = rng.normal(size=N).astype(np.float32)
+    ref = golden2["ukbf_%s_bias%d" % (act, has_bias)]
+    got = _oracle_bf16_tile(oracle, A, B, bias if has_bias else None, act)
+    d = bf16_ulp_diff(got, ref)
+    assert d.max() <= 2 and (d == 0).mean() > 0.99, (int(d.max()), float((d == 0).mean()))
+
+
 def test_group_scaled_oracle_reduces_to_the_per_token_form(oracle):
     """With one group the per-group definition (operators/matmul/matmul_ref_kernel.cpp:961-1003) is the per-token
     epilogue order that the golden reference cases pin: (acc * src_scale[m]) * wei_scale[n] + bias."""
