@@ -732,6 +732,44 @@ def run_single_gpu_extras(torch, capi, dev, peaks, int8_peak):
     out["config1_M128_K4096_N4096_u8zp_bias_relu_bf16"] = gemm(128, 4096, 4096, False, "relu", copies=8)
     torch.cuda.synchronize()
     capi.lib.b200dnn_clear_caches()
+
+    # ---- the non-quantised form of the same entry points (bf16:bf16:bf16, the dtype of the reference's MoE traces)
+    bf = capi.DT["bf16"]
+    bf16_peak = float(peaks["bf16"])
+
+    def bf16_roof(tf):
+        return {"bound": "tensor", "achieved": round(tf, 1), "peak": round(bf16_peak, 1), "unit": "TFLOP/s", "frac": round(tf / bf16_peak, 4),
+                "peak_source": "bf16 GEMM burst rate, " + peaks["src"]}
+    M, K, N = 2048, 4096, 14336
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+    W = (torch.randn(K, N, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+    bias = torch.randn(N, generator=g).to(dev)
+    o = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    d = capi.make_matmul(M, N, K, A, W, o, src_dt=bf, wei_dt=bf, dst_dt=bf, bias=bias, postops=["gelu_tanh"])
+    ms = _time_events(torch, lambda: capi.check(capi.matmul(d, st)), 20)
+    tf = 2.0 * M * N * K / ms / 1e9
+    out["bf16_prefill_M2048_K4096_N14336_bias_gelu"] = {"us": round(ms * 1e3, 1), "tflops": round(tf, 1), "roofline": bf16_roof(tf)}
+    del A, W, o
+    cfg = MOE["c4"]
+    T, H, I, E, k = cfg["T"], cfg["H"], cfg["I"], cfg["E"], cfg["topk"]
+    gd = torch.Generator(device=dev).manual_seed(2000)
+    keep, ex = [], (capi.MoeExpert * E)()
+    for e in range(E):
+        w13 = (torch.randn(H, 2 * I, generator=gd, device=dev) * 0.02).to(torch.bfloat16)
+        w2 = (torch.randn(I, H, generator=gd, device=dev) * 0.02).to(torch.bfloat16)
+        keep.append((w13, w2))
+        ex[e].wei_dt = bf
+        ex[e].w13, ex[e].ldb13, ex[e].w2, ex[e].ldb2 = w13.data_ptr(), 2 * I, w2.data_ptr(), H
+    x, logits = moe_inputs(torch, dev, cfg, T, 11)
+    o = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    ms = _time_events(torch, lambda: capi.check(capi.lib.b200dnn_moe_layer(x.data_ptr(), H, logits.data_ptr(), T, E, 0, k, ex, H, I, H, 0,
+                                                                           capi.ACT["silu_and_mul"], o.data_ptr(), H, st)), 5)
+    tf = moe_ops(T * k, H, I) / ms / 1e9
+    out["moe_mixtral_like_bf16_weights"] = {"tokens_per_s": round(T / ms * 1e3), "ms_per_layer": round(ms, 4), "tflops": round(tf, 1),
+                                            "roofline": bf16_roof(tf), "note": "same layer with bf16 experts, no quantisation"}
+    del keep, ex, x, logits, o
+    torch.cuda.synchronize()
+    capi.lib.b200dnn_clear_caches()
     torch.cuda.empty_cache()
     return out
 

@@ -71,7 +71,7 @@ def test_plain_gemm(capi, oracle, shape, dst):
 def test_against_reference_microkernel_outputs(capi, oracle, golden2, has_bias):
     """The committed outputs of the reference's own bf16 micro-kernel (tests/golden, generated from the compiled reference
     by tests/golden/make_golden_ref2.py): it sums in f32 in its own order, so at least 99 % of the elements are equal and none
-    is further than 2 bf16 ulp."""
+    is further than 2 bf16 ulp, except where the sum nearly cancels (there: within 2^-16 * sum_k |a||b|)."""
     from helpers import bf16_ulp_diff
     rng = np.random.default_rng(80)             # the inputs of make_golden_ref2.py::ukernel_bf16_inputs
     M, K, N = 21, 256, 128
@@ -79,8 +79,11 @@ def test_against_reference_microkernel_outputs(capi, oracle, golden2, has_bias):
     B = oracle.f32_to_bf16((rng.normal(size=(K, N)) * 0.06).astype(np.float32))
     bias = rng.normal(size=N).astype(np.float32)
     got = run(capi, M, N, K, A, B, "bf16", weights_const=False, bias=bias if has_bias else None)
-    d = bf16_ulp_diff(got, golden2["ukbf_none_bias%d" % has_bias])
-    assert d.max() <= 2 and (d == 0).mean() > 0.99, (int(d.max()), float((d == 0).mean()))
+    ref = golden2["ukbf_none_bias%d" % has_bias]
+    d = bf16_ulp_diff(got, ref)
+    # a result that nearly cancels carries both kernels' f32 accumulation errors: those elements are held to the stated bound
+    near = np.abs(oracle.bf16_to_f32(got).astype(np.float64) - oracle.bf16_to_f32(ref)) <= 2.0 ** -16 * abs_dot(oracle, A, B, False)
+    assert ((d <= 2) | near).all() and (d == 0).mean() > 0.99, (int(d.max()), float((d == 0).mean()))
 
 
 @pytest.mark.parametrize("pair", [0, 1])
