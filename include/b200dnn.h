@@ -41,7 +41,7 @@ extern "C" {
 #define B200DNN_FAILURE 0
 #define B200DNN_UNIMPLEMENTED (-1)
 
-enum { B200DNN_F32 = 1, B200DNN_BF16 = 3, B200DNN_S32 = 4, B200DNN_S8 = 7, B200DNN_S4 = 8, B200DNN_U8 = 11 };
+enum { B200DNN_F32 = 1, B200DNN_BF16 = 3, B200DNN_S32 = 4, B200DNN_S8 = 7, B200DNN_S4 = 8, B200DNN_U8 = 11, B200DNN_U4 = 12 };
 enum { B200DNN_MAX_POSTOPS = 8 };
 /* b200dnn_matmul_t::flags.  STABLE_WEIGHTS: the (prepacked or cached) weight was written before
  * any work still pending on the stream, so the decode kernel may start streaming it while the
@@ -103,6 +103,10 @@ typedef struct b200dnn_matmul_t {
    * optional, per-tensor s32.  Ignored for float and s32 destinations. */
   b200dnn_quant_t dst_scale;
   b200dnn_quant_t dst_zp;
+  /* weight zero points, read for u4 weights only (weight-only quantisation: bf16 source, s4 | u4 weights, no dynamic_quant;
+   * lowoha_matmul_utils.cpp:319-331): s8 or bf16, count 1, N or G*N like wei_scale.  w = bf16((q - zp) * scale) with an s8
+   * zero point, bf16((q - 8) * scale + zp) with a bf16 one (operators/matmul/matmul_ref_kernel.cpp:466-474). */
+  b200dnn_quant_t wei_zp;
 } b200dnn_matmul_t;
 
 B200DNN_API const char *b200dnn_last_error(void);

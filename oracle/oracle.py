@@ -405,6 +405,49 @@ def unpack_s4(packed, K, N, transB=False, ldb=None):
     return np.ascontiguousarray(v.T) if transB else v
 
 
+def pack_u4(W, transB=False, ldb=None):
+    """Unsigned 4-bit weights, same placement as pack_s4; W uint8 [K,N] with values in [0,15]."""
+    W = np.asarray(W, dtype=np.uint8)
+    assert W.max() <= 15
+    return pack_s4((W.astype(np.int16) - 16 * (W > 7)).astype(np.int8), transB, ldb)
+
+
+def woq_dequant(packed, K, N, wei_dt, scale, zp=None, transB=False, ldb=None):
+    """Weight-only quantisation, the reference's scalar definition (operators/matmul/matmul_ref_kernel.cpp:359-489): every
+    4-bit weight becomes a bf16 value; s4, or u4 with an integer (s8) zero point: w = bf16((q - zp) * scale) (zp = 0 for s4);
+    u4 with a bf16 zero point (uint16 bits): w = bf16((q - 8) * scale + zp).  scale (f32, or bf16 bits) and zp have 1, N or
+    G*N elements ({G,N}: group g = k // (K/G)).  Returns bf16 bits [K,N]."""
+    q = unpack_s4(packed, K, N, transB, ldb).astype(np.int32)
+    if wei_dt == "u4":
+        q = q & 0xF
+
+    def expand(v):
+        v = np.asarray(v)
+        v = bf16_to_f32(v) if v.dtype == np.uint16 else v.astype(np.float32)
+        v = v.reshape(-1)
+        if v.size == 1:
+            return np.full((K, N), v[0], dtype=np.float32)
+        if v.size == N:
+            return np.broadcast_to(v[None, :], (K, N)).astype(np.float32)
+        G = v.size // N
+        return np.repeat(v.reshape(G, N), K // G, axis=0).astype(np.float32)
+    s = expand(scale)
+    qf = q.astype(np.float32)
+    if wei_dt == "u4" and zp is not None and np.asarray(zp).dtype == np.uint16:
+        w = (qf - np.float32(8)) * s + expand(zp)
+    elif wei_dt == "u4":
+        w = (qf - expand(np.asarray(zp).astype(np.float32))) * s
+    else:
+        w = qf * s
+    return f32_to_bf16(w.astype(np.float32))
+
+
+def matmul_woq(A, packed, K, N, wei_dt, scale, zp=None, dst_dt="bf16", transB=False, ldb=None, bias=None, postops=()):
+    """matmul_direct with bf16 activations and s4 | u4 weights, no quantisation of the activations: the weights are
+    dequantised to bf16 (woq_dequant), then the bf16 x bf16 product."""
+    return matmul_bf16(A, woq_dequant(packed, K, N, wei_dt, scale, zp, transB, ldb), dst_dt, bias=bias, postops=postops)
+
+
 def quant_per_token_asym(x):
     """Asymmetric per-token dynamic quantisation: x [M,K] f32 or bf16-bits -> (u8 [M,K], f32 scales [M], s32 zero points [M])."""
     x = np.ascontiguousarray(x)

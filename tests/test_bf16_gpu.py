@@ -234,3 +234,59 @@ def test_moe_layer_bf16_end_to_end(capi, oracle, T, H, I, E, k, S):
     assert np.abs(oracle.bf16_to_f32(out)).sum() > 1e-3
     _close(oracle, out, out_ref, "moe layer")
     capi.lib.b200dnn_clear_caches()
+
+
+# ---------------------------------------------------------------------------------- weight-only quantisation (s4 | u4)
+@pytest.mark.parametrize("wei_dt,zp_kind", [("s4", None), ("u4", "s8"), ("u4", "bf16")])
+@pytest.mark.parametrize("gran", ["tensor", "channel", "group"])
+def test_weight_only_quantisation(capi, oracle, wei_dt, zp_kind, gran):
+    """bf16 activations x packed 4-bit weights, no dynamic quantisation (TestMatmul WOQ cases of the reference,
+    zendnnl/gtests/test_matmul.cpp:137 ff.): per-tensor, per-channel and per-group ({G,N}) scales in f32 or bf16 storage,
+    u4 with an s8 or a bf16 zero point.  Against the reference's scalar definition: dequantise to bf16, then bf16 x bf16."""
+    from helpers import assert_bf16_close
+    rng = np.random.default_rng(sum(map(ord, wei_dt + str(zp_kind) + gran)))
+    for M, K, N, gs, transB in [(40, 256, 136, 64, False), (200, 512, 264, 128, True)]:
+        G = K // gs
+        n_s = {"tensor": 1, "channel": N, "group": G * N}[gran]
+        A = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+        if wei_dt == "s4":
+            packed = oracle.pack_s4(rng.integers(-8, 8, (K, N), dtype=np.int8), transB)
+        else:
+            packed = oracle.pack_u4(rng.integers(0, 16, (K, N), dtype=np.uint8), transB)
+        scale = rng.uniform(0.005, 0.02, n_s).astype(np.float32)
+        if transB:
+            scale = oracle.f32_to_bf16(scale)            # scales in bf16 storage
+        zp = None
+        if zp_kind == "s8":
+            zp = rng.integers(5, 11, n_s, dtype=np.int8)
+        elif zp_kind == "bf16":
+            zp = oracle.f32_to_bf16(rng.uniform(-0.02, 0.02, n_s).astype(np.float32))
+        bias = rng.standard_normal(N).astype(np.float32)
+        ref = oracle.matmul_woq(A, packed, K, N, wei_dt, scale, zp, "bf16", transB=transB, bias=bias, postops=["gelu_tanh"])
+        out = np.zeros((M, N), dtype=np.uint16)
+        d = capi.make_matmul(M, N, K, A, packed, out, src_dt=capi.DT["bf16"], wei_dt=capi.DT[wei_dt], dst_dt=capi.DT["bf16"],
+                             transB=transB, ldb=K if transB else N, weights_const=True, bias=bias, postops=["gelu_tanh"],
+                             wei_scale=capi.quant(scale, count=n_s), wei_zp=None if zp is None else capi.quant(zp, count=n_s))
+        for _ in range(2):                      # the second call takes the cached pack
+            out[:] = 0
+            assert capi.matmul(d) == capi.SUCCESS, capi.last_error()
+            assert_bf16_close(out, ref, 1, "%s %s %s %s" % (wei_dt, zp_kind, gran, (M, K, N)), atol=2e-4)
+    capi.lib.b200dnn_clear_caches()
+
+
+def test_weight_only_quantisation_contract(capi, oracle):
+    M, K, N = 8, 64, 32
+    A = np.zeros((M, K), dtype=np.uint16); W4 = np.zeros(K * N // 2, dtype=np.uint8); out = np.zeros((M, N), dtype=np.uint16)
+    bf, sc = capi.DT["bf16"], np.ones(N, dtype=np.float32)
+
+    def mk(**kw):
+        args = dict(src_dt=bf, wei_dt=capi.DT["s4"], dst_dt=bf, weights_const=True, wei_scale=sc)
+        args.update(kw)
+        return capi.make_matmul(M, N, K, A, W4, out, **args)
+    assert capi.matmul(mk()) == capi.SUCCESS, capi.last_error()
+    assert capi.matmul(mk(weights_const=False)) == capi.FAILURE and "constant weights" in capi.last_error()
+    assert capi.matmul(mk(wei_scale=None)) == capi.FAILURE
+    assert capi.matmul(mk(wei_dt=capi.DT["u4"])) == capi.FAILURE and "mandatory" in capi.last_error()
+    assert capi.matmul(mk(wei_dt=capi.DT["u4"], wei_zp=np.zeros(N, dtype=np.float32))) == capi.FAILURE      # zero point must be s8 or bf16
+    assert capi.matmul(mk(wei_scale=capi.quant(np.ones(3 * N, dtype=np.float32), count=3 * N))) == capi.FAILURE   # K % G != 0
+    capi.lib.b200dnn_clear_caches()

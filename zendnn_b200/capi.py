@@ -40,7 +40,7 @@ class MatmulDesc(C.Structure):
                 ("src_scale", Quant), ("wei_scale", Quant), ("src_zp", Quant),
                 ("postops", PostOp * MAX_POSTOPS),
                 ("force_kernel", C.c_int32), ("flags", C.c_int32),
-                ("dst_scale", Quant), ("dst_zp", Quant)]
+                ("dst_scale", Quant), ("dst_zp", Quant), ("wei_zp", Quant)]
 
 FLAG_STABLE_WEIGHTS = 1
 
@@ -183,7 +183,7 @@ def quant(buf, count=None, dt=None):
 def make_matmul(M, N, K, src, weight, dst, *, src_dt, dst_dt, lda=None, ldb=None, ldc=None, transB=False,
                 bias=None, bias_dt=None, wei_format="n", weights_const=True, dynamic_quant=False,
                 src_scale=None, wei_scale=None, src_zp=None, postops=(), force_kernel=0, flags=0, wei_dt=None,
-                dst_scale=None, dst_zp=None):
+                dst_scale=None, dst_zp=None, wei_zp=None):
     d = MatmulDesc()
     d.M, d.N, d.K, d.transB = M, N, K, int(transB)
     d.src_dt, d.wei_dt, d.dst_dt = src_dt, (DT["s8"] if wei_dt is None else wei_dt), dst_dt
@@ -226,6 +226,8 @@ def make_matmul(M, N, K, src, weight, dst, *, src_dt, dst_dt, lda=None, ldb=None
         d.dst_scale = dst_scale if isinstance(dst_scale, Quant) else quant(dst_scale)
     if dst_zp is not None:
         d.dst_zp = dst_zp if isinstance(dst_zp, Quant) else quant(dst_zp)
+    if wei_zp is not None:
+        d.wei_zp = wei_zp if isinstance(wei_zp, Quant) else quant(wei_zp)
     return d
 
 

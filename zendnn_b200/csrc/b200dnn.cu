@@ -616,6 +616,7 @@ int32_t fill_epi(const b200dnn_matmul_t *d, EpiParams *e) {
 
 #include "gs_api.cuh"
 #include "bf16_api.cuh"
+#include "woq_api.cuh"
 
 // =========================================================================================== C ABI
 extern "C" {
@@ -947,6 +948,7 @@ int32_t b200dnn_moe_route(const float *logits, int32_t T, int32_t E, int32_t top
 int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   B2_CHECK(d, B200DNN_FAILURE, "null descriptor");
   B2_ENTER(stream);
+  if (is_woq_matmul(d)) return matmul_woq(d, st);               // bf16 source x s4|u4 weights, no dynamic quantisation
   if (is_group_scaled(d)) return matmul_group_scaled(d, st);   // per-group scales and W4A8: own validation and kernel
   if (is_bf16_matmul(d)) return matmul_bf16(d, st);             // bf16 x bf16: own validation, the kernel's bf16 form
   Runtime &R = rt();
@@ -1113,6 +1115,8 @@ int32_t b200dnn_clear_caches(void) {
       std::lock_guard<std::mutex> lk(D->cache_mu);
       for (auto &kv : D->wcache) { if (kv.second.owned) cudaFree(kv.second.owned); if (kv.second.ready) cudaEventDestroy(kv.second.ready); }
       D->wcache.clear();
+      for (auto &kv : D->woq_cache) { if (kv.second.owned) cudaFree(kv.second.owned); if (kv.second.ready) cudaEventDestroy(kv.second.ready); }
+      D->woq_cache.clear();
       for (auto &kv : D->host_packed) { if (kv.second.owned) cudaFree(kv.second.owned); if (kv.second.ready) cudaEventDestroy(kv.second.ready); }
       D->host_packed.clear();
       D->packed_registry.clear();

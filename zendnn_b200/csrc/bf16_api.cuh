@@ -88,12 +88,11 @@ int32_t validate_bf16_matmul(const b200dnn_matmul_t *d) {
   return B200DNN_SUCCESS;
 }
 
-int32_t matmul_bf16(const b200dnn_matmul_t *d, cudaStream_t st) {
+// the GEMM over a weight that already sits in the tile layout as bf16 (a packed bf16 weight, or 4-bit weights dequantised
+// at pack time)
+int32_t matmul_bf16_packed(const b200dnn_matmul_t *d, const PackedWeight &pw, cudaStream_t st) {
   Runtime &R = rt();
   const int M = d->M, N = d->N, K = d->K;
-  B2_TRY(validate_bf16_matmul(d));
-  PackedWeight pw;
-  B2_TRY(resolve_bf16_weight(d->weight, K, N, d->ldb, d->transB, 0, d->weights_const, st, &pw));
   EpiParams epi;
   fill_epi(d, &epi);
   const void *src_dev = nullptr;
@@ -134,6 +133,13 @@ int32_t matmul_bf16(const b200dnn_matmul_t *d, cudaStream_t st) {
   ta.n_groups = 1; ta.m_tiles_plain = (M + tile_rows - 1) / tile_rows; ta.shared_dst = 1;
   B2_TRY(launch_tc(A, lda * 2, false, M, N, 2 * K, pw, ta, epi, ta.m_tiles_plain, st));
   return finish_out({&o_dst}, st);
+}
+
+int32_t matmul_bf16(const b200dnn_matmul_t *d, cudaStream_t st) {
+  B2_TRY(validate_bf16_matmul(d));
+  PackedWeight pw;
+  B2_TRY(resolve_bf16_weight(d->weight, d->K, d->N, d->ldb, d->transB, 0, d->weights_const, st, &pw));
+  return matmul_bf16_packed(d, pw, st);
 }
 
 }  // namespace

@@ -109,7 +109,9 @@ status_t flatten(const char layout, const bool transA, const bool transB, const 
   const bool int_dst = p.dtypes.dst == data_type_t::s8 || p.dtypes.dst == data_type_t::u8;
   if (!int_dst && (p.quant_params.dst_scale.buff || p.quant_params.dst_zp.buff))
     return shim_fail(status_t::unimplemented, "a destination scale or zero point is implemented for s8/u8 destinations only");
-  if (p.quant_params.wei_zp.buff) return shim_fail(status_t::unimplemented, "weight zero-points are not implemented");
+  const bool woq_u4 = p.dtypes.wei == data_type_t::u4 && p.dtypes.src == data_type_t::bf16 && !p.dynamic_quant;
+  if (p.quant_params.wei_zp.buff && !woq_u4)
+    return shim_fail(status_t::unimplemented, "weight zero-points are implemented for u4 weight-only quantisation");
   if (p.postop_.size() > B200DNN_MAX_POSTOPS) return shim_fail(status_t::failure, "too many post-ops");
   // W4A8 (s4 weights, bf16 source quantised by the library): the reference wants s8 compute and 2-D scale dims
   // (lowoha_matmul_utils.cpp:101-145); the remaining rules are checked behind the C ABI
@@ -131,6 +133,7 @@ status_t flatten(const char layout, const bool transA, const bool transB, const 
   d->wei_scale = flat_quant(p.quant_params.wei_scale);
   d->src_zp = flat_quant(p.quant_params.src_zp);
   if (!p.quant_params.src_zp.buff) d->src_zp.count = 0;
+  if (woq_u4) d->wei_zp = flat_quant(p.quant_params.wei_zp);
   if (int_dst) {
     d->dst_scale = flat_quant(p.quant_params.dst_scale);
     d->dst_zp = flat_quant(p.quant_params.dst_zp);

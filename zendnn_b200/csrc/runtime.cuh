@@ -138,6 +138,8 @@ struct DeviceShared {
   PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
   std::mutex cache_mu;
   std::map<std::tuple<const void *, int64_t, int64_t, int64_t, int, int>, PackedWeight> wcache;
+  // 4-bit weights dequantised to bf16 at pack time: the scale and zero-point buffers are part of the identity
+  std::map<std::tuple<const void *, const void *, const void *, int64_t, int64_t, int64_t, int, int>, PackedWeight> woq_cache;
   std::map<const void *, PackedWeight> packed_registry;   // buffers written by b200dnn_prepack (device address)
   std::map<const void *, PackedWeight> host_packed;       // host-resident prepacked buffers uploaded once
   std::mutex ctx_mu;
