@@ -375,6 +375,28 @@ B200DNN_API int32_t b200dnn_clear_caches(void);
  * synchronous). */
 B200DNN_API int32_t b200dnn_stream_status(void *stream);
 
+/* ---- normalization_direct (lowoha_operators/normalization/lowoha_normalization.hpp:98-107, norm_params in
+ * lowoha_normalization_common.hpp:96-153): the operators on either side of the quantised GEMMs in a decoder layer.
+ * The input is a [batch, norm_size] matrix (BatchNorm: [batch, num_channels, norm_size]); f32 and bf16 buffers (f16:
+ * unimplemented); every pointer may be host or device memory.  norm_type uses the reference's values. ---- */
+enum { B200DNN_NORM_LAYER = 0, B200DNN_NORM_BATCH = 1, B200DNN_NORM_RMS = 2, B200DNN_NORM_FUSED_ADD_RMS = 3 };
+typedef struct b200dnn_norm_t {
+  int32_t norm_type;
+  int32_t use_scale, use_shift;   /* gamma / beta applied (beta is ignored by the two RMS forms) */
+  float epsilon;
+  int64_t batch, norm_size, num_channels;
+  int32_t src_dt, dst_dt, gamma_dt, beta_dt;
+  const void *input;
+  void *output;                   /* may be NULL when only the quantised form is wanted */
+  const void *gamma, *beta;
+  const float *running_mean, *running_var;   /* BatchNorm */
+  void *residual;                 /* fused-add RMSNorm: updated in place to residual + input (rounded to src_dt) */
+  /* No counterpart in the reference: the normalised row, rounded to dst_dt, also leaves as per-token symmetric s8 with
+   * one f32 scale per row (the arithmetic of b200dnn_quant_per_token), in the same pass.  Both NULL: off. */
+  void *quant_dst; int64_t quant_ld; float *quant_scale;
+} b200dnn_norm_t;
+B200DNN_API int32_t b200dnn_normalization(const b200dnn_norm_t *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -138,6 +138,31 @@ ZENDNNL_B200_API status_t group_dynamic_quant(const std::vector<const void *> &s
                                               const group_dynamic_quant_params_t &params);
 }  // namespace reorder
 
+// ------------------------------------------------------------------------------------------ normalization
+// Mirrors lowoha_operators/normalization/lowoha_normalization_common.hpp:63-153 (enum values, field order, defaults) and
+// lowoha_normalization.hpp:98-107.
+namespace normalization {
+using zendnnl::memory::data_type_t;
+using zendnnl::memory::status_t;
+
+enum class norm_type_t : int { NONE = -1, LAYER_NORM = 0, BATCH_NORM = 1, RMS_NORM = 2, FUSED_ADD_RMS_NORM = 3 };
+enum class norm_algo_t : int { none = -1, dynamic_dispatch = 0, reference = 1 };
+
+struct norm_params {
+  norm_type_t norm_type = norm_type_t::NONE;
+  uint64_t batch = 0, norm_size = 0, num_channels = 0;
+  float epsilon = 1e-5f;
+  bool use_scale = false, use_shift = false;
+  data_type_t src_dt = data_type_t::none, dst_dt = data_type_t::none, gamma_dt = data_type_t::f32, beta_dt = data_type_t::f32;
+  norm_algo_t algorithm = norm_algo_t::none;
+  int32_t num_threads = 0;
+  data_type_t accum_type = data_type_t::f32;
+};
+
+status_t normalization_direct(const void *input, void *output, const void *gamma, const void *beta, const void *running_mean,
+                              const void *running_var, void *residual, norm_params &params);
+}  // namespace normalization
+
 // ------------------------------------------------------------------------------------------ matmul
 namespace matmul {
 using namespace zendnnl::memory;

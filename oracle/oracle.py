@@ -643,6 +643,48 @@ def fused_moe_bf16(x_bf16, ids, weights, w13, w2, act="silu_and_mul", b13=None, 
     return out, slot_out, slot_z
 
 
+NORM = dict(layer_norm=0, batch_norm=1, rms_norm=2, fused_add_rms_norm=3)
+
+
+def _norm_call(fn, kind, x, gamma, beta, residual, running_mean, running_var, eps, dst_dt, channels):
+    x = np.ascontiguousarray(x)
+    if kind == "batch_norm":
+        batch, n = x.shape[0], int(np.prod(x.shape[2:], dtype=np.int64))
+    else:
+        batch, n = int(np.prod(x.shape[:-1], dtype=np.int64)), x.shape[-1]
+    out = np.empty(x.shape, dtype={"bf16": np.uint16, "f32": np.float32}[dst_dt])
+    g = None if gamma is None else np.ascontiguousarray(gamma)
+    bt = None if beta is None else np.ascontiguousarray(beta)
+    rm = None if running_mean is None else np.ascontiguousarray(running_mean, dtype=np.float32)
+    rv = None if running_var is None else np.ascontiguousarray(running_var, dtype=np.float32)
+    res = None if residual is None else np.array(residual, copy=True, order="C")
+    rc = fn(NORM[kind], _p(x), _p(out), _p(g), _p(bt), _p(rm), _p(rv), _p(res), C.c_int64(batch), C.c_int64(n), C.c_int64(channels),
+            C.c_float(eps), int(g is not None), int(bt is not None), _dt_of(x), DT[dst_dt], DT["f32"] if g is None else _dt_of(g),
+            DT["f32"] if bt is None else _dt_of(bt))
+    assert rc == 0, rc
+    return (out, res) if kind == "fused_add_rms_norm" else out
+
+
+def normalization(kind, x, gamma=None, beta=None, residual=None, running_mean=None, running_var=None, eps=1e-5, dst_dt=None):
+    """normalization_direct as the reference's scalar kernel defines it (kernel/reference_kernel.cpp, f32 accumulation):
+    kind in NORM; x f32 or bf16 bits, normalised over the last axis (batch_norm: x is [N, C, ...] with per-channel running
+    statistics).  fused_add_rms_norm returns (output, updated residual)."""
+    dst_dt = dst_dt or ("bf16" if np.asarray(x).dtype == np.uint16 else "f32")
+    ch = np.asarray(x).shape[1] if kind == "batch_norm" else 0
+    return _norm_call(lib().orc_normalization, kind, x, gamma, beta, residual, running_mean, running_var, eps, dst_dt, ch)
+
+
+def ref2_normalization(kind, x, gamma=None, beta=None, residual=None, running_mean=None, running_var=None, eps=1e-5, dst_dt=None):
+    """The reference's own scalar normalization kernel (normalization_reference_wrapper, compiled into libzendnn_ref2.so).
+    None if unavailable."""
+    r = ref2_lib()
+    if r is None or not hasattr(r, "ref2_normalization"):
+        return None
+    dst_dt = dst_dt or ("bf16" if np.asarray(x).dtype == np.uint16 else "f32")
+    ch = np.asarray(x).shape[1] if kind == "batch_norm" else 0
+    return _norm_call(r.ref2_normalization, kind, x, gamma, beta, residual, running_mean, running_var, eps, dst_dt, ch)
+
+
 def ref_int8_matmul(A_u8, B_s8, src_zp, src_scale, wei_scale, bias=None, fused_op=0, dst_dt="bf16"):
     """Runs the compiled reference tile kernel (per-tensor src scale/zp).  None if unavailable."""
     r = ref_lib()

@@ -12,6 +12,7 @@
 //   reorder/reorder_data_type/scalar_impl/scalar_granular_impl.cpp (static quantise / dequantise with granular scales)
 //   matmul/group_matmul/custom_kernel/ukernel/int8_microkernel.cpp (the DQ-INT8 tile micro-kernel of group_matmul_direct:
 //     VNNI GEMM, exact s32 compensation, x src scale, x weight scale, + bias, gated activation in registers)
+//   normalization/kernel/reference_kernel.cpp (the scalar LayerNorm / BatchNorm / RMSNorm / fused-add RMSNorm)
 //   matmul/group_matmul/custom_kernel/ukernel/bf16_microkernel.cpp (the bf16 tile micro-kernel of group_matmul_direct:
 //     VDPBF16PS GEMM with f32 accumulators, + bias, gated activation in registers)
 #include <cstdint>
@@ -22,6 +23,7 @@
 #include "lowoha_operators/matmul/group_matmul/custom_kernel/ukernel/int8_microkernel.hpp"
 #include "lowoha_operators/matmul/group_matmul/custom_kernel/ukernel/bf16_microkernel.hpp"
 
+#include "lowoha_operators/normalization/kernel/reference_kernel.hpp"
 #include "lowoha_operators/matmul/group_matmul/group_matmul_direct.hpp"
 #include "lowoha_operators/reorder/lowoha_reorder_utils.hpp"
 #include "lowoha_operators/reorder/reorder_data_type/scalar_impl/scalar_kernels.hpp"
@@ -197,4 +199,21 @@ API int ref2_bf16_ukernel(const uint16_t *A, const uint16_t *B, int M, int N, in
   }
   free(slab);
   return 0;
+}
+
+// The reference's scalar normalization kernel.  Same argument list as the oracle's orc_normalization; dtype codes are
+// data_type_t values.  type: 0 layer, 1 batch, 2 rms, 3 fused-add rms.
+API int ref2_normalization(int type, const void *x, void *y, const void *gamma, const void *beta, const float *run_mean,
+                           const float *run_var, void *residual, int64_t batch, int64_t n, int64_t channels, float eps,
+                           int use_scale, int use_shift, int src_dt, int dst_dt, int gamma_dt, int beta_dt) {
+  using namespace zendnnl::lowoha::normalization;
+  using zendnnl::common::data_type_t;
+  norm_params p;
+  p.norm_type = static_cast<norm_type_t>(type);
+  p.batch = (uint64_t)batch; p.norm_size = (uint64_t)n; p.num_channels = (uint64_t)channels;
+  p.epsilon = eps; p.use_scale = use_scale != 0; p.use_shift = use_shift != 0;
+  p.src_dt = static_cast<data_type_t>(src_dt); p.dst_dt = static_cast<data_type_t>(dst_dt);
+  p.gamma_dt = static_cast<data_type_t>(gamma_dt); p.beta_dt = static_cast<data_type_t>(beta_dt);
+  p.num_threads = 1;
+  return normalization_reference_wrapper(x, y, gamma, beta, run_mean, run_var, residual, p) == zendnnl::error_handling::status_t::success ? 0 : -1;
 }

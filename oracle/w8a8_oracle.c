@@ -592,3 +592,63 @@ ORC_API void orc_router_topk(const float *logits, int T, int E, int k, int renor
     free(p);
   }
 }
+
+/* ======================================================================================
+ * normalization_direct, the scalar definition (lowoha_operators/normalization/kernel/reference_kernel.cpp, f32
+ * accumulation branch): LayerNorm :147-158,164,202-210 (mean, then the sum of squared deviations, both sequential in
+ * f32), BatchNorm :240-262, RMSNorm :383-388,417-421, fused-add RMSNorm :449-462,488-492 (the residual is stored rounded
+ * to the source type, the sum of squares uses the unrounded sums, the output the stored residual).
+ * type: 0 layer, 1 batch, 2 rms, 3 fused-add rms.  BatchNorm input is [batch, channels, n].
+ * ====================================================================================== */
+static inline void store_as(void *p, int dt, int64_t i, float v) {
+  if (dt == DT_BF16) ((uint16_t *)p)[i] = f32_to_bf16(v);
+  else ((float *)p)[i] = v;
+}
+ORC_API int orc_normalization(int type, const void *x, void *y, const void *gamma, const void *beta, const float *run_mean,
+                              const float *run_var, void *residual, int64_t batch, int64_t n, int64_t channels, float eps,
+                              int use_scale, int use_shift, int src_dt, int dst_dt, int gamma_dt, int beta_dt) {
+  if (type == 1) {
+    for (int64_t b = 0; b < batch; ++b)
+      for (int64_t c = 0; c < channels; ++c) {
+        const int64_t off = (b * channels + c) * n;
+        const float inv_std = 1.0f / sqrtf(run_var[c] + eps), m = run_mean[c];
+        const float g = use_scale ? load_as_f32(gamma, gamma_dt, c) : 0.0f, bt = use_shift ? load_as_f32(beta, beta_dt, c) : 0.0f;
+        for (int64_t s = 0; s < n; ++s) {
+          float v = (load_as_f32(x, src_dt, off + s) - m) * inv_std;
+          if (use_scale) v *= g;
+          if (use_shift) v += bt;
+          store_as(y, dst_dt, off + s, v);
+        }
+      }
+    return 0;
+  }
+  #pragma omp parallel for schedule(static)
+  for (int64_t b = 0; b < batch; ++b) {
+    const int64_t off = b * n;
+    float mean = 0.0f, inv;
+    if (type == 0) {
+      float sum = 0.0f;
+      for (int64_t i = 0; i < n; ++i) sum += load_as_f32(x, src_dt, off + i);
+      mean = sum / (float)n;
+      float ssd = 0.0f;
+      for (int64_t i = 0; i < n; ++i) { const float d = load_as_f32(x, src_dt, off + i) - mean; ssd += d * d; }
+      inv = 1.0f / sqrtf(ssd / (float)n + eps);
+    } else {
+      float sum_sq = 0.0f;
+      for (int64_t i = 0; i < n; ++i) {
+        float v = load_as_f32(x, src_dt, off + i);
+        if (type == 3) { v = load_as_f32(residual, src_dt, off + i) + v; store_as(residual, src_dt, off + i, v); }
+        sum_sq += v * v;
+      }
+      inv = 1.0f / sqrtf(sum_sq / (float)n + eps);
+    }
+    for (int64_t i = 0; i < n; ++i) {
+      float v = type == 3 ? load_as_f32(residual, src_dt, off + i) : load_as_f32(x, src_dt, off + i);
+      if (type == 0) v = (v - mean) * inv; else v = v * inv;
+      if (use_scale) v *= load_as_f32(gamma, gamma_dt, i);
+      if (use_shift && type == 0) v += load_as_f32(beta, beta_dt, i);
+      store_as(y, dst_dt, off + i, v);
+    }
+  }
+  return 0;
+}

@@ -64,6 +64,22 @@ def ukernel_bf16_inputs():
     return A, B, bias
 
 
+def norm_inputs():
+    """Inputs of the normalization cases: a [7, 300] matrix with an offset and a wide row, gamma / beta, a residual, and a
+    [3, 5, 11] tensor with running statistics for BatchNorm."""
+    rng = np.random.default_rng(81)
+    x = (rng.normal(size=(7, 300)) * 3 + 0.5).astype(np.float32)
+    x[2] *= 100.0
+    x[4] = 0.0
+    gamma = rng.normal(size=300).astype(np.float32)
+    beta = rng.normal(size=300).astype(np.float32)
+    res = rng.normal(size=(7, 300)).astype(np.float32)
+    xb = rng.normal(size=(3, 5, 11)).astype(np.float32)
+    rm = rng.normal(size=5).astype(np.float32)
+    rv = rng.uniform(0.5, 2.0, 5).astype(np.float32)
+    return x, gamma, beta, res, xb, rm, rv
+
+
 PG_GROUPS = [2, 4, 8, 16]
 UK_ACTS = ["none", "silu_and_mul", "gelu_and_mul", "swiglu_oai_mul"]
 
@@ -111,6 +127,15 @@ def run(tag):
                 r = O.ref2_int8_ukernel(A, B, sa, sw, bias if hb else None, a)
                 assert r is not None, "the reference micro-kernel needs AVX-512 VNNI"
                 out["uk_%s_bias%d" % (a, hb)] = r
+        x, gamma, beta, res, xb, rm, rv = norm_inputs()
+        for dt in ("f32", "bf16"):
+            cv = (lambda a: O.f32_to_bf16(a)) if dt == "bf16" else (lambda a: a)
+            out["norm_layer_%s" % dt] = O.ref2_normalization("layer_norm", cv(x), gamma, beta)
+            out["norm_layer_noaffine_%s" % dt] = O.ref2_normalization("layer_norm", cv(x))
+            out["norm_rms_%s" % dt] = O.ref2_normalization("rms_norm", cv(x), gamma)
+            o, r = O.ref2_normalization("fused_add_rms_norm", cv(x), gamma, residual=cv(res))
+            out["norm_fused_%s" % dt], out["norm_fused_res_%s" % dt] = o, r
+            out["norm_batch_%s" % dt] = O.ref2_normalization("batch_norm", cv(xb), gamma[:5], beta[:5], running_mean=rm, running_var=rv)
         A, B, bias = ukernel_bf16_inputs()
         for a in UK_ACTS:
             for hb in (0, 1):

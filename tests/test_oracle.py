@@ -343,6 +343,37 @@ def test_bf16_tile_arithmetic_against_reference_microkernel(oracle, golden2, act
     assert d.max() <= 2 and (d == 0).mean() > 0.99, (int(d.max()), float((d == 0).mean()))
 
 
+def _norm_inputs():
+    # the same seeded inputs as tests/golden/make_golden_ref2.py::norm_inputs
+    rng = np.random.default_rng(81)
+    x = (rng.normal(size=(7, 300)) * 3 + 0.5).astype(np.float32)
+    x[2] *= 100.0
+    x[4] = 0.0
+    gamma = rng.normal(size=300).astype(np.float32)
+    beta = rng.normal(size=300).astype(np.float32)
+    res = rng.normal(size=(7, 300)).astype(np.float32)
+    xb = rng.normal(size=(3, 5, 11)).astype(np.float32)
+    rm = rng.normal(size=5).astype(np.float32)
+    rv = rng.uniform(0.5, 2.0, 5).astype(np.float32)
+    return x, gamma, beta, res, xb, rm, rv
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_normalization_equals_reference_scalar_kernel(oracle, golden2, dt):
+    """Outputs of the reference's own scalar normalization kernel (lowoha_operators/normalization/kernel/reference_kernel.cpp,
+    driven by oracle/ref_driver2.cpp): LayerNorm with and without gamma / beta, RMSNorm, fused-add RMSNorm (output and the
+    residual it updates in place) and BatchNorm, f32 and bf16 buffers: bit for bit."""
+    x, gamma, beta, res, xb, rm, rv = _norm_inputs()
+    cv = (lambda a: oracle.f32_to_bf16(a)) if dt == "bf16" else (lambda a: a)
+    assert (oracle.normalization("layer_norm", cv(x), gamma, beta) == golden2["norm_layer_%s" % dt]).all()
+    assert (oracle.normalization("layer_norm", cv(x)) == golden2["norm_layer_noaffine_%s" % dt]).all()
+    assert (oracle.normalization("rms_norm", cv(x), gamma) == golden2["norm_rms_%s" % dt]).all()
+    o, r = oracle.normalization("fused_add_rms_norm", cv(x), gamma, residual=cv(res))
+    assert (o == golden2["norm_fused_%s" % dt]).all() and (r == golden2["norm_fused_res_%s" % dt]).all()
+    got = oracle.normalization("batch_norm", cv(xb), gamma[:5], beta[:5], running_mean=rm, running_var=rv)
+    assert (got == golden2["norm_batch_%s" % dt]).all()
+
+
 def test_group_scaled_oracle_reduces_to_the_per_token_form(oracle):
     """With one group the per-group definition (operators/matmul/matmul_ref_kernel.cpp:961-1003) is the per-token
     epilogue order that the golden reference cases pin: (acc * src_scale[m]) * wei_scale[n] + bias."""

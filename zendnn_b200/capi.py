@@ -55,6 +55,18 @@ class MoeExpert(C.Structure):
                 ("dst_op1", C.c_void_p), ("ldc_op1", C.c_int64)]
 
 
+class NormDesc(C.Structure):
+    _fields_ = [("norm_type", C.c_int32), ("use_scale", C.c_int32), ("use_shift", C.c_int32), ("epsilon", C.c_float),
+                ("batch", C.c_int64), ("norm_size", C.c_int64), ("num_channels", C.c_int64),
+                ("src_dt", C.c_int32), ("dst_dt", C.c_int32), ("gamma_dt", C.c_int32), ("beta_dt", C.c_int32),
+                ("input", C.c_void_p), ("output", C.c_void_p), ("gamma", C.c_void_p), ("beta", C.c_void_p),
+                ("running_mean", C.c_void_p), ("running_var", C.c_void_p), ("residual", C.c_void_p),
+                ("quant_dst", C.c_void_p), ("quant_ld", C.c_int64), ("quant_scale", C.c_void_p)]
+
+
+NORM = dict(layer_norm=0, batch_norm=1, rms_norm=2, fused_add_rms_norm=3)
+
+
 class EpConfig(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("num_experts", C.c_int32), ("num_shared", C.c_int32),
                 ("topk", C.c_int32), ("max_tokens", C.c_int32), ("K", C.c_int32), ("I", C.c_int32), ("H", C.c_int32),
@@ -74,7 +86,7 @@ EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b20
            "b200dnn_moe_weighted_reduce_rows", "b200dnn_ep_create", "b200dnn_ep_destroy", "b200dnn_ep_local_expert_count",
            "b200dnn_ep_set_experts", "b200dnn_ep_nccl_unique_id", "b200dnn_ep_connect_nccl", "b200dnn_ep_connect_local",
            "b200dnn_moe_layer_ep", "b200dnn_moe_layer_ep_local", "b200dnn_ep_rows_per_rank", "b200dnn_ep_status",
-           "b200dnn_phase_timing", "b200dnn_phase_times", "b200dnn_measure_int8_peak"]
+           "b200dnn_phase_timing", "b200dnn_phase_times", "b200dnn_measure_int8_peak", "b200dnn_normalization"]
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -99,6 +111,7 @@ lib.b200dnn_dequant_static.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i64,
 lib.b200dnn_gated_act.argtypes = [vp, i32, i64, i64, i64, i32, vp]
 lib.b200dnn_moe_weighted_reduce.argtypes = [vp, vp, i32, i32, i32, i32, i32, vp, i64, vp]
 lib.b200dnn_quant_per_token_asym.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, vp, vp]
+lib.b200dnn_normalization.argtypes = [C.POINTER(NormDesc), C.c_void_p]
 lib.b200dnn_nshard_range.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64), C.POINTER(i32)]
 lib.b200dnn_nshard_create.argtypes = [i32, i32, vp, vp, C.POINTER(vp)]
 lib.b200dnn_nshard_destroy.argtypes = [vp]

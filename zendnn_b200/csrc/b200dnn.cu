@@ -1134,3 +1134,4 @@ int32_t b200dnn_clear_caches(void) {
 #include "moe_ep.cuh"
 #include "group_api.cuh"
 #include "nshard_api.cuh"
+#include "norm_api.cuh"

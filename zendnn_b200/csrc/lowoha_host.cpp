@@ -498,3 +498,25 @@ status_t group_dynamic_quant(const std::vector<const void *> &src, const std::ve
 }  // namespace reorder
 }  // namespace lowoha
 }  // namespace zendnnl
+
+// ------------------------------------------------------------------------------------------------ normalization
+namespace zendnnl { namespace lowoha { namespace normalization {
+
+status_t normalization_direct(const void *input, void *output, const void *gamma, const void *beta, const void *running_mean,
+                              const void *running_var, void *residual, norm_params &params) {
+  b200dnn_norm_t d;
+  std::memset(&d, 0, sizeof d);
+  d.norm_type = static_cast<int32_t>(params.norm_type);
+  d.use_scale = params.use_scale ? 1 : 0; d.use_shift = params.use_shift ? 1 : 0;
+  d.epsilon = params.epsilon;
+  d.batch = static_cast<int64_t>(params.batch); d.norm_size = static_cast<int64_t>(params.norm_size);
+  d.num_channels = static_cast<int64_t>(params.num_channels);
+  d.src_dt = static_cast<int32_t>(params.src_dt); d.dst_dt = static_cast<int32_t>(params.dst_dt);
+  d.gamma_dt = static_cast<int32_t>(params.gamma_dt); d.beta_dt = static_cast<int32_t>(params.beta_dt);
+  d.input = input; d.output = output; d.gamma = gamma; d.beta = beta;
+  d.running_mean = static_cast<const float *>(running_mean); d.running_var = static_cast<const float *>(running_var);
+  d.residual = residual;
+  return from_c(b200dnn_normalization(&d, g_stream));
+}
+
+}}}  // namespace zendnnl::lowoha::normalization
