@@ -117,6 +117,132 @@ __global__ void __launch_bounds__(kNormThreads) norm_rows_kernel(const NormArgs 
   }
 }
 
+// The decoder-layer case at full width: bf16 rows of at most NV * 8 * blockDim elements, 16-byte aligned, bf16 out.  One
+// CTA per row; a thread keeps its NV vectors of eight elements in registers (as the bf16 pairs they are at every stage that
+// is kept) between the passes, so the row is read once and every access is a 16-byte vector (8 bytes for the s8 codes).
+// Same arithmetic as the generic kernel.
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 6 : (NV <= 4 ? 4 : 2)) norm_rows_vec_kernel(const NormArgs a) {
+  __shared__ float sh[kNormThreads / 32];
+  const int nvec = (int)(a.n >> 3);
+  auto lo = [](uint32_t w) { return __uint_as_float(w << 16); };
+  auto hi = [](uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); };
+  for (int64_t b = blockIdx.x; b < a.batch; b += gridDim.x) {
+    const int64_t off = b * a.n;
+    const uint4 *xv = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(a.x) + off);
+    uint4 *rv = a.residual ? reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.residual) + off) : nullptr;
+    uint32_t v[NV][4];
+    float s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      v[j][0] = v[j][1] = v[j][2] = v[j][3] = 0u;
+      if (i < nvec) {
+        const uint4 q = xv[i];
+        v[j][0] = q.x; v[j][1] = q.y; v[j][2] = q.z; v[j][3] = q.w;
+      }
+    }
+    if (a.type == NORM_FUSED_ADD_RMS) {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nvec) {
+          const uint4 r = rv[i];
+          const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float s_lo = __fadd_rn(lo(rw[e]), lo(v[j][e])), s_hi = __fadd_rn(hi(rw[e]), hi(v[j][e]));
+            s1 = __fmaf_rn(s_lo, s_lo, s1); s1 = __fmaf_rn(s_hi, s_hi, s1);
+            v[j][e] = pack_bf16x2(s_lo, s_hi);
+          }
+          rv[i] = make_uint4(v[j][0], v[j][1], v[j][2], v[j][3]);
+        }
+      }
+    } else if (a.type == NORM_RMS) {
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { s1 = __fmaf_rn(lo(v[j][e]), lo(v[j][e]), s1); s1 = __fmaf_rn(hi(v[j][e]), hi(v[j][e]), s1); }
+    } else {
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { s1 = __fadd_rn(s1, lo(v[j][e])); s1 = __fadd_rn(s1, hi(v[j][e])); }
+    }
+    s1 = norm_block_sum(s1, sh);
+    float mean = 0.f, inv;
+    if (a.type == NORM_LAYER) {
+      mean = __fdiv_rn(s1, (float)a.n);
+      float s2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+        if (threadIdx.x + j * blockDim.x < nvec) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float d0 = __fadd_rn(lo(v[j][e]), -mean), d1 = __fadd_rn(hi(v[j][e]), -mean);
+            s2 = __fmaf_rn(d0, d0, s2); s2 = __fmaf_rn(d1, d1, s2);
+          }
+        }
+      s2 = norm_block_sum(s2, sh);
+      inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(s2, (float)a.n), a.eps)));
+    } else inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(s1, (float)a.n), a.eps)));
+    float amax = 0.f;
+    const bool shift = a.use_shift && a.type == NORM_LAYER;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < nvec) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {          // two halves of four elements
+          float g[4] = {1.f, 1.f, 1.f, 1.f};
+          if (a.use_scale) {
+            if (a.gamma_dt == B200DNN_F32) {
+              const float4 g4 = reinterpret_cast<const float4 *>(a.gamma)[2 * i + h];
+              g[0] = g4.x; g[1] = g4.y; g[2] = g4.z; g[3] = g4.w;
+            } else {
+              const uint2 gq = reinterpret_cast<const uint2 *>(a.gamma)[2 * i + h];
+              g[0] = lo(gq.x); g[1] = hi(gq.x); g[2] = lo(gq.y); g[3] = hi(gq.y);
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const uint32_t w = v[j][2 * h + e];
+            float y0 = __fmul_rn(__fadd_rn(lo(w), -mean), inv), y1 = __fmul_rn(__fadd_rn(hi(w), -mean), inv);
+            if (a.use_scale) { y0 = __fmul_rn(y0, g[2 * e]); y1 = __fmul_rn(y1, g[2 * e + 1]); }
+            if (shift) {
+              y0 = __fadd_rn(y0, load_as_f32(a.beta, a.beta_dt, (int64_t)i * 8 + 4 * h + 2 * e));
+              y1 = __fadd_rn(y1, load_as_f32(a.beta, a.beta_dt, (int64_t)i * 8 + 4 * h + 2 * e + 1));
+            }
+            const uint32_t o = pack_bf16x2(y0, y1);
+            v[j][2 * h + e] = o;
+            if (a.q) {
+              uint32_t mag = o & 0x7FFF7FFFu;
+              mag &= ~__vcmpgeu2(mag, 0x7F807F80u);        // non-finite values do not enter the maximum
+              amax = fmaxf(amax, fmaxf(__uint_as_float(mag << 16), __uint_as_float(mag & 0xFFFF0000u)));
+            }
+          }
+        }
+        if (a.y) reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.y) + off)[i] = make_uint4(v[j][0], v[j][1], v[j][2], v[j][3]);
+      }
+    }
+    if (a.q) {
+      const float scale = scale_from_absmax(norm_block_max(amax, sh));
+      const float rinv = __frcp_rn(scale);
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nvec) {
+          // eight codes at a time on packed f32x2 arithmetic, one near-tie test per vector (quant_kernels.cuh)
+          int8_t c[8];
+          quant_vec<uint16_t>(make_uint4(v[j][0], v[j][1], v[j][2], v[j][3]), scale, rinv, c);
+          *reinterpret_cast<uint2 *>(a.q + b * a.q_ld + (int64_t)i * 8) = *reinterpret_cast<const uint2 *>(c);
+        }
+      }
+      if (threadIdx.x == 0) a.q_scale[b] = scale;
+    }
+  }
+}
+
 // BatchNorm: element-wise with per-channel constants
 __global__ void norm_batch_kernel(const NormArgs a, const float *mean, const float *var, int64_t C, int64_t spatial) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -206,6 +332,29 @@ extern "C" int32_t b200dnn_normalization(const b200dnn_norm_t *d, void *stream) 
     B2_TRY(stage_in(d->running_var, (size_t)d->num_channels * 4, st, &v));
     norm_batch_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, st>>>(a, (const float *)m, (const float *)v, d->num_channels, n);
   } else {
+    // full-width form: bf16 in and out, whole 16-byte vectors everywhere, at most 8 vectors per thread
+    auto al16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    const bool vec = d->src_dt == B200DNN_BF16 && d->dst_dt == B200DNN_BF16 && n % 8 == 0 && n <= (int64_t)kNormThreads * 64 &&
+                     al16(a.x) && al16(a.y) && al16(a.residual) && (!a.use_scale || al16(a.gamma)) &&
+                     (!a.q || (a.q_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(a.q) & 7) == 0)) && env_int("B200DNN_NORM_VEC", 1) != 0;
+    if (vec) {
+      const int nvec = (int)(n / 8);
+      // two vectors per thread before the CTA grows (measured: 58 us for 16384 rows of 4096 against 122 us with four and
+      // 195 us with eight: registers, and so resident CTAs, matter more than bytes in flight per thread)
+      const int per = env_int("B200DNN_NORM_NV", 2);
+      int threads = 32;
+      while (threads < kNormThreads && threads * per < nvec) threads <<= 1;
+      const int nv = (nvec + threads - 1) / threads;
+      const long long cap = (long long)R.sm_count * 64;
+      const unsigned grid = (unsigned)(batch < cap ? batch : cap);
+      if (nv <= 1) norm_rows_vec_kernel<1><<<grid, threads, 0, st>>>(a);
+      else if (nv <= 2) norm_rows_vec_kernel<2><<<grid, threads, 0, st>>>(a);
+      else if (nv <= 4) norm_rows_vec_kernel<4><<<grid, threads, 0, st>>>(a);
+      else norm_rows_vec_kernel<8><<<grid, threads, 0, st>>>(a);
+      B2_LAUNCHED();
+      B2_CUDA(cudaGetLastError());
+      return finish_out({&o_y, &o_res, &o_q, &o_s}, st);
+    }
     a.staged = n <= kNormSmemElems ? 1 : 0;
     const size_t smem = a.staged ? (size_t)n * 4 : 0;
     B2_TRY(ensure_max_smem((const void *)norm_rows_kernel, (size_t)kNormSmemElems * 4));

@@ -4,11 +4,13 @@
   python -m zendnn_b200.run_case moe <c4|c5> [--reps R] [--wdt s8|bf16]
   python -m zendnn_b200.run_case gs <w4a8|s8> M K N --gs G [--copies C] [--reps R]
   python -m zendnn_b200.run_case bf16 M K N [--copies C] [--reps R] [--act gelu_tanh] [--bias]
+  python -m zendnn_b200.run_case norm <rms|fused_add_rms|layer> ROWS COLS [--quant] [--no-output] [--reps R]
 
 matmul: s8 per-token activations x s8 per-channel prepacked weight -> bf16; `--copies` distinct prepacked
 weights are used in turn (pick copies * K * N above the L2 size to keep the weight stream in HBM);
 `--dyn` passes bf16 activations with dynamic_quant.  bf16: bf16 activations x bf16 weights (cached by the library
-after the first call) -> bf16.  moe: b200dnn_moe_layer at the shapes of the two MoE
+after the first call) -> bf16.  norm: normalization_direct over a bf16 [ROWS, COLS] matrix with an f32 gamma, optionally with
+the fused per-token quantised output; buffers rotate so that every call reads from HBM.  moe: b200dnn_moe_layer at the shapes of the two MoE
 configurations (c4: 4096 tokens, hidden 4096, FFN 14336, 8 experts top-2; c5: 16384 tokens, hidden 2048,
 FFN 1408, 64 experts top-6 + 2 shared, Zipf-skewed routing).  Prints the mean time per call.
 """
@@ -85,6 +87,51 @@ def _bf16(args):
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (args.reps * len(descs))
     print("bf16 M%d K%d N%d: %.2f us per call, %.0f TFLOP/s (stream order, not graph-replayed)" % (M, K, N, us, 2.0 * M * K * N / us / 1e6))
+
+
+def _norm(args):
+    import ctypes as C
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    R, N = args.rows, args.cols
+    copies = max(2, int(300e6 // (R * N * 2)) + 1)
+    g = torch.Generator(device=dev).manual_seed(0)
+    xs = [torch.randn(R, N, generator=g, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    res = [torch.randn(R, N, generator=g, device=dev).to(torch.bfloat16) for _ in range(copies)] if args.kind == "fused_add_rms" else None
+    gamma = torch.randn(N, generator=g, device=dev)
+    beta = torch.randn(N, generator=g, device=dev)
+    out = torch.empty(R, N, dtype=torch.bfloat16, device=dev)
+    q = torch.empty(R, N, dtype=torch.int8, device=dev)
+    sc = torch.empty(R, dtype=torch.float32, device=dev)
+    descs = []
+    for i in range(copies):
+        d = capi.NormDesc()
+        d.norm_type = capi.NORM[{"rms": "rms_norm", "fused_add_rms": "fused_add_rms_norm", "layer": "layer_norm"}[args.kind]]
+        d.batch, d.norm_size, d.epsilon, d.use_scale, d.use_shift = R, N, 1e-6, 1, int(args.kind == "layer")
+        d.src_dt = d.dst_dt = capi.DT["bf16"]; d.gamma_dt = d.beta_dt = capi.DT["f32"]
+        d.input, d.gamma, d.beta = xs[i].data_ptr(), gamma.data_ptr(), beta.data_ptr()
+        d.output = None if args.no_output else out.data_ptr()
+        if res is not None:
+            d.residual = res[i].data_ptr()
+        if args.quant:
+            d.quant_dst, d.quant_ld, d.quant_scale = q.data_ptr(), N, sc.data_ptr()
+        descs.append(d)
+    for d in descs:
+        capi.check(capi.lib.b200dnn_normalization(C.byref(d), st))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.reps):
+        for d in descs:
+            capi.check(capi.lib.b200dnn_normalization(C.byref(d), st))
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.reps * copies)
+    elem = 2 + (0 if args.no_output else 2) + (4 if res is not None else 0) + (1 if args.quant else 0)
+    print("norm %s rows %d cols %d%s%s: %.2f us per call, %.0f GB/s (%d bytes per element)" %
+          (args.kind, R, N, " +quant" if args.quant else "", " no bf16 output" if args.no_output else "", us, R * N * elem / us / 1e3, elem))
 
 
 def _gs(args):
@@ -221,12 +268,18 @@ def main():
     b.add_argument("--reps", type=int, default=5)
     b.add_argument("--act", default=None)
     b.add_argument("--bias", action="store_true")
+    nm = sub.add_parser("norm")
+    nm.add_argument("kind", choices=["rms", "fused_add_rms", "layer"])
+    nm.add_argument("rows", type=int); nm.add_argument("cols", type=int)
+    nm.add_argument("--quant", action="store_true")
+    nm.add_argument("--no-output", action="store_true", dest="no_output")
+    nm.add_argument("--reps", type=int, default=5)
     e = sub.add_parser("moe")
     e.add_argument("config", choices=["c4", "c5"])
     e.add_argument("--reps", type=int, default=3)
     e.add_argument("--wdt", choices=["s8", "bf16"], default="s8", help="expert weights: s8 (dynamic INT8) or bf16 (no quantisation)")
     args = ap.parse_args()
-    {"matmul": _matmul, "moe": _moe, "gs": _gs, "bf16": _bf16}[args.what](args)
+    {"matmul": _matmul, "moe": _moe, "gs": _gs, "bf16": _bf16, "norm": _norm}[args.what](args)
 
 
 if __name__ == "__main__":
