@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 6 : (NV <= 4 ? 4 : 2))
       inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(s2, (float)a.n), a.eps)));
     } else inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(s1, (float)a.n), a.eps)));
     float amax = 0.f;
-    const bool shift = a.use_shift && a.type == NORM_LAYER;
+    const bool layer = a.type == NORM_LAYER, shift = a.use_shift && layer;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
@@ -204,38 +204,83 @@ __global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 6 : (NV <= 4 ? 4 : 2))
               g[0] = lo(gq.x); g[1] = hi(gq.x); g[2] = lo(gq.y); g[3] = hi(gq.y);
             }
           }
+          float bt[4] = {0.f, 0.f, 0.f, 0.f};
+          if (shift) {
+            if (a.beta_dt == B200DNN_F32) {
+              const float4 b4 = reinterpret_cast<const float4 *>(a.beta)[2 * i + h];
+              bt[0] = b4.x; bt[1] = b4.y; bt[2] = b4.z; bt[3] = b4.w;
+            } else {
+              const uint2 bq = reinterpret_cast<const uint2 *>(a.beta)[2 * i + h];
+              bt[0] = lo(bq.x); bt[1] = hi(bq.x); bt[2] = lo(bq.y); bt[3] = hi(bq.y);
+            }
+          }
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const uint32_t w = v[j][2 * h + e];
-            float y0 = __fmul_rn(__fadd_rn(lo(w), -mean), inv), y1 = __fmul_rn(__fadd_rn(hi(w), -mean), inv);
+            float y0 = lo(w), y1 = hi(w);
+            if (layer) { y0 = __fadd_rn(y0, -mean); y1 = __fadd_rn(y1, -mean); }
+            y0 = __fmul_rn(y0, inv); y1 = __fmul_rn(y1, inv);
             if (a.use_scale) { y0 = __fmul_rn(y0, g[2 * e]); y1 = __fmul_rn(y1, g[2 * e + 1]); }
-            if (shift) {
-              y0 = __fadd_rn(y0, load_as_f32(a.beta, a.beta_dt, (int64_t)i * 8 + 4 * h + 2 * e));
-              y1 = __fadd_rn(y1, load_as_f32(a.beta, a.beta_dt, (int64_t)i * 8 + 4 * h + 2 * e + 1));
-            }
+            if (shift) { y0 = __fadd_rn(y0, bt[2 * e]); y1 = __fadd_rn(y1, bt[2 * e + 1]); }
             const uint32_t o = pack_bf16x2(y0, y1);
             v[j][2 * h + e] = o;
-            if (a.q) {
-              uint32_t mag = o & 0x7FFF7FFFu;
-              mag &= ~__vcmpgeu2(mag, 0x7F807F80u);        // non-finite values do not enter the maximum
-              amax = fmaxf(amax, fmaxf(__uint_as_float(mag << 16), __uint_as_float(mag & 0xFFFF0000u)));
-            }
+            // rounding to bf16 is monotonic: the largest rounded magnitude is the rounded largest magnitude (a NaN does not
+            // enter fmaxf; an infinity does and is dealt with after the loop)
+            if (a.q) amax = fmaxf(amax, fmaxf(fabsf(y0), fabsf(y1)));
           }
         }
         if (a.y) reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(a.y) + off)[i] = make_uint4(v[j][0], v[j][1], v[j][2], v[j][3]);
       }
     }
     if (a.q) {
-      const float scale = scale_from_absmax(norm_block_max(amax, sh));
+      amax = norm_block_max(amax, sh);
+      amax = __uint_as_float(pack_bf16x2(amax, 0.0f) << 16);
+      if (!finite_f32(amax)) {
+        // an infinite element (it quantises to 0): take the maximum over the finite rounded values instead
+        uint32_t mb = 0u;
+#pragma unroll
+        for (int j = 0; j < NV; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t m0 = (v[j][e] << 16) & 0x7FFFFFFFu, m1 = v[j][e] & 0x7FFF0000u;
+            mb = max(mb, m0 < 0x7F800000u ? m0 : 0u);
+            mb = max(mb, m1 < 0x7F800000u ? m1 : 0u);
+          }
+        amax = norm_block_max(__uint_as_float(mb), sh);
+      }
+      const float scale = scale_from_absmax(amax);
       const float rinv = __frcp_rn(scale);
+      // q = rne(v / scale) without a division: m = v * rinv + 1.5 * 2^23 holds the integer nearest to the product in its low
+      // byte; d = v * rinv - that integer is the product's distance from it, and whenever |d| < 0.4999 (d^2 < 0.2499, one
+      // fused operation whose sign bit is and-ed over the vector) the product and the exact quotient round alike: rinv is
+      // the correctly rounded reciprocal, so v * rinv is within 127.5 * 2^-24 < 1e-5 of v / scale.  An element that fails
+      // the test, through a near-tie or because it is not finite, takes the exact division.
+      const float magic = 12582912.0f;
 #pragma unroll
       for (int j = 0; j < NV; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < nvec) {
-          // eight codes at a time on packed f32x2 arithmetic, one near-tie test per vector (quant_kernels.cuh)
-          int8_t c[8];
-          quant_vec<uint16_t>(make_uint4(v[j][0], v[j][1], v[j][2], v[j][3]), scale, rinv, c);
-          *reinterpret_cast<uint2 *>(a.q + b * a.q_ld + (int64_t)i * 8) = *reinterpret_cast<const uint2 *>(c);
+          uint32_t mbits[8], ok = 0x80000000u;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float v0 = lo(v[j][e]), v1 = hi(v[j][e]);
+            const float m0 = __fmaf_rn(v0, rinv, magic), m1 = __fmaf_rn(v1, rinv, magic);
+            const float d0 = __fmaf_rn(v0, rinv, __fsub_rn(magic, m0)), d1 = __fmaf_rn(v1, rinv, __fsub_rn(magic, m1));
+            const uint32_t c0 = __float_as_uint(__fmaf_rn(d0, d0, -0.2499f)), c1 = __float_as_uint(__fmaf_rn(d1, d1, -0.2499f));
+            ok &= c0 & c1;
+            mbits[2 * e] = __float_as_uint(m0); mbits[2 * e + 1] = __float_as_uint(m1);
+          }
+          if (!ok) {
+            // only the elements that failed take the division (about two in ten thousand)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float ve = (e & 1) ? hi(v[j][e >> 1]) : lo(v[j][e >> 1]);
+              const float de = __fmaf_rn(ve, rinv, __fsub_rn(magic, __uint_as_float(mbits[e])));
+              if (!(__fmaf_rn(de, de, -0.2499f) < 0.0f)) mbits[e] = (uint32_t)(uint8_t)quant_sym(ve, scale);
+            }
+          }
+          *reinterpret_cast<uint2 *>(a.q + b * a.q_ld + (int64_t)i * 8) =
+              make_uint2(low_bytes4(mbits[0], mbits[1], mbits[2], mbits[3]), low_bytes4(mbits[4], mbits[5], mbits[6], mbits[7]));
         }
       }
       if (threadIdx.x == 0) a.q_scale[b] = scale;
@@ -335,7 +380,7 @@ extern "C" int32_t b200dnn_normalization(const b200dnn_norm_t *d, void *stream) 
     // full-width form: bf16 in and out, whole 16-byte vectors everywhere, at most 8 vectors per thread
     auto al16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     const bool vec = d->src_dt == B200DNN_BF16 && d->dst_dt == B200DNN_BF16 && n % 8 == 0 && n <= (int64_t)kNormThreads * 64 &&
-                     al16(a.x) && al16(a.y) && al16(a.residual) && (!a.use_scale || al16(a.gamma)) &&
+                     al16(a.x) && al16(a.y) && al16(a.residual) && (!a.use_scale || al16(a.gamma)) && (!(a.use_shift && !rms) || al16(a.beta)) &&
                      (!a.q || (a.q_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(a.q) & 7) == 0)) && env_int("B200DNN_NORM_VEC", 1) != 0;
     if (vec) {
       const int nvec = (int)(n / 8);
