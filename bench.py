@@ -769,6 +769,51 @@ def run_single_gpu_extras(torch, capi, dev, peaks, int8_peak):
                                             "roofline": bf16_roof(tf), "note": "same layer with bf16 experts, no quantisation"}
     del keep, ex, x, logits, o
     torch.cuda.synchronize()
+
+    # ---- the operator in front of the block: fused-add RMSNorm whose result leaves as per-token s8 (and as bf16)
+    import ctypes as C
+    Rn, Dn = 16384, 4096
+    copies = 3                                              # 3 x 134 MB of activations in turn: every call reads from HBM
+    xs = [torch.randn(Rn, Dn, generator=gd, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    rs = [torch.randn(Rn, Dn, generator=gd, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    gamma = torch.randn(Dn, generator=gd, device=dev)
+    y = torch.empty(Rn, Dn, dtype=torch.bfloat16, device=dev)
+    q = torch.empty(Rn, Dn, dtype=torch.int8, device=dev)
+    sc = torch.empty(Rn, dtype=torch.float32, device=dev)
+    hbm = float(peaks["hbm"])
+
+    def norm_case(kind, quant, out):
+        ds = []
+        for i in range(copies):
+            d = capi.NormDesc()
+            d.norm_type, d.batch, d.norm_size, d.epsilon, d.use_scale = capi.NORM[kind], Rn, Dn, 1e-6, 1
+            d.src_dt = d.dst_dt = bf
+            d.gamma_dt = d.beta_dt = capi.DT["f32"]
+            d.input, d.gamma = xs[i].data_ptr(), gamma.data_ptr()
+            d.output = y.data_ptr() if out else None
+            if kind == "fused_add_rms_norm":
+                d.residual = rs[i].data_ptr()
+            if quant:
+                d.quant_dst, d.quant_ld, d.quant_scale = q.data_ptr(), Dn, sc.data_ptr()
+            ds.append(d)
+        it = [0]
+
+        def call():
+            capi.check(capi.lib.b200dnn_normalization(C.byref(ds[it[0] % copies]), st))
+            it[0] += 1
+        ms = _time_events(torch, call, 12, warm=3)
+        per = 2 + (2 if out else 0) + (4 if kind == "fused_add_rms_norm" else 0) + (1 if quant else 0)
+        gbs = Rn * Dn * per / ms / 1e6
+        return {"us": round(ms * 1e3, 1), "bytes_per_element": per, "gbs": round(gbs, 1),
+                "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": round(hbm, 1), "unit": "GB/s", "frac": round(gbs / hbm, 4),
+                             "peak_source": peaks["src"]}}
+    out["norm_rows16384_cols4096_bf16"] = {
+        "rms_norm": norm_case("rms_norm", False, True),
+        "fused_add_rms_norm": norm_case("fused_add_rms_norm", False, True),
+        "fused_add_rms_norm_with_s8_output": norm_case("fused_add_rms_norm", True, True),
+        "rms_norm_s8_output_only": norm_case("rms_norm", True, False)}
+    del xs, rs, y, q, sc
+    torch.cuda.synchronize()
     capi.lib.b200dnn_clear_caches()
     torch.cuda.empty_cache()
     return out

@@ -159,8 +159,9 @@ struct norm_params {
   data_type_t accum_type = data_type_t::f32;
 };
 
-status_t normalization_direct(const void *input, void *output, const void *gamma, const void *beta, const void *running_mean,
-                              const void *running_var, void *residual, norm_params &params);
+ZENDNNL_B200_API status_t normalization_direct(const void *input, void *output, const void *gamma, const void *beta,
+                                               const void *running_mean, const void *running_var, void *residual,
+                                               norm_params &params);
 }  // namespace normalization
 
 // ------------------------------------------------------------------------------------------ matmul

@@ -212,6 +212,46 @@ static void test_bf16_matmul_direct() {
   CHECK(st == status_t::failure, "bf16 matmul_direct with a source scale must fail (got %d)", (int)st);
 }
 
+// normalization_direct: RMSNorm and fused-add RMSNorm on bf16 rows against the scalar definition
+// (lowoha_operators/normalization/kernel/reference_kernel.cpp:383-421, 449-492)
+static void test_normalization_direct() {
+  using namespace zendnnl::lowoha::normalization;
+  Rng r(15);
+  const int B = 37, D = 520;
+  std::vector<uint16_t> X((size_t)B * D), R0((size_t)B * D), Y((size_t)B * D, 0);
+  std::vector<float> gamma(D);
+  for (auto &v : X) v = f2bf(r.rn() * 2.0f);
+  for (auto &v : R0) v = f2bf(r.rn());
+  for (auto &v : gamma) v = r.rn();
+  for (int fused = 0; fused < 2; ++fused) {
+    std::vector<uint16_t> Rs = R0;
+    norm_params p;
+    p.norm_type = fused ? norm_type_t::FUSED_ADD_RMS_NORM : norm_type_t::RMS_NORM;
+    p.batch = B; p.norm_size = D; p.epsilon = 1e-6f; p.use_scale = true;
+    p.src_dt = data_type_t::bf16; p.dst_dt = data_type_t::bf16; p.gamma_dt = data_type_t::f32;
+    status_t st = normalization_direct(X.data(), Y.data(), gamma.data(), nullptr, nullptr, nullptr, fused ? Rs.data() : nullptr, p);
+    CHECK(st == status_t::success, "normalization_direct (fused=%d): %s", fused, last_error());
+    int worst = 0, res_bad = 0;
+    for (int b = 0; b < B; ++b) {
+      float ss = 0.f;
+      std::vector<float> row(D);
+      for (int i = 0; i < D; ++i) {
+        float v = bf2f(X[(size_t)b * D + i]);
+        if (fused) { v = bf2f(R0[(size_t)b * D + i]) + v; res_bad += f2bf(v) != Rs[(size_t)b * D + i]; row[i] = bf2f(f2bf(v)); }
+        else row[i] = v;
+        ss += v * v;
+      }
+      const float inv = 1.0f / std::sqrt(ss / (float)D + 1e-6f);
+      for (int i = 0; i < D; ++i) worst = std::max(worst, ulp_diff(Y[(size_t)b * D + i], f2bf(row[i] * inv * gamma[i])));
+    }
+    CHECK(worst <= 1 && res_bad == 0, "normalization_direct (fused=%d): %d bf16 ulp, %d residual elements differ", fused, worst, res_bad);
+  }
+  norm_params bad;
+  bad.norm_type = norm_type_t::RMS_NORM; bad.batch = 1; bad.norm_size = 8; bad.epsilon = 0.f;
+  bad.src_dt = data_type_t::bf16; bad.dst_dt = data_type_t::bf16;
+  CHECK(normalization_direct(X.data(), Y.data(), nullptr, nullptr, nullptr, nullptr, nullptr, bad) == status_t::failure, "epsilon 0 must fail");
+}
+
 // INT8 with a quantised u8 / s8 output tensor: dst_scale and dst_zp close the epilogue chain
 // (backends/aocl/aocl_postop.cpp:1421-1448), clamp and nearbyint as operators/matmul/matmul_ref_kernel.cpp:155-192
 static void test_int8_requantised_dst() {
@@ -599,6 +639,7 @@ int main(int argc, char **argv) {
   RUN(test_w4a8_bf16());
   RUN(test_int8_requantised_dst());
   RUN(test_bf16_matmul_direct());
+  RUN(test_normalization_direct());
   RUN(test_reorder_and_prepack());
   RUN(test_fused_moe_vs_two_call(false, false, false));
   RUN(test_fused_moe_vs_two_call(true, true, false));
