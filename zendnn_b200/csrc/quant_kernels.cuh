@@ -27,13 +27,14 @@ __device__ __forceinline__ int8_t quant_sym(float v, float scale) {
 }
 // Same result as quant_sym without a division or a conversion instruction in the common case, for a scale that
 // comes from the abs-max of the row itself (so |v/scale| <= 127 up to rounding).  rinv = __frcp_rn(scale).
-// v*rinv is within 1e-4 of the rounded quotient, so whenever it is at least 1e-3 away from a half integer
-// both round to the same integer; adding 1.5*2^23 rounds to that integer (nearest-even) and leaves its two's
-// complement in the low mantissa byte.  The rare near-tie and every non-finite input take the exact division.
+// rinv is the correctly rounded reciprocal, so v*rinv, its rounding and the rounded quotient v/scale all lie within
+// 3 * 127.5 * 2^-24 < 2.3e-5 of the true quotient: whenever v*rinv is at least 1e-4 away from a half integer they round to the
+// same integer; adding 1.5*2^23 rounds to that integer (nearest-even) and leaves its two's complement in the low mantissa
+// byte.  The rare near-tie (two elements in ten thousand) and every non-finite input take the exact division.
 __device__ __forceinline__ int8_t quant_sym_r(float v, float scale, float rinv) {
   const float magic = 12582912.0f;
   const float qa = v * rinv, m = qa + magic, t = m - magic;
-  if (fabsf(qa - t) < 0.499f) return (int8_t)(__float_as_int(m) & 0xFF);
+  if (fabsf(qa - t) < 0.4999f) return (int8_t)(__float_as_int(m) & 0xFF);
   return quant_sym(v, scale);
 }
 
@@ -41,7 +42,8 @@ __device__ __forceinline__ int8_t quant_sym_r(float v, float scale, float rinv) 
 //   m = v*rinv + 1.5*2^23 (one fused rounding: the integer nearest to the product), t' = 1.5*2^23 - m = -round,
 //   d = v*rinv + t' (the product's distance from that integer),
 // three packed instructions instead of eight scalar ones, and ONE near-tie test per vector: the largest |d| (a
-// NaN-propagating maximum, so non-finite inputs fail the test as well) must stay below 0.499.  Returns false when the
+// NaN-propagating maximum, so non-finite inputs fail the test as well) must stay below 0.4999 (a wider band, 0.499, sent
+// two vectors in a hundred, and with them four warps in ten, through the divisions).  Returns false when the
 // vector needs the exact division; o[] then holds nothing useful.
 __device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
 __device__ __forceinline__ void f32x2_unpack(uint64_t r, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(r)); }
@@ -63,7 +65,7 @@ __device__ __forceinline__ bool quant_pairs_fast(const float (&v)[2 * PAIRS], fl
     m_bits[2 * p] = __float_as_uint(m0); m_bits[2 * p + 1] = __float_as_uint(m1);
     e = max_nan_abs(max_nan_abs(e, d0), d1);
   }
-  return e < 0.499f;
+  return e < 0.4999f;
 }
 // low bytes of four words -> one word
 __device__ __forceinline__ uint32_t low_bytes4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
