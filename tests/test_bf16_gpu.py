@@ -290,3 +290,45 @@ def test_weight_only_quantisation_contract(capi, oracle):
     assert capi.matmul(mk(wei_dt=capi.DT["u4"], wei_zp=np.zeros(N, dtype=np.float32))) == capi.FAILURE      # zero point must be s8 or bf16
     assert capi.matmul(mk(wei_scale=capi.quant(np.ones(3 * N, dtype=np.float32), count=3 * N))) == capi.FAILURE   # K % G != 0
     capi.lib.b200dnn_clear_caches()
+
+
+# ---------------------------------------------------------------------------------- group_matmul_direct, plain mode, bf16 experts
+def test_group_matmul_bf16_one_grouped_launch(capi, oracle, monkeypatch):
+    """Plain (parallel) mode of group_matmul_direct with bf16 x bf16 experts of one shape: one grouped launch whose results are
+    those of separate matmul calls (identical bytes), checked against the oracle per expert, with ragged and empty experts, a
+    bias on some experts only and padded destinations."""
+    from helpers import assert_bf16_close
+    rng = np.random.default_rng(23)
+    Ms, K, N, ldc = [200, 0, 37, 130, 1, 300], 264, 392, 400
+    bf = capi.DT["bf16"]
+    descs = (capi.MatmulDesc * len(Ms))()
+    keep, outs, refs = [], [], []
+    for g, M in enumerate(Ms):
+        A = oracle.f32_to_bf16(rng.standard_normal((max(M, 1), K)).astype(np.float32))
+        W = oracle.f32_to_bf16((rng.standard_normal((K, N)) * 0.06).astype(np.float32))
+        bias = rng.standard_normal(N).astype(np.float32) if g % 2 == 0 else None
+        out = np.zeros((max(M, 1), ldc), dtype=np.uint16)
+        keep.append((A, W, bias)); outs.append(out)
+        descs[g] = capi.make_matmul(M, N, K, A, W, out, src_dt=bf, wei_dt=bf, dst_dt=bf, ldc=ldc, bias=bias, postops=["swish"],
+                                    weights_const=True)
+        refs.append(oracle.matmul_bf16(A[:M], W, "bf16", bias=bias, postops=["swish"]) if M else None)
+    capi.check(capi.lib.b200dnn_group_matmul(len(Ms), descs, None))          # packs the weights
+    for o in outs:
+        o[:] = 0
+    n0 = capi.lib.b200dnn_launch_count()
+    capi.check(capi.lib.b200dnn_group_matmul(len(Ms), descs, None))
+    assert capi.lib.b200dnn_launch_count() - n0 == 1, "expected one grouped launch"
+    grouped = [o.copy() for o in outs]
+    for g, M in enumerate(Ms):
+        if not M:
+            assert not outs[g].any()
+            continue
+        assert_bf16_close(outs[g][:M, :N], refs[g], 1, "expert %d" % g, atol=2e-4)
+        assert not outs[g][:, N:].any(), "padding columns of expert %d were written" % g
+    monkeypatch.setenv("B200DNN_GROUPED_PLAIN", "0")
+    for o in outs:
+        o[:] = 0
+    capi.check(capi.lib.b200dnn_group_matmul(len(Ms), descs, None))
+    for g in range(len(Ms)):
+        assert (outs[g] == grouped[g]).all(), "expert %d: grouped and separate calls differ" % g
+    capi.lib.b200dnn_clear_caches()

@@ -2,7 +2,8 @@
 // independent GEMM with its own source, weight, bias and destination
 // (lowoha_operators/matmul/group_matmul/group_matmul_parallel_common.hpp:1240-1248: experts with M == 0 are skipped).
 // Experts that share one problem shape run as ONE grouped tcgen05 launch (the same kernel as the fused MoE's second
-// GEMM: one tensor map per expert, per-expert epilogue pointers); anything else runs expert by expert through
+// GEMM: one tensor map per expert, per-expert epilogue pointers), W8A8 experts and bf16 x bf16 experts alike; anything else
+// runs expert by expert through
 // b200dnn_matmul, so the results are those of G separate calls either way.  Included at the end of b200dnn.cu.
 #pragma once
 
@@ -154,11 +155,103 @@ int32_t group_matmul_grouped(int G, const b200dnn_matmul_t *d, void *stream) {
   return B200DNN_SUCCESS;
 }
 
+// bf16 x bf16 experts of one shape (no quantisation, no scales): the same grouped launch on the kernel's bf16 form
+bool group_is_uniform_bf16(int G, const b200dnn_matmul_t *d) {
+  const b200dnn_matmul_t *f = nullptr;
+  long long rows = 0;
+  int active = 0, bias_dt = 0;
+  for (int g = 0; g < G; ++g) {
+    const b200dnn_matmul_t &x = d[g];
+    if (x.M <= 0) { if (x.M < 0) return false; continue; }
+    ++active; rows += x.M;
+    if (!f) f = &x;
+    if (!is_bf16_matmul(&x) || (x.dst_dt != B200DNN_BF16 && x.dst_dt != B200DNN_F32)) return false;
+    if (x.bias) {
+      if (bias_dt && x.bias_dt != bias_dt) return false;
+      bias_dt = x.bias_dt;
+    }
+    if (x.K != f->K || x.N != f->N || x.transB != f->transB || x.dst_dt != f->dst_dt || x.weights_const != f->weights_const ||
+        x.n_postops != f->n_postops || x.force_kernel != 0 || (x.wei_format != 'n' && x.wei_format != 0))
+      return false;
+    for (int i = 0; i < x.n_postops; ++i) {
+      const b200dnn_postop_t &p = x.postops[i], &q = f->postops[i];
+      if (p.type == PO_BINARY_ADD || p.type == PO_BINARY_MUL) return false;
+      if (p.type != q.type || p.alpha != q.alpha || p.beta != q.beta) return false;
+    }
+  }
+  return active >= 2 && rows > 16ll * active;
+}
+
+int32_t group_matmul_grouped_bf16(int G, const b200dnn_matmul_t *d, void *stream) {
+  B2_ENTER(stream);
+  Runtime &Rt = rt();
+  const b200dnn_matmul_t *f = nullptr;
+  std::vector<int32_t> row_off(G + 1, 0), tile_prefix(G + 1, 0);
+  long long rows_all = 0;
+  for (int g = 0; g < G; ++g) if (d[g].M > 0) { rows_all += d[g].M; if (!f) f = &d[g]; }
+  const int K = f->K, N = f->N;
+  const int tile_rows = tc_tile_rows(rows_all, N);
+  for (int g = 0; g < G; ++g) {
+    const int m = d[g].M > 0 ? d[g].M : 0;
+    if (m) B2_TRY(validate_bf16_matmul(&d[g]));
+    row_off[g + 1] = row_off[g] + m;
+    tile_prefix[g + 1] = tile_prefix[g] + (m + tile_rows - 1) / tile_rows;
+  }
+  const int R = row_off[G];
+  const int64_t Kq = round_up(K, 8);
+  std::vector<PackedWeight> pws(G);
+  std::vector<TcGroupDesc> gd(G);
+  std::vector<Staged> outs(G);
+  uint16_t *X = (uint16_t *)Rt.ws.alloc((size_t)R * Kq * 2);
+  B2_CHECK(X, B200DNN_FAILURE, "workspace allocation failed");
+  int first = -1;
+  for (int g = 0; g < G; ++g) {
+    outs[g].copy_back = false;
+    if (d[g].M <= 0) continue;
+    if (first < 0) first = g;
+    B2_TRY(resolve_bf16_weight(d[g].weight, K, N, d[g].ldb, d[g].transB, 0, d[g].weights_const, st, &pws[g]));
+    const void *b = nullptr, *src = nullptr;
+    if (d[g].bias) B2_TRY(stage_in(d[g].bias, (size_t)N * dt_size(d[g].bias_dt), st, &b));
+    B2_TRY(stage_in(d[g].src, span_bytes(d[g].M, K, d[g].lda, B200DNN_BF16), st, &src));
+    B2_TRY(stage_out(d[g].dst, span_bytes(d[g].M, N, d[g].ldc, d[g].dst_dt), st, &outs[g], d[g].ldc != N));
+    gd[g] = TcGroupDesc{nullptr, nullptr, b, outs[g].dev, d[g].ldc};
+    // the experts' rows back to back at a pitch the copy engine accepts
+    B2_CUDA(cudaMemcpy2DAsync(X + (size_t)row_off[g] * Kq, (size_t)Kq * 2, src, (size_t)d[g].lda * 2, (size_t)K * 2, (size_t)d[g].M,
+                              cudaMemcpyDefault, st));
+  }
+  for (int g = 0; g < G; ++g) if (d[g].M <= 0) { pws[g] = pws[first]; gd[g] = TcGroupDesc{nullptr, nullptr, nullptr, nullptr, 0}; }
+  void *gd_dev = nullptr, *tabs = nullptr;
+  B2_TRY(upload_blob(gd.data(), sizeof(TcGroupDesc) * G, st, &gd_dev));
+  std::vector<int32_t> both(2 * (G + 1));
+  memcpy(both.data(), row_off.data(), sizeof(int32_t) * (G + 1));
+  memcpy(both.data() + G + 1, tile_prefix.data(), sizeof(int32_t) * (G + 1));
+  B2_TRY(upload_blob(both.data(), both.size() * sizeof(int32_t), st, &tabs));
+  const int32_t *row_off_dev = (const int32_t *)tabs, *tile_prefix_dev = row_off_dev + G + 1;
+  EpiParams e{};
+  e.dst = nullptr; e.ldc = N; e.dst_dt = f->dst_dt;
+  for (int g = 0; g < G; ++g) if (d[g].M > 0 && d[g].bias) e.bias_dt = d[g].bias_dt;
+  e.n_po = f->n_postops;
+  for (int i = 0; i < f->n_postops; ++i) {
+    const b200dnn_postop_t &p = f->postops[i];
+    e.po[i].type = p.type; e.po[i].dt = p.dt; e.po[i].ld = 0; e.po[i].alpha = p.alpha; e.po[i].beta = p.beta; e.po[i].buff = nullptr;
+  }
+  B2_TRY(grouped_gemm((const uint8_t *)X, Kq * 2, R, N, 2 * K, pws, row_off_dev, tile_prefix_dev, (const TcGroupDesc *)gd_dev, tile_prefix[G], e,
+                      false, st, tile_rows, true));
+  bool any = false;
+  for (auto &s : outs) {
+    if (s.copy_back) { B2_CUDA(cudaMemcpyAsync(s.host, s.dev, s.bytes, cudaMemcpyDeviceToHost, st)); any = true; }
+    else if (s.sync) any = true;
+  }
+  if (any) B2_TRY(check_tc_status(st));
+  return B200DNN_SUCCESS;
+}
+
 }  // namespace
 
 extern "C" int32_t b200dnn_group_matmul(int32_t G, const b200dnn_matmul_t *d, void *stream) {
   B2_CHECK(G > 0 && d, B200DNN_FAILURE, "group matmul: bad argument");
   if (group_is_uniform(G, d) && env_int("B200DNN_GROUPED_PLAIN", 1) != 0) return group_matmul_grouped(G, d, stream);
+  if (group_is_uniform_bf16(G, d) && env_int("B200DNN_GROUPED_PLAIN", 1) != 0) return group_matmul_grouped_bf16(G, d, stream);
   for (int g = 0; g < G; ++g) {
     B2_CHECK(d[g].M >= 0, B200DNN_FAILURE, "group matmul: expert %d has negative M", g);
     if (d[g].M == 0) continue;
