@@ -122,6 +122,8 @@ def test_parse_grp_lines():
     assert B.grp_unsupported_reason(c) is None
     u = B.parse_grp_line("4, 32, 2880, 5760, 200, bf16:s8:bf16, true, 50, 4, 3, 2880, 1, 32")
     assert u["M"] == [32] * 4 and u["total_experts"] == 32 and B.grp_unsupported_reason(u) is None
+    t = B.parse_grp_line("9, 9:32:1:1:18:5:32:12:18, 2880, 5760, 100, bf16:bf16:bf16, true, 20, 4, 3, 2880, 1, 32  # freq=4")
+    assert t["total_experts"] == 32 and t["M"][1] == 32 and B.grp_unsupported_reason(t) is None     # trailing comment of the shipped traces
     plain = B.parse_grp_line("8, 4, 4096, 14336, 200, bf16:s8:bf16, true, 50")
     assert "fused" in B.grp_unsupported_reason(plain)
     assert B.parse_grp_line("# comment") is None

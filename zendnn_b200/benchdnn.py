@@ -274,7 +274,8 @@ GRP_HEADER = ("ops, M, K, N, iters, warmup, dtypes, moe, gated_act, N_down, tota
 def parse_grp_line(line):
     if not line.strip() or line.lstrip().startswith("#"):
         return None
-    parts = [p.strip() for p in line.strip().split(",")]
+    # the shipped traces end their rows with "# freq=N" (the reference's std::stoi stops at the blank before it)
+    parts = [p.strip() for p in line.split("#", 1)[0].strip().split(",")]
     if len(parts) < 8:
         raise ValueError("expected num_ops, M, K, N, iters, dt, is_weights_const, warmup: %r" % line)
     parts += [""] * (13 - len(parts))
