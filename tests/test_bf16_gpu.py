@@ -86,6 +86,22 @@ def test_against_reference_microkernel_outputs(capi, oracle, golden2, has_bias):
     assert ((d <= 2) | near).all() and (d == 0).mean() > 0.99, (int(d.max()), float((d == 0).mean()))
 
 
+@pytest.mark.parametrize("splits", [2, 3, 4])
+def test_split_form(capi, oracle, monkeypatch, splits):
+    """Clusters of 2-4 CTAs share one tile's K blocks and add their f32 partial sums in a fixed order (small-M GEMMs whose
+    tiles do not fill the GPU): same tolerance as the unsplit kernel, and the same bytes on every call."""
+    monkeypatch.setenv("B200DNN_TC_KSPLIT", str(splits))
+    rng = np.random.default_rng(40 + splits)
+    for M, K, N in [(16, 4096, 512), (128, 2048, 384), (200, 1100, 264)]:
+        A, W = make(oracle, rng, M, K, N, wstd=0.05)
+        bias = rng.standard_normal(N).astype(np.float32)
+        ref = oracle.matmul_bf16(A, W, "f32", bias=bias).astype(np.float64)
+        got = run(capi, M, N, K, A, W, "f32", weights_const=False, bias=bias)
+        check(oracle, got, ref, abs_dot(oracle, A, W, False) + 1.0, "f32", "splits=%d %s" % (splits, (M, K, N)))
+        again = run(capi, M, N, K, A, W, "f32", weights_const=False, bias=bias)
+        assert (again == got).all()
+
+
 @pytest.mark.parametrize("pair", [0, 1])
 def test_pair_form_and_bias(capi, oracle, monkeypatch, pair):
     """Both tile forms (one CTA per 128-row tile, two CTAs per 256-row tile), f32 and bf16 bias."""

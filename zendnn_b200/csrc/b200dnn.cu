@@ -494,7 +494,7 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
 #endif
   args.BN = pick_bn(m_tiles_hint, N, R.sm_count, pw0.gated, args.pair);
   args.k_splits = 1;
-  if (!args.f16 && !args.pair && args.n_groups <= 1 && !args.maps_b && !args.groups && !args.tile_prefix && !pw0.gated) pick_split(m_tiles_hint, N, args.k_blocks, &args.BN, &args.k_splits);
+  if (!args.pair && args.n_groups <= 1 && !args.maps_b && !args.groups && !args.tile_prefix && !pw0.gated) pick_split(m_tiles_hint, N, args.k_blocks, &args.BN, &args.k_splits);
   B2_CHECK(args.BN % 32 == 0 && args.BN >= 32 && args.BN <= 256 && (!pw0.gated || args.BN % 64 == 0), B200DNN_FAILURE,
            "bad tile width %d", args.BN);
   B2_CHECK(!args.pair || (args.BN % 32 == 0 && args.BN >= 64 && (!pw0.gated || args.BN % 128 == 0)), B200DNN_FAILURE,
@@ -583,7 +583,10 @@ int32_t launch_tc(const uint8_t *A, int64_t lda, bool a_unsigned, int M_total, i
       ++na;
       cfg.gridDim = dim3((unsigned)(tiles * args.k_splits));
       cfg.attrs = attr; cfg.numAttrs = na;
-      B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<true>, map_a, map_b, map_c, args, epi));
+      if (args.f16) {
+        B2_TRY(ensure_max_smem((const void *)tc_gemm_kernel<true, false, true>, kTcSmemBudget + 1024));
+        B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<true, false, true>, map_a, map_b, map_c, args, epi));
+      } else B2_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<true>, map_a, map_b, map_c, args, epi));
     } else {
       cfg.gridDim = dim3((unsigned)grid);
       cfg.attrs = attr; cfg.numAttrs = na;

@@ -483,8 +483,8 @@ __device__ __forceinline__ void tc_epi_dispatch(int fast_act, const EpiParams &e
 
 // SPLIT: launched in clusters of a.k_splits CTAs, one tile per cluster (see TcGemmArgs::k_splits); plain, non-gated form only.
 // PAIR: launched in clusters of two CTAs that share [256 x BN] tiles through cta_group::2 MMAs (see the head of this file).
-// F16: the bf16 x bf16 form (kind::f16 MMAs over the same byte tiles, f32 accumulators); not with SPLIT, whose partial sums
-// are added as integers.
+// F16: the bf16 x bf16 form (kind::f16 MMAs over the same byte tiles, f32 accumulators); with SPLIT its f32 partial sums are
+// added in a fixed order.
 template <bool SPLIT, bool PAIR = false, bool F16 = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
@@ -505,7 +505,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0) TC_STAMP(0);
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   static_assert(!(SPLIT && PAIR), "the split form and the pair form are separate kernels");
-  static_assert(!(SPLIT && F16), "the split form adds int32 partial sums");
+
   // pair form: this CTA holds its 128 rows of A and its half of the tile's weight rows
   const uint32_t a_bytes = kTcBM * kTcBK, b_bytes = (uint32_t)(PAIR ? a.BN / 2 : a.BN) * kTcBK, stage_bytes = a_bytes + b_bytes;
   const int S = a.stages;
@@ -879,7 +879,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const uint4 v = ld_cluster_v4(rb + (uint32_t)(i * 512));
-            sum[i].x += v.x; sum[i].y += v.y; sum[i].z += v.z; sum[i].w += v.w;
+            if constexpr (F16) {
+              // f32 partial sums: added in a fixed order (own share first, then the other CTAs by rank), so a result is
+              // reproducible; it is not the unsplit kernel's sum bit for bit
+              sum[i].x = __float_as_uint(__fadd_rn(__uint_as_float(sum[i].x), __uint_as_float(v.x)));
+              sum[i].y = __float_as_uint(__fadd_rn(__uint_as_float(sum[i].y), __uint_as_float(v.y)));
+              sum[i].z = __float_as_uint(__fadd_rn(__uint_as_float(sum[i].z), __uint_as_float(v.z)));
+              sum[i].w = __float_as_uint(__fadd_rn(__uint_as_float(sum[i].w), __uint_as_float(v.w)));
+            } else { sum[i].x += v.x; sum[i].y += v.y; sum[i].z += v.z; sum[i].w += v.w; }
           }
         }
 #pragma unroll
@@ -895,7 +902,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint4 v = ld_shared_v4(base + (uint32_t)((u ^ (row_in_tile & 7)) << 4));
           r[4 * u] = v.x; r[4 * u + 1] = v.y; r[4 * u + 2] = v.z; r[4 * u + 3] = v.w;
         }
-        tc_epi_dispatch<false>(a.fast_act, epi, cx, r, tcols, c * 32, pc_tile + c * 32, a.N, m_dst, has_bias, es, lane);
+        tc_epi_dispatch<F16>(a.fast_act, epi, cx, r, tcols, c * 32, pc_tile + c * 32, a.N, m_dst, has_bias, es, lane);
       }
     }
     // nobody leaves while a neighbour may still read its shared memory: arrive as soon as the own reads are done,
