@@ -205,7 +205,8 @@ def test_w4a8_per_tensor_source_scale(capi, oracle, shape):
     ref = oracle.matmul_group_scaled(A, W, np.repeat(s, M), sw, "bf16")
     out = np.zeros((M, N), dtype=np.uint16)
     sc = np.zeros(1, dtype=np.float32)
-    d = capi.make_matmul(M, N, K, X, oracle.pack_s4(W), out, src_dt=capi.DT["bf16"], dst_dt=capi.DT["bf16"], src_scale=capi.quant(sc, count=1),
+    packed = oracle.pack_s4(W)          # the descriptor holds only the address: the array must outlive the call
+    d = capi.make_matmul(M, N, K, X, packed, out, src_dt=capi.DT["bf16"], dst_dt=capi.DT["bf16"], src_scale=capi.quant(sc, count=1),
                          wei_scale=capi.quant(sw, count=G * N), weights_const=False, dynamic_quant=True, wei_dt=capi.DT["s4"])
     _call(capi, d)
     assert (sc == s).all()
