@@ -257,10 +257,11 @@ def test_postop_chain_and_strides(capi, oracle, kernel):
           dict(type="clip", alpha=-0.5, beta=0.75)]
     ref = oracle.matmul_w8a8(np.ascontiguousarray(A), W, "f32", src_scale=[0.05], wei_scale=sw, postops=po)
     out = np.full((M, ldc), 7.0, dtype=np.float32)
+    ss = np.array([0.05], dtype=np.float32)         # the descriptor holds only the address: kept alive for the call
     if True:
         out[:] = 7.0
         d = capi.make_matmul(M, N, K, Afull, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["f32"], lda=lda, ldc=ldc,
-                             weights_const=False, src_scale=np.array([0.05], dtype=np.float32), wei_scale=sw, postops=po,
+                             weights_const=False, src_scale=ss, wei_scale=sw, postops=po,
                              force_kernel=kernel)
         assert capi.matmul(d) == capi.SUCCESS, capi.last_error()
         assert np.allclose(out[:, :N], ref, rtol=2e-6, atol=1e-6)
