@@ -252,6 +252,50 @@ static void test_normalization_direct() {
   CHECK(normalization_direct(X.data(), Y.data(), nullptr, nullptr, nullptr, nullptr, nullptr, bad) == status_t::failure, "epsilon 0 must fail");
 }
 
+// group_matmul_direct, sequential mode (one src, several layers: layer i + 1 reads layer i's destination;
+// matmul/group_matmul_direct.cpp:1138-1163): two dynamically quantised W8A8 layers against the same two calls of matmul_direct
+static void test_group_matmul_sequential_chain() {
+  Rng r(16);
+  const int M = 45, K0 = 256, N0 = 192, N1 = 136;
+  std::vector<uint16_t> X((size_t)M * K0);
+  for (auto &v : X) v = f2bf(r.rn());
+  std::vector<int8_t> W0((size_t)K0 * N0), W1((size_t)N0 * N1);
+  for (auto &v : W0) v = (int8_t)r.ri(-127, 127);
+  for (auto &v : W1) v = (int8_t)r.ri(-127, 127);
+  std::vector<float> s0(N0), s1(N1), b0(N0);
+  for (auto &v : s0) v = r.rf(1e-4f, 5e-4f);
+  for (auto &v : s1) v = r.rf(1e-3f, 5e-3f);
+  for (auto &v : b0) v = r.rn();
+  auto params_for = [&](std::vector<float> &ws, int n) {
+    matmul_params p;
+    p.dtypes.src = data_type_t::bf16; p.dtypes.wei = data_type_t::s8; p.dtypes.dst = data_type_t::bf16; p.dtypes.bias = data_type_t::f32;
+    p.dtypes.compute = data_type_t::s8; p.dynamic_quant = true;
+    p.quant_params.src_scale.dt = data_type_t::f32; p.quant_params.src_scale.dims = {M, 1};
+    p.quant_params.wei_scale.buff = ws.data(); p.quant_params.wei_scale.dt = data_type_t::f32; p.quant_params.wei_scale.dims = {1, n};
+    return p;
+  };
+  matmul_params p0 = params_for(s0, N0), p1 = params_for(s1, N1);
+  matmul_post_op relu; relu.po_type = post_op_type_t::relu; p0.postop_.push_back(relu);
+  std::vector<uint16_t> Y0((size_t)M * N0, 0), Y1((size_t)M * N1, 0), R0((size_t)M * N0, 0), R1((size_t)M * N1, 0);
+  status_t st = group_matmul_direct({'r', 'r'}, {false, false}, {false, false}, {M, M}, {N0, N1}, {K0, N0}, {1.f, 1.f}, {X.data()}, {K0, N0},
+                                    {W0.data(), W1.data()}, {N0, N1}, {b0.data(), nullptr}, {0.f, 0.f}, {Y0.data(), Y1.data()}, {N0, N1},
+                                    {true, true}, {p0, p1}, nullptr, nullptr, nullptr);
+  CHECK(st == status_t::success, "sequential chain: %s", last_error());
+  matmul_batch_params_t bp;
+  st = matmul_direct('r', false, false, M, N0, K0, 1.f, X.data(), K0, W0.data(), N0, b0.data(), 0.f, R0.data(), N0, true, bp, p0);
+  CHECK(st == status_t::success, "layer 0 alone: %s", last_error());
+  st = matmul_direct('r', false, false, M, N1, N0, 1.f, R0.data(), N0, W1.data(), N1, nullptr, 0.f, R1.data(), N1, true, bp, p1);
+  CHECK(st == status_t::success, "layer 1 alone: %s", last_error());
+  CHECK(Y0 == R0 && Y1 == R1, "sequential chain differs from the same two calls of matmul_direct");
+  double sum = 0; for (auto v : Y1) sum += std::fabs(bf2f(v));
+  CHECK(sum > 1.0, "sequential chain produced an all-zero result");
+  // contract: K of a layer must be N of the one before; the MoE extras belong to the parallel mode
+  st = group_matmul_direct({'r', 'r'}, {false, false}, {false, false}, {M, M}, {N0, N1}, {K0, N0 + 8}, {1.f, 1.f}, {X.data()}, {K0, N0},
+                           {W0.data(), W1.data()}, {N0, N1}, {nullptr, nullptr}, {0.f, 0.f}, {Y0.data(), Y1.data()}, {N0, N1}, {true, true},
+                           {p0, p1}, nullptr, nullptr, nullptr);
+  CHECK(st == status_t::failure, "sequential chain with K[1] != N[0] must fail");
+}
+
 // INT8 with a quantised u8 / s8 output tensor: dst_scale and dst_zp close the epilogue chain
 // (backends/aocl/aocl_postop.cpp:1421-1448), clamp and nearbyint as operators/matmul/matmul_ref_kernel.cpp:155-192
 static void test_int8_requantised_dst() {
@@ -640,6 +684,7 @@ int main(int argc, char **argv) {
   RUN(test_int8_requantised_dst());
   RUN(test_bf16_matmul_direct());
   RUN(test_normalization_direct());
+  RUN(test_group_matmul_sequential_chain());
   RUN(test_reorder_and_prepack());
   RUN(test_fused_moe_vs_two_call(false, false, false));
   RUN(test_fused_moe_vs_two_call(true, true, false));

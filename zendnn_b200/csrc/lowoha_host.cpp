@@ -229,9 +229,32 @@ static status_t group_matmul_impl(const std::vector<char> &layout, const std::ve
       !at_least(ldb.size()) || !at_least(bias.size()) || !at_least(beta.size()) || !at_least(ldc.size()) ||
       !at_least(is_weights_const.size()) || !at_least(params.size()))
     return shim_fail(status_t::failure, "group_matmul_direct: a per-expert vector is shorter than the number of operations");
-  if (src.size() == 1 && num_ops > 1) return shim_fail(status_t::unimplemented, "sequential (chained) group mode is not implemented");
-  if (!at_least(src.size())) return shim_fail(status_t::failure, "group_matmul_direct: src vector too short");
   const grp_matmul_gated_act_t act = gated_act ? gated_act->act : grp_matmul_gated_act_t::none;
+  if (src.size() == 1 && num_ops > 1) {
+    // ---- sequential chain (group_matmul_direct.cpp:424-456 rules, :1138-1163 dispatch): layer i + 1 reads layer i's
+    // destination with its leading dimension; M is constant and K[i] == N[i-1]
+    if (moe_postop) return shim_fail(status_t::failure, "group_matmul_direct: moe_postop is only supported in parallel mode (src.size() == num_ops)");
+    if (act != grp_matmul_gated_act_t::none) return shim_fail(status_t::failure, "group_matmul_direct: gated_act is only supported in parallel mode (src.size() == num_ops)");
+    if (fused) return shim_fail(status_t::failure, "group_matmul_direct: fused_moe is only supported in parallel mode (src.size() == num_ops)");
+    if (!at_least(dst.size())) return shim_fail(status_t::failure, "group_matmul_direct: dst vector too short");
+    if (!src[0]) return shim_fail(status_t::failure, "group_matmul sequential: null src pointer");
+    for (size_t i = 0; i < num_ops; ++i) {
+      if (!weight[i] || !dst[i]) return shim_fail(status_t::failure, "group_matmul sequential: null pointer at an operation");
+      if (M[i] <= 0 || N[i] <= 0 || K[i] <= 0) return shim_fail(status_t::failure, "group_matmul sequential: invalid dimensions at an operation");
+      if (i && M[i] != M[0]) return shim_fail(status_t::failure, "group_matmul sequential: M must be constant across layers");
+      if (i && K[i] != N[i - 1]) return shim_fail(status_t::failure, "group_matmul sequential: dimension mismatch between layers (K[i] != N[i-1])");
+    }
+    const matmul_batch_params_t bp;
+    for (size_t i = 0; i < num_ops; ++i) {
+      b200dnn_matmul_t d;
+      status_t st = flatten(layout[i], transA[i], transB[i], M[i], N[i], K[i], alpha[i], i ? dst[i - 1] : src[0], i ? ldc[i - 1] : lda[0],
+                            weight[i], ldb[i], bias[i], beta[i], dst[i], ldc[i], is_weights_const[i], bp, params[i], &d);
+      if (st == status_t::success) st = from_c(b200dnn_matmul(&d, g_stream));
+      if (st != status_t::success) return st;
+    }
+    return status_t::success;
+  }
+  if (!at_least(src.size())) return shim_fail(status_t::failure, "group_matmul_direct: src vector too short");
 
   if (fused) {
     // ---- fused MoE: Op1 (gate|up) -> gated activation -> per-token requantisation -> Op2 (down) [-> weighted reduce]
