@@ -107,6 +107,9 @@ typedef struct b200dnn_matmul_t {
    * lowoha_matmul_utils.cpp:319-331): s8 or bf16, count 1, N or G*N like wei_scale.  w = bf16((q - zp) * scale) with an s8
    * zero point, bf16((q - 8) * scale + zp) with a bf16 one (operators/matmul/matmul_ref_kernel.cpp:466-474). */
   b200dnn_quant_t wei_zp;
+  int32_t transA;        /* != 0: the source is stored transposed, element (m, k) at src[k * lda + m] with lda >= M (matmul_direct's
+                          * transA, lowoha_matmul.hpp:95-99); it is transposed into the workspace first */
+  int32_t reserved_a;
 } b200dnn_matmul_t;
 
 B200DNN_API const char *b200dnn_last_error(void);

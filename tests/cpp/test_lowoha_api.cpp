@@ -296,6 +296,32 @@ static void test_group_matmul_sequential_chain() {
   CHECK(st == status_t::failure, "sequential chain with K[1] != N[0] must fail");
 }
 
+// matmul_direct with transA: the source stored [K, lda] gives the same bytes as the untransposed call
+static void test_int8_transposed_source() {
+  Rng r(17);
+  const int M = 70, K = 200, N = 96, lda_t = 72;
+  std::vector<int8_t> A((size_t)M * K), At((size_t)K * lda_t, 0), W((size_t)K * N);
+  for (auto &v : A) v = (int8_t)r.ri(-127, 127);
+  for (auto &v : W) v = (int8_t)r.ri(-127, 127);
+  for (int m = 0; m < M; ++m) for (int k = 0; k < K; ++k) At[(size_t)k * lda_t + m] = A[(size_t)m * K + k];
+  std::vector<float> sa(M), ws(N);
+  for (auto &v : sa) v = r.rf(0.01f, 0.05f);
+  for (auto &v : ws) v = r.rf(1e-4f, 5e-4f);
+  matmul_params p;
+  p.dtypes.src = data_type_t::s8; p.dtypes.wei = data_type_t::s8; p.dtypes.dst = data_type_t::bf16;
+  p.quant_params.src_scale.buff = sa.data(); p.quant_params.src_scale.dt = data_type_t::f32; p.quant_params.src_scale.dims = {M, 1};
+  p.quant_params.wei_scale.buff = ws.data(); p.quant_params.wei_scale.dt = data_type_t::f32; p.quant_params.wei_scale.dims = {1, N};
+  matmul_batch_params_t bp;
+  std::vector<uint16_t> C0((size_t)M * N, 0), C1((size_t)M * N, 1);
+  status_t st = matmul_direct('r', false, false, M, N, K, 1.0f, A.data(), K, W.data(), N, nullptr, 0.0f, C0.data(), N, false, bp, p);
+  CHECK(st == status_t::success, "untransposed: %s", last_error());
+  st = matmul_direct('r', true, false, M, N, K, 1.0f, At.data(), lda_t, W.data(), N, nullptr, 0.0f, C1.data(), N, false, bp, p);
+  CHECK(st == status_t::success, "transA: %s", last_error());
+  CHECK(C0 == C1, "transA result differs from the untransposed call");
+  st = matmul_direct('r', true, false, M, N, K, 1.0f, At.data(), M - 1, W.data(), N, nullptr, 0.0f, C1.data(), N, false, bp, p);
+  CHECK(st == status_t::failure, "transA with lda < M must fail");
+}
+
 // INT8 with a quantised u8 / s8 output tensor: dst_scale and dst_zp close the epilogue chain
 // (backends/aocl/aocl_postop.cpp:1421-1448), clamp and nearbyint as operators/matmul/matmul_ref_kernel.cpp:155-192
 static void test_int8_requantised_dst() {
@@ -638,7 +664,7 @@ static void test_contract_violations() {
   CHECK(matmul_direct('r', false, false, 4, 16, 64, 1.0f, nullptr, 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p) == status_t::failure, "null src accepted");
   CHECK(matmul_direct('r', false, false, 0, 16, 64, 1.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p) == status_t::failure, "M = 0 accepted");
   CHECK(matmul_direct('c', false, false, 4, 16, 64, 1.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p) == status_t::unimplemented, "column-major not reported");
-  CHECK(matmul_direct('r', true, false, 4, 16, 64, 1.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p) == status_t::unimplemented, "transA not reported");
+  CHECK(matmul_direct('r', true, false, 4, 16, 64, 1.0f, A.data(), 3, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p) == status_t::failure, "transA with lda < M not reported");
   CHECK(matmul_direct('r', false, false, 4, 16, 64, 2.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p) == status_t::unimplemented, "alpha != 1 not reported");
   matmul_params p4 = p; p4.dtypes.wei = data_type_t::s4;
   CHECK(matmul_direct('r', false, false, 4, 16, 64, 1.0f, A.data(), 64, W.data(), 16, nullptr, 0.0f, C.data(), 16, false, bp, p4) == status_t::failure, "s4 weights with a pre-quantised s8 source accepted");
@@ -662,7 +688,7 @@ static void test_contract_violations() {
 
 #define RUN(call) do { std::fprintf(stderr, "running %s\n", #call); call; } while (0)
 
-// one refused call (transA is refused in the shim, before any device work): with the reference's log knobs set the
+// one refused call (alpha = 2 is refused in the shim, before any device work): with the reference's log knobs set the
 // caller sees one line for it on stderr, without them none
 static int log_line_only() {
   matmul_params p;
@@ -670,7 +696,7 @@ static int log_line_only() {
   matmul_batch_params_t bp;
   int8_t a[8] = {0}, w[8] = {0};
   uint16_t d[4] = {0};
-  status_t st = matmul_direct('r', true, false, 2, 2, 4, 1.0f, a, 4, w, 2, nullptr, 0.0f, d, 2, true, bp, p);
+  status_t st = matmul_direct('r', true, false, 2, 2, 4, 2.0f, a, 4, w, 2, nullptr, 0.0f, d, 2, true, bp, p);   // alpha = 2: refused in the shim
   return st == status_t::success ? 1 : 0;
 }
 
@@ -685,6 +711,7 @@ int main(int argc, char **argv) {
   RUN(test_bf16_matmul_direct());
   RUN(test_normalization_direct());
   RUN(test_group_matmul_sequential_chain());
+  RUN(test_int8_transposed_source());
   RUN(test_reorder_and_prepack());
   RUN(test_fused_moe_vs_two_call(false, false, false));
   RUN(test_fused_moe_vs_two_call(true, true, false));

@@ -33,7 +33,6 @@ def test_parse_defaults_comments_and_pipeline():
     ("128, 256, 64, 1, bf16:s4:bf16, true, f32, , , x, true, false, false, 1.0, 0.0, per-group, 128, bf16", "weights s4"),
     ("128, 256, 64, 1, bf16:s8:bf16, false, f32, , , x, true, false, false, 1.0, 0.0, per-channel, , f32, 0, true, per-group, 128, bf16",
      "per-group source"),
-    ("128, 256, 64, 1, u8:s8:bf16, false, f32, , , x, true, true, false", "transposed source"),
     ("128, 256, 64, 1, u8:s8:bf16, false, f32, , , x, true, false, false, 2.0, 0.0", "alpha"),
     ("128, 256, 64, 1, bf16:s8:bf16", "without src_dynamic_quant"),
 ])
@@ -81,11 +80,14 @@ def test_matmul_lines_compute_what_the_oracle_computes(oracle):
              "64, 256, 128, 2, s8:s8:f32, false, f32, binary_add, , , true, false, true",
              "64, 256, 128:64, 2, bf16:s8:bf16, true, f32, gelu_tanh, , , true, false, true, 1.0, 0.0, per-channel, , f32, 0, true, per-token"]
     lines.append("70, 256, 128:64, 2, bf16:bf16:bf16, true, f32, gelu_tanh")
+    lines.append("96, 256, 128, 2, u8:s8:bf16, true, f32, relu, , , true, true, false")           # transposed source
     for line in lines:
         cfg, cap = B.parse_line(line), {}
         total, status = B.run_config(cfg, capture=cap)
         assert status == "success" and total > 0, (line, status)
         src = _u16(cap["x"])
+        if cfg["transA"]:
+            src = np.ascontiguousarray(src.T)
         for li, L in enumerate(cap["layers"]):
             w = L["w"].T if cfg["transB"] else L["w"]
             if cfg["wdt"] == "bf16":

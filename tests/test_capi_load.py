@@ -36,7 +36,7 @@ def test_struct_layout_matches_header():
     from zendnn_b200 import capi
     assert ctypes.sizeof(capi.Quant) == 24
     assert ctypes.sizeof(capi.PostOp) == 32
-    assert ctypes.sizeof(capi.MatmulDesc) == 4 * 8 + 3 * 8 + 4 * 8 + 4 * 4 + 3 * 24 + 8 * 32 + 8 + 3 * 24
+    assert ctypes.sizeof(capi.MatmulDesc) == 4 * 8 + 3 * 8 + 4 * 8 + 4 * 4 + 3 * 24 + 8 * 32 + 8 + 3 * 24 + 8
     assert ctypes.sizeof(capi.MoeExpert) == 136
 
 

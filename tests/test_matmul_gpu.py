@@ -641,3 +641,29 @@ def test_requantised_destination_contract(capi):
     d = capi.make_matmul(M, N, K, A, W, out, src_dt=capi.DT["s8"], dst_dt=capi.DT["s8"], weights_const=False,
                          dst_zp=np.zeros(1, dtype=np.int32))
     assert capi.matmul(d) == capi.UNIMPLEMENTED
+
+
+def test_transposed_source(capi, oracle):
+    """matmul_direct's transA: a source stored [K, lda] (element (m, k) at k * lda + m) gives the bytes of the untransposed
+    call, on the INT8 path (u8 with a zero point, decode-sized and prefill-sized M) and on the bf16 path."""
+    rng = np.random.default_rng(91)
+    for M, K, N in [(4, 256, 136), (150, 328, 200)]:
+        lda_t = M + 5
+        A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+        At = np.zeros((K, lda_t), dtype=np.uint8); At[:, :M] = A.T
+        W = rng.integers(-128, 128, (K, N), dtype=np.int8)
+        ws = rng.uniform(0.002, 0.01, N).astype(np.float32)
+        ss, zp = np.array([0.02], dtype=np.float32), np.array([128], dtype=np.int32)
+        ref = run(capi, M, N, K, A, W, "bf16", weights_const=False, src_scale=ss, wei_scale=ws, src_zp=zp)
+        got = run(capi, M, N, K, At, W, "bf16", weights_const=False, src_scale=ss, wei_scale=ws, src_zp=zp, transA=True, lda=lda_t,
+                  src_dt=capi.DT["u8"])
+        assert (got == ref).all(), (M, K, N)
+        X = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+        Xt = np.zeros((K, lda_t), dtype=np.uint16); Xt[:, :M] = X.T
+        Wb = oracle.f32_to_bf16((rng.standard_normal((K, N)) * 0.05).astype(np.float32))
+        bf = capi.DT["bf16"]
+        o0, o1 = np.zeros((M, N), dtype=np.uint16), np.zeros((M, N), dtype=np.uint16)
+        assert capi.matmul(capi.make_matmul(M, N, K, X, Wb, o0, src_dt=bf, wei_dt=bf, dst_dt=bf, weights_const=False)) == capi.SUCCESS
+        assert capi.matmul(capi.make_matmul(M, N, K, Xt, Wb, o1, src_dt=bf, wei_dt=bf, dst_dt=bf, weights_const=False, transA=True,
+                                            lda=lda_t)) == capi.SUCCESS, capi.last_error()
+        assert (o0 == o1).all() and o0.any()

@@ -14,7 +14,7 @@ src_scale_granularity, src_group_size, src_scale_dt.  Lines starting with '#' an
 What runs: the INT8 path of matmul_direct (u8|s8 source with static per-tensor scale and zero point, or bf16|f32
 source with src_dynamic_quant and per-token or per-tensor scales; s8 weights with per-channel or per-tensor scales;
 bf16|f32|s32 destination) and the bf16 x bf16 path (bf16:bf16:bf16|f32, no quantisation).  Everything else (f32
-weights, s4 weights, per-group scales, transposed source,
+weights, s4 weights, per-group scales,
 alpha/beta other than 1/0, batched lines) is reported as `unimplemented`, which is the status the library returns
 for it.  Multi-layer lines (n = a:b:c) run as a pipeline: layer i+1 consumes the bf16 output of layer i.
 `--cache_mode=warm` rotates over `--num_weight_buffers` weight copies (default: enough to exceed the L2 size), `hot`
@@ -128,8 +128,6 @@ def unsupported_reason(cfg):
         return "destination %s" % cfg["ddt"]
     if cfg["wgran"] == "per-group":
         return "per-group weight scales"
-    if cfg["transA"]:
-        return "transposed source"
     if cfg["alpha"] != 1.0 or cfg["beta"] != 0.0:
         return "alpha/beta other than 1/0"
     known = {"relu", "gelu_tanh", "gelu_erf", "sigmoid", "swish", "tanh", "elu", "leaky_relu", "binary_add", "binary_mul"}
@@ -212,6 +210,9 @@ def run_config(cfg, cache_mode="hot", num_weight_buffers=0, capture=None):
     sscale = torch.tensor([0.02], device=dev)
     szp = torch.tensor([128], dtype=torch.int32, device=dev) if cfg["sdt"] == "u8" else None
 
+    if cfg["transA"]:
+        x = x.t().contiguous()                     # stored [K, M]: element (m, k) at k * M + m
+
     def descs(it):
         ds, src, src_dt = [], x, cfg["sdt"]
         for li, L in enumerate(layers):
@@ -227,7 +228,7 @@ def run_config(cfg, cache_mode="hot", num_weight_buffers=0, capture=None):
                 if szp is not None:
                     kw["src_zp"] = szp
             ds.append(capi.make_matmul(M, L["n"], L["k"], src, w, L["out"], src_dt=capi.DT[src_dt], dst_dt=capi.DT[L["ddt"]],
-                                       transB=cfg["transB"], bias=L["bias"], weights_const=cfg["is_weights_const"],
+                                       transB=cfg["transB"], transA=bool(cfg["transA"]) and li == 0, bias=L["bias"], weights_const=cfg["is_weights_const"],
                                        dynamic_quant=dyn, wei_scale=None if wbf16 else L["wscale"], postops=L["pos"], **kw))
             src, src_dt = L["out"], "bf16"
         return ds

@@ -40,7 +40,7 @@ class MatmulDesc(C.Structure):
                 ("src_scale", Quant), ("wei_scale", Quant), ("src_zp", Quant),
                 ("postops", PostOp * MAX_POSTOPS),
                 ("force_kernel", C.c_int32), ("flags", C.c_int32),
-                ("dst_scale", Quant), ("dst_zp", Quant), ("wei_zp", Quant)]
+                ("dst_scale", Quant), ("dst_zp", Quant), ("wei_zp", Quant), ("transA", C.c_int32), ("reserved_a", C.c_int32)]
 
 FLAG_STABLE_WEIGHTS = 1
 
@@ -196,12 +196,13 @@ def quant(buf, count=None, dt=None):
 def make_matmul(M, N, K, src, weight, dst, *, src_dt, dst_dt, lda=None, ldb=None, ldc=None, transB=False,
                 bias=None, bias_dt=None, wei_format="n", weights_const=True, dynamic_quant=False,
                 src_scale=None, wei_scale=None, src_zp=None, postops=(), force_kernel=0, flags=0, wei_dt=None,
-                dst_scale=None, dst_zp=None, wei_zp=None):
+                dst_scale=None, dst_zp=None, wei_zp=None, transA=False):
     d = MatmulDesc()
     d.M, d.N, d.K, d.transB = M, N, K, int(transB)
+    d.transA = int(transA)
     d.src_dt, d.wei_dt, d.dst_dt = src_dt, (DT["s8"] if wei_dt is None else wei_dt), dst_dt
     d.bias_dt = bias_dt if bias_dt is not None else (dt_of(bias) if bias is not None else 0)
-    d.lda = lda if lda is not None else K
+    d.lda = lda if lda is not None else (M if transA else K)
     d.ldb = ldb if ldb is not None else (K if transB else N)
     d.ldc = ldc if ldc is not None else N
     d.src, d.weight, d.bias, d.dst = ptr(src), ptr(weight), ptr(bias), ptr(dst)

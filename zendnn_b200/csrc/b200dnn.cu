@@ -617,6 +617,48 @@ int32_t fill_epi(const b200dnn_matmul_t *d, EpiParams *e) {
 
 }  // namespace
 
+namespace {
+// matmul_direct's transA: the source arrives as [K, lda] (element (m, k) at k * lda + m) and is transposed into the
+// workspace as [M, pitch]; 32 x 32 tiles through shared memory, elements of 1, 2 or 4 bytes.
+template <typename T>
+__global__ void transpose_src_kernel(const T *src, int64_t lda, int M, int K, T *dst, int64_t pitch) {
+  __shared__ T tile[32][33];
+  const int k0 = blockIdx.y * 32, m0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int k = k0 + r, m = m0 + threadIdx.x;
+    if (k < K && m < M) tile[r][threadIdx.x] = src[(int64_t)k * lda + m];
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int m = m0 + r, k = k0 + threadIdx.x;
+    if (m < M && k < K) dst[(int64_t)m * pitch + k] = tile[threadIdx.x][r];
+  }
+}
+
+int32_t untranspose_source(const b200dnn_matmul_t *d, b200dnn_matmul_t *t, cudaStream_t st) {
+  const int M = d->M, K = d->K;
+  B2_CHECK(d->src && M > 0 && K > 0, B200DNN_FAILURE, "null src or non-positive dimension");
+  B2_CHECK(d->lda >= M, B200DNN_FAILURE, "transA: lda smaller than M");
+  const size_t esz = dt_size(d->src_dt);
+  B2_CHECK(esz == 1 || esz == 2 || esz == 4, B200DNN_UNIMPLEMENTED, "transA: source dtype %d", d->src_dt);
+  const void *src = nullptr;
+  B2_TRY(stage_in(d->src, span_bytes(K, M, d->lda, d->src_dt), st, &src));
+  const int64_t pitch = round_up(K, (int64_t)(16 / esz));
+  void *buf = rt().ws.alloc((size_t)M * pitch * esz);
+  B2_CHECK(buf, B200DNN_FAILURE, "workspace allocation failed");
+  if (pitch != K) B2_CUDA(cudaMemsetAsync(buf, 0, (size_t)M * pitch * esz, st));
+  dim3 grid((unsigned)((M + 31) / 32), (unsigned)((K + 31) / 32)), block(32, 8);
+  if (esz == 1) transpose_src_kernel<uint8_t><<<grid, block, 0, st>>>((const uint8_t *)src, d->lda, M, K, (uint8_t *)buf, pitch);
+  else if (esz == 2) transpose_src_kernel<uint16_t><<<grid, block, 0, st>>>((const uint16_t *)src, d->lda, M, K, (uint16_t *)buf, pitch);
+  else transpose_src_kernel<uint32_t><<<grid, block, 0, st>>>((const uint32_t *)src, d->lda, M, K, (uint32_t *)buf, pitch);
+  B2_LAUNCHED();
+  B2_CUDA(cudaGetLastError());
+  *t = *d;
+  t->transA = 0; t->src = buf; t->lda = pitch;
+  return B200DNN_SUCCESS;
+}
+}  // namespace
+
 #include "gs_api.cuh"
 #include "bf16_api.cuh"
 #include "woq_api.cuh"
@@ -951,6 +993,8 @@ int32_t b200dnn_moe_route(const float *logits, int32_t T, int32_t E, int32_t top
 int32_t b200dnn_matmul(const b200dnn_matmul_t *d, void *stream) {
   B2_CHECK(d, B200DNN_FAILURE, "null descriptor");
   B2_ENTER(stream);
+  b200dnn_matmul_t untransposed;
+  if (d->transA) { B2_TRY(untranspose_source(d, &untransposed, st)); d = &untransposed; }
   if (is_woq_matmul(d)) return matmul_woq(d, st);               // bf16 source x s4|u4 weights, no dynamic quantisation
   if (is_group_scaled(d)) return matmul_group_scaled(d, st);   // per-group scales and W4A8: own validation and kernel
   if (is_bf16_matmul(d)) return matmul_bf16(d, st);             // bf16 x bf16: own validation, the kernel's bf16 form

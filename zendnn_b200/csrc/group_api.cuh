@@ -23,6 +23,7 @@ bool group_is_uniform(int G, const b200dnn_matmul_t *d) {
       if (bias_dt && x.bias_dt != bias_dt) return false;
       bias_dt = x.bias_dt;
     }
+    if (x.transA) return false;             // transposed sources go through b200dnn_matmul one by one
     if (x.K != f->K || x.N != f->N || x.transB != f->transB || x.wei_format != f->wei_format || x.src_dt != f->src_dt ||
         x.wei_dt != f->wei_dt || x.dst_dt != f->dst_dt || x.dynamic_quant != f->dynamic_quant ||
         x.weights_const != f->weights_const || x.n_postops != f->n_postops || x.force_kernel != 0)
@@ -170,6 +171,7 @@ bool group_is_uniform_bf16(int G, const b200dnn_matmul_t *d) {
       if (bias_dt && x.bias_dt != bias_dt) return false;
       bias_dt = x.bias_dt;
     }
+    if (x.transA) return false;
     if (x.K != f->K || x.N != f->N || x.transB != f->transB || x.dst_dt != f->dst_dt || x.weights_const != f->weights_const ||
         x.n_postops != f->n_postops || x.force_kernel != 0 || (x.wei_format != 'n' && x.wei_format != 0))
       return false;

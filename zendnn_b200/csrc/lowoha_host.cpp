@@ -102,7 +102,6 @@ status_t flatten(const char layout, const bool transA, const bool transB, const 
                  const float beta, void *dst, const int ldc, const bool is_weights_const,
                  const matmul_batch_params_t &bp, const matmul_params &p, b200dnn_matmul_t *d) {
   if (layout != 'r' && layout != 'R') return shim_fail(status_t::unimplemented, "only row-major layout is implemented");
-  if (transA) return shim_fail(status_t::unimplemented, "transA is not implemented");
   if (bp.Batch_A != 1 || bp.Batch_B != 1) return shim_fail(status_t::unimplemented, "batched matmul is not implemented");
   if (alpha != 1.0f || beta != 0.0f) return shim_fail(status_t::unimplemented, "only alpha = 1, beta = 0 is implemented");
   if (p.packing.pack_format_b != 0) return shim_fail(status_t::unimplemented, "GGML-packed weights are not implemented");
@@ -121,7 +120,7 @@ status_t flatten(const char layout, const bool transA, const bool transB, const 
     if (p.quant_params.src_scale.dims.size() != 2) return shim_fail(status_t::failure, "W4A8 requires source scale dims {1,1}, {M,1}, or {M,G}");
   }
   std::memset(d, 0, sizeof *d);
-  d->M = M; d->N = N; d->K = K; d->transB = transB ? 1 : 0;
+  d->M = M; d->N = N; d->K = K; d->transB = transB ? 1 : 0; d->transA = transA ? 1 : 0;
   d->src_dt = static_cast<int32_t>(p.dtypes.src); d->wei_dt = static_cast<int32_t>(p.dtypes.wei);
   d->dst_dt = static_cast<int32_t>(p.dtypes.dst); d->bias_dt = static_cast<int32_t>(p.dtypes.bias);
   d->lda = lda; d->ldb = ldb; d->ldc = ldc;

@@ -113,6 +113,7 @@ extern "C" int32_t b200dnn_matmul_static_scratch(const b200dnn_matmul_t *d, void
   const int M = d->M, N = d->N, K = d->K;
   // the contract of b200dnn_matmul, then what this entry point leaves out
   B2_TRY(validate_matmul_desc(d));
+  B2_CHECK(!d->transA, B200DNN_UNIMPLEMENTED, "a transposed source needs a workspace pass: use b200dnn_matmul");
   B2_CHECK(d->dst_dt != B200DNN_S8 && d->dst_dt != B200DNN_U8, B200DNN_UNIMPLEMENTED,
            "requantised s8/u8 destinations need a workspace pass: use b200dnn_matmul");
   B2_CHECK(d->wei_format == 'r', B200DNN_UNIMPLEMENTED, "static-scratch matmul takes a prepacked weight (mem_format_b='r') only");
