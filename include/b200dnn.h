@@ -400,6 +400,22 @@ typedef struct b200dnn_norm_t {
 } b200dnn_norm_t;
 B200DNN_API int32_t b200dnn_normalization(const b200dnn_norm_t *desc, void *stream);
 
+/* ---- sdpa_direct (lowoha_operators/sdpa/lowoha_sdpa.hpp:48-55, sdpa_params in lowoha_sdpa_common.hpp:57-103):
+ * output = softmax(Q K^T * scale + mask) V per (batch, head); bf16 tensors with [batch, head, seq, dim] strides (dim stride
+ * 1), optional additive mask (f32 | bf16, 2-D [seq, kv] or 4-D broadcastable), causal masking (key j > query i), scale 0 =
+ * 1/sqrt(head_dim).  Computed in the form of the reference's BMM backend (scores, softmax, P V as three steps per head). ---- */
+typedef struct b200dnn_sdpa_t {
+  int64_t batch, num_heads, seq_len, kv_seq_len, head_dim;
+  int64_t q_stride[4], k_stride[4], v_stride[4], o_stride[4];   /* elements, order b, h, s, d */
+  int32_t mask_ndims; int32_t is_causal;
+  int64_t mask_sizes[4], mask_strides[4];                        /* the first mask_ndims entries */
+  int32_t qkv_dt, out_dt, mask_dt; int32_t reserved;
+  double scale, dropout_p;
+  const void *query, *key, *value, *attn_mask;
+  void *output;
+} b200dnn_sdpa_t;
+B200DNN_API int32_t b200dnn_sdpa(const b200dnn_sdpa_t *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -685,6 +685,30 @@ def ref2_normalization(kind, x, gamma=None, beta=None, residual=None, running_me
     return _norm_call(r.ref2_normalization, kind, x, gamma, beta, residual, running_mean, running_var, eps, dst_dt, ch)
 
 
+def sdpa(q, k, v, mask=None, scale=0.0, causal=False):
+    """softmax(Q K^T * scale + mask) V per (batch, head), the steps of the reference's BMM backend
+    (lowoha_operators/sdpa/bmm_sdpa/lowoha_sdpa_bmm.cpp): scores from the exact bf16 products (summed in double, rounded to
+    f32), scale (0: 1/sqrt(head_dim)), additive mask and causal mask (key j > query i) on the f32 scores, softmax in f32,
+    probabilities rounded to bf16, P V summed in double, rounded to f32 and then to bf16.  q [B,H,S,D], k / v [B,H,KV,D] as
+    bf16 bits; mask f32 broadcastable to [B,H,S,KV].  Returns bf16 bits [B,H,S,D]."""
+    qf, kf, vf = (bf16_to_f32(a).astype(np.float64) for a in (q, k, v))
+    B, H, S, D = qf.shape
+    KV = kf.shape[2]
+    sc = np.float32(1.0 / np.sqrt(np.float32(D))) if scale == 0.0 else np.float32(scale)
+    s = np.einsum("bhsd,bhkd->bhsk", qf, kf).astype(np.float32) * sc
+    if mask is not None:
+        s = s + np.broadcast_to(np.asarray(mask, dtype=np.float32), s.shape)
+    if causal:
+        s = np.where(np.arange(KV)[None, :] > np.arange(S)[:, None], np.float32(-np.inf), s)
+    m = s.max(axis=-1, keepdims=True)
+    m = np.where(np.isfinite(m), m, np.float32(0))
+    e = np.exp((s - m).astype(np.float32)).astype(np.float32)
+    tot = e.sum(axis=-1, keepdims=True, dtype=np.float32)
+    p = np.where(tot > 0, e / np.where(tot > 0, tot, 1), 0).astype(np.float32)
+    pb = bf16_to_f32(f32_to_bf16(p)).astype(np.float64)
+    return f32_to_bf16(np.einsum("bhsk,bhkd->bhsd", pb, vf).astype(np.float32))
+
+
 def ref_int8_matmul(A_u8, B_s8, src_zp, src_scale, wei_scale, bias=None, fused_op=0, dst_dt="bf16"):
     """Runs the compiled reference tile kernel (per-tensor src scale/zp).  None if unavailable."""
     r = ref_lib()

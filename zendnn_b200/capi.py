@@ -67,6 +67,15 @@ class NormDesc(C.Structure):
 NORM = dict(layer_norm=0, batch_norm=1, rms_norm=2, fused_add_rms_norm=3)
 
 
+class SdpaDesc(C.Structure):
+    _fields_ = [("batch", C.c_int64), ("num_heads", C.c_int64), ("seq_len", C.c_int64), ("kv_seq_len", C.c_int64), ("head_dim", C.c_int64),
+                ("q_stride", C.c_int64 * 4), ("k_stride", C.c_int64 * 4), ("v_stride", C.c_int64 * 4), ("o_stride", C.c_int64 * 4),
+                ("mask_ndims", C.c_int32), ("is_causal", C.c_int32), ("mask_sizes", C.c_int64 * 4), ("mask_strides", C.c_int64 * 4),
+                ("qkv_dt", C.c_int32), ("out_dt", C.c_int32), ("mask_dt", C.c_int32), ("reserved", C.c_int32),
+                ("scale", C.c_double), ("dropout_p", C.c_double),
+                ("query", C.c_void_p), ("key", C.c_void_p), ("value", C.c_void_p), ("attn_mask", C.c_void_p), ("output", C.c_void_p)]
+
+
 class EpConfig(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("num_experts", C.c_int32), ("num_shared", C.c_int32),
                 ("topk", C.c_int32), ("max_tokens", C.c_int32), ("K", C.c_int32), ("I", C.c_int32), ("H", C.c_int32),
@@ -86,7 +95,7 @@ EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b20
            "b200dnn_moe_weighted_reduce_rows", "b200dnn_ep_create", "b200dnn_ep_destroy", "b200dnn_ep_local_expert_count",
            "b200dnn_ep_set_experts", "b200dnn_ep_nccl_unique_id", "b200dnn_ep_connect_nccl", "b200dnn_ep_connect_local",
            "b200dnn_moe_layer_ep", "b200dnn_moe_layer_ep_local", "b200dnn_ep_rows_per_rank", "b200dnn_ep_status",
-           "b200dnn_phase_timing", "b200dnn_phase_times", "b200dnn_measure_int8_peak", "b200dnn_normalization"]
+           "b200dnn_phase_timing", "b200dnn_phase_times", "b200dnn_measure_int8_peak", "b200dnn_normalization", "b200dnn_sdpa"]
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -112,6 +121,7 @@ lib.b200dnn_gated_act.argtypes = [vp, i32, i64, i64, i64, i32, vp]
 lib.b200dnn_moe_weighted_reduce.argtypes = [vp, vp, i32, i32, i32, i32, i32, vp, i64, vp]
 lib.b200dnn_quant_per_token_asym.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, vp, vp]
 lib.b200dnn_normalization.argtypes = [C.POINTER(NormDesc), C.c_void_p]
+lib.b200dnn_sdpa.argtypes = [C.POINTER(SdpaDesc), C.c_void_p]
 lib.b200dnn_nshard_range.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64), C.POINTER(i32)]
 lib.b200dnn_nshard_create.argtypes = [i32, i32, vp, vp, C.POINTER(vp)]
 lib.b200dnn_nshard_destroy.argtypes = [vp]

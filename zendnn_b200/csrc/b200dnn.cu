@@ -1182,3 +1182,4 @@ int32_t b200dnn_clear_caches(void) {
 #include "group_api.cuh"
 #include "nshard_api.cuh"
 #include "norm_api.cuh"
+#include "sdpa_api.cuh"

@@ -52,6 +52,16 @@ __device__ __forceinline__ float norm_block_max(float v, float *sh) {
   __syncthreads();
   return r;
 }
+__device__ __forceinline__ float norm_block_max_signed(float v, float *sh) {      // values may be negative (scores)
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = sh[0];
+  for (int i = 1; i < (int)(blockDim.x >> 5); ++i) r = fmaxf(r, sh[i]);
+  __syncthreads();
+  return r;
+}
 __device__ __forceinline__ float norm_round_to(float v, int32_t dt) {
   return dt == B200DNN_BF16 ? __uint_as_float(pack_bf16x2(v, 0.0f) << 16) : v;
 }

@@ -80,6 +80,10 @@ struct Workspace {
     return p;
   }
   void release() { for (auto &b : blocks) cudaFree(b.p); blocks.clear(); }
+  // a call that repeats a sub-step (one attention head after the other) gives the sub-step's allocations back: work on one
+  // stream is ordered, so the next sub-step may write where the previous one has read
+  std::vector<size_t> mark() const { std::vector<size_t> m; for (auto &b : blocks) m.push_back(b.used); return m; }
+  void restore(const std::vector<size_t> &m) { for (size_t i = 0; i < blocks.size(); ++i) blocks[i].used = i < m.size() ? m[i] : 0; }
 };
 
 struct PackedWeight {
