@@ -164,6 +164,36 @@ ZENDNNL_B200_API status_t normalization_direct(const void *input, void *output, 
                                                norm_params &params);
 }  // namespace normalization
 
+// ------------------------------------------------------------------------------------------ sdpa
+// Mirrors lowoha_operators/sdpa/lowoha_sdpa_common.hpp:31-103 (field order and defaults) and lowoha_sdpa.hpp:48-55.
+namespace sdpa {
+using zendnnl::memory::data_type_t;
+using zendnnl::memory::status_t;
+
+enum class mask_type_t { none = 0, causal = 1, custom = 2 };
+
+struct sdpa_params {
+  int64_t batch = 1, num_heads = 1, seq_len = 0, kv_seq_len = 0, head_dim = 0;
+  int64_t q_stride_b = 0, q_stride_h = 0, q_stride_s = 0, q_stride_d = 1;
+  int64_t k_stride_b = 0, k_stride_h = 0, k_stride_s = 0, k_stride_d = 1;
+  int64_t v_stride_b = 0, v_stride_h = 0, v_stride_s = 0, v_stride_d = 1;
+  int64_t o_stride_b = 0, o_stride_h = 0, o_stride_s = 0, o_stride_d = 1;
+  int mask_ndims = 0;
+  int64_t mask_sizes[4] = {0, 0, 0, 0};
+  int64_t mask_strides[4] = {0, 0, 0, 0};
+  mask_type_t mask_type = mask_type_t::none;
+  int64_t mask_dims[3] = {0, 0, 0};
+  data_type_t qkv_dt = data_type_t::none, out_dt = data_type_t::none, mask_dt = data_type_t::none;
+  double scale = 0.0;
+  bool is_causal = false;
+  double dropout_p = 0.0;
+  int32_t num_threads = 0;
+};
+
+ZENDNNL_B200_API status_t sdpa_direct(const void *query, const void *key, const void *value, const void *attn_mask, void *output,
+                                      sdpa_params &params);
+}  // namespace sdpa
+
 // ------------------------------------------------------------------------------------------ matmul
 namespace matmul {
 using namespace zendnnl::memory;

@@ -322,6 +322,47 @@ static void test_int8_transposed_source() {
   CHECK(st == status_t::failure, "transA with lda < M must fail");
 }
 
+// sdpa_direct: causal self-attention on contiguous [batch, heads, seq, dim] bf16 tensors against a scalar softmax attention
+static void test_sdpa_direct() {
+  using namespace zendnnl::lowoha::sdpa;
+  Rng r(18);
+  const int B = 2, H = 2, S = 40, D = 32;
+  const size_t n = (size_t)B * H * S * D;
+  std::vector<uint16_t> Q(n), K(n), V(n), O(n, 0);
+  for (auto &v : Q) v = f2bf(r.rn());
+  for (auto &v : K) v = f2bf(r.rn());
+  for (auto &v : V) v = f2bf(r.rn());
+  sdpa_params p;
+  p.batch = B; p.num_heads = H; p.seq_len = S; p.kv_seq_len = S; p.head_dim = D;
+  p.q_stride_b = p.k_stride_b = p.v_stride_b = p.o_stride_b = (int64_t)H * S * D;
+  p.q_stride_h = p.k_stride_h = p.v_stride_h = p.o_stride_h = (int64_t)S * D;
+  p.q_stride_s = p.k_stride_s = p.v_stride_s = p.o_stride_s = D;
+  p.qkv_dt = data_type_t::bf16; p.out_dt = data_type_t::bf16; p.is_causal = true;
+  status_t st = sdpa_direct(Q.data(), K.data(), V.data(), nullptr, O.data(), p);
+  CHECK(st == status_t::success, "sdpa_direct: %s", last_error());
+  double worst = 0.0;
+  const float scale = 1.0f / std::sqrt((float)D);
+  for (int bh = 0; bh < B * H; ++bh)
+    for (int i = 0; i < S; ++i) {
+      std::vector<double> pr(i + 1);
+      double mx = -1e30, sum = 0.0;
+      for (int j = 0; j <= i; ++j) {
+        double s = 0.0;
+        for (int c = 0; c < D; ++c) s += (double)bf2f(Q[((size_t)bh * S + i) * D + c]) * (double)bf2f(K[((size_t)bh * S + j) * D + c]);
+        pr[j] = s * scale; mx = std::max(mx, pr[j]);
+      }
+      for (int j = 0; j <= i; ++j) { pr[j] = std::exp(pr[j] - mx); sum += pr[j]; }
+      for (int c = 0; c < D; ++c) {
+        double o = 0.0;
+        for (int j = 0; j <= i; ++j) o += pr[j] / sum * (double)bf2f(V[((size_t)bh * S + j) * D + c]);
+        worst = std::max(worst, std::fabs(o - (double)bf2f(O[((size_t)bh * S + i) * D + c])));
+      }
+    }
+  CHECK(worst < 0.03, "sdpa_direct: largest absolute difference %.4f", worst);
+  p.dropout_p = 0.5;
+  CHECK(sdpa_direct(Q.data(), K.data(), V.data(), nullptr, O.data(), p) == status_t::failure, "dropout must fail");
+}
+
 // INT8 with a quantised u8 / s8 output tensor: dst_scale and dst_zp close the epilogue chain
 // (backends/aocl/aocl_postop.cpp:1421-1448), clamp and nearbyint as operators/matmul/matmul_ref_kernel.cpp:155-192
 static void test_int8_requantised_dst() {
@@ -712,6 +753,7 @@ int main(int argc, char **argv) {
   RUN(test_normalization_direct());
   RUN(test_group_matmul_sequential_chain());
   RUN(test_int8_transposed_source());
+  RUN(test_sdpa_direct());
   RUN(test_reorder_and_prepack());
   RUN(test_fused_moe_vs_two_call(false, false, false));
   RUN(test_fused_moe_vs_two_call(true, true, false));

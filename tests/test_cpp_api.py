@@ -28,7 +28,7 @@ def test_cpp_caller_compiles_and_links():
     syms = subprocess.check_output(["nm", "-DC", os.path.join(PKG, "libzendnnl_b200.so")], text=True)
     for name in ("zendnnl::lowoha::matmul::matmul_direct(", "zendnnl::lowoha::matmul::group_matmul_direct(",
                  "zendnnl::lowoha::reorder::reorder_direct(", "zendnnl::lowoha::reorder::weight_prepack_size(",
-                 "zendnnl::lowoha::reorder::group_dynamic_quant(", "zendnnl::lowoha::normalization::normalization_direct("):
+                 "zendnnl::lowoha::reorder::group_dynamic_quant(", "zendnnl::lowoha::normalization::normalization_direct(", "zendnnl::lowoha::sdpa::sdpa_direct("):
         assert name in syms, name
 
 

@@ -70,6 +70,23 @@ def test_plain_and_causal(capi, oracle, shape, causal):
     close(oracle, out, oracle.sdpa(q, k, v, causal=causal), v, (shape, causal))
 
 
+def test_head_by_head_form_on_contiguous_tensors(capi, oracle, monkeypatch):
+    """Contiguous [batch, head, seq, dim] tensors take the grouped launches; the head-by-head form must give the same answer
+    (to the tolerance), here with a 4-D mask and the causal mask together."""
+    monkeypatch.setenv("B200DNN_SDPA_GROUPED", "0")
+    rng = np.random.default_rng(8)
+    B, H, S, KV, D = 2, 2, 130, 130, 64
+    q, k, v = make(oracle, rng, B, H, S, KV, D)
+    m4 = rng.standard_normal((B, H, S, KV)).astype(np.float32)
+    st, out = run(capi, q, k, v, mask=m4, causal=True)
+    assert st == capi.SUCCESS, capi.last_error()
+    close(oracle, out, oracle.sdpa(q, k, v, m4, causal=True), v, "head by head")
+    monkeypatch.setenv("B200DNN_SDPA_GROUPED", "1")
+    st, out2 = run(capi, q, k, v, mask=m4, causal=True)
+    assert st == capi.SUCCESS, capi.last_error()
+    close(oracle, out2, oracle.sdpa(q, k, v, m4, causal=True), v, "grouped")
+
+
 def test_masks_scale_and_strides(capi, oracle):
     rng = np.random.default_rng(5)
     B, H, S, KV, D = 2, 3, 70, 90, 64

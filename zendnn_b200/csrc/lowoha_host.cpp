@@ -542,3 +542,25 @@ status_t normalization_direct(const void *input, void *output, const void *gamma
 }
 
 }}}  // namespace zendnnl::lowoha::normalization
+
+// ------------------------------------------------------------------------------------------------ sdpa
+namespace zendnnl { namespace lowoha { namespace sdpa {
+
+status_t sdpa_direct(const void *query, const void *key, const void *value, const void *attn_mask, void *output, sdpa_params &p) {
+  b200dnn_sdpa_t d;
+  std::memset(&d, 0, sizeof d);
+  d.batch = p.batch; d.num_heads = p.num_heads; d.seq_len = p.seq_len; d.kv_seq_len = p.kv_seq_len; d.head_dim = p.head_dim;
+  const int64_t qs[4] = {p.q_stride_b, p.q_stride_h, p.q_stride_s, p.q_stride_d}, ks[4] = {p.k_stride_b, p.k_stride_h, p.k_stride_s, p.k_stride_d};
+  const int64_t vs[4] = {p.v_stride_b, p.v_stride_h, p.v_stride_s, p.v_stride_d}, os[4] = {p.o_stride_b, p.o_stride_h, p.o_stride_s, p.o_stride_d};
+  for (int i = 0; i < 4; ++i) {
+    d.q_stride[i] = qs[i]; d.k_stride[i] = ks[i]; d.v_stride[i] = vs[i]; d.o_stride[i] = os[i];
+    d.mask_sizes[i] = p.mask_sizes[i]; d.mask_strides[i] = p.mask_strides[i];
+  }
+  d.mask_ndims = p.mask_ndims; d.is_causal = p.is_causal ? 1 : 0;
+  d.qkv_dt = static_cast<int32_t>(p.qkv_dt); d.out_dt = static_cast<int32_t>(p.out_dt); d.mask_dt = static_cast<int32_t>(p.mask_dt);
+  d.scale = p.scale; d.dropout_p = p.dropout_p;
+  d.query = query; d.key = key; d.value = value; d.attn_mask = attn_mask; d.output = output;
+  return from_c(b200dnn_sdpa(&d, g_stream));
+}
+
+}}}  // namespace zendnnl::lowoha::sdpa

@@ -98,8 +98,8 @@ static __global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t *W
 // bf16 weight into the same byte layout (a packed row holds 2*K bytes of K, zero-padded to Kp bytes): the tcgen05
 // kernel's bf16 form reads the same [BN rows x 128 B] boxes, 64 elements of K each.
 // grid: (Kp/128, Np/32); block 256.  Each CTA moves a [64 k][32 n] tile of 2-byte elements through shared memory.
-static __global__ void __launch_bounds__(256) pack_weight_bf16_kernel(const uint16_t *W, int64_t ldb, int transB, int64_t K, int64_t N,
-                                                               int64_t Kp, int gated, int64_t I, uint8_t *Wt) {
+static __device__ __forceinline__ void pack_weight_bf16_tile(const uint16_t *W, int64_t ldb, int transB, int64_t K, int64_t N,
+                                                             int64_t Kp, int gated, int64_t I, uint8_t *Wt) {
   __shared__ uint16_t tile[32][64 + 2];
   const int64_t k0 = (int64_t)blockIdx.x * 64, pn0 = (int64_t)blockIdx.y * 32;
   const int64_t n0 = packed_to_logical(pn0, gated, I);
@@ -124,6 +124,20 @@ static __global__ void __launch_bounds__(256) pack_weight_bf16_kernel(const uint
     const uint32_t v = (uint32_t)tile[nn][2 * k2] | ((uint32_t)tile[nn][2 * k2 + 1] << 16);
     *reinterpret_cast<uint32_t *>(Wt + wt_offset(pn0 + nn, (k0 + 2 * k2) * 2, Kp)) = v;
   }
+}
+
+static __global__ void __launch_bounds__(256) pack_weight_bf16_kernel(const uint16_t *W, int64_t ldb, int transB, int64_t K, int64_t N,
+                                                               int64_t Kp, int gated, int64_t I, uint8_t *Wt) {
+  pack_weight_bf16_tile(W, ldb, transB, K, N, Kp, gated, I, Wt);
+}
+// many matrices of one shape in one launch (the K or V blocks of attention heads): matrix z = (b, h) starts at
+// W + b * stride_b + h * stride_h and is packed to Wt + z * pack_stride.  grid: (Kp/128, Np/32, matrices)
+static __global__ void __launch_bounds__(256) pack_weight_bf16_batched_kernel(const uint16_t *W, int64_t stride_b, int64_t stride_h, int heads,
+                                                                       int first, int64_t ldb, int transB, int64_t K, int64_t N,
+                                                                       int64_t Kp, uint8_t *Wt, size_t pack_stride) {
+  const int z = first + (int)blockIdx.z;
+  pack_weight_bf16_tile(W + (int64_t)(z / heads) * stride_b + (int64_t)(z % heads) * stride_h, ldb, transB, K, N, Kp, 0, 0,
+                        Wt + (size_t)blockIdx.z * pack_stride);
 }
 
 // one warp per packed row

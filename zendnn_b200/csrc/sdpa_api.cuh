@@ -7,32 +7,38 @@
 //   P           = softmax(S * scale + mask) over kv, f32, rounded to bf16; causal: key j > query i is masked
 //   O_bh        = P V_bh               bf16 x bf16 -> out_dt
 // scale == 0 means 1 / sqrt(head_dim) (bmm_sdpa/lowoha_sdpa_utils.cpp:25-27).  A row whose keys are all masked gives zeros.
-// Not a flash kernel: the scores make a round trip through HBM (seq * kv * 6 bytes per head), five launches per head.
+// Not a flash kernel: the scores make a round trip through HBM (seq * kv * 6 bytes per head).  Tensors whose query rows
+// follow each other at one pitch over all heads ([batch, head, seq, dim] storage) take five launches for all heads (K and V
+// of every head into the tile layout, two grouped products, one softmax); other layouts go head by head.
 // Included at the end of b200dnn.cu.
 #pragma once
 
 namespace {
 
 struct SoftmaxArgs {
-  const float *S; int64_t lds;
+  const float *S; int64_t lds;          // scores of the heads of this launch back to back: row r = head * seq + i
   uint16_t *P; int64_t ldp;
   int seq, kv;
   float scale;
   int causal;
-  const void *mask; int32_t mask_dt; int64_t mask_row_stride;     // mask row i at mask + i * row_stride (0: broadcast over rows)
+  // mask element (b, h, i, j) at mask + b * mb + h * mh + i * mi + j (a stride of 0 broadcasts); head0: first (b * H + h) of the launch
+  const void *mask; int32_t mask_dt; int64_t mb, mh, mi; int heads, head0;
 };
 
 // one CTA per query row
 __global__ void __launch_bounds__(256) sdpa_softmax_kernel(const SoftmaxArgs a) {
   __shared__ float sh[8];
-  const int i = blockIdx.x;
-  const float *s = a.S + (int64_t)i * a.lds;
-  uint16_t *p = a.P + (int64_t)i * a.ldp;
+  const int64_t r = blockIdx.x;
+  const int i = (int)(r % a.seq);
+  const int64_t bh = a.head0 + r / a.seq;
+  const float *s = a.S + r * a.lds;
+  uint16_t *p = a.P + r * a.ldp;
   const int n_keys = a.causal ? min(a.kv, i + 1) : a.kv;
   const float ninf = __int_as_float(0xff800000);
+  const int64_t moff = a.mask ? (bh / a.heads) * a.mb + (bh % a.heads) * a.mh + (int64_t)i * a.mi : 0;
   auto score = [&](int j) {
     float x = __fmul_rn(s[j], a.scale);
-    if (a.mask) x = __fadd_rn(x, load_as_f32(a.mask, a.mask_dt, (int64_t)i * a.mask_row_stride + j));
+    if (a.mask) x = __fadd_rn(x, load_as_f32(a.mask, a.mask_dt, moff + j));
     return x;
   };
   float m = ninf;
@@ -103,10 +109,80 @@ extern "C" int32_t b200dnn_sdpa(const b200dnn_sdpa_t *d, void *stream) {
   B2_TRY(stage_out(d->output, (size_t)span(nq, d->o_stride) * 2, st, &o_out, true));
 
   const int64_t kvp = round_up(KV, 8);
+  const float scale = d->scale == 0.0 ? 1.0f / std::sqrt((float)D) : (float)d->scale;
+  const int64_t mb = msz[0] > 1 ? mst[0] : 0, mh = msz[1] > 1 ? mst[1] : 0, mi = msz[2] > 1 ? mst[2] : 0;
+
+  // ---- all heads at once: when the query rows of all heads follow each other at one pitch, the two products are grouped
+  // launches (one group per head, the head's K or V as its weight) and the softmax is one launch; several rounds when the
+  // scores of all heads would not fit 1.5 GB
+  const bool rows_regular = d->q_stride[1] == S * d->q_stride[2] && (B == 1 || d->q_stride[0] == H * d->q_stride[1]) &&
+                            d->q_stride[2] % 8 == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 && B * H * S < (1ll << 30);
+  if (rows_regular && env_int("B200DNN_SDPA_GROUPED", 1) != 0) {
+    const int64_t G = B * H;
+    int64_t per_round = (int64_t)((1536ll << 20) / (S * (KV * 4 + kvp * 2)));
+    per_round = per_round < 1 ? 1 : (per_round > G ? G : per_round);
+    float *Sbuf = (float *)R.ws.alloc((size_t)per_round * S * KV * 4);
+    uint16_t *Pbuf = (uint16_t *)R.ws.alloc((size_t)per_round * S * kvp * 2);
+    B2_CHECK(Sbuf && Pbuf, B200DNN_FAILURE, "workspace allocation failed");
+    const std::vector<size_t> mark = R.ws.mark();
+    for (int64_t g0 = 0; g0 < G; g0 += per_round) {
+      R.ws.restore(mark);
+      const int n = (int)(G - g0 < per_round ? G - g0 : per_round);
+      const int tile_rows = tc_tile_rows((long long)n * S, (int)(KV < D ? KV : D));
+      std::vector<int32_t> tabs(2 * (n + 1));
+      std::vector<PackedWeight> pk(n), pv(n);
+      std::vector<TcGroupDesc> g1(n), g2(n);
+      // every head's K (as a transposed weight, [kv, d]) and V ([kv, d]) into the tile layout: one launch each
+      const int64_t kKp = round_up(2 * D, 128), kNp = round_up(KV, 128), vKp = round_up(2 * KV, 128), vNp = round_up(D, 128);
+      const size_t k_bytes = (size_t)kKp * kNp, v_bytes = (size_t)vKp * vNp;
+      uint8_t *kpack = (uint8_t *)R.ws.alloc(k_bytes * n), *vpack = (uint8_t *)R.ws.alloc(v_bytes * n);
+      B2_CHECK(kpack && vpack, B200DNN_FAILURE, "workspace allocation failed");
+      for (int z0 = 0; z0 < n; z0 += 32768) {          // (the grid's third dimension ends at 65535)
+        const int nz = n - z0 < 32768 ? n - z0 : 32768;
+        pack_weight_bf16_batched_kernel<<<dim3((unsigned)(kKp / 128), (unsigned)(kNp / 32), (unsigned)nz), 256, 0, st>>>(
+            (const uint16_t *)k, d->k_stride[0], d->k_stride[1], (int)H, (int)(g0 + z0), d->k_stride[2], 1, D, KV, kKp, kpack + k_bytes * z0, k_bytes);
+        pack_weight_bf16_batched_kernel<<<dim3((unsigned)(vKp / 128), (unsigned)(vNp / 32), (unsigned)nz), 256, 0, st>>>(
+            (const uint16_t *)v, d->v_stride[0], d->v_stride[1], (int)H, (int)(g0 + z0), d->v_stride[2], 0, KV, D, vKp, vpack + v_bytes * z0, v_bytes);
+        B2_LAUNCHED(); B2_LAUNCHED();
+      }
+      B2_CUDA(cudaGetLastError());
+      for (int g = 0; g < n; ++g) {
+        const int64_t b = (g0 + g) / H, h = (g0 + g) % H;
+        tabs[g + 1] = (int32_t)((g + 1) * S);
+        tabs[n + 1 + g + 1] = tabs[n + 1 + g] + (int32_t)((S + tile_rows - 1) / tile_rows);
+        pk[g].wt = (const int8_t *)(kpack + k_bytes * g); pk[g].K = D; pk[g].N = KV; pk[g].Kp = kKp; pk[g].Np = kNp;
+        pv[g].wt = (const int8_t *)(vpack + v_bytes * g); pv[g].K = KV; pv[g].N = D; pv[g].Kp = vKp; pv[g].Np = vNp;
+        g1[g] = TcGroupDesc{nullptr, nullptr, nullptr, Sbuf + (size_t)g * S * KV, KV};
+        g2[g] = TcGroupDesc{nullptr, nullptr, nullptr, (uint16_t *)o_out.dev + b * d->o_stride[0] + h * d->o_stride[1], d->o_stride[2]};
+      }
+      void *tabs_dev, *g1_dev, *g2_dev;
+      B2_TRY(upload_blob(tabs.data(), tabs.size() * 4, st, &tabs_dev));
+      B2_TRY(upload_blob(g1.data(), sizeof(TcGroupDesc) * n, st, &g1_dev));
+      B2_TRY(upload_blob(g2.data(), sizeof(TcGroupDesc) * n, st, &g2_dev));
+      const int32_t *row_off = (const int32_t *)tabs_dev, *tile_prefix = row_off + n + 1;
+      const uint16_t *q0 = (const uint16_t *)q + (g0 / H) * d->q_stride[0] + (g0 % H) * d->q_stride[1];
+      EpiParams e1{};
+      e1.ldc = KV; e1.dst_dt = B200DNN_F32;
+      B2_TRY(grouped_gemm((const uint8_t *)q0, d->q_stride[2] * 2, (int)(n * S), (int)KV, (int)(2 * D), pk, row_off, tile_prefix, (const TcGroupDesc *)g1_dev,
+                          tabs[2 * n + 1], e1, false, st, tile_rows, true));
+      SoftmaxArgs sa{};
+      sa.S = Sbuf; sa.lds = KV; sa.P = Pbuf; sa.ldp = kvp; sa.seq = (int)S; sa.kv = (int)KV; sa.scale = scale; sa.causal = d->is_causal ? 1 : 0;
+      sa.mask = mk; sa.mask_dt = d->mask_dt; sa.mb = mb; sa.mh = mh; sa.mi = mi; sa.heads = (int)H; sa.head0 = (int)g0;
+      sdpa_softmax_kernel<<<(unsigned)(n * S), 256, 0, st>>>(sa);
+      B2_LAUNCHED();
+      B2_CUDA(cudaGetLastError());
+      EpiParams e2{};
+      e2.ldc = D; e2.dst_dt = d->out_dt;
+      B2_TRY(grouped_gemm((const uint8_t *)Pbuf, kvp * 2, (int)(n * S), (int)D, (int)(2 * KV), pv, row_off, tile_prefix, (const TcGroupDesc *)g2_dev,
+                          tabs[2 * n + 1], e2, false, st, tile_rows, true));
+    }
+    return finish_out({&o_out}, st);
+  }
+
+  // ---- head by head (any strides)
   float *Sbuf = (float *)R.ws.alloc((size_t)S * KV * 4);
   uint16_t *Pbuf = (uint16_t *)R.ws.alloc((size_t)S * kvp * 2);
   B2_CHECK(Sbuf && Pbuf, B200DNN_FAILURE, "workspace allocation failed");
-  const float scale = d->scale == 0.0 ? 1.0f / std::sqrt((float)D) : (float)d->scale;
   const std::vector<size_t> mark = R.ws.mark();
   for (int64_t b = 0; b < B; ++b)
     for (int64_t h = 0; h < H; ++h) {
@@ -123,10 +199,7 @@ extern "C" int32_t b200dnn_sdpa(const b200dnn_sdpa_t *d, void *stream) {
       B2_TRY(matmul_bf16(&g, st));
       SoftmaxArgs sa{};
       sa.S = Sbuf; sa.lds = KV; sa.P = Pbuf; sa.ldp = kvp; sa.seq = (int)S; sa.kv = (int)KV; sa.scale = scale; sa.causal = d->is_causal ? 1 : 0;
-      if (mk) {
-        sa.mask = (const uint8_t *)mk + (size_t)((msz[0] > 1 ? b * mst[0] : 0) + (msz[1] > 1 ? h * mst[1] : 0)) * dt_size(d->mask_dt);
-        sa.mask_dt = d->mask_dt; sa.mask_row_stride = msz[2] > 1 ? mst[2] : 0;
-      }
+      sa.mask = mk; sa.mask_dt = d->mask_dt; sa.mb = mb; sa.mh = mh; sa.mi = mi; sa.heads = (int)H; sa.head0 = (int)(b * H + h);
       sdpa_softmax_kernel<<<(unsigned)S, 256, 0, st>>>(sa);
       B2_LAUNCHED();
       B2_CUDA(cudaGetLastError());

@@ -5,6 +5,7 @@
   python -m zendnn_b200.run_case gs <w4a8|s8> M K N --gs G [--copies C] [--reps R]
   python -m zendnn_b200.run_case bf16 M K N [--copies C] [--reps R] [--act gelu_tanh] [--bias]
   python -m zendnn_b200.run_case norm <rms|fused_add_rms|layer> ROWS COLS [--quant] [--no-output] [--reps R]
+  python -m zendnn_b200.run_case sdpa BATCH HEADS SEQ DIM [--causal] [--reps R]
 
 matmul: s8 per-token activations x s8 per-channel prepacked weight -> bf16; `--copies` distinct prepacked
 weights are used in turn (pick copies * K * N above the L2 size to keep the weight stream in HBM);
@@ -132,6 +133,38 @@ def _norm(args):
     elem = 2 + (0 if args.no_output else 2) + (4 if res is not None else 0) + (1 if args.quant else 0)
     print("norm %s rows %d cols %d%s%s: %.2f us per call, %.0f GB/s (%d bytes per element)" %
           (args.kind, R, N, " +quant" if args.quant else "", " no bf16 output" if args.no_output else "", us, R * N * elem / us / 1e3, elem))
+
+
+def _sdpa(args):
+    import ctypes as C
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    B, H, S, D = args.batch, args.heads, args.seq, args.dim
+    g = torch.Generator(device=dev).manual_seed(0)
+    q, k, v = (torch.randn(B, H, S, D, generator=g, device=dev).to(torch.bfloat16) for _ in range(3))
+    o = torch.empty_like(q)
+    d = capi.SdpaDesc()
+    d.batch, d.num_heads, d.seq_len, d.kv_seq_len, d.head_dim = B, H, S, S, D
+    for name in ("q_stride", "k_stride", "v_stride", "o_stride"):
+        setattr(d, name, (C.c_int64 * 4)(H * S * D, S * D, D, 1))
+    d.qkv_dt = d.out_dt = capi.DT["bf16"]
+    d.is_causal = int(args.causal)
+    d.query, d.key, d.value, d.output = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    for _ in range(2):
+        capi.check(capi.lib.b200dnn_sdpa(C.byref(d), st))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.reps):
+        capi.check(capi.lib.b200dnn_sdpa(C.byref(d), st))
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.reps
+    flops = 4.0 * B * H * S * S * D
+    print("sdpa B%d H%d S%d D%d%s: %.1f us per call, %.0f TFLOP/s of 4*B*H*S*S*D (BMM form: the scores pass through HBM)" %
+          (B, H, S, D, " causal" if args.causal else "", us, flops / us / 1e6))
 
 
 def _gs(args):
@@ -274,12 +307,16 @@ def main():
     nm.add_argument("--quant", action="store_true")
     nm.add_argument("--no-output", action="store_true", dest="no_output")
     nm.add_argument("--reps", type=int, default=5)
+    sd = sub.add_parser("sdpa")
+    sd.add_argument("batch", type=int); sd.add_argument("heads", type=int); sd.add_argument("seq", type=int); sd.add_argument("dim", type=int)
+    sd.add_argument("--causal", action="store_true")
+    sd.add_argument("--reps", type=int, default=3)
     e = sub.add_parser("moe")
     e.add_argument("config", choices=["c4", "c5"])
     e.add_argument("--reps", type=int, default=3)
     e.add_argument("--wdt", choices=["s8", "bf16"], default="s8", help="expert weights: s8 (dynamic INT8) or bf16 (no quantisation)")
     args = ap.parse_args()
-    {"matmul": _matmul, "moe": _moe, "gs": _gs, "bf16": _bf16, "norm": _norm}[args.what](args)
+    {"matmul": _matmul, "moe": _moe, "gs": _gs, "bf16": _bf16, "norm": _norm, "sdpa": _sdpa}[args.what](args)
 
 
 if __name__ == "__main__":
