@@ -856,6 +856,24 @@ def run_single_gpu_extras(torch, capi, dev, peaks, int8_peak):
         "rms_norm_s8_output_only": norm_case("rms_norm", True, False)}
     del xs, rs, y, q, sc
     torch.cuda.synchronize()
+
+    # ---- attention beside the block (BMM form on the bf16 kernels: the scores pass through HBM)
+    Bs, Hs, Ss, Ds = 1, 32, 2048, 128
+    qkv = [torch.randn(Bs, Hs, Ss, Ds, generator=gd, device=dev).to(torch.bfloat16) for _ in range(3)]
+    oa = torch.empty_like(qkv[0])
+    sd = capi.SdpaDesc()
+    sd.batch, sd.num_heads, sd.seq_len, sd.kv_seq_len, sd.head_dim = Bs, Hs, Ss, Ss, Ds
+    for name in ("q_stride", "k_stride", "v_stride", "o_stride"):
+        setattr(sd, name, (C.c_int64 * 4)(Hs * Ss * Ds, Ss * Ds, Ds, 1))
+    sd.qkv_dt = sd.out_dt = bf
+    sd.is_causal = 1
+    sd.query, sd.key, sd.value, sd.output = qkv[0].data_ptr(), qkv[1].data_ptr(), qkv[2].data_ptr(), oa.data_ptr()
+    ms = _time_events(torch, lambda: capi.check(capi.lib.b200dnn_sdpa(C.byref(sd), st)), 5)
+    tf = 4.0 * Bs * Hs * Ss * Ss * Ds / ms / 1e9
+    out["sdpa_bf16_H32_S2048_D128_causal"] = {"us": round(ms * 1e3, 1), "tflops_of_4BHSSD": round(tf, 1), "roofline": bf16_roof(tf),
+                                              "note": "BMM form (scores, softmax, P V as separate steps): bound by the scores' HBM round trip"}
+    del qkv, oa
+    torch.cuda.synchronize()
     capi.lib.b200dnn_clear_caches()
     torch.cuda.empty_cache()
     return out
