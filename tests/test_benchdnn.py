@@ -20,6 +20,7 @@ def test_parse_defaults_comments_and_pipeline():
     c = B.parse_line("16, 128, 64:32, 5, u8:s8:bf16")
     assert c["n"] == [64, 32] and c["is_weights_const"] and not c["bias"] and c["wgran"] == "per-channel"
     assert c["alpha"] == 1.0 and c["beta"] == 0.0 and not c["dyn"]
+    assert B.parse_line("16, 128, 64, 5, u8:s8:bf16   # a trailing comment")["n"] == [64]
     with pytest.raises(ValueError):
         B.parse_line("16, 128")
     with pytest.raises(ValueError):

@@ -68,7 +68,7 @@ def _gran(s, default):
 
 def parse_line(line):
     """One input-file line -> config dict, or None for comments / blank lines.  Raises ValueError on a malformed line."""
-    text = line.split("#", 1)[0].strip() if line.lstrip().startswith("#") else line.strip()
+    text = line.split("#", 1)[0].strip()          # whole-line and trailing comments
     if not text:
         return None
     parts = [p.strip() for p in text.split(",")]
@@ -398,7 +398,7 @@ REORDER_HEADER = ("batch, rows, cols, iters, src_dtype, dst_dtype, algo, scale_g
 def parse_reorder_line(line):
     if not line.strip() or line.lstrip().startswith("#"):
         return None
-    parts = [p.strip() for p in line.strip().split(",")]
+    parts = [p.strip() for p in line.split("#", 1)[0].strip().split(",")]
     if len(parts) < 10:
         raise ValueError("expected batch, rows, cols, iters, src, dst, algo, granularity, group_size, dynamic_quant: %r" % line)
     parts += [""] * (12 - len(parts))
