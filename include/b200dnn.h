@@ -155,6 +155,14 @@ B200DNN_API size_t b200dnn_prepack_size(int64_t K, int64_t N, int32_t gated);
  * writes the packed weight (K-major rows padded for TMA, column sums appended) into dst. */
 B200DNN_API int32_t b200dnn_prepack(const void *weight, int64_t K, int64_t N, int64_t ldb, int32_t transB,
                         int32_t gated, void *dst, void *stream);
+/* The two reorder_direct calls that prepare an INT8 weight from a float one, as one call: per-channel dynamic
+ * quantisation (reorder/lowoha_reorder.cpp:186, scale dims {1,N}) and the prepack reorder
+ * (reorder/prepack/lowoha_prepack.cpp:315).  weight [K,N] (or [N,K] with transB) in bf16|f32 -> dst in the layout
+ * b200dnn_prepack writes (b200dnn_prepack_bytes(K,N) bytes) and N f32 scales, indexed by the caller's column.  The
+ * bytes and the scales are those of b200dnn_quant_dynamic followed by b200dnn_prepack; the s8 matrix in the caller's
+ * layout is never written. */
+B200DNN_API int32_t b200dnn_quant_prepack(const void *weight, int32_t wei_dt, int64_t K, int64_t N, int64_t ldb,
+                        int32_t transB, int32_t gated, void *dst, float *scale, void *stream);
 
 /* reorder_direct, dynamic per-token symmetric quantisation (reorder/lowoha_reorder.cpp:119-136):
  * src [M,K] f32|bf16 with row stride src_ld -> dst s8 [M,K] (row stride dst_ld; dst may be NULL:

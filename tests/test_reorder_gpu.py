@@ -217,3 +217,68 @@ def test_prepack_gated_interleave(capi):
     # packed rows: g[0:32] u[0:32] g[32:64] u[32:64]
     exp = np.concatenate([W[:, 0:32], W[:, I:I + 32], W[:, 32:64], W[:, I + 32:I + 64]], axis=1).T
     assert (wt == exp).all()
+
+
+@pytest.mark.parametrize("gated", [0, 1, 2])
+@pytest.mark.parametrize("transB", [False, True])
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("K,N", [(64, 64), (300, 192), (1024, 4096)])
+def test_quant_prepack_one_call(capi, oracle, K, N, dt, transB, gated):
+    """Float weight -> per-channel s8 -> packed layout in one call: the scales are the oracle's, and the packed buffer is
+    byte for byte the one that per-channel quantisation followed by the prepack writes."""
+    rng = np.random.default_rng(K * 3 + N + gated)
+    wf = (rng.normal(size=(K, N)) * rng.uniform(0.005, 0.05, size=(1, N))).astype(np.float32)
+    wf[:, 3] = 0.0                                   # an all-zero channel
+    w = oracle.f32_to_bf16(wf) if dt == "bf16" else wf
+    q_ref, s_ref = oracle.quant_weights_per_channel(w)
+    src = np.ascontiguousarray(w.T) if transB else w
+    ldb = K if transB else N
+    size = capi.lib.b200dnn_prepack_size(K, N, gated)
+    one = np.zeros(size, dtype=np.uint8)
+    s = np.zeros(N, dtype=np.float32)
+    st = capi.lib.b200dnn_quant_prepack(capi.ptr(src), capi.DT[dt], K, N, ldb, int(transB), gated, capi.ptr(one), capi.ptr(s), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert (s == s_ref).all()
+    # the two calls it replaces
+    q = np.zeros((K, N), dtype=np.int8); s2 = np.zeros(N, dtype=np.float32)
+    st = capi.lib.b200dnn_quant_dynamic(capi.ptr(w), capi.DT[dt], K, N, N, 1, capi.ptr(q), N, capi.ptr(s2), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert (q == q_ref).all()
+    two = np.zeros(size, dtype=np.uint8)
+    assert capi.lib.b200dnn_prepack(capi.ptr(q), K, N, N, 0, gated, capi.ptr(two), None) == capi.SUCCESS, capi.last_error()
+    Np = -(-N // 128) * 128
+    assert (one[:256] == two[:256]).all(), "header"
+    assert (one[256:256 + 4 * Np] == two[256:256 + 4 * Np]).all(), "column sums"
+    assert (one == two).all(), int((one != two).sum())
+
+
+def test_quant_prepack_feeds_matmul(capi, oracle):
+    """The buffer of the one-call form is a prepacked weight: matmul_direct on it gives the oracle's bytes for the
+    quantised weight and its scales."""
+    rng = np.random.default_rng(77)
+    M, K, N = 48, 512, 384
+    w = oracle.f32_to_bf16((rng.normal(size=(K, N)) * 0.03).astype(np.float32))
+    q_ref, s_ref = oracle.quant_weights_per_channel(w)
+    packed = np.zeros(capi.lib.b200dnn_prepack_size(K, N, 0), dtype=np.uint8)
+    sw = np.zeros(N, dtype=np.float32)
+    st = capi.lib.b200dnn_quant_prepack(capi.ptr(w), capi.DT["bf16"], K, N, N, 0, 0, capi.ptr(packed), capi.ptr(sw), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    A = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    sa = rng.uniform(0.01, 0.05, M).astype(np.float32)
+    dst = np.zeros((M, N), dtype=np.uint16)
+    d = capi.make_matmul(M, N, K, A, packed, dst, src_dt=capi.DT["s8"], dst_dt=capi.DT["bf16"], wei_format="r",
+                         src_scale=sa, wei_scale=sw)
+    assert capi.matmul(d) == capi.SUCCESS, capi.last_error()
+    ref = oracle.matmul_w8a8(A, q_ref, "bf16", src_scale=sa, wei_scale=s_ref)
+    assert (dst == ref).all()
+
+
+def test_quant_prepack_contract(capi):
+    w = np.zeros((64, 64), dtype=np.float32)
+    buf = np.zeros(capi.lib.b200dnn_prepack_size(64, 64, 0), dtype=np.uint8)
+    s = np.zeros(64, dtype=np.float32)
+    f = capi.lib.b200dnn_quant_prepack
+    assert f(None, capi.DT["f32"], 64, 64, 64, 0, 0, capi.ptr(buf), capi.ptr(s), None) == capi.FAILURE
+    assert f(capi.ptr(w), capi.DT["f32"], 64, 64, 32, 0, 0, capi.ptr(buf), capi.ptr(s), None) == capi.FAILURE
+    assert f(capi.ptr(w), capi.DT["s8"], 64, 64, 64, 0, 0, capi.ptr(buf), capi.ptr(s), None) == capi.UNIMPLEMENTED
+    assert f(capi.ptr(w), capi.DT["f32"], 64, 48, 64, 0, 1, capi.ptr(buf), capi.ptr(s), None) == capi.UNIMPLEMENTED

@@ -88,7 +88,7 @@ PHASE_NAMES = ["route+rank", "count exchange", "quantise+dispatch", "barrier aft
 
 EXPORTS = ["b200dnn_last_error", "b200dnn_version", "b200dnn_device_count", "b200dnn_launch_count",
            "b200dnn_matmul", "b200dnn_matmul_static_scratch", "b200dnn_static_scratch_query", "b200dnn_prepack_size", "b200dnn_prepack", "b200dnn_quant_per_token",
-           "b200dnn_group_quant_per_token", "b200dnn_quant_per_token_asym", "b200dnn_quant_dynamic", "b200dnn_quant_static",
+           "b200dnn_group_quant_per_token", "b200dnn_quant_per_token_asym", "b200dnn_quant_dynamic", "b200dnn_quant_prepack", "b200dnn_quant_static",
            "b200dnn_dequant_static", "b200dnn_gated_act", "b200dnn_moe_weighted_reduce", "b200dnn_fused_moe", "b200dnn_group_matmul", "b200dnn_nshard_range", "b200dnn_nshard_create", "b200dnn_nshard_destroy", "b200dnn_matmul_nshard",
            "b200dnn_moe_route", "b200dnn_moe_layer", "b200dnn_clear_caches", "b200dnn_stream_status", "b200dnn_moe_sort_slots",
            "b200dnn_quant_per_token_gather", "b200dnn_quant_per_token_scatter", "b200dnn_moe_experts_s8",
@@ -112,6 +112,7 @@ lib.b200dnn_matmul.argtypes = [C.POINTER(MatmulDesc), vp]
 lib.b200dnn_matmul_static_scratch.argtypes = [C.POINTER(MatmulDesc), vp]
 lib.b200dnn_static_scratch_query.argtypes = [i32, i32, i32, i32, C.POINTER(C.c_size_t)]
 lib.b200dnn_prepack.argtypes = [vp, i64, i64, i64, i32, i32, vp, vp]
+lib.b200dnn_quant_prepack.argtypes = [vp, i32, i64, i64, i64, i32, i32, vp, vp, vp]
 lib.b200dnn_quant_per_token.argtypes = [vp, i32, i64, i64, i64, vp, i64, vp, i32, vp]
 lib.b200dnn_group_quant_per_token.argtypes = [i32, vp, i32, vp, vp, vp, vp, vp, vp, i32, vp]
 lib.b200dnn_quant_dynamic.argtypes = [vp, i32, i64, i64, i64, i32, vp, i64, vp, vp]

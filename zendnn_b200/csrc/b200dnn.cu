@@ -52,7 +52,7 @@ int32_t pack_into(const void *w_dev, int64_t K, int64_t N, int64_t ldb, int tran
   B2_CHECK((reinterpret_cast<uintptr_t>(base) & 255) == 0, B200DNN_FAILURE, "prepack destination must be 256-byte aligned");
   int32_t *colsum = reinterpret_cast<int32_t *>(base + kPackHeaderBytes);
   int8_t *wt = reinterpret_cast<int8_t *>(base + kPackHeaderBytes + Np * 4);
-  pack_header_kernel<<<1, 1, 0, st>>>(reinterpret_cast<PackHeader *>(base), K, N, Kp, Np, gated, I);
+  pack_header_kernel<<<1, kPackHeaderBytes / 4, 0, st>>>(reinterpret_cast<PackHeader *>(base), K, N, Kp, Np, gated, I);
   B2_LAUNCHED();
   dim3 grid((unsigned)(Kp / 64), (unsigned)(Np / 32));
   pack_weight_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const int8_t *>(w_dev), ldb, transB, K, N, Kp, gated, I, wt);
@@ -1183,3 +1183,4 @@ int32_t b200dnn_clear_caches(void) {
 #include "nshard_api.cuh"
 #include "norm_api.cuh"
 #include "sdpa_api.cuh"
+#include "quant_prepack_api.cuh"

@@ -156,7 +156,12 @@ static __global__ void __launch_bounds__(256) pack_colsum_kernel(const int8_t *W
   if (lane == 0) colsum[row] = s;
 }
 
+// block of kPackHeaderBytes/4 threads: the bytes of the header block that carry no field are written as zero, so that a
+// packed buffer is a function of the weight alone
 static __global__ void pack_header_kernel(PackHeader *h, int64_t K, int64_t N, int64_t Kp, int64_t Np, int gated, int64_t I) {
+  reinterpret_cast<uint32_t *>(h)[threadIdx.x] = 0u;
+  __syncthreads();
+  if (threadIdx.x != 0) return;
   h->magic = kPackMagic; h->version = 1; h->K = K; h->N = N; h->Kp = Kp; h->Np = Np; h->gated = gated; h->I = (int32_t)I;
 }
 
