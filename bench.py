@@ -874,6 +874,33 @@ def run_single_gpu_extras(torch, capi, dev, peaks, int8_peak):
                                               "note": "BMM form (scores, softmax, P V as separate steps): bound by the scores' HBM round trip"}
     del qkv, oa
     torch.cuda.synchronize()
+
+    # ---- weight preparation at load time: bf16 checkpoint weight -> per-channel s8 in the packed layout
+    Kw, Nw = 4096, 14336
+    ws = [(torch.randn(Kw, Nw, generator=gd, device=dev) * 0.02).to(torch.bfloat16) for _ in range(2)]
+    pk = torch.empty(capi.lib.b200dnn_prepack_size(Kw, Nw, 0), dtype=torch.uint8, device=dev)
+    q8 = torch.empty(Kw, Nw, dtype=torch.int8, device=dev)
+    sw = torch.empty(Nw, dtype=torch.float32, device=dev)
+    it = [0]
+
+    def one_call():
+        w = ws[it[0] % 2]; it[0] += 1
+        capi.check(capi.lib.b200dnn_quant_prepack(w.data_ptr(), bf, Kw, Nw, Nw, 0, 0, pk.data_ptr(), sw.data_ptr(), st))
+
+    def two_calls():
+        w = ws[it[0] % 2]; it[0] += 1
+        capi.check(capi.lib.b200dnn_quant_dynamic(w.data_ptr(), bf, Kw, Nw, Nw, 1, q8.data_ptr(), Nw, sw.data_ptr(), st))
+        capi.check(capi.lib.b200dnn_prepack(q8.data_ptr(), Kw, Nw, Nw, 0, 0, pk.data_ptr(), st))
+    ms1 = _time_events(torch, one_call, 10, warm=3)
+    ms2 = _time_events(torch, two_calls, 10, warm=3)
+    gbs = Kw * Nw * 5 / ms1 / 1e6                          # the weight read twice (column maxima, then pack) + the s8 written
+    out["weight_quant_prepack_K4096_N14336_bf16"] = {
+        "one_call_us": round(ms1 * 1e3, 1), "quant_dynamic_then_prepack_us": round(ms2 * 1e3, 1), "bytes_per_element": 5,
+        "gbs": round(gbs, 1),
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": round(hbm, 1), "unit": "GB/s", "frac": round(gbs / hbm, 4),
+                     "peak_source": peaks["src"]}}
+    del ws, pk, q8, sw
+    torch.cuda.synchronize()
     capi.lib.b200dnn_clear_caches()
     torch.cuda.empty_cache()
     return out
