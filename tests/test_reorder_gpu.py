@@ -252,6 +252,29 @@ def test_quant_prepack_one_call(capi, oracle, K, N, dt, transB, gated):
     assert (one == two).all(), int((one != two).sum())
 
 
+@pytest.mark.parametrize("transB", [False, True])
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("K,N,pad", [(130, 100, 0), (70, 13, 0), (96, 40, 3)])
+def test_quant_prepack_ragged(capi, oracle, K, N, pad, dt, transB):
+    """Shapes that are no multiple of the tile or of a 16-byte load, and a padded leading dimension."""
+    rng = np.random.default_rng(K + N)
+    wf = (rng.normal(size=(K, N)) * 0.02).astype(np.float32)
+    w = oracle.f32_to_bf16(wf) if dt == "bf16" else wf
+    q_ref, s_ref = oracle.quant_weights_per_channel(w)
+    lay = np.ascontiguousarray(w.T) if transB else w
+    ldb = lay.shape[1] + pad
+    src = np.zeros((lay.shape[0], ldb), dtype=lay.dtype)
+    src[:, :lay.shape[1]] = lay
+    size = capi.lib.b200dnn_prepack_size(K, N, 0)
+    one = np.zeros(size, dtype=np.uint8); two = np.zeros(size, dtype=np.uint8)
+    s = np.zeros(N, dtype=np.float32)
+    st = capi.lib.b200dnn_quant_prepack(capi.ptr(src), capi.DT[dt], K, N, ldb, int(transB), 0, capi.ptr(one), capi.ptr(s), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert (s == s_ref).all()
+    assert capi.lib.b200dnn_prepack(capi.ptr(q_ref), K, N, N, 0, 0, capi.ptr(two), None) == capi.SUCCESS, capi.last_error()
+    assert (one == two).all(), int((one != two).sum())
+
+
 def test_quant_prepack_feeds_matmul(capi, oracle):
     """The buffer of the one-call form is a prepacked weight: matmul_direct on it gives the oracle's bytes for the
     quantised weight and its scales."""

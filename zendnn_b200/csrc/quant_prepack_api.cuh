@@ -24,17 +24,46 @@ __global__ void __launch_bounds__(256) absmax_rows_kernel(const T *src, int64_t 
   if (lane == 0) out[r] = __float_as_uint(amax);
 }
 
+// abs-max of every column of a [rows, cols] matrix with 16-byte loads: a thread owns 16/sizeof(T) neighbouring columns
+// over the rows of its blockIdx.y slice, so a warp reads 512 contiguous bytes of each row.  The caller checks that the
+// base is 16-byte aligned and that cols and ld are multiples of 16/sizeof(T).  out must be zero before the launch.
+template <typename T>
+__global__ void __launch_bounds__(256) absmax_cols_vec_kernel(const T *src, int64_t rows, int64_t cols, int64_t ld, uint32_t *out) {
+  constexpr int E = 16 / (int)sizeof(T);
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g * E >= cols) return;
+  const int64_t rows_per = (rows + gridDim.y - 1) / gridDim.y;
+  const int64_t m0 = (int64_t)blockIdx.y * rows_per, m1 = min(rows, m0 + rows_per);
+  float amax[E];
+#pragma unroll
+  for (int i = 0; i < E; ++i) amax[i] = 0.f;
+#pragma unroll 4
+  for (int64_t m = m0; m < m1; ++m) {
+    const uint4 v = *reinterpret_cast<const uint4 *>(src + m * ld + g * E);
+    const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float f = elem_to_f32<T>(e[i]);
+      if (finite_f32(f)) amax[i] = fmaxf(amax[i], fabsf(f));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < E; ++i) atomicMax(out + g * E + i, __float_as_uint(amax[i]));
+}
+
 __device__ __forceinline__ int8_t quant_channel(float v, float s) {
   const int q = __float2int_rn(__fdiv_rn(v, s));
   return (int8_t)max(-128, min(127, q));
 }
 
-// pack_weight_kernel with the quantisation in its load: grid (Kp/64, Np/32), block 256, a [64 k][32 n] tile per CTA
+// pack_weight_kernel with the quantisation in its load: grid (Np/32, Kp/64), block 256, a [64 k][32 n] tile per CTA.
+// Tiles that neighbour along n are neighbours in launch order: for the [K,N] form they read adjacent runs of the same
+// rows of the weight.
 template <typename T>
 __global__ void __launch_bounds__(256) pack_quant_weight_kernel(const T *W, int64_t ldb, int transB, int64_t K, int64_t N, int64_t Kp,
                                                                 int gated, int64_t I, const float *scale, int8_t *Wt) {
   __shared__ int8_t tile[32][64 + 4];
-  const int64_t k0 = (int64_t)blockIdx.x * 64, pn0 = (int64_t)blockIdx.y * 32;
+  const int64_t k0 = (int64_t)blockIdx.y * 64, pn0 = (int64_t)blockIdx.x * 32;
   const int64_t n0 = packed_to_logical(pn0, gated, I);
   const int64_t nstep = gated == 2 ? 2 : 1;
   const int tid = threadIdx.x;
@@ -75,8 +104,15 @@ int32_t quant_pack_launch(const T *w, int64_t K, int64_t N, int64_t ldb, int tra
     absmax_rows_kernel<T><<<(unsigned)((N + 7) / 8), 256, 0, st>>>(w, N, K, ldb, amax);
   } else {
     B2_CUDA(cudaMemsetAsync(amax, 0, (size_t)N * 4, st));
-    dim3 grid((unsigned)((N + 255) / 256), (unsigned)(K < 64 ? 1 : (K / 64 > 256 ? 256 : K / 64)));
-    absmax_cols_kernel<T><<<grid, 256, 0, st>>>(w, K, N, ldb, 1, amax);
+    constexpr int E = 16 / (int)sizeof(T);
+    const unsigned slices = (unsigned)(K < 64 ? 1 : (K / 64 > 256 ? 256 : K / 64));
+    if ((reinterpret_cast<uintptr_t>(w) & 15) == 0 && N % E == 0 && ldb % E == 0) {
+      dim3 grid((unsigned)((N / E + 255) / 256), slices);
+      absmax_cols_vec_kernel<T><<<grid, 256, 0, st>>>(w, K, N, ldb, amax);
+    } else {
+      dim3 grid((unsigned)((N + 255) / 256), slices);
+      absmax_cols_kernel<T><<<grid, 256, 0, st>>>(w, K, N, ldb, 1, amax);
+    }
   }
   B2_LAUNCHED();
   scales_from_absmax_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(amax, N, scale_dev);
@@ -85,7 +121,8 @@ int32_t quant_pack_launch(const T *w, int64_t K, int64_t N, int64_t ldb, int tra
   int8_t *wt = reinterpret_cast<int8_t *>(base + kPackHeaderBytes + Np * 4);
   pack_header_kernel<<<1, kPackHeaderBytes / 4, 0, st>>>(reinterpret_cast<PackHeader *>(base), K, N, Kp, Np, gated, I);
   B2_LAUNCHED();
-  dim3 pgrid((unsigned)(Kp / 64), (unsigned)(Np / 32));
+  B2_CHECK(Kp / 64 <= 65535, B200DNN_UNIMPLEMENTED, "quant_prepack: K=%lld is too large", (long long)K);
+  dim3 pgrid((unsigned)(Np / 32), (unsigned)(Kp / 64));
   pack_quant_weight_kernel<T><<<pgrid, 256, 0, st>>>(w, ldb, transB, K, N, Kp, gated, I, scale_dev, wt);
   B2_LAUNCHED();
   pack_colsum_kernel<<<(unsigned)((Np + 7) / 8), 256, 0, st>>>(wt, Np, Kp, colsum);
