@@ -1,6 +1,6 @@
 """Generates tests/golden/int8_ref_cases.npz from the REFERENCE's own INT8 tile kernel.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run in a container that has the reference checkout (its location: the ZENDNN_REFERENCE_ROOT variable):
     python tests/golden/make_golden.py
 It builds oracle/_ref/libzendnn_ref.so from the reference sources (oracle/Makefile), runs the
 reference kernel (u8 x s8 -> s32, per-tensor source scale and zero-point, per-tensor or

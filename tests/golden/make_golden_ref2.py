@@ -2,7 +2,7 @@
 quantisation kernels, the gated activations (AVX-512 and scalar paths), the MoE weighted reduce, the per-channel /
 per-tensor dynamic scales and the static quantise / dequantise.
 
-Run in a container that has the reference checkout (default /root/reference) and AVX-512:
+Run in a container that has the reference checkout (its location: the ZENDNN_REFERENCE_ROOT variable) and AVX-512:
     python tests/golden/make_golden_ref2.py
 It builds oracle/_ref/libzendnn_ref2.so from the reference sources (oracle/Makefile, oracle/ref_driver2.cpp),
 runs the reference functions on seeded inputs and stores inputs and outputs.  The scalar paths are produced by
