@@ -275,6 +275,27 @@ def test_quant_prepack_ragged(capi, oracle, K, N, pad, dt, transB):
     assert (one == two).all(), int((one != two).sum())
 
 
+@pytest.mark.parametrize("transB", [False, True])
+def test_quant_prepack_non_finite(capi, transB):
+    """inf and nan in the weight: ignored by the channel maxima, and coded as the two separate calls code them."""
+    rng = np.random.default_rng(9)
+    K, N = 192, 128
+    w = (rng.normal(size=(K, N)) * 0.02).astype(np.float32)
+    w[3, 5], w[100, 5], w[7, 64], w[191, 127] = np.inf, -np.inf, np.nan, np.inf
+    src = np.ascontiguousarray(w.T) if transB else w
+    size = capi.lib.b200dnn_prepack_size(K, N, 0)
+    one = np.zeros(size, dtype=np.uint8); two = np.zeros(size, dtype=np.uint8)
+    s1 = np.zeros(N, dtype=np.float32); s2 = np.zeros(N, dtype=np.float32)
+    st = capi.lib.b200dnn_quant_prepack(capi.ptr(src), capi.DT["f32"], K, N, K if transB else N, int(transB), 0, capi.ptr(one), capi.ptr(s1), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    q = np.zeros((K, N), dtype=np.int8)
+    st = capi.lib.b200dnn_quant_dynamic(capi.ptr(w), capi.DT["f32"], K, N, N, 1, capi.ptr(q), N, capi.ptr(s2), None)
+    assert st == capi.SUCCESS, capi.last_error()
+    assert capi.lib.b200dnn_prepack(capi.ptr(q), K, N, N, 0, 0, capi.ptr(two), None) == capi.SUCCESS, capi.last_error()
+    assert np.isfinite(s1).all() and (s1 == s2).all()
+    assert (one == two).all(), int((one != two).sum())
+
+
 def test_quant_prepack_feeds_matmul(capi, oracle):
     """The buffer of the one-call form is a prepacked weight: matmul_direct on it gives the oracle's bytes for the
     quantised weight and its scales."""

@@ -56,6 +56,16 @@ __device__ __forceinline__ int8_t quant_channel(float v, float s) {
   return (int8_t)max(-128, min(127, q));
 }
 
+// The same code without a division in the common case (the argument of quant_sym_r: the scale comes from the abs-max of
+// the channel itself, so every finite |v/s| <= 127 up to rounding, and away from a near-tie v*rinv rounds to the integer
+// the rounded quotient rounds to).  Near-ties and non-finite inputs take the division.
+__device__ __forceinline__ int8_t quant_channel_r(float v, float s, float rinv) {
+  const float magic = 12582912.0f;
+  const float qa = v * rinv, m = qa + magic, t = m - magic;
+  if (fabsf(qa - t) < 0.4999f) return (int8_t)(__float_as_int(m) & 0xFF);
+  return quant_channel(v, s);
+}
+
 // pack_weight_kernel with the quantisation in its load: grid (Np/32, Kp/64), block 256, a [64 k][32 n] tile per CTA.
 // Tiles that neighbour along n are neighbours in launch order: for the [K,N] form they read adjacent runs of the same
 // rows of the weight.
@@ -67,21 +77,29 @@ __global__ void __launch_bounds__(256) pack_quant_weight_kernel(const T *W, int6
   const int64_t n0 = packed_to_logical(pn0, gated, I);
   const int64_t nstep = gated == 2 ? 2 : 1;
   const int tid = threadIdx.x;
+  __shared__ float s_scale[32], s_rinv[32];
+  if (tid < 32) {
+    const float sc = pn0 + tid < N ? scale[n0 + tid * nstep] : 1.f;
+    s_scale[tid] = sc; s_rinv[tid] = __frcp_rn(sc);
+  }
+  __syncthreads();
   if (!transB) {
     const int nn = tid & 31;                    // fixed per thread: 256 is a multiple of 32
     const int64_t n = n0 + nn * nstep;
     const bool n_ok = pn0 + nn < N;
-    const float s = n_ok ? scale[n] : 1.f;
+    const float sc = s_scale[nn], rinv = s_rinv[nn];
+#pragma unroll
     for (int kk = tid >> 5; kk < 64; kk += 8) {
       const int64_t k = k0 + kk;
-      tile[nn][kk] = (k < K && n_ok) ? quant_channel(elem_to_f32<T>(W[k * ldb + n]), s) : (int8_t)0;
+      tile[nn][kk] = (k < K && n_ok) ? quant_channel_r(elem_to_f32<T>(W[k * ldb + n]), sc, rinv) : (int8_t)0;
     }
   } else {
     const int kk = tid & 63;
     const int64_t k = k0 + kk;
+#pragma unroll
     for (int nn = tid >> 6; nn < 32; nn += 4) {
       const int64_t n = n0 + nn * nstep;
-      tile[nn][kk] = (k < K && pn0 + nn < N) ? quant_channel(elem_to_f32<T>(W[n * ldb + k]), scale[n]) : (int8_t)0;
+      tile[nn][kk] = (k < K && pn0 + nn < N) ? quant_channel_r(elem_to_f32<T>(W[n * ldb + k]), s_scale[nn], s_rinv[nn]) : (int8_t)0;
     }
   }
   __syncthreads();

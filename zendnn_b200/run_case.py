@@ -276,6 +276,35 @@ def _moe(args):
     print("  gemm1 %.0f TOPS, gemm2 %.0f TOPS" % (2.0 * rows * H * 2 * I / buf[4] / 1e9, 2.0 * rows * I * H / buf[6] / 1e9))
 
 
+def _wprep(args):
+    """Weight preparation: a bf16 [K,N] weight to per-channel s8 in the packed layout, one call."""
+    import torch
+    from . import capi
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream().cuda_stream
+    K, N = args.K, args.N
+    g = torch.Generator(device=dev).manual_seed(0)
+    ws = [(torch.randn(K, N, generator=g, device=dev) * 0.02).to(torch.bfloat16) for _ in range(2)]
+    if args.transB:
+        ws = [w.t().contiguous() for w in ws]
+    pk = torch.empty(capi.lib.b200dnn_prepack_size(K, N, 0), dtype=torch.uint8, device=dev)
+    sw = torch.empty(N, dtype=torch.float32, device=dev)
+
+    def call(i):
+        capi.check(capi.lib.b200dnn_quant_prepack(ws[i % 2].data_ptr(), capi.DT["bf16"], K, N, K if args.transB else N,
+                                                  int(args.transB), 0, pk.data_ptr(), sw.data_ptr(), st))
+    call(0)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.reps):
+        call(i + 1)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.reps
+    print("wprep K%d N%d transB=%d: %.1f us per call, %.0f GB/s of 5 bytes per element" % (K, N, int(args.transB), us, 5.0 * K * N / us / 1e3))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -315,8 +344,12 @@ def main():
     e.add_argument("config", choices=["c4", "c5"])
     e.add_argument("--reps", type=int, default=3)
     e.add_argument("--wdt", choices=["s8", "bf16"], default="s8", help="expert weights: s8 (dynamic INT8) or bf16 (no quantisation)")
+    wp = sub.add_parser("wprep")
+    wp.add_argument("K", type=int); wp.add_argument("N", type=int)
+    wp.add_argument("--transB", action="store_true")
+    wp.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()
-    {"matmul": _matmul, "moe": _moe, "gs": _gs, "bf16": _bf16, "norm": _norm, "sdpa": _sdpa}[args.what](args)
+    {"wprep": _wprep, "matmul": _matmul, "moe": _moe, "gs": _gs, "bf16": _bf16, "norm": _norm, "sdpa": _sdpa}[args.what](args)
 
 
 if __name__ == "__main__":
